@@ -1,0 +1,381 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-linear hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--sweep]
+
+Headline workload (N = 1): the MLX-affine int4 g64 linears of Llama-3.2-3B at decode,
+M = 1 — one step streams all 28 layers x (q, k, v, o, gate, up, down) = 196 linears,
+1.585 GB of packed weights (far larger than the 126 MB L2, so every step reads HBM).
+`value` is algorithmic bytes per second (packed codes + scales + biases + activations in
+and out), i.e. the achieved weight-stream bandwidth the metric asks for at M = 1.
+`--sweep` adds TFLOP/s for M >= 64 and the fp8 path as extra keys.
+
+With N > 1 every rank runs the same workload on its own GPU (independent replicas, no
+data-path collective; weak scaling) and the tensor-parallel 70B-shaped fp8 stack is timed
+separately under the `tp` key.
+
+`--impl reference` times the reference project's CPU implementation of the same linears
+(its Rust cannot be built here, so this is the C++ restatement in oracle/) on the host
+cores; rank 0 only.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from scratchy_b200 import synth  # noqa: E402
+
+N_LAYERS = 28
+LAYER_ORDER = ["q", "k", "v", "o", "gate", "up", "down"]
+METRIC = "int4_g64_decode_linear_weight_stream"
+UNIT = "GB/s"
+
+
+def affine_alg_bytes(M, N, K):
+    """Algorithmic bytes of one int4 g64 linear: codes + bf16 scale/bias per group + x in + y out."""
+    return N * K // 2 + 2 * (N * K // 64) * 2 + M * K * 2 + M * N * 2
+
+
+def fp8_alg_bytes(M, N, K):
+    return N * K + 4 * N + 2 * M * K + 2 * M * N
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "src": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "src": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.p = None
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                       "-i", str(gpu_index), "-lms", "100"], stdout=self.f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.p = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.p is None:
+            return out
+        time.sleep(0.15)
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except Exception:
+            self.p.kill()
+        self.f.flush()
+        rows = [r.strip().split(", ") for r in open(self.f.name) if r.strip()]
+        os.unlink(self.f.name)
+        sm, mx, reasons = [], [], set()
+        for r in rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except Exception:
+                continue
+            names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+            for name, v in zip(names, r[5:9]):
+                if v.strip().lower().startswith("active"):
+                    reasons.add(name)
+        if sm:
+            out = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                   "samples": len(sm)}
+        return out
+
+
+# ------------------------------------------------------------------------------------ reference arm
+def cpu_linears(threads_note=True):
+    import oracle
+    shapes = [synth.LLAMA_3_2_3B[n] for n in LAYER_ORDER]
+    data = []
+    for i, (K, N) in enumerate(shapes):
+        w, s, b = synth.affine_int4_weights(N, K, 64, 100 + i)
+        x = synth.activations_bf16(1, K, 200 + i)
+        data.append((w.view(np.uint8).reshape(-1), s, b, x, N, K))
+    return oracle, data
+
+
+def time_cpu_layer(reps: int):
+    """One 'sample' = the 7 int4 linears of one Llama-3.2-3B layer at M = 1 through the oracle."""
+    oracle, data = cpu_linears()
+    byts = sum(affine_alg_bytes(1, N, K) for *_, N, K in data)
+    oracle.affine_qmm_t_b4(*data[1][:4], 1, data[1][4], data[1][5], 64)    # warm the thread pool
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        for pk, s, b, x, N, K in data:
+            oracle.affine_qmm_t_b4(pk, s, b, x, 1, N, K, 64)
+    dt = (time.perf_counter() - t0) / reps
+    return byts / dt / 1e9, dt, oracle.num_threads()
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    for _ in range(max(args.warmup, 1)):
+        time_cpu_layer(1)
+    vals = []
+    t_all = 0.0
+    for _ in range(args.steps):
+        v, dt, cores = time_cpu_layer(1)
+        vals.append(v)
+        t_all += dt
+    value = float(np.mean(vals))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * t_all / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "llama-3.2-3b int4 g64 linears (q,k,v,o,gate,up,down), M=1",
+                   "step": "one layer (7 linears) on the host cores: a bounded sample of the 28-layer GPU step"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": "7 linears of one layer per step, C++/OpenMP restatement of "
+                                   "cpu_reference::affine_qmm_t_b4 (the Rust reference cannot be built here)"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------ GPU arm
+def build_int4_model(device, n_layers):
+    import torch
+    from scratchy_b200 import AffineQuantLinear
+    layers = []
+    # one set of synthetic checkpoint tensors per shape, re-drawn per layer on the device
+    for li in range(n_layers):
+        row = []
+        for name in LAYER_ORDER:
+            K, N = synth.LLAMA_3_2_3B[name]
+            g = torch.Generator(device=device)
+            g.manual_seed(1000 * li + len(row))
+            w = torch.randint(-2 ** 31, 2 ** 31 - 1, (N, K // 8), dtype=torch.int32, device=device, generator=g)
+            s = (torch.randn((N, K // 64), device=device, generator=g) * 0.02).abs().add(1e-3).to(torch.bfloat16)
+            b = (-8.0 * s.float() + torch.randn((N, K // 64), device=device, generator=g) * 1e-3).to(torch.bfloat16)
+            row.append(AffineQuantLinear.from_tensors(w, s, b, 64, 4))
+        layers.append(row)
+    torch.cuda.synchronize(device)
+    return layers
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    from scratchy_b200 import _lib
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    ctx = _lib.context(local_rank)
+    peaks = measured_peaks()
+
+    M = 1
+    layers = build_int4_model(device, N_LAYERS)
+    shapes = [synth.LLAMA_3_2_3B[n] for n in LAYER_ORDER]
+    step_bytes = N_LAYERS * sum(affine_alg_bytes(M, N, K) for K, N in shapes)
+    xs = [torch.randn((M, K), device=device).to(torch.bfloat16) for K, _ in shapes]
+    ys = [torch.empty((M, N), dtype=torch.bfloat16, device=device) for _, N in shapes]
+
+    def step():
+        for row in layers:
+            for lin, x, y in zip(row, xs, ys):
+                lin.forward(x, out=y)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    # ---- device-resident timing
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    launches0 = ctx.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    barrier()
+    ms = ev0.elapsed_time(ev1)
+    launches = ctx.launch_count() - launches0
+    clocks = sampler.stop() if sampler else None
+
+    # ---- end to end: host (pinned) activations in, host results out, through the public API
+    hx = [torch.randn((M, K)).to(torch.bfloat16).pin_memory() for K, _ in shapes]
+    hy = [torch.empty((M, N), dtype=torch.bfloat16).pin_memory() for _, N in shapes]
+    h2d = N_LAYERS * sum(t.numel() * 2 for t in hx)
+    d2h = N_LAYERS * sum(t.numel() * 2 for t in hy)
+
+    def step_e2e():
+        for row in layers:
+            for lin, x, y, cx, cy in zip(row, xs, ys, hx, hy):
+                x.copy_(cx, non_blocking=True)
+                lin.forward(x, out=y)
+                cy.copy_(y, non_blocking=True)
+        torch.cuda.current_stream(device).synchronize()
+
+    for _ in range(max(1, args.warmup // 2)):
+        step_e2e()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step_e2e()
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1)
+
+    t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, ms_e2e = float(t[0]), float(t[1])
+
+    value = world * step_bytes * args.steps / (ms * 1e-3) / 1e9
+    e2e_value = world * step_bytes * args.steps / (ms_e2e * 1e-3) / 1e9
+    per_launch_us = ms * 1e3 / max(launches, 1)
+    achieved = step_bytes * args.steps / (ms * 1e-3) / 1e9          # one GPU's kernel stream
+
+    extra = {}
+    if args.sweep and rank == 0:
+        extra["sweep"] = run_sweep(device, ctx)
+
+    if rank == 0:
+        cpu_v, cpu_dt, cores = time_cpu_layer(max(1, int(12.0 / max(time_cpu_layer(1)[1], 1e-3))))
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "llama-3.2-3b int4 g64 linears (q,k,v,o,gate,up,down) x 28 layers, M=1",
+                       "bytes_per_step": step_bytes, "l2": "inputs larger than L2 (1.585 GB of distinct weights per step)",
+                       "replicas": world},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["src"],
+                         "kernel": "affine_b4_gemv_kernel", "avg_launch_us": per_launch_us,
+                         "alg_bytes_per_launch": step_bytes / (N_LAYERS * len(LAYER_ORDER))},
+            "cpu_baseline": {"value": cpu_v, "unit": UNIT, "cores": cores, "kind": "port",
+                             "sample": f"7 linears of one layer, {cpu_dt * 1e3:.1f} ms per pass, oracle C++/OpenMP"},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+        }
+        line.update(extra)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_sweep(device, ctx):
+    """Extra (not the headline): per-shape timings over M for int4 (3B shapes) and fp8 (7B shapes)."""
+    import torch
+    from scratchy_b200 import AffineQuantLinear, Fp8Linear
+    peaks = measured_peaks()
+    out = []
+
+    def timeit(fn, reps):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(device)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize(device)
+        return a.elapsed_time(b) * 1e-3 / reps
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    for name in ["q", "k", "gate", "down"]:
+        K, N = synth.LLAMA_3_2_3B[name]
+        # enough distinct copies that consecutive calls miss L2
+        copies = max(2, int((192 << 20) // (N * K * 9 // 16)) + 1)
+        lins = []
+        for c in range(copies):
+            w = torch.randint(-2 ** 31, 2 ** 31 - 1, (N, K // 8), dtype=torch.int32, device=device)
+            s = (torch.randn((N, K // 64), device=device) * 0.02).abs().add(1e-3).to(torch.bfloat16)
+            b = (-8.0 * s.float()).to(torch.bfloat16)
+            lins.append(AffineQuantLinear.from_tensors(w, s, b))
+        for M in [1, 4, 16, 64, 512, 2048]:
+            x = torch.randn((M, K), device=device).to(torch.bfloat16)
+            y = torch.empty((M, N), dtype=torch.bfloat16, device=device)
+            ws = torch.empty(max(16, lins[0].workspace_bytes(M)), dtype=torch.uint8, device=device)
+            idx = [0]
+
+            def fn():
+                lins[idx[0] % copies].forward(x, out=y, workspace=ws)
+                idx[0] += 1
+            dt = timeit(fn, 20 if M <= 64 else 5)
+            out.append({"kind": "int4", "shape": name, "M": M, "N": N, "K": K, "us": dt * 1e6,
+                        "GBps": affine_alg_bytes(M, N, K) / dt / 1e9, "TFLOPs": 2.0 * M * N * K / dt / 1e12,
+                        "frac_hbm": affine_alg_bytes(M, N, K) / dt / 1e9 / peaks["hbm_gbs"],
+                        "frac_bf16": 2.0 * M * N * K / dt / 1e12 / peaks["bf16_tflops"]})
+        del lins
+    for name in ["q", "k", "gate", "down"]:
+        K, N = synth.QWEN_2_5_7B[name]
+        copies = max(2, int((192 << 20) // (N * K)) + 1)
+        lins = []
+        for c in range(copies):
+            w = torch.randint(0, 120, (N, K), dtype=torch.uint8, device=device)
+            lins.append(Fp8Linear.from_tensors(w, torch.rand(N, device=device) * 1e-3 + 1e-4))
+        for M in [1, 16, 256, 2048, 8192]:
+            x = torch.randn((M, K), device=device).to(torch.bfloat16)
+            y = torch.empty((M, N), dtype=torch.bfloat16, device=device)
+            ws = torch.empty(lins[0].workspace_bytes(M), dtype=torch.uint8, device=device)
+            idx = [0]
+
+            def fn():
+                lins[idx[0] % copies].forward(x, out=y, workspace=ws)
+                idx[0] += 1
+            dt = timeit(fn, 20 if M <= 16 else 3)
+            out.append({"kind": "fp8", "shape": name, "M": M, "N": N, "K": K, "us": dt * 1e6,
+                        "GBps": fp8_alg_bytes(M, N, K) / dt / 1e9, "TFLOPs": 2.0 * M * N * K / dt / 1e12,
+                        "frac_hbm": fp8_alg_bytes(M, N, K) / dt / 1e9 / peaks["hbm_gbs"]})
+        del lins
+    del flush
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--sweep", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,133 @@
+/*
+ * scratchy_cuda.h — C ABI of the B200 (sm_100a) quantized-linear kernels.
+ *
+ * This is the boundary a `cuda` target of the reference project binds through a
+ * thin `extern "C"` shim: every entry point takes plain pointers and sizes, an
+ * explicit CUDA stream (passed as `void*`, i.e. a `cudaStream_t`), returns an
+ * `int32_t` status (0 = OK, negative = error), never throws, never aborts and
+ * allocates nothing on the step path.  All device pointers must be 16-byte
+ * aligned unless stated otherwise.  One caller thread drives one stream; the
+ * library keeps no global mutable state besides the per-device context.
+ *
+ * Each declaration cites the reference interface it replaces (paths relative to
+ * the reference project's root).
+ */
+#ifndef SCRATCHY_CUDA_H_
+#define SCRATCHY_CUDA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------- */
+#define SCR_OK              0
+#define SCR_E_ARG          -1   /* null pointer / bad enum                              */
+#define SCR_E_SHAPE        -2   /* shape violates the preset's law (K % group, ...)     */
+#define SCR_E_ALIGN        -3   /* pointer not 16-byte aligned                          */
+#define SCR_E_DTYPE        -4   /* unsupported bits / group size / dtype                */
+#define SCR_E_CUDA         -5   /* a CUDA runtime call or a kernel launch failed        */
+#define SCR_E_WORKSPACE    -6   /* workspace missing or too small                       */
+#define SCR_E_UNSUPPORTED  -7   /* valid request this build does not implement          */
+#define SCR_E_TIMEOUT      -8   /* a bounded device-side wait ran out                   */
+#define SCR_E_COMM         -9   /* tensor-parallel communicator error                   */
+
+typedef struct scr_ctx scr_ctx;
+
+/* Human-readable name of a status code. */
+const char* scr_status_string(int32_t status);
+/* Detail text of the last error recorded on this context (empty string if none). */
+const char* scr_last_error(const scr_ctx* ctx);
+
+/* ---- lifecycle ----------------------------------------------------------
+ * Replaces the Metal target's device bring-up behind `Worker::init_device`
+ * (crates/serving/engine/src/worker.rs:50-84).  `scr_cuda_init` makes `device`
+ * current, checks that it is an sm_100 part and records its SM count. */
+int32_t scr_cuda_init(int32_t device, scr_ctx** out);
+int32_t scr_cuda_destroy(scr_ctx* ctx);
+/* Number of kernels this context has launched since creation (bench accounting). */
+int64_t scr_launch_count(const scr_ctx* ctx);
+
+/* ---- MLX affine int4, group 64: load-time repack --------------------------
+ * Replaces `MetalAffineQuantOps::load` (crates/targets/metal/src/layers_quant.rs:289-345)
+ * + `load_layered_linear_affine_quant` (crates/targets/metal/src/loaders.rs:96-116): the
+ * checkpoint tensors of `AffineQuantLinear` (crates/models/quantization/src/layers_quant.rs:33-52)
+ *   w       U32  [N, K/8]   element i of a word at bits [4i, 4i+4)
+ *   scales  BF16 [N, K/64]
+ *   biases  BF16 [N, K/64]
+ * already resident on the device, are rewritten once into the kernels' streaming
+ * layout (`dst`, `scr_affine_b4_repack_size` bytes, 128-byte aligned).
+ * Validation follows layers_quant.rs:310-338: bits == 4, K % group == 0; this build
+ * implements group == 64 only (SCR_E_DTYPE otherwise). */
+int32_t scr_affine_b4_repack_size(int32_t N, int32_t K, int32_t group, size_t* bytes);
+int32_t scr_affine_b4_repack(scr_ctx* ctx, const uint32_t* w, const uint16_t* scales_bf16,
+                             const uint16_t* biases_bf16, int32_t N, int32_t K, int32_t group,
+                             void* dst, void* stream);
+
+/* Test hook: dequantise the *repacked* buffer back to dense bf16 [N, K] with the very
+ * device code the matvec and the GEMM use.  Must equal, bit for bit,
+ * `affine_dequant_b4_to_dtype` (crates/models/quantization/src/affine.rs:35-196). */
+int32_t scr_affine_b4_dequant_dump(scr_ctx* ctx, const void* packed, int32_t N, int32_t K,
+                                   int32_t group, uint16_t* w_bf16, void* stream);
+
+/* ---- MLX affine int4: forward ---------------------------------------------
+ * Replaces the `MetalStep::AffineQmm(AffineMatmul{input, output, layer, n, k, group_size,
+ * bits, ..})` step (crates/targets/metal/src/tape/step.rs:456-470) and its M-bucket
+ * kernel pickers (crates/targets/metal/src/tape/quantized.rs:130-157,403-426,563-595):
+ *   y[M,N] (bf16) = x[M,K] (bf16) @ dequant(W)[N,K]^T, f32 accumulation, one rounding,
+ * the contraction of `cpu_reference::affine_qmm_t_b4` (crates/targets/metal/src/cpu_reference.rs:107-137).
+ * The kernel is chosen from M (matvec for M <= 16, tensor-core GEMM above).
+ * `workspace` may be NULL when `scr_linear_workspace_size` reports 0 bytes. */
+#define SCR_KIND_AFFINE_B4   0
+#define SCR_KIND_FP8_DYNAMIC 1
+int32_t scr_linear_workspace_size(int32_t kind, int32_t M, int32_t N, int32_t K, size_t* bytes);
+int32_t scr_linear_affine_b4(scr_ctx* ctx, const void* packed, const uint16_t* x_bf16,
+                             int32_t M, int32_t N, int32_t K, int32_t group, uint16_t* y_bf16,
+                             void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- fp8-dynamic-per-channel: load-time repack ----------------------------
+ * Replaces the `load_layered_fp8...` loaders the reference's codegen names but no live
+ * target implements (Metal refuses fp8: crates/targets/metal/compiler/src/steps_from_tape.rs:2009).
+ * Payload of `Fp8Linear` (crates/layers/src/layers.rs:179-191): `w_e4m3` FP8 E4M3 [N,K],
+ * `w_scale` F32 [N] (per output channel).  `dst` receives the tiled layout the kernels
+ * stream (`scr_fp8_repack_size` bytes, 128-byte aligned; the scales are copied into it). */
+int32_t scr_fp8_repack_size(int32_t N, int32_t K, size_t* bytes);
+int32_t scr_fp8_repack(scr_ctx* ctx, const uint8_t* w_e4m3, const float* w_scale, int32_t N,
+                       int32_t K, void* dst, void* stream);
+
+/* ---- fp8-dynamic-per-channel: per-token activation quantisation -----------
+ * Replaces the shared W8A8 activation-quantise chain `fp8_quantize_descriptors`
+ * (backends/spyre/crates/ktir/ktir-superdsc/src/emit/ktir_matmul_fp8.rs:123-322,430-531):
+ *   a_scale[m] = min(max(absmax(x[m,:]) * (1/448), 1/448^2), 448);  x_q = e4m3(clip(x / a_scale, +-448))
+ * with the reference encoder's rounding (backends/spyre/crates/ktir/ktir-core/src/codec.rs:1023-1070).
+ * `act` is an opaque activation pack of `scr_fp8_act_size(M, K)` bytes that several
+ * linears reading the same activation may share (the reference shares one quantise
+ * across q/k/v and gate/up: ktir_matmul_fp8.rs:47-100). */
+int32_t scr_fp8_act_size(int32_t M, int32_t K, size_t* bytes);
+int32_t scr_fp8_quant_per_token(scr_ctx* ctx, const uint16_t* x_bf16, int32_t M, int32_t K,
+                                void* act, void* stream);
+/* Test hook: unpack an activation pack to plain x_q [M,K] bytes and a_scale [M]. */
+int32_t scr_fp8_act_unpack(scr_ctx* ctx, const void* act, int32_t M, int32_t K, uint8_t* xq,
+                           float* a_scale, void* stream);
+/* Test hook: the device e4m3 encoder on `count` f32 values (codec.rs:1023-1070). */
+int32_t scr_e4m3_encode(scr_ctx* ctx, const float* v, int64_t count, uint8_t* out, void* stream);
+
+/* ---- fp8-dynamic-per-channel: forward -------------------------------------
+ * Replaces the arity-3 fp8 matmul body (ktir_matmul_fp8.rs:633-720; program
+ * backends/spyre/kernels/matmul_fp8.py:46-82):
+ *   y[m,n] (bf16) = ((sum_k x_q[m,k] * w_q[n,k]) * a_scale[m]) * w_scale[n],  f32 accumulation.
+ * `scr_linear_fp8` consumes an activation pack; `scr_linear_fp8_dynamic` is the whole
+ * generated Linear (quantise, then contract) and needs a workspace that holds the pack. */
+int32_t scr_linear_fp8(scr_ctx* ctx, const void* packed, const void* act, int32_t M, int32_t N,
+                       int32_t K, uint16_t* y_bf16, void* workspace, size_t workspace_bytes,
+                       void* stream);
+int32_t scr_linear_fp8_dynamic(scr_ctx* ctx, const void* packed, const uint16_t* x_bf16, int32_t M,
+                               int32_t N, int32_t K, uint16_t* y_bf16, void* workspace,
+                               size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SCRATCHY_CUDA_H_ */

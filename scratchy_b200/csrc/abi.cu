@@ -1,0 +1,60 @@
+// Context lifecycle, status strings and the workspace query of the C ABI.
+#include "common.cuh"
+#include <new>
+
+size_t affine_workspace_bytes(int M, int N, int K);
+size_t fp8_workspace_bytes(int M, int N, int K);
+
+extern "C" const char* scr_status_string(int32_t s) {
+    switch (s) {
+        case SCR_OK: return "SCR_OK";
+        case SCR_E_ARG: return "SCR_E_ARG";
+        case SCR_E_SHAPE: return "SCR_E_SHAPE";
+        case SCR_E_ALIGN: return "SCR_E_ALIGN";
+        case SCR_E_DTYPE: return "SCR_E_DTYPE";
+        case SCR_E_CUDA: return "SCR_E_CUDA";
+        case SCR_E_WORKSPACE: return "SCR_E_WORKSPACE";
+        case SCR_E_UNSUPPORTED: return "SCR_E_UNSUPPORTED";
+        case SCR_E_TIMEOUT: return "SCR_E_TIMEOUT";
+        case SCR_E_COMM: return "SCR_E_COMM";
+        default: return "SCR_E_UNKNOWN";
+    }
+}
+
+extern "C" const char* scr_last_error(const scr_ctx* ctx) { return ctx ? ctx->err : "null context"; }
+
+extern "C" int32_t scr_cuda_init(int32_t device, scr_ctx** out) {
+    if (!out) return SCR_E_ARG;
+    *out = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count <= 0) return SCR_E_CUDA;
+    if (device < 0 || device >= count) return SCR_E_ARG;
+    if (cudaSetDevice(device) != cudaSuccess) return SCR_E_CUDA;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return SCR_E_CUDA;
+    if (prop.major != 10) return SCR_E_UNSUPPORTED;   // the kernels are sm_100a only
+    scr_ctx* c = new (std::nothrow) scr_ctx();
+    if (!c) return SCR_E_CUDA;
+    c->device = device;
+    c->sm_count = prop.multiProcessorCount;
+    c->cc_major = prop.major;
+    c->cc_minor = prop.minor;
+    *out = c;
+    return SCR_OK;
+}
+
+extern "C" int32_t scr_cuda_destroy(scr_ctx* ctx) {
+    if (!ctx) return SCR_E_ARG;
+    delete ctx;
+    return SCR_OK;
+}
+
+extern "C" int64_t scr_launch_count(const scr_ctx* ctx) { return ctx ? (int64_t)ctx->launches.load() : 0; }
+
+extern "C" int32_t scr_linear_workspace_size(int32_t kind, int32_t M, int32_t N, int32_t K, size_t* bytes) {
+    if (!bytes) return SCR_E_ARG;
+    if (M <= 0 || N <= 0 || K <= 0) return SCR_E_SHAPE;
+    if (kind == SCR_KIND_AFFINE_B4) { *bytes = affine_workspace_bytes(M, N, K); return SCR_OK; }
+    if (kind == SCR_KIND_FP8_DYNAMIC) { *bytes = fp8_workspace_bytes(M, N, K); return SCR_OK; }
+    return SCR_E_ARG;
+}

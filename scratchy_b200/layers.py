@@ -1,0 +1,328 @@
+"""Host-side mirror of the reference's quantized-linear layer and loader interface.
+
+Reference (paths relative to its root):
+  * payload types        crates/models/quantization/src/layers_quant.rs:33-52 (`AffineQuantLinear`),
+                         crates/layers/src/layers.rs:179-191 (`Fp8Linear`), :212-236 (`LinearLayer`)
+  * loaders              crates/targets/metal/src/layers_quant.rs:289-345 (`MetalAffineQuantOps::load`),
+                         crates/targets/metal/src/loaders.rs:96-116 (`load_layered_linear_affine_quant`)
+  * weight store         crates/layers/src/weights.rs (`GpuWeights::take`, `contains`)
+  * the forward step     crates/targets/metal/src/tape/step.rs:456-470 (`AffineMatmul`)
+
+Names, argument meaning and error behaviour follow those; the arithmetic runs only in the
+CUDA library (``_lib``).  torch tensors are used as device buffers and for the stream.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import torch
+
+from . import _lib
+from ._lib import KIND_AFFINE_B4, KIND_FP8_DYNAMIC, ScratchyCudaError
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream(device) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _dev_index(device) -> int:
+    d = torch.device(device)
+    return d.index if d.index is not None else torch.cuda.current_device()
+
+
+class GpuWeights:
+    """A named store of device tensors, the loader vocabulary of `GpuWeights` in the reference
+    (crates/layers/src/weights.rs): `take` removes and returns a tensor, `contains` probes."""
+
+    def __init__(self, tensors: Dict[str, torch.Tensor], scale_dtype: Optional[torch.dtype] = torch.bfloat16):
+        self._t = dict(tensors)
+        self._scale_dtype = scale_dtype
+
+    def contains(self, name: str) -> bool:
+        return name in self._t
+
+    def take(self, name: str) -> torch.Tensor:
+        if name not in self._t:
+            raise KeyError(f"tensor `{name}` not found in checkpoint")
+        return self._t.pop(name)
+
+    def rmsnorm_scale_dtype(self) -> Optional[torch.dtype]:
+        return self._scale_dtype
+
+
+def affine_packed_cols(in_features: int, bits: int) -> int:
+    """crates/targets/metal/src/layers_quant.rs:46-48."""
+    return (in_features * bits + 31) // 32
+
+
+@dataclass
+class AffineQuantLinear:
+    """MLX affine int4 linear, repacked for the B200 kernels at load time.
+
+    `packed` is the streaming layout written by `scr_affine_b4_repack`; the checkpoint
+    tensors are released after the repack unless `keep_source` was set.
+    """
+    packed: torch.Tensor
+    in_features: int
+    out_features: int
+    group_size: int
+    bits: int
+    linear_bias: Optional[torch.Tensor] = None
+    source: Optional[dict] = field(default=None, repr=False)
+
+    # ---- MetalAffineQuantOps::load (layers_quant.rs:289-345)
+    @classmethod
+    def load(cls, weights: GpuWeights, prefix: str, group_size: int, bits: int, expected_in_features: int,
+             keep_source: bool = False) -> "AffineQuantLinear":
+        weight = weights.take(f"{prefix}.weight")
+        scales = _take_affine_scales(weights, f"{prefix}.scales")
+        affine_biases = _take_affine_scales(weights, f"{prefix}.biases")
+        linear_bias = weights.take(f"{prefix}.bias") if weights.contains(f"{prefix}.bias") else None
+        if weight.dim() != 2:
+            raise ValueError(f"`{prefix}.weight` must be 2-D, got {tuple(weight.shape)}")
+        out_features, packed_cols = int(weight.shape[0]), int(weight.shape[1])
+        in_features = packed_cols * 32 // bits
+        if (packed_cols * 32) % bits != 0 or affine_packed_cols(in_features, bits) != packed_cols:
+            raise ValueError(
+                f"affine quant checkpoint/preset mismatch at `{prefix}`: packed `.weight` is "
+                f"[{out_features}, {packed_cols}], implying in_features={in_features} at bits={bits}; "
+                f"this build expects in_features={expected_in_features}.")
+        if in_features != expected_in_features:
+            raise ValueError(
+                f"affine quant checkpoint/preset mismatch at `{prefix}`: packed `.weight` implies "
+                f"in_features={in_features} at bits={bits}, but this build expects "
+                f"in_features={expected_in_features}")
+        if in_features % group_size != 0:
+            raise ValueError(f"`{prefix}`: in_features={in_features} not divisible by group_size={group_size}")
+        want = (out_features, in_features // group_size)
+        if tuple(scales.shape) != want or tuple(affine_biases.shape) != want:
+            raise ValueError(f"`{prefix}`: scales/biases must be {want}, got {tuple(scales.shape)} / "
+                             f"{tuple(affine_biases.shape)}")
+        return cls.from_tensors(weight, scales, affine_biases, group_size, bits, linear_bias, keep_source)
+
+    @classmethod
+    def from_tensors(cls, weight: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor, group_size: int = 64,
+                     bits: int = 4, linear_bias: Optional[torch.Tensor] = None,
+                     keep_source: bool = False) -> "AffineQuantLinear":
+        if bits != 4:
+            raise ScratchyCudaError(-4, f"bits={bits}: the cuda target implements the 4-bit preset only")
+        if weight.dtype not in (torch.int32, torch.uint32):
+            raise ValueError(f"`.weight` must be U32, got {weight.dtype}")
+        if scales.dtype != torch.bfloat16 or biases.dtype != torch.bfloat16:
+            raise ValueError("scales/biases must be bf16 for this build")
+        if not weight.is_cuda:
+            raise ScratchyCudaError(-5, "weights must be on a CUDA device (there is no CPU path)")
+        dev = weight.device
+        N, K = int(weight.shape[0]), int(weight.shape[1]) * 8
+        ctx = _lib.context(_dev_index(dev))
+        L = _lib.lib()
+        size = ctypes.c_size_t(0)
+        ctx.check(L.scr_affine_b4_repack_size(N, K, group_size, ctypes.byref(size)))
+        packed = torch.empty(size.value, dtype=torch.uint8, device=dev)
+        weight, scales, biases = weight.contiguous(), scales.contiguous(), biases.contiguous()
+        ctx.check(L.scr_affine_b4_repack(ctx.handle, _ptr(weight), _ptr(scales), _ptr(biases), N, K, group_size,
+                                         _ptr(packed), _stream(dev)))
+        src = {"weight": weight, "scales": scales, "biases": biases} if keep_source else None
+        return cls(packed, K, N, group_size, bits, linear_bias, src)
+
+    def workspace_bytes(self, M: int) -> int:
+        size = ctypes.c_size_t(0)
+        st = _lib.lib().scr_linear_workspace_size(KIND_AFFINE_B4, M, self.out_features, self.in_features,
+                                                  ctypes.byref(size))
+        if st:
+            raise ScratchyCudaError(st, "scr_linear_workspace_size")
+        return size.value
+
+    # ---- the `AffineMatmul` step (tape/step.rs:456-470): y = x @ dequant(W)^T
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None,
+                workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if x.dtype != torch.bfloat16 or not x.is_cuda:
+            raise ValueError("x must be a bf16 CUDA tensor")
+        if x.shape[-1] != self.in_features:
+            raise ValueError(f"x has {x.shape[-1]} features, layer expects {self.in_features}")
+        x2 = x.reshape(-1, self.in_features).contiguous()
+        M = int(x2.shape[0])
+        dev = x2.device
+        if out is None:
+            out = torch.empty((M, self.out_features), dtype=torch.bfloat16, device=dev)
+        ctx = _lib.context(_dev_index(dev))
+        need = self.workspace_bytes(M)
+        if need and (workspace is None or workspace.numel() < need):
+            workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+        ctx.check(_lib.lib().scr_linear_affine_b4(
+            ctx.handle, _ptr(self.packed), _ptr(x2), M, self.out_features, self.in_features, self.group_size,
+            _ptr(out), _ptr(workspace), ctypes.c_size_t(workspace.numel() if workspace is not None else 0),
+            _stream(dev)))
+        return out.reshape(*x.shape[:-1], self.out_features)
+
+    def dequantize(self) -> torch.Tensor:
+        """Test hook: dense bf16 [N, K] from the repacked buffer (`scr_affine_b4_dequant_dump`)."""
+        dev = self.packed.device
+        w = torch.empty((self.out_features, self.in_features), dtype=torch.bfloat16, device=dev)
+        ctx = _lib.context(_dev_index(dev))
+        ctx.check(_lib.lib().scr_affine_b4_dequant_dump(ctx.handle, _ptr(self.packed), self.out_features,
+                                                        self.in_features, self.group_size, _ptr(w), _stream(dev)))
+        return w
+
+
+def _take_affine_scales(weights: GpuWeights, name: str) -> torch.Tensor:
+    """`take_affine_scales` (layers_quant.rs:270-285): refuse scales that are not the pinned dtype."""
+    compiled = weights.rmsnorm_scale_dtype()
+    if compiled is None:
+        raise ValueError(f"`{name}`: no scale dtype pinned")
+    t = weights.take(name)
+    if t.dtype != compiled:
+        raise ValueError(f"`{name}` is {t.dtype} on disk; this build's quantized kernels read {compiled}")
+    return t
+
+
+@dataclass
+class Fp8ActPack:
+    """A per-token quantised activation (x_q, a_scale) that several linears may share."""
+    buf: torch.Tensor
+    M: int
+    K: int
+
+    def unpack(self):
+        """Test hook: plain x_q [M,K] uint8 and a_scale [M] f32."""
+        dev = self.buf.device
+        xq = torch.empty((self.M, self.K), dtype=torch.uint8, device=dev)
+        a = torch.empty((self.M,), dtype=torch.float32, device=dev)
+        ctx = _lib.context(_dev_index(dev))
+        ctx.check(_lib.lib().scr_fp8_act_unpack(ctx.handle, _ptr(self.buf), self.M, self.K, _ptr(xq), _ptr(a),
+                                                _stream(dev)))
+        return xq, a
+
+
+@dataclass
+class Fp8Linear:
+    """fp8-dynamic-per-channel linear: e4m3 weights [N,K], f32 scale per output channel,
+    activations quantised per token at run time (crates/layers/src/layers.rs:179-191)."""
+    packed: torch.Tensor
+    in_features: int
+    out_features: int
+
+    @classmethod
+    def load(cls, weights: GpuWeights, prefix: str, expected_in_features: int) -> "Fp8Linear":
+        weight = weights.take(f"{prefix}.weight")
+        scale = weights.take(f"{prefix}.weight_scale")
+        if weight.dim() != 2 or int(weight.shape[1]) != expected_in_features:
+            raise ValueError(f"`{prefix}.weight` is {tuple(weight.shape)}; this build expects "
+                             f"in_features={expected_in_features}")
+        return cls.from_tensors(weight, scale)
+
+    @classmethod
+    def from_tensors(cls, weight_e4m3: torch.Tensor, weight_scale: torch.Tensor) -> "Fp8Linear":
+        if weight_e4m3.dtype not in (torch.uint8, torch.float8_e4m3fn):
+            raise ValueError(f"`.weight` must be FP8 E4M3 bytes, got {weight_e4m3.dtype}")
+        if not weight_e4m3.is_cuda:
+            raise ScratchyCudaError(-5, "weights must be on a CUDA device (there is no CPU path)")
+        N, K = int(weight_e4m3.shape[0]), int(weight_e4m3.shape[1])
+        scale = weight_scale.reshape(-1).to(torch.float32).contiguous()   # [N] or [N,1] per-channel
+        if scale.numel() != N:
+            raise ValueError(f"`.weight_scale` must hold {N} per-channel scales, got {tuple(weight_scale.shape)}")
+        dev = weight_e4m3.device
+        ctx = _lib.context(_dev_index(dev))
+        L = _lib.lib()
+        size = ctypes.c_size_t(0)
+        ctx.check(L.scr_fp8_repack_size(N, K, ctypes.byref(size)))
+        packed = torch.empty(size.value, dtype=torch.uint8, device=dev)
+        w = weight_e4m3.contiguous().view(torch.uint8)
+        ctx.check(L.scr_fp8_repack(ctx.handle, _ptr(w), _ptr(scale), N, K, _ptr(packed), _stream(dev)))
+        return cls(packed, K, N)
+
+    @staticmethod
+    def quantize_activation(x: torch.Tensor) -> Fp8ActPack:
+        if x.dtype != torch.bfloat16 or not x.is_cuda:
+            raise ValueError("x must be a bf16 CUDA tensor")
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        M, K = int(x2.shape[0]), int(x2.shape[1])
+        dev = x2.device
+        ctx = _lib.context(_dev_index(dev))
+        L = _lib.lib()
+        size = ctypes.c_size_t(0)
+        ctx.check(L.scr_fp8_act_size(M, K, ctypes.byref(size)))
+        buf = torch.empty(size.value, dtype=torch.uint8, device=dev)
+        ctx.check(L.scr_fp8_quant_per_token(ctx.handle, _ptr(x2), M, K, _ptr(buf), _stream(dev)))
+        return Fp8ActPack(buf, M, K)
+
+    def workspace_bytes(self, M: int) -> int:
+        size = ctypes.c_size_t(0)
+        st = _lib.lib().scr_linear_workspace_size(KIND_FP8_DYNAMIC, M, self.out_features, self.in_features,
+                                                  ctypes.byref(size))
+        if st:
+            raise ScratchyCudaError(st, "scr_linear_workspace_size")
+        return size.value
+
+    def forward_quantized(self, act: Fp8ActPack, out: Optional[torch.Tensor] = None,
+                          workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if act.K != self.in_features:
+            raise ValueError(f"activation has {act.K} features, layer expects {self.in_features}")
+        dev = act.buf.device
+        if out is None:
+            out = torch.empty((act.M, self.out_features), dtype=torch.bfloat16, device=dev)
+        ctx = _lib.context(_dev_index(dev))
+        need = self.workspace_bytes(act.M)
+        if workspace is None or workspace.numel() < need:
+            workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
+        ctx.check(_lib.lib().scr_linear_fp8(ctx.handle, _ptr(self.packed), _ptr(act.buf), act.M, self.out_features,
+                                            self.in_features, _ptr(out), _ptr(workspace),
+                                            ctypes.c_size_t(workspace.numel()), _stream(dev)))
+        return out
+
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None,
+                workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The whole generated Linear: quantise per token, contract, dequantise (`scr_linear_fp8_dynamic`)."""
+        if x.dtype != torch.bfloat16 or not x.is_cuda:
+            raise ValueError("x must be a bf16 CUDA tensor")
+        if x.shape[-1] != self.in_features:
+            raise ValueError(f"x has {x.shape[-1]} features, layer expects {self.in_features}")
+        x2 = x.reshape(-1, self.in_features).contiguous()
+        M = int(x2.shape[0])
+        dev = x2.device
+        if out is None:
+            out = torch.empty((M, self.out_features), dtype=torch.bfloat16, device=dev)
+        ctx = _lib.context(_dev_index(dev))
+        need = self.workspace_bytes(M)
+        if workspace is None or workspace.numel() < need:
+            workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+        ctx.check(_lib.lib().scr_linear_fp8_dynamic(ctx.handle, _ptr(self.packed), _ptr(x2), M, self.out_features,
+                                                    self.in_features, _ptr(out), _ptr(workspace),
+                                                    ctypes.c_size_t(workspace.numel()), _stream(dev)))
+        return out.reshape(*x.shape[:-1], self.out_features)
+
+
+class LinearLayer:
+    """The variants of the reference's `LinearLayer` enum this target lowers
+    (crates/layers/src/layers.rs:212-236): `AffineQuant` and `Fp8`."""
+
+    AffineQuant = AffineQuantLinear
+    Fp8 = Fp8Linear
+
+    @staticmethod
+    def load_affine_quant(weights: GpuWeights, prefix: str, group_size: int, bits: int,
+                          expected_in_features: int) -> AffineQuantLinear:
+        return AffineQuantLinear.load(weights, prefix, group_size, bits, expected_in_features)
+
+    @staticmethod
+    def load_fp8(weights: GpuWeights, prefix: str, expected_in_features: int) -> Fp8Linear:
+        return Fp8Linear.load(weights, prefix, expected_in_features)
+
+
+def load_layered_linear_affine_quant(gw: GpuWeights, n_layers: int, root: str, suffix: str, group_size: int,
+                                     bits: int, in_features: int) -> List[AffineQuantLinear]:
+    """crates/targets/metal/src/loaders.rs:96-116: one layer per `{root}.{i}.{suffix}`."""
+    return [LinearLayer.load_affine_quant(gw, f"{root}.{i}.{suffix}", group_size, bits, in_features)
+            for i in range(n_layers)]
+
+
+def load_layered_linear_fp8_dynamic(gw: GpuWeights, n_layers: int, root: str, suffix: str,
+                                    in_features: int) -> List[Fp8Linear]:
+    """The `load_layered_fp8...` loader the reference's codegen names (no live target implements it)."""
+    return [LinearLayer.load_fp8(gw, f"{root}.{i}.{suffix}", in_features) for i in range(n_layers)]

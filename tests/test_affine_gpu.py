@@ -1,0 +1,167 @@
+"""GPU parity of the MLX affine int4 path against the CPU oracle (through the C ABI).
+
+Bars: dequantised weights bit-exact; bf16 outputs within relative L2 1e-3 of the oracle's
+f32-accumulated result (the tolerance the baseline configuration states), max-abs printed.
+"""
+import ctypes
+import glob
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+from scratchy_b200 import synth
+from util import bf16_dev, bits_of, max_abs, rel_l2, u32_dev
+
+pytestmark = pytest.mark.gpu
+REL_L2_TOL = 1e-3
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def make_layer(w, s, b):
+    from scratchy_b200 import AffineQuantLinear
+    return AffineQuantLinear.from_tensors(u32_dev(w), bf16_dev(s), bf16_dev(b), 64, 4)
+
+
+def run_case(N, K, M, seed, w=None, s=None, b=None, x=None):
+    import torch
+    if w is None:
+        w, s, b = synth.affine_int4_weights(N, K, 64, seed)
+        x = synth.activations_bf16(M, K, seed + 1)
+    layer = make_layer(w, s, b)
+    y = layer.forward(bf16_dev(x).reshape(M, K))
+    torch.cuda.synchronize()
+    want = oracle.affine_qmm_t_b4(w.view(np.uint8).reshape(-1), s, b, x, M, N, K, 64)
+    got = bits_of(y).reshape(M, N)
+    return got, want
+
+
+@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(GOLD, "affine_b4_*.npz"))))
+def test_golden_fixtures(path):
+    import torch
+    g = np.load(path)
+    N, K, M = g["w"].shape[0], g["w"].shape[1] * 8, g["x"].shape[0]
+    layer = make_layer(g["w"], g["scales"], g["biases"])
+    wd = bits_of(layer.dequantize()).reshape(N, K)
+    assert np.array_equal(wd, g["w_dequant"]), "dequantised weights must be bit-exact"
+    y = bits_of(layer.forward(bf16_dev(g["x"]).reshape(M, K))).reshape(M, N)
+    torch.cuda.synchronize()
+    assert rel_l2(y, g["y"]) <= REL_L2_TOL
+
+
+@pytest.mark.parametrize("N,K", [(8192, 3072), (1024, 3072), (3072, 8192), (8, 64), (24, 192), (130, 320)])
+def test_dequant_bit_exact(N, K):
+    w, s, b = synth.affine_int4_weights(N, K, 64, synth.seed_for("deq", N, K))
+    layer = make_layer(w, s, b)
+    got = bits_of(layer.dequantize()).reshape(N, K)
+    want = oracle.affine_dequant_b4(w.view(np.uint8).reshape(-1), s, b, N, K, 64)
+    assert np.array_equal(got, want)
+
+
+def test_dequant_bit_exact_adversarial_scales():
+    """Scales/biases that stress the rounding contract: the reference test distribution
+    (scales 0.01+0.04u, biases u-0.5), zero scale/bias, tiny biases far below the product
+    (the double-rounding case), large magnitudes, negative scales, subnormal values."""
+    N, K = 64, 256
+    rng = np.random.default_rng(5)
+    w, s, b = synth.affine_int4_weights(N, K, 64, 9)
+    G = K // 64
+    sf = (0.01 + 0.04 * rng.random((N, G))).astype(np.float32)
+    bf = (rng.random((N, G)) - 0.5).astype(np.float32)
+    sf[0] = 0.0
+    bf[1] = 0.0
+    bf[2] = 1e-30
+    bf[3] = -1e-20
+    sf[4] = 1.5
+    bf[4] = 2.0 ** -14
+    sf[5] = -0.037
+    sf[6] = 3.0e4
+    bf[6] = -2.4e5
+    sf[7] = 1e-40
+    bf[8] = 1e-39
+    sf[9] = 1.0078125       # 1 + 2^-7 : products land on bf16 half-way points for odd codes
+    bf[9] = 2.0 ** -20
+    sf[10] = 1.0078125
+    bf[10] = -(2.0 ** -30)
+    sf[11] = 257.0
+    bf[11] = 1e-6
+    s = synth.f32_to_bf16_bits(sf)
+    b = synth.f32_to_bf16_bits(bf)
+    layer = make_layer(w, s, b)
+    got = bits_of(layer.dequantize()).reshape(N, K)
+    want = oracle.affine_dequant_b4(w.view(np.uint8).reshape(-1), s, b, N, K, 64)
+    bad = np.argwhere(got != want)
+    assert bad.size == 0, f"first mismatches (row, k): {bad[:8].tolist()}"
+
+
+def test_config0_single_linear_m1():
+    """BASELINE config 0: M=1, K=3072, N=8192, seed 0."""
+    w, s, b = synth.affine_int4_weights(8192, 3072, 64, 0)
+    x = synth.activations_bf16(1, 3072, 1)
+    got, want = run_case(8192, 3072, 1, 0, w, s, b, x)
+    r = rel_l2(got, want)
+    print(f"config0 rel_l2={r:.3e} max_abs={max_abs(got, want):.3e} exact={np.mean(got == want):.4f}")
+    assert r <= REL_L2_TOL
+
+
+@pytest.mark.parametrize("name", ["q", "k", "gate", "down"])
+@pytest.mark.parametrize("M", [1, 4, 16])
+def test_llama_3b_shapes_decode(name, M):
+    K, N = synth.LLAMA_3_2_3B[name]
+    got, want = run_case(N, K, M, synth.seed_for("aff", N, K, M))
+    r = rel_l2(got, want)
+    print(f"{name} M={M} rel_l2={r:.3e} max_abs={max_abs(got, want):.3e}")
+    assert r <= REL_L2_TOL
+
+
+@pytest.mark.parametrize("N,K,M", [(8, 64, 1), (16, 64, 2), (24, 192, 5), (130, 320, 9), (100, 1024, 16), (48, 128, 7)])
+def test_ragged_and_small_shapes(N, K, M):
+    got, want = run_case(N, K, M, synth.seed_for("rag", N, K, M))
+    assert rel_l2(got, want) <= REL_L2_TOL
+
+
+@pytest.mark.parametrize("M", [17, 64, 100])
+def test_prefill_rows_small_matrix(M):
+    got, want = run_case(256, 512, M, synth.seed_for("pre", M))
+    assert rel_l2(got, want) <= REL_L2_TOL
+
+
+def test_linearity_and_determinism_full_size():
+    """Size-independent properties at a full layer shape: y(2x) == 2 y(x) exactly (power-of-two
+    scaling commutes with every rounding), and two runs are bit-identical (fixed reduction order)."""
+    import torch
+    K, N = synth.LLAMA_3_2_3B["gate"]
+    w, s, b = synth.affine_int4_weights(N, K, 64, 3)
+    layer = make_layer(w, s, b)
+    x = bf16_dev(synth.activations_bf16(4, K, 4)).reshape(4, K)
+    y1 = layer.forward(x)
+    y2 = layer.forward(x)
+    y3 = layer.forward(x * 2)
+    torch.cuda.synchronize()
+    assert torch.equal(y1, y2)
+    assert torch.equal(y1 * 2, y3)
+
+
+def test_zero_activation_gives_zero():
+    import torch
+    w, s, b = synth.affine_int4_weights(64, 128, 64, 3)
+    layer = make_layer(w, s, b)
+    y = layer.forward(torch.zeros((3, 128), dtype=torch.bfloat16, device="cuda"))
+    assert not y.any()
+
+
+def test_error_codes_through_the_abi():
+    import torch
+    from scratchy_b200 import _lib
+    ctx = _lib.context(0)
+    L = _lib.lib()
+    buf = torch.zeros(4096, dtype=torch.uint8, device="cuda")
+    p = ctypes.c_void_p(buf.data_ptr())
+    assert L.scr_linear_affine_b4(ctx.handle, p, p, 1, 16, 96, 64, p, None, 0, None) == -2     # K % group
+    assert L.scr_linear_affine_b4(ctx.handle, p, p, 1, 16, 128, 32, p, None, 0, None) == -4    # group 32
+    assert L.scr_linear_affine_b4(ctx.handle, p, p, 0, 16, 128, 64, p, None, 0, None) == -2    # M
+    assert L.scr_linear_affine_b4(ctx.handle, None, p, 1, 16, 128, 64, p, None, 0, None) == -1
+    mis = ctypes.c_void_p(buf.data_ptr() + 4)
+    assert L.scr_linear_affine_b4(ctx.handle, mis, p, 1, 16, 128, 64, p, None, 0, None) == -3
+    assert b"aligned" in L.scr_last_error(ctx.handle)

@@ -1,0 +1,84 @@
+"""Host-side mirror of the reference's loader interface: validation and error behaviour (no GPU)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from scratchy_b200 import AffineQuantLinear, Fp8Linear, GpuWeights, LinearLayer, ScratchyCudaError, synth
+from scratchy_b200.layers import affine_packed_cols, load_layered_linear_affine_quant
+
+
+def _ckpt(N=16, K=128, prefix="model.layers.0.self_attn.q_proj", scale_dtype=torch.bfloat16):
+    w, s, b = synth.affine_int4_weights(N, K, 64, 3)
+    return {
+        f"{prefix}.weight": torch.from_numpy(w.view(np.int32)),
+        f"{prefix}.scales": torch.from_numpy(s.view(np.int16)).view(torch.bfloat16).to(scale_dtype),
+        f"{prefix}.biases": torch.from_numpy(b.view(np.int16)).view(torch.bfloat16).to(scale_dtype),
+    }
+
+
+def test_affine_packed_cols_law():
+    # crates/targets/metal/src/layers_quant.rs:46-48
+    assert affine_packed_cols(3072, 4) == 384 and affine_packed_cols(64, 4) == 8
+
+
+def test_load_rejects_wrong_in_features():
+    gw = GpuWeights(_ckpt())
+    with pytest.raises(ValueError, match="in_features=128.*expects in_features=256"):
+        LinearLayer.load_affine_quant(gw, "model.layers.0.self_attn.q_proj", 64, 4, 256)
+
+
+def test_load_rejects_unpinned_or_mismatched_scale_dtype():
+    with pytest.raises(ValueError, match="no scale dtype pinned"):
+        AffineQuantLinear.load(GpuWeights(_ckpt(), scale_dtype=None), "model.layers.0.self_attn.q_proj", 64, 4, 128)
+    with pytest.raises(ValueError, match="on disk"):
+        AffineQuantLinear.load(GpuWeights(_ckpt(scale_dtype=torch.float16)), "model.layers.0.self_attn.q_proj",
+                               64, 4, 128)
+
+
+def test_load_missing_tensor_is_a_key_error():
+    with pytest.raises(KeyError, match="not found"):
+        AffineQuantLinear.load(GpuWeights({}), "nope", 64, 4, 128)
+
+
+def test_cpu_tensors_are_refused_there_is_no_cpu_path():
+    gw = GpuWeights(_ckpt())
+    with pytest.raises(ScratchyCudaError, match="no CPU path"):
+        AffineQuantLinear.load(gw, "model.layers.0.self_attn.q_proj", 64, 4, 128)
+    with pytest.raises(ScratchyCudaError, match="no CPU path"):
+        Fp8Linear.from_tensors(torch.zeros((16, 128), dtype=torch.uint8), torch.ones(16))
+
+
+def test_only_the_four_bit_preset_is_lowered():
+    ck = _ckpt()
+    with pytest.raises(ScratchyCudaError):
+        AffineQuantLinear.from_tensors(ck["model.layers.0.self_attn.q_proj.weight"],
+                                       ck["model.layers.0.self_attn.q_proj.scales"],
+                                       ck["model.layers.0.self_attn.q_proj.biases"], 64, 8)
+
+
+def test_layered_loader_walks_root_i_suffix():
+    tensors = {}
+    for i in range(2):
+        tensors.update(_ckpt(prefix=f"model.layers.{i}.mlp.up_proj"))
+    gw = GpuWeights(tensors)
+    with pytest.raises(ScratchyCudaError):      # reaches the repack of layer 0, which needs a device
+        load_layered_linear_affine_quant(gw, 2, "model.layers", "mlp.up_proj", 64, 4, 128)
+    assert not gw.contains("model.layers.0.mlp.up_proj.weight")   # layer 0 was taken
+    assert gw.contains("model.layers.1.mlp.up_proj.weight")
+
+
+def test_synthetic_weight_packing_matches_the_checkpoint_nibble_order():
+    # element k of a row sits at bits [4*(k%8), +4) of word k//8 == low nibble first in the byte stream
+    w, s, b = synth.affine_int4_weights(4, 64, 64, 5)
+    packed = w.view(np.uint8).reshape(-1)
+    codes = np.empty(4 * 64, np.uint8)
+    codes[0::2] = packed & 0xF
+    codes[1::2] = packed >> 4
+    words = w.reshape(-1)
+    for idx in (0, 1, 7, 8, 63, 64, 255):
+        assert codes[idx] == (int(words[idx // 8]) >> (4 * (idx % 8))) & 0xF
+    scale_one = np.full(4, 0x3F80, np.uint16)
+    zero = np.zeros(4, np.uint16)
+    wd = oracle.affine_dequant_b4(packed, scale_one, zero, 4, 64, 64)
+    assert np.array_equal(oracle.bf16_bits_to_f32(wd).reshape(-1).astype(np.uint8), codes)
