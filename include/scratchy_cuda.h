@@ -49,6 +49,12 @@ int32_t scr_cuda_init(int32_t device, scr_ctx** out);
 int32_t scr_cuda_destroy(scr_ctx* ctx);
 /* Number of kernels this context has launched since creation (bench accounting). */
 int64_t scr_launch_count(const scr_ctx* ctx);
+/* Health probe, the device-side half of `Executor::check_health`
+ * (crates/serving/engine/src/executor.rs:454): every wait inside the tensor-core kernels is
+ * bounded; one that runs out records a code in a device word instead of hanging.  This call
+ * synchronises `stream`, reads and clears the word and returns SCR_E_TIMEOUT if it was set
+ * (`code` receives the raw value; may be NULL).  Not for the step path. */
+int32_t scr_device_status(scr_ctx* ctx, void* stream, int32_t* code);
 
 /* ---- MLX affine int4, group 64: load-time repack --------------------------
  * Replaces `MetalAffineQuantOps::load` (crates/targets/metal/src/layers_quant.rs:289-345)

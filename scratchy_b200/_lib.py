@@ -36,6 +36,7 @@ SIGNATURES = {
     "scr_cuda_init": (_i32, [_i32, ctypes.POINTER(_vp)]),
     "scr_cuda_destroy": (_i32, [_vp]),
     "scr_launch_count": (_i64, [_vp]),
+    "scr_device_status": (_i32, [_vp, _vp, ctypes.POINTER(_i32)]),
     "scr_affine_b4_repack_size": (_i32, [_i32, _i32, _i32, _psz]),
     "scr_affine_b4_repack": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp]),
     "scr_affine_b4_dequant_dump": (_i32, [_vp, _vp, _i32, _i32, _i32, _vp, _vp]),
@@ -89,6 +90,10 @@ class Context:
         if status != OK:
             detail = lib().scr_last_error(self._h)
             raise ScratchyCudaError(status, detail.decode() if detail else "")
+
+    def device_status(self, stream=None) -> None:
+        """Synchronise and raise if a bounded device-side wait ran out (`scr_device_status`)."""
+        self.check(lib().scr_device_status(self._h, stream, None))
 
     def launch_count(self) -> int:
         return int(lib().scr_launch_count(self._h))

@@ -39,12 +39,17 @@ extern "C" int32_t scr_cuda_init(int32_t device, scr_ctx** out) {
     c->sm_count = prop.multiProcessorCount;
     c->cc_major = prop.major;
     c->cc_minor = prop.minor;
+    if (cudaMalloc((void**)&c->dev_status, sizeof(int)) != cudaSuccess || cudaMemset(c->dev_status, 0, sizeof(int)) != cudaSuccess) {
+        delete c;
+        return SCR_E_CUDA;
+    }
     *out = c;
     return SCR_OK;
 }
 
 extern "C" int32_t scr_cuda_destroy(scr_ctx* ctx) {
     if (!ctx) return SCR_E_ARG;
+    if (ctx->dev_status) cudaFree(ctx->dev_status);
     delete ctx;
     return SCR_OK;
 }
@@ -57,4 +62,19 @@ extern "C" int32_t scr_linear_workspace_size(int32_t kind, int32_t M, int32_t N,
     if (kind == SCR_KIND_AFFINE_B4) { *bytes = affine_workspace_bytes(M, N, K); return SCR_OK; }
     if (kind == SCR_KIND_FP8_DYNAMIC) { *bytes = fp8_workspace_bytes(M, N, K); return SCR_OK; }
     return SCR_E_ARG;
+}
+
+extern "C" int32_t scr_device_status(scr_ctx* ctx, void* stream, int32_t* code) {
+    SCR_REQUIRE_CTX(ctx);
+    int host = 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e = cudaMemcpyAsync(&host, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "device status read: %s", cudaGetErrorString(e));
+    if (code) *code = host;
+    if (host != 0) {
+        cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), st);
+        return scr_fail(ctx, SCR_E_TIMEOUT, "a bounded device-side wait ran out (code %d)", host);
+    }
+    return SCR_OK;
 }

@@ -1,10 +1,205 @@
-// fp8-dynamic-per-channel: prefill GEMM on tcgen05 tensor cores (kind::f8f6f4).
-// (placeholder: the dispatcher uses token tiles through the matvec kernel until enabled)
+// fp8-dynamic-per-channel: prefill GEMM on tcgen05 tensor cores (kind::f8f6f4, e4m3 x e4m3,
+// f32 accumulators in TMEM), M > 16.
+//
+//   y[m,n] = bf16( (sum_k x_q[m,k] * w_q[n,k]) * a_scale[m] * w_scale[n] )
+//
+// Persistent, warp-specialised CTA (192 threads), one per SM:
+//   warp 0     producer: 1-D bulk (TMA) copies of pre-swizzled 16 KB tiles into a 4-stage ring
+//   warp 1     owns TMEM; one elected thread issues tcgen05.mma (A = 128 tokens, B = BN channels,
+//              4 x K=32 per 128-byte k-tile) and commits stage/accumulator barriers
+//   warps 2-5  epilogue: tcgen05.ld the 128 x BN f32 accumulator (thread = token row), apply
+//              (acc * a_scale[m]) * w_scale[n], round to bf16, 16-byte stores
+// Two accumulator buffers in TMEM (2 x BN columns) let the epilogue of tile i overlap the
+// main loop of tile i+1.  Both operands arrive in the exact K-major / 128-byte-swizzle image
+// the MMA reads (weights repacked at load time, activations written that way by the
+// quantisation kernel), so no tensor map and no multicast is involved.
 #include "fp8.cuh"
+#include "tc_common.cuh"
 
-bool fp8_gemm_tc_enabled() { return false; }
+bool fp8_gemm_tc_enabled() { return true; }
 size_t fp8_gemm_tc_workspace(int, int, int) { return 0; }
-int32_t fp8_gemm_tc_launch(scr_ctx* ctx, const uint8_t*, const uint8_t*, uint16_t*, int, int, int, void*, size_t,
-                           cudaStream_t) {
-    return scr_fail(ctx, SCR_E_UNSUPPORTED, "tensor-core fp8 GEMM not built");
+
+#define F8G_STAGES 4
+#define F8G_THREADS 192
+
+template <int BN>
+struct F8GSmem {
+    static constexpr uint32_t kStageBytes = 16384u + (uint32_t)BN * 128u;
+    static constexpr uint32_t kBarOffset = F8G_STAGES * kStageBytes;
+    static constexpr uint32_t kTotal = kBarOffset + 256u + 1024u;     // barriers + alignment slack
+};
+
+template <int BN>
+__global__ void __launch_bounds__(F8G_THREADS, 1)
+fp8_gemm_tc_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_scale, const uint8_t* __restrict__ xq,
+                   const float* __restrict__ a_scale, uint16_t* __restrict__ y, int M, int N, int KT, int NT, int MT,
+                   int M_pad, int* __restrict__ status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bar_base = smem_base + F8GSmem<BN>::kBarOffset;
+    // barrier slots (8 bytes each): full[S], empty[S], acc_full[2], acc_empty[2]; then the TMEM pointer
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (F8G_STAGES + s); };
+    auto accf_bar = [&](int b) { return bar_base + 8u * (2 * F8G_STAGES + b); };
+    auto acce_bar = [&](int b) { return bar_base + 8u * (2 * F8G_STAGES + 2 + b); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + F8GSmem<BN>::kBarOffset + 8 * (2 * F8G_STAGES + 4));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int NTB = (NT * 128 + BN - 1) / BN;            // channel tiles of BN
+    const int tiles = MT * NTB;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < F8G_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), 128); }
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32((const void*)tmem_slot), 2 * BN);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+                const int mt = tile % MT, nb = tile / MT;
+                const int nt0 = nb * (BN / 128);
+                const int ntn = min(BN / 128, NT - nt0);                  // 128-row weight tiles in this channel tile
+                for (int kt = 0; kt < KT; ++kt) {
+                    mbar_wait(empty_bar(s), ph ^ 1u, status, TC_ERR_EMPTY_WAIT);
+                    const uint32_t sa = smem_base + s * F8GSmem<BN>::kStageBytes;
+                    const uint32_t sb = sa + 16384u;
+                    mbar_arrive_expect_tx(full_bar(s), 16384u * (1 + ntn));
+                    bulk_g2s(sa, xq + (size_t)kt * ((size_t)M_pad * 128) + (size_t)mt * 16384, 16384u, full_bar(s));
+                    for (int j = 0; j < ntn; ++j)
+                        bulk_g2s(sb + j * 16384u, wpack + ((size_t)(nt0 + j) * KT + kt) * FP8_TILE_BYTES, 16384u, full_bar(s));
+                    if (++s == F8G_STAGES) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            int it = 0;
+            for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
+                const int nb = tile / MT;
+                const int nt0 = nb * (BN / 128);
+                const int ntn = min(BN / 128, NT - nt0);
+                const uint32_t idesc = umma_idesc(0, 0, 128, 128u * ntn);
+                const int buf = it & 1;
+                mbar_wait(acce_bar(buf), ((uint32_t)(it >> 1) & 1u) ^ 1u, status, TC_ERR_ACC_EMPTY);
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+                for (int kt = 0; kt < KT; ++kt) {
+                    mbar_wait(full_bar(s), ph, status, TC_ERR_FULL_WAIT);
+                    tc_fence_after();
+                    const uint32_t sa = smem_base + s * F8GSmem<BN>::kStageBytes;
+                    const uint64_t adesc = umma_desc_k_sw128(sa);
+                    const uint64_t bdesc = umma_desc_k_sw128(sa + 16384u);
+#pragma unroll
+                    for (int k4 = 0; k4 < 4; ++k4)
+                        umma_f8f6f4(d_tmem, adesc + (uint64_t)(2 * k4), bdesc + (uint64_t)(2 * k4), idesc, (kt | k4) != 0);
+                    umma_commit(empty_bar(s));
+                    if (++s == F8G_STAGES) { s = 0; ph ^= 1u; }
+                }
+                umma_commit(accf_bar(buf));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5)
+        const int q = warp & 3;                                   // TMEM lane quadrant this warp may read
+        const bool vec_ok = (N % 8) == 0;
+        int it = 0;
+        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
+            const int mt = tile % MT, nb = tile / MT;
+            const int n0 = nb * BN;
+            const int bn_cur = min(BN, NT * 128 - n0);
+            const int buf = it & 1;
+            mbar_wait(accf_bar(buf), (uint32_t)(it >> 1) & 1u, status, TC_ERR_ACC_FULL);
+            tc_fence_after();
+            const int m = mt * 128 + q * 32 + lane;
+            const float as = (m < M) ? a_scale[m] : 0.f;
+            uint16_t* yrow = y + (size_t)m * N;
+            for (int c = 0; c < bn_cur / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + c * 32), r);
+                tmem_ld_wait();
+                const int nc = n0 + c * 32;
+                if (m < M && nc < N) {
+                    uint32_t o[16];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float4 ws = __ldg(reinterpret_cast<const float4*>(w_scale + nc) + j);   // scales are padded to NT*128
+                        const float v0 = __fmul_rn(__fmul_rn(__uint_as_float(r[4 * j + 0]), as), ws.x);
+                        const float v1 = __fmul_rn(__fmul_rn(__uint_as_float(r[4 * j + 1]), as), ws.y);
+                        const float v2 = __fmul_rn(__fmul_rn(__uint_as_float(r[4 * j + 2]), as), ws.z);
+                        const float v3 = __fmul_rn(__fmul_rn(__uint_as_float(r[4 * j + 3]), as), ws.w);
+                        const __nv_bfloat162 p0 = __floats2bfloat162_rn(v0, v1);
+                        const __nv_bfloat162 p1 = __floats2bfloat162_rn(v2, v3);
+                        o[2 * j] = *reinterpret_cast<const uint32_t*>(&p0);
+                        o[2 * j + 1] = *reinterpret_cast<const uint32_t*>(&p1);
+                    }
+                    if (vec_ok && nc + 32 <= N) {
+                        uint4* dst = reinterpret_cast<uint4*>(yrow + nc);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) dst[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (nc + j < N) yrow[nc + j] = (uint16_t)((o[j >> 1] >> ((j & 1) * 16)) & 0xFFFFu);
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(acce_bar(buf));
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 2 * BN);
+    }
+}
+
+template <int BN>
+static int32_t fp8_gemm_launch_bn(scr_ctx* ctx, const uint8_t* wpack, const uint8_t* act, uint16_t* y, int M, int N, int K,
+                                  cudaStream_t stream) {
+    const Fp8Geom g = fp8_geom(N, K);
+    const float* w_scale = reinterpret_cast<const float*>(wpack + (size_t)g.NT * g.KT * FP8_TILE_BYTES);
+    const float* a_scale = reinterpret_cast<const float*>(act);
+    const uint8_t* xq = act + fp8_act_scale_bytes(M);
+    const int MT = scr_ceil_div(M, 128);
+    const int NTB = (g.NT * 128 + BN - 1) / BN;
+    const int tiles = MT * NTB;
+    const int grid = std::min(tiles, ctx->sm_count);
+    cudaError_t e = cudaFuncSetAttribute(fp8_gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)F8GSmem<BN>::kTotal);
+    if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "fp8_gemm smem attribute: %s", cudaGetErrorString(e));
+    fp8_gemm_tc_kernel<BN><<<grid, F8G_THREADS, F8GSmem<BN>::kTotal, stream>>>(wpack, w_scale, xq, a_scale, y, M, N, g.KT,
+                                                                              g.NT, MT, MT * 128, ctx->dev_status);
+    return scr_check_launch(ctx, "fp8_gemm_tc");
+}
+
+int32_t fp8_gemm_tc_launch(scr_ctx* ctx, const uint8_t* wpack, const uint8_t* act, uint16_t* y, int M, int N, int K, void*,
+                           size_t, cudaStream_t stream) {
+    if (((uintptr_t)(act + fp8_act_scale_bytes(M)) & 127u) != 0 || ((uintptr_t)wpack & 127u) != 0)
+        return scr_fail(ctx, SCR_E_ALIGN, "weight pack and activation pack must be 128-byte aligned for the GEMM path");
+    if (!scr_aligned16(y)) return scr_fail(ctx, SCR_E_ALIGN, "y must be 16-byte aligned");
+    // Wide channel tiles when there are enough of them to fill the machine, narrow otherwise.
+    const Fp8Geom g = fp8_geom(N, K);
+    const int MT = scr_ceil_div(M, 128);
+    const int tiles256 = MT * scr_ceil_div(g.NT, 2);
+    if (tiles256 >= ctx->sm_count) return fp8_gemm_launch_bn<256>(ctx, wpack, act, y, M, N, K, stream);
+    return fp8_gemm_launch_bn<128>(ctx, wpack, act, y, M, N, K, stream);
 }

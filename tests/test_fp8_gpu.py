@@ -140,3 +140,55 @@ def test_determinism_full_size():
     torch.cuda.synchronize()
     assert torch.equal(y1, y2)
     assert torch.equal(y1 * 2, y3)       # the per-token scale doubles, x_q is unchanged
+
+
+# ---------------------------------------------------------------- prefill (tensor-core GEMM, M > 16)
+def _device_ok():
+    from scratchy_b200 import _lib
+    _lib.context(0).device_status()
+
+
+@pytest.mark.parametrize("N,K,M", [(128, 128, 32), (128, 256, 128), (256, 512, 130), (384, 200, 200), (130, 328, 77),
+                                   (512, 384, 300)])
+def test_prefill_gemm_small(N, K, M):
+    got, want = run_case(N, K, M, synth.seed_for("g8", N, K, M))
+    _device_ok()
+    r = rel_l2(got, want)
+    print(f"N={N} K={K} M={M} rel_l2={r:.3e} max_abs={max_abs(got, want):.3e}")
+    assert r <= REL_L2_TOL
+
+
+@pytest.mark.parametrize("name,M", [("k", 256), ("q", 256)])
+def test_prefill_gemm_qwen_shapes_full_oracle(name, M):
+    K, N = synth.QWEN_2_5_7B[name]
+    got, want = run_case(N, K, M, synth.seed_for("g8f", N, K, M))
+    _device_ok()
+    r = rel_l2(got, want)
+    print(f"{name} M={M} rel_l2={r:.3e} max_abs={max_abs(got, want):.3e}")
+    assert r <= REL_L2_TOL
+
+
+@pytest.mark.parametrize("name,M", [("gate", 2048), ("down", 2048), ("gate", 8192)])
+def test_prefill_gemm_full_size_sampled_rows(name, M):
+    """Full BASELINE sizes: oracle on a seeded subset of 16 token rows; x_q and a_scale of those rows
+    must be bit-exact and the outputs within tolerance; the whole output must be finite."""
+    import torch
+    from scratchy_b200 import Fp8Linear
+    K, N = synth.QWEN_2_5_7B[name]
+    wq, ws = oracle.fp8_quantize_weight_per_channel(synth.fp8_weights_f32(N, K, synth.seed_for("g8s", N, K)))
+    x = synth.activations_bf16(M, K, synth.seed_for("g8sx", M, K))
+    layer = make_layer(wq, ws)
+    xdev = bf16_dev(x).reshape(M, K)
+    y = layer.forward(xdev)
+    torch.cuda.synchronize()
+    _device_ok()
+    assert bool(torch.isfinite(y.float()).all())
+    rows = np.sort(np.random.default_rng(1).choice(M, 16, replace=False))
+    xq_want, a_want = oracle.fp8_quant_per_token(x[rows], len(rows), K)
+    xq, a = Fp8Linear.quantize_activation(xdev).unpack()
+    assert np.array_equal(xq.cpu().numpy()[rows], xq_want) and np.array_equal(a.cpu().numpy()[rows], a_want)
+    want = oracle.fp8_linear(xq_want, a_want, wq, ws, len(rows), N, K)
+    got = bits_of(y).reshape(M, N)[rows]
+    r = rel_l2(got, want)
+    print(f"{name} M={M} sampled rel_l2={r:.3e} max_abs={max_abs(got, want):.3e}")
+    assert r <= REL_L2_TOL
