@@ -242,17 +242,32 @@ def run_gpu(args):
     # ---- end to end: host (pinned) activations in, host results out, through the public API.
     # Every linear's input is copied from pinned host memory and its output copied back inside
     # the timed region; the copies are captured in the same graph as the launches.
-    hx = [torch.randn((M, K)).to(torch.bfloat16).pin_memory() for K, _ in shapes]
-    hy = [torch.empty((M, N), dtype=torch.bfloat16).pin_memory() for _, N in shapes]
-    h2d = N_LAYERS * sum(t.numel() * 2 for t in hx)
-    d2h = N_LAYERS * sum(t.numel() * 2 for t in hy)
+    # One pinned staging buffer holds the step's activations (one row-set per linear of every
+    # layer) and one receives all outputs: one H2D and one D2H copy per step.
+    in_elems = [M * K for K, _ in shapes]
+    out_elems = [M * N for _, N in shapes]
+    h_in = torch.randn(N_LAYERS * sum(in_elems)).to(torch.bfloat16).pin_memory()
+    h_out = torch.empty(N_LAYERS * sum(out_elems), dtype=torch.bfloat16).pin_memory()
+    d_in = torch.empty_like(h_in, device=device)
+    d_out = torch.empty_like(h_out, device=device)
+    h2d = h_in.numel() * 2
+    d2h = h_out.numel() * 2
+    views = []
+    oi = oo = 0
+    for li in range(N_LAYERS):
+        row = []
+        for (K, N), ne_i, ne_o in zip(shapes, in_elems, out_elems):
+            row.append((d_in[oi:oi + ne_i].view(M, K), d_out[oo:oo + ne_o].view(M, N)))
+            oi += ne_i
+            oo += ne_o
+        views.append(row)
 
     def step_e2e():
-        for row in layers:
-            for lin, x, y, cx, cy in zip(row, xs, ys, hx, hy):
-                x.copy_(cx, non_blocking=True)
+        d_in.copy_(h_in, non_blocking=True)
+        for row, vrow in zip(layers, views):
+            for lin, (x, y) in zip(row, vrow):
                 lin.forward(x, out=y)
-                cy.copy_(y, non_blocking=True)
+        h_out.copy_(d_out, non_blocking=True)
 
     step_e2e()
     barrier()
@@ -311,29 +326,37 @@ def run_gpu(args):
 
 
 def run_sweep(device, ctx):
-    """Extra (not the headline): per-shape timings over M for int4 (3B shapes) and fp8 (7B shapes)."""
+    """Extra (not the headline): per-shape timings over M for int4 (3B shapes) and fp8 (7B shapes).
+    Each case cycles over enough distinct weight copies that consecutive calls miss L2, captured
+    as one CUDA graph of `reps` calls and replayed."""
     import torch
     from scratchy_b200 import AffineQuantLinear, Fp8Linear
     peaks = measured_peaks()
     out = []
+    side = torch.cuda.Stream(device)
 
-    def timeit(fn, reps):
+    def time_graph(calls, replays):
+        for c in calls[:2]:
+            c()
+        torch.cuda.synchronize(device)
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr, stream=side):
+            for c in calls:
+                c()
         for _ in range(3):
-            fn()
+            gr.replay()
         torch.cuda.synchronize(device)
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        for _ in range(reps):
-            fn()
+        for _ in range(replays):
+            gr.replay()
         b.record()
         torch.cuda.synchronize(device)
-        return a.elapsed_time(b) * 1e-3 / reps
+        return a.elapsed_time(b) * 1e-3 / (replays * len(calls))
 
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
     for name in ["q", "k", "gate", "down"]:
         K, N = synth.LLAMA_3_2_3B[name]
-        # enough distinct copies that consecutive calls miss L2
-        copies = max(2, int((192 << 20) // (N * K * 9 // 16)) + 1)
+        copies = max(2, int((256 << 20) // (N * K * 9 // 16)) + 1)
         lins = []
         for c in range(copies):
             w = torch.randint(-2 ** 31, 2 ** 31 - 1, (N, K // 8), dtype=torch.int32, device=device)
@@ -344,12 +367,9 @@ def run_sweep(device, ctx):
             x = torch.randn((M, K), device=device).to(torch.bfloat16)
             y = torch.empty((M, N), dtype=torch.bfloat16, device=device)
             ws = torch.empty(max(16, lins[0].workspace_bytes(M)), dtype=torch.uint8, device=device)
-            idx = [0]
-
-            def fn():
-                lins[idx[0] % copies].forward(x, out=y, workspace=ws)
-                idx[0] += 1
-            dt = timeit(fn, 20 if M <= 64 else 5)
+            reps = copies if M <= 64 else min(copies, 8)
+            calls = [(lambda l=l: l.forward(x, out=y, workspace=ws)) for l in lins[:reps]]
+            dt = time_graph(calls, 5 if M <= 64 else 2)
             out.append({"kind": "int4", "shape": name, "M": M, "N": N, "K": K, "us": dt * 1e6,
                         "GBps": affine_alg_bytes(M, N, K) / dt / 1e9, "TFLOPs": 2.0 * M * N * K / dt / 1e12,
                         "frac_hbm": affine_alg_bytes(M, N, K) / dt / 1e9 / peaks["hbm_gbs"],
@@ -357,7 +377,7 @@ def run_sweep(device, ctx):
         del lins
     for name in ["q", "k", "gate", "down"]:
         K, N = synth.QWEN_2_5_7B[name]
-        copies = max(2, int((192 << 20) // (N * K)) + 1)
+        copies = max(2, int((256 << 20) // (N * K)) + 1)
         lins = []
         for c in range(copies):
             w = torch.randint(0, 120, (N, K), dtype=torch.uint8, device=device)
@@ -366,17 +386,14 @@ def run_sweep(device, ctx):
             x = torch.randn((M, K), device=device).to(torch.bfloat16)
             y = torch.empty((M, N), dtype=torch.bfloat16, device=device)
             ws = torch.empty(lins[0].workspace_bytes(M), dtype=torch.uint8, device=device)
-            idx = [0]
-
-            def fn():
-                lins[idx[0] % copies].forward(x, out=y, workspace=ws)
-                idx[0] += 1
-            dt = timeit(fn, 20 if M <= 16 else 3)
+            reps = copies if M <= 256 else min(copies, 4)
+            calls = [(lambda l=l: l.forward(x, out=y, workspace=ws)) for l in lins[:reps]]
+            dt = time_graph(calls, 5 if M <= 256 else 2)
             out.append({"kind": "fp8", "shape": name, "M": M, "N": N, "K": K, "us": dt * 1e6,
                         "GBps": fp8_alg_bytes(M, N, K) / dt / 1e9, "TFLOPs": 2.0 * M * N * K / dt / 1e12,
-                        "frac_hbm": fp8_alg_bytes(M, N, K) / dt / 1e9 / peaks["hbm_gbs"]})
+                        "frac_hbm": fp8_alg_bytes(M, N, K) / dt / 1e9 / peaks["hbm_gbs"],
+                        "note": "per-token quantise + contraction (two launches)"})
         del lins
-    del flush
     return out
 
 

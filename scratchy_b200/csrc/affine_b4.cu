@@ -81,20 +81,77 @@ __global__ void affine_b4_dump_kernel(const uint8_t* __restrict__ packed, int N,
     }
 }
 
+// ---- small PTX helpers for the matvec kernels ------------------------------------------
+__device__ __forceinline__ uint32_t gemv_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void gemv_mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void gemv_fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void gemv_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void gemv_bulk_g2s(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+// Bounded wait on a stage barrier: gives up after 2^20 polls (or as soon as another waiter has
+// recorded a failure), records code 6 in the status word and lets the kernel run to its end.
+__device__ __forceinline__ void gemv_wait(uint32_t bar, uint32_t parity, int* status) {
+    for (uint32_t i = 0; i < (1u << 20); ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return;
+        if ((i & 255u) == 255u && *reinterpret_cast<volatile int*>(status) != 0) return;
+    }
+    atomicCAS(status, 0, 6);
+}
+__device__ __forceinline__ uint4 gemv_lds_v4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 gemv_lds_v2(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t gemv_cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void gemv_cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void gemv_st_cluster_rank0_f32(const float* local_ptr, float v) {
+    const uint32_t local = (uint32_t)__cvta_generic_to_shared(local_ptr);
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(0));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+
 // ------------------------------------------------------------------------------------
 // Decode matvec, M <= 16.
 //
-// A warp owns one row-block (16 weight rows) over a set of k-chunks and feeds
-// mma.sync.m16n8k16 (bf16 x bf16 -> f32) with the dequantised weights as the A operand
-// straight from registers; the tokens are the 8 columns of the B operand (MT = 1: up to 8
-// tokens, MT = 2: up to 16).  Lane (g, t) holds codes of rows g and g+8 at
-// k = 128kc + 32t + [0,32) and the activations of token g (and g+8) at the same k, so the
+// Persistent CTAs of 8 warps.  A CTA walks row-blocks (16 weight rows) rb = blockIdx.x,
+// += gridDim.x; its warps interleave the row-block's k-chunks (warp w takes kc = w, w+8, ...),
+// so the cross-warp reduction stays inside the CTA: partial accumulators go through
+// double-buffered shared memory once per row-block, in fixed warp order (deterministic).
+//
+// Weights stream HBM -> shared memory through per-warp rings of 1-D bulk (TMA) copies, one
+// 1152-byte block per stage, each stage with its own mbarrier; the ring runs ahead across
+// row-block boundaries, so GEMV_STAGES-1 blocks per warp are always in flight.  A stage is read
+// back with two conflict-free 16-byte loads per lane and dequantised in registers; the
+// dequantised bf16 weights are the A operand of mma.sync.m16n8k16 and the tokens the 8 columns
+// of B (MT = 1: up to 8 tokens, MT = 2: up to 16).  Lane (g, t) holds codes of rows g and g+8
+// at k = 128kc + 32t + [0,32) and the activations of token g (and g+8) at the same k, so the
 // contraction index is permuted identically on both operands.
 //
-// Grid: (RB_real, SPLIT).  The 8 warps of a CTA interleave the CTA's k-chunks; partial
-// sums are reduced through shared memory in warp order, and, when SPLIT > 1, across the
-// SPLIT CTAs of a thread-block cluster through distributed shared memory in rank order
-// (deterministic; no global scratch).
+// When there are too few row-blocks to fill the machine, gridDim.y = SPLIT CTAs form a
+// thread-block cluster that splits the k-chunks and reduces through distributed shared memory
+// in rank order.  Every wait is bounded (see gemv_wait).
 // ------------------------------------------------------------------------------------
 __device__ __forceinline__ void mma_bf16_16816(float d[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                uint32_t b0, uint32_t b1) {
@@ -104,41 +161,17 @@ __device__ __forceinline__ void mma_bf16_16816(float d[4], uint32_t a0, uint32_t
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ uint32_t map_to_cluster_rank(uint32_t smem_addr, uint32_t rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
-    return r;
-}
-__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
-    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
-}
-
-#define GEMV_WARPS 4
-#define GEMV_STAGES 4
+#define GEMV_WARPS 8
+#define GEMV_STAGES 6
 #define GEMV_MAX_SPLIT 8
 
-struct GemvStage {
-    uint4 p0, p1;   // codes of rows g / g+8
-    uint2 sb;       // (scale, bias) of rows g / g+8
-};
-
-__device__ __forceinline__ void gemv_stage_load(GemvStage& s, const uint8_t* blk, int lane) {
-    s.p0 = ld_stream_v4(blk + lane * 16);
-    s.p1 = ld_stream_v4(blk + 512 + lane * 16);
-    s.sb = ld_stream_v2(blk + 1024 + ((lane >> 2) * 2 + ((lane & 3) >> 1)) * 8);
-}
-
 template <int MT>
-__device__ __forceinline__ void gemv_stage_compute(const GemvStage& s, float acc[MT][4], const uint16_t* __restrict__ x,
-                                                   int kc, int K, int g, int t, bool tok_ok0, bool tok_ok1) {
+__device__ __forceinline__ void gemv_block_compute(uint32_t stage, float acc[MT][4], const uint16_t* __restrict__ x,
+                                                   int kc, int K, int lane, bool tok_ok0, bool tok_ok1) {
+    const int g = lane >> 2, t = lane & 3;
+    const uint4 p0 = gemv_lds_v4(stage + lane * 16);
+    const uint4 p1 = gemv_lds_v4(stage + 512 + lane * 16);
+    const uint2 sb = gemv_lds_v2(stage + 1024 + (g * 2 + (t >> 1)) * 8);
     const int k0 = kc * 128 + t * 32;
     uint32_t xr[MT][16];
 #pragma unroll
@@ -153,8 +186,8 @@ __device__ __forceinline__ void gemv_stage_compute(const GemvStage& s, float acc
         }
     }
     uint32_t w0[16], w1[16];
-    affine_dequant_piece(s.p0, s.sb.x, w0);
-    affine_dequant_piece(s.p1, s.sb.y, w1);
+    affine_dequant_piece(p0, sb.x, w0);
+    affine_dequant_piece(p1, sb.y, w1);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
 #pragma unroll
@@ -168,113 +201,120 @@ __device__ __forceinline__ void gemv_stage_compute(const GemvStage& s, float acc
 }
 
 template <int MT, int SPLIT_CLUSTER>
-__global__ void __launch_bounds__(GEMV_WARPS * 32)
+__global__ void __launch_bounds__(GEMV_WARPS * 32, 2)
 affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __restrict__ x, uint16_t* __restrict__ y,
-                      int M, int N, int K, int RB, int KC, int split) {
-    // [warp][lane][MT*4] partials, then (cluster) [rank][16 rows][MT*8 tokens]
-    __shared__ float red[GEMV_WARPS][32][MT * 4];
+                      int M, int N, int K, int RB, int KC, int rb_real, int split, int* __restrict__ status) {
+    extern __shared__ __align__(128) uint8_t gemv_ring[];          // [GEMV_WARPS][GEMV_STAGES][AFF_BLOCK_BYTES]
+    __shared__ __align__(8) uint64_t bars[GEMV_WARPS][GEMV_STAGES];
+    __shared__ float red[2][GEMV_WARPS][32][MT * 4];
     __shared__ float cl_part[SPLIT_CLUSTER ? GEMV_MAX_SPLIT : 1][16][MT * 8];
 
-    const int rb = blockIdx.x;
-    const int sp = SPLIT_CLUSTER ? int(cluster_ctarank()) : 0;
+    const int sp = SPLIT_CLUSTER ? int(gemv_cluster_ctarank()) : 0;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int g = lane >> 2, t = lane & 3;
+    const int g = lane >> 2;
 
-    // k-chunks of this CTA: [kc_lo, kc_hi), interleaved over the warps
+    // k-chunks of this CTA: [kc_lo, kc_hi); warp w takes kc_lo + w, + GEMV_WARPS, ...
     const int per = (KC + split - 1) / split;
     const int kc_lo = sp * per;
     const int kc_hi = min(KC, kc_lo + per);
+    const int kc_first = kc_lo + warp;
+    const bool has_work = kc_first < kc_hi;
 
-    float acc[MT][4];
+    if (lane == 0) {
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) acc[mt][i] = 0.f;
-
-    const size_t chunk_stride = (size_t)RB * AFF_BLOCK_BYTES;
-    const uint8_t* base = packed + (size_t)rb * AFF_BLOCK_BYTES;
-    const bool tok_ok0 = g < M;
-    const bool tok_ok1 = (MT > 1) && (g + 8 < M);
-
-    // register ring of GEMV_STAGES chunks in flight per warp
-    GemvStage st[GEMV_STAGES];
-    int kc = kc_lo + warp;
-#pragma unroll
-    for (int d = 0; d < GEMV_STAGES; ++d) {
-        const int k = kc + d * GEMV_WARPS;
-        if (k < kc_hi) gemv_stage_load(st[d], base + (size_t)k * chunk_stride, lane);
+        for (int d = 0; d < GEMV_STAGES; ++d) gemv_mbar_init(gemv_smem_u32(&bars[warp][d]), 1);
     }
-    for (; kc < kc_hi; kc += GEMV_STAGES * GEMV_WARPS) {
-#pragma unroll
-        for (int d = 0; d < GEMV_STAGES; ++d) {
-            const int kcur = kc + d * GEMV_WARPS;
-            if (kcur < kc_hi) {
-                const GemvStage cur = st[d];
-                const int knext = kcur + GEMV_STAGES * GEMV_WARPS;
-                if (knext < kc_hi) gemv_stage_load(st[d], base + (size_t)knext * chunk_stride, lane);
-                gemv_stage_compute<MT>(cur, acc, x, kcur, K, g, t, tok_ok0, tok_ok1);
-            }
-        }
-    }
-
-    // cross-warp reduction, fixed warp order
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) red[warp][lane][mt * 4 + i] = acc[mt][i];
+    gemv_fence_mbar_init();
     __syncthreads();
 
-    // MT*4 accumulator slots per lane: thread e sums slot (ln, idx) over the warps
-    constexpr int SLOTS = 32 * MT * 4;
-    static_assert(SLOTS % (GEMV_WARPS * 32) == 0 || SLOTS <= GEMV_WARPS * 32, "slot mapping");
-    constexpr int PER_THREAD = (SLOTS + GEMV_WARPS * 32 - 1) / (GEMV_WARPS * 32);
-    float total[PER_THREAD];
-    int row[PER_THREAD], tok[PER_THREAD];
+    const size_t chunk_stride = (size_t)RB * AFF_BLOCK_BYTES;
+    const uint32_t ring_base = gemv_smem_u32(gemv_ring) + (uint32_t)warp * (GEMV_STAGES * AFF_BLOCK_BYTES);
+    const uint32_t bar_base = gemv_smem_u32(&bars[warp][0]);
+
+    // producer cursor (only lane 0 uses it): next block to request, in consumption order
+    int prb = blockIdx.x, pkc = kc_first, pslot = 0;
+    auto issue = [&]() {
+        if (has_work && prb < rb_real) {
+            const uint32_t bar = bar_base + 8u * pslot;
+            gemv_arrive_expect_tx(bar, AFF_BLOCK_BYTES);
+            gemv_bulk_g2s(ring_base + pslot * AFF_BLOCK_BYTES, packed + (size_t)pkc * chunk_stride + (size_t)prb * AFF_BLOCK_BYTES,
+                          AFF_BLOCK_BYTES, bar);
+            pkc += GEMV_WARPS;
+            if (pkc >= kc_hi) { pkc = kc_first; prb += gridDim.x; }
+        }
+        pslot = (pslot + 1 == GEMV_STAGES) ? 0 : pslot + 1;
+    };
+    if (lane == 0) {
+#pragma unroll 1
+        for (int d = 0; d < GEMV_STAGES; ++d) issue();
+    }
+
+    const bool tok_ok0 = g < M;
+    const bool tok_ok1 = (MT > 1) && (g + 8 < M);
+    int slot = 0;
+    uint32_t phases = 0;                       // bit d = parity the next wait on stage d expects
+    int it = 0;
+
+    for (int rb = blockIdx.x; rb < rb_real; rb += gridDim.x, ++it) {
+        float acc[MT][4];
 #pragma unroll
-    for (int u = 0; u < PER_THREAD; ++u) {
-        const int e = threadIdx.x + u * GEMV_WARPS * 32;
-        total[u] = 0.f; row[u] = 0; tok[u] = 0;
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[mt][i] = 0.f;
+
+        for (int kc = kc_first; kc < kc_hi; kc += GEMV_WARPS) {
+            gemv_wait(bar_base + 8u * slot, (phases >> slot) & 1u, status);
+            gemv_block_compute<MT>(ring_base + slot * AFF_BLOCK_BYTES, acc, x, kc, K, lane, tok_ok0, tok_ok1);
+            phases ^= 1u << slot;
+            __syncwarp();                      // every lane has consumed the stage: refill it
+            if (lane == 0) issue();
+            slot = (slot + 1 == GEMV_STAGES) ? 0 : slot + 1;
+        }
+
+        // cross-warp reduction of this row-block, fixed warp order, double-buffered
+        const int buf = it & 1;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) red[buf][warp][lane][mt * 4 + i] = acc[mt][i];
+        __syncthreads();
+
+        // thread e owns accumulator slot (ln, idx): c0,c1 -> row g, tokens 2t,2t+1 ; c2,c3 -> row g+8
+        constexpr int SLOTS = 32 * MT * 4;     // <= 256 = blockDim.x
+        const int e = threadIdx.x;
         if (e < SLOTS) {
             const int ln = e / (MT * 4), idx = e % (MT * 4);
             const int mt = idx >> 2, i = idx & 3;
+            const int row = (ln >> 2) + ((i >> 1) ? 8 : 0);
+            const int tok = mt * 8 + (ln & 3) * 2 + (i & 1);
+            const int n = rb * 16 + row;
+            if (tok < M) {
+                float total = 0.f;
 #pragma unroll
-            for (int wdx = 0; wdx < GEMV_WARPS; ++wdx) total[u] += red[wdx][ln][idx];
-            // accumulator fragment: c0,c1 -> row g, tokens 2t,2t+1 ; c2,c3 -> row g+8
-            row[u] = (ln >> 2) + ((i >> 1) ? 8 : 0);
-            tok[u] = mt * 8 + (ln & 3) * 2 + (i & 1);
-        }
-    }
-
-    if (SPLIT_CLUSTER) {
-        // every CTA of the cluster deposits its partials in rank 0's shared memory
-#pragma unroll
-        for (int u = 0; u < PER_THREAD; ++u) {
-            const int e = threadIdx.x + u * GEMV_WARPS * 32;
-            if (e < SLOTS) {
-                const uint32_t local = (uint32_t)__cvta_generic_to_shared(&cl_part[sp][row[u]][tok[u]]);
-                st_cluster_f32(map_to_cluster_rank(local, 0), total[u]);
+                for (int wdx = 0; wdx < GEMV_WARPS; ++wdx) total += red[buf][wdx][ln][idx];
+                if (SPLIT_CLUSTER) {
+                    gemv_st_cluster_rank0_f32(&cl_part[sp][row][tok], total);
+                } else if (n < N) {
+                    const __nv_bfloat16 v = __float2bfloat16_rn(total);
+                    y[(size_t)tok * N + n] = *reinterpret_cast<const uint16_t*>(&v);
+                }
             }
         }
-        cluster_sync_all();
-        if (sp != 0) return;
-#pragma unroll
-        for (int u = 0; u < PER_THREAD; ++u) {
-            const int e = threadIdx.x + u * GEMV_WARPS * 32;
-            if (e < SLOTS) {
-                float s = 0.f;
-                for (int r = 0; r < split; ++r) s += cl_part[r][row[u]][tok[u]];   // rank order
-                total[u] = s;
-            }
-        }
-    }
-#pragma unroll
-    for (int u = 0; u < PER_THREAD; ++u) {
-        const int e = threadIdx.x + u * GEMV_WARPS * 32;
-        if (e < SLOTS) {
-            const int n = rb * 16 + row[u];
-            if (n < N && tok[u] < M) {
-                const __nv_bfloat16 v = __float2bfloat16_rn(total[u]);
-                y[(size_t)tok[u] * N + n] = *reinterpret_cast<const uint16_t*>(&v);
+        if (SPLIT_CLUSTER) {
+            // one row-block per CTA in cluster mode (gridDim.x == rb_real): exchange once
+            gemv_cluster_sync_all();
+            if (sp == 0 && e < SLOTS) {
+                const int ln = e / (MT * 4), idx = e % (MT * 4);
+                const int mt = idx >> 2, i = idx & 3;
+                const int row = (ln >> 2) + ((i >> 1) ? 8 : 0);
+                const int tok = mt * 8 + (ln & 3) * 2 + (i & 1);
+                const int n = rb * 16 + row;
+                if (tok < M && n < N) {
+                    float s = 0.f;
+                    for (int r = 0; r < split; ++r) s += cl_part[r][row][tok];   // rank order
+                    const __nv_bfloat16 v = __float2bfloat16_rn(s);
+                    y[(size_t)tok * N + n] = *reinterpret_cast<const uint16_t*>(&v);
+                }
             }
         }
     }
@@ -331,21 +371,19 @@ extern "C" int32_t scr_affine_b4_dequant_dump(scr_ctx* ctx, const void* packed, 
     return scr_check_launch(ctx, "affine_b4_dequant_dump");
 }
 
-// Split of a row-block's k-chunks over the CTAs of a cluster.  Cost model: the busiest
-// SM runs ceil(ctas / sms) CTAs back to back, each as long as its busiest warp
-// (ceil(chunks_per_cta / warps) chunks); a split adds the cluster exchange.
-static int affine_gemv_pick_split(int rb_real, int KC, int sms) {
-    int best = 1;
-    long long best_cost = -1;
-    for (int s = 1; s <= GEMV_MAX_SPLIT && s <= KC; ++s) {
-        const long long ctas = (long long)rb_real * s;
-        const long long per_sm = (ctas + sms - 1) / sms;
-        const int cpc = (KC + s - 1) / s;
-        const int cpw = (cpc + GEMV_WARPS - 1) / GEMV_WARPS;
-        const long long cost = per_sm * cpw * 8 + (s > 1 ? per_sm * 2 : 0);
-        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = s; }
+// Launch shape.  With enough row-blocks the grid is persistent (two CTAs per SM) and nothing
+// is split; with few row-blocks each CTA takes one row-block and a cluster of `split` CTAs
+// shares its k-chunks so that about one CTA per SM is busy.
+static void affine_gemv_shape(int rb_real, int KC, int sms, int* grid_x, int* split) {
+    if (rb_real >= sms) {
+        *grid_x = std::min(rb_real, 2 * sms);
+        *split = 1;
+        return;
     }
-    return best;
+    int s = 1;
+    while (s * 2 <= GEMV_MAX_SPLIT && rb_real * s * 2 <= 2 * sms && KC / (s * 2) >= GEMV_WARPS / 2) s *= 2;
+    *grid_x = rb_real;
+    *split = s;
 }
 
 template <int MT>
@@ -353,15 +391,22 @@ static int32_t affine_gemv_launch(scr_ctx* ctx, const uint8_t* packed, const uin
                                   int K, cudaStream_t stream) {
     const AffineGeom g = affine_geom(N, K);
     const int rb_real = scr_ceil_div(N, 16);
-    const int split = affine_gemv_pick_split(rb_real, g.KC, ctx->sm_count);
+    int grid_x = 1, split = 1;
+    affine_gemv_shape(rb_real, g.KC, ctx->sm_count, &grid_x, &split);
+    constexpr int kRingBytes = GEMV_WARPS * GEMV_STAGES * AFF_BLOCK_BYTES;
     if (split == 1) {
-        affine_b4_gemv_kernel<MT, 0><<<dim3(rb_real, 1), GEMV_WARPS * 32, 0, stream>>>(packed, x, y, M, N, K, g.RB, g.KC, 1);
+        cudaError_t e0 = cudaFuncSetAttribute(affine_b4_gemv_kernel<MT, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes);
+        if (e0 != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine_b4_gemv smem attribute: %s", cudaGetErrorString(e0));
+        affine_b4_gemv_kernel<MT, 0><<<dim3(grid_x, 1), GEMV_WARPS * 32, kRingBytes, stream>>>(packed, x, y, M, N, K, g.RB, g.KC,
+                                                                                              rb_real, 1, ctx->dev_status);
         return scr_check_launch(ctx, "affine_b4_gemv");
     }
+    cudaError_t e1 = cudaFuncSetAttribute(affine_b4_gemv_kernel<MT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes);
+    if (e1 != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine_b4_gemv smem attribute: %s", cudaGetErrorString(e1));
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(rb_real, split, 1);
+    cfg.gridDim = dim3(grid_x, split, 1);
     cfg.blockDim = dim3(GEMV_WARPS * 32, 1, 1);
-    cfg.dynamicSmemBytes = 0;
+    cfg.dynamicSmemBytes = kRingBytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -370,7 +415,8 @@ static int32_t affine_gemv_launch(scr_ctx* ctx, const uint8_t* packed, const uin
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, affine_b4_gemv_kernel<MT, 1>, packed, x, y, M, N, K, g.RB, g.KC, split);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, affine_b4_gemv_kernel<MT, 1>, packed, x, y, M, N, K, g.RB, g.KC, rb_real, split,
+                                       ctx->dev_status);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine_b4_gemv cluster launch: %s", cudaGetErrorString(e));
     return scr_check_launch(ctx, "affine_b4_gemv(cluster)");
 }

@@ -131,13 +131,17 @@ __global__ void e4m3_encode_kernel(const float* __restrict__ v, long long count,
 }
 
 // ------------------------------------------------------------------------------------
-// Decode matvec, M <= 16: weights go from HBM straight into the A operand of
-// mma.sync.m16n8k32 (e4m3 x e4m3 -> f32); no dequantisation arithmetic at all.
-// A warp owns 16 weight rows (two 8-row swizzle groups of a tile) over a set of k-tiles;
-// lane (g, t) loads the 16-byte chunks t and t+4 of rows g and g+8 and the same chunks of
-// token g's quantised activations, so both operands see the same permutation of k.
-// Grid (ceil(N/16), split); split > 1 runs as a thread-block cluster and reduces over
-// distributed shared memory in rank order.
+// Decode matvec, M <= 16: e4m3 weights are the A operand of mma.sync.m16n8k32
+// (e4m3 x e4m3 -> f32) exactly as stored; there is no dequantisation arithmetic.
+//
+// Persistent CTAs of 8 warps walk row-blocks (16 weight rows = two 8-row swizzle groups of a
+// 128 x 128 tile, 2 KB per k-tile) rb = blockIdx.x, += gridDim.x; the warps interleave the
+// k-tiles and reduce through double-buffered shared memory in warp order.  Weights stream
+// HBM -> shared memory through per-warp rings of 1-D bulk (TMA) copies (2 KB per stage, one
+// mbarrier each, running ahead across row-blocks).  Lane (g, t) reads the 16-byte chunks t and
+// t+4 of rows g and g+8 and the same chunks of token g's quantised activations, so both
+// operands see the same permutation of k.  With few row-blocks, gridDim.y = SPLIT CTAs form a
+// cluster that splits the k-tiles and reduces over distributed shared memory in rank order.
 // ------------------------------------------------------------------------------------
 __device__ __forceinline__ void mma_e4m3_16832(float d[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                uint32_t b0, uint32_t b1) {
@@ -146,6 +150,7 @@ __device__ __forceinline__ void mma_e4m3_16832(float d[4], uint32_t a0, uint32_t
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ uint32_t f8v_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ uint32_t fp8_cluster_ctarank() {
     uint32_t r;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -160,27 +165,36 @@ __device__ __forceinline__ void fp8_st_cluster_rank0_f32(const float* local_ptr,
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(0));
     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }
-
-#define F8V_WARPS 4
-#define F8V_STAGES 4
-#define F8V_MAX_SPLIT 8
-
-struct F8Stage {
-    uint4 a_lo, a_hi;     // row g: chunks t, t+4
-    uint4 b_lo, b_hi;     // row g+8
-};
-
-__device__ __forceinline__ void f8_stage_load(F8Stage& s, const uint8_t* rowblk, int g, int t) {
-    const uint8_t* r0 = rowblk + g * 128;
-    s.a_lo = ld_stream_v4(r0 + ((t ^ g) << 4));
-    s.a_hi = ld_stream_v4(r0 + (((t + 4) ^ g) << 4));
-    s.b_lo = ld_stream_v4(r0 + 1024 + ((t ^ g) << 4));
-    s.b_hi = ld_stream_v4(r0 + 1024 + (((t + 4) ^ g) << 4));
+__device__ __forceinline__ void f8v_wait(uint32_t bar, uint32_t parity, int* status) {
+    for (uint32_t i = 0; i < (1u << 20); ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return;
+        if ((i & 255u) == 255u && *reinterpret_cast<volatile int*>(status) != 0) return;
+    }
+    atomicCAS(status, 0, 7);
+}
+__device__ __forceinline__ uint4 f8v_lds_v4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
 }
 
+#define F8V_WARPS 8
+#define F8V_STAGES 5
+#define F8V_STAGE_BYTES 2048
+#define F8V_MAX_SPLIT 8
+
 template <int MT>
-__device__ __forceinline__ void f8_stage_compute(const F8Stage& s, float acc[MT][4], const uint8_t* __restrict__ xq,
+__device__ __forceinline__ void f8_block_compute(uint32_t stage, float acc[MT][4], const uint8_t* __restrict__ xq,
                                                  int kt, int K16, int g, int t, bool ok0, bool ok1) {
+    const uint32_t r0 = stage + g * 128;
+    const uint4 a_lo = f8v_lds_v4(r0 + ((t ^ g) << 4));
+    const uint4 a_hi = f8v_lds_v4(r0 + (((t + 4) ^ g) << 4));
+    const uint4 b_lo = f8v_lds_v4(r0 + 1024 + ((t ^ g) << 4));
+    const uint4 b_hi = f8v_lds_v4(r0 + 1024 + (((t + 4) ^ g) << 4));
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
         const bool ok = (mt == 0) ? ok0 : ok1;
@@ -188,21 +202,23 @@ __device__ __forceinline__ void f8_stage_compute(const F8Stage& s, float acc[MT]
         uint4 xlo = make_uint4(0, 0, 0, 0), xhi = make_uint4(0, 0, 0, 0);
         if (ok && kt * 128 + t * 16 < K16) xlo = ld_nc_v4(xr + t * 16);
         if (ok && kt * 128 + (t + 4) * 16 < K16) xhi = ld_nc_v4(xr + (t + 4) * 16);
-        mma_e4m3_16832(acc[mt], s.a_lo.x, s.b_lo.x, s.a_lo.y, s.b_lo.y, xlo.x, xlo.y);
-        mma_e4m3_16832(acc[mt], s.a_lo.z, s.b_lo.z, s.a_lo.w, s.b_lo.w, xlo.z, xlo.w);
-        mma_e4m3_16832(acc[mt], s.a_hi.x, s.b_hi.x, s.a_hi.y, s.b_hi.y, xhi.x, xhi.y);
-        mma_e4m3_16832(acc[mt], s.a_hi.z, s.b_hi.z, s.a_hi.w, s.b_hi.w, xhi.z, xhi.w);
+        mma_e4m3_16832(acc[mt], a_lo.x, b_lo.x, a_lo.y, b_lo.y, xlo.x, xlo.y);
+        mma_e4m3_16832(acc[mt], a_lo.z, b_lo.z, a_lo.w, b_lo.w, xlo.z, xlo.w);
+        mma_e4m3_16832(acc[mt], a_hi.x, b_hi.x, a_hi.y, b_hi.y, xhi.x, xhi.y);
+        mma_e4m3_16832(acc[mt], a_hi.z, b_hi.z, a_hi.w, b_hi.w, xhi.z, xhi.w);
     }
 }
 
 template <int MT, int SPLIT_CLUSTER>
-__global__ void __launch_bounds__(F8V_WARPS * 32)
+__global__ void __launch_bounds__(F8V_WARPS * 32, 2)
 fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_scale, const uint8_t* __restrict__ xq,
-                const float* __restrict__ a_scale, uint16_t* __restrict__ y, int M, int N, int K16, int KT, int split) {
-    __shared__ float red[F8V_WARPS][32][MT * 4];
+                const float* __restrict__ a_scale, uint16_t* __restrict__ y, int M, int N, int K16, int KT, int rb_real,
+                int split, int* __restrict__ status) {
+    extern __shared__ __align__(128) uint8_t f8v_ring[];           // [F8V_WARPS][F8V_STAGES][2048]
+    __shared__ __align__(8) uint64_t bars[F8V_WARPS][F8V_STAGES];
+    __shared__ float red[2][F8V_WARPS][32][MT * 4];
     __shared__ float cl_part[SPLIT_CLUSTER ? F8V_MAX_SPLIT : 1][16][MT * 8];
 
-    const int rb = blockIdx.x;
     const int sp = SPLIT_CLUSTER ? int(fp8_cluster_ctarank()) : 0;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -210,89 +226,98 @@ fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_s
     const int per = (KT + split - 1) / split;
     const int kt_lo = sp * per;
     const int kt_hi = min(KT, kt_lo + per);
+    const int kt_first = kt_lo + warp;
+    const bool has_work = kt_first < kt_hi;
 
-    float acc[MT][4];
+    if (lane == 0) {
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) acc[mt][i] = 0.f;
-
-    // row-block rb = rows [16rb, 16rb+16) = swizzle groups 2j, 2j+1 of tile row nt
-    const uint8_t* base = wpack + (size_t)(rb >> 3) * KT * FP8_TILE_BYTES + (size_t)(rb & 7) * 2048;
-    const bool ok0 = g < M;
-    const bool ok1 = (MT > 1) && (g + 8 < M);
-
-    F8Stage st[F8V_STAGES];
-    int kt = kt_lo + warp;
-#pragma unroll
-    for (int d = 0; d < F8V_STAGES; ++d) {
-        const int k = kt + d * F8V_WARPS;
-        if (k < kt_hi) f8_stage_load(st[d], base + (size_t)k * FP8_TILE_BYTES, g, t);
+        for (int d = 0; d < F8V_STAGES; ++d)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(f8v_smem_u32(&bars[warp][d])), "r"(1) : "memory");
     }
-    for (; kt < kt_hi; kt += F8V_STAGES * F8V_WARPS) {
-#pragma unroll
-        for (int d = 0; d < F8V_STAGES; ++d) {
-            const int kcur = kt + d * F8V_WARPS;
-            if (kcur < kt_hi) {
-                const F8Stage cur = st[d];
-                const int knext = kcur + F8V_STAGES * F8V_WARPS;
-                if (knext < kt_hi) f8_stage_load(st[d], base + (size_t)knext * FP8_TILE_BYTES, g, t);
-                f8_stage_compute<MT>(cur, acc, xq, kcur, K16, g, t, ok0, ok1);
-            }
-        }
-    }
-
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) red[warp][lane][mt * 4 + i] = acc[mt][i];
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     __syncthreads();
 
-    constexpr int SLOTS = 32 * MT * 4;
-    constexpr int PER_THREAD = (SLOTS + F8V_WARPS * 32 - 1) / (F8V_WARPS * 32);
-    float total[PER_THREAD];
-    int row[PER_THREAD], tok[PER_THREAD];
-#pragma unroll
-    for (int u = 0; u < PER_THREAD; ++u) {
-        const int e = threadIdx.x + u * F8V_WARPS * 32;
-        total[u] = 0.f; row[u] = 0; tok[u] = 0;
-        if (e < SLOTS) {
-            const int ln = e / (MT * 4), idx = e % (MT * 4);
-            const int mt = idx >> 2, i = idx & 3;
-#pragma unroll
-            for (int wdx = 0; wdx < F8V_WARPS; ++wdx) total[u] += red[wdx][ln][idx];
-            row[u] = (ln >> 2) + ((i >> 1) ? 8 : 0);
-            tok[u] = mt * 8 + (ln & 3) * 2 + (i & 1);
+    const uint32_t ring_base = f8v_smem_u32(f8v_ring) + (uint32_t)warp * (F8V_STAGES * F8V_STAGE_BYTES);
+    const uint32_t bar_base = f8v_smem_u32(&bars[warp][0]);
+
+    // row-block rb = rows [16rb, 16rb+16) = swizzle groups 2j, 2j+1 (j = rb % 8) of tile row rb / 8
+    auto block_ptr = [&](int rb, int kt) {
+        return wpack + ((size_t)(rb >> 3) * KT + kt) * FP8_TILE_BYTES + (size_t)(rb & 7) * F8V_STAGE_BYTES;
+    };
+    int prb = blockIdx.x, pkt = kt_first, pslot = 0;
+    auto issue = [&]() {
+        if (has_work && prb < rb_real) {
+            const uint32_t bar = bar_base + 8u * pslot;
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(F8V_STAGE_BYTES) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(ring_base + pslot * F8V_STAGE_BYTES), "l"(block_ptr(prb, pkt)), "r"(F8V_STAGE_BYTES), "r"(bar) : "memory");
+            pkt += F8V_WARPS;
+            if (pkt >= kt_hi) { pkt = kt_first; prb += gridDim.x; }
         }
+        pslot = (pslot + 1 == F8V_STAGES) ? 0 : pslot + 1;
+    };
+    if (lane == 0) {
+#pragma unroll 1
+        for (int d = 0; d < F8V_STAGES; ++d) issue();
     }
-    if (SPLIT_CLUSTER) {
+
+    const bool ok0 = g < M;
+    const bool ok1 = (MT > 1) && (g + 8 < M);
+    int slot = 0;
+    uint32_t phases = 0;
+    int it = 0;
+
+    for (int rb = blockIdx.x; rb < rb_real; rb += gridDim.x, ++it) {
+        float acc[MT][4];
 #pragma unroll
-        for (int u = 0; u < PER_THREAD; ++u) {
-            const int e = threadIdx.x + u * F8V_WARPS * 32;
-            if (e < SLOTS) fp8_st_cluster_rank0_f32(&cl_part[sp][row[u]][tok[u]], total[u]);
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[mt][i] = 0.f;
+
+        for (int kt = kt_first; kt < kt_hi; kt += F8V_WARPS) {
+            f8v_wait(bar_base + 8u * slot, (phases >> slot) & 1u, status);
+            f8_block_compute<MT>(ring_base + slot * F8V_STAGE_BYTES, acc, xq, kt, K16, g, t, ok0, ok1);
+            phases ^= 1u << slot;
+            __syncwarp();
+            if (lane == 0) issue();
+            slot = (slot + 1 == F8V_STAGES) ? 0 : slot + 1;
         }
-        fp8_cluster_sync_all();
-        if (sp != 0) return;
+
+        const int buf = it & 1;
 #pragma unroll
-        for (int u = 0; u < PER_THREAD; ++u) {
-            const int e = threadIdx.x + u * F8V_WARPS * 32;
-            if (e < SLOTS) {
-                float s = 0.f;
-                for (int r = 0; r < split; ++r) s += cl_part[r][row[u]][tok[u]];
-                total[u] = s;
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) red[buf][warp][lane][mt * 4 + i] = acc[mt][i];
+        __syncthreads();
+
+        constexpr int SLOTS = 32 * MT * 4;
+        const int e = threadIdx.x;
+        const int ln = e / (MT * 4), idx = e % (MT * 4);
+        const int mt_ = idx >> 2, i_ = idx & 3;
+        const int row = (ln >> 2) + ((i_ >> 1) ? 8 : 0);
+        const int tok = mt_ * 8 + (ln & 3) * 2 + (i_ & 1);
+        const int n = rb * 16 + row;
+        if (e < SLOTS && tok < M) {
+            float total = 0.f;
+#pragma unroll
+            for (int wdx = 0; wdx < F8V_WARPS; ++wdx) total += red[buf][wdx][ln][idx];
+            if (SPLIT_CLUSTER) {
+                fp8_st_cluster_rank0_f32(&cl_part[sp][row][tok], total);
+            } else if (n < N) {
+                // (raw * a_scale[m]) * w_scale[n], in that order (ktir_matmul_fp8.rs:676-712)
+                const float o = __fmul_rn(__fmul_rn(total, a_scale[tok]), w_scale[n]);
+                const __nv_bfloat16 v = __float2bfloat16_rn(o);
+                y[(size_t)tok * N + n] = *reinterpret_cast<const uint16_t*>(&v);
             }
         }
-    }
-#pragma unroll
-    for (int u = 0; u < PER_THREAD; ++u) {
-        const int e = threadIdx.x + u * F8V_WARPS * 32;
-        if (e < SLOTS) {
-            const int n = rb * 16 + row[u];
-            if (n < N && tok[u] < M) {
-                // (raw * a_scale[m]) * w_scale[n], in that order (ktir_matmul_fp8.rs:676-712)
-                const float o = __fmul_rn(__fmul_rn(total[u], a_scale[tok[u]]), w_scale[n]);
+        if (SPLIT_CLUSTER) {
+            fp8_cluster_sync_all();
+            if (sp == 0 && e < SLOTS && tok < M && n < N) {
+                float s = 0.f;
+                for (int r = 0; r < split; ++r) s += cl_part[r][row][tok];
+                const float o = __fmul_rn(__fmul_rn(s, a_scale[tok]), w_scale[n]);
                 const __nv_bfloat16 v = __float2bfloat16_rn(o);
-                y[(size_t)tok[u] * N + n] = *reinterpret_cast<const uint16_t*>(&v);
+                y[(size_t)tok * N + n] = *reinterpret_cast<const uint16_t*>(&v);
             }
         }
     }
@@ -373,18 +398,16 @@ extern "C" int32_t scr_e4m3_encode(scr_ctx* ctx, const float* v, int64_t count, 
     return scr_check_launch(ctx, "e4m3_encode");
 }
 
-static int fp8_gemv_pick_split(int rb_real, int KT, int sms) {
-    int best = 1;
-    long long best_cost = -1;
-    for (int s = 1; s <= F8V_MAX_SPLIT && s <= KT; ++s) {
-        const long long ctas = (long long)rb_real * s;
-        const long long per_sm = (ctas + sms - 1) / sms;
-        const int cpc = (KT + s - 1) / s;
-        const int cpw = (cpc + F8V_WARPS - 1) / F8V_WARPS;
-        const long long cost = per_sm * cpw * 8 + (s > 1 ? per_sm * 2 : 0);
-        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = s; }
+static void fp8_gemv_shape(int rb_real, int KT, int sms, int* grid_x, int* split) {
+    if (rb_real >= sms) {
+        *grid_x = std::min(rb_real, 2 * sms);
+        *split = 1;
+        return;
     }
-    return best;
+    int s = 1;
+    while (s * 2 <= F8V_MAX_SPLIT && rb_real * s * 2 <= 2 * sms && KT / (s * 2) >= F8V_WARPS / 2) s *= 2;
+    *grid_x = rb_real;
+    *split = s;
 }
 
 template <int MT>
@@ -394,15 +417,22 @@ static int32_t fp8_gemv_launch(scr_ctx* ctx, const uint8_t* wpack, const uint8_t
     const float* w_scale = reinterpret_cast<const float*>(wpack + (size_t)g.NT * g.KT * FP8_TILE_BYTES);
     const int K16 = scr_ceil_div(K, 16) * 16;
     const int rb_real = scr_ceil_div(N, 16);
-    const int split = fp8_gemv_pick_split(rb_real, g.KT, ctx->sm_count);
+    int grid_x = 1, split = 1;
+    fp8_gemv_shape(rb_real, g.KT, ctx->sm_count, &grid_x, &split);
+    constexpr int kRingBytes = F8V_WARPS * F8V_STAGES * F8V_STAGE_BYTES;
     if (split == 1) {
-        fp8_gemv_kernel<MT, 0><<<dim3(rb_real, 1), F8V_WARPS * 32, 0, stream>>>(wpack, w_scale, xq, a_scale, y, M, N, K16,
-                                                                               g.KT, 1);
+        cudaError_t e0 = cudaFuncSetAttribute(fp8_gemv_kernel<MT, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes);
+        if (e0 != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "fp8_gemv smem attribute: %s", cudaGetErrorString(e0));
+        fp8_gemv_kernel<MT, 0><<<dim3(grid_x, 1), F8V_WARPS * 32, kRingBytes, stream>>>(wpack, w_scale, xq, a_scale, y, M, N, K16,
+                                                                                       g.KT, rb_real, 1, ctx->dev_status);
         return scr_check_launch(ctx, "fp8_gemv");
     }
+    cudaError_t e1 = cudaFuncSetAttribute(fp8_gemv_kernel<MT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes);
+    if (e1 != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "fp8_gemv smem attribute: %s", cudaGetErrorString(e1));
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(rb_real, split, 1);
+    cfg.gridDim = dim3(grid_x, split, 1);
     cfg.blockDim = dim3(F8V_WARPS * 32, 1, 1);
+    cfg.dynamicSmemBytes = kRingBytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -411,7 +441,8 @@ static int32_t fp8_gemv_launch(scr_ctx* ctx, const uint8_t* wpack, const uint8_t
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, fp8_gemv_kernel<MT, 1>, wpack, w_scale, xq, a_scale, y, M, N, K16, g.KT, split);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, fp8_gemv_kernel<MT, 1>, wpack, w_scale, xq, a_scale, y, M, N, K16, g.KT, rb_real,
+                                       split, ctx->dev_status);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "fp8_gemv cluster launch: %s", cudaGetErrorString(e));
     return scr_check_launch(ctx, "fp8_gemv(cluster)");
 }
