@@ -18,7 +18,7 @@ __device__ __forceinline__ uint32_t affine_interleave_word(uint32_t src) {
 
 __global__ void affine_b4_repack_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict__ scales,
                                         const uint16_t* __restrict__ biases, int N, int K, int RB, int KC,
-                                        uint8_t* __restrict__ dst) {
+                                        uint8_t* __restrict__ dst, unsigned int* __restrict__ slow_flag) {
     const long long nblocks = (long long)RB * KC;
     const long long items = nblocks * 80;               // 64 pieces + 16 scale entries per block
     for (long long it = blockIdx.x * (long long)blockDim.x + threadIdx.x; it < items;
@@ -51,6 +51,7 @@ __global__ void affine_b4_repack_kernel(const uint32_t* __restrict__ w, const ui
                 if (r1 < N) v.y = uint32_t(scales[(size_t)r1 * G + grp]) | (uint32_t(biases[(size_t)r1 * G + grp]) << 16);
             }
             *reinterpret_cast<uint2*>(out + 1024 + e * 8) = v;
+            if (affine_slow_group(v.x) || affine_slow_group(v.y)) atomicOr(slow_flag, 1u);
         }
     }
 }
@@ -61,6 +62,7 @@ __global__ void affine_b4_repack_kernel(const uint32_t* __restrict__ w, const ui
 __global__ void affine_b4_dump_kernel(const uint8_t* __restrict__ packed, int N, int K, int RB, int KC,
                                       uint16_t* __restrict__ out) {
     const long long items = (long long)RB * KC * 64;
+    const bool check = *reinterpret_cast<const unsigned int*>(packed + (size_t)RB * KC * AFF_BLOCK_BYTES) != 0;
     for (long long it = blockIdx.x * (long long)blockDim.x + threadIdx.x; it < items;
          it += (long long)gridDim.x * blockDim.x) {
         const long long blk = it / 64;
@@ -74,7 +76,8 @@ __global__ void affine_b4_dump_kernel(const uint8_t* __restrict__ packed, int N,
         const uint4 piece = *reinterpret_cast<const uint4*>(b + half * 512 + lane * 16);
         const uint2 sb2 = *reinterpret_cast<const uint2*>(b + 1024 + (g * 2 + (t >> 1)) * 8);
         uint32_t regs[16];
-        affine_dequant_piece(piece, half ? sb2.y : sb2.x, regs);
+        if (check) affine_dequant_piece<true>(piece, half ? sb2.y : sb2.x, regs);
+        else affine_dequant_piece<false>(piece, half ? sb2.y : sb2.x, regs);
         uint4* o = reinterpret_cast<uint4*>(out + (size_t)row * K + k0);
 #pragma unroll
         for (int i = 0; i < 4; ++i) o[i] = make_uint4(regs[4 * i], regs[4 * i + 1], regs[4 * i + 2], regs[4 * i + 3]);
@@ -97,6 +100,7 @@ __device__ __forceinline__ void gemv_bulk_g2s(uint32_t dst_smem, const void* src
 // Bounded wait on a stage barrier: gives up after 2^20 polls (or as soon as another waiter has
 // recorded a failure), records code 6 in the status word and lets the kernel run to its end.
 __device__ __forceinline__ void gemv_wait(uint32_t bar, uint32_t parity, int* status) {
+#pragma unroll 1
     for (uint32_t i = 0; i < (1u << 20); ++i) {
         uint32_t ok;
         asm volatile(
@@ -165,53 +169,43 @@ __device__ __forceinline__ void mma_bf16_16816(float d[4], uint32_t a0, uint32_t
 #define GEMV_STAGES 6
 #define GEMV_MAX_SPLIT 8
 
-template <int MT>
-__device__ __forceinline__ void gemv_block_compute(uint32_t stage, float acc[MT][4], const uint16_t* __restrict__ x,
-                                                   int kc, int K, int lane, bool tok_ok0, bool tok_ok1) {
-    const int g = lane >> 2, t = lane & 3;
+// One 1152-byte block from shared memory against the activations.  Tokens beyond M and k beyond K
+// read clamped (valid) activation addresses instead of zeros: a column of B only reaches the
+// same column of D, which is discarded for tokens >= M, and padded k meets zero weights.
+template <int MT, bool CHECK>
+__device__ __forceinline__ void gemv_block_compute(uint32_t stage, float acc[2][MT][4], const uint16_t* const xrow[MT],
+                                                   int k0, int lane) {
     const uint4 p0 = gemv_lds_v4(stage + lane * 16);
     const uint4 p1 = gemv_lds_v4(stage + 512 + lane * 16);
-    const uint2 sb = gemv_lds_v2(stage + 1024 + (g * 2 + (t >> 1)) * 8);
-    const int k0 = kc * 128 + t * 32;
-    uint32_t xr[MT][16];
+    const uint2 sb = gemv_lds_v2(stage + 1024 + ((lane >> 2) * 2 + ((lane & 3) >> 1)) * 8);
+    uint4 xv[MT][4];
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-        const bool ok = (mt == 0 ? tok_ok0 : tok_ok1) && (k0 < K);
-        const uint16_t* xp = x + (size_t)(mt * 8 + g) * K + k0;
+    for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (ok) v = ld_nc_v4(xp + 8 * i);
-            xr[mt][4 * i + 0] = v.x; xr[mt][4 * i + 1] = v.y; xr[mt][4 * i + 2] = v.z; xr[mt][4 * i + 3] = v.w;
-        }
-    }
+        for (int i = 0; i < 4; ++i) xv[mt][i] = ld_nc_v4(xrow[mt] + k0 + 8 * i);
     uint32_t w0[16], w1[16];
-    affine_dequant_piece(p0, sb.x, w0);
-    affine_dequant_piece(p1, sb.y, w1);
+    affine_dequant_piece<CHECK>(p0, sb.x, w0);
+    affine_dequant_piece<CHECK>(p1, sb.y, w1);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
-            mma_bf16_16816(acc[mt], w0[4 * i + 0], w1[4 * i + 0], w0[4 * i + 1], w1[4 * i + 1],
-                           xr[mt][4 * i + 0], xr[mt][4 * i + 1]);
-            mma_bf16_16816(acc[mt], w0[4 * i + 2], w1[4 * i + 2], w0[4 * i + 3], w1[4 * i + 3],
-                           xr[mt][4 * i + 2], xr[mt][4 * i + 3]);
+            // two independent accumulator sets halve the dependent-MMA chain
+            mma_bf16_16816(acc[0][mt], w0[4 * i + 0], w1[4 * i + 0], w0[4 * i + 1], w1[4 * i + 1], xv[mt][i].x, xv[mt][i].y);
+            mma_bf16_16816(acc[1][mt], w0[4 * i + 2], w1[4 * i + 2], w0[4 * i + 3], w1[4 * i + 3], xv[mt][i].z, xv[mt][i].w);
         }
     }
 }
 
-template <int MT, int SPLIT_CLUSTER>
-__global__ void __launch_bounds__(GEMV_WARPS * 32, 2)
-affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __restrict__ x, uint16_t* __restrict__ y,
-                      int M, int N, int K, int RB, int KC, int rb_real, int split, int* __restrict__ status) {
-    extern __shared__ __align__(128) uint8_t gemv_ring[];          // [GEMV_WARPS][GEMV_STAGES][AFF_BLOCK_BYTES]
-    __shared__ __align__(8) uint64_t bars[GEMV_WARPS][GEMV_STAGES];
-    __shared__ float red[2][GEMV_WARPS][32][MT * 4];
-    __shared__ float cl_part[SPLIT_CLUSTER ? GEMV_MAX_SPLIT : 1][16][MT * 8];
-
+template <int MT, int SPLIT_CLUSTER, bool CHECK>
+__device__ __forceinline__ void gemv_main(const uint8_t* __restrict__ packed, const uint16_t* __restrict__ x,
+                                          uint16_t* __restrict__ y, int M, int N, int K, int RB, int KC, int rb_real,
+                                          int split, int* __restrict__ status, uint8_t* ring_gen,
+                                          uint64_t (*bars)[GEMV_STAGES], float (*red)[GEMV_WARPS][32][MT * 4],
+                                          float (*cl_part)[16][MT * 8]) {
     const int sp = SPLIT_CLUSTER ? int(gemv_cluster_ctarank()) : 0;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int g = lane >> 2;
+    const int g = lane >> 2, t = lane & 3;
 
     // k-chunks of this CTA: [kc_lo, kc_hi); warp w takes kc_lo + w, + GEMV_WARPS, ...
     const int per = (KC + split - 1) / split;
@@ -220,15 +214,8 @@ affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __rest
     const int kc_first = kc_lo + warp;
     const bool has_work = kc_first < kc_hi;
 
-    if (lane == 0) {
-#pragma unroll
-        for (int d = 0; d < GEMV_STAGES; ++d) gemv_mbar_init(gemv_smem_u32(&bars[warp][d]), 1);
-    }
-    gemv_fence_mbar_init();
-    __syncthreads();
-
     const size_t chunk_stride = (size_t)RB * AFF_BLOCK_BYTES;
-    const uint32_t ring_base = gemv_smem_u32(gemv_ring) + (uint32_t)warp * (GEMV_STAGES * AFF_BLOCK_BYTES);
+    const uint32_t ring_base = gemv_smem_u32(ring_gen) + (uint32_t)warp * (GEMV_STAGES * AFF_BLOCK_BYTES);
     const uint32_t bar_base = gemv_smem_u32(&bars[warp][0]);
 
     // producer cursor (only lane 0 uses it): next block to request, in consumption order
@@ -249,22 +236,31 @@ affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __rest
         for (int d = 0; d < GEMV_STAGES; ++d) issue();
     }
 
-    const bool tok_ok0 = g < M;
-    const bool tok_ok1 = (MT > 1) && (g + 8 < M);
+    // activation rows this lane feeds into the B operand (clamped to a valid token)
+    const uint16_t* xrow[MT];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) xrow[mt] = x + (size_t)min(mt * 8 + g, M - 1) * K;
+    const int kt_off = t * 32;
+
     int slot = 0;
     uint32_t phases = 0;                       // bit d = parity the next wait on stage d expects
     int it = 0;
 
     for (int rb = blockIdx.x; rb < rb_real; rb += gridDim.x, ++it) {
-        float acc[MT][4];
+        float acc[2][MT][4];
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
+        for (int a = 0; a < 2; ++a)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) acc[mt][i] = 0.f;
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[a][mt][i] = 0.f;
 
+#pragma unroll 1
         for (int kc = kc_first; kc < kc_hi; kc += GEMV_WARPS) {
             gemv_wait(bar_base + 8u * slot, (phases >> slot) & 1u, status);
-            gemv_block_compute<MT>(ring_base + slot * AFF_BLOCK_BYTES, acc, x, kc, K, lane, tok_ok0, tok_ok1);
+            int k0 = kc * 128 + kt_off;
+            if (k0 >= K) k0 = 0;               // padded k: the weights there are zero
+            gemv_block_compute<MT, CHECK>(ring_base + slot * AFF_BLOCK_BYTES, acc, xrow, k0, lane);
             phases ^= 1u << slot;
             __syncwarp();                      // every lane has consumed the stage: refill it
             if (lane == 0) issue();
@@ -276,48 +272,60 @@ affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __rest
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) red[buf][warp][lane][mt * 4 + i] = acc[mt][i];
+            for (int i = 0; i < 4; ++i) red[buf][warp][lane][mt * 4 + i] = acc[0][mt][i] + acc[1][mt][i];
         __syncthreads();
 
         // thread e owns accumulator slot (ln, idx): c0,c1 -> row g, tokens 2t,2t+1 ; c2,c3 -> row g+8
         constexpr int SLOTS = 32 * MT * 4;     // <= 256 = blockDim.x
         const int e = threadIdx.x;
-        if (e < SLOTS) {
-            const int ln = e / (MT * 4), idx = e % (MT * 4);
-            const int mt = idx >> 2, i = idx & 3;
-            const int row = (ln >> 2) + ((i >> 1) ? 8 : 0);
-            const int tok = mt * 8 + (ln & 3) * 2 + (i & 1);
-            const int n = rb * 16 + row;
-            if (tok < M) {
-                float total = 0.f;
+        const int ln = e / (MT * 4), idx = e % (MT * 4);
+        const int row = (ln >> 2) + (((idx & 3) >> 1) ? 8 : 0);
+        const int tok = (idx >> 2) * 8 + (ln & 3) * 2 + (idx & 1);
+        const int n = rb * 16 + row;
+        if (e < SLOTS && tok < M) {
+            float total = 0.f;
 #pragma unroll
-                for (int wdx = 0; wdx < GEMV_WARPS; ++wdx) total += red[buf][wdx][ln][idx];
-                if (SPLIT_CLUSTER) {
-                    gemv_st_cluster_rank0_f32(&cl_part[sp][row][tok], total);
-                } else if (n < N) {
-                    const __nv_bfloat16 v = __float2bfloat16_rn(total);
-                    y[(size_t)tok * N + n] = *reinterpret_cast<const uint16_t*>(&v);
-                }
+            for (int wdx = 0; wdx < GEMV_WARPS; ++wdx) total += red[buf][wdx][ln][idx];
+            if (SPLIT_CLUSTER) {
+                gemv_st_cluster_rank0_f32(&cl_part[sp][row][tok], total);
+            } else if (n < N) {
+                const __nv_bfloat16 v = __float2bfloat16_rn(total);
+                y[(size_t)tok * N + n] = *reinterpret_cast<const uint16_t*>(&v);
             }
         }
         if (SPLIT_CLUSTER) {
             // one row-block per CTA in cluster mode (gridDim.x == rb_real): exchange once
             gemv_cluster_sync_all();
-            if (sp == 0 && e < SLOTS) {
-                const int ln = e / (MT * 4), idx = e % (MT * 4);
-                const int mt = idx >> 2, i = idx & 3;
-                const int row = (ln >> 2) + ((i >> 1) ? 8 : 0);
-                const int tok = mt * 8 + (ln & 3) * 2 + (i & 1);
-                const int n = rb * 16 + row;
-                if (tok < M && n < N) {
-                    float s = 0.f;
-                    for (int r = 0; r < split; ++r) s += cl_part[r][row][tok];   // rank order
-                    const __nv_bfloat16 v = __float2bfloat16_rn(s);
-                    y[(size_t)tok * N + n] = *reinterpret_cast<const uint16_t*>(&v);
-                }
+            if (sp == 0 && e < SLOTS && tok < M && n < N) {
+                float s = 0.f;
+                for (int r = 0; r < split; ++r) s += cl_part[r][row][tok];   // rank order
+                const __nv_bfloat16 v = __float2bfloat16_rn(s);
+                y[(size_t)tok * N + n] = *reinterpret_cast<const uint16_t*>(&v);
             }
         }
     }
+}
+
+template <int MT, int SPLIT_CLUSTER>
+__global__ void __launch_bounds__(GEMV_WARPS * 32, 2)
+affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __restrict__ x, uint16_t* __restrict__ y,
+                      int M, int N, int K, int RB, int KC, int rb_real, int split, int* __restrict__ status) {
+    extern __shared__ __align__(128) uint8_t gemv_ring[];          // [GEMV_WARPS][GEMV_STAGES][AFF_BLOCK_BYTES]
+    __shared__ __align__(8) uint64_t bars[GEMV_WARPS][GEMV_STAGES];
+    __shared__ float red[2][GEMV_WARPS][32][MT * 4];
+    __shared__ float cl_part[SPLIT_CLUSTER ? GEMV_MAX_SPLIT : 1][16][MT * 8];
+
+    if ((threadIdx.x & 31) == 0) {
+#pragma unroll
+        for (int d = 0; d < GEMV_STAGES; ++d) gemv_mbar_init(gemv_smem_u32(&bars[threadIdx.x >> 5][d]), 1);
+    }
+    gemv_fence_mbar_init();
+    __syncthreads();
+
+    // one word per matrix says whether any group needs the exact (two-step rounding) path
+    const bool check = *reinterpret_cast<const unsigned int*>(packed + (size_t)RB * KC * AFF_BLOCK_BYTES) != 0;
+    if (check) gemv_main<MT, SPLIT_CLUSTER, true>(packed, x, y, M, N, K, RB, KC, rb_real, split, status, gemv_ring, bars, red, cl_part);
+    else gemv_main<MT, SPLIT_CLUSTER, false>(packed, x, y, M, N, K, RB, KC, rb_real, split, status, gemv_ring, bars, red, cl_part);
 }
 
 // ------------------------------------------------------------------------------------
@@ -336,7 +344,7 @@ extern "C" int32_t scr_affine_b4_repack_size(int32_t N, int32_t K, int32_t group
     if (group != 64) return SCR_E_DTYPE;
     if (K % group != 0) return SCR_E_SHAPE;
     const AffineGeom g = affine_geom(N, K);
-    *bytes = (size_t)g.RB * g.KC * AFF_BLOCK_BYTES;
+    *bytes = affine_packed_bytes(g);
     return SCR_OK;
 }
 
@@ -351,8 +359,11 @@ extern "C" int32_t scr_affine_b4_repack(scr_ctx* ctx, const uint32_t* w, const u
     const long long items = (long long)g.RB * g.KC * 80;
     const int threads = 256;
     const int blocks = (int)std::min<long long>((items + threads - 1) / threads, (long long)ctx->sm_count * 32);
+    unsigned int* flag = reinterpret_cast<unsigned int*>((uint8_t*)dst + affine_blocks_bytes(g));
+    cudaError_t e = cudaMemsetAsync(flag, 0, AFF_TRAILER_BYTES, (cudaStream_t)stream);
+    if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine_b4_repack memset: %s", cudaGetErrorString(e));
     affine_b4_repack_kernel<<<blocks, threads, 0, (cudaStream_t)stream>>>(w, scales, biases, N, K, g.RB, g.KC,
-                                                                         (uint8_t*)dst);
+                                                                         (uint8_t*)dst, flag);
     return scr_check_launch(ctx, "affine_b4_repack");
 }
 

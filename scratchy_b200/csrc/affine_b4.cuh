@@ -27,6 +27,9 @@
 //   [4j, 4j+4) and e_{2j+1} at bits [16+4j, 16+4j+4): `(word >> 4j) & 0x000F000F` is then
 //   the pair (e_{2j}, e_{2j+1}) in the two 16-bit halves, in natural order.
 //   Padding rows / k hold code 0, scale 0, bias 0, which dequantise to exactly 0.
+//   A 128-byte trailer follows the blocks; its first word is non-zero when some group of the
+//   matrix needs the exact path (set by the repack kernel), so the kernels test one word per
+//   launch instead of every group.
 #pragma once
 
 #include "common.cuh"
@@ -35,6 +38,7 @@
 #define AFF_BLOCK_ROWS 16
 #define AFF_BLOCK_K 128
 #define AFF_ROW_PAD 128
+#define AFF_TRAILER_BYTES 128
 
 struct AffineGeom {
     int N, K;        // logical
@@ -49,10 +53,12 @@ static inline AffineGeom affine_geom(int N, int K) {
     g.KC = scr_ceil_div(K, AFF_BLOCK_K);
     return g;
 }
+static inline size_t affine_blocks_bytes(const AffineGeom& g) { return (size_t)g.RB * g.KC * AFF_BLOCK_BYTES; }
+static inline size_t affine_packed_bytes(const AffineGeom& g) { return affine_blocks_bytes(g) + AFF_TRAILER_BYTES; }
 
 // True when the packed-bf16 fast path could differ from the reference's two-step rounding
 // (see the header comment) or would involve bf16/f32 subnormals.
-__device__ __forceinline__ bool affine_slow_group(uint32_t sb /* scale | bias << 16 */) {
+__host__ __device__ __forceinline__ bool affine_slow_group(uint32_t sb /* scale | bias << 16 */) {
     const uint32_t s = sb & 0x7FFFu, b = (sb >> 16) & 0x7FFFu;      // magnitudes, sign stripped
     const int es = int(s >> 7), eb = int(b >> 7);                    // biased exponents
     const bool tiny = (s != 0 && es < 20) || (b != 0 && eb < 20);
@@ -96,8 +102,10 @@ __device__ __forceinline__ void affine_dequant_word_fast(uint32_t word, uint32_t
 }
 
 // A 16-byte piece (32 codes of one row, one group) -> 16 bf16x2 registers in k order.
+// CHECK = false is for matrices whose trailer flag says no group needs the exact path.
+template <bool CHECK>
 __device__ __forceinline__ void affine_dequant_piece(const uint4& piece, uint32_t sb, uint32_t out[16]) {
-    if (affine_slow_group(sb)) {
+    if (CHECK && affine_slow_group(sb)) {
         const uint4 r0 = affine_dequant_word_exact(piece.x, sb);
         const uint4 r1 = affine_dequant_word_exact(piece.y, sb);
         const uint4 r2 = affine_dequant_word_exact(piece.z, sb);

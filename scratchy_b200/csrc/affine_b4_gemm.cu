@@ -165,6 +165,7 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
         // ------------------------------------------------------------------ dequantise (warps 2..5)
         const int dw = warp - 2;                       // 0..3
         const int g = lane >> 2, t = lane & 3;
+        const bool check = *reinterpret_cast<const unsigned int*>(packed + (size_t)RB * KC * AFF_BLOCK_BYTES) != 0;
         int sp = 0, sd = 0;
         uint32_t php = 0, phd = 0;
         for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
@@ -182,7 +183,8 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
                     const uint4 piece = ld_shared_v4(blk + half * 512 + lane * 16);
                     const uint32_t sb = ld_shared_u32(blk + 1024 + (g * 2 + (t >> 1)) * 8 + half * 4);
                     uint32_t w[16];
-                    affine_dequant_piece(piece, sb, w);
+                    if (check) affine_dequant_piece<true>(piece, sb, w);
+                    else affine_dequant_piece<false>(piece, sb, w);
                     // row = 16 rbl + 8 half + g -> 8-row group (2 rbl + half), row-in-group g;
                     // k = 32 t + [0,32) -> atom t>>1, 16-byte chunks (t&1)*4 + [0,4)
                     const uint32_t rowbase = ds + (uint32_t)(t >> 1) * (uint32_t)(BN * 128) + (uint32_t)(2 * rbl + half) * 1024u +

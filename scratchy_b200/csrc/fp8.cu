@@ -187,9 +187,11 @@ __device__ __forceinline__ uint4 f8v_lds_v4(uint32_t addr) {
 #define F8V_STAGE_BYTES 2048
 #define F8V_MAX_SPLIT 8
 
+// One 2 KB block (16 rows x 128 k) from shared memory against the quantised activations.  Tokens
+// beyond M read a clamped (valid) row: a column of B only reaches the same, discarded, column of D.
 template <int MT>
-__device__ __forceinline__ void f8_block_compute(uint32_t stage, float acc[MT][4], const uint8_t* __restrict__ xq,
-                                                 int kt, int K16, int g, int t, bool ok0, bool ok1) {
+__device__ __forceinline__ void f8_block_compute(uint32_t stage, float acc[2][MT][4], const uint8_t* const xrow[MT],
+                                                 int koff_lo, int koff_hi, int g, int t) {
     const uint32_t r0 = stage + g * 128;
     const uint4 a_lo = f8v_lds_v4(r0 + ((t ^ g) << 4));
     const uint4 a_hi = f8v_lds_v4(r0 + (((t + 4) ^ g) << 4));
@@ -197,15 +199,12 @@ __device__ __forceinline__ void f8_block_compute(uint32_t stage, float acc[MT][4
     const uint4 b_hi = f8v_lds_v4(r0 + 1024 + (((t + 4) ^ g) << 4));
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
-        const bool ok = (mt == 0) ? ok0 : ok1;
-        const uint8_t* xr = xq + (size_t)(mt * 8 + g) * K16 + kt * 128;
-        uint4 xlo = make_uint4(0, 0, 0, 0), xhi = make_uint4(0, 0, 0, 0);
-        if (ok && kt * 128 + t * 16 < K16) xlo = ld_nc_v4(xr + t * 16);
-        if (ok && kt * 128 + (t + 4) * 16 < K16) xhi = ld_nc_v4(xr + (t + 4) * 16);
-        mma_e4m3_16832(acc[mt], a_lo.x, b_lo.x, a_lo.y, b_lo.y, xlo.x, xlo.y);
-        mma_e4m3_16832(acc[mt], a_lo.z, b_lo.z, a_lo.w, b_lo.w, xlo.z, xlo.w);
-        mma_e4m3_16832(acc[mt], a_hi.x, b_hi.x, a_hi.y, b_hi.y, xhi.x, xhi.y);
-        mma_e4m3_16832(acc[mt], a_hi.z, b_hi.z, a_hi.w, b_hi.w, xhi.z, xhi.w);
+        const uint4 xlo = ld_nc_v4(xrow[mt] + koff_lo);
+        const uint4 xhi = ld_nc_v4(xrow[mt] + koff_hi);
+        mma_e4m3_16832(acc[0][mt], a_lo.x, b_lo.x, a_lo.y, b_lo.y, xlo.x, xlo.y);
+        mma_e4m3_16832(acc[1][mt], a_lo.z, b_lo.z, a_lo.w, b_lo.w, xlo.z, xlo.w);
+        mma_e4m3_16832(acc[0][mt], a_hi.x, b_hi.x, a_hi.y, b_hi.y, xhi.x, xhi.y);
+        mma_e4m3_16832(acc[1][mt], a_hi.z, b_hi.z, a_hi.w, b_hi.w, xhi.z, xhi.w);
     }
 }
 
@@ -261,22 +260,30 @@ fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_s
         for (int d = 0; d < F8V_STAGES; ++d) issue();
     }
 
-    const bool ok0 = g < M;
-    const bool ok1 = (MT > 1) && (g + 8 < M);
+    const uint8_t* xrow[MT];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) xrow[mt] = xq + (size_t)min(mt * 8 + g, M - 1) * K16;
     int slot = 0;
     uint32_t phases = 0;
     int it = 0;
 
     for (int rb = blockIdx.x; rb < rb_real; rb += gridDim.x, ++it) {
-        float acc[MT][4];
+        float acc[2][MT][4];
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
+        for (int a = 0; a < 2; ++a)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) acc[mt][i] = 0.f;
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[a][mt][i] = 0.f;
 
+#pragma unroll 1
         for (int kt = kt_first; kt < kt_hi; kt += F8V_WARPS) {
             f8v_wait(bar_base + 8u * slot, (phases >> slot) & 1u, status);
-            f8_block_compute<MT>(ring_base + slot * F8V_STAGE_BYTES, acc, xq, kt, K16, g, t, ok0, ok1);
+            // k beyond the row (K16 not a multiple of 128) meets zero weights: read offset 0 instead
+            int klo = kt * 128 + t * 16, khi = klo + 64;
+            if (klo >= K16) klo = 0;
+            if (khi >= K16) khi = 0;
+            f8_block_compute<MT>(ring_base + slot * F8V_STAGE_BYTES, acc, xrow, klo, khi, g, t);
             phases ^= 1u << slot;
             __syncwarp();
             if (lane == 0) issue();
@@ -287,7 +294,7 @@ fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_s
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) red[buf][warp][lane][mt * 4 + i] = acc[mt][i];
+            for (int i = 0; i < 4; ++i) red[buf][warp][lane][mt * 4 + i] = acc[0][mt][i] + acc[1][mt][i];
         __syncthreads();
 
         constexpr int SLOTS = 32 * MT * 4;

@@ -38,12 +38,13 @@ def test_status_strings():
 def test_affine_repack_size_law():
     L = _lib.lib()
     s = ctypes.c_size_t()
-    # 4.5 bits per weight: codes + bf16 scale and bias per group of 64, no padding at 128-multiples
+    # 4.5 bits per weight: codes + bf16 scale and bias per group of 64, no padding at 128-multiples,
+    # plus a 128-byte trailer
     assert L.scr_affine_b4_repack_size(8192, 3072, 64, ctypes.byref(s)) == 0
-    assert s.value == 8192 * 3072 // 2 + 2 * 2 * 8192 * 3072 // 64
+    assert s.value == 8192 * 3072 // 2 + 2 * 2 * 8192 * 3072 // 64 + 128
     # rows pad to 128, k to 128
     assert L.scr_affine_b4_repack_size(8, 64, 64, ctypes.byref(s)) == 0
-    assert s.value == (128 // 16) * 1 * 1152
+    assert s.value == (128 // 16) * 1 * 1152 + 128
     # the preset's law: K % group == 0 (crates/compiler/subtile/src/lower.rs:112-127), group 64 only here
     assert L.scr_affine_b4_repack_size(16, 96, 64, ctypes.byref(s)) == -2
     assert L.scr_affine_b4_repack_size(16, 128, 32, ctypes.byref(s)) == -4
