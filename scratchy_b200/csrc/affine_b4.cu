@@ -25,7 +25,7 @@ __global__ void affine_b4_repack_kernel(const uint32_t* __restrict__ w, const ui
          it += (long long)gridDim.x * blockDim.x) {
         const long long blk = it / 80;
         const int sub = int(it % 80);
-        const int kc = int(blk / RB), rb = int(blk % RB);
+        const int rb = int(blk / KC), kc = int(blk % KC);
         uint8_t* out = dst + blk * AFF_BLOCK_BYTES;
         if (sub < 64) {
             const int half = sub >> 5, lane = sub & 31, g = lane >> 2, t = lane & 3;
@@ -51,7 +51,7 @@ __global__ void affine_b4_repack_kernel(const uint32_t* __restrict__ w, const ui
                 if (r1 < N) v.y = uint32_t(scales[(size_t)r1 * G + grp]) | (uint32_t(biases[(size_t)r1 * G + grp]) << 16);
             }
             *reinterpret_cast<uint2*>(out + 1024 + e * 8) = v;
-            if (affine_slow_group(v.x) || affine_slow_group(v.y)) atomicOr(slow_flag, 1u);
+            if (affine_group_needs_generic(v.x) || affine_group_needs_generic(v.y)) atomicOr(slow_flag, 1u);
         }
     }
 }
@@ -67,7 +67,7 @@ __global__ void affine_b4_dump_kernel(const uint8_t* __restrict__ packed, int N,
          it += (long long)gridDim.x * blockDim.x) {
         const long long blk = it / 64;
         const int sub = int(it % 64);
-        const int kc = int(blk / RB), rb = int(blk % RB);
+        const int rb = int(blk / KC), kc = int(blk % KC);
         const int half = sub >> 5, lane = sub & 31, g = lane >> 2, t = lane & 3;
         const int row = rb * 16 + half * 8 + g;
         const int k0 = kc * 128 + t * 32;
@@ -76,8 +76,24 @@ __global__ void affine_b4_dump_kernel(const uint8_t* __restrict__ packed, int N,
         const uint4 piece = *reinterpret_cast<const uint4*>(b + half * 512 + lane * 16);
         const uint2 sb2 = *reinterpret_cast<const uint2*>(b + 1024 + (g * 2 + (t >> 1)) * 8);
         uint32_t regs[16];
-        if (check) affine_dequant_piece<true>(piece, half ? sb2.y : sb2.x, regs);
-        else affine_dequant_piece<false>(piece, half ? sb2.y : sb2.x, regs);
+        const uint32_t sb = half ? sb2.y : sb2.x;
+        if (check) {
+            affine_dequant_piece<true>(piece, sb, regs);
+        } else {
+            // the scaled variant the kernels use, brought back by the exact factor 2^7
+            const AffineScaled c = affine_scaled_consts(sb);
+            affine_dequant_word_scaled(piece.x, c, regs + 0);
+            affine_dequant_word_scaled(piece.y, c, regs + 4);
+            affine_dequant_word_scaled(piece.z, c, regs + 8);
+            affine_dequant_word_scaled(piece.w, c, regs + 12);
+            const uint32_t k128 = 0x43004300u;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const __nv_bfloat162 v = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&regs[i]),
+                                                 *reinterpret_cast<const __nv_bfloat162*>(&k128));
+                regs[i] = *reinterpret_cast<const uint32_t*>(&v);
+            }
+        }
         uint4* o = reinterpret_cast<uint4*>(out + (size_t)row * K + k0);
 #pragma unroll
         for (int i = 0; i < 4; ++i) o[i] = make_uint4(regs[4 * i], regs[4 * i + 1], regs[4 * i + 2], regs[4 * i + 3]);
@@ -139,23 +155,21 @@ __device__ __forceinline__ void gemv_st_cluster_rank0_f32(const float* local_ptr
 // ------------------------------------------------------------------------------------
 // Decode matvec, M <= 16.
 //
-// Persistent CTAs of 8 warps.  A CTA walks row-blocks (16 weight rows) rb = blockIdx.x,
-// += gridDim.x; its warps interleave the row-block's k-chunks (warp w takes kc = w, w+8, ...),
-// so the cross-warp reduction stays inside the CTA: partial accumulators go through
-// double-buffered shared memory once per row-block, in fixed warp order (deterministic).
+// Persistent CTAs of 8 consumer warps + 1 producer warp.  A CTA walks row-blocks (16 weight
+// rows) rb = blockIdx.x, += gridDim.x.  The producer streams each row-block's contiguous
+// k extent HBM -> shared memory with 1-D bulk (TMA) copies of up to 8 blocks (9216 bytes) per
+// stage of a 4-stage ring (full/empty mbarriers), running ahead across row-block boundaries.
+// Consumer warp w takes block w of every stage: two conflict-free 16-byte shared loads per
+// lane, dequantisation in registers, and the dequantised bf16 weights as the A operand of
+// mma.sync.m16n8k16 with the tokens as the 8 columns of B (MT = 1: up to 8 tokens, MT = 2: up
+// to 16).  Lane (g, t) holds codes of rows g and g+8 at k = 128kc + 32t + [0,32) and the
+// activations of token g (and g+8) at the same k, so the contraction index is permuted
+// identically on both operands.  Partial sums of the 8 warps meet once per row-block in
+// double-buffered shared memory, summed in warp order (deterministic).
 //
-// Weights stream HBM -> shared memory through per-warp rings of 1-D bulk (TMA) copies, one
-// 1152-byte block per stage, each stage with its own mbarrier; the ring runs ahead across
-// row-block boundaries, so GEMV_STAGES-1 blocks per warp are always in flight.  A stage is read
-// back with two conflict-free 16-byte loads per lane and dequantised in registers; the
-// dequantised bf16 weights are the A operand of mma.sync.m16n8k16 and the tokens the 8 columns
-// of B (MT = 1: up to 8 tokens, MT = 2: up to 16).  Lane (g, t) holds codes of rows g and g+8
-// at k = 128kc + 32t + [0,32) and the activations of token g (and g+8) at the same k, so the
-// contraction index is permuted identically on both operands.
-//
-// When there are too few row-blocks to fill the machine, gridDim.y = SPLIT CTAs form a
-// thread-block cluster that splits the k-chunks and reduces through distributed shared memory
-// in rank order.  Every wait is bounded (see gemv_wait).
+// With too few row-blocks to fill the machine, gridDim.y = SPLIT CTAs form a thread-block
+// cluster that splits the k extent and reduces through distributed shared memory in rank
+// order.  Every wait is bounded (gemv_wait).
 // ------------------------------------------------------------------------------------
 __device__ __forceinline__ void mma_bf16_16816(float d[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                uint32_t b0, uint32_t b1) {
@@ -164,88 +178,80 @@ __device__ __forceinline__ void mma_bf16_16816(float d[4], uint32_t a0, uint32_t
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ void gemv_mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void gemv_consumer_sync() {          // the 8 consumer warps only
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+}
 
-#define GEMV_WARPS 8
-#define GEMV_STAGES 6
+#define GEMV_CWARPS 8
+#define GEMV_THREADS ((GEMV_CWARPS + 1) * 32)
+#define GEMV_STAGES 4
+#define GEMV_STAGE_BYTES (GEMV_CWARPS * AFF_BLOCK_BYTES)
 #define GEMV_MAX_SPLIT 8
 
-// One 1152-byte block from shared memory against the activations.  Tokens beyond M and k beyond K
-// read clamped (valid) activation addresses instead of zeros: a column of B only reaches the
-// same column of D, which is discarded for tokens >= M, and padded k meets zero weights.
+// One 1152-byte block from shared memory against pre-loaded activations (xv: this lane's 32
+// activations per token tile, in k order).
 template <int MT, bool CHECK>
-__device__ __forceinline__ void gemv_block_compute(uint32_t stage, float acc[2][MT][4], const uint16_t* const xrow[MT],
-                                                   int k0, int lane) {
-    const uint4 p0 = gemv_lds_v4(stage + lane * 16);
-    const uint4 p1 = gemv_lds_v4(stage + 512 + lane * 16);
-    const uint2 sb = gemv_lds_v2(stage + 1024 + ((lane >> 2) * 2 + ((lane & 3) >> 1)) * 8);
-    uint4 xv[MT][4];
+__device__ __forceinline__ void gemv_block_compute(uint32_t blk, float acc[2][MT][4], const uint4 xv[MT][4], int lane) {
+    const uint4 p0 = gemv_lds_v4(blk + lane * 16);
+    const uint4 p1 = gemv_lds_v4(blk + 512 + lane * 16);
+    const uint2 sb = gemv_lds_v2(blk + 1024 + ((lane >> 2) * 2 + ((lane & 3) >> 1)) * 8);
+    const uint32_t wa[4] = {p0.x, p0.y, p0.z, p0.w};
+    const uint32_t wb[4] = {p1.x, p1.y, p1.z, p1.w};
+    if (CHECK) {
+        // generic variant: per-group test for the exact path; weights unscaled
+        const uint32_t s2a = __byte_perm(sb.x, sb.x, 0x1010), b2a = __byte_perm(sb.x, sb.x, 0x3232);
+        const uint32_t s2b = __byte_perm(sb.y, sb.y, 0x1010), b2b = __byte_perm(sb.y, sb.y, 0x3232);
+        const bool slow_a = affine_slow_group(sb.x);
+        const bool slow_b = affine_slow_group(sb.y);
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
+        for (int i = 0; i < 4; ++i) {
+            uint32_t w0[4], w1[4];
+            affine_dequant_word<true>(wa[i], sb.x, s2a, b2a, slow_a, w0);
+            affine_dequant_word<true>(wb[i], sb.y, s2b, b2b, slow_b, w1);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) xv[mt][i] = ld_nc_v4(xrow[mt] + k0 + 8 * i);
-    uint32_t w0[16], w1[16];
-    affine_dequant_piece<CHECK>(p0, sb.x, w0);
-    affine_dequant_piece<CHECK>(p1, sb.y, w1);
+            for (int mt = 0; mt < MT; ++mt) {
+                mma_bf16_16816(acc[0][mt], w0[0], w1[0], w0[1], w1[1], xv[mt][i].x, xv[mt][i].y);
+                mma_bf16_16816(acc[1][mt], w0[2], w1[2], w0[3], w1[3], xv[mt][i].z, xv[mt][i].w);
+            }
+        }
+    } else {
+        // scaled variant: weights carry a factor 2^-7 that the caller removes from the accumulators
+        const AffineScaled ca = affine_scaled_consts(sb.x);
+        const AffineScaled cb = affine_scaled_consts(sb.y);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < 4; ++i) {
+            uint32_t w0[4], w1[4];
+            affine_dequant_word_scaled(wa[i], ca, w0);
+            affine_dequant_word_scaled(wb[i], cb, w1);
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-            // two independent accumulator sets halve the dependent-MMA chain
-            mma_bf16_16816(acc[0][mt], w0[4 * i + 0], w1[4 * i + 0], w0[4 * i + 1], w1[4 * i + 1], xv[mt][i].x, xv[mt][i].y);
-            mma_bf16_16816(acc[1][mt], w0[4 * i + 2], w1[4 * i + 2], w0[4 * i + 3], w1[4 * i + 3], xv[mt][i].z, xv[mt][i].w);
+            for (int mt = 0; mt < MT; ++mt) {
+                // two independent accumulator sets halve the dependent-MMA chain
+                mma_bf16_16816(acc[0][mt], w0[0], w1[0], w0[1], w1[1], xv[mt][i].x, xv[mt][i].y);
+                mma_bf16_16816(acc[1][mt], w0[2], w1[2], w0[3], w1[3], xv[mt][i].z, xv[mt][i].w);
+            }
         }
     }
 }
 
 template <int MT, int SPLIT_CLUSTER, bool CHECK>
-__device__ __forceinline__ void gemv_main(const uint8_t* __restrict__ packed, const uint16_t* __restrict__ x,
-                                          uint16_t* __restrict__ y, int M, int N, int K, int RB, int KC, int rb_real,
-                                          int split, int* __restrict__ status, uint8_t* ring_gen,
-                                          uint64_t (*bars)[GEMV_STAGES], float (*red)[GEMV_WARPS][32][MT * 4],
-                                          float (*cl_part)[16][MT * 8]) {
-    const int sp = SPLIT_CLUSTER ? int(gemv_cluster_ctarank()) : 0;
+__device__ __forceinline__ void gemv_consumer(const uint16_t* __restrict__ x, uint16_t* __restrict__ y, int M, int N,
+                                              int K, int kc_lo, int kc_hi, int nstage, int rb_real, int split, int sp,
+                                              int* __restrict__ status, uint32_t ring_base, uint32_t full_base,
+                                              uint32_t empty_base, float (*red)[GEMV_CWARPS][32][MT * 4],
+                                              float (*cl_part)[16][MT * 8]) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-
-    // k-chunks of this CTA: [kc_lo, kc_hi); warp w takes kc_lo + w, + GEMV_WARPS, ...
-    const int per = (KC + split - 1) / split;
-    const int kc_lo = sp * per;
-    const int kc_hi = min(KC, kc_lo + per);
-    const int kc_first = kc_lo + warp;
-    const bool has_work = kc_first < kc_hi;
-
-    const size_t chunk_stride = (size_t)RB * AFF_BLOCK_BYTES;
-    const uint32_t ring_base = gemv_smem_u32(ring_gen) + (uint32_t)warp * (GEMV_STAGES * AFF_BLOCK_BYTES);
-    const uint32_t bar_base = gemv_smem_u32(&bars[warp][0]);
-
-    // producer cursor (only lane 0 uses it): next block to request, in consumption order
-    int prb = blockIdx.x, pkc = kc_first, pslot = 0;
-    auto issue = [&]() {
-        if (has_work && prb < rb_real) {
-            const uint32_t bar = bar_base + 8u * pslot;
-            gemv_arrive_expect_tx(bar, AFF_BLOCK_BYTES);
-            gemv_bulk_g2s(ring_base + pslot * AFF_BLOCK_BYTES, packed + (size_t)pkc * chunk_stride + (size_t)prb * AFF_BLOCK_BYTES,
-                          AFF_BLOCK_BYTES, bar);
-            pkc += GEMV_WARPS;
-            if (pkc >= kc_hi) { pkc = kc_first; prb += gridDim.x; }
-        }
-        pslot = (pslot + 1 == GEMV_STAGES) ? 0 : pslot + 1;
-    };
-    if (lane == 0) {
-#pragma unroll 1
-        for (int d = 0; d < GEMV_STAGES; ++d) issue();
-    }
-
-    // activation rows this lane feeds into the B operand (clamped to a valid token)
+    // activation rows this lane feeds into the B operand.  Tokens beyond M read a clamped (valid)
+    // row: a column of B only reaches the same column of D, which is discarded for tokens >= M.
     const uint16_t* xrow[MT];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) xrow[mt] = x + (size_t)min(mt * 8 + g, M - 1) * K;
-    const int kt_off = t * 32;
 
-    int slot = 0;
-    uint32_t phases = 0;                       // bit d = parity the next wait on stage d expects
+    uint32_t n_it = 0;                         // stages consumed so far (ring position and phase)
     int it = 0;
-
     for (int rb = blockIdx.x; rb < rb_real; rb += gridDim.x, ++it) {
         float acc[2][MT][4];
 #pragma unroll
@@ -256,15 +262,22 @@ __device__ __forceinline__ void gemv_main(const uint8_t* __restrict__ packed, co
                 for (int i = 0; i < 4; ++i) acc[a][mt][i] = 0.f;
 
 #pragma unroll 1
-        for (int kc = kc_first; kc < kc_hi; kc += GEMV_WARPS) {
-            gemv_wait(bar_base + 8u * slot, (phases >> slot) & 1u, status);
-            int k0 = kc * 128 + kt_off;
-            if (k0 >= K) k0 = 0;               // padded k: the weights there are zero
-            gemv_block_compute<MT, CHECK>(ring_base + slot * AFF_BLOCK_BYTES, acc, xrow, k0, lane);
-            phases ^= 1u << slot;
-            __syncwarp();                      // every lane has consumed the stage: refill it
-            if (lane == 0) issue();
-            slot = (slot + 1 == GEMV_STAGES) ? 0 : slot + 1;
+        for (int j = 0; j < nstage; ++j, ++n_it) {
+            const int kc = kc_lo + j * GEMV_CWARPS + warp;
+            const bool active = kc < kc_hi;                       // warp-uniform
+            const uint32_t slot = n_it & (GEMV_STAGES - 1);
+            // the activations do not depend on the ring: fetch them while the weights are in flight
+            uint4 xv[MT][4];
+            int k0 = kc * 128 + t * 32;
+            if (k0 >= K) k0 = 0;                                  // padded k (zero weights) or idle warp
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) xv[mt][i] = ld_nc_v4(xrow[mt] + k0 + 8 * i);
+            gemv_wait(full_base + 8u * slot, (n_it / GEMV_STAGES) & 1u, status);
+            if (active) gemv_block_compute<MT, CHECK>(ring_base + slot * GEMV_STAGE_BYTES + warp * AFF_BLOCK_BYTES, acc, xv, lane);
+            __syncwarp();                                         // every lane has consumed the stage
+            if (lane == 0) gemv_mbar_arrive(empty_base + 8u * slot);
         }
 
         // cross-warp reduction of this row-block, fixed warp order, double-buffered
@@ -272,11 +285,12 @@ __device__ __forceinline__ void gemv_main(const uint8_t* __restrict__ packed, co
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) red[buf][warp][lane][mt * 4 + i] = acc[0][mt][i] + acc[1][mt][i];
-        __syncthreads();
+            for (int i = 0; i < 4; ++i)
+                red[buf][warp][lane][mt * 4 + i] = (acc[0][mt][i] + acc[1][mt][i]) * (CHECK ? 1.0f : AFF_SCALED_FACTOR);
+        gemv_consumer_sync();
 
         // thread e owns accumulator slot (ln, idx): c0,c1 -> row g, tokens 2t,2t+1 ; c2,c3 -> row g+8
-        constexpr int SLOTS = 32 * MT * 4;     // <= 256 = blockDim.x
+        constexpr int SLOTS = 32 * MT * 4;     // <= 256 consumer threads
         const int e = threadIdx.x;
         const int ln = e / (MT * 4), idx = e % (MT * 4);
         const int row = (ln >> 2) + (((idx & 3) >> 1) ? 8 : 0);
@@ -285,7 +299,7 @@ __device__ __forceinline__ void gemv_main(const uint8_t* __restrict__ packed, co
         if (e < SLOTS && tok < M) {
             float total = 0.f;
 #pragma unroll
-            for (int wdx = 0; wdx < GEMV_WARPS; ++wdx) total += red[buf][wdx][ln][idx];
+            for (int wdx = 0; wdx < GEMV_CWARPS; ++wdx) total += red[buf][wdx][ln][idx];
             if (SPLIT_CLUSTER) {
                 gemv_st_cluster_rank0_f32(&cl_part[sp][row][tok], total);
             } else if (n < N) {
@@ -293,39 +307,84 @@ __device__ __forceinline__ void gemv_main(const uint8_t* __restrict__ packed, co
                 y[(size_t)tok * N + n] = *reinterpret_cast<const uint16_t*>(&v);
             }
         }
-        if (SPLIT_CLUSTER) {
-            // one row-block per CTA in cluster mode (gridDim.x == rb_real): exchange once
-            gemv_cluster_sync_all();
-            if (sp == 0 && e < SLOTS && tok < M && n < N) {
-                float s = 0.f;
-                for (int r = 0; r < split; ++r) s += cl_part[r][row][tok];   // rank order
-                const __nv_bfloat16 v = __float2bfloat16_rn(s);
-                y[(size_t)tok * N + n] = *reinterpret_cast<const uint16_t*>(&v);
-            }
-        }
     }
 }
 
 template <int MT, int SPLIT_CLUSTER>
-__global__ void __launch_bounds__(GEMV_WARPS * 32, 2)
+__global__ void __launch_bounds__(GEMV_THREADS, (MT == 1 ? 3 : 2))
 affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __restrict__ x, uint16_t* __restrict__ y,
                       int M, int N, int K, int RB, int KC, int rb_real, int split, int* __restrict__ status) {
-    extern __shared__ __align__(128) uint8_t gemv_ring[];          // [GEMV_WARPS][GEMV_STAGES][AFF_BLOCK_BYTES]
-    __shared__ __align__(8) uint64_t bars[GEMV_WARPS][GEMV_STAGES];
-    __shared__ float red[2][GEMV_WARPS][32][MT * 4];
+    extern __shared__ __align__(128) uint8_t gemv_ring[];          // [GEMV_STAGES][8 blocks]
+    __shared__ __align__(8) uint64_t full_bar[GEMV_STAGES];
+    __shared__ __align__(8) uint64_t empty_bar[GEMV_STAGES];
+    __shared__ float red[2][GEMV_CWARPS][32][MT * 4];
     __shared__ float cl_part[SPLIT_CLUSTER ? GEMV_MAX_SPLIT : 1][16][MT * 8];
 
-    if ((threadIdx.x & 31) == 0) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
 #pragma unroll
-        for (int d = 0; d < GEMV_STAGES; ++d) gemv_mbar_init(gemv_smem_u32(&bars[threadIdx.x >> 5][d]), 1);
+        for (int d = 0; d < GEMV_STAGES; ++d) {
+            gemv_mbar_init(gemv_smem_u32(&full_bar[d]), 1);
+            gemv_mbar_init(gemv_smem_u32(&empty_bar[d]), GEMV_CWARPS);
+        }
     }
     gemv_fence_mbar_init();
     __syncthreads();
 
-    // one word per matrix says whether any group needs the exact (two-step rounding) path
-    const bool check = *reinterpret_cast<const unsigned int*>(packed + (size_t)RB * KC * AFF_BLOCK_BYTES) != 0;
-    if (check) gemv_main<MT, SPLIT_CLUSTER, true>(packed, x, y, M, N, K, RB, KC, rb_real, split, status, gemv_ring, bars, red, cl_part);
-    else gemv_main<MT, SPLIT_CLUSTER, false>(packed, x, y, M, N, K, RB, KC, rb_real, split, status, gemv_ring, bars, red, cl_part);
+    const int sp = SPLIT_CLUSTER ? int(gemv_cluster_ctarank()) : 0;
+    // k-chunks of this CTA: [kc_lo, kc_hi), consumed 8 at a time
+    const int per = (KC + split - 1) / split;
+    const int kc_lo = sp * per;
+    const int kc_hi = min(KC, kc_lo + per);
+    const int nstage = (max(kc_hi - kc_lo, 0) + GEMV_CWARPS - 1) / GEMV_CWARPS;
+    const uint32_t ring_base = gemv_smem_u32(gemv_ring);
+    const uint32_t full_base = gemv_smem_u32(&full_bar[0]);
+    const uint32_t empty_base = gemv_smem_u32(&empty_bar[0]);
+
+    if (warp == GEMV_CWARPS) {
+        // ---- producer warp: one lane streams the row-blocks' k extents into the ring
+        if (lane == 0) {
+            uint32_t n_it = 0;
+            for (int rb = blockIdx.x; rb < rb_real; rb += gridDim.x) {
+                const uint8_t* src = packed + ((size_t)rb * KC + kc_lo) * AFF_BLOCK_BYTES;
+                for (int j = 0; j < nstage; ++j, ++n_it) {
+                    const uint32_t slot = n_it & (GEMV_STAGES - 1);
+                    gemv_wait(empty_base + 8u * slot, ((n_it / GEMV_STAGES) & 1u) ^ 1u, status);
+                    const uint32_t bytes = (uint32_t)min(GEMV_CWARPS, kc_hi - kc_lo - j * GEMV_CWARPS) * AFF_BLOCK_BYTES;
+                    gemv_arrive_expect_tx(full_base + 8u * slot, bytes);
+                    gemv_bulk_g2s(ring_base + slot * GEMV_STAGE_BYTES, src + (size_t)j * GEMV_STAGE_BYTES, bytes,
+                                  full_base + 8u * slot);
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        // one word per matrix says whether any group needs the exact (two-step rounding) path
+        const bool check = *reinterpret_cast<const unsigned int*>(packed + (size_t)RB * KC * AFF_BLOCK_BYTES) != 0;
+        if (check)
+            gemv_consumer<MT, SPLIT_CLUSTER, true>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, status, ring_base,
+                                                   full_base, empty_base, red, cl_part);
+        else
+            gemv_consumer<MT, SPLIT_CLUSTER, false>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, status, ring_base,
+                                                    full_base, empty_base, red, cl_part);
+    }
+
+    if (SPLIT_CLUSTER) {
+        // one row-block per CTA in cluster mode (gridDim.x == rb_real): exchange once, rank order
+        gemv_cluster_sync_all();
+        constexpr int SLOTS = 32 * MT * 4;
+        const int e = threadIdx.x;
+        const int ln = e / (MT * 4), idx = e % (MT * 4);
+        const int row = (ln >> 2) + (((idx & 3) >> 1) ? 8 : 0);
+        const int tok = (idx >> 2) * 8 + (ln & 3) * 2 + (idx & 1);
+        const int n = blockIdx.x * 16 + row;
+        if (sp == 0 && e < SLOTS && tok < M && n < N) {
+            float s = 0.f;
+            for (int r = 0; r < split; ++r) s += cl_part[r][row][tok];
+            const __nv_bfloat16 v = __float2bfloat16_rn(s);
+            y[(size_t)tok * N + n] = *reinterpret_cast<const uint16_t*>(&v);
+        }
+    }
 }
 
 // ------------------------------------------------------------------------------------
@@ -387,12 +446,12 @@ extern "C" int32_t scr_affine_b4_dequant_dump(scr_ctx* ctx, const void* packed, 
 // shares its k-chunks so that about one CTA per SM is busy.
 static void affine_gemv_shape(int rb_real, int KC, int sms, int* grid_x, int* split) {
     if (rb_real >= sms) {
-        *grid_x = std::min(rb_real, 2 * sms);
+        *grid_x = std::min(rb_real, 3 * sms);
         *split = 1;
         return;
     }
     int s = 1;
-    while (s * 2 <= GEMV_MAX_SPLIT && rb_real * s * 2 <= 2 * sms && KC / (s * 2) >= GEMV_WARPS / 2) s *= 2;
+    while (s * 2 <= GEMV_MAX_SPLIT && rb_real * s * 2 <= 2 * sms && KC / (s * 2) >= GEMV_CWARPS / 2) s *= 2;
     *grid_x = rb_real;
     *split = s;
 }
@@ -404,11 +463,11 @@ static int32_t affine_gemv_launch(scr_ctx* ctx, const uint8_t* packed, const uin
     const int rb_real = scr_ceil_div(N, 16);
     int grid_x = 1, split = 1;
     affine_gemv_shape(rb_real, g.KC, ctx->sm_count, &grid_x, &split);
-    constexpr int kRingBytes = GEMV_WARPS * GEMV_STAGES * AFF_BLOCK_BYTES;
+    constexpr int kRingBytes = GEMV_STAGES * GEMV_STAGE_BYTES;
     if (split == 1) {
         cudaError_t e0 = cudaFuncSetAttribute(affine_b4_gemv_kernel<MT, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes);
         if (e0 != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine_b4_gemv smem attribute: %s", cudaGetErrorString(e0));
-        affine_b4_gemv_kernel<MT, 0><<<dim3(grid_x, 1), GEMV_WARPS * 32, kRingBytes, stream>>>(packed, x, y, M, N, K, g.RB, g.KC,
+        affine_b4_gemv_kernel<MT, 0><<<dim3(grid_x, 1), GEMV_THREADS, kRingBytes, stream>>>(packed, x, y, M, N, K, g.RB, g.KC,
                                                                                               rb_real, 1, ctx->dev_status);
         return scr_check_launch(ctx, "affine_b4_gemv");
     }
@@ -416,7 +475,7 @@ static int32_t affine_gemv_launch(scr_ctx* ctx, const uint8_t* packed, const uin
     if (e1 != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine_b4_gemv smem attribute: %s", cudaGetErrorString(e1));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid_x, split, 1);
-    cfg.blockDim = dim3(GEMV_WARPS * 32, 1, 1);
+    cfg.blockDim = dim3(GEMV_THREADS, 1, 1);
     cfg.dynamicSmemBytes = kRingBytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];

@@ -7,18 +7,26 @@
 // The f32 product of a bf16 scale (8 significant bits) and a 4-bit code is exact, so the
 // f32 stage rounds once (the add) and the bf16 conversion rounds a second time.
 //
-// Fast path: one packed `fma.rn.bf16x2` computes the exact scale*code + bias and rounds
-// ONCE to bf16.  That equals the reference's two-step rounding unless the f32 stage is
-// inexact and lands on a bf16 half-way point, which needs 0 < |bias| < 2^-13 |scale|
-// (the bias entirely below f32's window under the product).  Groups whose (scale, bias)
-// could do that, or that hold a value tiny enough for flush-to-zero to matter, take the
-// exact f32 path instead (`affine_slow_group`).
+// Packed path: one `fma.rn.bf16x2` computes the exact scale*code + bias and rounds ONCE to
+// bf16.  That equals the reference's two-step rounding unless the f32 stage is inexact and
+// lands on a bf16 half-way point, which needs 0 < |bias| < 2^-13 |scale| (the bias entirely
+// below f32's window under the product).  Groups whose (scale, bias) could do that, or that
+// hold a value tiny enough for flush-to-zero to matter, take the exact f32 path instead
+// (`affine_slow_group`).
+//
+// Two packed variants exist.  The generic one builds 128 + code with a mask-or, subtracts 128
+// and tests every group for the exact path.  The scaled one is used when the repack kernel
+// found no group that needs the exact path and every scale below 2 in magnitude (trailer flag
+// == 0): a code left in place in bits [0,4) or [4,8) of a 16-bit half IS the bf16 number
+// code * 2^-133 (resp. 16 * code * 2^-133, the subnormal/first-binade range is linear in the
+// low 8 bits), so fma(scale * 2^126 [or 2^122], bits, bias * 2^-7) = w * 2^-7 with the same
+// single rounding; the factor 2^7 is applied, exactly, to the f32 accumulator afterwards.
 //
 // Streaming layout ("blocks"), produced once at load time by the repack kernel:
 //   N is padded to a multiple of 128 rows and K to a multiple of 128; a block covers
-//   16 rows x 128 k and is 1152 bytes; block (kc, rb) sits at ((kc * RB) + rb) * 1152
-//   with RB = N_pad / 16, i.e. k-chunk-major so that the 8 row-blocks of a 128-row GEMM
-//   tile are one contiguous 9216-byte run.
+//   16 rows x 128 k and is 1152 bytes; block (rb, kc) sits at ((rb * KC) + kc) * 1152
+//   with KC = K_pad / 128, i.e. row-block-major: the whole k extent of 16 rows is one
+//   contiguous run, which the decode matvec streams with a few large bulk copies.
 //   bytes [   0, 512): half 0 = rows 16rb + g,     piece `lane = 4g + t` (16 bytes) holds the
 //   bytes [ 512,1024): half 1 = rows 16rb + 8 + g  32 codes k = 128kc + 32t + [0,32) of its row
 //   bytes [1024,1152): for (g, h = 0..1): 8 bytes at 1024 + (2g + h) * 8 =
@@ -98,6 +106,64 @@ __device__ __forceinline__ void affine_dequant_word_fast(uint32_t word, uint32_t
         __nv_bfloat162 qf = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&q), m128);   // exact: code
         __nv_bfloat162 w = __hfma2(s, qf, b);                        // fused, one rounding to bf16
         out[j] = *reinterpret_cast<const uint32_t*>(&w);
+    }
+}
+
+// True when the scaled variant must not be used for this group.
+__host__ __device__ __forceinline__ bool affine_group_needs_generic(uint32_t sb) {
+    const uint32_t s = sb & 0x7FFFu;
+    return affine_slow_group(sb) || (s != 0 && int(s >> 7) > 127);
+}
+
+// Scaled variant: the group's constants, made once per 16-byte piece.
+struct AffineScaled {
+    uint32_t s_lo;    // scale * 2^126 in both halves (codes in bits [0,4) of a half)
+    uint32_t s_hi;    // scale * 2^122 in both halves (codes in bits [4,8) of a half)
+    uint32_t b7;      // bias * 2^-7 in both halves
+};
+__device__ __forceinline__ AffineScaled affine_scaled_consts(uint32_t sb) {
+    const uint32_t s2 = __byte_perm(sb, sb, 0x1010), b2 = __byte_perm(sb, sb, 0x3232);
+    const uint32_t k126 = 0x7E807E80u, k122 = 0x7C807C80u, km7 = 0x3C003C00u;   // 2^126, 2^122, 2^-7 as bf16x2
+    const __nv_bfloat162 s = *reinterpret_cast<const __nv_bfloat162*>(&s2);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&b2);
+    const __nv_bfloat162 a = __hmul2(s, *reinterpret_cast<const __nv_bfloat162*>(&k126));
+    const __nv_bfloat162 c = __hmul2(s, *reinterpret_cast<const __nv_bfloat162*>(&k122));
+    const __nv_bfloat162 d = __hmul2(b, *reinterpret_cast<const __nv_bfloat162*>(&km7));
+    AffineScaled r;
+    r.s_lo = *reinterpret_cast<const uint32_t*>(&a);
+    r.s_hi = *reinterpret_cast<const uint32_t*>(&c);
+    r.b7 = *reinterpret_cast<const uint32_t*>(&d);
+    return r;
+}
+// One word (8 codes) -> 4 bf16x2 registers holding w * 2^-7, natural k order.
+__device__ __forceinline__ void affine_dequant_word_scaled(uint32_t word, const AffineScaled& c, uint32_t out[4]) {
+    const __nv_bfloat162 s_lo = *reinterpret_cast<const __nv_bfloat162*>(&c.s_lo);
+    const __nv_bfloat162 s_hi = *reinterpret_cast<const __nv_bfloat162*>(&c.s_hi);
+    const __nv_bfloat162 b7 = *reinterpret_cast<const __nv_bfloat162*>(&c.b7);
+    const uint32_t w8 = word >> 8;
+    const uint32_t q0 = word & 0x000F000Fu, q1 = word & 0x00F000F0u;
+    const uint32_t q2 = w8 & 0x000F000Fu, q3 = w8 & 0x00F000F0u;
+    const __nv_bfloat162 r0 = __hfma2(s_lo, *reinterpret_cast<const __nv_bfloat162*>(&q0), b7);
+    const __nv_bfloat162 r1 = __hfma2(s_hi, *reinterpret_cast<const __nv_bfloat162*>(&q1), b7);
+    const __nv_bfloat162 r2 = __hfma2(s_lo, *reinterpret_cast<const __nv_bfloat162*>(&q2), b7);
+    const __nv_bfloat162 r3 = __hfma2(s_hi, *reinterpret_cast<const __nv_bfloat162*>(&q3), b7);
+    out[0] = *reinterpret_cast<const uint32_t*>(&r0);
+    out[1] = *reinterpret_cast<const uint32_t*>(&r1);
+    out[2] = *reinterpret_cast<const uint32_t*>(&r2);
+    out[3] = *reinterpret_cast<const uint32_t*>(&r3);
+}
+#define AFF_SCALED_FACTOR 128.0f      // multiply accumulators of scaled weights by this (exact)
+
+// One word with the group's pre-duplicated scale / bias; `slow` (evaluated once per group by the
+// caller, only when the matrix's trailer flag is set) selects the exact path.
+template <bool CHECK>
+__device__ __forceinline__ void affine_dequant_word(uint32_t word, uint32_t sb, uint32_t s2, uint32_t b2, bool slow,
+                                                    uint32_t out[4]) {
+    if (CHECK && slow) {
+        const uint4 r = affine_dequant_word_exact(word, sb);
+        out[0] = r.x; out[1] = r.y; out[2] = r.z; out[3] = r.w;
+    } else {
+        affine_dequant_word_fast(word, s2, b2, out);
     }
 }
 

@@ -5,7 +5,7 @@
 // Persistent, warp-specialised CTA (320 threads), one per SM:
 //   warp 0      producer: per 128-k chunk, two TMA tile loads of the activations (tensor map over
 //               x[M,K], 64 x 128 box, 128-byte swizzle; out-of-range rows/k read as zero) and one
-//               1-D bulk copy of the packed weight blocks (BN/16 contiguous 1152-byte blocks)
+//               1-D bulk copy per row-block of the packed weight blocks (BN/16 x 1152 bytes)
 //   warp 1      owns TMEM; one elected thread issues tcgen05.mma kind::f16 (A = 128 tokens,
 //               B = BN channels, 8 x K=16 per chunk) and commits the stage / accumulator barriers
 //   warps 2-5   dequantise: packed codes (shared) -> bf16 via affine_dequant_piece -> the K-major
@@ -112,8 +112,9 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
                 for (int kc = 0; kc < KC; ++kc) {
                     mbar_wait(pempty(sp), php ^ 1u, status, TC_ERR_EMPTY_WAIT);
                     mbar_arrive_expect_tx(pfull(sp), (uint32_t)rbn * AFF_BLOCK_BYTES);
-                    bulk_g2s(smem_base + S::kPOff + sp * S::kPStage, packed + ((size_t)kc * RB + rb0) * AFF_BLOCK_BYTES,
-                             (uint32_t)rbn * AFF_BLOCK_BYTES, pfull(sp));
+                    for (int j = 0; j < rbn; ++j)       // row-block-major packing: one block per row-block
+                        bulk_g2s(smem_base + S::kPOff + sp * S::kPStage + j * AFF_BLOCK_BYTES,
+                                 packed + ((size_t)(rb0 + j) * KC + kc) * AFF_BLOCK_BYTES, AFF_BLOCK_BYTES, pfull(sp));
                     if (++sp == A4G_SP) { sp = 0; php ^= 1u; }
 
                     mbar_wait(xempty(sx), phx ^ 1u, status, TC_ERR_EMPTY_WAIT);
@@ -183,8 +184,16 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
                     const uint4 piece = ld_shared_v4(blk + half * 512 + lane * 16);
                     const uint32_t sb = ld_shared_u32(blk + 1024 + (g * 2 + (t >> 1)) * 8 + half * 4);
                     uint32_t w[16];
-                    if (check) affine_dequant_piece<true>(piece, sb, w);
-                    else affine_dequant_piece<false>(piece, sb, w);
+                    if (check) {
+                        affine_dequant_piece<true>(piece, sb, w);
+                    } else {
+                        // scaled variant (w * 2^-7); the epilogue multiplies the accumulators by 2^7
+                        const AffineScaled c = affine_scaled_consts(sb);
+                        affine_dequant_word_scaled(piece.x, c, w + 0);
+                        affine_dequant_word_scaled(piece.y, c, w + 4);
+                        affine_dequant_word_scaled(piece.z, c, w + 8);
+                        affine_dequant_word_scaled(piece.w, c, w + 12);
+                    }
                     // row = 16 rbl + 8 half + g -> 8-row group (2 rbl + half), row-in-group g;
                     // k = 32 t + [0,32) -> atom t>>1, 16-byte chunks (t&1)*4 + [0,4)
                     const uint32_t rowbase = ds + (uint32_t)(t >> 1) * (uint32_t)(BN * 128) + (uint32_t)(2 * rbl + half) * 1024u +
@@ -215,6 +224,8 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
         // ------------------------------------------------------------------ epilogue (warps 6..9)
         const int q = warp & 3;
         const bool vec_ok = (N % 8) == 0;
+        const float out_scale =
+            (*reinterpret_cast<const unsigned int*>(packed + (size_t)RB * KC * AFF_BLOCK_BYTES) != 0) ? 1.0f : AFF_SCALED_FACTOR;
         int it = 0;
         for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
             const int mt = tile % MT, nb = tile / MT;
@@ -234,7 +245,8 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
                     uint32_t o[16];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        const __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                        const __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(r[2 * j]) * out_scale,
+                                                                        __uint_as_float(r[2 * j + 1]) * out_scale);
                         o[j] = *reinterpret_cast<const uint32_t*>(&p);
                     }
                     if (vec_ok && nc + 32 <= N) {
