@@ -56,6 +56,12 @@ __global__ void affine_b4_repack_kernel(const uint32_t* __restrict__ w, const ui
     }
 }
 
+// The matvec kernels prefetch weights before they wait for the preceding kernel of the stream
+// (programmatic dependent launch), which is only sound if the weights are complete by then.
+// A plain launch of this empty kernel after the repack puts a full stream-order dependency
+// between the repack and anything launched later.
+__global__ void affine_b4_repack_fence_kernel() {}
+
 // ------------------------------------------------------------------------------------
 // Dump hook: streaming blocks -> dense bf16 [N, K], through affine_dequant_piece.
 // ------------------------------------------------------------------------------------
@@ -330,6 +336,10 @@ affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __rest
     }
     gemv_fence_mbar_init();
     __syncthreads();
+    // Programmatic dependent launch: let the next kernel of the stream start its own weight
+    // prefetch as this one drains.  Weights are load-time constants, so this kernel's producer
+    // starts at once; only the consumers wait for the preceding kernel (which wrote x).
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     const int sp = SPLIT_CLUSTER ? int(gemv_cluster_ctarank()) : 0;
     // k-chunks of this CTA: [kc_lo, kc_hi), consumed 8 at a time
@@ -359,6 +369,7 @@ affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __rest
         }
         __syncwarp();
     } else {
+        asm volatile("griddepcontrol.wait;" ::: "memory");        // x (and y's previous readers) are settled
         // one word per matrix says whether any group needs the exact (two-step rounding) path
         const bool check = *reinterpret_cast<const unsigned int*>(packed + (size_t)RB * KC * AFF_BLOCK_BYTES) != 0;
         if (check)
@@ -423,7 +434,10 @@ extern "C" int32_t scr_affine_b4_repack(scr_ctx* ctx, const uint32_t* w, const u
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine_b4_repack memset: %s", cudaGetErrorString(e));
     affine_b4_repack_kernel<<<blocks, threads, 0, (cudaStream_t)stream>>>(w, scales, biases, N, K, g.RB, g.KC,
                                                                          (uint8_t*)dst, flag);
-    return scr_check_launch(ctx, "affine_b4_repack");
+    int32_t st2 = scr_check_launch(ctx, "affine_b4_repack");
+    if (st2) return st2;
+    affine_b4_repack_fence_kernel<<<1, 32, 0, (cudaStream_t)stream>>>();
+    return scr_check_launch(ctx, "affine_b4_repack_fence");
 }
 
 extern "C" int32_t scr_affine_b4_dequant_dump(scr_ctx* ctx, const void* packed, int32_t N, int32_t K, int32_t group,
@@ -464,31 +478,31 @@ static int32_t affine_gemv_launch(scr_ctx* ctx, const uint8_t* packed, const uin
     int grid_x = 1, split = 1;
     affine_gemv_shape(rb_real, g.KC, ctx->sm_count, &grid_x, &split);
     constexpr int kRingBytes = GEMV_STAGES * GEMV_STAGE_BYTES;
-    if (split == 1) {
-        cudaError_t e0 = cudaFuncSetAttribute(affine_b4_gemv_kernel<MT, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes);
-        if (e0 != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine_b4_gemv smem attribute: %s", cudaGetErrorString(e0));
-        affine_b4_gemv_kernel<MT, 0><<<dim3(grid_x, 1), GEMV_THREADS, kRingBytes, stream>>>(packed, x, y, M, N, K, g.RB, g.KC,
-                                                                                              rb_real, 1, ctx->dev_status);
-        return scr_check_launch(ctx, "affine_b4_gemv");
-    }
-    cudaError_t e1 = cudaFuncSetAttribute(affine_b4_gemv_kernel<MT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes);
-    if (e1 != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine_b4_gemv smem attribute: %s", cudaGetErrorString(e1));
+    auto kernel = (split == 1) ? affine_b4_gemv_kernel<MT, 0> : affine_b4_gemv_kernel<MT, 1>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes);
+    if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine_b4_gemv smem attribute: %s", cudaGetErrorString(e));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid_x, split, 1);
     cfg.blockDim = dim3(GEMV_THREADS, 1, 1);
     cfg.dynamicSmemBytes = kRingBytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = split;
-    attr[0].val.clusterDim.z = 1;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+    if (split > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = 1;
+        attr[na].val.clusterDim.y = split;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, affine_b4_gemv_kernel<MT, 1>, packed, x, y, M, N, K, g.RB, g.KC, rb_real, split,
-                                       ctx->dev_status);
-    if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine_b4_gemv cluster launch: %s", cudaGetErrorString(e));
-    return scr_check_launch(ctx, "affine_b4_gemv(cluster)");
+    cfg.numAttrs = na;
+    e = cudaLaunchKernelEx(&cfg, kernel, packed, x, y, M, N, K, g.RB, g.KC, rb_real, split, ctx->dev_status);
+    if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine_b4_gemv launch: %s", cudaGetErrorString(e));
+    return scr_check_launch(ctx, "affine_b4_gemv");
 }
 
 // Defined in affine_b4_gemm.cu
