@@ -35,6 +35,8 @@ __global__ void fp8_repack_kernel(const uint8_t* __restrict__ w, const float* __
         sc[i] = (i < N) ? w_scale[i] : 0.f;
 }
 
+__global__ void fp8_repack_fence_kernel() {}
+
 // ------------------------------------------------------------------------------------
 // Per-token dynamic quantisation.  One CTA per token row: absmax, then encode.
 //   a_scale = min(max(absmax * (1/448), 1/448/448), 448); inv = 1 / a_scale (IEEE division);
@@ -134,14 +136,17 @@ __global__ void e4m3_encode_kernel(const float* __restrict__ v, long long count,
 // Decode matvec, M <= 16: e4m3 weights are the A operand of mma.sync.m16n8k32
 // (e4m3 x e4m3 -> f32) exactly as stored; there is no dequantisation arithmetic.
 //
-// Persistent CTAs of 8 warps walk row-blocks (16 weight rows = two 8-row swizzle groups of a
-// 128 x 128 tile, 2 KB per k-tile) rb = blockIdx.x, += gridDim.x; the warps interleave the
-// k-tiles and reduce through double-buffered shared memory in warp order.  Weights stream
-// HBM -> shared memory through per-warp rings of 1-D bulk (TMA) copies (2 KB per stage, one
-// mbarrier each, running ahead across row-blocks).  Lane (g, t) reads the 16-byte chunks t and
-// t+4 of rows g and g+8 and the same chunks of token g's quantised activations, so both
-// operands see the same permutation of k.  With few row-blocks, gridDim.y = SPLIT CTAs form a
-// cluster that splits the k-tiles and reduces over distributed shared memory in rank order.
+// Persistent CTAs of 8 consumer warps + 1 producer warp walk row-blocks (16 weight rows = two
+// 8-row swizzle groups of a 128 x 128 tile, 2 KB per k-tile) rb = blockIdx.x, += gridDim.x.
+// The producer streams 8 k-tiles (8 x 2 KB 1-D bulk copies) per stage of a 4-stage ring with
+// full/empty mbarriers, running ahead across row-blocks; consumer warp w takes k-tile w of every
+// stage.  Lane (g, t) reads the 16-byte chunks t and t+4 of rows g and g+8 and the same chunks
+// of token g's quantised activations, so both operands see the same permutation of k.  The 8
+// warps' partial sums meet once per row-block in double-buffered shared memory (warp order).
+// With few row-blocks, gridDim.y = SPLIT CTAs form a cluster that splits the k-tiles and
+// reduces over distributed shared memory in rank order.  Launched with programmatic stream
+// serialisation: the weight prefetch starts before the preceding kernel has finished, the
+// consumers wait for it (griddepcontrol.wait) before they touch the activations.
 // ------------------------------------------------------------------------------------
 __device__ __forceinline__ void mma_e4m3_16832(float d[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                uint32_t b0, uint32_t b1) {
@@ -165,7 +170,10 @@ __device__ __forceinline__ void fp8_st_cluster_rank0_f32(const float* local_ptr,
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(0));
     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }
+// Bounded wait: gives up after 2^20 polls (or once another waiter recorded a failure), records
+// code 7 in the status word and lets the kernel run to its end.
 __device__ __forceinline__ void f8v_wait(uint32_t bar, uint32_t parity, int* status) {
+#pragma unroll 1
     for (uint32_t i = 0; i < (1u << 20); ++i) {
         uint32_t ok;
         asm volatile(
@@ -182,150 +190,168 @@ __device__ __forceinline__ uint4 f8v_lds_v4(uint32_t addr) {
     return v;
 }
 
-#define F8V_WARPS 8
-#define F8V_STAGES 5
-#define F8V_STAGE_BYTES 2048
+#define F8V_CWARPS 8
+#define F8V_THREADS ((F8V_CWARPS + 1) * 32)
+#define F8V_STAGES 4
+#define F8V_BLOCK_BYTES 2048
+#define F8V_STAGE_BYTES (F8V_CWARPS * F8V_BLOCK_BYTES)
 #define F8V_MAX_SPLIT 8
 
 // One 2 KB block (16 rows x 128 k) from shared memory against the quantised activations.  Tokens
 // beyond M read a clamped (valid) row: a column of B only reaches the same, discarded, column of D.
 template <int MT>
-__device__ __forceinline__ void f8_block_compute(uint32_t stage, float acc[2][MT][4], const uint8_t* const xrow[MT],
-                                                 int koff_lo, int koff_hi, int g, int t) {
-    const uint32_t r0 = stage + g * 128;
+__device__ __forceinline__ void f8_block_compute(uint32_t blk, float acc[2][MT][4], const uint4 xlo[MT], const uint4 xhi[MT],
+                                                 int g, int t) {
+    const uint32_t r0 = blk + g * 128;
     const uint4 a_lo = f8v_lds_v4(r0 + ((t ^ g) << 4));
     const uint4 a_hi = f8v_lds_v4(r0 + (((t + 4) ^ g) << 4));
     const uint4 b_lo = f8v_lds_v4(r0 + 1024 + ((t ^ g) << 4));
     const uint4 b_hi = f8v_lds_v4(r0 + 1024 + (((t + 4) ^ g) << 4));
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
-        const uint4 xlo = ld_nc_v4(xrow[mt] + koff_lo);
-        const uint4 xhi = ld_nc_v4(xrow[mt] + koff_hi);
-        mma_e4m3_16832(acc[0][mt], a_lo.x, b_lo.x, a_lo.y, b_lo.y, xlo.x, xlo.y);
-        mma_e4m3_16832(acc[1][mt], a_lo.z, b_lo.z, a_lo.w, b_lo.w, xlo.z, xlo.w);
-        mma_e4m3_16832(acc[0][mt], a_hi.x, b_hi.x, a_hi.y, b_hi.y, xhi.x, xhi.y);
-        mma_e4m3_16832(acc[1][mt], a_hi.z, b_hi.z, a_hi.w, b_hi.w, xhi.z, xhi.w);
+        mma_e4m3_16832(acc[0][mt], a_lo.x, b_lo.x, a_lo.y, b_lo.y, xlo[mt].x, xlo[mt].y);
+        mma_e4m3_16832(acc[1][mt], a_lo.z, b_lo.z, a_lo.w, b_lo.w, xlo[mt].z, xlo[mt].w);
+        mma_e4m3_16832(acc[0][mt], a_hi.x, b_hi.x, a_hi.y, b_hi.y, xhi[mt].x, xhi[mt].y);
+        mma_e4m3_16832(acc[1][mt], a_hi.z, b_hi.z, a_hi.w, b_hi.w, xhi[mt].z, xhi[mt].w);
     }
 }
 
 template <int MT, int SPLIT_CLUSTER>
-__global__ void __launch_bounds__(F8V_WARPS * 32, 2)
+__global__ void __launch_bounds__(F8V_THREADS, (MT == 1 ? 3 : 2))
 fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_scale, const uint8_t* __restrict__ xq,
                 const float* __restrict__ a_scale, uint16_t* __restrict__ y, int M, int N, int K16, int KT, int rb_real,
                 int split, int* __restrict__ status) {
-    extern __shared__ __align__(128) uint8_t f8v_ring[];           // [F8V_WARPS][F8V_STAGES][2048]
-    __shared__ __align__(8) uint64_t bars[F8V_WARPS][F8V_STAGES];
-    __shared__ float red[2][F8V_WARPS][32][MT * 4];
+    extern __shared__ __align__(128) uint8_t f8v_ring[];           // [F8V_STAGES][8 blocks of 2 KB]
+    __shared__ __align__(8) uint64_t full_bar[F8V_STAGES];
+    __shared__ __align__(8) uint64_t empty_bar[F8V_STAGES];
+    __shared__ float red[2][F8V_CWARPS][32][MT * 4];
     __shared__ float cl_part[SPLIT_CLUSTER ? F8V_MAX_SPLIT : 1][16][MT * 8];
 
-    const int sp = SPLIT_CLUSTER ? int(fp8_cluster_ctarank()) : 0;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-
-    const int per = (KT + split - 1) / split;
-    const int kt_lo = sp * per;
-    const int kt_hi = min(KT, kt_lo + per);
-    const int kt_first = kt_lo + warp;
-    const bool has_work = kt_first < kt_hi;
-
-    if (lane == 0) {
+    if (threadIdx.x == 0) {
 #pragma unroll
-        for (int d = 0; d < F8V_STAGES; ++d)
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(f8v_smem_u32(&bars[warp][d])), "r"(1) : "memory");
+        for (int d = 0; d < F8V_STAGES; ++d) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(f8v_smem_u32(&full_bar[d])), "r"(1) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(f8v_smem_u32(&empty_bar[d])), "r"(F8V_CWARPS) : "memory");
+        }
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     __syncthreads();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    const uint32_t ring_base = f8v_smem_u32(f8v_ring) + (uint32_t)warp * (F8V_STAGES * F8V_STAGE_BYTES);
-    const uint32_t bar_base = f8v_smem_u32(&bars[warp][0]);
+    const int sp = SPLIT_CLUSTER ? int(fp8_cluster_ctarank()) : 0;
+    const int per = (KT + split - 1) / split;
+    const int kt_lo = sp * per;
+    const int kt_hi = min(KT, kt_lo + per);
+    const int nstage = (max(kt_hi - kt_lo, 0) + F8V_CWARPS - 1) / F8V_CWARPS;
+    const uint32_t ring_base = f8v_smem_u32(f8v_ring);
+    const uint32_t full_base = f8v_smem_u32(&full_bar[0]);
+    const uint32_t empty_base = f8v_smem_u32(&empty_bar[0]);
 
-    // row-block rb = rows [16rb, 16rb+16) = swizzle groups 2j, 2j+1 (j = rb % 8) of tile row rb / 8
-    auto block_ptr = [&](int rb, int kt) {
-        return wpack + ((size_t)(rb >> 3) * KT + kt) * FP8_TILE_BYTES + (size_t)(rb & 7) * F8V_STAGE_BYTES;
-    };
-    int prb = blockIdx.x, pkt = kt_first, pslot = 0;
-    auto issue = [&]() {
-        if (has_work && prb < rb_real) {
-            const uint32_t bar = bar_base + 8u * pslot;
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(F8V_STAGE_BYTES) : "memory");
-            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                         ::"r"(ring_base + pslot * F8V_STAGE_BYTES), "l"(block_ptr(prb, pkt)), "r"(F8V_STAGE_BYTES), "r"(bar) : "memory");
-            pkt += F8V_WARPS;
-            if (pkt >= kt_hi) { pkt = kt_first; prb += gridDim.x; }
+    if (warp == F8V_CWARPS) {
+        // ---- producer: weights are load-time constants, so it never waits for the previous kernel
+        if (lane == 0) {
+            uint32_t n_it = 0;
+            for (int rb = blockIdx.x; rb < rb_real; rb += gridDim.x) {
+                // row-block rb = swizzle groups 2j, 2j+1 (j = rb % 8) of tile row rb / 8
+                const uint8_t* src = wpack + ((size_t)(rb >> 3) * KT + kt_lo) * FP8_TILE_BYTES + (size_t)(rb & 7) * F8V_BLOCK_BYTES;
+                for (int j = 0; j < nstage; ++j, ++n_it) {
+                    const uint32_t slot = n_it & (F8V_STAGES - 1);
+                    f8v_wait(empty_base + 8u * slot, ((n_it / F8V_STAGES) & 1u) ^ 1u, status);
+                    const int nblk = min(F8V_CWARPS, kt_hi - kt_lo - j * F8V_CWARPS);
+                    const uint32_t bar = full_base + 8u * slot;
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(nblk * F8V_BLOCK_BYTES) : "memory");
+                    for (int b = 0; b < nblk; ++b)
+                        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                     ::"r"(ring_base + slot * F8V_STAGE_BYTES + b * F8V_BLOCK_BYTES),
+                                       "l"(src + (size_t)(j * F8V_CWARPS + b) * FP8_TILE_BYTES), "r"(F8V_BLOCK_BYTES), "r"(bar) : "memory");
+                }
+            }
         }
-        pslot = (pslot + 1 == F8V_STAGES) ? 0 : pslot + 1;
-    };
-    if (lane == 0) {
+        __syncwarp();
+    } else {
+        asm volatile("griddepcontrol.wait;" ::: "memory");        // the activations are settled
+        const uint8_t* xrow[MT];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) xrow[mt] = xq + (size_t)min(mt * 8 + g, M - 1) * K16;
+        uint32_t n_it = 0;
+        int it = 0;
+        for (int rb = blockIdx.x; rb < rb_real; rb += gridDim.x, ++it) {
+            float acc[2][MT][4];
+#pragma unroll
+            for (int a = 0; a < 2; ++a)
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) acc[a][mt][i] = 0.f;
+
 #pragma unroll 1
-        for (int d = 0; d < F8V_STAGES; ++d) issue();
-    }
-
-    const uint8_t* xrow[MT];
+            for (int j = 0; j < nstage; ++j, ++n_it) {
+                const int kt = kt_lo + j * F8V_CWARPS + warp;
+                const bool active = kt < kt_hi;                   // warp-uniform
+                const uint32_t slot = n_it & (F8V_STAGES - 1);
+                // k beyond the row (K16 not a multiple of 128, or an idle warp) meets zero weights
+                // or is not used: read offset 0 instead
+                int klo = kt * 128 + t * 16, khi = klo + 64;
+                if (klo >= K16) klo = 0;
+                if (khi >= K16) khi = 0;
+                uint4 xlo[MT], xhi[MT];
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) xrow[mt] = xq + (size_t)min(mt * 8 + g, M - 1) * K16;
-    int slot = 0;
-    uint32_t phases = 0;
-    int it = 0;
+                for (int mt = 0; mt < MT; ++mt) {
+                    xlo[mt] = ld_nc_v4(xrow[mt] + klo);
+                    xhi[mt] = ld_nc_v4(xrow[mt] + khi);
+                }
+                f8v_wait(full_base + 8u * slot, (n_it / F8V_STAGES) & 1u, status);
+                if (active) f8_block_compute<MT>(ring_base + slot * F8V_STAGE_BYTES + warp * F8V_BLOCK_BYTES, acc, xlo, xhi, g, t);
+                __syncwarp();
+                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_base + 8u * slot) : "memory");
+            }
 
-    for (int rb = blockIdx.x; rb < rb_real; rb += gridDim.x, ++it) {
-        float acc[2][MT][4];
-#pragma unroll
-        for (int a = 0; a < 2; ++a)
+            const int buf = it & 1;
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) acc[a][mt][i] = 0.f;
+                for (int i = 0; i < 4; ++i) red[buf][warp][lane][mt * 4 + i] = acc[0][mt][i] + acc[1][mt][i];
+            asm volatile("bar.sync 1, 256;" ::: "memory");        // the 8 consumer warps
 
-#pragma unroll 1
-        for (int kt = kt_first; kt < kt_hi; kt += F8V_WARPS) {
-            f8v_wait(bar_base + 8u * slot, (phases >> slot) & 1u, status);
-            // k beyond the row (K16 not a multiple of 128) meets zero weights: read offset 0 instead
-            int klo = kt * 128 + t * 16, khi = klo + 64;
-            if (klo >= K16) klo = 0;
-            if (khi >= K16) khi = 0;
-            f8_block_compute<MT>(ring_base + slot * F8V_STAGE_BYTES, acc, xrow, klo, khi, g, t);
-            phases ^= 1u << slot;
-            __syncwarp();
-            if (lane == 0) issue();
-            slot = (slot + 1 == F8V_STAGES) ? 0 : slot + 1;
+            constexpr int SLOTS = 32 * MT * 4;
+            const int e = threadIdx.x;
+            const int ln = e / (MT * 4), idx = e % (MT * 4);
+            const int row = (ln >> 2) + (((idx & 3) >> 1) ? 8 : 0);
+            const int tok = (idx >> 2) * 8 + (ln & 3) * 2 + (idx & 1);
+            const int n = rb * 16 + row;
+            if (e < SLOTS && tok < M) {
+                float total = 0.f;
+#pragma unroll
+                for (int wdx = 0; wdx < F8V_CWARPS; ++wdx) total += red[buf][wdx][ln][idx];
+                if (SPLIT_CLUSTER) {
+                    fp8_st_cluster_rank0_f32(&cl_part[sp][row][tok], total);
+                } else if (n < N) {
+                    // (raw * a_scale[m]) * w_scale[n], in that order (ktir_matmul_fp8.rs:676-712)
+                    const float o = __fmul_rn(__fmul_rn(total, a_scale[tok]), w_scale[n]);
+                    const __nv_bfloat16 v = __float2bfloat16_rn(o);
+                    y[(size_t)tok * N + n] = *reinterpret_cast<const uint16_t*>(&v);
+                }
+            }
         }
+    }
 
-        const int buf = it & 1;
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) red[buf][warp][lane][mt * 4 + i] = acc[0][mt][i] + acc[1][mt][i];
-        __syncthreads();
-
+    if (SPLIT_CLUSTER) {
+        // one row-block per CTA in cluster mode (gridDim.x == rb_real): exchange once, rank order
+        fp8_cluster_sync_all();
         constexpr int SLOTS = 32 * MT * 4;
         const int e = threadIdx.x;
         const int ln = e / (MT * 4), idx = e % (MT * 4);
-        const int mt_ = idx >> 2, i_ = idx & 3;
-        const int row = (ln >> 2) + ((i_ >> 1) ? 8 : 0);
-        const int tok = mt_ * 8 + (ln & 3) * 2 + (i_ & 1);
-        const int n = rb * 16 + row;
-        if (e < SLOTS && tok < M) {
-            float total = 0.f;
-#pragma unroll
-            for (int wdx = 0; wdx < F8V_WARPS; ++wdx) total += red[buf][wdx][ln][idx];
-            if (SPLIT_CLUSTER) {
-                fp8_st_cluster_rank0_f32(&cl_part[sp][row][tok], total);
-            } else if (n < N) {
-                // (raw * a_scale[m]) * w_scale[n], in that order (ktir_matmul_fp8.rs:676-712)
-                const float o = __fmul_rn(__fmul_rn(total, a_scale[tok]), w_scale[n]);
-                const __nv_bfloat16 v = __float2bfloat16_rn(o);
-                y[(size_t)tok * N + n] = *reinterpret_cast<const uint16_t*>(&v);
-            }
-        }
-        if (SPLIT_CLUSTER) {
-            fp8_cluster_sync_all();
-            if (sp == 0 && e < SLOTS && tok < M && n < N) {
-                float s = 0.f;
-                for (int r = 0; r < split; ++r) s += cl_part[r][row][tok];
-                const float o = __fmul_rn(__fmul_rn(s, a_scale[tok]), w_scale[n]);
-                const __nv_bfloat16 v = __float2bfloat16_rn(o);
-                y[(size_t)tok * N + n] = *reinterpret_cast<const uint16_t*>(&v);
-            }
+        const int row = (ln >> 2) + (((idx & 3) >> 1) ? 8 : 0);
+        const int tok = (idx >> 2) * 8 + (ln & 3) * 2 + (idx & 1);
+        const int n = blockIdx.x * 16 + row;
+        if (sp == 0 && e < SLOTS && tok < M && n < N) {
+            float s = 0.f;
+            for (int r = 0; r < split; ++r) s += cl_part[r][row][tok];
+            const float o = __fmul_rn(__fmul_rn(s, a_scale[tok]), w_scale[n]);
+            const __nv_bfloat16 v = __float2bfloat16_rn(o);
+            y[(size_t)tok * N + n] = *reinterpret_cast<const uint16_t*>(&v);
         }
     }
 }
@@ -363,7 +389,12 @@ extern "C" int32_t scr_fp8_repack(scr_ctx* ctx, const uint8_t* w, const float* w
     const int threads = 256;
     const int blocks = (int)std::min<long long>((chunks + threads - 1) / threads, (long long)ctx->sm_count * 32);
     fp8_repack_kernel<<<blocks, threads, 0, (cudaStream_t)stream>>>(w, w_scale, N, K, g.NT, g.KT, (uint8_t*)dst);
-    return scr_check_launch(ctx, "fp8_repack");
+    int32_t st2 = scr_check_launch(ctx, "fp8_repack");
+    if (st2) return st2;
+    // a plain launch after the repack: kernels that prefetch weights ahead of their stream
+    // dependency (programmatic dependent launch) must never follow the repack directly
+    fp8_repack_fence_kernel<<<1, 32, 0, (cudaStream_t)stream>>>();
+    return scr_check_launch(ctx, "fp8_repack_fence");
 }
 
 extern "C" int32_t scr_fp8_act_size(int32_t M, int32_t K, size_t* bytes) {
@@ -407,12 +438,12 @@ extern "C" int32_t scr_e4m3_encode(scr_ctx* ctx, const float* v, int64_t count, 
 
 static void fp8_gemv_shape(int rb_real, int KT, int sms, int* grid_x, int* split) {
     if (rb_real >= sms) {
-        *grid_x = std::min(rb_real, 2 * sms);
+        *grid_x = std::min(rb_real, 3 * sms);
         *split = 1;
         return;
     }
     int s = 1;
-    while (s * 2 <= F8V_MAX_SPLIT && rb_real * s * 2 <= 2 * sms && KT / (s * 2) >= F8V_WARPS / 2) s *= 2;
+    while (s * 2 <= F8V_MAX_SPLIT && rb_real * s * 2 <= 2 * sms && KT / (s * 2) >= F8V_CWARPS / 2) s *= 2;
     *grid_x = rb_real;
     *split = s;
 }
@@ -426,32 +457,32 @@ static int32_t fp8_gemv_launch(scr_ctx* ctx, const uint8_t* wpack, const uint8_t
     const int rb_real = scr_ceil_div(N, 16);
     int grid_x = 1, split = 1;
     fp8_gemv_shape(rb_real, g.KT, ctx->sm_count, &grid_x, &split);
-    constexpr int kRingBytes = F8V_WARPS * F8V_STAGES * F8V_STAGE_BYTES;
-    if (split == 1) {
-        cudaError_t e0 = cudaFuncSetAttribute(fp8_gemv_kernel<MT, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes);
-        if (e0 != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "fp8_gemv smem attribute: %s", cudaGetErrorString(e0));
-        fp8_gemv_kernel<MT, 0><<<dim3(grid_x, 1), F8V_WARPS * 32, kRingBytes, stream>>>(wpack, w_scale, xq, a_scale, y, M, N, K16,
-                                                                                       g.KT, rb_real, 1, ctx->dev_status);
-        return scr_check_launch(ctx, "fp8_gemv");
-    }
-    cudaError_t e1 = cudaFuncSetAttribute(fp8_gemv_kernel<MT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes);
-    if (e1 != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "fp8_gemv smem attribute: %s", cudaGetErrorString(e1));
+    constexpr int kRingBytes = F8V_STAGES * F8V_STAGE_BYTES;
+    auto kernel = (split == 1) ? fp8_gemv_kernel<MT, 0> : fp8_gemv_kernel<MT, 1>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes);
+    if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "fp8_gemv smem attribute: %s", cudaGetErrorString(e));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid_x, split, 1);
-    cfg.blockDim = dim3(F8V_WARPS * 32, 1, 1);
+    cfg.blockDim = dim3(F8V_THREADS, 1, 1);
     cfg.dynamicSmemBytes = kRingBytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = split;
-    attr[0].val.clusterDim.z = 1;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+    if (split > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = 1;
+        attr[na].val.clusterDim.y = split;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, fp8_gemv_kernel<MT, 1>, wpack, w_scale, xq, a_scale, y, M, N, K16, g.KT, rb_real,
-                                       split, ctx->dev_status);
-    if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "fp8_gemv cluster launch: %s", cudaGetErrorString(e));
-    return scr_check_launch(ctx, "fp8_gemv(cluster)");
+    cfg.numAttrs = na;
+    e = cudaLaunchKernelEx(&cfg, kernel, wpack, w_scale, xq, a_scale, y, M, N, K16, g.KT, rb_real, split, ctx->dev_status);
+    if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "fp8_gemv launch: %s", cudaGetErrorString(e));
+    return scr_check_launch(ctx, "fp8_gemv");
 }
 
 size_t fp8_workspace_bytes(int M, int N, int K) {
