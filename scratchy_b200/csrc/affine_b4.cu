@@ -459,15 +459,23 @@ extern "C" int32_t scr_affine_b4_dequant_dump(scr_ctx* ctx, const void* packed, 
 // is split; with few row-blocks each CTA takes one row-block and a cluster of `split` CTAs
 // shares its k-chunks so that about one CTA per SM is busy.
 static void affine_gemv_shape(int rb_real, int KC, int sms, int* grid_x, int* split) {
-    if (rb_real >= sms) {
-        *grid_x = std::min(rb_real, 3 * sms);
+    // Enough row-blocks: persistent CTAs (3 per SM) walk them, nothing is split.
+    const int slots = 3 * sms;
+    if (rb_real >= slots) {
+        *grid_x = slots;
         *split = 1;
         return;
     }
-    int s = 1;
-    while (s * 2 <= GEMV_MAX_SPLIT && rb_real * s * 2 <= 2 * sms && KC / (s * 2) >= GEMV_CWARPS / 2) s *= 2;
+    // Fewer: one row-block per CTA and a cluster of `s` CTAs shares its k extent, chosen so that
+    // everything is resident at once and the longest CTA runs the fewest ring stages.
+    int best = 1, best_stages = (KC + GEMV_CWARPS - 1) / GEMV_CWARPS;
+    for (int s = 2; s <= GEMV_MAX_SPLIT && rb_real * s <= slots; ++s) {
+        const int per = (KC + s - 1) / s;
+        const int stages = (per + GEMV_CWARPS - 1) / GEMV_CWARPS;
+        if (stages < best_stages) { best_stages = stages; best = s; }
+    }
     *grid_x = rb_real;
-    *split = s;
+    *split = best;
 }
 
 template <int MT>

@@ -436,16 +436,24 @@ extern "C" int32_t scr_e4m3_encode(scr_ctx* ctx, const float* v, int64_t count, 
     return scr_check_launch(ctx, "e4m3_encode");
 }
 
-static void fp8_gemv_shape(int rb_real, int KT, int sms, int* grid_x, int* split) {
-    if (rb_real >= sms) {
-        *grid_x = std::min(rb_real, 3 * sms);
+static void fp8_gemv_shape(int rb_real, int KC, int sms, int* grid_x, int* split) {
+    // Enough row-blocks: persistent CTAs (3 per SM) walk them, nothing is split.
+    const int slots = 3 * sms;
+    if (rb_real >= slots) {
+        *grid_x = slots;
         *split = 1;
         return;
     }
-    int s = 1;
-    while (s * 2 <= F8V_MAX_SPLIT && rb_real * s * 2 <= 2 * sms && KT / (s * 2) >= F8V_CWARPS / 2) s *= 2;
+    // Fewer: one row-block per CTA and a cluster of `s` CTAs shares its k extent, chosen so that
+    // everything is resident at once and the longest CTA runs the fewest ring stages.
+    int best = 1, best_stages = (KC + F8V_CWARPS - 1) / F8V_CWARPS;
+    for (int s = 2; s <= F8V_MAX_SPLIT && rb_real * s <= slots; ++s) {
+        const int per = (KC + s - 1) / s;
+        const int stages = (per + F8V_CWARPS - 1) / F8V_CWARPS;
+        if (stages < best_stages) { best_stages = stages; best = s; }
+    }
     *grid_x = rb_real;
-    *split = s;
+    *split = best;
 }
 
 template <int MT>
