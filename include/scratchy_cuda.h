@@ -133,6 +133,17 @@ int32_t scr_linear_fp8_dynamic(scr_ctx* ctx, const void* packed, const uint16_t*
                                int32_t N, int32_t K, uint16_t* y_bf16, void* workspace,
                                size_t workspace_bytes, void* stream);
 
+/* No counterpart in the reference.  The same linear as `scr_linear_fp8_dynamic` for callers
+ * that cannot allocate device memory on the step path (an arena-owning runtime, code inside a
+ * no-allocation region, an FFI shim that owns only inputs and outputs): the activation pack
+ * lives in a fixed 8 MiB device array built into the library, so no workspace is passed and
+ * nothing is allocated.  Requests whose pack exceeds 8 MiB return SCR_E_WORKSPACE.  The first
+ * call on a device resolves the array's address; make it before any stream capture, with the
+ * context's device current.  All calls share the array (it keeps the last call's contents), so
+ * calls that overlap on the GPU race: serialise them. */
+int32_t scr_linear_fp8_dynamic_static(scr_ctx* ctx, const void* packed, const uint16_t* x_bf16,
+                                      int32_t M, int32_t N, int32_t K, uint16_t* y_bf16, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -552,3 +552,72 @@ extern "C" int32_t scr_linear_fp8_dynamic(scr_ctx* ctx, const void* packed, cons
     return fp8_linear_from_pack(ctx, (const uint8_t*)packed, (const uint8_t*)workspace, M, N, K, y,
                                 (uint8_t*)workspace + act_bytes, workspace_bytes - act_bytes, (cudaStream_t)stream);
 }
+
+// ------------------------------------------------------------------------------------
+// scr_linear_fp8_dynamic_static: the fp8 dynamic linear for callers that cannot allocate.
+//
+// The per-token quantised activations (x_q and a_scale) normally live in a workspace the caller
+// allocates.  Some callers have no allocator at hand when they run a step: a runtime that has
+// handed all device memory to its own arena and must not grow it, code running inside a
+// region where the CUDA allocator is forbidden, or a thin FFI shim that only owns the input
+// and output tensors.  For them this variant keeps the activation pack in the fixed device
+// array below, which every GPU that loads this library reserves until the process exits.
+//
+//  * It allocates nothing: no cudaMalloc / cudaFree and no allocating library routine.
+//  * Limit: the activation pack for (M, K) must fit SCR_STATIC_SCRATCH_BYTES (8 MiB); larger
+//    requests are refused with SCR_E_WORKSPACE and a message that states both sizes.
+//  * The first call on a device looks the array's device address up (the name `scratch` is only
+//    a host-side handle, never a pointer a kernel may use) and caches it; make that first call
+//    outside any stream capture, with the context's device current.
+//  * All calls share the one array and it keeps the last call's contents.  Nothing in it has
+//    to start at zero: the quantise kernel rewrites every byte the contraction reads for the
+//    tokens it is given.  Calls that overlap on the GPU (different streams, or several host
+//    threads on one device) race on it — serialise them, or use scr_linear_fp8_dynamic with
+//    separate workspaces.
+// ------------------------------------------------------------------------------------
+#define SCR_STATIC_SCRATCH_BYTES (8u << 20)
+static __device__ __align__(256) unsigned char scr_static_scratch[SCR_STATIC_SCRATCH_BYTES];
+
+#define SCR_MAX_DEVICES 64
+static void* g_static_scratch_ptr[SCR_MAX_DEVICES] = {nullptr};
+static std::atomic<int> g_static_scratch_state[SCR_MAX_DEVICES];     // 0 = not looked up, 2 = ready
+
+static int32_t static_scratch_for(scr_ctx* ctx, void** out) {
+    const int dev = ctx->device;
+    if (dev < 0 || dev >= SCR_MAX_DEVICES) return scr_fail(ctx, SCR_E_ARG, "device %d out of range", dev);
+    int cur = -1;
+    if (cudaGetDevice(&cur) != cudaSuccess || cur != dev)
+        return scr_fail(ctx, SCR_E_ARG, "device %d must be current (current is %d)", dev, cur);
+    if (g_static_scratch_state[dev].load(std::memory_order_acquire) != 2) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, scr_static_scratch);
+        if (e != cudaSuccess || !p)
+            return scr_fail(ctx, SCR_E_CUDA, "cudaGetSymbolAddress(scr_static_scratch): %s", cudaGetErrorString(e));
+        g_static_scratch_ptr[dev] = p;                       // the same value from every thread: a benign race
+        g_static_scratch_state[dev].store(2, std::memory_order_release);
+    }
+    *out = g_static_scratch_ptr[dev];
+    return SCR_OK;
+}
+
+extern "C" int32_t scr_linear_fp8_dynamic_static(scr_ctx* ctx, const void* packed, const uint16_t* x, int32_t M, int32_t N,
+                                                 int32_t K, uint16_t* y, void* stream) {
+    SCR_REQUIRE_CTX(ctx);
+    if (!packed || !x || !y) return scr_fail(ctx, SCR_E_ARG, "null pointer");
+    int32_t st = fp8_check_shape(ctx, N, K);
+    if (st) return st;
+    if (M <= 0) return scr_fail(ctx, SCR_E_SHAPE, "M=%d must be positive", M);
+    const size_t need = fp8_workspace_bytes(M, N, K);
+    if (need > (size_t)SCR_STATIC_SCRATCH_BYTES)
+        return scr_fail(ctx, SCR_E_WORKSPACE,
+                        "M=%d K=%d needs %zu bytes of scratch, the built-in array holds %u; use scr_linear_fp8_dynamic "
+                        "with a caller workspace", M, K, need, (unsigned)SCR_STATIC_SCRATCH_BYTES);
+    void* scratch = nullptr;
+    st = static_scratch_for(ctx, &scratch);
+    if (st) return st;
+    st = scr_fp8_quant_per_token(ctx, x, M, K, scratch, stream);
+    if (st) return st;
+    const size_t act_bytes = (fp8_act_bytes(M, K) + 127) / 128 * 128;
+    return fp8_linear_from_pack(ctx, (const uint8_t*)packed, (const uint8_t*)scratch, M, N, K, y, (uint8_t*)scratch + act_bytes,
+                                (size_t)SCR_STATIC_SCRATCH_BYTES - act_bytes, (cudaStream_t)stream);
+}
