@@ -299,6 +299,12 @@ def run_gpu(args):
     extra = {}
     if args.sweep and rank == 0:
         extra["sweep"] = run_sweep(device, ctx)
+    if world > 1 or args.sweep:
+        del layers, graph, graph_e2e
+        torch.cuda.empty_cache()
+        tp_res = run_tp(device, world, rank)
+        if rank == 0:
+            extra["tp"] = tp_res
 
     if rank == 0:
         cpu_v, cpu_dt, cores = time_cpu_layer(max(1, int(12.0 / max(time_cpu_layer(1)[1], 1e-3))))
@@ -394,6 +400,92 @@ def run_sweep(device, ctx):
                         "frac_hbm": fp8_alg_bytes(M, N, K) / dt / 1e9 / peaks["hbm_gbs"],
                         "note": "per-token quantise + contraction (two launches)"})
         del lins
+    return out
+
+
+def run_tp(device, world, rank):
+    """BASELINE config 4: Llama-3-70B-shaped fp8 per-channel linears, tensor parallel over `world`
+    GPUs: column-parallel qkv and gate/up, row-parallel o and down, each followed by an NCCL
+    all-reduce of the f32 partials [M, 8192] and one rounding to bf16.  One "layer" = qkv, o,
+    gate_up, down (attention and the activation function are outside the path; the row-parallel
+    inputs are slices of the preceding outputs).  Weights are random e4m3 bytes of the per-rank
+    shard shapes; three layer copies rotate so that small-M steps read HBM, not L2."""
+    import torch
+    import torch.distributed as dist
+    from scratchy_b200 import Fp8Linear, tp as tpmod
+    tpw = tpmod.TpWorld(world, rank)
+    comm = tpmod.TpCommunicator(tpw)
+    H, QKV, FF = 8192, 10240, 28672
+    copies = 3
+
+    def lin(n, k, seed):
+        g = torch.Generator(device=device)
+        g.manual_seed(seed)
+        w = torch.randint(0, 0x7E, (n, k), dtype=torch.uint8, device=device, generator=g)
+        return Fp8Linear.from_tensors(w, torch.rand(n, device=device, generator=g) * 1e-3 + 1e-4)
+
+    layers = []
+    for c in range(copies):
+        layers.append({"qkv": lin(QKV // world, H, 10 * c + 1), "o": lin(H, H // world, 10 * c + 2),
+                       "gate_up": lin(2 * FF // world, H, 10 * c + 3), "down": lin(H, FF // world, 10 * c + 4)})
+    out = []
+    side = torch.cuda.Stream(device)
+    for M in [1, 32, 256, 8192]:
+        x = torch.randn((M, H), device=device).to(torch.bfloat16)
+        ws = torch.empty(max(l.workspace_bytes(M) for l in layers[0].values()), dtype=torch.uint8, device=device)
+        bufs = {"qkv": torch.empty((M, QKV // world), dtype=torch.bfloat16, device=device),
+                "gu": torch.empty((M, 2 * FF // world), dtype=torch.bfloat16, device=device),
+                "po": torch.empty((M, H), dtype=torch.float32, device=device),
+                "pd": torch.empty((M, H), dtype=torch.float32, device=device)}
+
+        def layer_step(L):
+            L["qkv"].forward(x, out=bufs["qkv"], workspace=ws)
+            a = bufs["qkv"][:, :H // world].contiguous()
+            L["o"].forward_partial(a, out=bufs["po"], workspace=ws)
+            comm.all_reduce(bufs["po"])
+            h = tpmod.partial_to_bf16(bufs["po"])
+            L["gate_up"].forward(h, out=bufs["gu"], workspace=ws)
+            d = bufs["gu"][:, :FF // world].contiguous()
+            L["down"].forward_partial(d, out=bufs["pd"], workspace=ws)
+            comm.all_reduce(bufs["pd"])
+            return tpmod.partial_to_bf16(bufs["pd"])
+
+        def step():
+            for L in layers:
+                layer_step(L)
+
+        step()
+        torch.cuda.synchronize(device)
+        mode = "graph"
+        try:
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=side):
+                step()
+            run = gr.replay
+        except Exception:
+            mode = "eager"
+            run = step
+        reps = 20 if M <= 256 else 3
+        for _ in range(3):
+            run()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            run()
+        b.record()
+        torch.cuda.synchronize(device)
+        t = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us_layer = float(t[0]) * 1e3 / (reps * copies)
+        flops = 2.0 * M * H * (QKV + H + 2 * FF + FF)
+        out.append({"M": M, "tp": world, "us_per_layer": us_layer, "layers_per_s": 1e6 / us_layer,
+                    "tok_per_s_per_layer": M * 1e6 / us_layer, "TFLOPs_all_gpus": flops / us_layer / 1e6,
+                    "weight_GBps_per_gpu": (H * (QKV + H + 3 * FF) / world) / us_layer / 1e3, "launch": mode,
+                    "allreduce": "f32 [M,8192] x2 per layer (NCCL)"})
     return out
 
 

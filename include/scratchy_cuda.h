@@ -133,6 +133,21 @@ int32_t scr_linear_fp8_dynamic(scr_ctx* ctx, const void* packed, const uint16_t*
                                int32_t N, int32_t K, uint16_t* y_bf16, void* workspace,
                                size_t workspace_bytes, void* stream);
 
+/* ---- tensor parallel: row-parallel partials --------------------------------
+ * A row-parallel linear (o, down) holds a K-slice of the weight and yields a `Partial`
+ * (crates/compiler/subtile/src/tensor_parallel.rs:508-625): these variants write the UNROUNDED
+ * f32 sums [M,N] instead of bf16, the caller all-reduces them over the ranks (the reference's
+ * meaning: a sum in rank order, tensor_parallel.rs:1350-1362) and rounds once with
+ * `scr_partial_to_bf16`.  Same arguments otherwise as `scr_linear_affine_b4` / `scr_linear_fp8`. */
+int32_t scr_linear_affine_b4_partial(scr_ctx* ctx, const void* packed, const uint16_t* x_bf16,
+                                     int32_t M, int32_t N, int32_t K, int32_t group, float* y_f32,
+                                     void* workspace, size_t workspace_bytes, void* stream);
+int32_t scr_linear_fp8_partial(scr_ctx* ctx, const void* packed, const void* act, int32_t M,
+                               int32_t N, int32_t K, float* y_f32, void* workspace,
+                               size_t workspace_bytes, void* stream);
+int32_t scr_partial_to_bf16(scr_ctx* ctx, const float* in, int64_t count, uint16_t* out_bf16,
+                            void* stream);
+
 /* No counterpart in the reference.  The same linear as `scr_linear_fp8_dynamic` for callers
  * that cannot allocate device memory on the step path (an arena-owning runtime, code inside a
  * no-allocation region, an FFI shim that owns only inputs and outputs): the activation pack

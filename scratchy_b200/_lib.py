@@ -50,6 +50,9 @@ SIGNATURES = {
     "scr_e4m3_encode": (_i32, [_vp, _vp, _i64, _vp, _vp]),
     "scr_linear_fp8": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _sz, _vp]),
     "scr_linear_fp8_dynamic": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _sz, _vp]),
+    "scr_linear_affine_b4_partial": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _sz, _vp]),
+    "scr_linear_fp8_partial": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _sz, _vp]),
+    "scr_partial_to_bf16": (_i32, [_vp, _vp, _i64, _vp, _vp]),
     "scr_linear_fp8_dynamic_static": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp]),
 }
 

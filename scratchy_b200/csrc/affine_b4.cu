@@ -245,7 +245,7 @@ __device__ __forceinline__ void gemv_block_compute(uint32_t blk, float acc[2][MT
 template <int MT, int SPLIT_CLUSTER, bool CHECK>
 __device__ __forceinline__ void gemv_consumer(const uint16_t* __restrict__ x, uint16_t* __restrict__ y, int M, int N,
                                               int K, int kc_lo, int kc_hi, int nstage, int rb_real, int split, int sp,
-                                              int* __restrict__ status, uint32_t ring_base, uint32_t full_base,
+                                              int out_f32, int* __restrict__ status, uint32_t ring_base, uint32_t full_base,
                                               uint32_t empty_base, float (*red)[GEMV_CWARPS][32][MT * 4],
                                               float (*cl_part)[16][MT * 8]) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -309,8 +309,12 @@ __device__ __forceinline__ void gemv_consumer(const uint16_t* __restrict__ x, ui
             if (SPLIT_CLUSTER) {
                 gemv_st_cluster_rank0_f32(&cl_part[sp][row][tok], total);
             } else if (n < N) {
-                const __nv_bfloat16 v = __float2bfloat16_rn(total);
-                y[(size_t)tok * N + n] = *reinterpret_cast<const uint16_t*>(&v);
+                if (out_f32) {
+                    reinterpret_cast<float*>(y)[(size_t)tok * N + n] = total;
+                } else {
+                    const __nv_bfloat16 v = __float2bfloat16_rn(total);
+                    y[(size_t)tok * N + n] = *reinterpret_cast<const uint16_t*>(&v);
+                }
             }
         }
     }
@@ -319,7 +323,8 @@ __device__ __forceinline__ void gemv_consumer(const uint16_t* __restrict__ x, ui
 template <int MT, int SPLIT_CLUSTER>
 __global__ void __launch_bounds__(GEMV_THREADS, (MT == 1 ? 3 : 2))
 affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __restrict__ x, uint16_t* __restrict__ y,
-                      int M, int N, int K, int RB, int KC, int rb_real, int split, int* __restrict__ status) {
+                      int M, int N, int K, int RB, int KC, int rb_real, int split, int out_f32,
+                      int* __restrict__ status) {
     extern __shared__ __align__(128) uint8_t gemv_ring[];          // [GEMV_STAGES][8 blocks]
     __shared__ __align__(8) uint64_t full_bar[GEMV_STAGES];
     __shared__ __align__(8) uint64_t empty_bar[GEMV_STAGES];
@@ -373,10 +378,10 @@ affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __rest
         // one word per matrix says whether any group needs the exact (two-step rounding) path
         const bool check = *reinterpret_cast<const unsigned int*>(packed + (size_t)RB * KC * AFF_BLOCK_BYTES) != 0;
         if (check)
-            gemv_consumer<MT, SPLIT_CLUSTER, true>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, status, ring_base,
+            gemv_consumer<MT, SPLIT_CLUSTER, true>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, out_f32, status, ring_base,
                                                    full_base, empty_base, red, cl_part);
         else
-            gemv_consumer<MT, SPLIT_CLUSTER, false>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, status, ring_base,
+            gemv_consumer<MT, SPLIT_CLUSTER, false>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, out_f32, status, ring_base,
                                                     full_base, empty_base, red, cl_part);
     }
 
@@ -392,8 +397,12 @@ affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __rest
         if (sp == 0 && e < SLOTS && tok < M && n < N) {
             float s = 0.f;
             for (int r = 0; r < split; ++r) s += cl_part[r][row][tok];
-            const __nv_bfloat16 v = __float2bfloat16_rn(s);
-            y[(size_t)tok * N + n] = *reinterpret_cast<const uint16_t*>(&v);
+            if (out_f32) {
+                reinterpret_cast<float*>(y)[(size_t)tok * N + n] = s;
+            } else {
+                const __nv_bfloat16 v = __float2bfloat16_rn(s);
+                y[(size_t)tok * N + n] = *reinterpret_cast<const uint16_t*>(&v);
+            }
         }
     }
 }
@@ -508,7 +517,7 @@ static int32_t affine_gemv_launch(scr_ctx* ctx, const uint8_t* packed, const uin
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    e = cudaLaunchKernelEx(&cfg, kernel, packed, x, y, M, N, K, g.RB, g.KC, rb_real, split, ctx->dev_status);
+    e = cudaLaunchKernelEx(&cfg, kernel, packed, x, y, M, N, K, g.RB, g.KC, rb_real, split, ctx->out_f32, ctx->dev_status);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine_b4_gemv launch: %s", cudaGetErrorString(e));
     return scr_check_launch(ctx, "affine_b4_gemv");
 }

@@ -60,7 +60,8 @@ __device__ __forceinline__ uint32_t ld_shared_u32(uint32_t addr) {
 template <int BN>
 __global__ void __launch_bounds__(A4G_THREADS, 1)
 affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_t* __restrict__ packed,
-                         uint16_t* __restrict__ y, int M, int N, int RB, int KC, int MT, int* __restrict__ status) {
+                         uint16_t* __restrict__ y, int M, int N, int RB, int KC, int MT, int out_f32,
+                         int* __restrict__ status) {
     using S = A4GSmem<BN>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -241,7 +242,24 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
                 tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + c * 32), r);
                 tmem_ld_wait();
                 const int nc = n0 + c * 32;
-                if (m < M && nc < N) {
+                if (m < M && nc < N && out_f32) {
+                    // unrounded f32 partials (row-parallel layers: summed over ranks before the rounding)
+                    float* frow = reinterpret_cast<float*>(y) + (size_t)m * N + nc;
+                    const bool v4 = (N % 4) == 0 && nc + 32 <= N;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float4 v = make_float4(__uint_as_float(r[4 * j]) * out_scale, __uint_as_float(r[4 * j + 1]) * out_scale,
+                                                     __uint_as_float(r[4 * j + 2]) * out_scale, __uint_as_float(r[4 * j + 3]) * out_scale);
+                        if (v4) {
+                            reinterpret_cast<float4*>(frow)[j] = v;
+                        } else {
+                            if (nc + 4 * j + 0 < N) frow[4 * j + 0] = v.x;
+                            if (nc + 4 * j + 1 < N) frow[4 * j + 1] = v.y;
+                            if (nc + 4 * j + 2 < N) frow[4 * j + 2] = v.z;
+                            if (nc + 4 * j + 3 < N) frow[4 * j + 3] = v.w;
+                        }
+                    }
+                } else if (m < M && nc < N) {
                     uint32_t o[16];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
@@ -314,6 +332,6 @@ int32_t affine_b4_gemm_tc_launch(scr_ctx* ctx, const uint8_t* packed, const uint
                                          (int)A4GSmem<BN>::kTotal);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine gemm smem attribute: %s", cudaGetErrorString(e));
     affine_b4_gemm_tc_kernel<BN><<<grid, A4G_THREADS, A4GSmem<BN>::kTotal, stream>>>(map, packed, y, M, N, g.RB, g.KC, MT,
-                                                                                    ctx->dev_status);
+                                                                                    ctx->out_f32, ctx->dev_status);
     return scr_check_launch(ctx, "affine_b4_gemm_tc");
 }

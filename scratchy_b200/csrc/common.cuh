@@ -15,6 +15,7 @@ struct scr_ctx {
     int sm_count = 0;
     int cc_major = 0, cc_minor = 0;
     std::atomic<long long> launches{0};
+    int out_f32 = 0;                // set by the *_partial entry points for the duration of a call
     int* dev_status = nullptr;      // device word: first bounded wait that ran out (0 = none)
     char err[256] = {0};
 };

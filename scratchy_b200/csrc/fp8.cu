@@ -220,7 +220,7 @@ template <int MT, int SPLIT_CLUSTER>
 __global__ void __launch_bounds__(F8V_THREADS, (MT == 1 ? 3 : 2))
 fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_scale, const uint8_t* __restrict__ xq,
                 const float* __restrict__ a_scale, uint16_t* __restrict__ y, int M, int N, int K16, int KT, int rb_real,
-                int split, int* __restrict__ status) {
+                int split, int out_f32, int* __restrict__ status) {
     extern __shared__ __align__(128) uint8_t f8v_ring[];           // [F8V_STAGES][8 blocks of 2 KB]
     __shared__ __align__(8) uint64_t full_bar[F8V_STAGES];
     __shared__ __align__(8) uint64_t empty_bar[F8V_STAGES];
@@ -330,8 +330,12 @@ fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_s
                 } else if (n < N) {
                     // (raw * a_scale[m]) * w_scale[n], in that order (ktir_matmul_fp8.rs:676-712)
                     const float o = __fmul_rn(__fmul_rn(total, a_scale[tok]), w_scale[n]);
-                    const __nv_bfloat16 v = __float2bfloat16_rn(o);
-                    y[(size_t)tok * N + n] = *reinterpret_cast<const uint16_t*>(&v);
+                    if (out_f32) {
+                        reinterpret_cast<float*>(y)[(size_t)tok * N + n] = o;
+                    } else {
+                        const __nv_bfloat16 v = __float2bfloat16_rn(o);
+                        y[(size_t)tok * N + n] = *reinterpret_cast<const uint16_t*>(&v);
+                    }
                 }
             }
         }
@@ -350,8 +354,12 @@ fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_s
             float s = 0.f;
             for (int r = 0; r < split; ++r) s += cl_part[r][row][tok];
             const float o = __fmul_rn(__fmul_rn(s, a_scale[tok]), w_scale[n]);
-            const __nv_bfloat16 v = __float2bfloat16_rn(o);
-            y[(size_t)tok * N + n] = *reinterpret_cast<const uint16_t*>(&v);
+            if (out_f32) {
+                reinterpret_cast<float*>(y)[(size_t)tok * N + n] = o;
+            } else {
+                const __nv_bfloat16 v = __float2bfloat16_rn(o);
+                y[(size_t)tok * N + n] = *reinterpret_cast<const uint16_t*>(&v);
+            }
         }
     }
 }
@@ -488,7 +496,7 @@ static int32_t fp8_gemv_launch(scr_ctx* ctx, const uint8_t* wpack, const uint8_t
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    e = cudaLaunchKernelEx(&cfg, kernel, wpack, w_scale, xq, a_scale, y, M, N, K16, g.KT, rb_real, split, ctx->dev_status);
+    e = cudaLaunchKernelEx(&cfg, kernel, wpack, w_scale, xq, a_scale, y, M, N, K16, g.KT, rb_real, split, ctx->out_f32, ctx->dev_status);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "fp8_gemv launch: %s", cudaGetErrorString(e));
     return scr_check_launch(ctx, "fp8_gemv");
 }

@@ -33,7 +33,7 @@ template <int BN>
 __global__ void __launch_bounds__(F8G_THREADS, 1)
 fp8_gemm_tc_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_scale, const uint8_t* __restrict__ xq,
                    const float* __restrict__ a_scale, uint16_t* __restrict__ y, int M, int N, int KT, int NT, int MT,
-                   int M_pad, int* __restrict__ status) {
+                   int M_pad, int out_f32, int* __restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -134,7 +134,28 @@ fp8_gemm_tc_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ 
                 tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + c * 32), r);
                 tmem_ld_wait();
                 const int nc = n0 + c * 32;
-                if (m < M && nc < N) {
+                if (m < M && nc < N && out_f32) {
+                    // unrounded f32 partials (row-parallel layers: summed over ranks before the rounding)
+                    float* frow = reinterpret_cast<float*>(y) + (size_t)m * N + nc;
+                    const bool v4 = (N % 4) == 0 && nc + 32 <= N;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float4 ws = __ldg(reinterpret_cast<const float4*>(w_scale + nc) + j);
+                        float4 v;
+                        v.x = __fmul_rn(__fmul_rn(__uint_as_float(r[4 * j + 0]), as), ws.x);
+                        v.y = __fmul_rn(__fmul_rn(__uint_as_float(r[4 * j + 1]), as), ws.y);
+                        v.z = __fmul_rn(__fmul_rn(__uint_as_float(r[4 * j + 2]), as), ws.z);
+                        v.w = __fmul_rn(__fmul_rn(__uint_as_float(r[4 * j + 3]), as), ws.w);
+                        if (v4) {
+                            reinterpret_cast<float4*>(frow)[j] = v;
+                        } else {
+                            if (nc + 4 * j + 0 < N) frow[4 * j + 0] = v.x;
+                            if (nc + 4 * j + 1 < N) frow[4 * j + 1] = v.y;
+                            if (nc + 4 * j + 2 < N) frow[4 * j + 2] = v.z;
+                            if (nc + 4 * j + 3 < N) frow[4 * j + 3] = v.w;
+                        }
+                    }
+                } else if (m < M && nc < N) {
                     uint32_t o[16];
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
@@ -187,7 +208,7 @@ static int32_t fp8_gemm_launch_bn(scr_ctx* ctx, const uint8_t* wpack, const uint
                                          (int)F8GSmem<BN>::kTotal);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "fp8_gemm smem attribute: %s", cudaGetErrorString(e));
     fp8_gemm_tc_kernel<BN><<<grid, F8G_THREADS, F8GSmem<BN>::kTotal, stream>>>(wpack, w_scale, xq, a_scale, y, M, N, g.KT,
-                                                                              g.NT, MT, MT * 128, ctx->dev_status);
+                                                                              g.NT, MT, MT * 128, ctx->out_f32, ctx->dev_status);
     return scr_check_launch(ctx, "fp8_gemm_tc");
 }
 

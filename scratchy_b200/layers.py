@@ -161,6 +161,24 @@ class AffineQuantLinear:
             _stream(dev)))
         return out.reshape(*x.shape[:-1], self.out_features)
 
+    def forward_partial(self, x: torch.Tensor, out: Optional[torch.Tensor] = None,
+                        workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Row-parallel use: unrounded f32 sums over this rank's K-slice (`scr_linear_affine_b4_partial`)."""
+        x2 = x.reshape(-1, self.in_features).contiguous()
+        M = int(x2.shape[0])
+        dev = x2.device
+        if out is None:
+            out = torch.empty((M, self.out_features), dtype=torch.float32, device=dev)
+        ctx = _lib.context(_dev_index(dev))
+        need = self.workspace_bytes(M)
+        if need and (workspace is None or workspace.numel() < need):
+            workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+        ctx.check(_lib.lib().scr_linear_affine_b4_partial(
+            ctx.handle, _ptr(self.packed), _ptr(x2), M, self.out_features, self.in_features, self.group_size,
+            _ptr(out), _ptr(workspace), ctypes.c_size_t(workspace.numel() if workspace is not None else 0),
+            _stream(dev)))
+        return out
+
     def dequantize(self) -> torch.Tensor:
         """Test hook: dense bf16 [N, K] from the repacked buffer (`scr_affine_b4_dequant_dump`)."""
         dev = self.packed.device
@@ -274,6 +292,23 @@ class Fp8Linear:
         ctx.check(_lib.lib().scr_linear_fp8(ctx.handle, _ptr(self.packed), _ptr(act.buf), act.M, self.out_features,
                                             self.in_features, _ptr(out), _ptr(workspace),
                                             ctypes.c_size_t(workspace.numel()), _stream(dev)))
+        return out
+
+    def forward_partial(self, x: torch.Tensor, out: Optional[torch.Tensor] = None,
+                        workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Row-parallel use: quantise this rank's K-slice per token, unrounded f32 sums out
+        (`scr_fp8_quant_per_token` + `scr_linear_fp8_partial`)."""
+        act = self.quantize_activation(x)
+        dev = act.buf.device
+        if out is None:
+            out = torch.empty((act.M, self.out_features), dtype=torch.float32, device=dev)
+        ctx = _lib.context(_dev_index(dev))
+        need = self.workspace_bytes(act.M)
+        if workspace is None or workspace.numel() < need:
+            workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
+        ctx.check(_lib.lib().scr_linear_fp8_partial(ctx.handle, _ptr(self.packed), _ptr(act.buf), act.M,
+                                                    self.out_features, self.in_features, _ptr(out), _ptr(workspace),
+                                                    ctypes.c_size_t(workspace.numel()), _stream(dev)))
         return out
 
     def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None,

@@ -1,0 +1,142 @@
+"""Tensor-parallel sharding of the quantized linears — host-side mirror of the reference's law.
+
+Reference (paths relative to its root):
+  * world typing            crates/core/tp-world/src/lib.rs:19-125 (`TpWorld<N>`, `Rank`)
+  * slice law               crates/compiler/subtile/src/tensor_parallel.rs:1172-1240 (`slice_source`):
+                            a whole activation splits the weight's output channels (`SourceShard::Cols`
+                            of the `[K,N]` view = row blocks of the on-disk `[N,K]`; a per-channel scale
+                            follows N); a column-split activation splits the contraction
+                            (`SourceShard::Rows` of `[K,N]` = column blocks of `[N,K]`; scale whole; the
+                            affine preset needs `(K/W) % group == 0`, :534-537) and leaves a `Partial`
+  * collective meaning      tensor_parallel.rs:1342-1393 (`eval_collective`): AllReduce sums the ranks'
+                            operands; the reference's host evaluator does it in rank order in f32
+
+One process per GPU; `torch.distributed` (NCCL on GPUs, gloo in the CPU tests) is the plumbing.
+The per-rank linears are the ordinary `AffineQuantLinear` / `Fp8Linear` over the sliced tensors:
+slicing happens on the checkpoint tensors, before the load-time repack.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+VALID_WORLDS = (1, 2, 4, 8)          # the build features tp-2/4/8 of crates/core/tp-world/Cargo.toml:18-24
+
+
+@dataclass(frozen=True)
+class TpWorld:
+    """`TpWorld<N>` + `Rank`: a world size from {1,2,4,8} and this process's rank in it."""
+    world: int
+    rank: int
+
+    def __post_init__(self):
+        if self.world not in VALID_WORLDS:
+            raise ValueError(f"tensor-parallel world must be one of {VALID_WORLDS}, got {self.world}")
+        if not 0 <= self.rank < self.world:
+            raise ValueError(f"rank {self.rank} outside world {self.world}")
+
+
+def slice_rows(full: torch.Tensor, tp: TpWorld) -> torch.Tensor:
+    """Rank's block of rows of a 2-D (or 1-D, per-row) tensor: `full[r*lr:(r+1)*lr]`."""
+    n = full.shape[0]
+    if n % tp.world != 0:
+        raise ValueError(f"{n} rows do not split over {tp.world} ranks")
+    lr = n // tp.world
+    return full[tp.rank * lr:(tp.rank + 1) * lr].contiguous()
+
+
+def slice_cols(full: torch.Tensor, tp: TpWorld, unit: int = 1) -> torch.Tensor:
+    """Rank's block of columns of a 2-D tensor; `unit` = logical elements per stored column
+    (8 for U32-packed int4 codes, 64 for per-group scales)."""
+    c = full.shape[1]
+    if c % tp.world != 0:
+        raise ValueError(f"{c * unit} columns do not split over {tp.world} ranks")
+    lc = c // tp.world
+    return full[:, tp.rank * lc:(tp.rank + 1) * lc].contiguous()
+
+
+# ---------------------------------------------------------------------------- affine int4
+def shard_affine_column_parallel(weight, scales, biases, tp: TpWorld):
+    """q/k/v/gate/up: split the output channels (rows of `[N, K/8]`, `[N, K/64]`)."""
+    return slice_rows(weight, tp), slice_rows(scales, tp), slice_rows(biases, tp)
+
+
+def shard_affine_row_parallel(weight, scales, biases, tp: TpWorld, group_size: int = 64):
+    """o/down: split the contraction (columns).  Refused unless `(K/W) % group == 0`
+    (tensor_parallel.rs:534-537)."""
+    K = weight.shape[1] * 8
+    if (K // tp.world) % group_size != 0 or K % tp.world != 0:
+        raise ValueError(f"K={K} over {tp.world} ranks leaves {K / tp.world} per rank, not a multiple of "
+                         f"group_size={group_size}")
+    return slice_cols(weight, tp, 8), slice_cols(scales, tp, group_size), slice_cols(biases, tp, group_size)
+
+
+# ---------------------------------------------------------------------------- fp8 per-channel
+def shard_fp8_column_parallel(weight_e4m3, weight_scale, tp: TpWorld):
+    return slice_rows(weight_e4m3, tp), slice_rows(weight_scale.reshape(-1), tp)
+
+
+def shard_fp8_row_parallel(weight_e4m3, weight_scale, tp: TpWorld):
+    """The per-channel scale stays whole; each rank quantises its own K-slice of the activation
+    per token, so `a_scale` differs per rank and the partials are dequantised before the sum."""
+    return slice_cols(weight_e4m3, tp), weight_scale.reshape(-1).contiguous()
+
+
+# ---------------------------------------------------------------------------- collective
+class TpCommunicator:
+    """The `SubOp::AllReduce` of a row-parallel layer: a sum over the ranks of a process group."""
+
+    def __init__(self, tp: TpWorld, group: Optional[dist.ProcessGroup] = None):
+        self.tp = tp
+        self.group = group
+        if tp.world > 1:
+            if not dist.is_initialized():
+                raise RuntimeError("torch.distributed is not initialised")
+            ws = dist.get_world_size(group)
+            if ws != tp.world:
+                raise ValueError(f"process group has {ws} ranks, TpWorld says {tp.world}")
+
+    def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        if self.tp.world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+        return t
+
+
+def partial_to_bf16(part: torch.Tensor) -> torch.Tensor:
+    """`scr_partial_to_bf16`: the single rounding after the all-reduce."""
+    import ctypes
+    from . import _lib
+    dev = part.device
+    out = torch.empty(part.shape, dtype=torch.bfloat16, device=dev)
+    ctx = _lib.context(dev.index if dev.index is not None else torch.cuda.current_device())
+    ctx.check(_lib.lib().scr_partial_to_bf16(ctx.handle, ctypes.c_void_p(part.data_ptr()), part.numel(),
+                                             ctypes.c_void_p(out.data_ptr()),
+                                             ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)))
+    return out
+
+
+class RowParallel:
+    """A row-parallel linear (o, down): local contraction over the rank's K-slice, then the all-reduce."""
+
+    def __init__(self, linear, comm: TpCommunicator):
+        self.linear = linear
+        self.comm = comm
+
+    def forward(self, x_local: torch.Tensor, workspace=None) -> torch.Tensor:
+        """f32 partials over the rank's K-slice, summed over ranks, rounded to bf16 once."""
+        part = self.linear.forward_partial(x_local, workspace=workspace)
+        self.comm.all_reduce(part)
+        return partial_to_bf16(part)
+
+
+class ColumnParallel:
+    """A column-parallel linear (q/k/v, gate/up): whole activation in, the rank's channels out."""
+
+    def __init__(self, linear):
+        self.linear = linear
+
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, workspace=None) -> torch.Tensor:
+        return self.linear.forward(x, out=out, workspace=workspace)

@@ -1,0 +1,110 @@
+"""Tensor-parallel parity on the GPU.
+
+One-GPU part: the `Partial` (f32) outputs of a row-parallel slice, summed in rank order on the
+host, must match the lockstep oracle at the same world size (parity is per world size: each
+rank quantises its own K-slice per token, so fp8 results differ slightly from TP=1 by design).
+Multi-GPU part (needs >= 2 devices, skipped otherwise): two processes, NCCL all-reduce.
+"""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+import oracle
+from scratchy_b200 import synth
+from test_tp_cpu import lockstep_affine_row_parallel, lockstep_fp8_row_parallel
+from util import bf16_dev, bits_of, rel_l2, to_dev, u32_dev
+
+pytestmark = pytest.mark.gpu
+REL_L2_TOL = 1e-3
+
+
+@pytest.mark.parametrize("W,M", [(2, 1), (8, 4), (4, 40)])
+def test_affine_row_parallel_partials_one_gpu(W, M):
+    import torch
+    from scratchy_b200 import AffineQuantLinear
+    N, K = 256, 2048
+    w, s, b = synth.affine_int4_weights(N, K, 64, 31)
+    x = synth.activations_bf16(M, K, 32)
+    parts = []
+    for r in range(W):
+        lin = AffineQuantLinear.from_tensors(u32_dev(oracle.slice_cols(w, W, r)), bf16_dev(oracle.slice_cols(s, W, r)),
+                                             bf16_dev(oracle.slice_cols(b, W, r)))
+        parts.append(lin.forward_partial(bf16_dev(oracle.slice_cols(x, W, r)).reshape(M, K // W)).cpu().numpy())
+    torch.cuda.synchronize()
+    got = oracle.f32_to_bf16_bits(oracle.allreduce_rank_order(parts))
+    want, _ = lockstep_affine_row_parallel(w, s, b, x, W)
+    assert rel_l2(got, want) <= REL_L2_TOL
+
+
+@pytest.mark.parametrize("W,M", [(2, 1), (8, 16), (4, 40)])
+def test_fp8_row_parallel_partials_one_gpu(W, M):
+    import torch
+    from scratchy_b200 import Fp8Linear
+    N, K = 256, 2048
+    wq, ws = oracle.fp8_quantize_weight_per_channel(synth.fp8_weights_f32(N, K, 33))
+    x = synth.activations_bf16(M, K, 34)
+    parts = []
+    for r in range(W):
+        lin = Fp8Linear.from_tensors(to_dev(oracle.slice_cols(wq, W, r)), to_dev(ws))
+        parts.append(lin.forward_partial(bf16_dev(oracle.slice_cols(x, W, r)).reshape(M, K // W)).cpu().numpy())
+    torch.cuda.synchronize()
+    got = oracle.f32_to_bf16_bits(oracle.allreduce_rank_order(parts))
+    want, _ = lockstep_fp8_row_parallel(wq, ws, x, W)
+    assert rel_l2(got, want) <= REL_L2_TOL
+
+
+def _nccl_worker(rank, world, port, q):
+    import torch
+    import torch.distributed as dist
+    from scratchy_b200 import AffineQuantLinear, Fp8Linear, tp as tpmod
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        tp = tpmod.TpWorld(world, rank)
+        comm = tpmod.TpCommunicator(tp)
+        N, K, M = 512, 4096, 8
+        ok = True
+        w, s, b = synth.affine_int4_weights(N, K, 64, 41)
+        x = synth.activations_bf16(M, K, 42)
+        dev = torch.device("cuda", rank)
+        wt = torch.from_numpy(w.view(np.int32)).to(dev)
+        st = torch.from_numpy(s.view(np.int16)).view(torch.bfloat16).to(dev)
+        bt = torch.from_numpy(b.view(np.int16)).view(torch.bfloat16).to(dev)
+        xt = torch.from_numpy(x.view(np.int16)).view(torch.bfloat16).to(dev)
+        lin = AffineQuantLinear.from_tensors(*tpmod.shard_affine_row_parallel(wt, st, bt, tp))
+        y = tpmod.RowParallel(lin, comm).forward(tpmod.slice_cols(xt, tp))
+        want, _ = lockstep_affine_row_parallel(w, s, b, x, world)
+        ok &= rel_l2(y.view(torch.int16).cpu().numpy().view(np.uint16), want) <= REL_L2_TOL
+        wq, ws = oracle.fp8_quantize_weight_per_channel(synth.fp8_weights_f32(N, K, 43))
+        flin = Fp8Linear.from_tensors(*tpmod.shard_fp8_row_parallel(torch.from_numpy(wq).to(dev),
+                                                                    torch.from_numpy(ws).to(dev), tp))
+        y = tpmod.RowParallel(flin, comm).forward(tpmod.slice_cols(xt, tp))
+        want, _ = lockstep_fp8_row_parallel(wq, ws, x, world)
+        ok &= rel_l2(y.view(torch.int16).cpu().numpy().view(np.uint16), want) <= REL_L2_TOL
+        torch.cuda.synchronize()
+        q.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_nccl_row_parallel():
+    import torch
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    with socket.socket() as sk:
+        sk.bind(("127.0.0.1", 0))
+        port = sk.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_nccl_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert sorted(res) == [(0, True), (1, True)]
