@@ -316,7 +316,10 @@ def run_gpu(args):
                        "bytes_per_step": step_bytes, "l2": "inputs larger than L2 (1.585 GB of distinct weights per step)",
                        "replicas": world, "launch": "one CUDA graph of 196 matvec launches per step"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["src"],
+                         "frac": achieved / peaks["hbm_gbs"],
+                         # dram__bytes_read+write per launch from the ncu capture summarised under profiles/
+                         # (launch-weighted mean over the 7 shapes; 1.0016 x the algorithmic bytes)
+                         "traffic": 8117138, "peak_source": peaks["src"],
                          "kernel": "affine_b4_gemv_kernel", "avg_launch_us": per_launch_us,
                          "alg_bytes_per_launch": step_bytes / (N_LAYERS * len(LAYER_ORDER))},
             "cpu_baseline": {"value": cpu_v, "unit": UNIT, "cores": cores, "kind": "port",
