@@ -202,10 +202,32 @@ def run_gpu(args):
     xs = [torch.randn((M, K), device=device).to(torch.bfloat16) for K, _ in shapes]
     ys = [torch.empty((M, N), dtype=torch.bfloat16, device=device) for _, N in shapes]
 
+    # Dataflow of the reference's Llama forward (crates/models/arch/dsl/llama.py:10-30): q, k and v read
+    # the same normed activation and are independent of each other, as are gate and up; o waits for the
+    # three, down for the two.  The tape keeps exactly those dependencies: independent linears go to
+    # parallel branches of the graph (forked streams at capture), dependent ones join first.
+    branch = [torch.cuda.Stream(device) for _ in range(2)]
+
+    def run_group(row, idxs):
+        cur = torch.cuda.current_stream(device)
+        if len(idxs) == 1 or args.serial:
+            for i in idxs:
+                row[i].forward(xs[i], out=ys[i])
+            return
+        for b, i in enumerate(idxs[1:]):
+            branch[b].wait_stream(cur)
+            with torch.cuda.stream(branch[b]):
+                row[i].forward(xs[i], out=ys[i])
+        row[idxs[0]].forward(xs[idxs[0]], out=ys[idxs[0]])
+        for b in range(len(idxs) - 1):
+            cur.wait_stream(branch[b])
+
     def step():
         for row in layers:
-            for lin, x, y in zip(row, xs, ys):
-                lin.forward(x, out=y)
+            run_group(row, [0, 1, 2])      # q, k, v
+            run_group(row, [3])            # o
+            run_group(row, [4, 5])         # gate, up
+            run_group(row, [6])            # down
 
     def barrier():
         if world > 1:
@@ -265,8 +287,19 @@ def run_gpu(args):
     def step_e2e():
         d_in.copy_(h_in, non_blocking=True)
         for row, vrow in zip(layers, views):
-            for lin, (x, y) in zip(row, vrow):
-                lin.forward(x, out=y)
+            for idxs in ([0, 1, 2], [3], [4, 5], [6]):
+                cur = torch.cuda.current_stream(device)
+                if len(idxs) == 1 or args.serial:
+                    for i in idxs:
+                        row[i].forward(vrow[i][0], out=vrow[i][1])
+                    continue
+                for b, i in enumerate(idxs[1:]):
+                    branch[b].wait_stream(cur)
+                    with torch.cuda.stream(branch[b]):
+                        row[i].forward(vrow[i][0], out=vrow[i][1])
+                row[idxs[0]].forward(vrow[idxs[0]][0], out=vrow[idxs[0]][1])
+                for b in range(len(idxs) - 1):
+                    cur.wait_stream(branch[b])
         h_out.copy_(d_out, non_blocking=True)
 
     step_e2e()
@@ -314,7 +347,8 @@ def run_gpu(args):
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "llama-3.2-3b int4 g64 linears (q,k,v,o,gate,up,down) x 28 layers, M=1",
                        "bytes_per_step": step_bytes, "l2": "inputs larger than L2 (1.585 GB of distinct weights per step)",
-                       "replicas": world, "launch": "one CUDA graph of 196 matvec launches per step"},
+                       "replicas": world, "launch": "one CUDA graph of 196 matvec launches per step; q/k/v and gate/up on parallel branches"
+                       if not args.serial else "one CUDA graph of 196 matvec launches per step, one branch"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"],
                          # dram__bytes_read+write per launch from the ncu capture summarised under profiles/
@@ -499,6 +533,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--sweep", action="store_true")
+    ap.add_argument("--serial", action="store_true", help="one branch: every linear waits for the previous one")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
