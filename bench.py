@@ -526,6 +526,42 @@ def run_tp(device, world, rank):
     return out
 
 
+def run_case(args):
+    """`--case kind,shape,M`: one linear, timed alone over rotating weight copies (profiling aid; prints one line)."""
+    import torch
+    from scratchy_b200 import AffineQuantLinear, Fp8Linear
+    kind, name, M = args.case.split(",")
+    M = int(M)
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    K, N = (synth.LLAMA_3_2_3B if kind == "int4" else synth.QWEN_2_5_7B)[name]
+    copies = max(2, int((256 << 20) // (N * K)) + 1)
+    lins = []
+    for c in range(copies):
+        if kind == "int4":
+            w = torch.randint(-2 ** 31, 2 ** 31 - 1, (N, K // 8), dtype=torch.int32, device=device)
+            s_ = (torch.randn((N, K // 64), device=device) * 0.02).abs().add(1e-3).to(torch.bfloat16)
+            lins.append(AffineQuantLinear.from_tensors(w, s_, (-8.0 * s_.float()).to(torch.bfloat16)))
+        else:
+            w = torch.randint(0, 120, (N, K), dtype=torch.uint8, device=device)
+            lins.append(Fp8Linear.from_tensors(w, torch.rand(N, device=device) * 1e-3 + 1e-4))
+    x = torch.randn((M, K), device=device).to(torch.bfloat16)
+    y = torch.empty((M, N), dtype=torch.bfloat16, device=device)
+    ws = torch.empty(max(16, lins[0].workspace_bytes(M)), dtype=torch.uint8, device=device)
+    for l in lins[:2]:
+        l.forward(x, out=y, workspace=ws)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = args.steps
+    a.record()
+    for i in range(reps):
+        lins[i % copies].forward(x, out=y, workspace=ws)
+    b.record()
+    torch.cuda.synchronize()
+    dt = a.elapsed_time(b) * 1e-3 / reps
+    print(json.dumps({"case": args.case, "us": dt * 1e6, "TFLOPs": 2.0 * M * N * K / dt / 1e12, "N": N, "K": K, "M": M}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -534,7 +570,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--sweep", action="store_true")
     ap.add_argument("--serial", action="store_true", help="one branch: every linear waits for the previous one")
+    ap.add_argument("--case", default=None, help="kind,shape,M e.g. int4,gate,2048: time one linear alone")
     args = ap.parse_args()
+    if args.case:
+        run_case(args)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

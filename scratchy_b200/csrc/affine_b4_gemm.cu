@@ -2,18 +2,19 @@
 //
 //   y[m,n] = bf16( sum_k x[m,k] * w[n,k] ),  w = the bit-exact bf16 dequantisation of the codes
 //
-// Persistent, warp-specialised CTA (320 threads), one per SM:
-//   warp 0      producer: per 128-k chunk, two TMA tile loads of the activations (tensor map over
-//               x[M,K], 64 x 128 box, 128-byte swizzle; out-of-range rows/k read as zero) and one
-//               1-D bulk copy per row-block of the packed weight blocks (BN/16 x 1152 bytes)
-//   warp 1      owns TMEM; one elected thread issues tcgen05.mma kind::f16 (A = 128 tokens,
-//               B = BN channels, 8 x K=16 per chunk) and commits the stage / accumulator barriers
-//   warps 2-5   dequantise: packed codes (shared) -> bf16 via affine_dequant_piece -> the K-major
-//               128-byte-swizzled operand image the MMA reads (bank-conflict-free 16-byte stores)
-//   warps 6-9   epilogue: tcgen05.ld the 128 x BN f32 accumulator (thread = token row), round to
-//               bf16, 16-byte stores
-// Two accumulator buffers in TMEM overlap the epilogue of tile i with the main loop of tile i+1.
-// No multicast: every CTA issues its own loads.
+// Persistent, warp-specialised CTA (448 threads), one per SM; a tile is TM x 128 tokens by 128
+// channels (TM = 2 when M > 128, so every dequantised weight tile feeds two MMAs):
+//   warp 0       producer: per 128-k chunk, 2 x TM TMA tile loads of the activations (tensor map over
+//                x[M,K], 64 x 128 box, 128-byte swizzle; out-of-range rows/k read as zero) and one
+//                1-D bulk copy per row-block of the packed weight blocks (8 x 1152 bytes)
+//   warp 1       owns TMEM; one elected thread issues tcgen05.mma kind::f16 (A = 128 tokens,
+//                B = 128 channels, 8 x K=16 per chunk and token half) and commits the barriers
+//   warps 2-9    dequantise: packed codes (shared) -> bf16 -> the K-major 128-byte-swizzled operand
+//                image the MMA reads (bank-conflict-free 16-byte stores)
+//   warps 10-13  epilogue: tcgen05.ld the 128 x 128 f32 accumulators (thread = token row), round to
+//                bf16 (or keep f32 partials), 16-byte stores
+// TMEM holds 2 buffers x TM accumulators of 128 columns, so the epilogue of tile i overlaps the
+// main loop of tile i+1.  No multicast: every CTA issues its own loads.
 #include <cuda.h>
 
 #include "affine_b4.cuh"
@@ -22,18 +23,20 @@
 bool affine_b4_gemm_tc_enabled() { return true; }
 size_t affine_b4_gemm_tc_workspace(int, int, int) { return 0; }
 
-#define A4G_THREADS 320
-#define A4G_SX 3          // activation stages (32 KB each)
+#define A4G_THREADS 448
+#define A4G_DQ_WARPS 8
 #define A4G_SP 3          // packed-weight stages
 #define A4G_SD 2          // dequantised-weight stages
+#define A4G_BN 128
 
-template <int BN>
+template <int TM>
 struct A4GSmem {
-    static constexpr uint32_t kXStage = 32768u;                         // 2 atoms of 128 rows x 128 B
-    static constexpr uint32_t kDStage = 2u * (uint32_t)BN * 128u;       // 2 atoms of BN rows x 128 B
-    static constexpr uint32_t kPStage = (uint32_t)(BN / 16) * AFF_BLOCK_BYTES;
+    static constexpr int kSX = (TM == 1) ? 3 : 2;                       // activation stages
+    static constexpr uint32_t kXStage = 32768u * TM;                    // TM x 2 atoms of 128 rows x 128 B
+    static constexpr uint32_t kDStage = 2u * A4G_BN * 128u;             // 2 atoms of 128 rows x 128 B
+    static constexpr uint32_t kPStage = (uint32_t)(A4G_BN / 16) * AFF_BLOCK_BYTES;
     static constexpr uint32_t kXOff = 0;
-    static constexpr uint32_t kDOff = kXOff + A4G_SX * kXStage;
+    static constexpr uint32_t kDOff = kXOff + kSX * kXStage;
     static constexpr uint32_t kPOff = kDOff + A4G_SD * kDStage;
     static constexpr uint32_t kBarOff = (kPOff + A4G_SP * kPStage + 127u) & ~127u;
     static constexpr uint32_t kTotal = kBarOff + 256u + 1024u;
@@ -57,43 +60,44 @@ __device__ __forceinline__ uint32_t ld_shared_u32(uint32_t addr) {
     return v;
 }
 
-template <int BN>
+template <int TM>
 __global__ void __launch_bounds__(A4G_THREADS, 1)
 affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_t* __restrict__ packed,
                          uint16_t* __restrict__ y, int M, int N, int RB, int KC, int MT, int out_f32,
                          int* __restrict__ status) {
-    using S = A4GSmem<BN>;
+    using S = A4GSmem<TM>;
+    constexpr int SX = S::kSX;
+    constexpr int BN = A4G_BN;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t bar_base = smem_base + S::kBarOff;
     // barrier slots: xfull[SX] xempty[SX] pfull[SP] pempty[SP] dfull[SD] dempty[SD] accf[2] acce[2]
     auto xfull = [&](int s) { return bar_base + 8u * s; };
-    auto xempty = [&](int s) { return bar_base + 8u * (A4G_SX + s); };
-    auto pfull = [&](int s) { return bar_base + 8u * (2 * A4G_SX + s); };
-    auto pempty = [&](int s) { return bar_base + 8u * (2 * A4G_SX + A4G_SP + s); };
-    auto dfull = [&](int s) { return bar_base + 8u * (2 * A4G_SX + 2 * A4G_SP + s); };
-    auto dempty = [&](int s) { return bar_base + 8u * (2 * A4G_SX + 2 * A4G_SP + A4G_SD + s); };
-    constexpr int kAccSlot = 2 * A4G_SX + 2 * A4G_SP + 2 * A4G_SD;
+    auto xempty = [&](int s) { return bar_base + 8u * (SX + s); };
+    auto pfull = [&](int s) { return bar_base + 8u * (2 * SX + s); };
+    auto pempty = [&](int s) { return bar_base + 8u * (2 * SX + A4G_SP + s); };
+    auto dfull = [&](int s) { return bar_base + 8u * (2 * SX + 2 * A4G_SP + s); };
+    auto dempty = [&](int s) { return bar_base + 8u * (2 * SX + 2 * A4G_SP + A4G_SD + s); };
+    constexpr int kAccSlot = 2 * SX + 2 * A4G_SP + 2 * A4G_SD;
     auto accf = [&](int b) { return bar_base + 8u * (kAccSlot + b); };
     auto acce = [&](int b) { return bar_base + 8u * (kAccSlot + 2 + b); };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + S::kBarOff + 8 * (kAccSlot + 4));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int NTB = RB * 16 / BN;                        // RB is a multiple of 8 (N padded to 128)
-    const int NTBc = (RB * 16 + BN - 1) / BN;
-    const int tiles = MT * NTBc;
-    (void)NTB;
+    const int tiles = MT * NTB;                          // MT = token tiles of 128 * TM
+    constexpr uint32_t kAccCols = (uint32_t)(TM * BN);   // TMEM columns per accumulator buffer
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < A4G_SX; ++s) { mbar_init(xfull(s), 1); mbar_init(xempty(s), 1); }
-        for (int s = 0; s < A4G_SP; ++s) { mbar_init(pfull(s), 1); mbar_init(pempty(s), 128); }
-        for (int s = 0; s < A4G_SD; ++s) { mbar_init(dfull(s), 128); mbar_init(dempty(s), 1); }
+        for (int s = 0; s < SX; ++s) { mbar_init(xfull(s), 1); mbar_init(xempty(s), 1); }
+        for (int s = 0; s < A4G_SP; ++s) { mbar_init(pfull(s), 1); mbar_init(pempty(s), A4G_DQ_WARPS * 32); }
+        for (int s = 0; s < A4G_SD; ++s) { mbar_init(dfull(s), A4G_DQ_WARPS * 32); mbar_init(dempty(s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(accf(b), 1); mbar_init(acce(b), 128); }
         fence_mbar_init();
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32((const void*)tmem_slot), 2 * BN);
+        tmem_alloc(smem_u32((const void*)tmem_slot), 2 * kAccCols);
         tmem_relinquish();
     }
     tc_fence_before();
@@ -109,11 +113,10 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
             for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
                 const int mt = tile % MT, nb = tile / MT;
                 const int rb0 = nb * (BN / 16);
-                const int rbn = min(BN / 16, RB - rb0);
                 for (int kc = 0; kc < KC; ++kc) {
                     mbar_wait(pempty(sp), php ^ 1u, status, TC_ERR_EMPTY_WAIT);
-                    mbar_arrive_expect_tx(pfull(sp), (uint32_t)rbn * AFF_BLOCK_BYTES);
-                    for (int j = 0; j < rbn; ++j)       // row-block-major packing: one block per row-block
+                    mbar_arrive_expect_tx(pfull(sp), S::kPStage);
+                    for (int j = 0; j < BN / 16; ++j)   // row-block-major packing: one block per row-block
                         bulk_g2s(smem_base + S::kPOff + sp * S::kPStage + j * AFF_BLOCK_BYTES,
                                  packed + ((size_t)(rb0 + j) * KC + kc) * AFF_BLOCK_BYTES, AFF_BLOCK_BYTES, pfull(sp));
                     if (++sp == A4G_SP) { sp = 0; php ^= 1u; }
@@ -121,9 +124,12 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
                     mbar_wait(xempty(sx), phx ^ 1u, status, TC_ERR_EMPTY_WAIT);
                     mbar_arrive_expect_tx(xfull(sx), S::kXStage);
                     const uint32_t xs = smem_base + S::kXOff + sx * S::kXStage;
-                    tma_load_2d(xs, &x_map, kc * 128, mt * 128, xfull(sx));
-                    tma_load_2d(xs + 16384u, &x_map, kc * 128 + 64, mt * 128, xfull(sx));
-                    if (++sx == A4G_SX) { sx = 0; phx ^= 1u; }
+#pragma unroll
+                    for (int h = 0; h < TM; ++h) {
+                        tma_load_2d(xs + h * 32768u, &x_map, kc * 128, (mt * TM + h) * 128, xfull(sx));
+                        tma_load_2d(xs + h * 32768u + 16384u, &x_map, kc * 128 + 64, (mt * TM + h) * 128, xfull(sx));
+                    }
+                    if (++sx == SX) { sx = 0; phx ^= 1u; }
                 }
             }
         }
@@ -133,14 +139,12 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
             int sx = 0, sd = 0;
             uint32_t phx = 0, phd = 0;
             int it = 0;
+            const uint32_t idesc = umma_idesc(1, 1, 128, BN);
             for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
-                const int nb = tile / MT;
-                const int rbn = min(BN / 16, RB - nb * (BN / 16));
-                const uint32_t idesc = umma_idesc(1, 1, 128, 16u * rbn);
                 const int buf = it & 1;
                 mbar_wait(acce(buf), ((uint32_t)(it >> 1) & 1u) ^ 1u, status, TC_ERR_ACC_EMPTY);
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+                const uint32_t d_tmem = tmem_base + (uint32_t)buf * kAccCols;
                 for (int kc = 0; kc < KC; ++kc) {
                     mbar_wait(xfull(sx), phx, status, TC_ERR_FULL_WAIT);
                     mbar_wait(dfull(sd), phd, status, TC_ERR_DEQ_WAIT);
@@ -148,41 +152,49 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
                     const uint32_t xs = smem_base + S::kXOff + sx * S::kXStage;
                     const uint32_t ds = smem_base + S::kDOff + sd * S::kDStage;
 #pragma unroll
-                    for (int a = 0; a < 2; ++a) {
-                        const uint64_t adesc = umma_desc_k_sw128(xs + a * 16384u);
-                        const uint64_t bdesc = umma_desc_k_sw128(ds + a * (uint32_t)(BN * 128));
+                    for (int h = 0; h < TM; ++h) {
 #pragma unroll
-                        for (int k4 = 0; k4 < 4; ++k4)
-                            umma_f16(d_tmem, adesc + (uint64_t)(2 * k4), bdesc + (uint64_t)(2 * k4), idesc, (kc | a | k4) != 0);
+                        for (int a = 0; a < 2; ++a) {
+                            const uint64_t adesc = umma_desc_k_sw128(xs + h * 32768u + a * 16384u);
+                            const uint64_t bdesc = umma_desc_k_sw128(ds + a * (uint32_t)(BN * 128));
+#pragma unroll
+                            for (int k4 = 0; k4 < 4; ++k4)
+                                umma_f16(d_tmem + (uint32_t)(h * BN), adesc + (uint64_t)(2 * k4), bdesc + (uint64_t)(2 * k4), idesc,
+                                         (kc | a | k4) != 0);
+                        }
                     }
                     umma_commit(xempty(sx));
                     umma_commit(dempty(sd));
-                    if (++sx == A4G_SX) { sx = 0; phx ^= 1u; }
+                    if (++sx == SX) { sx = 0; phx ^= 1u; }
                     if (++sd == A4G_SD) { sd = 0; phd ^= 1u; }
                 }
                 umma_commit(accf(buf));
             }
         }
-    } else if (warp < 6) {
-        // ------------------------------------------------------------------ dequantise (warps 2..5)
-        const int dw = warp - 2;                       // 0..3
-        const int g = lane >> 2, t = lane & 3;
+    }
+    else if (warp < 2 + A4G_DQ_WARPS) {
+        // ------------------------------------------------------------------ dequantise (warps 2..9)
+        const int dw = warp - 2;
+        // Lane -> piece of a (row-block, half) pair, arranged so that the eight lanes of a quarter-warp
+        // hold four rows and one k-quarter pair: their 16-byte stores then hit eight distinct bank groups.
+        const int g = ((lane >> 3) & 1) * 4 + ((lane & 7) >> 1);
+        const int t = (lane >> 4) * 2 + (lane & 1);
         const bool check = *reinterpret_cast<const unsigned int*>(packed + (size_t)RB * KC * AFF_BLOCK_BYTES) != 0;
         int sp = 0, sd = 0;
         uint32_t php = 0, phd = 0;
         for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
-            const int nb = tile / MT;
-            const int rbn = min(BN / 16, RB - nb * (BN / 16));
             for (int kc = 0; kc < KC; ++kc) {
                 mbar_wait(pfull(sp), php, status, TC_ERR_FULL_WAIT);
                 mbar_wait(dempty(sd), phd ^ 1u, status, TC_ERR_EMPTY_WAIT);
                 const uint32_t ps = smem_base + S::kPOff + sp * S::kPStage;
                 const uint32_t ds = smem_base + S::kDOff + sd * S::kDStage;
-                // (row-block, half) pairs of this stage, dealt round-robin to the four warps
-                for (int pr = dw; pr < 2 * rbn; pr += 4) {
+                // 16 (row-block, half) pairs per stage, two per warp
+#pragma unroll
+                for (int u = 0; u < 2 * (BN / 16) / A4G_DQ_WARPS; ++u) {
+                    const int pr = dw + u * A4G_DQ_WARPS;
                     const int rbl = pr >> 1, half = pr & 1;
                     const uint32_t blk = ps + (uint32_t)rbl * AFF_BLOCK_BYTES;
-                    const uint4 piece = ld_shared_v4(blk + half * 512 + lane * 16);
+                    const uint4 piece = ld_shared_v4(blk + half * 512 + (4 * g + t) * 16);
                     const uint32_t sb = ld_shared_u32(blk + 1024 + (g * 2 + (t >> 1)) * 8 + half * 4);
                     uint32_t w[16];
                     if (check) {
@@ -196,22 +208,13 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
                         affine_dequant_word_scaled(piece.w, c, w + 12);
                     }
                     // row = 16 rbl + 8 half + g -> 8-row group (2 rbl + half), row-in-group g;
-                    // k = 32 t + [0,32) -> atom t>>1, 16-byte chunks (t&1)*4 + [0,4)
+                    // k = 32 t + [0,32) -> atom t>>1, 16-byte chunks (t&1)*4 + [0,4), swizzled with g
                     const uint32_t rowbase = ds + (uint32_t)(t >> 1) * (uint32_t)(BN * 128) + (uint32_t)(2 * rbl + half) * 1024u +
                                              (uint32_t)g * 128u;
-                    // Store order rotated by two for the upper k-half so that the eight lanes of a
-                    // quarter-warp hit eight distinct 16-byte bank groups (static register indexing).
-                    const bool rot = (t >> 1) != 0;
 #pragma unroll
-                    for (int jj = 0; jj < 4; ++jj) {
-                        const int ja = jj, jb = jj ^ 2;
-                        const uint32_t v0 = rot ? w[4 * jb] : w[4 * ja];
-                        const uint32_t v1 = rot ? w[4 * jb + 1] : w[4 * ja + 1];
-                        const uint32_t v2 = rot ? w[4 * jb + 2] : w[4 * ja + 2];
-                        const uint32_t v3 = rot ? w[4 * jb + 3] : w[4 * ja + 3];
-                        const int j = rot ? jb : ja;
+                    for (int j = 0; j < 4; ++j) {
                         const uint32_t chunk = (uint32_t)(((t & 1) * 4 + j) ^ g);
-                        st_shared_v4(rowbase + chunk * 16u, v0, v1, v2, v3);
+                        st_shared_v4(rowbase + chunk * 16u, w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
                     }
                 }
                 fence_proxy_async_smem();              // generic-proxy stores -> visible to the tensor core
@@ -222,8 +225,8 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
             }
         }
     } else {
-        // ------------------------------------------------------------------ epilogue (warps 6..9)
-        const int q = warp & 3;
+        // ------------------------------------------------------------------ epilogue (warps 10..13)
+        const int q = warp & 3;                        // TMEM lane quadrant this warp may read
         const bool vec_ok = (N % 8) == 0;
         const float out_scale =
             (*reinterpret_cast<const unsigned int*>(packed + (size_t)RB * KC * AFF_BLOCK_BYTES) != 0) ? 1.0f : AFF_SCALED_FACTOR;
@@ -231,50 +234,52 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
         for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
             const int mt = tile % MT, nb = tile / MT;
             const int n0 = nb * BN;
-            const int bn_cur = min(BN, RB * 16 - n0);
             const int buf = it & 1;
             mbar_wait(accf(buf), (uint32_t)(it >> 1) & 1u, status, TC_ERR_ACC_FULL);
             tc_fence_after();
-            const int m = mt * 128 + q * 32 + lane;
-            uint16_t* yrow = y + (size_t)m * N;
-            for (int c = 0; c < bn_cur / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + c * 32), r);
-                tmem_ld_wait();
-                const int nc = n0 + c * 32;
-                if (m < M && nc < N && out_f32) {
-                    // unrounded f32 partials (row-parallel layers: summed over ranks before the rounding)
-                    float* frow = reinterpret_cast<float*>(y) + (size_t)m * N + nc;
-                    const bool v4 = (N % 4) == 0 && nc + 32 <= N;
+#pragma unroll 1
+            for (int h = 0; h < TM; ++h) {
+                const int m = (mt * TM + h) * 128 + q * 32 + lane;
+                uint16_t* yrow = y + (size_t)m * N;
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)buf * kAccCols + (uint32_t)(h * BN + c * 32), r);
+                    tmem_ld_wait();
+                    const int nc = n0 + c * 32;
+                    if (m < M && nc < N && out_f32) {
+                        // unrounded f32 partials (row-parallel layers: summed over ranks before the rounding)
+                        float* frow = reinterpret_cast<float*>(y) + (size_t)m * N + nc;
+                        const bool v4 = (N % 4) == 0 && nc + 32 <= N;
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const float4 v = make_float4(__uint_as_float(r[4 * j]) * out_scale, __uint_as_float(r[4 * j + 1]) * out_scale,
-                                                     __uint_as_float(r[4 * j + 2]) * out_scale, __uint_as_float(r[4 * j + 3]) * out_scale);
-                        if (v4) {
-                            reinterpret_cast<float4*>(frow)[j] = v;
-                        } else {
-                            if (nc + 4 * j + 0 < N) frow[4 * j + 0] = v.x;
-                            if (nc + 4 * j + 1 < N) frow[4 * j + 1] = v.y;
-                            if (nc + 4 * j + 2 < N) frow[4 * j + 2] = v.z;
-                            if (nc + 4 * j + 3 < N) frow[4 * j + 3] = v.w;
+                        for (int j = 0; j < 8; ++j) {
+                            const float4 v = make_float4(__uint_as_float(r[4 * j]) * out_scale, __uint_as_float(r[4 * j + 1]) * out_scale,
+                                                         __uint_as_float(r[4 * j + 2]) * out_scale, __uint_as_float(r[4 * j + 3]) * out_scale);
+                            if (v4) {
+                                reinterpret_cast<float4*>(frow)[j] = v;
+                            } else {
+                                if (nc + 4 * j + 0 < N) frow[4 * j + 0] = v.x;
+                                if (nc + 4 * j + 1 < N) frow[4 * j + 1] = v.y;
+                                if (nc + 4 * j + 2 < N) frow[4 * j + 2] = v.z;
+                                if (nc + 4 * j + 3 < N) frow[4 * j + 3] = v.w;
+                            }
                         }
-                    }
-                } else if (m < M && nc < N) {
-                    uint32_t o[16];
+                    } else if (m < M && nc < N) {
+                        uint32_t o[16];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(r[2 * j]) * out_scale,
-                                                                        __uint_as_float(r[2 * j + 1]) * out_scale);
-                        o[j] = *reinterpret_cast<const uint32_t*>(&p);
-                    }
-                    if (vec_ok && nc + 32 <= N) {
-                        uint4* dst = reinterpret_cast<uint4*>(yrow + nc);
+                        for (int j = 0; j < 16; ++j) {
+                            const __nv_bfloat162 pk = __floats2bfloat162_rn(__uint_as_float(r[2 * j]) * out_scale,
+                                                                             __uint_as_float(r[2 * j + 1]) * out_scale);
+                            o[j] = *reinterpret_cast<const uint32_t*>(&pk);
+                        }
+                        if (vec_ok && nc + 32 <= N) {
+                            uint4* dst = reinterpret_cast<uint4*>(yrow + nc);
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) dst[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
-                    } else {
+                            for (int j = 0; j < 4; ++j) dst[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+                        } else {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (nc + j < N) yrow[nc + j] = (uint16_t)((o[j >> 1] >> ((j & 1) * 16)) & 0xFFFFu);
+                            for (int j = 0; j < 32; ++j)
+                                if (nc + j < N) yrow[nc + j] = (uint16_t)((o[j >> 1] >> ((j & 1) * 16)) & 0xFFFFu);
+                        }
                     }
                 }
             }
@@ -287,7 +292,7 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, 2 * BN);
+        tmem_dealloc(tmem_base, 2 * kAccCols);
     }
 }
 
@@ -308,9 +313,23 @@ static PFN_encodeTiled get_encode_fn() {
     return fn;
 }
 
+template <int TM>
+static int32_t affine_gemm_launch_tm(scr_ctx* ctx, const CUtensorMap& map, const uint8_t* packed, uint16_t* y, int M, int N,
+                                     int K, cudaStream_t stream) {
+    const AffineGeom g = affine_geom(N, K);
+    const int MT = scr_ceil_div(M, 128 * TM);
+    const int tiles = MT * (g.RB * 16 / A4G_BN);
+    const int grid = std::min(tiles, ctx->sm_count);
+    cudaError_t e = cudaFuncSetAttribute(affine_b4_gemm_tc_kernel<TM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)A4GSmem<TM>::kTotal);
+    if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine gemm smem attribute: %s", cudaGetErrorString(e));
+    affine_b4_gemm_tc_kernel<TM><<<grid, A4G_THREADS, A4GSmem<TM>::kTotal, stream>>>(map, packed, y, M, N, g.RB, g.KC, MT,
+                                                                                    ctx->out_f32, ctx->dev_status);
+    return scr_check_launch(ctx, "affine_b4_gemm_tc");
+}
+
 int32_t affine_b4_gemm_tc_launch(scr_ctx* ctx, const uint8_t* packed, const uint16_t* x, uint16_t* y, int M, int N, int K,
                                  void*, size_t, cudaStream_t stream) {
-    constexpr int BN = 128;
     if (((uintptr_t)packed & 127u) != 0) return scr_fail(ctx, SCR_E_ALIGN, "packed weights must be 128-byte aligned for the GEMM path");
     if (!scr_aligned16(y)) return scr_fail(ctx, SCR_E_ALIGN, "y must be 16-byte aligned");
     PFN_encodeTiled enc = get_encode_fn();
@@ -323,15 +342,10 @@ int32_t affine_b4_gemm_tc_launch(scr_ctx* ctx, const uint8_t* packed, const uint
     CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)x, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return scr_fail(ctx, SCR_E_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
-
+    // 256-token tiles reuse every dequantised weight tile twice; below 129 tokens they would be half empty.
+    // They also need enough tiles to fill the machine.
     const AffineGeom g = affine_geom(N, K);
-    const int MT = scr_ceil_div(M, 128);
-    const int tiles = MT * ((g.RB * 16 + BN - 1) / BN);
-    const int grid = std::min(tiles, ctx->sm_count);
-    cudaError_t e = cudaFuncSetAttribute(affine_b4_gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)A4GSmem<BN>::kTotal);
-    if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine gemm smem attribute: %s", cudaGetErrorString(e));
-    affine_b4_gemm_tc_kernel<BN><<<grid, A4G_THREADS, A4GSmem<BN>::kTotal, stream>>>(map, packed, y, M, N, g.RB, g.KC, MT,
-                                                                                    ctx->out_f32, ctx->dev_status);
-    return scr_check_launch(ctx, "affine_b4_gemm_tc");
+    const int tiles2 = scr_ceil_div(M, 256) * (g.RB * 16 / A4G_BN);
+    if (M > 128 && tiles2 >= ctx->sm_count / 2) return affine_gemm_launch_tm<2>(ctx, map, packed, y, M, N, K, stream);
+    return affine_gemm_launch_tm<1>(ctx, map, packed, y, M, N, K, stream);
 }
