@@ -21,7 +21,11 @@
 #include "tc_common.cuh"
 
 bool affine_b4_gemm_tc_enabled() { return true; }
-size_t affine_b4_gemm_tc_workspace(int, int, int) { return 0; }
+static int affine_gemm_ksplit(int M, int N, int K, int sms);
+size_t affine_b4_gemm_tc_workspace(int M, int N, int K) {
+    const int ks = affine_gemm_ksplit(M, N, K, tc_sm_count());
+    return ks > 1 ? (size_t)ks * M * N * sizeof(float) : 0;
+}
 
 #define A4G_THREADS 448
 #define A4G_DQ_WARPS 8
@@ -64,7 +68,7 @@ template <int TM>
 __global__ void __launch_bounds__(A4G_THREADS, 1)
 affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_t* __restrict__ packed,
                          uint16_t* __restrict__ y, int M, int N, int RB, int KC, int MT, int out_f32,
-                         int* __restrict__ status) {
+                         int ksplit, float* __restrict__ slabs, int* __restrict__ status) {
     using S = A4GSmem<TM>;
     constexpr int SX = S::kSX;
     constexpr int BN = A4G_BN;
@@ -86,7 +90,8 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int NTB = RB * 16 / BN;                        // RB is a multiple of 8 (N padded to 128)
-    const int tiles = MT * NTB;                          // MT = token tiles of 128 * TM
+    const int tiles = MT * NTB * ksplit;                 // MT = token tiles of 128 * TM; ksplit CTAs share a tile's k
+    const int kc_per = (KC + ksplit - 1) / ksplit;
     constexpr uint32_t kAccCols = (uint32_t)(TM * BN);   // TMEM columns per accumulator buffer
 
     if (threadIdx.x == 0) {
@@ -111,9 +116,11 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
             int sx = 0, sp = 0;
             uint32_t phx = 0, php = 0;
             for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
-                const int mt = tile % MT, nb = tile / MT;
+                const int ks = tile % ksplit, t2 = tile / ksplit;
+                const int mt = t2 % MT, nb = t2 / MT;
                 const int rb0 = nb * (BN / 16);
-                for (int kc = 0; kc < KC; ++kc) {
+                const int kc_lo = ks * kc_per, kc_hi = min(KC, kc_lo + kc_per);
+                for (int kc = kc_lo; kc < kc_hi; ++kc) {
                     mbar_wait(pempty(sp), php ^ 1u, status, TC_ERR_EMPTY_WAIT);
                     mbar_arrive_expect_tx(pfull(sp), S::kPStage);
                     for (int j = 0; j < BN / 16; ++j)   // row-block-major packing: one block per row-block
@@ -145,7 +152,8 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
                 mbar_wait(acce(buf), ((uint32_t)(it >> 1) & 1u) ^ 1u, status, TC_ERR_ACC_EMPTY);
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)buf * kAccCols;
-                for (int kc = 0; kc < KC; ++kc) {
+                const int kc_lo = (tile % ksplit) * kc_per, kc_hi = min(KC, kc_lo + kc_per);
+                for (int kc = kc_lo; kc < kc_hi; ++kc) {
                     mbar_wait(xfull(sx), phx, status, TC_ERR_FULL_WAIT);
                     mbar_wait(dfull(sd), phd, status, TC_ERR_DEQ_WAIT);
                     tc_fence_after();
@@ -160,7 +168,7 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
 #pragma unroll
                             for (int k4 = 0; k4 < 4; ++k4)
                                 umma_f16(d_tmem + (uint32_t)(h * BN), adesc + (uint64_t)(2 * k4), bdesc + (uint64_t)(2 * k4), idesc,
-                                         (kc | a | k4) != 0);
+                                         ((kc - kc_lo) | a | k4) != 0);
                         }
                     }
                     umma_commit(xempty(sx));
@@ -183,7 +191,8 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
         int sp = 0, sd = 0;
         uint32_t php = 0, phd = 0;
         for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
-            for (int kc = 0; kc < KC; ++kc) {
+            const int kc_lo = (tile % ksplit) * kc_per, kc_hi = min(KC, kc_lo + kc_per);
+            for (int kc = kc_lo; kc < kc_hi; ++kc) {
                 mbar_wait(pfull(sp), php, status, TC_ERR_FULL_WAIT);
                 mbar_wait(dempty(sd), phd ^ 1u, status, TC_ERR_EMPTY_WAIT);
                 const uint32_t ps = smem_base + S::kPOff + sp * S::kPStage;
@@ -232,9 +241,13 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
             (*reinterpret_cast<const unsigned int*>(packed + (size_t)RB * KC * AFF_BLOCK_BYTES) != 0) ? 1.0f : AFF_SCALED_FACTOR;
         int it = 0;
         for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
-            const int mt = tile % MT, nb = tile / MT;
+            const int ks = tile % ksplit, t2 = tile / ksplit;
+            const int mt = t2 % MT, nb = t2 / MT;
             const int n0 = nb * BN;
             const int buf = it & 1;
+            // split-K: every CTA of a tile writes f32 into its own slab, summed afterwards
+            const bool f32mode = out_f32 || ksplit > 1;
+            float* fbase = ksplit > 1 ? slabs + (size_t)ks * M * N : reinterpret_cast<float*>(y);
             mbar_wait(accf(buf), (uint32_t)(it >> 1) & 1u, status, TC_ERR_ACC_FULL);
             tc_fence_after();
 #pragma unroll 1
@@ -246,9 +259,9 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
                     tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)buf * kAccCols + (uint32_t)(h * BN + c * 32), r);
                     tmem_ld_wait();
                     const int nc = n0 + c * 32;
-                    if (m < M && nc < N && out_f32) {
-                        // unrounded f32 partials (row-parallel layers: summed over ranks before the rounding)
-                        float* frow = reinterpret_cast<float*>(y) + (size_t)m * N + nc;
+                    if (m < M && nc < N && f32mode) {
+                        // unrounded f32 (row-parallel partials, or a split-K slab)
+                        float* frow = fbase + (size_t)m * N + nc;
                         const bool v4 = (N % 4) == 0 && nc + 32 <= N;
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
@@ -313,23 +326,38 @@ static PFN_encodeTiled get_encode_fn() {
     return fn;
 }
 
+static int affine_gemm_tm(int M, int N, int K, int sms) {
+    // 256-token tiles reuse every dequantised weight tile twice; below 129 tokens they would be half
+    // empty, and they need enough tiles to fill the machine.
+    const AffineGeom g = affine_geom(N, K);
+    const int tiles2 = scr_ceil_div(M, 256) * (g.RB * 16 / A4G_BN);
+    return (M > 128 && tiles2 >= sms / 2) ? 2 : 1;
+}
+static int affine_gemm_ksplit(int M, int N, int K, int sms) {
+    const AffineGeom g = affine_geom(N, K);
+    const int tm = affine_gemm_tm(M, N, K, sms);
+    return tc_pick_ksplit(scr_ceil_div(M, 128 * tm) * (g.RB * 16 / A4G_BN), g.KC, sms);
+}
+
 template <int TM>
 static int32_t affine_gemm_launch_tm(scr_ctx* ctx, const CUtensorMap& map, const uint8_t* packed, uint16_t* y, int M, int N,
-                                     int K, cudaStream_t stream) {
+                                     int K, int ksplit, float* slabs, cudaStream_t stream) {
     const AffineGeom g = affine_geom(N, K);
     const int MT = scr_ceil_div(M, 128 * TM);
-    const int tiles = MT * (g.RB * 16 / A4G_BN);
+    const int tiles = MT * (g.RB * 16 / A4G_BN) * ksplit;
     const int grid = std::min(tiles, ctx->sm_count);
     cudaError_t e = cudaFuncSetAttribute(affine_b4_gemm_tc_kernel<TM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)A4GSmem<TM>::kTotal);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine gemm smem attribute: %s", cudaGetErrorString(e));
     affine_b4_gemm_tc_kernel<TM><<<grid, A4G_THREADS, A4GSmem<TM>::kTotal, stream>>>(map, packed, y, M, N, g.RB, g.KC, MT,
-                                                                                    ctx->out_f32, ctx->dev_status);
-    return scr_check_launch(ctx, "affine_b4_gemm_tc");
+                                                                                    ctx->out_f32, ksplit, slabs, ctx->dev_status);
+    int32_t st = scr_check_launch(ctx, "affine_b4_gemm_tc");
+    if (st || ksplit == 1) return st;
+    return tc_splitk_finish(ctx, slabs, ksplit, (long long)M * N, y, stream);
 }
 
 int32_t affine_b4_gemm_tc_launch(scr_ctx* ctx, const uint8_t* packed, const uint16_t* x, uint16_t* y, int M, int N, int K,
-                                 void*, size_t, cudaStream_t stream) {
+                                 void* workspace, size_t, cudaStream_t stream) {
     if (((uintptr_t)packed & 127u) != 0) return scr_fail(ctx, SCR_E_ALIGN, "packed weights must be 128-byte aligned for the GEMM path");
     if (!scr_aligned16(y)) return scr_fail(ctx, SCR_E_ALIGN, "y must be 16-byte aligned");
     PFN_encodeTiled enc = get_encode_fn();
@@ -342,10 +370,10 @@ int32_t affine_b4_gemm_tc_launch(scr_ctx* ctx, const uint8_t* packed, const uint
     CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)x, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return scr_fail(ctx, SCR_E_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
-    // 256-token tiles reuse every dequantised weight tile twice; below 129 tokens they would be half empty.
-    // They also need enough tiles to fill the machine.
-    const AffineGeom g = affine_geom(N, K);
-    const int tiles2 = scr_ceil_div(M, 256) * (g.RB * 16 / A4G_BN);
-    if (M > 128 && tiles2 >= ctx->sm_count / 2) return affine_gemm_launch_tm<2>(ctx, map, packed, y, M, N, K, stream);
-    return affine_gemm_launch_tm<1>(ctx, map, packed, y, M, N, K, stream);
+    const int ksplit = affine_gemm_ksplit(M, N, K, ctx->sm_count);
+    float* slabs = reinterpret_cast<float*>(workspace);
+    if (ksplit > 1 && (!slabs || !scr_aligned16(slabs))) return scr_fail(ctx, SCR_E_WORKSPACE, "split-K needs an aligned workspace");
+    if (affine_gemm_tm(M, N, K, ctx->sm_count) == 2)
+        return affine_gemm_launch_tm<2>(ctx, map, packed, y, M, N, K, ksplit, slabs, stream);
+    return affine_gemm_launch_tm<1>(ctx, map, packed, y, M, N, K, ksplit, slabs, stream);
 }

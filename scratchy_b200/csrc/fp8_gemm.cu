@@ -17,7 +17,20 @@
 #include "tc_common.cuh"
 
 bool fp8_gemm_tc_enabled() { return true; }
-size_t fp8_gemm_tc_workspace(int, int, int) { return 0; }
+static int fp8_gemm_bn(int M, int N, int K, int sms) {
+    // wide channel tiles when there are enough of them to fill the machine, narrow otherwise
+    const Fp8Geom g = fp8_geom(N, K);
+    return (scr_ceil_div(M, 128) * scr_ceil_div(g.NT, 2) >= sms) ? 256 : 128;
+}
+static int fp8_gemm_ksplit(int M, int N, int K, int sms) {
+    const Fp8Geom g = fp8_geom(N, K);
+    const int bn = fp8_gemm_bn(M, N, K, sms);
+    return tc_pick_ksplit(scr_ceil_div(M, 128) * ((g.NT * 128 + bn - 1) / bn), g.KT, sms);
+}
+size_t fp8_gemm_tc_workspace(int M, int N, int K) {
+    const int ks = fp8_gemm_ksplit(M, N, K, tc_sm_count());
+    return ks > 1 ? (size_t)ks * M * N * sizeof(float) : 0;
+}
 
 #define F8G_STAGES 4
 #define F8G_THREADS 192
@@ -33,7 +46,7 @@ template <int BN>
 __global__ void __launch_bounds__(F8G_THREADS, 1)
 fp8_gemm_tc_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_scale, const uint8_t* __restrict__ xq,
                    const float* __restrict__ a_scale, uint16_t* __restrict__ y, int M, int N, int KT, int NT, int MT,
-                   int M_pad, int out_f32, int* __restrict__ status) {
+                   int M_pad, int out_f32, int ksplit, float* __restrict__ slabs, int* __restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -47,7 +60,8 @@ fp8_gemm_tc_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ 
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int NTB = (NT * 128 + BN - 1) / BN;            // channel tiles of BN
-    const int tiles = MT * NTB;
+    const int tiles = MT * NTB * ksplit;                 // ksplit CTAs share a tile's k extent
+    const int kt_per = (KT + ksplit - 1) / ksplit;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < F8G_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -69,10 +83,12 @@ fp8_gemm_tc_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ 
             int s = 0;
             uint32_t ph = 0;
             for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
-                const int mt = tile % MT, nb = tile / MT;
+                const int ks = tile % ksplit, t2 = tile / ksplit;
+                const int mt = t2 % MT, nb = t2 / MT;
                 const int nt0 = nb * (BN / 128);
                 const int ntn = min(BN / 128, NT - nt0);                  // 128-row weight tiles in this channel tile
-                for (int kt = 0; kt < KT; ++kt) {
+                const int kt_lo = ks * kt_per, kt_hi = min(KT, kt_lo + kt_per);
+                for (int kt = kt_lo; kt < kt_hi; ++kt) {
                     mbar_wait(empty_bar(s), ph ^ 1u, status, TC_ERR_EMPTY_WAIT);
                     const uint32_t sa = smem_base + s * F8GSmem<BN>::kStageBytes;
                     const uint32_t sb = sa + 16384u;
@@ -91,15 +107,16 @@ fp8_gemm_tc_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ 
             uint32_t ph = 0;
             int it = 0;
             for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
-                const int nb = tile / MT;
+                const int nb = (tile / ksplit) / MT;
                 const int nt0 = nb * (BN / 128);
                 const int ntn = min(BN / 128, NT - nt0);
+                const int kt_lo = (tile % ksplit) * kt_per, kt_hi = min(KT, kt_lo + kt_per);
                 const uint32_t idesc = umma_idesc(0, 0, 128, 128u * ntn);
                 const int buf = it & 1;
                 mbar_wait(acce_bar(buf), ((uint32_t)(it >> 1) & 1u) ^ 1u, status, TC_ERR_ACC_EMPTY);
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
-                for (int kt = 0; kt < KT; ++kt) {
+                for (int kt = kt_lo; kt < kt_hi; ++kt) {
                     mbar_wait(full_bar(s), ph, status, TC_ERR_FULL_WAIT);
                     tc_fence_after();
                     const uint32_t sa = smem_base + s * F8GSmem<BN>::kStageBytes;
@@ -107,7 +124,7 @@ fp8_gemm_tc_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ 
                     const uint64_t bdesc = umma_desc_k_sw128(sa + 16384u);
 #pragma unroll
                     for (int k4 = 0; k4 < 4; ++k4)
-                        umma_f8f6f4(d_tmem, adesc + (uint64_t)(2 * k4), bdesc + (uint64_t)(2 * k4), idesc, (kt | k4) != 0);
+                        umma_f8f6f4(d_tmem, adesc + (uint64_t)(2 * k4), bdesc + (uint64_t)(2 * k4), idesc, ((kt - kt_lo) | k4) != 0);
                     umma_commit(empty_bar(s));
                     if (++s == F8G_STAGES) { s = 0; ph ^= 1u; }
                 }
@@ -120,10 +137,14 @@ fp8_gemm_tc_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ 
         const bool vec_ok = (N % 8) == 0;
         int it = 0;
         for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
-            const int mt = tile % MT, nb = tile / MT;
+            const int ks = tile % ksplit, t2 = tile / ksplit;
+            const int mt = t2 % MT, nb = t2 / MT;
             const int n0 = nb * BN;
             const int bn_cur = min(BN, NT * 128 - n0);
             const int buf = it & 1;
+            // split-K: every CTA of a tile writes f32 into its own slab, summed afterwards
+            const bool f32mode = out_f32 || ksplit > 1;
+            float* fbase = ksplit > 1 ? slabs + (size_t)ks * M * N : reinterpret_cast<float*>(y);
             mbar_wait(accf_bar(buf), (uint32_t)(it >> 1) & 1u, status, TC_ERR_ACC_FULL);
             tc_fence_after();
             const int m = mt * 128 + q * 32 + lane;
@@ -134,9 +155,9 @@ fp8_gemm_tc_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ 
                 tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + c * 32), r);
                 tmem_ld_wait();
                 const int nc = n0 + c * 32;
-                if (m < M && nc < N && out_f32) {
-                    // unrounded f32 partials (row-parallel layers: summed over ranks before the rounding)
-                    float* frow = reinterpret_cast<float*>(y) + (size_t)m * N + nc;
+                if (m < M && nc < N && f32mode) {
+                    // unrounded f32 (row-parallel partials, or a split-K slab)
+                    float* frow = fbase + (size_t)m * N + nc;
                     const bool v4 = (N % 4) == 0 && nc + 32 <= N;
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
@@ -195,32 +216,33 @@ fp8_gemm_tc_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ 
 
 template <int BN>
 static int32_t fp8_gemm_launch_bn(scr_ctx* ctx, const uint8_t* wpack, const uint8_t* act, uint16_t* y, int M, int N, int K,
-                                  cudaStream_t stream) {
+                                  int ksplit, float* slabs, cudaStream_t stream) {
     const Fp8Geom g = fp8_geom(N, K);
     const float* w_scale = reinterpret_cast<const float*>(wpack + (size_t)g.NT * g.KT * FP8_TILE_BYTES);
     const float* a_scale = reinterpret_cast<const float*>(act);
     const uint8_t* xq = act + fp8_act_scale_bytes(M);
     const int MT = scr_ceil_div(M, 128);
     const int NTB = (g.NT * 128 + BN - 1) / BN;
-    const int tiles = MT * NTB;
+    const int tiles = MT * NTB * ksplit;
     const int grid = std::min(tiles, ctx->sm_count);
     cudaError_t e = cudaFuncSetAttribute(fp8_gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)F8GSmem<BN>::kTotal);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "fp8_gemm smem attribute: %s", cudaGetErrorString(e));
     fp8_gemm_tc_kernel<BN><<<grid, F8G_THREADS, F8GSmem<BN>::kTotal, stream>>>(wpack, w_scale, xq, a_scale, y, M, N, g.KT,
-                                                                              g.NT, MT, MT * 128, ctx->out_f32, ctx->dev_status);
-    return scr_check_launch(ctx, "fp8_gemm_tc");
+                                                                              g.NT, MT, MT * 128, ctx->out_f32, ksplit, slabs, ctx->dev_status);
+    int32_t st = scr_check_launch(ctx, "fp8_gemm_tc");
+    if (st || ksplit == 1) return st;
+    return tc_splitk_finish(ctx, slabs, ksplit, (long long)M * N, y, stream);
 }
 
-int32_t fp8_gemm_tc_launch(scr_ctx* ctx, const uint8_t* wpack, const uint8_t* act, uint16_t* y, int M, int N, int K, void*,
-                           size_t, cudaStream_t stream) {
+int32_t fp8_gemm_tc_launch(scr_ctx* ctx, const uint8_t* wpack, const uint8_t* act, uint16_t* y, int M, int N, int K,
+                           void* workspace, size_t, cudaStream_t stream) {
     if (((uintptr_t)(act + fp8_act_scale_bytes(M)) & 127u) != 0 || ((uintptr_t)wpack & 127u) != 0)
         return scr_fail(ctx, SCR_E_ALIGN, "weight pack and activation pack must be 128-byte aligned for the GEMM path");
     if (!scr_aligned16(y)) return scr_fail(ctx, SCR_E_ALIGN, "y must be 16-byte aligned");
-    // Wide channel tiles when there are enough of them to fill the machine, narrow otherwise.
-    const Fp8Geom g = fp8_geom(N, K);
-    const int MT = scr_ceil_div(M, 128);
-    const int tiles256 = MT * scr_ceil_div(g.NT, 2);
-    if (tiles256 >= ctx->sm_count) return fp8_gemm_launch_bn<256>(ctx, wpack, act, y, M, N, K, stream);
-    return fp8_gemm_launch_bn<128>(ctx, wpack, act, y, M, N, K, stream);
+    const int ksplit = fp8_gemm_ksplit(M, N, K, ctx->sm_count);
+    float* slabs = reinterpret_cast<float*>(workspace);
+    if (ksplit > 1 && (!slabs || !scr_aligned16(slabs))) return scr_fail(ctx, SCR_E_WORKSPACE, "split-K needs an aligned workspace");
+    if (fp8_gemm_bn(M, N, K, ctx->sm_count) == 256) return fp8_gemm_launch_bn<256>(ctx, wpack, act, y, M, N, K, ksplit, slabs, stream);
+    return fp8_gemm_launch_bn<128>(ctx, wpack, act, y, M, N, K, ksplit, slabs, stream);
 }

@@ -125,6 +125,29 @@ __host__ __device__ __forceinline__ uint32_t umma_idesc(uint32_t a_fmt, uint32_t
     return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | ((N >> 3) << 17) | ((M >> 4) << 24);
 }
 
+// Split-K for launches with too few output tiles to fill the machine: `ksplit` CTAs share a tile's
+// k extent, each writes its f32 partial tile into its own slab [ks][M][N] of the workspace and a
+// finishing kernel sums the slabs in slab order (deterministic) and rounds once.
+static inline int tc_pick_ksplit(int tiles, int k_steps, int sms) {
+    if (tiles * 2 > sms) return 1;
+    int ks = sms / tiles;
+    if (ks > 8) ks = 8;
+    if (ks > k_steps / 4) ks = k_steps / 4;
+    return ks < 1 ? 1 : ks;
+}
+static inline int tc_sm_count() {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0)
+            sms = v;
+        else
+            return 148;        // no device (size queries on a CPU-only host): a B200's count
+    }
+    return sms;
+}
+int32_t tc_splitk_finish(scr_ctx* ctx, const float* slabs, int ksplit, long long count, uint16_t* y, cudaStream_t stream);
+
 __device__ __forceinline__ bool elect_one() {
     uint32_t pred;
     asm volatile(
