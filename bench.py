@@ -330,6 +330,12 @@ def run_gpu(args):
     achieved = step_bytes * args.steps / (ms * 1e-3) / 1e9          # one GPU's kernel stream
 
     extra = {}
+    if world == 1 and not args.no_decode:
+        del layers, graph, graph_e2e
+        layers = graph = graph_e2e = None
+        torch.cuda.empty_cache()
+        extra["decode"] = {"workload": "llama-3.2-3b random-init, all linears int4 g64, bf16 paged KV, one CUDA graph per step",
+                           "cases": run_decode(device)}
     if args.sweep and rank == 0:
         extra["sweep"] = run_sweep(device, ctx)
     if world > 1 or args.sweep:
@@ -437,6 +443,56 @@ def run_sweep(device, ctx):
                         "frac_hbm": fp8_alg_bytes(M, N, K) / dt / 1e9 / peaks["hbm_gbs"],
                         "note": "per-token quantise + contraction (two launches)"})
         del lins
+    return out
+
+
+def run_decode(device, steps=20, batches=(1, 8, 32), context=2048, block_size=16):
+    """BASELINE config 3: random-init Llama-3.2-3B, every linear MLX int4 g64 (lm_head too), one decode
+    step at context `context` with a bf16 paged KV cache, the whole step one CUDA graph.
+    tok/s = batch / step time.  The step streams all packed weights (larger than L2) plus the batch's KV."""
+    import torch
+    from scratchy_b200 import _lib, decode
+    peaks = measured_peaks()
+    cfg = decode.LLAMA_3_2_3B
+    dec = decode.LlamaDecoder(cfg, decode.synthetic_checkpoint_on_device(cfg, device, 0), device, max_pos=context + 64)
+    ctx = _lib.context(device.index)
+    out = []
+    blocks_per_seq = (context + 1 + block_size - 1) // block_size
+    for batch in batches:
+        cache = decode.PagedKvCache(cfg, batch * blocks_per_seq, block_size, device)
+        g = torch.Generator(device=device)
+        g.manual_seed(batch)
+        for t in cache.k + cache.v:
+            t.copy_(torch.randn(t.shape, device=device, generator=g).to(torch.bfloat16))
+        buf = dec.buffers(batch, blocks_per_seq)
+        buf.ids.copy_(torch.randint(0, cfg.vocab, (batch,), device=device, generator=g, dtype=torch.int32))
+        buf.positions.fill_(context)
+        buf.seq_used_k.fill_(context + 1)
+        table = torch.randperm(batch * blocks_per_seq, device=device, generator=g).to(torch.int32)
+        buf.block_table.copy_(table.reshape(batch, blocks_per_seq))
+        buf.slot_mapping.copy_(buf.block_table[:, context // block_size] * block_size + context % block_size)
+        n0 = ctx.launch_count()
+        dec.step(buf, cache)
+        launches = ctx.launch_count() - n0
+        graph = dec.capture(buf, cache)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize(device)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            graph.replay()
+        b.record()
+        torch.cuda.synchronize(device)
+        dt = a.elapsed_time(b) * 1e-3 / steps
+        ctx.device_status(None)
+        kv_bytes = batch * (context + 1) * cfg.n_kv_heads * cfg.head_dim * 2 * 2 * cfg.n_layers
+        moved = dec.weight_bytes() + kv_bytes
+        out.append({"batch": batch, "context": context, "ms_per_step": dt * 1e3, "tok_per_s": batch / dt,
+                    "launches_per_step": int(launches), "weight_bytes": dec.weight_bytes(), "kv_bytes": kv_bytes,
+                    "GBps": moved / dt / 1e9, "frac_hbm": moved / dt / 1e9 / peaks["hbm_gbs"]})
+        del graph, buf, cache
+        torch.cuda.empty_cache()
     return out
 
 
@@ -570,6 +626,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--sweep", action="store_true")
     ap.add_argument("--serial", action="store_true", help="one branch: every linear waits for the previous one")
+    ap.add_argument("--no-decode", action="store_true", help="skip the whole-decode-step section (config 3)")
     ap.add_argument("--case", default=None, help="kind,shape,M e.g. int4,gate,2048: time one linear alone")
     args = ap.parse_args()
     if args.case:

@@ -53,7 +53,9 @@ int64_t scr_launch_count(const scr_ctx* ctx);
  * (crates/serving/engine/src/executor.rs:454): every wait inside the tensor-core kernels is
  * bounded; one that runs out records a code in a device word instead of hanging.  This call
  * synchronises `stream`, reads and clears the word and returns SCR_E_TIMEOUT if it was set
- * (`code` receives the raw value; may be NULL).  Not for the step path. */
+ * (`code` receives the raw value; may be NULL), or SCR_E_ARG if the word holds a device-side
+ * argument check of the decode-step operators (a token id, position, slot or block id out of
+ * range).  Not for the step path. */
 int32_t scr_device_status(scr_ctx* ctx, void* stream, int32_t* code);
 
 /* ---- MLX affine int4, group 64: load-time repack --------------------------
@@ -147,6 +149,57 @@ int32_t scr_linear_fp8_partial(scr_ctx* ctx, const void* packed, const void* act
                                size_t workspace_bytes, void* stream);
 int32_t scr_partial_to_bf16(scr_ctx* ctx, const float* in, int64_t count, uint16_t* out_bf16,
                             void* stream);
+
+/* ---- the operators either side of the linears in one decode step -----------
+ * bf16 activations, f32 arithmetic.  Each replaces the device instruction whose host golden
+ * is the cited function of crates/targets/metal/src/cpu_golden.rs ("Mirrors
+ * `Instruction::<Name>` (CUDA) and Metal `KernelId::<Name>`").  Row strides `ld_*` are in
+ * elements, so q / k / v may be column slices of one fused projection output.  Token ids,
+ * positions, slots and block ids are checked on the device: an out-of-range value records a
+ * code that `scr_device_status` reports as SCR_E_ARG, and the access is skipped. */
+/* `embed` (cpu_golden.rs:114-124): out[i,:] = table[ids[i],:].  hidden % 8 == 0. */
+int32_t scr_embed_bf16(scr_ctx* ctx, const uint32_t* ids, int32_t n_ids, const uint16_t* table,
+                       int32_t vocab, int32_t hidden, uint16_t* out, void* stream);
+/* `rmsnorm` (cpu_golden.rs:25-37) over `rows` rows: out = x * (1/sqrt(mean(x^2)+eps)) * weight. */
+int32_t scr_rmsnorm_bf16(scr_ctx* ctx, const uint16_t* x, const uint16_t* weight, uint16_t* out,
+                         int32_t rows, int32_t hidden, float eps, void* stream);
+/* `fused_add_rmsnorm` (cpu_golden.rs:171-200): residual += delta in place (stored as bf16), out =
+ * rmsnorm(residual as stored).  `out` may be `delta` (the reference writes the norm there). */
+int32_t scr_fused_add_rmsnorm_bf16(scr_ctx* ctx, uint16_t* residual, const uint16_t* delta,
+                                   const uint16_t* weight, uint16_t* out, int32_t rows,
+                                   int32_t hidden, float eps, void* stream);
+/* `fused_gate_up_silu_mul` (cpu_golden.rs:211-219): out[r,i] = gate[r,i]/(1+exp(-gate[r,i])) * up[r,i];
+ * gate and up have row stride ld_in (halves of one fused gate/up output), out is dense [rows, inter]. */
+int32_t scr_silu_mul_bf16(scr_ctx* ctx, const uint16_t* gate, const uint16_t* up, int64_t ld_in,
+                          uint16_t* out, int32_t rows, int32_t inter, void* stream);
+/* `rope_append` (cpu_golden.rs:289-362): NeoX pairing, f32 cos/sin tables [max_pos, head_dim]
+ * (first half of each row read); q_out = rotated q (may be q itself); rotated k and unrotated v
+ * go to global slot slot_mapping[t] of the paged caches [num_blocks, num_kv_heads, block_size,
+ * head_dim] (crates/targets/metal/src/paged_kv_layout.rs:74-115).  The stored bf16 values are
+ * exactly the bf16 roundings of the golden's f32 results. */
+int32_t scr_rope_append_bf16(scr_ctx* ctx, const uint16_t* q, int64_t ld_q, const uint16_t* k,
+                             int64_t ld_k, const uint16_t* v, int64_t ld_v,
+                             const uint32_t* positions, const uint32_t* slot_mapping,
+                             const float* cos_table, const float* sin_table, int32_t max_pos,
+                             uint16_t* q_out, int64_t ld_qo, uint16_t* cache_k, uint16_t* cache_v,
+                             int32_t num_blocks, int32_t num_tokens, int32_t num_q_heads,
+                             int32_t num_kv_heads, int32_t head_dim, int32_t block_size,
+                             void* stream);
+/* `attention_via_cache` (cpu_golden.rs:386-460): one query token per sequence over the paged
+ * cache through block_table [batch, max_blocks_per_seq] and seq_used_k [batch]; softmax with
+ * inv_sum = 1/(sum_exp + 1e-6); seq_used_k == 0 yields zeros.  head_dim 64 or 128, up to 8
+ * query heads per kv head. */
+int32_t scr_attention_via_cache_bf16(scr_ctx* ctx, const uint16_t* q, int64_t ld_q,
+                                     const uint16_t* cache_k, const uint16_t* cache_v,
+                                     int32_t num_blocks, const uint32_t* block_table,
+                                     const uint32_t* seq_used_k, uint16_t* out, int64_t ld_o,
+                                     int32_t batch, int32_t num_q_heads, int32_t num_kv_heads,
+                                     int32_t head_dim, int32_t block_size,
+                                     int32_t max_blocks_per_seq, float attn_scale, void* stream);
+/* Greedy sampling (crates/targets/metal/tests/argmax_split_test.rs:24-33): per row the id of the
+ * largest value, the smallest id among equal ones, NaN never. */
+int32_t scr_argmax_bf16(scr_ctx* ctx, const uint16_t* logits, int64_t ld, int32_t rows,
+                        int32_t width, uint32_t* out, void* stream);
 
 /* No counterpart in the reference.  The same linear as `scr_linear_fp8_dynamic` for callers
  * that cannot allocate device memory on the step path (an arena-owning runtime, code inside a

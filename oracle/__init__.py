@@ -24,8 +24,8 @@ F16, BF16 = 0, 1  # discriminants of the reference's DType (crates/tensors/src/d
 
 def build(force: bool = False) -> str:
     """Compile liboracle.so if it is missing or older than its source."""
-    src = os.path.join(_HERE, "scratchy_oracle.cpp")
-    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+    srcs = [os.path.join(_HERE, f) for f in ("scratchy_oracle.cpp", "decode_oracle.cpp")]
+    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < max(os.path.getmtime(s) for s in srcs):
         subprocess.check_call(["make", "-C", _HERE, "-B", "liboracle.so"], stdout=subprocess.DEVNULL)
     return _SO
 
@@ -47,6 +47,7 @@ def lib() -> ctypes.CDLL:
         L.orc_f32_to_bf16.restype = ctypes.c_uint16
         L.orc_f32_to_bf16.argtypes = [ctypes.c_float]
         L.orc_num_threads.restype = ctypes.c_int
+        L.orc_embed.restype = ctypes.c_int
         _lib = L
     return _lib
 
@@ -192,4 +193,91 @@ def allreduce_rank_order(parts) -> np.ndarray:
     world = parts.shape[0]
     out = np.empty(parts.shape[1:], np.float32)
     lib().orc_allreduce_rank_order(_p(parts), world, ctypes.c_int64(out.size), _p(out))
+    return out
+
+
+# --------------------------------------------------------------------------- decode-step operators
+# f32 in, f32 out, exactly as the reference's host golden (decode_oracle.cpp cites the lines).
+def rmsnorm(x, weight, eps=1e-5) -> np.ndarray:
+    x = _c(x, np.float32)
+    w = _c(weight, np.float32)
+    rows, hidden = x.reshape(-1, w.size).shape
+    out = np.empty_like(x)
+    lib().orc_rmsnorm(_p(x), _p(w), _p(out), ctypes.c_int64(rows), ctypes.c_int64(hidden), ctypes.c_float(eps))
+    return out
+
+
+def fused_add_rmsnorm(residual, delta, weight, eps=1e-5, round_residual_bf16=False):
+    """Returns (residual_after_add, normed); the inputs are not modified."""
+    w = _c(weight, np.float32)
+    res = np.array(residual, dtype=np.float32, order="C", copy=True)
+    dl = np.array(delta, dtype=np.float32, order="C", copy=True)
+    rows, hidden = res.reshape(-1, w.size).shape
+    lib().orc_fused_add_rmsnorm(_p(res), _p(dl), _p(w), ctypes.c_float(eps), ctypes.c_int64(rows),
+                                ctypes.c_int64(hidden), ctypes.c_int(1 if round_residual_bf16 else 0))
+    return res, dl
+
+
+def silu_mul(gate, up) -> np.ndarray:
+    g = _c(gate, np.float32)
+    u = _c(up, np.float32)
+    out = np.empty_like(g)
+    lib().orc_silu_mul(_p(g), _p(u), _p(out), ctypes.c_int64(g.size))
+    return out
+
+
+def embed(ids, table) -> np.ndarray:
+    ids = _c(ids, np.uint32)
+    table = _c(table, np.float32)
+    vocab, hidden = table.shape
+    out = np.empty((ids.size, hidden), np.float32)
+    rc = lib().orc_embed(_p(ids), ctypes.c_int64(ids.size), _p(table), ctypes.c_int64(vocab),
+                         ctypes.c_int64(hidden), _p(out))
+    if rc != 0:
+        raise IndexError("token id outside the embedding table")
+    return out
+
+
+def rope_append(q, k, v, positions, slot_mapping, cos_table, sin_table, cache_k, cache_v, num_q_heads,
+                num_kv_heads, head_dim, block_size):
+    """Returns q_out; cache_k / cache_v (f32, C-contiguous) are updated in place."""
+    q = _c(q, np.float32)
+    k = _c(k, np.float32)
+    v = _c(v, np.float32)
+    pos = _c(positions, np.uint32)
+    slots = _c(slot_mapping, np.uint32)
+    cos = _c(cos_table, np.float32)
+    sin = _c(sin_table, np.float32)
+    assert cache_k.dtype == np.float32 and cache_k.flags.c_contiguous
+    assert cache_v.dtype == np.float32 and cache_v.flags.c_contiguous
+    assert cache_k.size % (num_kv_heads * block_size * head_dim) == 0 and cache_k.size == cache_v.size
+    q_out = np.empty_like(q)
+    lib().orc_rope_append(_p(q), _p(k), _p(v), _p(pos), _p(slots), _p(cos), _p(sin), _p(q_out), _p(cache_k),
+                          _p(cache_v), ctypes.c_int64(pos.size), ctypes.c_int64(num_q_heads),
+                          ctypes.c_int64(num_kv_heads), ctypes.c_int64(head_dim), ctypes.c_int64(block_size))
+    return q_out
+
+
+def attention_via_cache(q, cache_k, cache_v, block_table, seq_used_k, num_q_heads, num_kv_heads, head_dim,
+                        block_size, attn_scale) -> np.ndarray:
+    q = _c(q, np.float32)
+    ck = _c(cache_k, np.float32)
+    cv = _c(cache_v, np.float32)
+    bt = _c(block_table, np.uint32)
+    used = _c(seq_used_k, np.uint32)
+    batch = used.size
+    max_blocks = bt.size // max(batch, 1)
+    out = np.zeros((batch, num_q_heads * head_dim), np.float32)
+    lib().orc_attention_via_cache(_p(q), _p(ck), _p(cv), _p(bt), _p(used), _p(out), ctypes.c_int64(batch),
+                                  ctypes.c_int64(num_q_heads), ctypes.c_int64(num_kv_heads),
+                                  ctypes.c_int64(head_dim), ctypes.c_int64(block_size),
+                                  ctypes.c_int64(max_blocks), ctypes.c_float(attn_scale))
+    return out
+
+
+def argmax(logits) -> np.ndarray:
+    lg = _c(logits, np.float32)
+    rows, width = lg.shape
+    out = np.empty(rows, np.uint32)
+    lib().orc_argmax(_p(lg), ctypes.c_int64(rows), ctypes.c_int64(width), _p(out))
     return out

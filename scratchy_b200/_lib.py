@@ -54,6 +54,15 @@ SIGNATURES = {
     "scr_linear_fp8_partial": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _sz, _vp]),
     "scr_partial_to_bf16": (_i32, [_vp, _vp, _i64, _vp, _vp]),
     "scr_linear_fp8_dynamic_static": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp]),
+    "scr_embed_bf16": (_i32, [_vp, _vp, _i32, _vp, _i32, _i32, _vp, _vp]),
+    "scr_rmsnorm_bf16": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, ctypes.c_float, _vp]),
+    "scr_fused_add_rmsnorm_bf16": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, ctypes.c_float, _vp]),
+    "scr_silu_mul_bf16": (_i32, [_vp, _vp, _vp, _i64, _vp, _i32, _i32, _vp]),
+    "scr_rope_append_bf16": (_i32, [_vp, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _i32, _vp, _i64, _vp, _vp,
+                                    _i32, _i32, _i32, _i32, _i32, _i32, _vp]),
+    "scr_attention_via_cache_bf16": (_i32, [_vp, _vp, _i64, _vp, _vp, _i32, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32,
+                                            _i32, _i32, ctypes.c_float, _vp]),
+    "scr_argmax_bf16": (_i32, [_vp, _vp, _i64, _i32, _i32, _vp, _vp]),
 }
 
 _lib = None

@@ -74,6 +74,9 @@ extern "C" int32_t scr_device_status(scr_ctx* ctx, void* stream, int32_t* code) 
     if (code) *code = host;
     if (host != 0) {
         cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), st);
+        if ((host >> 24) == 0x0E)
+            return scr_fail(ctx, SCR_E_ARG, "a device-side argument check failed (code 0x%08x: %s out of range)", host,
+                            host == 0x0E000001 ? "token id" : host == 0x0E000002 ? "cache slot" : host == 0x0E000003 ? "block id / kv length" : "position");
         return scr_fail(ctx, SCR_E_TIMEOUT, "a bounded device-side wait ran out (code %d)", host);
     }
     return SCR_OK;

@@ -1,0 +1,616 @@
+// The operators either side of the quantized linears in one decode step: embedding gather,
+// RMSNorm (plain and fused with the residual add), SiLU(gate)*up, RoPE + paged-KV append,
+// paged decode attention and greedy argmax.  bf16 activations, f32 arithmetic.
+//
+// All of them are byte movers bounded by HBM / launch latency, not by arithmetic: the kernels
+// are plain vectorised loads and stores.  The attention kernel splits the KV range of one
+// (sequence, kv head) over the 8 CTAs of a thread-block cluster and merges the partial
+// softmax states through distributed shared memory, so it needs no workspace and no second
+// launch.
+//
+// Contracts (paths relative to the reference project's root): crates/targets/metal/src/
+// cpu_golden.rs:25-37 (rmsnorm), :114-124 (embed), :171-200 (fused_add_rmsnorm), :211-219
+// (fused_gate_up_silu_mul), :289-362 (rope_append), :386-460 (attention_via_cache); cache
+// addressing crates/targets/metal/src/paged_kv_layout.rs:74-115; argmax tie rule
+// crates/targets/metal/tests/argmax_split_test.rs:24-33.
+#include "common.cuh"
+
+#include <math.h>
+
+namespace {
+
+// Device-side argument checks record one of these in the context's status word and skip the
+// offending access instead of faulting.
+constexpr int DEV_BAD_TOKEN_ID = 0x0E000001;
+constexpr int DEV_BAD_SLOT = 0x0E000002;
+constexpr int DEV_BAD_BLOCK = 0x0E000003;
+constexpr int DEV_BAD_POSITION = 0x0E000004;
+
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t h) { return __uint_as_float(h << 16); }
+__device__ __forceinline__ uint32_t f32_to_bf16_bits(float f) {
+    const __nv_bfloat16 v = __float2bfloat16_rn(f);
+    return uint32_t(*reinterpret_cast<const uint16_t*>(&v));
+}
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+    f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xFFFF0000u);
+    f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xFFFF0000u);
+    f[4] = __uint_as_float(v.z << 16); f[5] = __uint_as_float(v.z & 0xFFFF0000u);
+    f[6] = __uint_as_float(v.w << 16); f[7] = __uint_as_float(v.w & 0xFFFF0000u);
+}
+__device__ __forceinline__ uint4 pack8(const float* f) {
+    uint4 v;
+    v.x = f32_to_bf16_bits(f[0]) | (f32_to_bf16_bits(f[1]) << 16);
+    v.y = f32_to_bf16_bits(f[2]) | (f32_to_bf16_bits(f[3]) << 16);
+    v.z = f32_to_bf16_bits(f[4]) | (f32_to_bf16_bits(f[5]) << 16);
+    v.w = f32_to_bf16_bits(f[6]) | (f32_to_bf16_bits(f[7]) << 16);
+    return v;
+}
+
+// ------------------------------------------------------------------------------- embed
+__global__ void embed_kernel(const uint32_t* __restrict__ ids, const uint4* __restrict__ table, uint32_t vocab, int hidden_v,
+                             uint4* __restrict__ out, int* status) {
+    const uint32_t id = ids[blockIdx.x];
+    const bool ok = id < vocab;
+    if (!ok && threadIdx.x == 0) atomicCAS(status, 0, DEV_BAD_TOKEN_ID);
+    const uint4* src = table + size_t(ok ? id : 0) * hidden_v;
+    uint4* dst = out + size_t(blockIdx.x) * hidden_v;
+    for (int v = threadIdx.x; v < hidden_v; v += blockDim.x) dst[v] = ok ? src[v] : make_uint4(0, 0, 0, 0);
+}
+
+// ------------------------------------------------------------------------------- rmsnorm
+constexpr int NORM_THREADS = 256;
+
+__device__ __forceinline__ float norm_block_sum(float v, float* red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.0f;
+#pragma unroll
+    for (int w = 0; w < NORM_THREADS / 32; ++w) t += red[w];
+    return t;
+}
+
+// One CTA per row.  ADD: residual <- bf16(residual + delta) in place, and the norm is taken
+// off the stored (rounded) residual; out may alias delta.  !ADD: out = rmsnorm(residual).
+template <bool ADD>
+__global__ void __launch_bounds__(NORM_THREADS) rmsnorm_kernel(uint16_t* __restrict__ residual, const uint16_t* delta,
+                                                               const uint16_t* __restrict__ weight, uint16_t* out, int hidden,
+                                                               float eps) {
+    extern __shared__ float row[];          // hidden floats
+    __shared__ float red[NORM_THREADS / 32];
+    const size_t base = size_t(blockIdx.x) * hidden;
+    const int nv = hidden >> 3;
+    float sum_sq = 0.0f;
+    for (int v = threadIdx.x; v < nv; v += NORM_THREADS) {
+        float f[8];
+        unpack8(*reinterpret_cast<const uint4*>(residual + base + v * 8), f);
+        if (ADD) {
+            float d[8];
+            unpack8(*reinterpret_cast<const uint4*>(delta + base + v * 8), d);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] = bf16_bits_to_f32(f32_to_bf16_bits(__fadd_rn(f[j], d[j])));
+            *reinterpret_cast<uint4*>(residual + base + v * 8) = pack8(f);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            row[v * 8 + j] = f[j];
+            sum_sq = __fadd_rn(sum_sq, __fmul_rn(f[j], f[j]));
+        }
+    }
+    const float total = norm_block_sum(sum_sq, red);
+    const float rms = __fsqrt_rn(__fadd_rn(__fdiv_rn(total, float(hidden)), eps));
+    const float inv_rms = __fdiv_rn(1.0f, rms);
+    for (int v = threadIdx.x; v < nv; v += NORM_THREADS) {
+        float w[8], o[8];
+        unpack8(*reinterpret_cast<const uint4*>(weight + v * 8), w);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = __fmul_rn(__fmul_rn(row[v * 8 + j], inv_rms), w[j]);
+        *reinterpret_cast<uint4*>(out + base + v * 8) = pack8(o);
+    }
+}
+
+// ------------------------------------------------------------------------------- silu(gate) * up
+__global__ void silu_mul_kernel(const uint16_t* __restrict__ gate, const uint16_t* __restrict__ up, long long ld_in,
+                                uint16_t* __restrict__ out, int inter_v, long long total_v) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total_v; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / inter_v;
+        const int v = int(i - r * inter_v);
+        float g[8], u[8], o[8];
+        unpack8(*reinterpret_cast<const uint4*>(gate + r * ld_in + v * 8), g);
+        unpack8(*reinterpret_cast<const uint4*>(up + r * ld_in + v * 8), u);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = __fmul_rn(__fdiv_rn(g[j], __fadd_rn(1.0f, expf(-g[j]))), u[j]);
+        *reinterpret_cast<uint4*>(out + (r * inter_v + v) * 8) = pack8(o);
+    }
+}
+
+// ------------------------------------------------------------------------------- rope + append
+// grid (num_q_heads + num_kv_heads, tokens).  A q-head CTA writes the rotated q; a kv-head
+// CTA writes the rotated k and the unrotated v into the token's cache slot.  Products and
+// the sum/difference are rounded separately (no fused multiply-add), as the contract's f32
+// statement does, so the stored bf16 values are exactly the rounded reference values.
+__global__ void rope_append_kernel(const uint16_t* q, long long ld_q, const uint16_t* __restrict__ k, long long ld_k,
+                                   const uint16_t* __restrict__ v, long long ld_v, const uint32_t* __restrict__ positions,
+                                   const uint32_t* __restrict__ slot_mapping, const float* __restrict__ cos_table,
+                                   const float* __restrict__ sin_table, uint32_t max_pos, uint16_t* q_out,
+                                   long long ld_qo, uint16_t* __restrict__ cache_k, uint16_t* __restrict__ cache_v,
+                                   uint32_t num_blocks, int num_q_heads, int num_kv_heads, int head_dim, int block_size,
+                                   int* status) {
+    const int t = blockIdx.y;
+    const int h = blockIdx.x;
+    const int half = head_dim >> 1;
+    const uint32_t pos = positions[t];
+    if (pos >= max_pos) {
+        if (threadIdx.x == 0) atomicCAS(status, 0, DEV_BAD_POSITION);
+        return;
+    }
+    const float* cos_row = cos_table + size_t(pos) * head_dim;
+    const float* sin_row = sin_table + size_t(pos) * head_dim;
+    if (h < num_q_heads) {
+        const uint16_t* src = q + t * ld_q + h * head_dim;
+        uint16_t* dst = q_out + t * ld_qo + h * head_dim;
+        for (int d = threadIdx.x; d < half; d += blockDim.x) {
+            const float x0 = bf16_bits_to_f32(src[d]), x1 = bf16_bits_to_f32(src[half + d]);
+            const float c = cos_row[d], s = sin_row[d];
+            const float r0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+            const float r1 = __fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, s));
+            dst[d] = uint16_t(f32_to_bf16_bits(r0));
+            dst[half + d] = uint16_t(f32_to_bf16_bits(r1));
+        }
+        return;
+    }
+    const int kh = h - num_q_heads;
+    const uint32_t slot = slot_mapping[t];
+    const uint32_t block = slot / uint32_t(block_size), in_block = slot % uint32_t(block_size);
+    if (block >= num_blocks) {
+        if (threadIdx.x == 0) atomicCAS(status, 0, DEV_BAD_SLOT);
+        return;
+    }
+    const size_t cache_base = ((size_t(block) * num_kv_heads + kh) * block_size + in_block) * head_dim;
+    const uint16_t* ksrc = k + t * ld_k + kh * head_dim;
+    const uint16_t* vsrc = v + t * ld_v + kh * head_dim;
+    for (int d = threadIdx.x; d < half; d += blockDim.x) {
+        const float x0 = bf16_bits_to_f32(ksrc[d]), x1 = bf16_bits_to_f32(ksrc[half + d]);
+        const float c = cos_row[d], s = sin_row[d];
+        const float r0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+        const float r1 = __fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, s));
+        cache_k[cache_base + d] = uint16_t(f32_to_bf16_bits(r0));
+        cache_k[cache_base + half + d] = uint16_t(f32_to_bf16_bits(r1));
+        cache_v[cache_base + d] = vsrc[d];
+        cache_v[cache_base + half + d] = vsrc[half + d];
+    }
+}
+
+// ------------------------------------------------------------------------------- argmax
+// One CTA per row: the largest value, the smallest index among equal ones, NaN never.
+constexpr int ARGMAX_THREADS = 1024;
+
+__device__ __forceinline__ void argmax_take(float v, uint32_t i, float& best, uint32_t& best_i) {
+    if (v > best || (v == best && i < best_i)) {
+        best = v;
+        best_i = i;
+    }
+}
+
+__global__ void __launch_bounds__(ARGMAX_THREADS) argmax_kernel(const uint16_t* __restrict__ logits, long long ld, int width,
+                                                                uint32_t* __restrict__ out) {
+    __shared__ float s_best[ARGMAX_THREADS / 32];
+    __shared__ uint32_t s_idx[ARGMAX_THREADS / 32];
+    const uint16_t* row = logits + blockIdx.x * ld;
+    float best = -INFINITY;
+    uint32_t best_i = 0;
+    const int nv = width >> 3;
+    for (int v = threadIdx.x; v < nv; v += ARGMAX_THREADS) {
+        float f[8];
+        unpack8(*reinterpret_cast<const uint4*>(row + v * 8), f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) argmax_take(f[j], uint32_t(v * 8 + j), best, best_i);
+    }
+    for (int i = (nv << 3) + threadIdx.x; i < width; i += ARGMAX_THREADS)
+        argmax_take(bf16_bits_to_f32(row[i]), uint32_t(i), best, best_i);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const uint32_t oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        argmax_take(ob, oi, best, best_i);
+    }
+    if ((threadIdx.x & 31) == 0) {
+        s_best[threadIdx.x >> 5] = best;
+        s_idx[threadIdx.x >> 5] = best_i;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < ARGMAX_THREADS / 32; ++w) argmax_take(s_best[w], s_idx[w], best, best_i);
+        out[blockIdx.x] = best_i;
+    }
+}
+
+
+// ------------------------------------------------------------------------------- paged decode attention
+// grid (ATT_SPLITS, num_kv_heads, batch), one cluster of ATT_SPLITS CTAs per (sequence, kv
+// head).  CTA `split` streams tokens [split*per, (split+1)*per) of the sequence's KV once and
+// serves all G query heads that share the kv head from the same loads.  LPT = D/8 lanes hold
+// one token's 16-byte pieces; every lane group keeps an online-softmax state (running maximum
+// m, sum l, weighted V sum) per query head.  States are merged lane group -> warp -> CTA ->
+// cluster; CTA 0 of the cluster applies inv_sum = 1 / (l + 1e-6) and stores bf16.
+constexpr int ATT_THREADS = 256;
+constexpr int ATT_WARPS = ATT_THREADS / 32;
+constexpr int ATT_SPLITS = 8;
+constexpr uint32_t ATT_NO_BLOCK = 0xFFFFFFFFu;
+
+__device__ __forceinline__ uint32_t att_cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void att_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Store `v` at the address of `local` inside CTA 0 of the cluster.
+__device__ __forceinline__ void att_store_rank0(float* local, float v) {
+    const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(local));
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(a), "r"(0));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+__device__ __forceinline__ float att_weight(float m, float m_new) { return m == -INFINITY ? 0.0f : expf(m - m_new); }
+
+template <int D, int G>
+__global__ void __launch_bounds__(ATT_THREADS) attention_decode_kernel(
+    const uint16_t* __restrict__ q, long long ld_q, const uint16_t* __restrict__ cache_k, const uint16_t* __restrict__ cache_v,
+    const uint32_t* __restrict__ block_table, const uint32_t* __restrict__ seq_used_k, uint16_t* __restrict__ out, long long ld_o,
+    int num_kv_heads, int block_size, int max_blocks_per_seq, uint32_t num_blocks, int table_cap, float scale, int* status) {
+    constexpr int LPT = D / 8;
+    constexpr int TPW = 32 / LPT;
+    constexpr int STATE = D + 2;                     // acc[D], m, l
+    constexpr int U = G <= 4 ? 4 : 2;                // tokens in flight per lane group
+    extern __shared__ __align__(16) unsigned char att_smem[];
+    float* warp_part = reinterpret_cast<float*>(att_smem);                 // [ATT_WARPS][G][STATE]
+    float* cl_part = warp_part + ATT_WARPS * G * STATE;                    // [ATT_SPLITS][G][STATE], filled on CTA 0
+    uint32_t* blocks = reinterpret_cast<uint32_t*>(cl_part + ATT_SPLITS * G * STATE);
+
+    const int split = int(att_cluster_rank());
+    const int kvh = blockIdx.y, b = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int grp = lane / LPT, l = lane % LPT;
+
+    long long kv_len_raw = seq_used_k[b];
+    const long long kv_cap = (long long)max_blocks_per_seq * block_size;
+    if (kv_len_raw > kv_cap) {
+        if (threadIdx.x == 0) atomicCAS(status, 0, DEV_BAD_BLOCK);
+        kv_len_raw = kv_cap;
+    }
+    const int kv_len = int(kv_len_raw);
+    const int per = (kv_len + ATT_SPLITS - 1) / ATT_SPLITS;
+    const int t_begin = min(split * per, kv_len), t_end = min(t_begin + per, kv_len);
+    const int first_blk = t_begin / block_size;
+    int nblk = t_end > t_begin ? (t_end - 1) / block_size - first_blk + 1 : 0;
+    if (nblk > table_cap) {                          // cannot happen for a consistent launch; never index past the slice
+        if (threadIdx.x == 0) atomicCAS(status, 0, DEV_BAD_BLOCK);
+        nblk = 0;
+    }
+    for (int i = threadIdx.x; i < nblk; i += ATT_THREADS) {
+        uint32_t pb = block_table[size_t(b) * max_blocks_per_seq + first_blk + i];
+        if (pb >= num_blocks) {
+            atomicCAS(status, 0, DEV_BAD_BLOCK);
+            pb = ATT_NO_BLOCK;
+        }
+        blocks[i] = pb;
+    }
+    float qf[G][8];
+#pragma unroll
+    for (int g = 0; g < G; ++g) unpack8(*reinterpret_cast<const uint4*>(q + b * ld_q + (kvh * G + g) * D + l * 8), qf[g]);
+    __syncthreads();
+
+    float m[G], lsum[G], acc[G][8];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        m[g] = -INFINITY;
+        lsum[g] = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[g][j] = 0.0f;
+    }
+    constexpr int PASS = ATT_WARPS * TPW;            // tokens one CTA pass covers
+    const int t_last = nblk > 0 ? t_end : t_begin;
+    for (int base = t_begin; base < t_last; base += PASS * U) {
+        uint4 kk[U], vv[U];
+        bool ok[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int t = base + u * PASS + warp * TPW + grp;
+            ok[u] = t < t_last;
+            kk[u] = make_uint4(0, 0, 0, 0);
+            vv[u] = make_uint4(0, 0, 0, 0);
+            if (ok[u]) {
+                const int lb = t / block_size;
+                const uint32_t pb = blocks[lb - first_blk];
+                ok[u] = pb != ATT_NO_BLOCK;
+                if (ok[u]) {
+                    const size_t off = ((size_t(pb) * num_kv_heads + kvh) * block_size + (t - lb * block_size)) * D + l * 8;
+                    kk[u] = ld_stream_v4(cache_k + off);
+                    vv[u] = ld_stream_v4(cache_v + off);
+                }
+            }
+        }
+        float s[U][G];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            float kf[8];
+            unpack8(kk[u], kf);
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float p = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) p = fmaf(qf[g][j], kf[j], p);
+#pragma unroll
+                for (int o = LPT / 2; o > 0; o >>= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
+                s[u][g] = ok[u] ? p * scale : -INFINITY;
+            }
+        }
+        float vf[U][8];
+#pragma unroll
+        for (int u = 0; u < U; ++u) unpack8(vv[u], vf[u]);
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float mn = m[g];
+#pragma unroll
+            for (int u = 0; u < U; ++u) mn = fmaxf(mn, s[u][g]);
+            if (mn == -INFINITY) continue;
+            const float corr = att_weight(m[g], mn);
+            lsum[g] *= corr;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[g][j] *= corr;
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const float p = ok[u] ? expf(s[u][g] - mn) : 0.0f;
+                lsum[g] += p;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[g][j] = fmaf(p, vf[u][j], acc[g][j]);
+            }
+            m[g] = mn;
+        }
+    }
+
+    // lane groups of a warp -> one state per warp
+#pragma unroll
+    for (int o = LPT; o < 32; o <<= 1) {
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const float mo = __shfl_xor_sync(0xffffffffu, m[g], o);
+            const float lo = __shfl_xor_sync(0xffffffffu, lsum[g], o);
+            const float mn = fmaxf(m[g], mo);
+            const float ca = att_weight(m[g], mn), cb = att_weight(mo, mn);
+            lsum[g] = lsum[g] * ca + lo * cb;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float ao = __shfl_xor_sync(0xffffffffu, acc[g][j], o);
+                acc[g][j] = acc[g][j] * ca + ao * cb;
+            }
+            m[g] = mn;
+        }
+    }
+    if (grp == 0) {
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float* st = warp_part + (warp * G + g) * STATE;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) st[l * 8 + j] = acc[g][j];
+            if (l == 0) {
+                st[D] = m[g];
+                st[D + 1] = lsum[g];
+            }
+        }
+    }
+    __syncthreads();
+    // warps -> CTA, pushed into CTA 0's cluster table
+    for (int idx = threadIdx.x; idx < G * D; idx += ATT_THREADS) {
+        const int g = idx / D, d = idx - g * D;
+        float mt = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; ++w) mt = fmaxf(mt, warp_part[(w * G + g) * STATE + D]);
+        float a = 0.0f, lt = 0.0f;
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; ++w) {
+            const float* st = warp_part + (w * G + g) * STATE;
+            const float c = att_weight(st[D], mt);
+            a += st[d] * c;
+            lt += st[D + 1] * c;
+        }
+        float* dst = cl_part + (split * G + g) * STATE;
+        att_store_rank0(dst + d, a);
+        if (d == 0) {
+            att_store_rank0(dst + D, mt);
+            att_store_rank0(dst + D + 1, lt);
+        }
+    }
+    att_cluster_sync();
+    if (split != 0) return;
+    for (int idx = threadIdx.x; idx < G * D; idx += ATT_THREADS) {
+        const int g = idx / D, d = idx - g * D;
+        float mt = -INFINITY;
+#pragma unroll
+        for (int sp = 0; sp < ATT_SPLITS; ++sp) mt = fmaxf(mt, cl_part[(sp * G + g) * STATE + D]);
+        float a = 0.0f, lt = 0.0f;
+#pragma unroll
+        for (int sp = 0; sp < ATT_SPLITS; ++sp) {
+            const float* st = cl_part + (sp * G + g) * STATE;
+            const float c = att_weight(st[D], mt);
+            a += st[d] * c;
+            lt += st[D + 1] * c;
+        }
+        const float inv_sum = __fdiv_rn(1.0f, lt + 1e-6f);
+        out[b * ld_o + (kvh * G + g) * D + d] = uint16_t(f32_to_bf16_bits(a * inv_sum));
+    }
+}
+
+template <int D, int G>
+cudaError_t attention_launch(const uint16_t* q, long long ld_q, const uint16_t* cache_k, const uint16_t* cache_v,
+                             const uint32_t* block_table, const uint32_t* seq_used_k, uint16_t* out, long long ld_o, int batch,
+                             int num_kv_heads, int block_size, int max_blocks_per_seq, uint32_t num_blocks, float scale,
+                             int* status, cudaStream_t stream) {
+    const int table_cap = max_blocks_per_seq / ATT_SPLITS + 3;
+    const size_t smem = size_t(ATT_WARPS + ATT_SPLITS) * G * (D + 2) * sizeof(float) + size_t(table_cap) * sizeof(uint32_t);
+    auto kernel = attention_decode_kernel<D, G>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess) return e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ATT_SPLITS, num_kv_heads, batch);
+    cfg.blockDim = dim3(ATT_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = ATT_SPLITS;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, q, ld_q, cache_k, cache_v, block_table, seq_used_k, out, ld_o, num_kv_heads,
+                              block_size, max_blocks_per_seq, num_blocks, table_cap, scale, status);
+}
+
+template <int D>
+cudaError_t attention_dispatch_g(int G, const uint16_t* q, long long ld_q, const uint16_t* ck, const uint16_t* cv,
+                                 const uint32_t* bt, const uint32_t* used, uint16_t* out, long long ld_o, int batch, int hkv,
+                                 int bs, int mb, uint32_t nb, float scale, int* status, cudaStream_t st) {
+    switch (G) {
+#define ATT_CASE(GG) case GG: return attention_launch<D, GG>(q, ld_q, ck, cv, bt, used, out, ld_o, batch, hkv, bs, mb, nb, scale, status, st)
+        ATT_CASE(1); ATT_CASE(2); ATT_CASE(3); ATT_CASE(4); ATT_CASE(5); ATT_CASE(6); ATT_CASE(7); ATT_CASE(8);
+#undef ATT_CASE
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace
+
+// =============================================================================== C ABI
+#define DEC_REQUIRE(cond, code, ...) do { if (!(cond)) return scr_fail(ctx, code, __VA_ARGS__); } while (0)
+
+extern "C" int32_t scr_embed_bf16(scr_ctx* ctx, const uint32_t* ids, int32_t n_ids, const uint16_t* table, int32_t vocab,
+                                  int32_t hidden, uint16_t* out, void* stream) {
+    SCR_REQUIRE_CTX(ctx);
+    DEC_REQUIRE(ids && table && out, SCR_E_ARG, "embed: null pointer");
+    DEC_REQUIRE(n_ids >= 0 && vocab > 0 && hidden > 0 && hidden % 8 == 0, SCR_E_SHAPE, "embed: hidden=%d must be a positive multiple of 8", hidden);
+    DEC_REQUIRE(scr_aligned16(table) && scr_aligned16(out), SCR_E_ALIGN, "embed: table/out not 16-byte aligned");
+    if (n_ids == 0) return SCR_OK;
+    embed_kernel<<<n_ids, 128, 0, (cudaStream_t)stream>>>(ids, reinterpret_cast<const uint4*>(table), uint32_t(vocab), hidden / 8,
+                                                          reinterpret_cast<uint4*>(out), ctx->dev_status);
+    return scr_check_launch(ctx, "embed");
+}
+
+static int32_t norm_launch(scr_ctx* ctx, bool add, uint16_t* residual, const uint16_t* delta, const uint16_t* weight,
+                           uint16_t* out, int32_t rows, int32_t hidden, float eps, void* stream) {
+    DEC_REQUIRE(residual && weight && out && (!add || delta), SCR_E_ARG, "rmsnorm: null pointer");
+    DEC_REQUIRE(rows >= 0 && hidden > 0 && hidden % 8 == 0, SCR_E_SHAPE, "rmsnorm: hidden=%d must be a positive multiple of 8", hidden);
+    DEC_REQUIRE(scr_aligned16(residual) && scr_aligned16(weight) && scr_aligned16(out) && (!add || scr_aligned16(delta)),
+                SCR_E_ALIGN, "rmsnorm: pointer not 16-byte aligned");
+    const size_t smem = size_t(hidden) * sizeof(float);
+    DEC_REQUIRE(smem <= 200 * 1024, SCR_E_UNSUPPORTED, "rmsnorm: hidden=%d exceeds the shared-memory row buffer", hidden);
+    if (rows == 0) return SCR_OK;
+    cudaError_t e = cudaSuccess;
+    if (add) {
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(rmsnorm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e == cudaSuccess) rmsnorm_kernel<true><<<rows, NORM_THREADS, smem, (cudaStream_t)stream>>>(residual, delta, weight, out, hidden, eps);
+    } else {
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(rmsnorm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e == cudaSuccess) rmsnorm_kernel<false><<<rows, NORM_THREADS, smem, (cudaStream_t)stream>>>(residual, nullptr, weight, out, hidden, eps);
+    }
+    if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "rmsnorm: %s", cudaGetErrorString(e));
+    return scr_check_launch(ctx, "rmsnorm");
+}
+
+extern "C" int32_t scr_rmsnorm_bf16(scr_ctx* ctx, const uint16_t* x, const uint16_t* weight, uint16_t* out, int32_t rows,
+                                    int32_t hidden, float eps, void* stream) {
+    SCR_REQUIRE_CTX(ctx);
+    return norm_launch(ctx, false, const_cast<uint16_t*>(x), nullptr, weight, out, rows, hidden, eps, stream);
+}
+
+extern "C" int32_t scr_fused_add_rmsnorm_bf16(scr_ctx* ctx, uint16_t* residual, const uint16_t* delta, const uint16_t* weight,
+                                              uint16_t* out, int32_t rows, int32_t hidden, float eps, void* stream) {
+    SCR_REQUIRE_CTX(ctx);
+    return norm_launch(ctx, true, residual, delta, weight, out, rows, hidden, eps, stream);
+}
+
+extern "C" int32_t scr_silu_mul_bf16(scr_ctx* ctx, const uint16_t* gate, const uint16_t* up, int64_t ld_in, uint16_t* out,
+                                     int32_t rows, int32_t inter, void* stream) {
+    SCR_REQUIRE_CTX(ctx);
+    DEC_REQUIRE(gate && up && out, SCR_E_ARG, "silu_mul: null pointer");
+    DEC_REQUIRE(rows >= 0 && inter > 0 && inter % 8 == 0 && ld_in >= inter && ld_in % 8 == 0, SCR_E_SHAPE,
+                "silu_mul: inter=%d and ld_in=%lld must be multiples of 8 with ld_in >= inter", inter, (long long)ld_in);
+    DEC_REQUIRE(scr_aligned16(gate) && scr_aligned16(up) && scr_aligned16(out), SCR_E_ALIGN, "silu_mul: pointer not 16-byte aligned");
+    if (rows == 0) return SCR_OK;
+    const long long total_v = (long long)rows * (inter / 8);
+    const int threads = 256;
+    const int blocks = int(std::min<long long>((total_v + threads - 1) / threads, (long long)ctx->sm_count * 8));
+    silu_mul_kernel<<<blocks, threads, 0, (cudaStream_t)stream>>>(gate, up, (long long)ld_in, out, inter / 8, total_v);
+    return scr_check_launch(ctx, "silu_mul");
+}
+
+extern "C" int32_t scr_rope_append_bf16(scr_ctx* ctx, const uint16_t* q, int64_t ld_q, const uint16_t* k, int64_t ld_k,
+                                        const uint16_t* v, int64_t ld_v, const uint32_t* positions, const uint32_t* slot_mapping,
+                                        const float* cos_table, const float* sin_table, int32_t max_pos, uint16_t* q_out,
+                                        int64_t ld_qo, uint16_t* cache_k, uint16_t* cache_v, int32_t num_blocks,
+                                        int32_t num_tokens, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
+                                        int32_t block_size, void* stream) {
+    SCR_REQUIRE_CTX(ctx);
+    DEC_REQUIRE(q && k && v && positions && slot_mapping && cos_table && sin_table && q_out && cache_k && cache_v, SCR_E_ARG,
+                "rope_append: null pointer");
+    DEC_REQUIRE(num_tokens >= 0 && num_q_heads > 0 && num_kv_heads > 0 && head_dim > 0 && head_dim % 2 == 0 && block_size > 0 &&
+                    num_blocks > 0 && max_pos > 0,
+                SCR_E_SHAPE, "rope_append: bad head / block geometry");
+    DEC_REQUIRE(ld_q >= (int64_t)num_q_heads * head_dim && ld_qo >= (int64_t)num_q_heads * head_dim &&
+                    ld_k >= (int64_t)num_kv_heads * head_dim && ld_v >= (int64_t)num_kv_heads * head_dim,
+                SCR_E_SHAPE, "rope_append: a row stride is shorter than its row");
+    if (num_tokens == 0) return SCR_OK;
+    const int threads = std::min(256, std::max(32, ((head_dim / 2 + 31) / 32) * 32));
+    rope_append_kernel<<<dim3(num_q_heads + num_kv_heads, num_tokens), threads, 0, (cudaStream_t)stream>>>(
+        q, ld_q, k, ld_k, v, ld_v, positions, slot_mapping, cos_table, sin_table, uint32_t(max_pos), q_out, ld_qo, cache_k, cache_v,
+        uint32_t(num_blocks), num_q_heads, num_kv_heads, head_dim, block_size, ctx->dev_status);
+    return scr_check_launch(ctx, "rope_append");
+}
+
+extern "C" int32_t scr_attention_via_cache_bf16(scr_ctx* ctx, const uint16_t* q, int64_t ld_q, const uint16_t* cache_k,
+                                                const uint16_t* cache_v, int32_t num_blocks, const uint32_t* block_table,
+                                                const uint32_t* seq_used_k, uint16_t* out, int64_t ld_o, int32_t batch,
+                                                int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, int32_t block_size,
+                                                int32_t max_blocks_per_seq, float attn_scale, void* stream) {
+    SCR_REQUIRE_CTX(ctx);
+    DEC_REQUIRE(q && cache_k && cache_v && block_table && seq_used_k && out, SCR_E_ARG, "attention: null pointer");
+    DEC_REQUIRE(batch >= 0 && num_q_heads > 0 && num_kv_heads > 0 && num_q_heads % num_kv_heads == 0 && block_size > 0 &&
+                    max_blocks_per_seq > 0 && num_blocks > 0,
+                SCR_E_SHAPE, "attention: bad head / block geometry");
+    const int G = num_q_heads / num_kv_heads;
+    DEC_REQUIRE(head_dim == 64 || head_dim == 128, SCR_E_UNSUPPORTED, "attention: head_dim=%d (64 and 128 are built)", head_dim);
+    DEC_REQUIRE(G <= 8, SCR_E_UNSUPPORTED, "attention: %d query heads per kv head (up to 8 are built)", G);
+    DEC_REQUIRE(batch <= 65535 && num_kv_heads <= 65535, SCR_E_SHAPE, "attention: batch / kv heads exceed the grid limits");
+    DEC_REQUIRE(ld_q >= (int64_t)num_q_heads * head_dim && ld_o >= (int64_t)num_q_heads * head_dim && ld_q % 8 == 0, SCR_E_SHAPE,
+                "attention: a row stride is shorter than its row or not a multiple of 8");
+    DEC_REQUIRE(scr_aligned16(q) && scr_aligned16(cache_k) && scr_aligned16(cache_v), SCR_E_ALIGN,
+                "attention: q / cache not 16-byte aligned");
+    DEC_REQUIRE(max_blocks_per_seq <= (1 << 20), SCR_E_UNSUPPORTED, "attention: block table wider than 2^20 blocks");
+    if (batch == 0) return SCR_OK;
+    cudaError_t e;
+    if (head_dim == 128)
+        e = attention_dispatch_g<128>(G, q, ld_q, cache_k, cache_v, block_table, seq_used_k, out, ld_o, batch, num_kv_heads,
+                                      block_size, max_blocks_per_seq, uint32_t(num_blocks), attn_scale, ctx->dev_status,
+                                      (cudaStream_t)stream);
+    else
+        e = attention_dispatch_g<64>(G, q, ld_q, cache_k, cache_v, block_table, seq_used_k, out, ld_o, batch, num_kv_heads,
+                                     block_size, max_blocks_per_seq, uint32_t(num_blocks), attn_scale, ctx->dev_status,
+                                     (cudaStream_t)stream);
+    if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "attention: %s", cudaGetErrorString(e));
+    return scr_check_launch(ctx, "attention_via_cache");
+}
+
+extern "C" int32_t scr_argmax_bf16(scr_ctx* ctx, const uint16_t* logits, int64_t ld, int32_t rows, int32_t width, uint32_t* out,
+                                   void* stream) {
+    SCR_REQUIRE_CTX(ctx);
+    DEC_REQUIRE(logits && out, SCR_E_ARG, "argmax: null pointer");
+    DEC_REQUIRE(rows >= 0 && width > 0 && ld >= width && ld % 8 == 0, SCR_E_SHAPE,
+                "argmax: width=%d, ld=%lld (ld must be a multiple of 8, at least width)", width, (long long)ld);
+    DEC_REQUIRE(scr_aligned16(logits), SCR_E_ALIGN, "argmax: logits not 16-byte aligned");
+    if (rows == 0) return SCR_OK;
+    argmax_kernel<<<rows, ARGMAX_THREADS, 0, (cudaStream_t)stream>>>(logits, (long long)ld, width, out);
+    return scr_check_launch(ctx, "argmax");
+}

@@ -52,6 +52,12 @@ class GpuWeights:
             raise KeyError(f"tensor `{name}` not found in checkpoint")
         return self._t.pop(name)
 
+    def peek(self, name: str) -> torch.Tensor:
+        """The tensor without removing it (`copy_cpu` in the reference leaves the part in the store)."""
+        if name not in self._t:
+            raise KeyError(f"tensor `{name}` not found in checkpoint")
+        return self._t[name]
+
     def rmsnorm_scale_dtype(self) -> Optional[torch.dtype]:
         return self._scale_dtype
 
@@ -105,6 +111,49 @@ class AffineQuantLinear:
             raise ValueError(f"`{prefix}`: scales/biases must be {want}, got {tuple(scales.shape)} / "
                              f"{tuple(affine_biases.shape)}")
         return cls.from_tensors(weight, scales, affine_biases, group_size, bits, linear_bias, keep_source)
+
+    # ---- MetalAffineQuantOps::load_rows_concat (layers_quant.rs:363-450): fused QKV / gate-up
+    @classmethod
+    def load_rows_concat(cls, weights: GpuWeights, prefixes, group_size: int, bits: int,
+                         expected_in_features: int) -> "AffineQuantLinear":
+        """One projection made of several projections' rows, in order.  A group runs along K, so a
+        row dequantises from its own codes, scale and bias wherever it sits.  A part's linear bias
+        is refused, not dropped; the parts stay in the store."""
+        if not prefixes:
+            raise ValueError("AffineQuantLinear::load_rows_concat: empty prefix list")
+        compiled = weights.rmsnorm_scale_dtype()
+        if compiled is None:
+            raise ValueError(f"`{prefixes[0]}.scales`: no scale dtype pinned")
+        codes, scales, biases = [], [], []
+        widths = None
+        for prefix in prefixes:
+            if weights.contains(f"{prefix}.bias"):
+                raise ValueError(f"affine rows concat: `{prefix}.bias` present — a fused projection carries no bias")
+            w, sc, b = weights.peek(f"{prefix}.weight"), weights.peek(f"{prefix}.scales"), weights.peek(f"{prefix}.biases")
+            if w.dtype not in (torch.int32, torch.uint32) or w.dim() != 2:
+                raise ValueError(f"affine rows concat: `{prefix}.weight` is {w.dtype} {tuple(w.shape)} "
+                                 "(expected U32 rank 2)")
+            for name, t in (("scales", sc), ("biases", b)):
+                if t.dtype != compiled:
+                    raise ValueError(f"`{prefix}.{name}` is {t.dtype} on disk; this build's quantized kernels "
+                                     f"read {compiled}")
+            rows, packed_cols = int(w.shape[0]), int(w.shape[1])
+            in_features = packed_cols * 32 // bits
+            if affine_packed_cols(in_features, bits) != packed_cols or in_features != expected_in_features:
+                raise ValueError(f"affine rows concat: `{prefix}.weight` [{rows}, {packed_cols}] is not a bits={bits} "
+                                 f"packing of in_features={expected_in_features}")
+            groups = in_features // group_size
+            if tuple(sc.shape) != (rows, groups) or tuple(b.shape) != (rows, groups):
+                raise ValueError(f"affine rows concat: `{prefix}` scales {tuple(sc.shape)} / biases "
+                                 f"{tuple(b.shape)} are not [{rows}, {groups}]")
+            if widths is None:
+                widths = (packed_cols, groups)
+            elif widths != (packed_cols, groups):
+                raise ValueError(f"affine rows concat: `{prefix}` row width differs from the first part's")
+            codes.append(w)
+            scales.append(sc)
+            biases.append(b)
+        return cls.from_tensors(torch.cat(codes, 0), torch.cat(scales, 0), torch.cat(biases, 0), group_size, bits)
 
     @classmethod
     def from_tensors(cls, weight: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor, group_size: int = 64,

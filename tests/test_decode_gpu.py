@@ -1,0 +1,305 @@
+"""GPU parity of the decode-step operators and of one whole decode step against the CPU oracle.
+
+Bars: index / byte work (embed, RoPE'd values, cache appends, argmax) bit-exact; floating-point
+operators within relative L2 1e-3 of the oracle's f32 result rounded to bf16; the chained step
+(dozens of bf16 roundings in sequence) within 1e-2 on the logits, with the tolerance stated here.
+"""
+import math
+
+import numpy as np
+import pytest
+
+import oracle
+from scratchy_b200 import synth
+from util import bf16_dev, bf16_to_f32, bits_of, rel_l2, to_dev
+
+pytestmark = pytest.mark.gpu
+REL_L2_TOL = 1e-3
+STEP_REL_L2_TOL = 1e-2
+
+
+def rbits(a):
+    return synth.f32_to_bf16_bits(np.asarray(a, np.float32))
+
+
+def i32_dev(a):
+    import torch
+    return torch.from_numpy(np.ascontiguousarray(a, np.uint32).view(np.int32)).cuda()
+
+
+def test_embed_bit_exact_and_checked():
+    import torch
+    from scratchy_b200 import _lib, decode
+    rng = np.random.default_rng(1)
+    table = rbits(rng.standard_normal((1000, 256)))
+    ids = rng.integers(0, 1000, size=37).astype(np.uint32)
+    out = decode.embed(i32_dev(ids), bf16_dev(table))
+    torch.cuda.synchronize()
+    assert np.array_equal(bits_of(out), table[ids])
+    # an id outside the table: the row is zero-filled and the context reports the check
+    bad = ids.copy()
+    bad[5] = 1000
+    out = decode.embed(i32_dev(bad), bf16_dev(table))
+    with pytest.raises(_lib.ScratchyCudaError) as e:
+        _lib.context(0).device_status(None)
+    assert e.value.status == -1
+    got = bits_of(out)
+    assert np.all(got[5] == 0) and np.array_equal(got[6], table[bad[6]])
+    _lib.context(0).device_status(None)          # cleared
+
+
+@pytest.mark.parametrize("rows,hidden", [(1, 3072), (8, 3072), (32, 8192), (3, 256), (2, 16384)])
+def test_rmsnorm(rows, hidden):
+    import torch
+    from scratchy_b200 import decode
+    rng = np.random.default_rng(synth.seed_for("rmsnorm", rows, hidden))
+    x = rbits(rng.standard_normal((rows, hidden)) * 3.0)
+    w = rbits(1.0 + 0.1 * rng.standard_normal(hidden))
+    out = decode.rmsnorm(bf16_dev(x), bf16_dev(w), 1e-5)
+    torch.cuda.synchronize()
+    want = rbits(oracle.rmsnorm(bf16_to_f32(x), bf16_to_f32(w), 1e-5))
+    assert rel_l2(bits_of(out), want) <= REL_L2_TOL
+    assert np.mean(bits_of(out) == want) > 0.98          # the sum order differs: a few 1-ulp flips at most
+
+
+@pytest.mark.parametrize("rows,hidden", [(1, 3072), (32, 3072), (5, 8192)])
+def test_fused_add_rmsnorm(rows, hidden):
+    import torch
+    from scratchy_b200 import decode
+    rng = np.random.default_rng(synth.seed_for("addnorm", rows, hidden))
+    r = rbits(rng.standard_normal((rows, hidden)))
+    d = rbits(rng.standard_normal((rows, hidden)) * 0.5)
+    w = rbits(1.0 + 0.1 * rng.standard_normal(hidden))
+    res = bf16_dev(r)
+    out = decode.fused_add_rmsnorm(res, bf16_dev(d), bf16_dev(w), 1e-5)
+    torch.cuda.synchronize()
+    want_res, want = oracle.fused_add_rmsnorm(bf16_to_f32(r), bf16_to_f32(d), bf16_to_f32(w), 1e-5,
+                                              round_residual_bf16=True)
+    assert np.array_equal(bits_of(res), rbits(want_res)), "the stored residual is bf16(r + d) exactly"
+    assert rel_l2(bits_of(out), rbits(want)) <= REL_L2_TOL
+    # the norm may be written over delta, as the reference does
+    dl = bf16_dev(d)
+    res2 = bf16_dev(r)
+    decode.fused_add_rmsnorm(res2, dl, bf16_dev(w), 1e-5, out=dl)
+    torch.cuda.synchronize()
+    assert np.array_equal(bits_of(dl), bits_of(out))
+
+
+@pytest.mark.parametrize("rows,inter", [(1, 8192), (32, 8192), (3, 64)])
+def test_silu_mul_on_fused_halves(rows, inter):
+    import torch
+    from scratchy_b200 import decode
+    rng = np.random.default_rng(synth.seed_for("silu", rows, inter))
+    gu = rbits(rng.standard_normal((rows, 2 * inter)) * 2.0)
+    t = bf16_dev(gu)
+    out = decode.silu_mul(t[:, :inter], t[:, inter:])
+    torch.cuda.synchronize()
+    want = rbits(oracle.silu_mul(bf16_to_f32(gu[:, :inter]), bf16_to_f32(gu[:, inter:])))
+    assert rel_l2(bits_of(out), want) <= REL_L2_TOL
+    assert np.mean(bits_of(out) == want) > 0.99
+
+
+def test_silu_mul_reference_signs():
+    """crates/targets/metal/src/cpu_golden.rs:1198-1209, on the device (8 columns: the vector width)."""
+    import torch
+    from scratchy_b200 import decode
+    g = rbits(np.array([[0.0, 1.0, -1.0, 0, 0, 0, 0, 0]]))
+    u = rbits(np.array([[5.0, 2.0, -1.0, 0, 0, 0, 0, 0]]))
+    out = bf16_to_f32(bits_of(decode.silu_mul(bf16_dev(g), bf16_dev(u))))
+    torch.cuda.synchronize()
+    assert abs(out[0, 0]) < 1e-5 and abs(out[0, 1] - 1.4621172) < 1e-2 and abs(out[0, 2] - 0.26894143) < 2e-3
+
+
+def _rope_case(tokens, hq, hkv, d, bs, nblk, seed):
+    rng = np.random.default_rng(seed)
+    qkv = rbits(rng.standard_normal((tokens, (hq + 2 * hkv) * d)))
+    cos, sin = (rng.uniform(-1, 1, size=(64, d)).astype(np.float32) for _ in range(2))
+    pos = rng.integers(0, 64, size=tokens).astype(np.uint32)
+    slots = rng.permutation(nblk * bs)[:tokens].astype(np.uint32)
+    ck = rbits(rng.standard_normal((nblk, hkv, bs, d)))
+    cv = rbits(rng.standard_normal((nblk, hkv, bs, d)))
+    return qkv, cos, sin, pos, slots, ck, cv
+
+
+@pytest.mark.parametrize("tokens,hq,hkv,d,bs,nblk", [(1, 24, 8, 128, 16, 9), (32, 24, 8, 128, 16, 40), (5, 4, 2, 64, 4, 7),
+                                                    (3, 2, 1, 8, 2, 5)])
+def test_rope_append_bit_exact(tokens, hq, hkv, d, bs, nblk):
+    import torch
+    from scratchy_b200 import decode
+    qkv, cos, sin, pos, slots, ck, cv = _rope_case(tokens, hq, hkv, d, bs, nblk, synth.seed_for("rope", tokens, hq, d))
+    qd, kd = hq * d, hkv * d
+    t = bf16_dev(qkv)
+    dk, dv = bf16_dev(ck), bf16_dev(cv)
+    decode.rope_append(t[:, :qd], t[:, qd:qd + kd], t[:, qd + kd:], i32_dev(pos), i32_dev(slots), to_dev(cos), to_dev(sin),
+                       dk, dv, hq, hkv, d, bs)
+    torch.cuda.synchronize()
+    f = bf16_to_f32(qkv)
+    ok, ov = bf16_to_f32(ck).copy(), bf16_to_f32(cv).copy()
+    q_want = oracle.rope_append(f[:, :qd], f[:, qd:qd + kd], f[:, qd + kd:], pos, slots, cos, sin, ok, ov, hq, hkv, d, bs)
+    got = bits_of(t)
+    assert np.array_equal(got[:, :qd], rbits(q_want)), "rotated q must equal the rounded reference value"
+    assert np.array_equal(got[:, qd:], qkv[:, qd:]), "k and v inputs are not modified"
+    assert np.array_equal(bits_of(dk), rbits(ok)) and np.array_equal(bits_of(dv), rbits(ov))
+
+
+def _attention_case(lens, hq, hkv, d, bs, seed, scale=None):
+    import torch
+    from scratchy_b200 import decode
+    rng = np.random.default_rng(seed)
+    batch = len(lens)
+    max_blocks = max(1, max((n + bs - 1) // bs for n in lens)) + 1
+    nblk = batch * max_blocks + 3
+    table = rng.permutation(nblk)[:batch * max_blocks].reshape(batch, max_blocks).astype(np.uint32)
+    ck = rbits(rng.standard_normal((nblk, hkv, bs, d)))
+    cv = rbits(rng.standard_normal((nblk, hkv, bs, d)))
+    q = rbits(rng.standard_normal((batch, hq * d)))
+    scale = 1.0 / math.sqrt(d) if scale is None else scale
+    out = decode.attention_via_cache(bf16_dev(q), bf16_dev(ck), bf16_dev(cv), i32_dev(table), i32_dev(np.array(lens)),
+                                     hq, hkv, d, bs, scale)
+    torch.cuda.synchronize()
+    want = oracle.attention_via_cache(bf16_to_f32(q), bf16_to_f32(ck), bf16_to_f32(cv), table, np.array(lens, np.uint32),
+                                      hq, hkv, d, bs, np.float32(scale))
+    return bits_of(out), rbits(want)
+
+
+@pytest.mark.parametrize("lens,hq,hkv,d,bs", [
+    ([2049], 24, 8, 128, 16),                 # Llama-3.2-3B geometry at context 2048 + the new token
+    ([2049, 77, 1, 300, 16, 17, 128, 640], 24, 8, 128, 16),
+    ([1, 7, 8, 9], 8, 8, 64, 4),              # one query head per kv head, fewer tokens than splits
+    ([513, 31], 8, 1, 128, 16),               # 8 query heads on one kv head
+    ([200, 95], 28, 4, 128, 32),              # 7 query heads per kv head
+    ([100], 4, 2, 64, 1),                     # block_size 1
+])
+def test_attention_via_cache(lens, hq, hkv, d, bs):
+    got, want = _attention_case(lens, hq, hkv, d, bs, synth.seed_for("attn", len(lens), hq, hkv, d, bs))
+    assert rel_l2(got, want) <= REL_L2_TOL
+
+
+def test_attention_zero_kv_len_is_zero():
+    """crates/targets/metal/src/cpu_golden.rs:1410-1435: seq_used_k = 0 leaves zeros."""
+    got, want = _attention_case([0, 5], 4, 2, 64, 4, 3)
+    assert np.all(bf16_to_f32(got[0]) == 0.0)
+    assert rel_l2(got[1], want[1]) <= REL_L2_TOL
+
+
+def test_attention_sharp_softmax():
+    """A large scale makes the softmax nearly one-hot: the running-maximum merge must not lose it."""
+    got, want = _attention_case([777, 1500], 24, 8, 128, 16, 5, scale=4.0)
+    assert rel_l2(got, want) <= REL_L2_TOL
+
+
+def test_argmax_bit_exact():
+    import torch
+    from scratchy_b200 import decode
+    rng = np.random.default_rng(9)
+    width = 128256
+    lg = rbits(rng.standard_normal((6, width)))
+    f = bf16_to_f32(lg).copy()
+    f[1, 777] = f[1, 90000] = 50.0            # equal maxima: the smaller id wins
+    f[2, :] = np.nan                          # NaN never wins: id 0
+    f[3, 5] = np.nan
+    f[3, 128255] = 60.0                       # the last element
+    f[4, :] = -np.inf
+    lg = rbits(f)
+    out = decode.argmax(bf16_dev(lg))
+    torch.cuda.synchronize()
+    want = oracle.argmax(bf16_to_f32(lg))
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), want)
+    assert want[1] == 777 and want[2] == 0 and want[3] == 128255 and want[4] == 0
+    # a ragged width (not a multiple of the vector width) behind a padded row stride
+    pad = bf16_dev(rbits(rng.standard_normal((3, 1008))))
+    got = decode.argmax(pad[:, :1003]).cpu().numpy().view(np.uint32)
+    assert np.array_equal(got, oracle.argmax(bf16_to_f32(bits_of(pad))[:, :1003]))
+
+
+# ------------------------------------------------------------------------------------ whole step
+def _oracle_linear(ck, prefixes, x_bits, k):
+    w = np.concatenate([ck[f"{p}.weight"] for p in prefixes], 0)
+    s = np.concatenate([ck[f"{p}.scales"] for p in prefixes], 0)
+    b = np.concatenate([ck[f"{p}.biases"] for p in prefixes], 0)
+    return oracle.affine_qmm_t_b4(w.view(np.uint8).reshape(-1), s, b, x_bits, x_bits.shape[0], w.shape[0], k, 64)
+
+
+def _oracle_step(cfg, ck, ids, pos, slots, table, used, cache_k, cache_v, cos, sin, bs):
+    """The step as a chain of oracle operators, rounding to bf16 wherever the device stores bf16."""
+    f, r = bf16_to_f32, rbits
+    qd, kd = cfg.q_dim, cfg.kv_dim
+    residual = ck["model.embed_tokens.weight"][ids]                       # bf16 bits
+    normed = r(oracle.rmsnorm(f(residual), f(ck["model.layers.0.input_layernorm.weight"]), cfg.rms_eps))
+    for i in range(cfg.n_layers):
+        root = f"model.layers.{i}"
+        qkv = _oracle_linear(ck, [f"{root}.self_attn.{p}_proj" for p in "qkv"], normed, cfg.hidden)
+        fq = f(qkv)
+        q_rot = oracle.rope_append(fq[:, :qd], fq[:, qd:qd + kd], fq[:, qd + kd:], pos, slots, cos, sin, cache_k[i],
+                                   cache_v[i], cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, bs)
+        cache_k[i][...] = f(r(cache_k[i]))                                 # the device cache holds bf16
+        attn = r(oracle.attention_via_cache(f(r(q_rot)), cache_k[i], cache_v[i], table, used, cfg.n_q_heads,
+                                            cfg.n_kv_heads, cfg.head_dim, bs, np.float32(1.0 / math.sqrt(cfg.head_dim))))
+        delta = _oracle_linear(ck, [f"{root}.self_attn.o_proj"], attn, qd)
+        res, nrm = oracle.fused_add_rmsnorm(f(residual), f(delta), f(ck[f"{root}.post_attention_layernorm.weight"]),
+                                            cfg.rms_eps, round_residual_bf16=True)
+        residual, normed = r(res), r(nrm)
+        gu = f(_oracle_linear(ck, [f"{root}.mlp.gate_proj", f"{root}.mlp.up_proj"], normed, cfg.hidden))
+        act = r(oracle.silu_mul(gu[:, :cfg.intermediate], gu[:, cfg.intermediate:]))
+        delta = _oracle_linear(ck, [f"{root}.mlp.down_proj"], act, cfg.intermediate)
+        nxt = ck[f"model.layers.{i + 1}.input_layernorm.weight"] if i + 1 < cfg.n_layers else ck["model.norm.weight"]
+        res, nrm = oracle.fused_add_rmsnorm(f(residual), f(delta), f(nxt), cfg.rms_eps, round_residual_bf16=True)
+        residual, normed = r(res), r(nrm)
+    return _oracle_linear(ck, ["lm_head"], normed, cfg.hidden)
+
+
+@pytest.mark.parametrize("batch", [1, 3, 20])
+def test_decode_step_matches_oracle_chain(batch):
+    """Two consecutive steps of a small random-init decoder (eager, then the same step replayed from a
+    CUDA graph) against the oracle chain; batch 20 takes the tensor-core linear path."""
+    import torch
+    from scratchy_b200 import decode
+    cfg = decode.LlamaConfig(hidden=256, n_layers=2, n_q_heads=4, n_kv_heads=2, head_dim=64, intermediate=512,
+                             vocab=1024, rope_theta=10000.0)
+    ck = decode.synthetic_checkpoint(cfg, seed=batch)
+    dec = decode.LlamaDecoder(cfg, ck, "cuda:0", max_pos=128)
+    bs, max_blocks = 4, 8
+    nblk = batch * max_blocks
+    cache = decode.PagedKvCache(cfg, nblk, bs, "cuda:0")
+    rng = np.random.default_rng(batch)
+    ctx_len = rng.integers(3, 20, size=batch)
+    table = rng.permutation(nblk).reshape(batch, max_blocks).astype(np.uint32)
+    # pre-fill the caches with random history
+    hist_k = [rbits(rng.standard_normal((nblk, cfg.n_kv_heads, bs, cfg.head_dim))) for _ in range(cfg.n_layers)]
+    hist_v = [rbits(rng.standard_normal((nblk, cfg.n_kv_heads, bs, cfg.head_dim))) for _ in range(cfg.n_layers)]
+    for i in range(cfg.n_layers):
+        cache.k[i].copy_(bf16_dev(hist_k[i]))
+        cache.v[i].copy_(bf16_dev(hist_v[i]))
+    ok = [bf16_to_f32(a).copy() for a in hist_k]
+    ov = [bf16_to_f32(a).copy() for a in hist_v]
+    cos, sin = decode.rope_tables(128, cfg.head_dim, cfg.rope_theta)
+    buf = dec.buffers(batch, max_blocks)
+    buf.block_table.copy_(i32_dev(table))
+    ids = rng.integers(0, cfg.vocab, size=batch).astype(np.uint32)
+    graph = None
+    for step in range(2):
+        pos = (ctx_len + step).astype(np.uint32)
+        slots = np.array([table[b, pos[b] // bs] * bs + pos[b] % bs for b in range(batch)], np.uint32)
+        used = (pos + 1).astype(np.uint32)
+        buf.ids.copy_(i32_dev(ids))
+        buf.positions.copy_(i32_dev(pos))
+        buf.slot_mapping.copy_(i32_dev(slots))
+        buf.seq_used_k.copy_(i32_dev(used))
+        if step == 0:
+            dec.step(buf, cache)
+        else:
+            # capture warms the step once more on the same inputs: appends are idempotent for fixed slots
+            graph = dec.capture(buf, cache)
+            graph.replay()
+        torch.cuda.synchronize()
+        want = _oracle_step(cfg, ck, ids, pos, slots, table, used, ok, ov, cos, sin, bs)
+        got = bits_of(buf.logits)
+        err = rel_l2(got, want)
+        assert err <= STEP_REL_L2_TOL, f"step {step}: logits rel-L2 {err:.3e}"
+        for i in range(cfg.n_layers):
+            assert rel_l2(bits_of(cache.v[i]), rbits(ov[i])) <= STEP_REL_L2_TOL
+        want_ids = oracle.argmax(bf16_to_f32(got))
+        assert np.array_equal(buf.next_ids.cpu().numpy().view(np.uint32), want_ids), "argmax of the device logits"
+        ids = want_ids.astype(np.uint32)
+    from scratchy_b200 import _lib
+    _lib.context(0).device_status(None)
