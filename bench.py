@@ -590,6 +590,8 @@ def run_case(args):
     M = int(M)
     device = torch.device("cuda", 0)
     torch.cuda.set_device(0)
+    if kind == "attn":
+        return run_case_attention(device, batch=int(name), context=M, reps=args.steps)
     K, N = (synth.LLAMA_3_2_3B if kind == "int4" else synth.QWEN_2_5_7B)[name]
     copies = max(2, int((256 << 20) // (N * K)) + 1)
     lins = []
@@ -618,6 +620,46 @@ def run_case(args):
     print(json.dumps({"case": args.case, "us": dt * 1e6, "TFLOPs": 2.0 * M * N * K / dt / 1e12, "N": N, "K": K, "M": M}))
 
 
+def run_case_attention(device, batch, context, reps, layers=28, block_size=16):
+    """`--case attn,<batch>,<context>`: the paged decode attention alone at the Llama-3.2-3B geometry,
+    one CUDA graph of `layers` calls over distinct caches (so consecutive calls miss L2), replayed."""
+    import torch
+    from scratchy_b200 import decode
+    cfg = decode.LLAMA_3_2_3B
+    blocks_per_seq = (context + block_size - 1) // block_size
+    nblk = batch * blocks_per_seq
+    shape = (nblk, cfg.n_kv_heads, block_size, cfg.head_dim)
+    ks = [torch.randn(shape, device=device).to(torch.bfloat16) for _ in range(layers)]
+    vs = [torch.randn(shape, device=device).to(torch.bfloat16) for _ in range(layers)]
+    q = torch.randn((batch, cfg.q_dim), device=device).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    table = torch.randperm(nblk, device=device).to(torch.int32).reshape(batch, blocks_per_seq)
+    used = torch.full((batch,), context, dtype=torch.int32, device=device)
+
+    def call(i):
+        decode.attention_via_cache(q, ks[i], vs[i], table, used, cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, block_size,
+                                   cfg.head_dim ** -0.5, out=out)
+    call(0)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream(device)
+    gr = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(gr, stream=side):
+        for i in range(layers):
+            call(i)
+    for _ in range(3):
+        gr.replay()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        gr.replay()
+    b.record()
+    torch.cuda.synchronize()
+    dt = a.elapsed_time(b) * 1e-3 / (reps * layers)
+    kv = batch * context * cfg.n_kv_heads * cfg.head_dim * 2 * 2
+    print(json.dumps({"case": f"attn,{batch},{context}", "us": dt * 1e6, "kv_bytes": kv, "GBps": kv / dt / 1e9}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -627,10 +669,19 @@ def main():
     ap.add_argument("--sweep", action="store_true")
     ap.add_argument("--serial", action="store_true", help="one branch: every linear waits for the previous one")
     ap.add_argument("--no-decode", action="store_true", help="skip the whole-decode-step section (config 3)")
+    ap.add_argument("--decode-only", action="store_true", help="run only the whole-decode-step section and print it")
+    ap.add_argument("--decode-batches", default="1,8,32")
     ap.add_argument("--case", default=None, help="kind,shape,M e.g. int4,gate,2048: time one linear alone")
     args = ap.parse_args()
     if args.case:
         run_case(args)
+        return
+    if args.decode_only:
+        import torch
+        device = torch.device("cuda", 0)
+        torch.cuda.set_device(device)
+        cases = run_decode(device, steps=args.steps, batches=tuple(int(b) for b in args.decode_batches.split(",")))
+        print(json.dumps({"decode": cases}))
         return
     if args.impl == "reference":
         run_reference(args)

@@ -13,7 +13,7 @@
 // (fused_gate_up_silu_mul), :289-362 (rope_append), :386-460 (attention_via_cache); cache
 // addressing crates/targets/metal/src/paged_kv_layout.rs:74-115; argmax tie rule
 // crates/targets/metal/tests/argmax_split_test.rs:24-33.
-#include "common.cuh"
+#include "tc_common.cuh"
 
 #include <math.h>
 
@@ -25,6 +25,27 @@ constexpr int DEV_BAD_TOKEN_ID = 0x0E000001;
 constexpr int DEV_BAD_SLOT = 0x0E000002;
 constexpr int DEV_BAD_BLOCK = 0x0E000003;
 constexpr int DEV_BAD_POSITION = 0x0E000004;
+
+// Programmatic dependent launch: every kernel here lets the next kernel of the stream start its own
+// prologue at once (a following matvec prefetches weights while this kernel runs) and waits for the
+// previous kernel's results before it touches any activation.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
 
 __device__ __forceinline__ float bf16_bits_to_f32(uint32_t h) { return __uint_as_float(h << 16); }
 __device__ __forceinline__ uint32_t f32_to_bf16_bits(float f) {
@@ -49,6 +70,8 @@ __device__ __forceinline__ uint4 pack8(const float* f) {
 // ------------------------------------------------------------------------------- embed
 __global__ void embed_kernel(const uint32_t* __restrict__ ids, const uint4* __restrict__ table, uint32_t vocab, int hidden_v,
                              uint4* __restrict__ out, int* status) {
+    pdl_trigger();
+    pdl_wait();
     const uint32_t id = ids[blockIdx.x];
     const bool ok = id < vocab;
     if (!ok && threadIdx.x == 0) atomicCAS(status, 0, DEV_BAD_TOKEN_ID);
@@ -79,6 +102,8 @@ __global__ void __launch_bounds__(NORM_THREADS) rmsnorm_kernel(uint16_t* __restr
                                                                float eps) {
     extern __shared__ float row[];          // hidden floats
     __shared__ float red[NORM_THREADS / 32];
+    pdl_trigger();
+    pdl_wait();
     const size_t base = size_t(blockIdx.x) * hidden;
     const int nv = hidden >> 3;
     float sum_sq = 0.0f;
@@ -113,6 +138,8 @@ __global__ void __launch_bounds__(NORM_THREADS) rmsnorm_kernel(uint16_t* __restr
 // ------------------------------------------------------------------------------- silu(gate) * up
 __global__ void silu_mul_kernel(const uint16_t* __restrict__ gate, const uint16_t* __restrict__ up, long long ld_in,
                                 uint16_t* __restrict__ out, int inter_v, long long total_v) {
+    pdl_trigger();
+    pdl_wait();
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total_v; i += (long long)gridDim.x * blockDim.x) {
         const long long r = i / inter_v;
         const int v = int(i - r * inter_v);
@@ -137,6 +164,8 @@ __global__ void rope_append_kernel(const uint16_t* q, long long ld_q, const uint
                                    long long ld_qo, uint16_t* __restrict__ cache_k, uint16_t* __restrict__ cache_v,
                                    uint32_t num_blocks, int num_q_heads, int num_kv_heads, int head_dim, int block_size,
                                    int* status) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.y;
     const int h = blockIdx.x;
     const int half = head_dim >> 1;
@@ -197,6 +226,8 @@ __global__ void __launch_bounds__(ARGMAX_THREADS) argmax_kernel(const uint16_t* 
                                                                 uint32_t* __restrict__ out) {
     __shared__ float s_best[ARGMAX_THREADS / 32];
     __shared__ uint32_t s_idx[ARGMAX_THREADS / 32];
+    pdl_trigger();
+    pdl_wait();
     const uint16_t* row = logits + blockIdx.x * ld;
     float best = -INFINITY;
     uint32_t best_i = 0;
@@ -256,6 +287,120 @@ __device__ __forceinline__ void att_store_rank0(float* local, float v) {
 }
 __device__ __forceinline__ float att_weight(float m, float m_new) { return m == -INFINITY ? 0.0f : expf(m - m_new); }
 
+
+// Warps -> CTA: called by the ATT_THREADS consumer threads once every warp has written its state
+// (acc[D], m, l per query head) to warp_part[warp][g].  With one split the output row is stored
+// directly; otherwise the CTA's state goes to CTA 0's table through distributed shared memory.
+template <int D>
+__device__ __forceinline__ void att_cta_merge(int G, int nwarps, const float* warp_part, float* cl_part, int split, int nsplit,
+                                              int q_head0, int b, uint16_t* __restrict__ out, long long ld_o) {
+    constexpr int STATE = D + 2;
+    __shared__ float wgt[8][ATT_WARPS + 2];          // per query head: the warps' weights, the merged maximum and sum
+    const int nthreads = nwarps * 32;
+    asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+    if (threadIdx.x < G) {
+        const int g = threadIdx.x;
+        float mt = -INFINITY;
+        for (int w = 0; w < nwarps; ++w) mt = fmaxf(mt, warp_part[(w * G + g) * STATE + D]);
+        float lt = 0.0f;
+        for (int w = 0; w < nwarps; ++w) {
+            const float c = att_weight(warp_part[(w * G + g) * STATE + D], mt);
+            wgt[g][w] = c;
+            lt += warp_part[(w * G + g) * STATE + D + 1] * c;
+        }
+        wgt[g][ATT_WARPS] = mt;
+        wgt[g][ATT_WARPS + 1] = lt;
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+    for (int idx = threadIdx.x; idx < G * D; idx += nthreads) {
+        const int g = idx / D, d = idx - g * D;
+        float a = 0.0f;
+        for (int w = 0; w < nwarps; ++w) a += warp_part[(w * G + g) * STATE + d] * wgt[g][w];
+        if (nsplit == 1) {
+            out[b * ld_o + (q_head0 + g) * D + d] = uint16_t(f32_to_bf16_bits(a * __fdiv_rn(1.0f, wgt[g][ATT_WARPS + 1] + 1e-6f)));
+        } else {
+            float* dst = cl_part + (split * G + g) * STATE;
+            att_store_rank0(dst + d, a);
+            if (d == 0) {
+                att_store_rank0(dst + D, wgt[g][ATT_WARPS]);
+                att_store_rank0(dst + D + 1, wgt[g][ATT_WARPS + 1]);
+            }
+        }
+    }
+}
+
+// Merge of the per-lane-group online-softmax states: lane groups -> warp (shuffles) -> CTA
+// (shared memory) -> cluster (stores into CTA 0's table through distributed shared memory).
+// CTA 0 of the cluster applies inv_sum = 1 / (l + 1e-6) and stores bf16.  Called by all
+// threads of the first ATT_THREADS (the consumer warps); `bar_id` names the CTA barrier they share.
+template <int D, int G>
+__device__ __forceinline__ void att_merge_and_store(float (&m)[G], float (&lsum)[G], float (&acc)[G][8], float* warp_part,
+                                                    float* cl_part, int split, int nsplit, int q_head0, int b,
+                                                    uint16_t* __restrict__ out, long long ld_o) {
+    constexpr int LPT = D / 8;
+    constexpr int STATE = D + 2;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int grp = lane / LPT, l = lane % LPT;
+#pragma unroll
+    for (int o = LPT; o < 32; o <<= 1) {
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const float mo = __shfl_xor_sync(0xffffffffu, m[g], o);
+            const float lo = __shfl_xor_sync(0xffffffffu, lsum[g], o);
+            const float mn = fmaxf(m[g], mo);
+            const float ca = att_weight(m[g], mn), cb = att_weight(mo, mn);
+            lsum[g] = lsum[g] * ca + lo * cb;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float ao = __shfl_xor_sync(0xffffffffu, acc[g][j], o);
+                acc[g][j] = acc[g][j] * ca + ao * cb;
+            }
+            m[g] = mn;
+        }
+    }
+    if (grp == 0) {
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float* st = warp_part + (warp * G + g) * STATE;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) st[l * 8 + j] = acc[g][j];
+            if (l == 0) {
+                st[D] = m[g];
+                st[D + 1] = lsum[g];
+            }
+        }
+    }
+    att_cta_merge<D>(G, ATT_WARPS, warp_part, cl_part, split, nsplit, q_head0, b, out, ld_o);
+}
+
+// After the cluster barrier: CTA 0 folds the splits' states and stores the output row.  Called by
+// every thread of CTA 0 (`nthreads` of them).
+template <int D>
+__device__ __forceinline__ void att_cluster_finish(int G, const float* cl_part, int nsplit, int q_head0, int b,
+                                                   uint16_t* __restrict__ out, long long ld_o, int nthreads) {
+    constexpr int STATE = D + 2;
+    __shared__ float swgt[8][ATT_SPLITS + 1];        // per query head: the splits' weights and 1 / (sum + 1e-6)
+    if (threadIdx.x < G) {
+        const int g = threadIdx.x;
+        float mt = -INFINITY;
+        for (int sp = 0; sp < nsplit; ++sp) mt = fmaxf(mt, cl_part[(sp * G + g) * STATE + D]);
+        float lt = 0.0f;
+        for (int sp = 0; sp < nsplit; ++sp) {
+            const float c = att_weight(cl_part[(sp * G + g) * STATE + D], mt);
+            swgt[g][sp] = c;
+            lt += cl_part[(sp * G + g) * STATE + D + 1] * c;
+        }
+        swgt[g][ATT_SPLITS] = __fdiv_rn(1.0f, lt + 1e-6f);
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * D; idx += nthreads) {
+        const int g = idx / D, d = idx - g * D;
+        float a = 0.0f;
+        for (int sp = 0; sp < nsplit; ++sp) a += cl_part[(sp * G + g) * STATE + d] * swgt[g][sp];
+        out[b * ld_o + (q_head0 + g) * D + d] = uint16_t(f32_to_bf16_bits(a * swgt[g][ATT_SPLITS]));
+    }
+}
+
 template <int D, int G>
 __global__ void __launch_bounds__(ATT_THREADS) attention_decode_kernel(
     const uint16_t* __restrict__ q, long long ld_q, const uint16_t* __restrict__ cache_k, const uint16_t* __restrict__ cache_v,
@@ -265,11 +410,13 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_decode_kernel(
     constexpr int TPW = 32 / LPT;
     constexpr int STATE = D + 2;                     // acc[D], m, l
     constexpr int U = G <= 4 ? 4 : 2;                // tokens in flight per lane group
-    extern __shared__ __align__(16) unsigned char att_smem[];
+    extern __shared__ __align__(128) unsigned char att_smem[];
     float* warp_part = reinterpret_cast<float*>(att_smem);                 // [ATT_WARPS][G][STATE]
     float* cl_part = warp_part + ATT_WARPS * G * STATE;                    // [ATT_SPLITS][G][STATE], filled on CTA 0
     uint32_t* blocks = reinterpret_cast<uint32_t*>(cl_part + ATT_SPLITS * G * STATE);
 
+    pdl_trigger();
+    pdl_wait();
     const int split = int(att_cluster_rank());
     const int kvh = blockIdx.y, b = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -372,110 +519,352 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_decode_kernel(
         }
     }
 
-    // lane groups of a warp -> one state per warp
-#pragma unroll
-    for (int o = LPT; o < 32; o <<= 1) {
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-            const float mo = __shfl_xor_sync(0xffffffffu, m[g], o);
-            const float lo = __shfl_xor_sync(0xffffffffu, lsum[g], o);
-            const float mn = fmaxf(m[g], mo);
-            const float ca = att_weight(m[g], mn), cb = att_weight(mo, mn);
-            lsum[g] = lsum[g] * ca + lo * cb;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const float ao = __shfl_xor_sync(0xffffffffu, acc[g][j], o);
-                acc[g][j] = acc[g][j] * ca + ao * cb;
-            }
-            m[g] = mn;
-        }
+    att_merge_and_store<D, G>(m, lsum, acc, warp_part, cl_part, split, ATT_SPLITS, kvh * G, b, out, ld_o);
+    att_cluster_sync();
+    if (split == 0) att_cluster_finish<D>(G, cl_part, ATT_SPLITS, kvh * G, b, out, ld_o, ATT_THREADS);
+}
+
+
+// ---- the streaming variant: TMA tiles + tensor cores -------------------------------------------
+// In the paged layout one (block, kv head) is a contiguous run of block_size tokens x D bf16.  A
+// producer warp brings those runs (K and V) into a shared-memory ring with one 3-D TMA tile load
+// each (tensor map over the cache viewed as [token][D/64][64], 128-byte swizzle), one ring stage
+// per cache block, completion counted in bytes on the stage's mbarrier; everything the ring holds
+// is in flight at once.  Each of the eight consumer warps takes whole blocks and runs them through
+// mma.sync m16n8k16: S = Q K^T with the (up to 8) query heads of the kv head as the rows of the
+// 16-row A operand and K read by ldmatrix; an online softmax on the accumulator fragments; O += P V
+// with V read by ldmatrix.trans and P split into a bf16 head and a bf16 remainder (two MMAs), so
+// the probabilities keep ~16 mantissa bits.  Scores, the softmax state and O stay in f32.
+// The cluster (1, 2, 4 or 8 CTAs, chosen by the host from the batch) splits the sequence by whole
+// blocks.  Every wait is bounded and reports through the status word.
+constexpr int ATTB_THREADS = ATT_THREADS + 32;
+constexpr int ATT_ERR_FULL = 0x0A000001;
+constexpr int ATT_ERR_EMPTY = 0x0A000002;
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const CUtensorMap* tmap, int c0, int c1, int c2, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(dst_smem), "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+// D(16x8,f32) += A(16x16,bf16) * B(16x8,bf16).  Rows 8..15 of A are zero here (a1 = a3 = 0), so the
+// accumulator halves of those rows (z0, z1) stay zero: callers pass a few shared dummies for them.
+__device__ __forceinline__ void mma_bf16_16816(float& c0, float& c1, float& z0, float& z1, uint32_t a0, uint32_t a2, uint32_t b0,
+                                               uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c0), "+f"(c1), "+f"(z0), "+f"(z1) : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) { return f32_to_bf16_bits(lo) | (f32_to_bf16_bits(hi) << 16); }
+
+template <int D>
+__global__ void __launch_bounds__(ATTB_THREADS) attention_decode_tc_kernel(
+    const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map, const uint16_t* __restrict__ q,
+    long long ld_q, const uint32_t* __restrict__ block_table, const uint32_t* __restrict__ seq_used_k,
+    uint16_t* __restrict__ out, long long ld_o, int G, int num_kv_heads, int block_size, int max_blocks_per_seq,
+    uint32_t num_blocks, int table_cap, int stages, float scale, int* status) {
+    constexpr int NH = D / 64;                       // 128-byte rows per token
+    constexpr int STATE = D + 2;
+    constexpr int KSTEPS = D / 16;
+    constexpr int NTILES = D / 8;
+    extern __shared__ __align__(128) unsigned char att_smem[];
+    const int nwarps = int(blockDim.x >> 5) - 1;     // consumer warps; the last warp is the producer
+    const uint32_t chunk = uint32_t(block_size) * D * 2;                   // bytes of one block's K (or V) for one kv head
+    const uint32_t half_bytes = uint32_t(block_size) * 128;                // one 64-dim half of it: [token][128 bytes], swizzled
+    unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(att_smem) + 1023) & ~uintptr_t(1023));
+    float* warp_part = reinterpret_cast<float*>(ring);                     // aliases the ring once it is drained
+    const size_t ring_bytes = max(size_t(stages) * 2 * chunk, size_t(nwarps) * G * STATE * sizeof(float));
+    float* cl_part = reinterpret_cast<float*>(ring + ((ring_bytes + 127) & ~size_t(127)));        // [nsplit<=8][G][STATE]
+    uint32_t* blocks = reinterpret_cast<uint32_t*>(cl_part + ATT_SPLITS * G * STATE);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(blocks + ((table_cap + 1) & ~1));                // full[stages], empty[stages]
+
+    pdl_trigger();
+    uint32_t nsplit;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(nsplit));
+    const int split = int(att_cluster_rank());
+    const int kvh = blockIdx.y, b = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    long long kv_len_raw = seq_used_k[b];
+    const long long kv_cap = (long long)max_blocks_per_seq * block_size;
+    if (kv_len_raw > kv_cap) {
+        if (threadIdx.x == 0) atomicCAS(status, 0, DEV_BAD_BLOCK);
+        kv_len_raw = kv_cap;
     }
-    if (grp == 0) {
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-            float* st = warp_part + (warp * G + g) * STATE;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) st[l * 8 + j] = acc[g][j];
-            if (l == 0) {
-                st[D] = m[g];
-                st[D + 1] = lsum[g];
-            }
+    const int kv_len = int(kv_len_raw);
+    const int total_blk = (kv_len + block_size - 1) / block_size;
+    const int per = (total_blk + int(nsplit) - 1) / int(nsplit);
+    const int first_blk = min(split * per, total_blk);
+    int nblk = min(per, total_blk - first_blk);
+    if (nblk > table_cap) {
+        if (threadIdx.x == 0) atomicCAS(status, 0, DEV_BAD_BLOCK);
+        nblk = 0;
+    }
+    for (int i = threadIdx.x; i < nblk; i += int(blockDim.x)) {
+        uint32_t pb = block_table[size_t(b) * max_blocks_per_seq + first_blk + i];
+        if (pb >= num_blocks) {                                            // never copy from outside the cache
+            atomicCAS(status, 0, DEV_BAD_BLOCK);
+            pb = 0;
         }
+        blocks[i] = pb;
+    }
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) {
+            mbar_init(smem_u32(&bars[s]), 1);
+            mbar_init(smem_u32(&bars[stages + s]), 1);
+        }
+        fence_mbar_init();
     }
     __syncthreads();
-    // warps -> CTA, pushed into CTA 0's cluster table
-    for (int idx = threadIdx.x; idx < G * D; idx += ATT_THREADS) {
-        const int g = idx / D, d = idx - g * D;
-        float mt = -INFINITY;
+    pdl_wait();                                      // q and the newest cache slot come from the previous kernels
+
+    if (warp == nwarps) {
+        // ---------------- producer: lane s owns ring stage s and issues, in order, every block that passes
+        // through it (a single thread's TMA issue rate would otherwise bound short sequences).  Consumer warp
+        // w owns stages [w*spw, (w+1)*spw) and takes blocks w, w+nwarps, ...; its j-th block sits in stage
+        // w*spw + j%spw.  Each side waits on one barrier strictly in phase order, so a parity wait is never
+        // more than one phase ahead of its barrier.
+        const int spw = stages / nwarps;
+        if (lane < stages) {
+            const int w = lane / spw, r = lane - w * spw;
+            const uint32_t full = smem_u32(&bars[lane]);
+            const uint32_t dst = smem_u32(ring + size_t(lane) * 2 * chunk);
+            for (int n = 0;; ++n) {
+                const int i = w + nwarps * (r + spw * n);
+                if (i >= nblk) break;
+                if (n >= 1 && !mbar_wait(smem_u32(&bars[stages + lane]), uint32_t((n - 1) & 1), status, ATT_ERR_EMPTY)) break;
+                const int token0 = int((blocks[i] * uint32_t(num_kv_heads) + uint32_t(kvh)) * uint32_t(block_size));
+                mbar_arrive_expect_tx(full, 2 * chunk);
 #pragma unroll
-        for (int w = 0; w < ATT_WARPS; ++w) mt = fmaxf(mt, warp_part[(w * G + g) * STATE + D]);
-        float a = 0.0f, lt = 0.0f;
+                for (int h = 0; h < NH; ++h) {                              // [half][token][128 bytes]: ldmatrix rows 8 tokens apart never share a bank
+                    tma_load_3d(dst + h * half_bytes, &k_map, 0, h, token0, full);
+                    tma_load_3d(dst + chunk + h * half_bytes, &v_map, 0, h, token0, full);
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------- consumers: warp w owns blocks w, w+8, ...
+        const int row = lane >> 2, quad = lane & 3;
+        uint32_t qa0[KSTEPS], qa2[KSTEPS];             // A fragments of Q: row = query head (zero beyond G), 16 dims per step
 #pragma unroll
-        for (int w = 0; w < ATT_WARPS; ++w) {
-            const float* st = warp_part + (w * G + g) * STATE;
-            const float c = att_weight(st[D], mt);
-            a += st[d] * c;
-            lt += st[D + 1] * c;
+        for (int kk = 0; kk < KSTEPS; ++kk) {
+            qa0[kk] = qa2[kk] = 0u;
+            if (row < G) {
+                const uint16_t* qp = q + b * ld_q + (size_t(kvh) * G + row) * D + kk * 16 + quad * 2;
+                qa0[kk] = *reinterpret_cast<const uint32_t*>(qp);
+                qa2[kk] = *reinterpret_cast<const uint32_t*>(qp + 8);
+            }
         }
-        float* dst = cl_part + (split * G + g) * STATE;
-        att_store_rank0(dst + d, a);
-        if (d == 0) {
-            att_store_rank0(dst + D, mt);
-            att_store_rank0(dst + D + 1, lt);
+        const float sl2 = scale * 1.4426950408889634f;                     // scores live in the log2 domain
+        float m2 = -INFINITY, lsum = 0.0f;                                 // this lane's row; lsum is the lane's share of the row sum
+        float o[NTILES][2];
+#pragma unroll
+        for (int nt = 0; nt < NTILES; ++nt) o[nt][0] = o[nt][1] = 0.0f;
+        float z[4][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}, {0.0f, 0.0f}, {0.0f, 0.0f}};   // rows 8..15: always zero, rotated to keep the MMAs independent
+        // ldmatrix lane roles: lane supplies the row address of matrix lane/8, row lane%8
+        const int lm = lane >> 3, lr = lane & 7;
+        bool alive = true;
+        const int spw = stages / nwarps;
+        for (int i = warp, j = 0; i < nblk && alive; i += nwarps, ++j) {
+            const int s = warp * spw + j % spw;
+            alive = mbar_wait(smem_u32(&bars[s]), uint32_t((j / spw) & 1), status, ATT_ERR_FULL);
+            if (!alive) break;
+            const uint32_t kst = smem_u32(ring + size_t(s) * 2 * chunk);
+            const uint32_t vst = kst + chunk;
+            const int t0 = (first_blk + i) * block_size;
+            for (int sub = 0; sub < block_size; sub += 16) {
+                if (t0 + sub >= kv_len) break;
+                // S[16 x 16 tokens] = Q K^T
+                float sc[2][2];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) sc[j][0] = sc[j][1] = 0.0f;
+#pragma unroll
+                for (int kk = 0; kk < KSTEPS; ++kk) {
+                    // matrices: (tokens 0-7, dims +0..7), (tokens 0-7, dims +8..15), (tokens 8-15, +0..7), (tokens 8-15, +8..15)
+                    const int token = sub + (lm >> 1) * 8 + lr;
+                    const int dchunk = kk * 2 + (lm & 1);                  // 16-byte piece of the token's D*2-byte row
+                    uint32_t kb[4];
+                    ldsm_x4(kst + (dchunk >> 3) * half_bytes + token * 128 + (((dchunk & 7) ^ (token & 7)) << 4), kb);
+                    mma_bf16_16816(sc[0][0], sc[0][1], z[0][0], z[0][1], qa0[kk], qa2[kk], kb[0], kb[1]);
+                    mma_bf16_16816(sc[1][0], sc[1][1], z[1][0], z[1][1], qa0[kk], qa2[kk], kb[2], kb[3]);
+                }
+                // online softmax on the row this lane holds (tokens j*8 + quad*2 + {0,1})
+                float rmax = -INFINITY;
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const bool valid = t0 + sub + j * 8 + quad * 2 + e < kv_len;
+                        sc[j][e] = valid ? sc[j][e] * sl2 : -INFINITY;
+                        rmax = fmaxf(rmax, sc[j][e]);
+                    }
+                }
+                rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 1));
+                rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, 2));
+                const float mn = fmaxf(m2, rmax);                          // finite: token t0+sub is valid
+                const float corr = fast_exp2(m2 - mn);                     // 0 on the first tile (m2 = -inf)
+                m2 = mn;
+                float p[2][2];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    p[j][0] = fast_exp2(sc[j][0] - mn);
+                    p[j][1] = fast_exp2(sc[j][1] - mn);
+                }
+                lsum = lsum * corr + (p[0][0] + p[0][1]) + (p[1][0] + p[1][1]);
+                if (__any_sync(0xffffffffu, corr != 1.0f)) {
+#pragma unroll
+                    for (int nt = 0; nt < NTILES; ++nt) {
+                        o[nt][0] *= corr;
+                        o[nt][1] *= corr;
+                    }
+                }
+                // P as the A operand of the second product: k = tokens; bf16 head + bf16 remainder
+                const uint32_t ph0 = pack_bf16x2(p[0][0], p[0][1]), ph2 = pack_bf16x2(p[1][0], p[1][1]);
+                const uint32_t pl0 = pack_bf16x2(p[0][0] - bf16_bits_to_f32(ph0 & 0xFFFFu), p[0][1] - __uint_as_float(ph0 & 0xFFFF0000u));
+                const uint32_t pl2 = pack_bf16x2(p[1][0] - bf16_bits_to_f32(ph2 & 0xFFFFu), p[1][1] - __uint_as_float(ph2 & 0xFFFF0000u));
+#pragma unroll
+                for (int nt = 0; nt < NTILES; nt += 2) {
+                    // matrices: (tokens 0-7, dims nt*8..), (tokens 8-15, dims nt*8..), (tokens 0-7, dims (nt+1)*8..), (tokens 8-15, ...)
+                    const int token = sub + (lm & 1) * 8 + lr;
+                    const int dchunk = nt + (lm >> 1);
+                    uint32_t vb[4];
+                    ldsm_x4_trans(vst + (dchunk >> 3) * half_bytes + token * 128 + (((dchunk & 7) ^ (token & 7)) << 4), vb);
+                    mma_bf16_16816(o[nt][0], o[nt][1], z[0][0], z[0][1], ph0, ph2, vb[0], vb[1]);
+                    mma_bf16_16816(o[nt + 1][0], o[nt + 1][1], z[1][0], z[1][1], ph0, ph2, vb[2], vb[3]);
+                    mma_bf16_16816(o[nt][0], o[nt][1], z[2][0], z[2][1], pl0, pl2, vb[0], vb[1]);
+                    mma_bf16_16816(o[nt + 1][0], o[nt + 1][1], z[3][0], z[3][1], pl0, pl2, vb[2], vb[3]);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars[stages + s]));
         }
+        lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
+        lsum += __shfl_xor_sync(0xffffffffu, lsum, 2);
+        // every warp is past its last ring read before warp_part (which aliases the ring) is written;
+        // the blocks another warp still waits for are that warp's own
+        asm volatile("bar.sync 1, %0;" ::"r"(nwarps * 32) : "memory");
+        if (row < G) {
+            float* st = warp_part + (warp * G + row) * STATE;
+#pragma unroll
+            for (int nt = 0; nt < NTILES; ++nt) {
+                st[nt * 8 + quad * 2] = o[nt][0];
+                st[nt * 8 + quad * 2 + 1] = o[nt][1];
+            }
+            if (quad == 0) {
+                st[D] = m2 * 0.6931471805599453f;                          // back to the natural-log domain of the merge
+                st[D + 1] = lsum;
+            }
+        }
+        att_cta_merge<D>(G, nwarps, warp_part, cl_part, split, int(nsplit), kvh * G, b, out, ld_o);
     }
-    att_cluster_sync();
-    if (split != 0) return;
-    for (int idx = threadIdx.x; idx < G * D; idx += ATT_THREADS) {
-        const int g = idx / D, d = idx - g * D;
-        float mt = -INFINITY;
-#pragma unroll
-        for (int sp = 0; sp < ATT_SPLITS; ++sp) mt = fmaxf(mt, cl_part[(sp * G + g) * STATE + D]);
-        float a = 0.0f, lt = 0.0f;
-#pragma unroll
-        for (int sp = 0; sp < ATT_SPLITS; ++sp) {
-            const float* st = cl_part + (sp * G + g) * STATE;
-            const float c = att_weight(st[D], mt);
-            a += st[d] * c;
-            lt += st[D + 1] * c;
-        }
-        const float inv_sum = __fdiv_rn(1.0f, lt + 1e-6f);
-        out[b * ld_o + (kvh * G + g) * D + d] = uint16_t(f32_to_bf16_bits(a * inv_sum));
+    if (nsplit > 1) {
+        att_cluster_sync();
+        if (split == 0) att_cluster_finish<D>(G, cl_part, int(nsplit), kvh * G, b, out, ld_o, int(blockDim.x));
     }
 }
+
+// Bytes of dynamic shared memory one CTA may take so that two CTAs fit on an SM.
+constexpr size_t ATT_SMEM_BUDGET = 110 * 1024;
+constexpr size_t ATT_SMEM_BUDGET_ALONE = 200 * 1024;
+constexpr int ATT_MAX_STAGES = 24;
 
 template <int D, int G>
 cudaError_t attention_launch(const uint16_t* q, long long ld_q, const uint16_t* cache_k, const uint16_t* cache_v,
                              const uint32_t* block_table, const uint32_t* seq_used_k, uint16_t* out, long long ld_o, int batch,
                              int num_kv_heads, int block_size, int max_blocks_per_seq, uint32_t num_blocks, float scale,
-                             int* status, cudaStream_t stream) {
-    const int table_cap = max_blocks_per_seq / ATT_SPLITS + 3;
-    const size_t smem = size_t(ATT_WARPS + ATT_SPLITS) * G * (D + 2) * sizeof(float) + size_t(table_cap) * sizeof(uint32_t);
+                             int sm_count, int* status, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    cfg.stream = stream;
+
+    // streaming variant: blocks of a multiple of 16 tokens (one TMA box, 16-token MMA tiles), two ring stages in the budget
+    const size_t chunk = size_t(block_size) * D * 2;
+    const size_t part = size_t(ATT_SPLITS) * G * (D + 2) * sizeof(float);
+    const size_t warp_part = size_t(ATT_WARPS) * G * (D + 2) * sizeof(float);
+    int nsplit = ATT_SPLITS;                         // the most splits that still run as a single wave of two CTAs per SM
+    while (nsplit > 1 && (long long)batch * num_kv_heads * nsplit > 2LL * sm_count) nsplit /= 2;
+    const int table_cap = max_blocks_per_seq / nsplit + 2;
+    const size_t fixed = part + size_t((table_cap + 1) & ~1) * 4 + 2 * ATT_MAX_STAGES * sizeof(uint64_t) + 1024 + 128;
+    // alone on its SM (the grid does not oversubscribe the machine): 8 consumer warps and a deep ring;
+    // otherwise two CTAs per SM with 4 consumer warps each.  Every warp owns stages / warps ring stages
+    // and wants at least two of them, so that its next block loads while it works on the current one.
+    const bool alone = (long long)batch * num_kv_heads * nsplit <= sm_count;
+    const size_t budget = alone ? ATT_SMEM_BUDGET_ALONE : ATT_SMEM_BUDGET;
+    int nwarps = alone ? 8 : 4, spw = 0;
+    for (; nwarps >= 2; nwarps /= 2) {
+        spw = budget > fixed ? int(std::min<size_t>(3, (budget - fixed) / (2 * chunk * nwarps))) : 0;
+        if (spw >= 2) break;
+    }
+    if (spw < 2) {                                   // large blocks: settle for one stage per warp if that fits
+        nwarps = 2;
+        spw = budget > fixed ? int(std::min<size_t>(3, (budget - fixed) / (2 * chunk * nwarps))) : 0;
+    }
+    const unsigned long long total_tokens = (unsigned long long)num_blocks * num_kv_heads * block_size;
+    tc_encode_tiled_fn enc = tc_tensor_map_encoder();
+    if (enc && block_size % 16 == 0 && block_size <= 256 && total_tokens < (1ull << 31) && spw >= 1) {
+        const int stages = spw * nwarps;
+        const size_t ring = std::max(size_t(stages) * 2 * chunk, size_t(nwarps) * G * (D + 2) * sizeof(float));
+        const size_t smem = ((ring + 127) & ~size_t(127)) + fixed;
+        CUtensorMap maps[2];
+        const cuuint64_t dims[3] = {64, cuuint64_t(D / 64), cuuint64_t(total_tokens)};
+        const cuuint64_t strides[2] = {128, cuuint64_t(D) * 2};
+        const cuuint32_t box[3] = {64, 1, cuuint32_t(block_size)};
+        const cuuint32_t estr[3] = {1, 1, 1};
+        const void* bases[2] = {cache_k, cache_v};
+        for (int i = 0; i < 2; ++i) {
+            const CUresult r = enc(&maps[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(bases[i]), dims, strides, box, estr,
+                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+        }
+        auto kernel = attention_decode_tc_kernel<D>;
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e != cudaSuccess) return e;
+        cfg.gridDim = dim3(nsplit, num_kv_heads, batch);
+        cfg.blockDim = dim3((nwarps + 1) * 32);
+        cfg.dynamicSmemBytes = smem;
+        attr[0].val.clusterDim.x = nsplit;
+        return cudaLaunchKernelEx(&cfg, kernel, maps[0], maps[1], q, ld_q, block_table, seq_used_k, out, ld_o, G, num_kv_heads,
+                                  block_size, max_blocks_per_seq, num_blocks, table_cap, stages, scale, status);
+    }
+    // small or odd blocks: per-token loads
+    const int cap1 = max_blocks_per_seq / ATT_SPLITS + 3;
+    const size_t smem = warp_part + part + size_t(cap1) * sizeof(uint32_t);
     auto kernel = attention_decode_kernel<D, G>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return e;
-    cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ATT_SPLITS, num_kv_heads, batch);
     cfg.blockDim = dim3(ATT_THREADS);
     cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = ATT_SPLITS;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kernel, q, ld_q, cache_k, cache_v, block_table, seq_used_k, out, ld_o, num_kv_heads,
-                              block_size, max_blocks_per_seq, num_blocks, table_cap, scale, status);
+                              block_size, max_blocks_per_seq, num_blocks, cap1, scale, status);
 }
 
 template <int D>
 cudaError_t attention_dispatch_g(int G, const uint16_t* q, long long ld_q, const uint16_t* ck, const uint16_t* cv,
                                  const uint32_t* bt, const uint32_t* used, uint16_t* out, long long ld_o, int batch, int hkv,
-                                 int bs, int mb, uint32_t nb, float scale, int* status, cudaStream_t st) {
+                                 int bs, int mb, uint32_t nb, float scale, int sms, int* status, cudaStream_t st) {
     switch (G) {
-#define ATT_CASE(GG) case GG: return attention_launch<D, GG>(q, ld_q, ck, cv, bt, used, out, ld_o, batch, hkv, bs, mb, nb, scale, status, st)
+#define ATT_CASE(GG) case GG: return attention_launch<D, GG>(q, ld_q, ck, cv, bt, used, out, ld_o, batch, hkv, bs, mb, nb, scale, sms, status, st)
         ATT_CASE(1); ATT_CASE(2); ATT_CASE(3); ATT_CASE(4); ATT_CASE(5); ATT_CASE(6); ATT_CASE(7); ATT_CASE(8);
 #undef ATT_CASE
         default: return cudaErrorInvalidValue;
@@ -494,8 +883,10 @@ extern "C" int32_t scr_embed_bf16(scr_ctx* ctx, const uint32_t* ids, int32_t n_i
     DEC_REQUIRE(n_ids >= 0 && vocab > 0 && hidden > 0 && hidden % 8 == 0, SCR_E_SHAPE, "embed: hidden=%d must be a positive multiple of 8", hidden);
     DEC_REQUIRE(scr_aligned16(table) && scr_aligned16(out), SCR_E_ALIGN, "embed: table/out not 16-byte aligned");
     if (n_ids == 0) return SCR_OK;
-    embed_kernel<<<n_ids, 128, 0, (cudaStream_t)stream>>>(ids, reinterpret_cast<const uint4*>(table), uint32_t(vocab), hidden / 8,
-                                                          reinterpret_cast<uint4*>(out), ctx->dev_status);
+    cudaError_t e = launch_pdl(embed_kernel, dim3(n_ids), dim3(128), 0, (cudaStream_t)stream, ids,
+                               reinterpret_cast<const uint4*>(table), uint32_t(vocab), hidden / 8, reinterpret_cast<uint4*>(out),
+                               ctx->dev_status);
+    if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "embed: %s", cudaGetErrorString(e));
     return scr_check_launch(ctx, "embed");
 }
 
@@ -511,10 +902,14 @@ static int32_t norm_launch(scr_ctx* ctx, bool add, uint16_t* residual, const uin
     cudaError_t e = cudaSuccess;
     if (add) {
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(rmsnorm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-        if (e == cudaSuccess) rmsnorm_kernel<true><<<rows, NORM_THREADS, smem, (cudaStream_t)stream>>>(residual, delta, weight, out, hidden, eps);
+        if (e == cudaSuccess)
+            e = launch_pdl(rmsnorm_kernel<true>, dim3(rows), dim3(NORM_THREADS), smem, (cudaStream_t)stream, residual, delta, weight,
+                           out, hidden, eps);
     } else {
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(rmsnorm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-        if (e == cudaSuccess) rmsnorm_kernel<false><<<rows, NORM_THREADS, smem, (cudaStream_t)stream>>>(residual, nullptr, weight, out, hidden, eps);
+        if (e == cudaSuccess)
+            e = launch_pdl(rmsnorm_kernel<false>, dim3(rows), dim3(NORM_THREADS), smem, (cudaStream_t)stream, residual,
+                           (const uint16_t*)nullptr, weight, out, hidden, eps);
     }
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "rmsnorm: %s", cudaGetErrorString(e));
     return scr_check_launch(ctx, "rmsnorm");
@@ -543,7 +938,9 @@ extern "C" int32_t scr_silu_mul_bf16(scr_ctx* ctx, const uint16_t* gate, const u
     const long long total_v = (long long)rows * (inter / 8);
     const int threads = 256;
     const int blocks = int(std::min<long long>((total_v + threads - 1) / threads, (long long)ctx->sm_count * 8));
-    silu_mul_kernel<<<blocks, threads, 0, (cudaStream_t)stream>>>(gate, up, (long long)ld_in, out, inter / 8, total_v);
+    cudaError_t e = launch_pdl(silu_mul_kernel, dim3(blocks), dim3(threads), 0, (cudaStream_t)stream, gate, up, (long long)ld_in,
+                               out, inter / 8, total_v);
+    if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "silu_mul: %s", cudaGetErrorString(e));
     return scr_check_launch(ctx, "silu_mul");
 }
 
@@ -564,9 +961,11 @@ extern "C" int32_t scr_rope_append_bf16(scr_ctx* ctx, const uint16_t* q, int64_t
                 SCR_E_SHAPE, "rope_append: a row stride is shorter than its row");
     if (num_tokens == 0) return SCR_OK;
     const int threads = std::min(256, std::max(32, ((head_dim / 2 + 31) / 32) * 32));
-    rope_append_kernel<<<dim3(num_q_heads + num_kv_heads, num_tokens), threads, 0, (cudaStream_t)stream>>>(
-        q, ld_q, k, ld_k, v, ld_v, positions, slot_mapping, cos_table, sin_table, uint32_t(max_pos), q_out, ld_qo, cache_k, cache_v,
-        uint32_t(num_blocks), num_q_heads, num_kv_heads, head_dim, block_size, ctx->dev_status);
+    cudaError_t e = launch_pdl(rope_append_kernel, dim3(num_q_heads + num_kv_heads, num_tokens), dim3(threads), 0,
+                               (cudaStream_t)stream, q, (long long)ld_q, k, (long long)ld_k, v, (long long)ld_v, positions,
+                               slot_mapping, cos_table, sin_table, uint32_t(max_pos), q_out, (long long)ld_qo, cache_k, cache_v,
+                               uint32_t(num_blocks), num_q_heads, num_kv_heads, head_dim, block_size, ctx->dev_status);
+    if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "rope_append: %s", cudaGetErrorString(e));
     return scr_check_launch(ctx, "rope_append");
 }
 
@@ -593,11 +992,11 @@ extern "C" int32_t scr_attention_via_cache_bf16(scr_ctx* ctx, const uint16_t* q,
     cudaError_t e;
     if (head_dim == 128)
         e = attention_dispatch_g<128>(G, q, ld_q, cache_k, cache_v, block_table, seq_used_k, out, ld_o, batch, num_kv_heads,
-                                      block_size, max_blocks_per_seq, uint32_t(num_blocks), attn_scale, ctx->dev_status,
+                                      block_size, max_blocks_per_seq, uint32_t(num_blocks), attn_scale, ctx->sm_count, ctx->dev_status,
                                       (cudaStream_t)stream);
     else
         e = attention_dispatch_g<64>(G, q, ld_q, cache_k, cache_v, block_table, seq_used_k, out, ld_o, batch, num_kv_heads,
-                                     block_size, max_blocks_per_seq, uint32_t(num_blocks), attn_scale, ctx->dev_status,
+                                     block_size, max_blocks_per_seq, uint32_t(num_blocks), attn_scale, ctx->sm_count, ctx->dev_status,
                                      (cudaStream_t)stream);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "attention: %s", cudaGetErrorString(e));
     return scr_check_launch(ctx, "attention_via_cache");
@@ -611,6 +1010,8 @@ extern "C" int32_t scr_argmax_bf16(scr_ctx* ctx, const uint16_t* logits, int64_t
                 "argmax: width=%d, ld=%lld (ld must be a multiple of 8, at least width)", width, (long long)ld);
     DEC_REQUIRE(scr_aligned16(logits), SCR_E_ALIGN, "argmax: logits not 16-byte aligned");
     if (rows == 0) return SCR_OK;
-    argmax_kernel<<<rows, ARGMAX_THREADS, 0, (cudaStream_t)stream>>>(logits, (long long)ld, width, out);
+    cudaError_t e = launch_pdl(argmax_kernel, dim3(rows), dim3(ARGMAX_THREADS), 0, (cudaStream_t)stream, logits, (long long)ld,
+                               width, out);
+    if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "argmax: %s", cudaGetErrorString(e));
     return scr_check_launch(ctx, "argmax");
 }

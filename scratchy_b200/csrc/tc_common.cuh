@@ -3,6 +3,8 @@
 // shared-memory and instruction descriptors.  Inline PTX only; no multicast anywhere.
 #pragma once
 
+#include <cuda.h>
+
 #include "common.cuh"
 
 // Every wait in these kernels is bounded: after TC_WAIT_LIMIT failed polls the waiter records
@@ -153,4 +155,21 @@ __device__ __forceinline__ bool elect_one() {
     asm volatile(
         "{\n\t.reg .pred p;\n\telect.sync _|p, 0xFFFFFFFF;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
     return pred != 0;
+}
+
+// ---- tensor maps ----------------------------------------------------------------------------
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda).
+typedef CUresult (*tc_encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                       const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                       CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static inline tc_encode_tiled_fn tc_tensor_map_encoder() {
+    static tc_encode_tiled_fn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (tc_encode_tiled_fn)p;
+    }
+    return fn;
 }

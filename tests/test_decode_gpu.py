@@ -18,6 +18,17 @@ REL_L2_TOL = 1e-3
 STEP_REL_L2_TOL = 1e-2
 
 
+@pytest.fixture(autouse=True)
+def _status_word_is_clean_between_tests():
+    """A test that trips a device-side check must not leak the recorded code into the next test."""
+    yield
+    from scratchy_b200 import _lib
+    try:
+        _lib.context(0).device_status(None)
+    except _lib.ScratchyCudaError:
+        pass
+
+
 def rbits(a):
     return synth.f32_to_bf16_bits(np.asarray(a, np.float32))
 
@@ -157,6 +168,8 @@ def _attention_case(lens, hq, hkv, d, bs, seed, scale=None):
     out = decode.attention_via_cache(bf16_dev(q), bf16_dev(ck), bf16_dev(cv), i32_dev(table), i32_dev(np.array(lens)),
                                      hq, hkv, d, bs, scale)
     torch.cuda.synchronize()
+    from scratchy_b200 import _lib
+    _lib.context(0).device_status(None)          # no bounded wait ran out, no block id was refused
     want = oracle.attention_via_cache(bf16_to_f32(q), bf16_to_f32(ck), bf16_to_f32(cv), table, np.array(lens, np.uint32),
                                       hq, hkv, d, bs, np.float32(scale))
     return bits_of(out), rbits(want)
@@ -169,6 +182,12 @@ def _attention_case(lens, hq, hkv, d, bs, seed, scale=None):
     ([513, 31], 8, 1, 128, 16),               # 8 query heads on one kv head
     ([200, 95], 28, 4, 128, 32),              # 7 query heads per kv head
     ([100], 4, 2, 64, 1),                     # block_size 1
+    ([700 - 13 * i for i in range(10)], 24, 8, 128, 16),      # 80 (sequence, kv head) pairs: clusters of 4
+    ([300 + 7 * i for i in range(20)], 24, 8, 128, 16),       # 160 pairs: clusters of 2
+    ([1 + 11 * i for i in range(40)], 24, 8, 128, 16),        # 320 pairs: one CTA per pair, no cluster
+    ([5000, 33], 8, 2, 128, 32),              # more blocks per CTA than ring stages: the ring wraps
+    ([200, 33, 16], 8, 8, 64, 16),            # head_dim 64 on the tensor-core path, one query head per kv head
+    ([1000], 16, 2, 64, 64),                  # head_dim 64, 8 query heads per kv head, 64-token blocks
 ])
 def test_attention_via_cache(lens, hq, hkv, d, bs):
     got, want = _attention_case(lens, hq, hkv, d, bs, synth.seed_for("attn", len(lens), hq, hkv, d, bs))
