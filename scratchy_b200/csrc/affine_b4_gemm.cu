@@ -2,16 +2,16 @@
 //
 //   y[m,n] = bf16( sum_k x[m,k] * w[n,k] ),  w = the bit-exact bf16 dequantisation of the codes
 //
-// Persistent, warp-specialised CTA (448 threads), one per SM; a tile is TM x 128 tokens by 128
+// Persistent, warp-specialised CTA (704 threads), one per SM; a tile is TM x 128 tokens by 128
 // channels (TM = 2 when M > 128, so every dequantised weight tile feeds two MMAs):
 //   warp 0       producer: per 128-k chunk, 2 x TM TMA tile loads of the activations (tensor map over
 //                x[M,K], 64 x 128 box, 128-byte swizzle; out-of-range rows/k read as zero) and one
 //                1-D bulk copy per row-block of the packed weight blocks (8 x 1152 bytes)
 //   warp 1       owns TMEM; one elected thread issues tcgen05.mma kind::f16 (A = 128 tokens,
 //                B = 128 channels, 8 x K=16 per chunk and token half) and commits the barriers
-//   warps 2-9    dequantise: packed codes (shared) -> bf16 -> the K-major 128-byte-swizzled operand
+//   warps 2-17   dequantise: packed codes (shared) -> bf16 -> the K-major 128-byte-swizzled operand
 //                image the MMA reads (bank-conflict-free 16-byte stores)
-//   warps 10-13  epilogue: tcgen05.ld the 128 x 128 f32 accumulators (thread = token row), round to
+//   warps 18-21  epilogue: tcgen05.ld the 128 x 128 f32 accumulators (thread = token row), round to
 //                bf16 (or keep f32 partials), 16-byte stores
 // TMEM holds 2 buffers x TM accumulators of 128 columns, so the epilogue of tile i overlaps the
 // main loop of tile i+1.  No multicast: every CTA issues its own loads.
@@ -27,8 +27,8 @@ size_t affine_b4_gemm_tc_workspace(int M, int N, int K) {
     return ks > 1 ? (size_t)ks * M * N * sizeof(float) : 0;
 }
 
-#define A4G_THREADS 448
-#define A4G_DQ_WARPS 8
+#define A4G_THREADS 704
+#define A4G_DQ_WARPS 16
 #define A4G_SP 3          // packed-weight stages
 #define A4G_SD 2          // dequantised-weight stages
 #define A4G_BN 128
@@ -181,7 +181,7 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
         }
     }
     else if (warp < 2 + A4G_DQ_WARPS) {
-        // ------------------------------------------------------------------ dequantise (warps 2..9)
+        // ------------------------------------------------------------------ dequantise (warps 2..17)
         const int dw = warp - 2;
         // Lane -> piece of a (row-block, half) pair, arranged so that the eight lanes of a quarter-warp
         // hold four rows and one k-quarter pair: their 16-byte stores then hit eight distinct bank groups.
@@ -197,7 +197,7 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
                 mbar_wait(dempty(sd), phd ^ 1u, status, TC_ERR_EMPTY_WAIT);
                 const uint32_t ps = smem_base + S::kPOff + sp * S::kPStage;
                 const uint32_t ds = smem_base + S::kDOff + sd * S::kDStage;
-                // 16 (row-block, half) pairs per stage, two per warp
+                // 16 (row-block, half) pairs per stage, one per warp
 #pragma unroll
                 for (int u = 0; u < 2 * (BN / 16) / A4G_DQ_WARPS; ++u) {
                     const int pr = dw + u * A4G_DQ_WARPS;
@@ -234,7 +234,7 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
             }
         }
     } else {
-        // ------------------------------------------------------------------ epilogue (warps 10..13)
+        // ------------------------------------------------------------------ epilogue (warps 18..21)
         const int q = warp & 3;                        // TMEM lane quadrant this warp may read
         const bool vec_ok = (N % 8) == 0;
         const float out_scale =
