@@ -374,6 +374,32 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+def measure_fp8_peak(device):
+    """Dense fp8 tensor peak, measured the way the bf16 figure in MEASURED_PEAKS.json was: a library
+    GEMM (`torch._scaled_mm`, e4m3 x e4m3 -> bf16, 8192^3), best of 10, CUDA events.  None if the
+    library call is not available."""
+    import torch
+    try:
+        n = 8192
+        a = torch.randn((n, n), device=device).to(torch.float8_e4m3fn)
+        b = torch.randn((n, n), device=device).to(torch.float8_e4m3fn).t()
+        one = torch.ones((), device=device)
+        for _ in range(3):
+            torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+        torch.cuda.synchronize(device)
+        best = float("inf")
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+            e1.record()
+            torch.cuda.synchronize(device)
+            best = min(best, e0.elapsed_time(e1))
+        return 2.0 * n ** 3 / (best * 1e-3) / 1e12
+    except Exception:
+        return None
+
+
 def run_sweep(device, ctx):
     """Extra (not the headline): per-shape timings over M for int4 (3B shapes) and fp8 (7B shapes).
     Each case cycles over enough distinct weight copies that consecutive calls miss L2, captured
@@ -381,7 +407,9 @@ def run_sweep(device, ctx):
     import torch
     from scratchy_b200 import AffineQuantLinear, Fp8Linear
     peaks = measured_peaks()
-    out = []
+    fp8_peak = measure_fp8_peak(device)
+    out = [{"kind": "peak", "fp8_tflops_scaled_mm_8192": fp8_peak, "fp8_tflops_nominal": 4500.0,
+            "bf16_tflops_measured": peaks["bf16_tflops"], "hbm_gbs_measured": peaks["hbm_gbs"], "hbm_gbs_nominal": 8000.0}]
     side = torch.cuda.Stream(device)
 
     def time_graph(calls, replays):
@@ -441,6 +469,8 @@ def run_sweep(device, ctx):
             out.append({"kind": "fp8", "shape": name, "M": M, "N": N, "K": K, "us": dt * 1e6,
                         "GBps": fp8_alg_bytes(M, N, K) / dt / 1e9, "TFLOPs": 2.0 * M * N * K / dt / 1e12,
                         "frac_hbm": fp8_alg_bytes(M, N, K) / dt / 1e9 / peaks["hbm_gbs"],
+                        "frac_fp8_measured": (2.0 * M * N * K / dt / 1e12 / fp8_peak) if fp8_peak else None,
+                        "frac_fp8_nominal": 2.0 * M * N * K / dt / 1e12 / 4500.0,
                         "note": "per-token quantise + contraction (two launches)"})
         del lins
     return out

@@ -226,3 +226,24 @@ def test_prefill_matches_decode_kernel_rows():
     torch.cuda.synchronize()
     _device_ok()
     assert rel_l2(bits_of(yb[5:6]), bits_of(y1)) <= 2e-4
+
+
+@pytest.mark.parametrize("M", [1, 7, 40])
+def test_rows_concat_equals_its_parts(M):
+    """crates/targets/metal/src/layers_quant.rs:363-450: the fused projection's rows are its parts' rows in
+    order, so its output columns are the parts' outputs side by side — bit for bit."""
+    import torch
+    from scratchy_b200 import AffineQuantLinear, GpuWeights
+    K, rows = 512, {"q": 384, "k": 128, "v": 128}
+    ck, parts = {}, {}
+    for i, (name, n) in enumerate(rows.items()):
+        w, s, b = synth.affine_int4_weights(n, K, 64, 40 + i)
+        ck[f"a.{name}.weight"], ck[f"a.{name}.scales"], ck[f"a.{name}.biases"] = u32_dev(w), bf16_dev(s), bf16_dev(b)
+        parts[name] = make_layer(w, s, b)
+    fused = AffineQuantLinear.load_rows_concat(GpuWeights(ck), ["a.q", "a.k", "a.v"], 64, 4, K)
+    assert fused.out_features == 640 and fused.in_features == K
+    x = bf16_dev(synth.activations_bf16(M, K, 50)).reshape(M, K)
+    got = bits_of(fused.forward(x)).reshape(M, 640)
+    want = np.concatenate([bits_of(parts[n].forward(x)).reshape(M, -1) for n in rows], axis=1)
+    torch.cuda.synchronize()
+    assert np.array_equal(got, want)

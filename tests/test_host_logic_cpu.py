@@ -82,3 +82,53 @@ def test_synthetic_weight_packing_matches_the_checkpoint_nibble_order():
     zero = np.zeros(4, np.uint16)
     wd = oracle.affine_dequant_b4(packed, scale_one, zero, 4, 64, 64)
     assert np.array_equal(oracle.bf16_bits_to_f32(wd).reshape(-1).astype(np.uint8), codes)
+
+
+# ---- `load_rows_concat` (crates/targets/metal/src/layers_quant.rs:363-450): the checks run before any upload
+def _qkv_ckpt(**kw):
+    ck = {}
+    for name, rows in (("q_proj", 32), ("k_proj", 16), ("v_proj", 16)):
+        ck.update(_ckpt(N=rows, K=128, prefix=f"a.{name}", **kw))
+    return ck
+
+
+def test_rows_concat_refuses_an_empty_list_a_bias_and_mismatched_parts():
+    with pytest.raises(ValueError, match="empty prefix list"):
+        AffineQuantLinear.load_rows_concat(GpuWeights(_qkv_ckpt()), [], 64, 4, 128)
+    ck = _qkv_ckpt()
+    ck["a.k_proj.bias"] = torch.zeros(16)
+    with pytest.raises(ValueError, match="carries no bias"):
+        AffineQuantLinear.load_rows_concat(GpuWeights(ck), ["a.q_proj", "a.k_proj"], 64, 4, 128)
+    with pytest.raises(ValueError, match="not a bits=4 packing of in_features=256"):
+        AffineQuantLinear.load_rows_concat(GpuWeights(_qkv_ckpt()), ["a.q_proj"], 64, 4, 256)
+    with pytest.raises(ValueError, match="on disk"):
+        AffineQuantLinear.load_rows_concat(GpuWeights(_qkv_ckpt(scale_dtype=torch.float16)), ["a.q_proj"], 64, 4, 128)
+    with pytest.raises(ValueError, match="no scale dtype pinned"):
+        AffineQuantLinear.load_rows_concat(GpuWeights(_qkv_ckpt(), scale_dtype=None), ["a.q_proj"], 64, 4, 128)
+    ck = _qkv_ckpt()
+    ck["a.v_proj.scales"] = ck["a.v_proj.scales"][:8]
+    with pytest.raises(ValueError, match=r"are not \[16, 2\]"):
+        AffineQuantLinear.load_rows_concat(GpuWeights(ck), ["a.q_proj", "a.v_proj"], 64, 4, 128)
+
+
+def test_rows_concat_leaves_the_parts_in_the_store():
+    gw = GpuWeights(_qkv_ckpt())
+    with pytest.raises(ScratchyCudaError, match="no CPU path"):        # validation passed; the upload refuses CPU tensors
+        AffineQuantLinear.load_rows_concat(gw, ["a.q_proj", "a.k_proj", "a.v_proj"], 64, 4, 128)
+    assert gw.contains("a.q_proj.weight") and gw.contains("a.v_proj.biases")
+
+
+def test_decode_rope_tables_and_checkpoint_shapes():
+    from scratchy_b200 import decode
+    cos, sin = decode.rope_tables(8, 64, 10000.0)
+    assert cos.shape == (8, 64) and np.allclose(cos[0], 1.0) and np.allclose(sin[0], 0.0)
+    assert np.allclose(cos[3, :32], np.cos(3.0 / 10000.0 ** (np.arange(32) * 2 / 64)), atol=1e-6)
+    assert np.array_equal(cos[:, :32], cos[:, 32:])
+    cfg = decode.LlamaConfig(hidden=128, n_layers=1, n_q_heads=2, n_kv_heads=1, head_dim=64, intermediate=256, vocab=64)
+    ck = decode.synthetic_checkpoint(cfg, 0)
+    assert ck["model.layers.0.self_attn.q_proj.weight"].shape == (128, 16)
+    assert ck["model.layers.0.self_attn.k_proj.scales"].shape == (64, 2)
+    assert ck["model.layers.0.mlp.down_proj.weight"].shape == (128, 32)
+    assert ck["lm_head.weight"].shape == (64, 16) and ck["model.embed_tokens.weight"].shape == (64, 128)
+    with pytest.raises(ScratchyCudaError, match="no CPU path"):
+        decode.LlamaDecoder(cfg, ck, "cpu")
