@@ -127,7 +127,9 @@ int32_t scr_e4m3_encode(scr_ctx* ctx, const float* v, int64_t count, uint8_t* ou
  * backends/spyre/kernels/matmul_fp8.py:46-82):
  *   y[m,n] (bf16) = ((sum_k x_q[m,k] * w_q[n,k]) * a_scale[m]) * w_scale[n],  f32 accumulation.
  * `scr_linear_fp8` consumes an activation pack; `scr_linear_fp8_dynamic` is the whole
- * generated Linear (quantise, then contract) and needs a workspace that holds the pack. */
+ * generated Linear (quantise, then contract) and needs a workspace that holds the pack.  For
+ * M <= 4 (and M*K <= 16 KiB of codes) the matvec quantises the activations itself — same x_q and
+ * a_scale bits, one launch, the workspace is not touched. */
 int32_t scr_linear_fp8(scr_ctx* ctx, const void* packed, const void* act, int32_t M, int32_t N,
                        int32_t K, uint16_t* y_bf16, void* workspace, size_t workspace_bytes,
                        void* stream);
@@ -147,6 +149,11 @@ int32_t scr_linear_affine_b4_partial(scr_ctx* ctx, const void* packed, const uin
 int32_t scr_linear_fp8_partial(scr_ctx* ctx, const void* packed, const void* act, int32_t M,
                                int32_t N, int32_t K, float* y_f32, void* workspace,
                                size_t workspace_bytes, void* stream);
+/* The whole row-parallel fp8 linear in one call: quantise this rank's K-slice per token (inside the
+ * matvec for M <= 4, where no pack is written), contract, f32 partials out. */
+int32_t scr_linear_fp8_dynamic_partial(scr_ctx* ctx, const void* packed, const uint16_t* x_bf16,
+                                       int32_t M, int32_t N, int32_t K, float* y_f32,
+                                       void* workspace, size_t workspace_bytes, void* stream);
 int32_t scr_partial_to_bf16(scr_ctx* ctx, const float* in, int64_t count, uint16_t* out_bf16,
                             void* stream);
 

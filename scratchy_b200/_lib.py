@@ -52,6 +52,7 @@ SIGNATURES = {
     "scr_linear_fp8_dynamic": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _sz, _vp]),
     "scr_linear_affine_b4_partial": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _sz, _vp]),
     "scr_linear_fp8_partial": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _sz, _vp]),
+    "scr_linear_fp8_dynamic_partial": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _sz, _vp]),
     "scr_partial_to_bf16": (_i32, [_vp, _vp, _i64, _vp, _vp]),
     "scr_linear_fp8_dynamic_static": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp]),
     "scr_embed_bf16": (_i32, [_vp, _vp, _i32, _vp, _i32, _i32, _vp, _vp]),

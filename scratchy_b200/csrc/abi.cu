@@ -111,6 +111,20 @@ extern "C" int32_t scr_linear_fp8_partial(scr_ctx* ctx, const void* packed, cons
     return st;
 }
 
+extern "C" int32_t scr_linear_fp8_dynamic(scr_ctx*, const void*, const uint16_t*, int32_t, int32_t, int32_t, uint16_t*, void*, size_t,
+                                          void*);
+
+extern "C" int32_t scr_linear_fp8_dynamic_partial(scr_ctx* ctx, const void* packed, const uint16_t* x, int32_t M, int32_t N,
+                                                  int32_t K, float* y_f32, void* workspace, size_t workspace_bytes,
+                                                  void* stream) {
+    if (!ctx) return SCR_E_ARG;
+    ctx->out_f32 = 1;
+    const int32_t st = scr_linear_fp8_dynamic(ctx, packed, x, M, N, K, reinterpret_cast<uint16_t*>(y_f32), workspace,
+                                              workspace_bytes, stream);
+    ctx->out_f32 = 0;
+    return st;
+}
+
 __global__ void partial_to_bf16_kernel(const float* __restrict__ in, long long count, uint16_t* __restrict__ out) {
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
         const __nv_bfloat16 v = __float2bfloat16_rn(in[i]);

@@ -216,16 +216,21 @@ __device__ __forceinline__ void f8_block_compute(uint32_t blk, float acc[2][MT][
     }
 }
 
-template <int MT, int SPLIT_CLUSTER>
+// FUSE_Q: the kernel takes the bf16 activations and quantises them itself (every CTA repeats the
+// per-token absmax and the encode into its own shared memory: a few KB from L2, one launch saved);
+// the arithmetic is the quantise kernel's, statement for statement, so x_q and a_scale are the same bits.
+template <int MT, int SPLIT_CLUSTER, int FUSE_Q>
 __global__ void __launch_bounds__(F8V_THREADS, (MT == 1 ? 3 : 2))
 fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_scale, const uint8_t* __restrict__ xq,
-                const float* __restrict__ a_scale, uint16_t* __restrict__ y, int M, int N, int K16, int KT, int rb_real,
-                int split, int out_f32, int* __restrict__ status) {
-    extern __shared__ __align__(128) uint8_t f8v_ring[];           // [F8V_STAGES][8 blocks of 2 KB]
+                const float* __restrict__ a_scale, const uint16_t* __restrict__ x_bf16, int K, uint16_t* __restrict__ y, int M,
+                int N, int K16, int KT, int rb_real, int split, int out_f32, int* __restrict__ status) {
+    extern __shared__ __align__(128) uint8_t f8v_ring[];           // [F8V_STAGES][8 blocks of 2 KB] (+ x_q [M][K16] when FUSE_Q)
     __shared__ __align__(8) uint64_t full_bar[F8V_STAGES];
     __shared__ __align__(8) uint64_t empty_bar[F8V_STAGES];
     __shared__ float red[2][F8V_CWARPS][32][MT * 4];
     __shared__ float cl_part[SPLIT_CLUSTER ? F8V_MAX_SPLIT : 1][16][MT * 8];
+    __shared__ float q_wmax[F8V_CWARPS];
+    __shared__ float q_scale[8];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -272,9 +277,63 @@ fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_s
         __syncwarp();
     } else {
         asm volatile("griddepcontrol.wait;" ::: "memory");        // the activations are settled
-        const uint8_t* xrow[MT];
+        const uint32_t xs_base = ring_base + F8V_STAGES * F8V_STAGE_BYTES;
+        if (FUSE_Q) {
+            uint8_t* xs = f8v_ring + F8V_STAGES * F8V_STAGE_BYTES;
+            const int tid = threadIdx.x;                          // 0..255: the consumer warps
+            for (int m = 0; m < M; ++m) {
+                const uint16_t* xr = x_bf16 + (size_t)m * K;
+                float amax = 0.f;
+                for (int v = tid; v < K / 8; v += F8V_CWARPS * 32) {
+                    const uint4 q = ld_nc_v4(xr + v * 8);
+                    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) xrow[mt] = xq + (size_t)min(mt * 8 + g, M - 1) * K16;
+                    for (int i = 0; i < 4; ++i) {
+                        amax = fmaxf(amax, fabsf(__uint_as_float(w[i] << 16)));
+                        amax = fmaxf(amax, fabsf(__uint_as_float(w[i] & 0xFFFF0000u)));
+                    }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+                if (lane == 0) q_wmax[warp] = amax;
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                float a = 0.f;
+#pragma unroll
+                for (int i = 0; i < F8V_CWARPS; ++i) a = fmaxf(a, q_wmax[i]);
+                const float sc = fminf(fmaxf(__fmul_rn(a, 1.0f / 448.0f), 1.0f / 448.0f / 448.0f), 448.0f);
+                const float inv = __fdiv_rn(1.0f, sc);
+                if (tid == 0) q_scale[m] = sc;
+                for (int c = tid; c < K16 / 16; c += F8V_CWARPS * 32) {
+                    const int k0 = c * 16;
+                    uint32_t out[4] = {0, 0, 0, 0};
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int kk = k0 + h * 8;
+                        if (kk < K) {
+                            const uint4 q = ld_nc_v4(xr + kk);
+                            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const float lo = fminf(fmaxf(__fmul_rn(__uint_as_float(w[i] << 16), inv), -448.0f), 448.0f);
+                                const float hi = fminf(fmaxf(__fmul_rn(__uint_as_float(w[i] & 0xFFFF0000u), inv), -448.0f), 448.0f);
+                                const uint32_t two = e4m3_encode_ref(lo) | (e4m3_encode_ref(hi) << 8);
+                                out[h * 2 + (i >> 1)] |= two << ((i & 1) * 16);
+                            }
+                        }
+                    }
+                    *reinterpret_cast<uint4*>(xs + (size_t)m * K16 + k0) = make_uint4(out[0], out[1], out[2], out[3]);
+                }
+                asm volatile("bar.sync 1, 256;" ::: "memory");    // q_wmax is reused; x_q of this token is complete
+            }
+        }
+        const float* a_scale_eff = FUSE_Q ? q_scale : a_scale;
+        const uint8_t* xrow[MT];
+        uint32_t xrow_s[MT];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+            xrow[mt] = xq + (size_t)min(mt * 8 + g, M - 1) * K16;
+            xrow_s[mt] = xs_base + (uint32_t)(min(mt * 8 + g, M - 1) * K16);
+        }
         uint32_t n_it = 0;
         int it = 0;
         for (int rb = blockIdx.x; rb < rb_real; rb += gridDim.x, ++it) {
@@ -299,8 +358,13 @@ fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_s
                 uint4 xlo[MT], xhi[MT];
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
-                    xlo[mt] = ld_nc_v4(xrow[mt] + klo);
-                    xhi[mt] = ld_nc_v4(xrow[mt] + khi);
+                    if (FUSE_Q) {
+                        xlo[mt] = f8v_lds_v4(xrow_s[mt] + klo);
+                        xhi[mt] = f8v_lds_v4(xrow_s[mt] + khi);
+                    } else {
+                        xlo[mt] = ld_nc_v4(xrow[mt] + klo);
+                        xhi[mt] = ld_nc_v4(xrow[mt] + khi);
+                    }
                 }
                 f8v_wait(full_base + 8u * slot, (n_it / F8V_STAGES) & 1u, status);
                 if (active) f8_block_compute<MT>(ring_base + slot * F8V_STAGE_BYTES + warp * F8V_BLOCK_BYTES, acc, xlo, xhi, g, t);
@@ -329,7 +393,7 @@ fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_s
                     fp8_st_cluster_rank0_f32(&cl_part[sp][row][tok], total);
                 } else if (n < N) {
                     // (raw * a_scale[m]) * w_scale[n], in that order (ktir_matmul_fp8.rs:676-712)
-                    const float o = __fmul_rn(__fmul_rn(total, a_scale[tok]), w_scale[n]);
+                    const float o = __fmul_rn(__fmul_rn(total, a_scale_eff[tok]), w_scale[n]);
                     if (out_f32) {
                         reinterpret_cast<float*>(y)[(size_t)tok * N + n] = o;
                     } else {
@@ -353,7 +417,7 @@ fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_s
         if (sp == 0 && e < SLOTS && tok < M && n < N) {
             float s = 0.f;
             for (int r = 0; r < split; ++r) s += cl_part[r][row][tok];
-            const float o = __fmul_rn(__fmul_rn(s, a_scale[tok]), w_scale[n]);
+            const float o = __fmul_rn(__fmul_rn(s, (FUSE_Q ? q_scale : a_scale)[tok]), w_scale[n]);
             if (out_f32) {
                 reinterpret_cast<float*>(y)[(size_t)tok * N + n] = o;
             } else {
@@ -464,17 +528,26 @@ static void fp8_gemv_shape(int rb_real, int KC, int sms, int* grid_x, int* split
     *split = best;
 }
 
+// Largest M and x_q footprint the matvec quantises by itself (beyond it the separate quantise kernel runs once).
+#define F8V_FUSE_MAX_M 4
+#define F8V_FUSE_MAX_BYTES (16 * 1024)
+static bool fp8_gemv_fuses_quant(int M, int K) {
+    return M <= F8V_FUSE_MAX_M && K % 8 == 0 && (size_t)M * (scr_ceil_div(K, 16) * 16) <= F8V_FUSE_MAX_BYTES;
+}
+
 template <int MT>
 static int32_t fp8_gemv_launch(scr_ctx* ctx, const uint8_t* wpack, const uint8_t* xq, const float* a_scale, uint16_t* y,
-                               int M, int N, int K, cudaStream_t stream) {
+                               int M, int N, int K, cudaStream_t stream, const uint16_t* x_bf16 = nullptr) {
     const Fp8Geom g = fp8_geom(N, K);
     const float* w_scale = reinterpret_cast<const float*>(wpack + (size_t)g.NT * g.KT * FP8_TILE_BYTES);
     const int K16 = scr_ceil_div(K, 16) * 16;
     const int rb_real = scr_ceil_div(N, 16);
     int grid_x = 1, split = 1;
     fp8_gemv_shape(rb_real, g.KT, ctx->sm_count, &grid_x, &split);
-    constexpr int kRingBytes = F8V_STAGES * F8V_STAGE_BYTES;
-    auto kernel = (split == 1) ? fp8_gemv_kernel<MT, 0> : fp8_gemv_kernel<MT, 1>;
+    const bool fuse = (MT == 1) && x_bf16 != nullptr;
+    const int kRingBytes = F8V_STAGES * F8V_STAGE_BYTES + (fuse ? M * K16 : 0);
+    auto kernel = fuse ? ((split == 1) ? fp8_gemv_kernel<1, 0, 1> : fp8_gemv_kernel<1, 1, 1>)
+                       : ((split == 1) ? fp8_gemv_kernel<MT, 0, 0> : fp8_gemv_kernel<MT, 1, 0>);
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "fp8_gemv smem attribute: %s", cudaGetErrorString(e));
     cudaLaunchConfig_t cfg = {};
@@ -496,7 +569,8 @@ static int32_t fp8_gemv_launch(scr_ctx* ctx, const uint8_t* wpack, const uint8_t
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    e = cudaLaunchKernelEx(&cfg, kernel, wpack, w_scale, xq, a_scale, y, M, N, K16, g.KT, rb_real, split, ctx->out_f32, ctx->dev_status);
+    e = cudaLaunchKernelEx(&cfg, kernel, wpack, w_scale, xq, a_scale, x_bf16, K, y, M, N, K16, g.KT, rb_real, split, ctx->out_f32,
+                           ctx->dev_status);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "fp8_gemv launch: %s", cudaGetErrorString(e));
     return scr_check_launch(ctx, "fp8_gemv");
 }
@@ -550,6 +624,11 @@ extern "C" int32_t scr_linear_fp8_dynamic(scr_ctx* ctx, const void* packed, cons
     int32_t st = fp8_check_shape(ctx, N, K);
     if (st) return st;
     if (M <= 0) return scr_fail(ctx, SCR_E_SHAPE, "M=%d must be positive", M);
+    if (fp8_gemv_fuses_quant(M, K)) {
+        // few tokens: the matvec quantises the activations itself, no pack and no second launch
+        if (!scr_aligned16(packed) || !scr_aligned16(x)) return scr_fail(ctx, SCR_E_ALIGN, "packed/x must be 16-byte aligned");
+        return fp8_gemv_launch<1>(ctx, (const uint8_t*)packed, nullptr, nullptr, y, M, N, K, (cudaStream_t)stream, x);
+    }
     const size_t need = fp8_workspace_bytes(M, N, K);
     if (!workspace || workspace_bytes < need)
         return scr_fail(ctx, SCR_E_WORKSPACE, "workspace %zu bytes < required %zu", workspace_bytes, need);

@@ -346,18 +346,19 @@ class Fp8Linear:
     def forward_partial(self, x: torch.Tensor, out: Optional[torch.Tensor] = None,
                         workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Row-parallel use: quantise this rank's K-slice per token, unrounded f32 sums out
-        (`scr_fp8_quant_per_token` + `scr_linear_fp8_partial`)."""
-        act = self.quantize_activation(x)
-        dev = act.buf.device
+        (`scr_linear_fp8_dynamic_partial`)."""
+        x2 = x.reshape(-1, self.in_features).contiguous()
+        M = int(x2.shape[0])
+        dev = x2.device
         if out is None:
-            out = torch.empty((act.M, self.out_features), dtype=torch.float32, device=dev)
+            out = torch.empty((M, self.out_features), dtype=torch.float32, device=dev)
         ctx = _lib.context(_dev_index(dev))
-        need = self.workspace_bytes(act.M)
+        need = self.workspace_bytes(M)
         if workspace is None or workspace.numel() < need:
             workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
-        ctx.check(_lib.lib().scr_linear_fp8_partial(ctx.handle, _ptr(self.packed), _ptr(act.buf), act.M,
-                                                    self.out_features, self.in_features, _ptr(out), _ptr(workspace),
-                                                    ctypes.c_size_t(workspace.numel()), _stream(dev)))
+        ctx.check(_lib.lib().scr_linear_fp8_dynamic_partial(ctx.handle, _ptr(self.packed), _ptr(x2), M, self.out_features,
+                                                            self.in_features, _ptr(out), _ptr(workspace),
+                                                            ctypes.c_size_t(workspace.numel()), _stream(dev)))
         return out
 
     def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None,

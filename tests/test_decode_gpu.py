@@ -322,3 +322,32 @@ def test_decode_step_matches_oracle_chain(batch):
         ids = want_ids.astype(np.uint32)
     from scratchy_b200 import _lib
     _lib.context(0).device_status(None)
+
+
+def test_decode_ops_against_the_committed_fixture():
+    """tests/golden/decode_ops_small.npz (written by tests/golden/make_golden.py from the oracle)."""
+    import os
+    import torch
+    from scratchy_b200 import decode
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "decode_ops_small.npz"))
+    gain = bf16_dev(g["norm_gain"])
+    assert rel_l2(bits_of(decode.rmsnorm(bf16_dev(g["norm_x"]), gain, 1e-5)), rbits(g["rmsnorm_f32"])) <= REL_L2_TOL
+    res = bf16_dev(g["norm_x"])
+    nrm = decode.fused_add_rmsnorm(res, bf16_dev(g["norm_delta"]), gain, 1e-5)
+    assert np.array_equal(bits_of(res), g["addnorm_residual"])
+    assert rel_l2(bits_of(nrm), rbits(g["addnorm_f32"])) <= REL_L2_TOL
+    gu = bf16_dev(g["silu_gate_up"])
+    assert rel_l2(bits_of(decode.silu_mul(gu[:, :128], gu[:, 128:])), rbits(g["silu_f32"])) <= REL_L2_TOL
+    hq, hkv, hd, bs, _ = (int(v) for v in g["rope_geom"])
+    qkv = bf16_dev(g["rope_qkv"])
+    ck, cv = bf16_dev(g["rope_cache_k_in"]), bf16_dev(g["rope_cache_v_in"])
+    decode.rope_append(qkv[:, :hq * hd], qkv[:, hq * hd:(hq + hkv) * hd], qkv[:, (hq + hkv) * hd:], i32_dev(g["rope_pos"]),
+                       i32_dev(g["rope_slots"]), to_dev(g["rope_cos"]), to_dev(g["rope_sin"]), ck, cv, hq, hkv, hd, bs)
+    assert np.array_equal(bits_of(qkv)[:, :hq * hd], g["rope_q_out"])
+    assert np.array_equal(bits_of(ck), g["rope_cache_k_out"]) and np.array_equal(bits_of(cv), g["rope_cache_v_out"])
+    att = decode.attention_via_cache(bf16_dev(g["attn_q"]), ck, cv, i32_dev(g["attn_table"]), i32_dev(g["attn_lens"]), hq, hkv,
+                                     hd, bs, hd ** -0.5)
+    assert rel_l2(bits_of(att), rbits(g["attn_f32"])) <= REL_L2_TOL
+    ids = decode.argmax(bf16_dev(g["argmax_logits"]))
+    torch.cuda.synchronize()
+    assert np.array_equal(ids.cpu().numpy().view(np.uint32), g["argmax_ids"])

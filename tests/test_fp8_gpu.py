@@ -192,3 +192,26 @@ def test_prefill_gemm_full_size_sampled_rows(name, M):
     r = rel_l2(got, want)
     print(f"{name} M={M} sampled rel_l2={r:.3e} max_abs={max_abs(got, want):.3e}")
     assert r <= REL_L2_TOL
+
+
+@pytest.mark.parametrize("N,K,M", [(3584, 3584, 1), (512, 3584, 4), (18944, 3584, 2), (130, 328, 3), (24, 200, 1),
+                                  (1280, 8192, 2), (8192, 1024, 1), (64, 16384, 1)])
+def test_matvec_quantises_by_itself_with_the_same_bits(N, K, M):
+    """For M <= 4 the whole linear is one launch: the matvec computes a_scale and x_q in shared memory.
+    Its output must equal, bit for bit, the two-step path (quantise kernel, then the matvec on the pack),
+    and the f32 partial variant must equal the pack's partial variant."""
+    import torch
+    from scratchy_b200 import Fp8Linear, _lib
+    wq, ws = oracle.fp8_quantize_weight_per_channel(synth.fp8_weights_f32(N, K, synth.seed_for("fuse", N, K)))
+    layer = make_layer(wq, ws)
+    x = bf16_dev(synth.activations_bf16(M, K, 7)).reshape(M, K)
+    n0 = _lib.context(0).launch_count()
+    fused = layer.forward(x)
+    assert _lib.context(0).launch_count() - n0 == 1, "one launch: no separate quantise kernel"
+    two_step = layer.forward_quantized(Fp8Linear.quantize_activation(x))
+    part = layer.forward_partial(x)
+    torch.cuda.synchronize()
+    assert np.array_equal(bits_of(fused), bits_of(two_step))
+    assert np.array_equal(bits_of(part.to(torch.bfloat16)), bits_of(fused))
+    want = oracle.fp8_dynamic_linear(bits_of(x).reshape(M, K), wq, ws, M, N, K)
+    assert rel_l2(bits_of(fused).reshape(M, N), want) <= REL_L2_TOL
