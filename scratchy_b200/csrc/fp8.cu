@@ -192,7 +192,9 @@ __device__ __forceinline__ uint4 f8v_lds_v4(uint32_t addr) {
 
 #define F8V_CWARPS 8
 #define F8V_THREADS ((F8V_CWARPS + 1) * 32)
-#define F8V_STAGES 4
+// 3 stages of 16 KB: with the static shared memory that is 61 KB per CTA, so three CTAs share an SM (four
+// stages made it two, and the 3-per-SM grid ran as one and a half waves) and a fused x_q of up to 14 KB still fits
+#define F8V_STAGES 3
 #define F8V_BLOCK_BYTES 2048
 #define F8V_STAGE_BYTES (F8V_CWARPS * F8V_BLOCK_BYTES)
 #define F8V_MAX_SPLIT 8
@@ -262,7 +264,7 @@ fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_s
                 // row-block rb = swizzle groups 2j, 2j+1 (j = rb % 8) of tile row rb / 8
                 const uint8_t* src = wpack + ((size_t)(rb >> 3) * KT + kt_lo) * FP8_TILE_BYTES + (size_t)(rb & 7) * F8V_BLOCK_BYTES;
                 for (int j = 0; j < nstage; ++j, ++n_it) {
-                    const uint32_t slot = n_it & (F8V_STAGES - 1);
+                    const uint32_t slot = n_it % F8V_STAGES;
                     f8v_wait(empty_base + 8u * slot, ((n_it / F8V_STAGES) & 1u) ^ 1u, status);
                     const int nblk = min(F8V_CWARPS, kt_hi - kt_lo - j * F8V_CWARPS);
                     const uint32_t bar = full_base + 8u * slot;
@@ -349,7 +351,7 @@ fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_s
             for (int j = 0; j < nstage; ++j, ++n_it) {
                 const int kt = kt_lo + j * F8V_CWARPS + warp;
                 const bool active = kt < kt_hi;                   // warp-uniform
-                const uint32_t slot = n_it & (F8V_STAGES - 1);
+                const uint32_t slot = n_it % F8V_STAGES;
                 // k beyond the row (K16 not a multiple of 128, or an idle warp) meets zero weights
                 // or is not used: read offset 0 instead
                 int klo = kt * 128 + t * 16, khi = klo + 64;
@@ -530,7 +532,7 @@ static void fp8_gemv_shape(int rb_real, int KC, int sms, int* grid_x, int* split
 
 // Largest M and x_q footprint the matvec quantises by itself (beyond it the separate quantise kernel runs once).
 #define F8V_FUSE_MAX_M 4
-#define F8V_FUSE_MAX_BYTES (16 * 1024)
+#define F8V_FUSE_MAX_BYTES (14 * 1024)
 static bool fp8_gemv_fuses_quant(int M, int K) {
     return M <= F8V_FUSE_MAX_M && K % 8 == 0 && (size_t)M * (scr_ceil_div(K, 16) * 16) <= F8V_FUSE_MAX_BYTES;
 }
