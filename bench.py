@@ -528,11 +528,12 @@ def run_decode(device, steps=20, batches=(1, 8, 32), context=2048, block_size=16
 
 def run_tp(device, world, rank):
     """BASELINE config 4: Llama-3-70B-shaped fp8 per-channel linears, tensor parallel over `world`
-    GPUs: column-parallel qkv and gate/up, row-parallel o and down, each followed by an NCCL
-    all-reduce of the f32 partials [M, 8192] and one rounding to bf16.  One "layer" = qkv, o,
-    gate_up, down (attention and the activation function are outside the path; the row-parallel
-    inputs are slices of the preceding outputs).  Weights are random e4m3 bytes of the per-rank
-    shard shapes; three layer copies rotate so that small-M steps read HBM, not L2."""
+    GPUs: column-parallel qkv and gate/up, row-parallel o and down, each followed by the all-reduce
+    of the f32 partials [M, 8192] and one rounding to bf16 — the one-shot peer-memory kernel
+    (`scr_tp_allreduce_partial`) up to M = 64, the process group's NCCL all-reduce above.  One
+    "layer" = qkv, o, gate_up, down (attention and the activation function are outside the path:
+    the row-parallel inputs are fixed buffers of their shapes).  Weights are random e4m3 bytes of
+    the per-rank shard shapes; three layer copies rotate so that small-M steps read HBM, not L2."""
     import torch
     import torch.distributed as dist
     from scratchy_b200 import Fp8Linear, tp as tpmod
@@ -540,6 +541,8 @@ def run_tp(device, world, rank):
     comm = tpmod.TpCommunicator(tpw)
     H, QKV, FF = 8192, 10240, 28672
     copies = 3
+    one_shot_max_m = 64
+    one = tpmod.OneShotAllReduce(tpw, device, max_elems=one_shot_max_m * H)
 
     def lin(n, k, seed):
         g = torch.Generator(device=device)
@@ -559,19 +562,30 @@ def run_tp(device, world, rank):
         bufs = {"qkv": torch.empty((M, QKV // world), dtype=torch.bfloat16, device=device),
                 "gu": torch.empty((M, 2 * FF // world), dtype=torch.bfloat16, device=device),
                 "po": torch.empty((M, H), dtype=torch.float32, device=device),
-                "pd": torch.empty((M, H), dtype=torch.float32, device=device)}
+                "pd": torch.empty((M, H), dtype=torch.float32, device=device),
+                "h": torch.empty((M, H), dtype=torch.bfloat16, device=device),
+                "y": torch.empty((M, H), dtype=torch.bfloat16, device=device),
+                "attn": torch.randn((M, H // world), device=device).to(torch.bfloat16),
+                "act": torch.randn((M, FF // world), device=device).to(torch.bfloat16)}
+        use_one_shot = M <= one_shot_max_m
+
+        def reduce_round(part, dst):
+            if world == 1:                       # nothing to exchange: the partial is the sum
+                dst.copy_(tpmod.partial_to_bf16(part))
+            elif use_one_shot:
+                one.all_reduce(part, out_bf16=dst)
+            else:
+                comm.all_reduce(part)
+                dst.copy_(tpmod.partial_to_bf16(part))
+            return dst
 
         def layer_step(L):
             L["qkv"].forward(x, out=bufs["qkv"], workspace=ws)
-            a = bufs["qkv"][:, :H // world].contiguous()
-            L["o"].forward_partial(a, out=bufs["po"], workspace=ws)
-            comm.all_reduce(bufs["po"])
-            h = tpmod.partial_to_bf16(bufs["po"])
+            L["o"].forward_partial(bufs["attn"], out=bufs["po"], workspace=ws)
+            h = reduce_round(bufs["po"], bufs["h"])
             L["gate_up"].forward(h, out=bufs["gu"], workspace=ws)
-            d = bufs["gu"][:, :FF // world].contiguous()
-            L["down"].forward_partial(d, out=bufs["pd"], workspace=ws)
-            comm.all_reduce(bufs["pd"])
-            return tpmod.partial_to_bf16(bufs["pd"])
+            L["down"].forward_partial(bufs["act"], out=bufs["pd"], workspace=ws)
+            return reduce_round(bufs["pd"], bufs["y"])
 
         def step():
             for L in layers:
@@ -608,7 +622,11 @@ def run_tp(device, world, rank):
         out.append({"M": M, "tp": world, "us_per_layer": us_layer, "layers_per_s": 1e6 / us_layer,
                     "tok_per_s_per_layer": M * 1e6 / us_layer, "TFLOPs_all_gpus": flops / us_layer / 1e6,
                     "weight_GBps_per_gpu": (H * (QKV + H + 3 * FF) / world) / us_layer / 1e3, "launch": mode,
-                    "allreduce": "f32 [M,8192] x2 per layer (NCCL)"})
+                    "allreduce": ("none (one rank)" if world == 1 else
+                                  "f32 [M,8192] x2 per layer, one-shot peer-memory kernel (rank-ordered sum)" if use_one_shot
+                                  else "f32 [M,8192] x2 per layer (NCCL)")})
+        del gr
+    one.close()
     return out
 
 

@@ -208,6 +208,25 @@ int32_t scr_attention_via_cache_bf16(scr_ctx* ctx, const uint16_t* q, int64_t ld
 int32_t scr_argmax_bf16(scr_ctx* ctx, const uint16_t* logits, int64_t ld, int32_t rows,
                         int32_t width, uint32_t* out, void* stream);
 
+/* ---- tensor parallel: the exchange step of a decode layer ---------------------
+ * `SubOp::AllReduce` after a row-parallel linear (crates/compiler/subtile/src/tensor_parallel.rs:
+ * 1342-1393): the ranks' f32 partials are summed in rank order 0..W-1 and rounded once.  For decode
+ * sizes this is one kernel per rank over NVLink peer memory (every rank stores its partials into a
+ * slot it owns on every rank, publishes a flag, waits — bounded — for the others, sums): the result
+ * is the rank-ordered sum bit for bit on every rank.  One process per GPU: each creates its
+ * communicator (the buffer is allocated here, once), the host exchanges the 64-byte handles by any
+ * means (the Python mirror uses torch.distributed) and every rank connects.  All ranks must issue
+ * the same sequence of all-reduce calls.  `count` <= `max_elems`, both multiples of 4. */
+#define SCR_TP_HANDLE_BYTES 64
+typedef struct scr_tp_comm scr_tp_comm;
+int32_t scr_tp_comm_create(scr_ctx* ctx, int32_t world, int32_t rank, int64_t max_elems,
+                           scr_tp_comm** out, uint8_t* handle_out /* SCR_TP_HANDLE_BYTES */);
+int32_t scr_tp_comm_connect(scr_tp_comm* comm, const uint8_t* handles /* world x SCR_TP_HANDLE_BYTES */);
+/* y_bf16 and/or y_f32 receive the reduced [count] values (either may be NULL, not both). */
+int32_t scr_tp_allreduce_partial(scr_tp_comm* comm, const float* partial, int64_t count,
+                                 uint16_t* y_bf16, float* y_f32, void* stream);
+int32_t scr_tp_comm_destroy(scr_tp_comm* comm);
+
 /* No counterpart in the reference.  The same linear as `scr_linear_fp8_dynamic` for callers
  * that cannot allocate device memory on the step path (an arena-owning runtime, code inside a
  * no-allocation region, an FFI shim that owns only inputs and outputs): the activation pack

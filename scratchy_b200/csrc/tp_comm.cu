@@ -1,0 +1,227 @@
+// Tensor-parallel exchange for decode: a one-shot all-reduce over NVLink peer memory.
+//
+// A row-parallel linear (o, down) leaves every rank with f32 partial sums [M, N]; the reference's
+// meaning of the collective that follows is "sum the ranks' operands in rank order"
+// (crates/compiler/subtile/src/tensor_parallel.rs:1350-1362), then round once.  For the few tokens of
+// a decode step the exchange is latency, not bandwidth: one kernel per rank
+//   1. stores its partials into a receive slot it owns in EVERY rank's buffer (plain peer stores),
+//   2. publishes a per-CTA flag on every rank (release, system scope),
+//   3. waits — bounded — for the flags of all ranks for the slices it owns,
+//   4. sums the W received copies in rank order 0..W-1 and rounds to bf16.
+// The result is the rank-ordered sum bit for bit on every rank (a library all-reduce promises no
+// order).  Buffers are cudaMalloc'd per rank and mapped into the peers through CUDA IPC handles that
+// the host exchanges once at start-up; the step path allocates nothing.  No multicast, no TMA here:
+// peer memory is only ever touched by ordinary loads and stores of this kernel.
+//
+// Calls alternate between two halves of the receive area (by a device-side call counter), which is
+// enough: a rank can start call e+1 only after every rank has pushed for call e, i.e. after every rank
+// has finished reading call e-1.  The call counter lives on the device and is advanced by the last CTA
+// of a launch, so a captured CUDA graph replays correctly.
+#include "common.cuh"
+
+#include <string.h>
+
+#include <algorithm>
+#include <new>
+
+#define TPC_MAX_WORLD 8
+#define TPC_MAX_CTAS 256
+#define TPC_THREADS 256
+#define TPC_SLICE (TPC_THREADS * 4)          // f32 elements one CTA moves per pass
+#define TPC_WAIT_LIMIT (1u << 22)
+#define TPC_ERR_FLAG_WAIT 0x0C000001
+
+struct TpcPeers {
+    float* recv[TPC_MAX_WORLD];              // base of each rank's receive area  [2][W][max_elems]
+    unsigned int* flags[TPC_MAX_WORLD];      // base of each rank's flag area     [2][W][TPC_MAX_CTAS]
+};
+
+struct scr_tp_comm {
+    scr_ctx* ctx = nullptr;
+    int world = 1, rank = 0;
+    long long max_elems = 0;
+    size_t bytes = 0, flags_off = 0;
+    unsigned char* local = nullptr;
+    unsigned char* peer[TPC_MAX_WORLD] = {nullptr};
+    bool opened[TPC_MAX_WORLD] = {false};
+    unsigned int* state = nullptr;           // device: [0] = call counter, [1] = CTAs finished in the running call
+    bool connected = false;
+};
+
+namespace {
+
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ float4 ld_cg_f4(const float* p) {
+    float4 v;
+    asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+    return v;
+}
+
+__global__ void __launch_bounds__(TPC_THREADS) tp_allreduce_kernel(TpcPeers peers, int world, int rank, long long max_elems,
+                                                                   const float* __restrict__ partial, long long count,
+                                                                   uint16_t* __restrict__ y_bf16, float* __restrict__ y_f32,
+                                                                   unsigned int* state, int* status) {
+    __shared__ unsigned int s_epoch;
+    const int c = blockIdx.x, tid = threadIdx.x;
+    if (tid == 0) s_epoch = *reinterpret_cast<volatile unsigned int*>(&state[0]) + 1u;
+    __syncthreads();
+    const unsigned int e = s_epoch;
+    const long long half = (long long)(e & 1u) * world;
+
+    // 1. my partials -> my slot in every rank's receive area
+    for (long long base = (long long)c * TPC_SLICE; base < count; base += (long long)gridDim.x * TPC_SLICE) {
+        const long long i = base + tid * 4;
+        if (i < count) {
+            const float4 v = *reinterpret_cast<const float4*>(partial + i);
+            for (int p = 0; p < world; ++p) *reinterpret_cast<float4*>(peers.recv[p] + (half + rank) * max_elems + i) = v;
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    // 2. publish, 3. wait for every rank's copy of my slices (bounded)
+    if (tid < world) {
+        st_release_sys(peers.flags[tid] + (half + rank) * TPC_MAX_CTAS + c, e);
+        const unsigned int* mine = peers.flags[rank] + (half + tid) * TPC_MAX_CTAS + c;
+        bool seen = false;
+        for (unsigned int it = 0; it < TPC_WAIT_LIMIT; ++it) {
+            if ((int)(ld_acquire_sys(mine) - e) >= 0) {
+                seen = true;
+                break;
+            }
+            if ((it & 1023u) == 1023u && *reinterpret_cast<volatile int*>(status) != 0) break;
+        }
+        if (!seen) atomicCAS(status, 0, TPC_ERR_FLAG_WAIT);
+    }
+    __syncthreads();
+    // 4. rank-ordered sum, one rounding
+    const float* mine_recv = peers.recv[rank];
+    for (long long base = (long long)c * TPC_SLICE; base < count; base += (long long)gridDim.x * TPC_SLICE) {
+        const long long i = base + tid * 4;
+        if (i < count) {
+            float4 s = ld_cg_f4(mine_recv + half * max_elems + i);
+            for (int q = 1; q < world; ++q) {
+                const float4 v = ld_cg_f4(mine_recv + (half + q) * max_elems + i);
+                s.x = __fadd_rn(s.x, v.x);
+                s.y = __fadd_rn(s.y, v.y);
+                s.z = __fadd_rn(s.z, v.z);
+                s.w = __fadd_rn(s.w, v.w);
+            }
+            if (y_f32) *reinterpret_cast<float4*>(y_f32 + i) = s;
+            if (y_bf16) {
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(s.x, s.y), hi = __floats2bfloat162_rn(s.z, s.w);
+                *reinterpret_cast<uint2*>(y_bf16 + i) =
+                    make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+            }
+        }
+    }
+    // 5. the last CTA to finish advances the call counter (every CTA has read it by then)
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        const unsigned int done = atomicAdd(&state[1], 1u);
+        if (done == gridDim.x - 1) {
+            state[1] = 0;
+            __threadfence();
+            *reinterpret_cast<volatile unsigned int*>(&state[0]) = e;
+        }
+    }
+}
+
+}  // namespace
+
+extern "C" int32_t scr_tp_comm_create(scr_ctx* ctx, int32_t world, int32_t rank, int64_t max_elems, scr_tp_comm** out,
+                                      uint8_t* handle_out) {
+    SCR_REQUIRE_CTX(ctx);
+    if (!out || !handle_out) return scr_fail(ctx, SCR_E_ARG, "tp comm: null pointer");
+    *out = nullptr;
+    if (!(world == 1 || world == 2 || world == 4 || world == 8) || rank < 0 || rank >= world)
+        return scr_fail(ctx, SCR_E_ARG, "tp comm: world %d / rank %d (worlds 1, 2, 4, 8)", world, rank);
+    if (max_elems <= 0 || max_elems % 4 != 0) return scr_fail(ctx, SCR_E_SHAPE, "tp comm: max_elems must be a positive multiple of 4");
+    static_assert(sizeof(cudaIpcMemHandle_t) == SCR_TP_HANDLE_BYTES, "IPC handle size");
+    scr_tp_comm* c = new (std::nothrow) scr_tp_comm();
+    if (!c) return scr_fail(ctx, SCR_E_CUDA, "tp comm: out of host memory");
+    c->ctx = ctx;
+    c->world = world;
+    c->rank = rank;
+    c->max_elems = max_elems;
+    c->flags_off = ((size_t)2 * world * max_elems * sizeof(float) + 255) & ~(size_t)255;
+    c->bytes = c->flags_off + (size_t)2 * world * TPC_MAX_CTAS * sizeof(unsigned int);
+    cudaError_t e = cudaMalloc((void**)&c->local, c->bytes);
+    if (e == cudaSuccess) e = cudaMemset(c->local, 0, c->bytes);
+    if (e == cudaSuccess) e = cudaMalloc((void**)&c->state, 2 * sizeof(unsigned int));
+    if (e == cudaSuccess) e = cudaMemset(c->state, 0, 2 * sizeof(unsigned int));
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, c->local);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        if (c->local) cudaFree(c->local);
+        if (c->state) cudaFree(c->state);
+        delete c;
+        return scr_fail(ctx, SCR_E_CUDA, "tp comm: %s", cudaGetErrorString(e));
+    }
+    memcpy(handle_out, &h, sizeof(h));
+    c->peer[rank] = c->local;
+    c->connected = (world == 1);
+    *out = c;
+    return SCR_OK;
+}
+
+extern "C" int32_t scr_tp_comm_connect(scr_tp_comm* comm, const uint8_t* handles) {
+    if (!comm || !handles) return SCR_E_ARG;
+    scr_ctx* ctx = comm->ctx;
+    for (int p = 0; p < comm->world; ++p) {
+        if (p == comm->rank || comm->opened[p]) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, handles + (size_t)p * SCR_TP_HANDLE_BYTES, sizeof(h));
+        void* ptr = nullptr;
+        const cudaError_t e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) return scr_fail(ctx, SCR_E_COMM, "tp comm: cannot map rank %d's buffer: %s", p, cudaGetErrorString(e));
+        comm->peer[p] = static_cast<unsigned char*>(ptr);
+        comm->opened[p] = true;
+    }
+    comm->connected = true;
+    return SCR_OK;
+}
+
+extern "C" int32_t scr_tp_allreduce_partial(scr_tp_comm* comm, const float* partial, int64_t count, uint16_t* y_bf16,
+                                            float* y_f32, void* stream) {
+    if (!comm) return SCR_E_ARG;
+    scr_ctx* ctx = comm->ctx;
+    ctx->err[0] = 0;
+    if (!partial || (!y_bf16 && !y_f32)) return scr_fail(ctx, SCR_E_ARG, "tp all-reduce: null pointer");
+    if (!comm->connected) return scr_fail(ctx, SCR_E_COMM, "tp all-reduce: peers are not connected");
+    if (count <= 0 || count % 4 != 0 || count > comm->max_elems)
+        return scr_fail(ctx, SCR_E_SHAPE, "tp all-reduce: count %lld must be a positive multiple of 4, at most %lld", (long long)count,
+                        comm->max_elems);
+    if (!scr_aligned16(partial) || (y_f32 && !scr_aligned16(y_f32)) || (y_bf16 && ((uintptr_t)y_bf16 & 7u)))
+        return scr_fail(ctx, SCR_E_ALIGN, "tp all-reduce: buffers must be 16-byte aligned");
+    TpcPeers peers;
+    for (int p = 0; p < TPC_MAX_WORLD; ++p) {
+        unsigned char* base = comm->peer[p < comm->world ? p : comm->rank];
+        peers.recv[p] = reinterpret_cast<float*>(base);
+        peers.flags[p] = reinterpret_cast<unsigned int*>(base + comm->flags_off);
+    }
+    const int grid = (int)std::min<long long>((count + TPC_SLICE - 1) / TPC_SLICE, TPC_MAX_CTAS);
+    tp_allreduce_kernel<<<grid, TPC_THREADS, 0, (cudaStream_t)stream>>>(peers, comm->world, comm->rank, comm->max_elems, partial,
+                                                                        (long long)count, y_bf16, y_f32, comm->state,
+                                                                        ctx->dev_status);
+    return scr_check_launch(ctx, "tp_allreduce");
+}
+
+extern "C" int32_t scr_tp_comm_destroy(scr_tp_comm* comm) {
+    if (!comm) return SCR_E_ARG;
+    cudaDeviceSynchronize();
+    for (int p = 0; p < comm->world; ++p)
+        if (comm->opened[p]) cudaIpcCloseMemHandle(comm->peer[p]);
+    if (comm->local) cudaFree(comm->local);
+    if (comm->state) cudaFree(comm->state);
+    delete comm;
+    return SCR_OK;
+}

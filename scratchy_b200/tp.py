@@ -105,6 +105,58 @@ class TpCommunicator:
         return t
 
 
+class OneShotAllReduce:
+    """The decode-size exchange: `scr_tp_allreduce_partial`, one kernel per rank over NVLink peer memory,
+    rank-ordered f32 sum and a single rounding (the reference's meaning of AllReduce, bit for bit).
+    Creating it allocates the rank's receive buffer and exchanges the IPC handles through the process
+    group; every rank must then issue the same sequence of calls."""
+
+    def __init__(self, tp: TpWorld, device, max_elems: int, group: Optional[dist.ProcessGroup] = None):
+        import ctypes
+        from . import _lib
+        self.tp, self.max_elems = tp, int(max_elems)
+        self.device = torch.device(device)
+        self._lib = _lib
+        self._ctx = _lib.context(self.device.index if self.device.index is not None else torch.cuda.current_device())
+        self._h = ctypes.c_void_p()
+        handle = (ctypes.c_uint8 * 64)()
+        with torch.cuda.device(self.device):
+            self._ctx.check(_lib.lib().scr_tp_comm_create(self._ctx.handle, tp.world, tp.rank, self.max_elems,
+                                                          ctypes.byref(self._h), handle))
+            if tp.world > 1:
+                if not dist.is_initialized():
+                    raise RuntimeError("torch.distributed is not initialised")
+                gathered = [None] * tp.world
+                dist.all_gather_object(gathered, bytes(handle), group=group)
+                blob = (ctypes.c_uint8 * (64 * tp.world)).from_buffer_copy(b"".join(gathered))
+                self._ctx.check(_lib.lib().scr_tp_comm_connect(self._h, blob))
+                dist.barrier(group=group)
+        self._group = group
+
+    def all_reduce(self, part: torch.Tensor, out_bf16: Optional[torch.Tensor] = None,
+                   out_f32: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """f32 partials in; the reduced values as bf16 (default) and/or f32 out."""
+        import ctypes
+        if part.dtype != torch.float32 or not part.is_cuda or not part.is_contiguous():
+            raise ValueError("partials must be a contiguous f32 CUDA tensor")
+        if out_bf16 is None and out_f32 is None:
+            out_bf16 = torch.empty(part.shape, dtype=torch.bfloat16, device=part.device)
+        self._ctx.check(self._lib.lib().scr_tp_allreduce_partial(
+            self._h, ctypes.c_void_p(part.data_ptr()), part.numel(),
+            ctypes.c_void_p(out_bf16.data_ptr()) if out_bf16 is not None else None,
+            ctypes.c_void_p(out_f32.data_ptr()) if out_f32 is not None else None,
+            ctypes.c_void_p(torch.cuda.current_stream(part.device).cuda_stream)))
+        return out_bf16 if out_bf16 is not None else out_f32
+
+    def close(self) -> None:
+        if self._h:
+            if self.tp.world > 1 and dist.is_initialized():
+                torch.cuda.synchronize(self.device)
+                dist.barrier(group=self._group)           # nobody frees a buffer a peer may still write
+            self._lib.lib().scr_tp_comm_destroy(self._h)
+            self._h = None
+
+
 def partial_to_bf16(part: torch.Tensor) -> torch.Tensor:
     """`scr_partial_to_bf16`: the single rounding after the all-reduce."""
     import ctypes
@@ -119,15 +171,20 @@ def partial_to_bf16(part: torch.Tensor) -> torch.Tensor:
 
 
 class RowParallel:
-    """A row-parallel linear (o, down): local contraction over the rank's K-slice, then the all-reduce."""
+    """A row-parallel linear (o, down): local contraction over the rank's K-slice, then the all-reduce.
+    With a `OneShotAllReduce` the exchange of decode-size outputs is one kernel over peer memory;
+    larger outputs (prefill) go through the process group's all-reduce."""
 
-    def __init__(self, linear, comm: TpCommunicator):
+    def __init__(self, linear, comm: TpCommunicator, one_shot: Optional[OneShotAllReduce] = None):
         self.linear = linear
         self.comm = comm
+        self.one_shot = one_shot
 
     def forward(self, x_local: torch.Tensor, workspace=None) -> torch.Tensor:
         """f32 partials over the rank's K-slice, summed over ranks, rounded to bf16 once."""
         part = self.linear.forward_partial(x_local, workspace=workspace)
+        if self.one_shot is not None and part.numel() <= self.one_shot.max_elems and part.numel() % 4 == 0:
+            return self.one_shot.all_reduce(part)
         self.comm.all_reduce(part)
         return partial_to_bf16(part)
 

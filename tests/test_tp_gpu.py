@@ -85,7 +85,35 @@ def _nccl_worker(rank, world, port, q):
         y = tpmod.RowParallel(flin, comm).forward(tpmod.slice_cols(xt, tp))
         want, _ = lockstep_fp8_row_parallel(wq, ws, x, world)
         ok &= rel_l2(y.view(torch.int16).cpu().numpy().view(np.uint16), want) <= REL_L2_TOL
+        # the one-shot exchange over peer memory: rank-ordered sum, bit for bit, eagerly and replayed from a graph
+        one = tpmod.OneShotAllReduce(tp, dev, max_elems=16 * 1024)
+        rng = np.random.default_rng(7)
+        parts = [rng.standard_normal((5, 1024)).astype(np.float32) * (1.0 + r) for r in range(world)]
+        want_bits = oracle.f32_to_bf16_bits(oracle.allreduce_rank_order(parts))
+        mine = torch.from_numpy(parts[rank]).to(dev)
+        for _ in range(3):                                   # consecutive calls alternate the receive halves
+            got = one.all_reduce(mine)
+            ok &= bool(np.array_equal(got.view(torch.int16).cpu().numpy().view(np.uint16), want_bits))
+        got16 = torch.empty((5, 1024), dtype=torch.bfloat16, device=dev)
+        got32 = torch.empty((5, 1024), dtype=torch.float32, device=dev)
         torch.cuda.synchronize()
+        dist.barrier()
+        side = torch.cuda.Stream(dev)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            one.all_reduce(mine, out_bf16=got16, out_f32=got32)
+        for _ in range(4):
+            got16.zero_()
+            graph.replay()
+            torch.cuda.synchronize()
+            ok &= bool(np.array_equal(got16.view(torch.int16).cpu().numpy().view(np.uint16), want_bits))
+            ok &= bool(np.array_equal(got32.cpu().numpy(), oracle.allreduce_rank_order(parts)))
+        y = tpmod.RowParallel(flin, comm, one_shot=one).forward(tpmod.slice_cols(xt, tp))
+        ok &= rel_l2(y.view(torch.int16).cpu().numpy().view(np.uint16), want) <= REL_L2_TOL
+        torch.cuda.synchronize()
+        _lib_ctx = __import__("scratchy_b200")._lib.context(rank)
+        _lib_ctx.device_status(None)                         # no bounded flag wait ran out
+        one.close()
         q.put((rank, bool(ok)))
     finally:
         dist.destroy_process_group()
@@ -108,3 +136,38 @@ def test_two_ranks_nccl_row_parallel():
     for p in procs:
         p.join(timeout=60)
     assert sorted(res) == [(0, True), (1, True)]
+
+
+def test_one_shot_all_reduce_single_rank():
+    """World size 1 runs the whole kernel on one GPU (push to itself, flag, wait, sum of one operand):
+    indexing, the device-side call counter, the two receive halves and graph replay."""
+    import torch
+    from scratchy_b200 import _lib, tp as tpmod
+    dev = torch.device("cuda", 0)
+    one = tpmod.OneShotAllReduce(tpmod.TpWorld(1, 0), dev, max_elems=300 * 1024)
+    rng = np.random.default_rng(3)
+    for shape in [(1, 8192), (16, 8192), (3, 1028), (1, 4), (37, 8192)]:      # 37 x 8192 > 256 CTAs x 1024: strided slices
+        part = torch.from_numpy(rng.standard_normal(shape).astype(np.float32)).to(dev)
+        got = one.all_reduce(part)
+        f32 = torch.empty(shape, dtype=torch.float32, device=dev)
+        one.all_reduce(part, out_f32=f32)
+        torch.cuda.synchronize()
+        assert np.array_equal(bits_of(got), oracle.f32_to_bf16_bits(part.cpu().numpy()))
+        assert torch.equal(f32, part)
+    part = torch.from_numpy(rng.standard_normal((2, 8192)).astype(np.float32)).to(dev)
+    out = torch.empty((2, 8192), dtype=torch.bfloat16, device=dev)
+    side = torch.cuda.Stream(dev)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        one.all_reduce(part, out_bf16=out)
+    for i in range(5):
+        part.copy_(torch.from_numpy(rng.standard_normal((2, 8192)).astype(np.float32)))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert np.array_equal(bits_of(out), oracle.f32_to_bf16_bits(part.cpu().numpy())), f"replay {i}"
+    _lib.context(0).device_status(None)
+    with pytest.raises(_lib.ScratchyCudaError):
+        one.all_reduce(torch.zeros(301 * 1024, device=dev))                    # beyond max_elems
+    with pytest.raises(_lib.ScratchyCudaError):
+        one.all_reduce(torch.zeros(6, device=dev))                             # not a multiple of 4
+    one.close()
