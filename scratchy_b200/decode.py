@@ -298,14 +298,15 @@ class DecodeBuffers:
 class LlamaDecoder:
     """Random-init or checkpoint-loaded Llama decoder whose every linear is MLX affine int4 g64."""
 
-    def __init__(self, cfg: LlamaConfig, checkpoint: dict, device, max_pos: int = 4096):
+    def __init__(self, cfg: LlamaConfig, checkpoint, device, max_pos: int = 4096):
+        """`checkpoint`: a `GpuWeights` (e.g. `CheckpointWeights.from_dir(...)`) or a dict of host / device
+        tensors with the HF Llama names."""
         if not torch.cuda.is_available():
             raise _lib.ScratchyCudaError(-5, "LlamaDecoder needs a CUDA device (there is no CPU path)")
         self.cfg, self.device = cfg, torch.device(device)
         dev = self.device
-        gw = GpuWeights({k: _to_device(v, dev) for k, v in checkpoint.items()
-                         if k.endswith((".weight", ".scales", ".biases")) and "layernorm" not in k
-                         and k not in ("model.norm.weight", "model.embed_tokens.weight")})
+        gw = checkpoint if isinstance(checkpoint, GpuWeights) else GpuWeights({k: _to_device(v, dev)
+                                                                              for k, v in checkpoint.items()})
         g, h = cfg.group_size, cfg.hidden
         self.layers: List[DecoderLayer] = []
         for i in range(cfg.n_layers):
@@ -318,12 +319,14 @@ class LlamaDecoder:
             for part in ("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "mlp.gate_proj", "mlp.up_proj"):
                 for suffix in ("weight", "scales", "biases"):
                     gw.take(f"{root}.{part}.{suffix}")          # the fused projections are built: drop the parts
-            self.layers.append(DecoderLayer(qkv, o, gate_up, down,
-                                            _to_device(checkpoint[f"{root}.input_layernorm.weight"], dev),
-                                            _to_device(checkpoint[f"{root}.post_attention_layernorm.weight"], dev)))
-        self.final_norm = _to_device(checkpoint["model.norm.weight"], dev)
-        self.embed_table = _to_device(checkpoint["model.embed_tokens.weight"], dev)
+            self.layers.append(DecoderLayer(qkv, o, gate_up, down, gw.take(f"{root}.input_layernorm.weight"),
+                                            gw.take(f"{root}.post_attention_layernorm.weight")))
+        self.final_norm = gw.take("model.norm.weight")
+        self.embed_table = gw.take("model.embed_tokens.weight")
         self.lm_head = AffineQuantLinear.load(gw, "lm_head", g, 4, h)
+        for t in [self.final_norm, self.embed_table] + [x for l in self.layers for x in (l.input_norm, l.post_norm)]:
+            if t.dtype != torch.bfloat16:
+                raise ValueError("norm gains and the embedding table must be bf16 for this build")
         cos, sin = rope_tables(max_pos, cfg.head_dim, cfg.rope_theta)
         self.cos, self.sin = torch.from_numpy(cos).to(dev), torch.from_numpy(sin).to(dev)
         self.attn_scale = 1.0 / math.sqrt(cfg.head_dim)

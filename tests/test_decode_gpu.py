@@ -351,3 +351,36 @@ def test_decode_ops_against_the_committed_fixture():
     ids = decode.argmax(bf16_dev(g["argmax_logits"]))
     torch.cuda.synchronize()
     assert np.array_equal(ids.cpu().numpy().view(np.uint32), g["argmax_ids"])
+
+
+def test_decoder_from_a_safetensors_directory(tmp_path):
+    """Checkpoint files -> mmap -> pinned staging -> device -> repack: the decoder loaded from disk produces
+    the same logits, bit for bit, as the one built from the in-memory tensors."""
+    import torch
+    from scratchy_b200 import decode
+    from scratchy_b200.weights import CheckpointWeights, write_safetensors
+    cfg = decode.LlamaConfig(hidden=256, n_layers=2, n_q_heads=4, n_kv_heads=2, head_dim=64, intermediate=512,
+                             vocab=1024, rope_theta=10000.0)
+    ck = decode.synthetic_checkpoint(cfg, seed=5)
+    on_disk = {k: ((v, "BF16") if v.dtype == np.uint16 else v) for k, v in ck.items()}
+    names = sorted(on_disk)
+    write_safetensors(str(tmp_path / "model-00001-of-00002.safetensors"), {k: on_disk[k] for k in names[::2]})
+    write_safetensors(str(tmp_path / "model-00002-of-00002.safetensors"), {k: on_disk[k] for k in names[1::2]})
+    gw = CheckpointWeights.from_dir(str(tmp_path), "cuda:0")
+    from_disk = decode.LlamaDecoder(cfg, gw, "cuda:0", max_pos=64)
+    assert not gw.contains("model.layers.0.self_attn.q_proj.weight") and not gw.contains("lm_head.scales")
+    in_memory = decode.LlamaDecoder(cfg, ck, "cuda:0", max_pos=64)
+    logits = []
+    for dec in (from_disk, in_memory):
+        cache = decode.PagedKvCache(cfg, 8, 4, "cuda:0")
+        buf = dec.buffers(2, 4)
+        buf.ids.copy_(i32_dev([3, 900]))
+        buf.positions.copy_(i32_dev([0, 5]))
+        buf.block_table.copy_(i32_dev([[0, 1, 2, 3], [4, 5, 6, 7]]))
+        buf.slot_mapping.copy_(i32_dev([0, 21]))
+        buf.seq_used_k.copy_(i32_dev([1, 6]))
+        dec.step(buf, cache)
+        torch.cuda.synchronize()
+        logits.append(bits_of(buf.logits))
+    assert np.array_equal(logits[0], logits[1])
+    gw.close()

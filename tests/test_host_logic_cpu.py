@@ -132,3 +132,62 @@ def test_decode_rope_tables_and_checkpoint_shapes():
     assert ck["lm_head.weight"].shape == (64, 16) and ck["model.embed_tokens.weight"].shape == (64, 128)
     with pytest.raises(ScratchyCudaError, match="no CPU path"):
         decode.LlamaDecoder(cfg, ck, "cpu")
+
+
+# ---- checkpoint files (crates/layers/src/weights.rs:473-520, 847-880)
+def test_safetensors_round_trip_single_file_and_index(tmp_path):
+    import json
+    from scratchy_b200.weights import CheckpointWeights, SafetensorsFile, write_safetensors
+    w, s, b = synth.affine_int4_weights(16, 128, 64, 1)
+    e4 = np.arange(32, dtype=np.uint8).reshape(4, 8)
+    one = tmp_path / "one"
+    one.mkdir()
+    write_safetensors(str(one / "model.safetensors"),
+                      {"a.weight": w, "a.scales": (s, "BF16"), "a.biases": (b, "BF16"), "f.weight": (e4, "F8_E4M3"),
+                       "f.weight_scale": np.linspace(0.1, 0.4, 4, dtype=np.float32)}, {"format": "pt"})
+    f = SafetensorsFile(str(one / "model.safetensors"))
+    assert f.entries["a.weight"][:2] == ("U32", (16, 16)) and f.metadata == {"format": "pt"}
+    gw = CheckpointWeights.from_dir(str(one), "cpu")
+    assert gw.contains("a.scales") and not gw.contains("a.bias")
+    t = gw.take("a.scales")
+    assert t.dtype == torch.bfloat16 and np.array_equal(t.view(torch.int16).numpy().view(np.uint16), s)
+    assert np.array_equal(gw.peek("a.weight").numpy().view(np.uint32), w) and gw.contains("a.weight")
+    assert np.array_equal(gw.take("a.weight").numpy().view(np.uint32), w) and not gw.contains("a.weight")
+    assert gw.take("f.weight").dtype == torch.uint8
+    with pytest.raises(KeyError, match="not found"):
+        gw.take("a.weight")
+    # sharded: an index routes names to shards
+    two = tmp_path / "two"
+    two.mkdir()
+    write_safetensors(str(two / "model-00001-of-00002.safetensors"), {"a.weight": w})
+    write_safetensors(str(two / "model-00002-of-00002.safetensors"), {"a.scales": (s, "BF16"), "a.biases": (b, "BF16")})
+    (two / "model.safetensors.index.json").write_text(json.dumps({"weight_map": {
+        "a.weight": "model-00001-of-00002.safetensors", "a.scales": "model-00002-of-00002.safetensors",
+        "a.biases": "model-00002-of-00002.safetensors"}}))
+    gw = CheckpointWeights.from_dir(str(two), "cpu")
+    assert gw.names() == ["a.biases", "a.scales", "a.weight"]
+    with pytest.raises(ValueError, match="in_features=128.*expects in_features=256"):
+        LinearLayer.load_affine_quant(gw, "a", 64, 4, 256)
+    # unindexed shards are found too; an empty directory is refused like the reference does
+    os_dir = tmp_path / "three"
+    os_dir.mkdir()
+    write_safetensors(str(os_dir / "part.safetensors"), {"x": np.zeros(3, np.float32)})
+    assert CheckpointWeights.from_dir(str(os_dir), "cpu").contains("x")
+    empty = tmp_path / "empty"
+    empty.mkdir()
+    with pytest.raises(FileNotFoundError, match="No safetensors files found"):
+        CheckpointWeights.from_dir(str(empty), "cpu")
+
+
+def test_safetensors_refuses_a_header_that_lies(tmp_path):
+    import json
+    import struct
+    from scratchy_b200.weights import SafetensorsFile
+    hdr = json.dumps({"x": {"dtype": "F32", "shape": [4], "data_offsets": [0, 8]}}).encode()
+    p = tmp_path / "bad.safetensors"
+    p.write_bytes(struct.pack("<Q", len(hdr)) + hdr + bytes(8))
+    with pytest.raises(ValueError, match="spans 8 bytes, its shape needs 16"):
+        SafetensorsFile(str(p))
+    p.write_bytes(bytes([1, 2]))
+    with pytest.raises(ValueError, match="too short"):
+        SafetensorsFile(str(p))
