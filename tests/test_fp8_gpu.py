@@ -197,7 +197,8 @@ def test_prefill_gemm_full_size_sampled_rows(name, M):
 @pytest.mark.parametrize("N,K,M", [(3584, 3584, 1), (512, 3584, 4), (18944, 3584, 2), (130, 328, 3), (24, 200, 1),
                                   (1280, 8192, 2), (8192, 1024, 1), (64, 16384, 1)])
 def test_matvec_quantises_by_itself_with_the_same_bits(N, K, M):
-    """For M <= 4 the whole linear is one launch: the matvec computes a_scale and x_q in shared memory.
+    """For M <= 4 (and up to 14 KiB of codes) the whole linear is one launch: the matvec computes a_scale and x_q in
+    shared memory.
     Its output must equal, bit for bit, the two-step path (quantise kernel, then the matvec on the pack),
     and the f32 partial variant must equal the pack's partial variant."""
     import torch
@@ -207,7 +208,8 @@ def test_matvec_quantises_by_itself_with_the_same_bits(N, K, M):
     x = bf16_dev(synth.activations_bf16(M, K, 7)).reshape(M, K)
     n0 = _lib.context(0).launch_count()
     fused = layer.forward(x)
-    assert _lib.context(0).launch_count() - n0 == 1, "one launch: no separate quantise kernel"
+    fuses = M <= 4 and M * ((K + 15) // 16 * 16) <= 14 * 1024          # beyond that the quantise kernel runs once
+    assert _lib.context(0).launch_count() - n0 == (1 if fuses else 2)
     two_step = layer.forward_quantized(Fp8Linear.quantize_activation(x))
     part = layer.forward_partial(x)
     torch.cuda.synchronize()
