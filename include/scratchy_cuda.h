@@ -195,7 +195,9 @@ int32_t scr_rope_append_bf16(scr_ctx* ctx, const uint16_t* q, int64_t ld_q, cons
 /* `attention_via_cache` (cpu_golden.rs:386-460): one query token per sequence over the paged
  * cache through block_table [batch, max_blocks_per_seq] and seq_used_k [batch]; softmax with
  * inv_sum = 1/(sum_exp + 1e-6); seq_used_k == 0 yields zeros.  head_dim 64 or 128, up to 8
- * query heads per kv head. */
+ * query heads per kv head.  block_table and seq_used_k are runtime bindings the host writes before
+ * the step (the reference's `BlockTable` / `SeqUsedK`): the kernel reads them while the previous
+ * kernel of the stream may still be running, so they must not be outputs of that kernel. */
 int32_t scr_attention_via_cache_bf16(scr_ctx* ctx, const uint16_t* q, int64_t ld_q,
                                      const uint16_t* cache_k, const uint16_t* cache_v,
                                      int32_t num_blocks, const uint32_t* block_table,

@@ -374,9 +374,11 @@ affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __rest
         }
         __syncwarp();
     } else {
+        // one word per matrix says whether any group needs the exact (two-step rounding) path; it is a
+        // load-time constant, so its (cold, HBM) fetch is issued before the wait and hides under it
+        const unsigned int trailer_flag = *reinterpret_cast<const volatile unsigned int*>(packed + (size_t)RB * KC * AFF_BLOCK_BYTES);
         asm volatile("griddepcontrol.wait;" ::: "memory");        // x (and y's previous readers) are settled
-        // one word per matrix says whether any group needs the exact (two-step rounding) path
-        const bool check = *reinterpret_cast<const unsigned int*>(packed + (size_t)RB * KC * AFF_BLOCK_BYTES) != 0;
+        const bool check = trailer_flag != 0;
         if (check)
             gemv_consumer<MT, SPLIT_CLUSTER, true>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, out_f32, status, ring_base,
                                                    full_base, empty_base, red, cl_part);

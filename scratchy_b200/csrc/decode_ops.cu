@@ -103,9 +103,18 @@ __global__ void __launch_bounds__(NORM_THREADS) rmsnorm_kernel(uint16_t* __restr
     extern __shared__ float row[];          // hidden floats
     __shared__ float red[NORM_THREADS / 32];
     pdl_trigger();
+    const int nv = hidden >> 3;
+    // the gains are load-time constants (cold in HBM once per step): fetch this thread's share before the
+    // wait, so that their latency hides under the previous kernel instead of following the reduction
+    constexpr int GAIN_PREFETCH = 4;        // covers hidden <= 8192; beyond that the rest is loaded late
+    uint4 gain[GAIN_PREFETCH];
+#pragma unroll
+    for (int i = 0; i < GAIN_PREFETCH; ++i) {
+        const int v = threadIdx.x + i * NORM_THREADS;
+        gain[i] = v < nv ? ld_nc_v4(weight + v * 8) : make_uint4(0, 0, 0, 0);
+    }
     pdl_wait();
     const size_t base = size_t(blockIdx.x) * hidden;
-    const int nv = hidden >> 3;
     float sum_sq = 0.0f;
     for (int v = threadIdx.x; v < nv; v += NORM_THREADS) {
         float f[8];
@@ -126,9 +135,14 @@ __global__ void __launch_bounds__(NORM_THREADS) rmsnorm_kernel(uint16_t* __restr
     const float total = norm_block_sum(sum_sq, red);
     const float rms = __fsqrt_rn(__fadd_rn(__fdiv_rn(total, float(hidden)), eps));
     const float inv_rms = __fdiv_rn(1.0f, rms);
-    for (int v = threadIdx.x; v < nv; v += NORM_THREADS) {
+    for (int v = threadIdx.x, i = 0; v < nv; v += NORM_THREADS, ++i) {
         float w[8], o[8];
-        unpack8(*reinterpret_cast<const uint4*>(weight + v * 8), w);
+        uint4 gv = make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int u = 0; u < GAIN_PREFETCH; ++u)
+            if (u == i) gv = gain[u];
+        if (i >= GAIN_PREFETCH) gv = *reinterpret_cast<const uint4*>(weight + v * 8);
+        unpack8(gv, w);
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] = __fmul_rn(__fmul_rn(row[v * 8 + j], inv_rms), w[j]);
         *reinterpret_cast<uint4*>(out + base + v * 8) = pack8(o);

@@ -248,6 +248,14 @@ fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_s
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     const int sp = SPLIT_CLUSTER ? int(fp8_cluster_ctarank()) : 0;
+    // cluster mode stores row-block blockIdx.x at the very end: fetch that row's (constant, cold) output
+    // scale now instead of at the tail
+    float ws_final = 0.f;
+    if (SPLIT_CLUSTER && sp == 0) {
+        const int e0 = threadIdx.x, ln0 = e0 / (MT * 4), idx0 = e0 % (MT * 4);
+        const int n0 = blockIdx.x * 16 + (ln0 >> 2) + (((idx0 & 3) >> 1) ? 8 : 0);
+        if (e0 < 32 * MT * 4 && n0 < N) ws_final = w_scale[n0];
+    }
     const int per = (KT + split - 1) / split;
     const int kt_lo = sp * per;
     const int kt_hi = min(KT, kt_lo + per);
@@ -346,6 +354,14 @@ fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_s
                 for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
                     for (int i = 0; i < 4; ++i) acc[a][mt][i] = 0.f;
+            // the output scale of the row this thread will store: a load-time constant, cold in HBM; fetch it
+            // now so that its latency hides under the k loop instead of sitting at the tail
+            float ws_mine = 0.f;
+            {
+                const int e0 = threadIdx.x, ln0 = e0 / (MT * 4), idx0 = e0 % (MT * 4);
+                const int n0 = rb * 16 + (ln0 >> 2) + (((idx0 & 3) >> 1) ? 8 : 0);
+                if (e0 < 32 * MT * 4 && n0 < N) ws_mine = w_scale[n0];
+            }
 
 #pragma unroll 1
             for (int j = 0; j < nstage; ++j, ++n_it) {
@@ -395,7 +411,7 @@ fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_s
                     fp8_st_cluster_rank0_f32(&cl_part[sp][row][tok], total);
                 } else if (n < N) {
                     // (raw * a_scale[m]) * w_scale[n], in that order (ktir_matmul_fp8.rs:676-712)
-                    const float o = __fmul_rn(__fmul_rn(total, a_scale_eff[tok]), w_scale[n]);
+                    const float o = __fmul_rn(__fmul_rn(total, a_scale_eff[tok]), ws_mine);
                     if (out_f32) {
                         reinterpret_cast<float*>(y)[(size_t)tok * N + n] = o;
                     } else {
@@ -419,7 +435,7 @@ fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_s
         if (sp == 0 && e < SLOTS && tok < M && n < N) {
             float s = 0.f;
             for (int r = 0; r < split; ++r) s += cl_part[r][row][tok];
-            const float o = __fmul_rn(__fmul_rn(s, (FUSE_Q ? q_scale : a_scale)[tok]), w_scale[n]);
+            const float o = __fmul_rn(__fmul_rn(s, (FUSE_Q ? q_scale : a_scale)[tok]), ws_final);
             if (out_f32) {
                 reinterpret_cast<float*>(y)[(size_t)tok * N + n] = o;
             } else {
