@@ -542,7 +542,19 @@ def run_tp(device, world, rank):
     H, QKV, FF = 8192, 10240, 28672
     copies = 3
     one_shot_max_m = 64
-    one = tpmod.OneShotAllReduce(tpw, device, max_elems=one_shot_max_m * H)
+    one, one_note = None, None
+    if world > 1:
+        # every rank must take the same path: agree on whether the peer-memory exchange came up everywhere
+        try:
+            one = tpmod.OneShotAllReduce(tpw, device, max_elems=one_shot_max_m * H)
+            ok = torch.ones(1, device=device)
+        except Exception as exc:                                  # e.g. peer access unavailable between two GPUs
+            one_note = f"one-shot exchange unavailable ({type(exc).__name__}); NCCL used"
+            ok = torch.zeros(1, device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if float(ok[0]) == 0.0:
+            one = None
+            one_note = one_note or "one-shot exchange unavailable on another rank; NCCL used"
 
     def lin(n, k, seed):
         g = torch.Generator(device=device)
@@ -567,7 +579,7 @@ def run_tp(device, world, rank):
                 "y": torch.empty((M, H), dtype=torch.bfloat16, device=device),
                 "attn": torch.randn((M, H // world), device=device).to(torch.bfloat16),
                 "act": torch.randn((M, FF // world), device=device).to(torch.bfloat16)}
-        use_one_shot = M <= one_shot_max_m
+        use_one_shot = one is not None and M <= one_shot_max_m
 
         def reduce_round(part, dst):
             if world == 1:                       # nothing to exchange: the partial is the sum
@@ -626,7 +638,15 @@ def run_tp(device, world, rank):
                                   "f32 [M,8192] x2 per layer, one-shot peer-memory kernel (rank-ordered sum)" if use_one_shot
                                   else "f32 [M,8192] x2 per layer (NCCL)")})
         del gr
-    one.close()
+    from scratchy_b200 import _lib
+    try:
+        _lib.context(device.index).device_status(None)
+    except _lib.ScratchyCudaError as exc:                         # a bounded wait ran out somewhere: the numbers are void
+        out.append({"error": str(exc)})
+    if one is not None:
+        one.close()
+    if one_note:
+        out.append({"note": one_note})
     return out
 
 
