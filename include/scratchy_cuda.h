@@ -94,6 +94,15 @@ int32_t scr_linear_workspace_size(int32_t kind, int32_t M, int32_t N, int32_t K,
 int32_t scr_linear_affine_b4(scr_ctx* ctx, const void* packed, const uint16_t* x_bf16,
                              int32_t M, int32_t N, int32_t K, int32_t group, uint16_t* y_bf16,
                              void* workspace, size_t workspace_bytes, void* stream);
+/* The fused gate/up projection with its activation, the `FusedGateUpSiluMul` end of the reference's
+ * matvec (`QmvEnds`, crates/targets/metal/src/tape/step.rs:472-482; golden cpu_golden.rs:211-219):
+ *   out[M, N2/2] (bf16) = silu(bf16(x @ gate^T)) * bf16(x @ up^T)
+ * for a matrix of N2 rows that holds, per block of 16 rows, 8 gate rows then the 8 up rows of the
+ * same channels (the Python mirror's `load_rows_interleave8`).  One launch; M <= 16 only
+ * (SCR_E_UNSUPPORTED above: run `scr_linear_affine_b4` and `scr_silu_mul_pairs8_bf16`). */
+int32_t scr_linear_affine_b4_silu_mul(scr_ctx* ctx, const void* packed, const uint16_t* x_bf16,
+                                      int32_t M, int32_t N2, int32_t K, int32_t group,
+                                      uint16_t* out_bf16, void* stream);
 
 /* ---- fp8-dynamic-per-channel: load-time repack ----------------------------
  * Replaces the `load_layered_fp8...` loaders the reference's codegen names but no live
@@ -179,6 +188,11 @@ int32_t scr_fused_add_rmsnorm_bf16(scr_ctx* ctx, uint16_t* residual, const uint1
  * gate and up have row stride ld_in (halves of one fused gate/up output), out is dense [rows, inter]. */
 int32_t scr_silu_mul_bf16(scr_ctx* ctx, const uint16_t* gate, const uint16_t* up, int64_t ld_in,
                           uint16_t* out, int32_t rows, int32_t inter, void* stream);
+/* The same on a fused gate/up output whose columns interleave gate and up in runs of 8 (8 gate
+ * columns, then the 8 up columns of the same channels) — the row order `scr_linear_affine_b4_silu_mul`
+ * expects of its matrix; used above 16 tokens, where that fused epilogue is not available. */
+int32_t scr_silu_mul_pairs8_bf16(scr_ctx* ctx, const uint16_t* gate_up, int64_t ld_in, uint16_t* out,
+                                 int32_t rows, int32_t inter, void* stream);
 /* `rope_append` (cpu_golden.rs:289-362): NeoX pairing, f32 cos/sin tables [max_pos, head_dim]
  * (first half of each row read); q_out = rotated q (may be q itself); rotated k and unrotated v
  * go to global slot slot_mapping[t] of the paged caches [num_blocks, num_kv_heads, block_size,

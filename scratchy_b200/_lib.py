@@ -42,6 +42,7 @@ SIGNATURES = {
     "scr_affine_b4_dequant_dump": (_i32, [_vp, _vp, _i32, _i32, _i32, _vp, _vp]),
     "scr_linear_workspace_size": (_i32, [_i32, _i32, _i32, _i32, _psz]),
     "scr_linear_affine_b4": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _sz, _vp]),
+    "scr_linear_affine_b4_silu_mul": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp]),
     "scr_fp8_repack_size": (_i32, [_i32, _i32, _psz]),
     "scr_fp8_repack": (_i32, [_vp, _vp, _vp, _i32, _i32, _vp, _vp]),
     "scr_fp8_act_size": (_i32, [_i32, _i32, _psz]),
@@ -63,6 +64,7 @@ SIGNATURES = {
     "scr_rmsnorm_bf16": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, ctypes.c_float, _vp]),
     "scr_fused_add_rmsnorm_bf16": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, ctypes.c_float, _vp]),
     "scr_silu_mul_bf16": (_i32, [_vp, _vp, _vp, _i64, _vp, _i32, _i32, _vp]),
+    "scr_silu_mul_pairs8_bf16": (_i32, [_vp, _vp, _i64, _vp, _i32, _i32, _vp]),
     "scr_rope_append_bf16": (_i32, [_vp, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _i32, _vp, _i64, _vp, _vp,
                                     _i32, _i32, _i32, _i32, _i32, _i32, _vp]),
     "scr_attention_via_cache_bf16": (_i32, [_vp, _vp, _i64, _vp, _vp, _i32, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32,

@@ -242,6 +242,29 @@ __device__ __forceinline__ void gemv_block_compute(uint32_t blk, float acc[2][MT
     }
 }
 
+// Output modes of the matvec epilogue (the `out_f32` argument): bf16, unrounded f32 partials, or the
+// gate/up pairing: the matrix holds, per 16-row block, 8 gate rows then the 8 up rows of the same
+// channels (the loader's `load_rows_interleave8`), so gate_i and up_i end up in the same lane two
+// accumulator slots apart; the lane holding the gate sum takes the up sum by shuffle and stores
+// bf16(silu(bf16(gate)) * bf16(up)) — the value the separate silu*up kernel computes from the two
+// bf16 outputs (crates/targets/metal/src/cpu_golden.rs:211-219), one launch saved.
+#define GEMV_OUT_BF16 0
+#define GEMV_OUT_F32 1
+#define GEMV_OUT_SILU_PAIRS 2
+
+// Called by all 32 lanes of a warp.  `total` is this lane's (row, token) sum; bit 1 of `idx` says
+// whether the row is a gate row (0) or the up row 8 below it (1).
+__device__ __forceinline__ void gemv_store_silu_pair(float total, int idx, int tok, int M, int channel, int channels,
+                                                     uint16_t* __restrict__ y) {
+    const float other = __shfl_xor_sync(0xffffffffu, total, 2);
+    if ((idx & 2) == 0 && tok < M && channel < channels) {
+        const float g = __bfloat162float(__float2bfloat16_rn(total));
+        const float u = __bfloat162float(__float2bfloat16_rn(other));
+        const __nv_bfloat16 v = __float2bfloat16_rn(__fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u));
+        y[(size_t)tok * channels + channel] = *reinterpret_cast<const uint16_t*>(&v);
+    }
+}
+
 template <int MT, int SPLIT_CLUSTER, bool CHECK>
 __device__ __forceinline__ void gemv_consumer(const uint16_t* __restrict__ x, uint16_t* __restrict__ y, int M, int N,
                                               int K, int kc_lo, int kc_hi, int nstage, int rb_real, int split, int sp,
@@ -302,13 +325,15 @@ __device__ __forceinline__ void gemv_consumer(const uint16_t* __restrict__ x, ui
         const int row = (ln >> 2) + (((idx & 3) >> 1) ? 8 : 0);
         const int tok = (idx >> 2) * 8 + (ln & 3) * 2 + (idx & 1);
         const int n = rb * 16 + row;
-        if (e < SLOTS && tok < M) {
+        if (e < SLOTS) {                       // warp-uniform: SLOTS is a multiple of 32
             float total = 0.f;
 #pragma unroll
             for (int wdx = 0; wdx < GEMV_CWARPS; ++wdx) total += red[buf][wdx][ln][idx];
             if (SPLIT_CLUSTER) {
-                gemv_st_cluster_rank0_f32(&cl_part[sp][row][tok], total);
-            } else if (n < N) {
+                if (tok < M) gemv_st_cluster_rank0_f32(&cl_part[sp][row][tok], total);
+            } else if (out_f32 == GEMV_OUT_SILU_PAIRS) {
+                gemv_store_silu_pair(total, idx, tok, M, rb * 8 + (ln >> 2), N >> 1, y);
+            } else if (tok < M && n < N) {
                 if (out_f32) {
                     reinterpret_cast<float*>(y)[(size_t)tok * N + n] = total;
                 } else {
@@ -396,7 +421,11 @@ affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __rest
         const int row = (ln >> 2) + (((idx & 3) >> 1) ? 8 : 0);
         const int tok = (idx >> 2) * 8 + (ln & 3) * 2 + (idx & 1);
         const int n = blockIdx.x * 16 + row;
-        if (sp == 0 && e < SLOTS && tok < M && n < N) {
+        if (sp == 0 && e < SLOTS && out_f32 == GEMV_OUT_SILU_PAIRS) {
+            float s = 0.f;
+            for (int r = 0; r < split; ++r) s += cl_part[r][row][min(tok, MT * 8 - 1)];
+            gemv_store_silu_pair(s, idx, tok, M, blockIdx.x * 8 + (ln >> 2), N >> 1, y);
+        } else if (sp == 0 && e < SLOTS && tok < M && n < N) {
             float s = 0.f;
             for (int r = 0; r < split; ++r) s += cl_part[r][row][tok];
             if (out_f32) {
@@ -562,4 +591,16 @@ extern "C" int32_t scr_linear_affine_b4(scr_ctx* ctx, const void* packed, const 
         if (st) return st;
     }
     return SCR_OK;
+}
+
+extern "C" int32_t scr_linear_affine_b4_silu_mul(scr_ctx* ctx, const void* packed, const uint16_t* x, int32_t M, int32_t N2,
+                                                 int32_t K, int32_t group, uint16_t* out, void* stream_) {
+    SCR_REQUIRE_CTX(ctx);
+    if (M > 16) return scr_fail(ctx, SCR_E_UNSUPPORTED, "fused silu*up epilogue: M=%d (the matvec path, M <= 16, has it)", M);
+    if (N2 <= 0 || N2 % 16 != 0) return scr_fail(ctx, SCR_E_SHAPE, "fused silu*up epilogue: %d fused rows (8 gate + 8 up per block)", N2);
+    if (ctx->out_f32 != 0) return scr_fail(ctx, SCR_E_ARG, "fused silu*up epilogue: partial output requested at the same time");
+    ctx->out_f32 = GEMV_OUT_SILU_PAIRS;
+    const int32_t st = scr_linear_affine_b4(ctx, packed, x, M, N2, K, group, out, nullptr, 0, stream_);
+    ctx->out_f32 = 0;
+    return st;
 }

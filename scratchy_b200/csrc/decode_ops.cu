@@ -150,16 +150,18 @@ __global__ void __launch_bounds__(NORM_THREADS) rmsnorm_kernel(uint16_t* __restr
 }
 
 // ------------------------------------------------------------------------------- silu(gate) * up
+// `vstride` = 8 for gate and up as two dense halves, 16 when the fused output interleaves them in runs of 8
+// columns (8 gate, then the 8 up of the same channels: the layout of the matvec's pairing epilogue).
 __global__ void silu_mul_kernel(const uint16_t* __restrict__ gate, const uint16_t* __restrict__ up, long long ld_in,
-                                uint16_t* __restrict__ out, int inter_v, long long total_v) {
+                                uint16_t* __restrict__ out, int inter_v, long long total_v, int vstride) {
     pdl_trigger();
     pdl_wait();
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total_v; i += (long long)gridDim.x * blockDim.x) {
         const long long r = i / inter_v;
         const int v = int(i - r * inter_v);
         float g[8], u[8], o[8];
-        unpack8(*reinterpret_cast<const uint4*>(gate + r * ld_in + v * 8), g);
-        unpack8(*reinterpret_cast<const uint4*>(up + r * ld_in + v * 8), u);
+        unpack8(*reinterpret_cast<const uint4*>(gate + r * ld_in + v * vstride), g);
+        unpack8(*reinterpret_cast<const uint4*>(up + r * ld_in + v * vstride), u);
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] = __fmul_rn(__fdiv_rn(g[j], __fadd_rn(1.0f, expf(-g[j]))), u[j]);
         *reinterpret_cast<uint4*>(out + (r * inter_v + v) * 8) = pack8(o);
@@ -941,9 +943,25 @@ extern "C" int32_t scr_fused_add_rmsnorm_bf16(scr_ctx* ctx, uint16_t* residual, 
     return norm_launch(ctx, true, residual, delta, weight, out, rows, hidden, eps, stream);
 }
 
+static int32_t silu_mul_launch(scr_ctx* ctx, const uint16_t* gate, const uint16_t* up, int64_t ld_in, uint16_t* out, int32_t rows,
+                               int32_t inter, int vstride, void* stream);
+
 extern "C" int32_t scr_silu_mul_bf16(scr_ctx* ctx, const uint16_t* gate, const uint16_t* up, int64_t ld_in, uint16_t* out,
                                      int32_t rows, int32_t inter, void* stream) {
     SCR_REQUIRE_CTX(ctx);
+    return silu_mul_launch(ctx, gate, up, ld_in, out, rows, inter, 8, stream);
+}
+
+extern "C" int32_t scr_silu_mul_pairs8_bf16(scr_ctx* ctx, const uint16_t* gate_up, int64_t ld_in, uint16_t* out, int32_t rows,
+                                            int32_t inter, void* stream) {
+    SCR_REQUIRE_CTX(ctx);
+    if (!gate_up) return scr_fail(ctx, SCR_E_ARG, "silu_mul: null pointer");
+    if (ld_in < 2 * (int64_t)inter) return scr_fail(ctx, SCR_E_SHAPE, "silu_mul: ld_in=%lld is shorter than 2*inter", (long long)ld_in);
+    return silu_mul_launch(ctx, gate_up, gate_up + 8, ld_in, out, rows, inter, 16, stream);
+}
+
+static int32_t silu_mul_launch(scr_ctx* ctx, const uint16_t* gate, const uint16_t* up, int64_t ld_in, uint16_t* out, int32_t rows,
+                               int32_t inter, int vstride, void* stream) {
     DEC_REQUIRE(gate && up && out, SCR_E_ARG, "silu_mul: null pointer");
     DEC_REQUIRE(rows >= 0 && inter > 0 && inter % 8 == 0 && ld_in >= inter && ld_in % 8 == 0, SCR_E_SHAPE,
                 "silu_mul: inter=%d and ld_in=%lld must be multiples of 8 with ld_in >= inter", inter, (long long)ld_in);
@@ -953,7 +971,7 @@ extern "C" int32_t scr_silu_mul_bf16(scr_ctx* ctx, const uint16_t* gate, const u
     const int threads = 256;
     const int blocks = int(std::min<long long>((total_v + threads - 1) / threads, (long long)ctx->sm_count * 8));
     cudaError_t e = launch_pdl(silu_mul_kernel, dim3(blocks), dim3(threads), 0, (cudaStream_t)stream, gate, up, (long long)ld_in,
-                               out, inter / 8, total_v);
+                               out, inter / 8, total_v, vstride);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "silu_mul: %s", cudaGetErrorString(e));
     return scr_check_launch(ctx, "silu_mul");
 }

@@ -314,7 +314,7 @@ class LlamaDecoder:
             qkv = AffineQuantLinear.load_rows_concat(
                 gw, [f"{root}.self_attn.q_proj", f"{root}.self_attn.k_proj", f"{root}.self_attn.v_proj"], g, 4, h)
             o = AffineQuantLinear.load(gw, f"{root}.self_attn.o_proj", g, 4, cfg.q_dim)
-            gate_up = AffineQuantLinear.load_rows_concat(gw, [f"{root}.mlp.gate_proj", f"{root}.mlp.up_proj"], g, 4, h)
+            gate_up = AffineQuantLinear.load_rows_interleave8(gw, f"{root}.mlp.gate_proj", f"{root}.mlp.up_proj", g, 4, h)
             down = AffineQuantLinear.load(gw, f"{root}.mlp.down_proj", g, 4, cfg.intermediate)
             for part in ("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "mlp.gate_proj", "mlp.up_proj"):
                 for suffix in ("weight", "scales", "biases"):
@@ -361,8 +361,7 @@ class LlamaDecoder:
                                 cfg.n_kv_heads, cfg.head_dim, cache.block_size, self.attn_scale, out=buf.attn)
             layer.o.forward(buf.attn, out=buf.delta, workspace=buf.workspace)
             fused_add_rmsnorm(buf.residual, buf.delta, layer.post_norm, cfg.rms_eps, out=buf.normed)
-            layer.gate_up.forward(buf.normed, out=buf.gate_up, workspace=buf.workspace)
-            silu_mul(buf.gate_up[:, :cfg.intermediate], buf.gate_up[:, cfg.intermediate:], out=buf.act)
+            layer.gate_up.forward_silu_mul(buf.normed, out=buf.act, scratch=buf.gate_up, workspace=buf.workspace)
             layer.down.forward(buf.act, out=buf.delta, workspace=buf.workspace)
             nxt = self.layers[i + 1].input_norm if i + 1 < len(self.layers) else self.final_norm
             fused_add_rmsnorm(buf.residual, buf.delta, nxt, cfg.rms_eps, out=buf.normed)

@@ -81,6 +81,7 @@ class AffineQuantLinear:
     bits: int
     linear_bias: Optional[torch.Tensor] = None
     source: Optional[dict] = field(default=None, repr=False)
+    pairs8: bool = False        # rows interleaved 8 gate / 8 up (see `load_rows_interleave8`)
 
     # ---- MetalAffineQuantOps::load (layers_quant.rs:289-345)
     @classmethod
@@ -113,12 +114,9 @@ class AffineQuantLinear:
         return cls.from_tensors(weight, scales, affine_biases, group_size, bits, linear_bias, keep_source)
 
     # ---- MetalAffineQuantOps::load_rows_concat (layers_quant.rs:363-450): fused QKV / gate-up
-    @classmethod
-    def load_rows_concat(cls, weights: GpuWeights, prefixes, group_size: int, bits: int,
-                         expected_in_features: int) -> "AffineQuantLinear":
-        """One projection made of several projections' rows, in order.  A group runs along K, so a
-        row dequantises from its own codes, scale and bias wherever it sits.  A part's linear bias
-        is refused, not dropped; the parts stay in the store."""
+    @staticmethod
+    def _collect_parts(weights: GpuWeights, prefixes, group_size: int, bits: int, expected_in_features: int):
+        """The checks of `load_rows_concat` (layers_quant.rs:363-430); returns the parts' codes, scales, biases."""
         if not prefixes:
             raise ValueError("AffineQuantLinear::load_rows_concat: empty prefix list")
         compiled = weights.rmsnorm_scale_dtype()
@@ -153,7 +151,59 @@ class AffineQuantLinear:
             codes.append(w)
             scales.append(sc)
             biases.append(b)
+        return codes, scales, biases
+
+    # ---- MetalAffineQuantOps::load_rows_concat (layers_quant.rs:363-450): fused QKV / gate-up
+    @classmethod
+    def load_rows_concat(cls, weights: GpuWeights, prefixes, group_size: int, bits: int,
+                         expected_in_features: int) -> "AffineQuantLinear":
+        """One projection made of several projections' rows, in order.  A group runs along K, so a
+        row dequantises from its own codes, scale and bias wherever it sits.  A part's linear bias
+        is refused, not dropped; the parts stay in the store."""
+        codes, scales, biases = cls._collect_parts(weights, prefixes, group_size, bits, expected_in_features)
         return cls.from_tensors(torch.cat(codes, 0), torch.cat(scales, 0), torch.cat(biases, 0), group_size, bits)
+
+    @classmethod
+    def load_rows_interleave8(cls, weights: GpuWeights, gate_prefix: str, up_prefix: str, group_size: int, bits: int,
+                              expected_in_features: int) -> "AffineQuantLinear":
+        """The fused gate/up projection in the row order of the fused silu*up epilogue: per 16 rows, 8 gate
+        rows then the 8 up rows of the same channels.  Same checks as `load_rows_concat`."""
+        (w, wu), (sc, su), (b, bu) = cls._collect_parts(weights, [gate_prefix, up_prefix], group_size, bits,
+                                                        expected_in_features)
+        inter = int(w.shape[0])
+        if w.shape[0] != wu.shape[0]:
+            raise ValueError("gate/up interleave: the two projections differ in out_features")
+        if inter % 8:
+            raise ValueError(f"gate/up interleave: {inter} channels per projection is not a multiple of 8")
+
+        def weave(a, c):
+            return torch.stack([a.reshape(inter // 8, 8, -1), c.reshape(inter // 8, 8, -1)], dim=1).reshape(2 * inter, -1)
+        out = cls.from_tensors(weave(w, wu), weave(sc, su), weave(b, bu), group_size, bits)
+        out.pairs8 = True
+        return out
+
+    def forward_silu_mul(self, x: torch.Tensor, out: Optional[torch.Tensor] = None,
+                         scratch: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """`silu(x @ gate^T) * (x @ up^T)` on a matrix built by `load_rows_interleave8`: one launch up to 16
+        tokens (`scr_linear_affine_b4_silu_mul`), the linear into `scratch` plus `scr_silu_mul_pairs8_bf16` above."""
+        if not getattr(self, "pairs8", False):
+            raise ValueError("forward_silu_mul needs a gate/up matrix built by load_rows_interleave8")
+        x2 = x.reshape(-1, self.in_features).contiguous()
+        M, inter = int(x2.shape[0]), self.out_features // 2
+        dev = x2.device
+        if out is None:
+            out = torch.empty((M, inter), dtype=torch.bfloat16, device=dev)
+        ctx = _lib.context(_dev_index(dev))
+        if M <= 16:
+            ctx.check(_lib.lib().scr_linear_affine_b4_silu_mul(ctx.handle, _ptr(self.packed), _ptr(x2), M, self.out_features,
+                                                               self.in_features, self.group_size, _ptr(out), _stream(dev)))
+            return out
+        if scratch is None:
+            scratch = torch.empty((M, self.out_features), dtype=torch.bfloat16, device=dev)
+        self.forward(x2, out=scratch, workspace=workspace)
+        ctx.check(_lib.lib().scr_silu_mul_pairs8_bf16(ctx.handle, _ptr(scratch), int(scratch.stride(0)), _ptr(out), M, inter,
+                                                      _stream(dev)))
+        return out
 
     @classmethod
     def from_tensors(cls, weight: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor, group_size: int = 64,

@@ -250,3 +250,39 @@ def test_rows_concat_equals_its_parts(M):
     wd = np.concatenate([bits_of(parts[n].dequantize()) for n in rows], axis=0)
     assert np.array_equal(bits_of(fused.dequantize()), wd)
     assert rel_l2(got, want) <= 1e-4 and np.mean(got == want) > 0.99
+
+
+@pytest.mark.parametrize("M", [1, 5, 16, 40])
+@pytest.mark.parametrize("inter,K", [(1024, 512), (200, 256), (8192, 3072)])
+def test_gate_up_with_fused_silu_mul(M, inter, K):
+    """`FusedGateUpSiluMul` (crates/targets/metal/src/cpu_golden.rs:211-219) as the matvec's epilogue: against the
+    oracle (two linears rounded to bf16, then silu*up in f32), and — up to 16 tokens — bit for bit against the
+    unfused path on the same interleaved matrix (linear, then the pairing silu*up kernel)."""
+    import torch
+    from scratchy_b200 import AffineQuantLinear, GpuWeights, _lib
+    from util import bf16_to_f32
+    ck, host = {}, {}
+    for i, name in enumerate(("gate", "up")):
+        w, s, b = synth.affine_int4_weights(inter, K, 64, synth.seed_for("gu", inter, K) + i)
+        host[name] = (w, s, b)
+        ck[f"m.{name}.weight"], ck[f"m.{name}.scales"], ck[f"m.{name}.biases"] = u32_dev(w), bf16_dev(s), bf16_dev(b)
+    lin = AffineQuantLinear.load_rows_interleave8(GpuWeights(ck), "m.gate", "m.up", 64, 4, K)
+    xb = synth.activations_bf16(M, K, 77)
+    x = bf16_dev(xb).reshape(M, K)
+    n0 = _lib.context(0).launch_count()
+    got = bits_of(lin.forward_silu_mul(x)).reshape(M, inter)
+    launches = _lib.context(0).launch_count() - n0
+    torch.cuda.synchronize()
+    g, u = (oracle.affine_qmm_t_b4(host[n][0].view(np.uint8).reshape(-1), host[n][1], host[n][2], xb, M, inter, K, 64)
+            for n in ("gate", "up"))
+    want = synth.f32_to_bf16_bits(oracle.silu_mul(bf16_to_f32(g), bf16_to_f32(u)))
+    assert rel_l2(got, want) <= REL_L2_TOL
+    if M <= 16:
+        assert launches == 1
+        fused_cols = lin.forward(x)                                   # [M, 2*inter], 8 gate / 8 up columns alternating
+        ctx = _lib.context(0)
+        two_step = torch.empty((M, inter), dtype=torch.bfloat16, device="cuda")
+        ctx.check(_lib.lib().scr_silu_mul_pairs8_bf16(ctx.handle, fused_cols.data_ptr(), 2 * inter, two_step.data_ptr(), M, inter,
+                                                      None))
+        torch.cuda.synchronize()
+        assert np.array_equal(got, bits_of(two_step).reshape(M, inter))
