@@ -71,7 +71,7 @@ class ClockSampler:
         self.p = None
         try:
             self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                       "-i", str(gpu_index), "-lms", "100"], stdout=self.f, stderr=subprocess.DEVNULL)
+                                       "-i", str(gpu_index), "-lms", "20"], stdout=self.f, stderr=subprocess.DEVNULL)
         except Exception:
             self.p = None
 
@@ -106,22 +106,31 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------ reference arm
-def cpu_linears(threads_note=True):
+_CPU_DATA = None
+
+
+def cpu_linears():
+    """The 7 int4 linears of one Llama-3.2-3B layer (synthetic, seeded), built once per process."""
+    global _CPU_DATA
     import oracle
-    shapes = [synth.LLAMA_3_2_3B[n] for n in LAYER_ORDER]
-    data = []
-    for i, (K, N) in enumerate(shapes):
-        w, s, b = synth.affine_int4_weights(N, K, 64, 100 + i)
-        x = synth.activations_bf16(1, K, 200 + i)
-        data.append((w.view(np.uint8).reshape(-1), s, b, x, N, K))
-    return oracle, data
+    if _CPU_DATA is None:
+        data = []
+        for i, name in enumerate(LAYER_ORDER):
+            K, N = synth.LLAMA_3_2_3B[name]
+            w, s, b = synth.affine_int4_weights(N, K, 64, 100 + i)
+            x = synth.activations_bf16(1, K, 200 + i)
+            data.append((w.view(np.uint8).reshape(-1), s, b, x, N, K))
+        _CPU_DATA = data
+    return oracle, _CPU_DATA
 
 
-def time_cpu_layer(reps: int):
-    """One 'sample' = the 7 int4 linears of one Llama-3.2-3B layer at M = 1 through the oracle."""
+def time_cpu_layer(reps: int, n_lin: int = 7):
+    """One 'sample' = the first `n_lin` of the 7 int4 linears of one Llama-3.2-3B layer at M = 1 through the
+    oracle; returns (algorithmic GB/s, seconds per sample, threads)."""
     oracle, data = cpu_linears()
+    data = data[:n_lin]
     byts = sum(affine_alg_bytes(1, N, K) for *_, N, K in data)
-    oracle.affine_qmm_t_b4(*data[1][:4], 1, data[1][4], data[1][5], 64)    # warm the thread pool
+    oracle.affine_qmm_t_b4(*data[0][:4], 1, data[0][4], data[0][5], 64)    # warm the thread pool
     t0 = time.perf_counter()
     for _ in range(reps):
         for pk, s, b, x, N, K in data:
@@ -131,26 +140,33 @@ def time_cpu_layer(reps: int):
 
 
 def run_reference(args):
+    """The reference arm: the reference's own CPU arithmetic for the path (the C++/OpenMP restatement — the Rust
+    sources cannot be built here) on all host threads.  A step is a bounded sample of the GPU arm's step: the
+    first n of one layer's 7 linears, n sized so that warm-up plus K steps stay within about two minutes."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    _, t_layer, _ = time_cpu_layer(1)
+    n_lin = max(1, min(7, int(7 * 120.0 / (max(args.steps + args.warmup, 1) * max(t_layer, 1e-3)))))
     for _ in range(max(args.warmup, 1)):
-        time_cpu_layer(1)
+        time_cpu_layer(1, n_lin)
     vals = []
     t_all = 0.0
     for _ in range(args.steps):
-        v, dt, cores = time_cpu_layer(1)
+        v, dt, cores = time_cpu_layer(1, n_lin)
         vals.append(v)
         t_all += dt
     value = float(np.mean(vals))
+    names = ",".join(LAYER_ORDER[:n_lin])
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * t_all / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "llama-3.2-3b int4 g64 linears (q,k,v,o,gate,up,down), M=1",
-                   "step": "one layer (7 linears) on the host cores: a bounded sample of the 28-layer GPU step"},
+                   "step": f"{n_lin} linear(s) of one layer ({names}) on the host cores: a bounded sample of the "
+                           "28-layer GPU step"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": "7 linears of one layer per step, C++/OpenMP restatement of "
+                         "sample": f"{n_lin} of one layer's 7 linears per step ({names}), C++/OpenMP restatement of "
                                    "cpu_reference::affine_qmm_t_b4 (the Rust reference cannot be built here)"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -245,11 +261,12 @@ def run_gpu(args):
         step()
     launches_per_step = ctx.launch_count() - l0
 
-    # ---- device-resident timing
+    # ---- device-resident timing (the clock sampler runs from the warm-up on, so that even a short timed
+    # region has samples taken under this load beside it)
+    sampler = ClockSampler(local_rank) if rank == 0 else None
     for _ in range(args.warmup):
         graph.replay()
     barrier()
-    sampler = ClockSampler(local_rank) if rank == 0 else None
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     ev0.record()
@@ -731,8 +748,8 @@ def run_case_attention(device, batch, context, reps, layers=28, block_size=16):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--sweep", action="store_true")
     ap.add_argument("--serial", action="store_true", help="one branch: every linear waits for the previous one")
