@@ -104,6 +104,20 @@ int32_t scr_linear_affine_b4_silu_mul(scr_ctx* ctx, const void* packed, const ui
                                       int32_t M, int32_t N2, int32_t K, int32_t group,
                                       uint16_t* out_bf16, void* stream);
 
+/* The o / down projection with the residual add and the following RMSNorm folded in (the reference's
+ * `QmvEnds` residual end, step.rs:472-482, and `fused_add_rmsnorm`, cpu_golden.rs:171-200), one launch:
+ *   residual[M,N] <- bf16(residual + bf16(x @ W^T));  normed[M,N] <- rmsnorm(residual, gain, eps)
+ * The last CTA to finish normalises the rows (partial sums of squares are added in CTA order:
+ * deterministic).  `scratch`: SCR_ENDS_SCRATCH_BYTES of device memory, zeroed once by the caller before
+ * the first call and left zeroed; calls that may overlap on the GPU need their own.  M <= 16 only
+ * (SCR_E_UNSUPPORTED above: run `scr_linear_affine_b4` and `scr_fused_add_rmsnorm_bf16`); N % 8 == 0. */
+#define SCR_ENDS_SCRATCH_BYTES 65536
+int32_t scr_linear_affine_b4_residual_rmsnorm(scr_ctx* ctx, const void* packed, const uint16_t* x_bf16,
+                                              int32_t M, int32_t N, int32_t K, int32_t group,
+                                              uint16_t* residual, const uint16_t* gain, float eps,
+                                              uint16_t* normed, void* scratch, size_t scratch_bytes,
+                                              void* stream);
+
 /* ---- fp8-dynamic-per-channel: load-time repack ----------------------------
  * Replaces the `load_layered_fp8...` loaders the reference's codegen names but no live
  * target implements (Metal refuses fp8: crates/targets/metal/compiler/src/steps_from_tape.rs:2009).
@@ -210,8 +224,10 @@ int32_t scr_rope_append_bf16(scr_ctx* ctx, const uint16_t* q, int64_t ld_q, cons
  * cache through block_table [batch, max_blocks_per_seq] and seq_used_k [batch]; softmax with
  * inv_sum = 1/(sum_exp + 1e-6); seq_used_k == 0 yields zeros.  head_dim 64 or 128, up to 8
  * query heads per kv head.  block_table and seq_used_k are runtime bindings the host writes before
- * the step (the reference's `BlockTable` / `SeqUsedK`): the kernel reads them while the previous
- * kernel of the stream may still be running, so they must not be outputs of that kernel. */
+ * the step (the reference's `BlockTable` / `SeqUsedK`): the kernel reads them, and streams every
+ * cache block except each sequence's last one, while the previous kernels of the stream may still
+ * be running — those kernels may produce q and the cache slot of token seq_used_k - 1 (what
+ * `scr_rope_append_bf16` does in a decode step), nothing else this call reads. */
 int32_t scr_attention_via_cache_bf16(scr_ctx* ctx, const uint16_t* q, int64_t ld_q,
                                      const uint16_t* cache_k, const uint16_t* cache_v,
                                      int32_t num_blocks, const uint32_t* block_table,

@@ -43,6 +43,8 @@ SIGNATURES = {
     "scr_linear_workspace_size": (_i32, [_i32, _i32, _i32, _i32, _psz]),
     "scr_linear_affine_b4": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _sz, _vp]),
     "scr_linear_affine_b4_silu_mul": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp]),
+    "scr_linear_affine_b4_residual_rmsnorm": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, ctypes.c_float, _vp,
+                                                     _vp, _sz, _vp]),
     "scr_fp8_repack_size": (_i32, [_i32, _i32, _psz]),
     "scr_fp8_repack": (_i32, [_vp, _vp, _vp, _i32, _i32, _vp, _vp]),
     "scr_fp8_act_size": (_i32, [_i32, _i32, _psz]),

@@ -265,14 +265,93 @@ __device__ __forceinline__ void gemv_store_silu_pair(float total, int idx, int t
     }
 }
 
+// GEMV_OUT_RESIDUAL_NORM: the o / down projection with the ends the reference folds around its matvec
+// (`QmvEnds`, crates/targets/metal/src/tape/step.rs:472-482), i.e. `fused_add_rmsnorm`
+// (crates/targets/metal/src/cpu_golden.rs:171-200) without a kernel of its own:
+//   residual[m,n] <- bf16(residual[m,n] + bf16(y[m,n]))          in the epilogue, element by element
+//   normed[m,:]   <- rmsnorm(residual[m,:], gain, eps)           by the last CTA to finish
+// Every CTA leaves the sum of squares of the residual values it stored (per token) in `scratch`, takes a
+// ticket, and the CTA that draws the last ticket adds the partial sums in CTA order (deterministic),
+// and normalises the rows.  `scratch` = the ticket counter (16 floats reserved), then [gridDim.x][16] f32; the
+// counter must be zero before the first call and is left zero.
+#define GEMV_OUT_RESIDUAL_NORM 3
+struct GemvEnds {
+    uint16_t* residual;
+    const uint16_t* gain;
+    uint16_t* normed;
+    float* scratch;         // [0] = ticket counter (as u32), [16 + cta*16 + token] = the CTAs' sums of squares
+    float eps;
+};
+
+__device__ __forceinline__ float gemv_bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+// The epilogue's element step: returns the square of the stored residual (0 outside the matrix).
+__device__ __forceinline__ float gemv_residual_update(float total, int tok, int M, int n, int N, const GemvEnds& ends) {
+    if (tok >= M || n >= N) return 0.f;
+    uint16_t* p = ends.residual + (size_t)tok * N + n;
+    const float r = gemv_bf16_round(__fadd_rn(__uint_as_float(uint32_t(*p) << 16), gemv_bf16_round(total)));
+    const __nv_bfloat16 rb = __float2bfloat16_rn(r);
+    *p = *reinterpret_cast<const uint16_t*>(&rb);
+    return __fmul_rn(r, r);
+}
+
+// The tail: called by `nthreads` threads of the CTA (a multiple of 32, thread ids 0..nthreads-1), all of which
+// reach every barrier `bar_id`.  `my_sq` = this CTA's sum of squares for token threadIdx.x (threads < M).
+__device__ __forceinline__ void gemv_norm_tail(float my_sq, int M, int N, int ncta, int cta, const GemvEnds& ends, int bar_id,
+                                               int nthreads) {
+    __shared__ int s_last;
+    __shared__ float s_inv[16];
+    const int tid = threadIdx.x;
+    if (tid < M) ends.scratch[16 + cta * 16 + tid] = my_sq;
+    __threadfence();
+    asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(nthreads) : "memory");
+    if (tid == 0) {
+        unsigned int* counter = reinterpret_cast<unsigned int*>(ends.scratch);
+        const unsigned int ticket = atomicAdd(counter, 1u);
+        s_last = (ticket == (unsigned int)ncta - 1u);
+        if (s_last) *counter = 0u;                   // every CTA has drawn: leave it ready for the next call
+        __threadfence();
+    }
+    asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(nthreads) : "memory");
+    if (!s_last) return;
+    // sum of squares per token, partials in CTA order: lane l adds CTAs l, l+32, ... then a fixed shuffle tree
+    const int warp = tid >> 5, lane = tid & 31, nwarps = nthreads >> 5;
+    for (int tok = warp; tok < M; tok += nwarps) {
+        float a = 0.f;
+        for (int c = lane; c < ncta; c += 32) a = __fadd_rn(a, __ldcg(ends.scratch + 16 + c * 16 + tok));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, o));
+        if (lane == 0) s_inv[tok] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(a, float(N)), ends.eps)));
+    }
+    asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(nthreads) : "memory");
+    const int nv = N >> 3;                           // N % 8 == 0 is checked on the host for this mode
+    for (int i = tid; i < M * nv; i += nthreads) {
+        const int tok = i / nv, v = i - tok * nv;
+        const uint4 rv = __ldcg(reinterpret_cast<const uint4*>(ends.residual + (size_t)tok * N) + v);
+        const uint4 gv = *reinterpret_cast<const uint4*>(ends.gain + v * 8);
+        const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w}, gw[4] = {gv.x, gv.y, gv.z, gv.w};
+        const float inv = s_inv[tok];
+        uint32_t ow[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float lo = __fmul_rn(__fmul_rn(__uint_as_float(rw[j] << 16), inv), __uint_as_float(gw[j] << 16));
+            const float hi = __fmul_rn(__fmul_rn(__uint_as_float(rw[j] & 0xFFFF0000u), inv), __uint_as_float(gw[j] & 0xFFFF0000u));
+            const __nv_bfloat162 pk = __floats2bfloat162_rn(lo, hi);
+            ow[j] = *reinterpret_cast<const uint32_t*>(&pk);
+        }
+        reinterpret_cast<uint4*>(ends.normed + (size_t)tok * N)[v] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+}
+
 template <int MT, int SPLIT_CLUSTER, bool CHECK>
 __device__ __forceinline__ void gemv_consumer(const uint16_t* __restrict__ x, uint16_t* __restrict__ y, int M, int N,
                                               int K, int kc_lo, int kc_hi, int nstage, int rb_real, int split, int sp,
                                               int out_f32, int* __restrict__ status, uint32_t ring_base, uint32_t full_base,
                                               uint32_t empty_base, float (*red)[GEMV_CWARPS][32][MT * 4],
-                                              float (*cl_part)[16][MT * 8]) {
+                                              float (*cl_part)[16][MT * 8], const GemvEnds& ends, float (*sq_s)[16][16]) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
+    float cta_sq = 0.f;                        // RESIDUAL_NORM: thread tok's sum of squares over this CTA's row-blocks
     // activation rows this lane feeds into the B operand.  Tokens beyond M read a clamped (valid)
     // row: a column of B only reaches the same column of D, which is discarded for tokens >= M.
     const uint16_t* xrow[MT];
@@ -333,6 +412,8 @@ __device__ __forceinline__ void gemv_consumer(const uint16_t* __restrict__ x, ui
                 if (tok < M) gemv_st_cluster_rank0_f32(&cl_part[sp][row][tok], total);
             } else if (out_f32 == GEMV_OUT_SILU_PAIRS) {
                 gemv_store_silu_pair(total, idx, tok, M, rb * 8 + (ln >> 2), N >> 1, y);
+            } else if (out_f32 == GEMV_OUT_RESIDUAL_NORM) {
+                sq_s[buf][tok][row] = gemv_residual_update(total, tok, M, n, N, ends);
             } else if (tok < M && n < N) {
                 if (out_f32) {
                     reinterpret_cast<float*>(y)[(size_t)tok * N + n] = total;
@@ -342,15 +423,25 @@ __device__ __forceinline__ void gemv_consumer(const uint16_t* __restrict__ x, ui
                 }
             }
         }
+        if (!SPLIT_CLUSTER && out_f32 == GEMV_OUT_RESIDUAL_NORM) {
+            gemv_consumer_sync();              // sq_s[buf] is complete (red[buf] is not reused before the next sync either)
+            if (threadIdx.x < M) {
+#pragma unroll
+                for (int r = 0; r < 16; ++r) cta_sq = __fadd_rn(cta_sq, sq_s[buf][threadIdx.x][r]);
+            }
+        }
     }
+    if (!SPLIT_CLUSTER && out_f32 == GEMV_OUT_RESIDUAL_NORM)
+        gemv_norm_tail(cta_sq, M, N, gridDim.x, blockIdx.x, ends, 1, GEMV_CWARPS * 32);
 }
 
 template <int MT, int SPLIT_CLUSTER>
 __global__ void __launch_bounds__(GEMV_THREADS, (MT == 1 ? 3 : 2))
 affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __restrict__ x, uint16_t* __restrict__ y,
                       int M, int N, int K, int RB, int KC, int rb_real, int split, int out_f32,
-                      int* __restrict__ status) {
+                      int* __restrict__ status, GemvEnds ends) {
     extern __shared__ __align__(128) uint8_t gemv_ring[];          // [GEMV_STAGES][8 blocks]
+    __shared__ float sq_s[2][16][16];                              // RESIDUAL_NORM: squares of the stored residuals [token][row]
     __shared__ __align__(8) uint64_t full_bar[GEMV_STAGES];
     __shared__ __align__(8) uint64_t empty_bar[GEMV_STAGES];
     __shared__ float red[2][GEMV_CWARPS][32][MT * 4];
@@ -406,10 +497,10 @@ affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __rest
         const bool check = trailer_flag != 0;
         if (check)
             gemv_consumer<MT, SPLIT_CLUSTER, true>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, out_f32, status, ring_base,
-                                                   full_base, empty_base, red, cl_part);
+                                                   full_base, empty_base, red, cl_part, ends, sq_s);
         else
             gemv_consumer<MT, SPLIT_CLUSTER, false>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, out_f32, status, ring_base,
-                                                    full_base, empty_base, red, cl_part);
+                                                    full_base, empty_base, red, cl_part, ends, sq_s);
     }
 
     if (SPLIT_CLUSTER) {
@@ -421,7 +512,23 @@ affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __rest
         const int row = (ln >> 2) + (((idx & 3) >> 1) ? 8 : 0);
         const int tok = (idx >> 2) * 8 + (ln & 3) * 2 + (idx & 1);
         const int n = blockIdx.x * 16 + row;
-        if (sp == 0 && e < SLOTS && out_f32 == GEMV_OUT_SILU_PAIRS) {
+        if (out_f32 == GEMV_OUT_RESIDUAL_NORM) {
+            if (sp != 0) return;                   // the cluster's CTA 0 owns the row-block's output (block-uniform exit)
+            if (e < 256) sq_s[0][e >> 4][e & 15] = 0.f;
+            __syncthreads();
+            if (e < SLOTS) {
+                float s = 0.f;
+                for (int r = 0; r < split; ++r) s += cl_part[r][row][tok];
+                sq_s[0][tok][row] = gemv_residual_update(s, tok, M, n, N, ends);
+            }
+            __syncthreads();
+            float cta_sq = 0.f;
+            if (e < M) {
+#pragma unroll
+                for (int r = 0; r < 16; ++r) cta_sq = __fadd_rn(cta_sq, sq_s[0][e][r]);
+            }
+            gemv_norm_tail(cta_sq, M, N, gridDim.x, blockIdx.x, ends, 2, GEMV_THREADS);
+        } else if (sp == 0 && e < SLOTS && out_f32 == GEMV_OUT_SILU_PAIRS) {
             float s = 0.f;
             for (int r = 0; r < split; ++r) s += cl_part[r][row][min(tok, MT * 8 - 1)];
             gemv_store_silu_pair(s, idx, tok, M, blockIdx.x * 8 + (ln >> 2), N >> 1, y);
@@ -548,7 +655,14 @@ static int32_t affine_gemv_launch(scr_ctx* ctx, const uint8_t* packed, const uin
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    e = cudaLaunchKernelEx(&cfg, kernel, packed, x, y, M, N, K, g.RB, g.KC, rb_real, split, ctx->out_f32, ctx->dev_status);
+    GemvEnds ends = {};
+    if (ctx->out_f32 == GEMV_OUT_RESIDUAL_NORM) {
+        if (!ctx->gemv_ends) return scr_fail(ctx, SCR_E_ARG, "residual + norm epilogue requested without its arguments");
+        ends = *static_cast<const GemvEnds*>(ctx->gemv_ends);
+        if ((size_t)(16 + grid_x * 16) * sizeof(float) > SCR_ENDS_SCRATCH_BYTES)
+            return scr_fail(ctx, SCR_E_WORKSPACE, "residual + norm epilogue: %d CTAs exceed the scratch", grid_x);
+    }
+    e = cudaLaunchKernelEx(&cfg, kernel, packed, x, y, M, N, K, g.RB, g.KC, rb_real, split, ctx->out_f32, ctx->dev_status, ends);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine_b4_gemv launch: %s", cudaGetErrorString(e));
     return scr_check_launch(ctx, "affine_b4_gemv");
 }
@@ -591,6 +705,29 @@ extern "C" int32_t scr_linear_affine_b4(scr_ctx* ctx, const void* packed, const 
         if (st) return st;
     }
     return SCR_OK;
+}
+
+extern "C" int32_t scr_linear_affine_b4_residual_rmsnorm(scr_ctx* ctx, const void* packed, const uint16_t* x, int32_t M,
+                                                         int32_t N, int32_t K, int32_t group, uint16_t* residual,
+                                                         const uint16_t* gain, float eps, uint16_t* normed, void* scratch,
+                                                         size_t scratch_bytes, void* stream_) {
+    SCR_REQUIRE_CTX(ctx);
+    if (M > 16) return scr_fail(ctx, SCR_E_UNSUPPORTED, "fused residual + norm epilogue: M=%d (the matvec path, M <= 16, has it)", M);
+    if (!residual || !gain || !normed || !scratch) return scr_fail(ctx, SCR_E_ARG, "fused residual + norm epilogue: null pointer");
+    if (N <= 0 || N % 8 != 0) return scr_fail(ctx, SCR_E_SHAPE, "fused residual + norm epilogue: N=%d must be a multiple of 8", N);
+    if (scratch_bytes < SCR_ENDS_SCRATCH_BYTES)
+        return scr_fail(ctx, SCR_E_WORKSPACE, "fused residual + norm epilogue: scratch %zu bytes < %d", scratch_bytes, SCR_ENDS_SCRATCH_BYTES);
+    if (!scr_aligned16(residual) || !scr_aligned16(gain) || !scr_aligned16(normed) || !scr_aligned16(scratch))
+        return scr_fail(ctx, SCR_E_ALIGN, "fused residual + norm epilogue: pointers must be 16-byte aligned");
+    if (ctx->out_f32 != 0) return scr_fail(ctx, SCR_E_ARG, "fused residual + norm epilogue: another output mode is active");
+    const GemvEnds ends = {residual, gain, normed, static_cast<float*>(scratch), eps};
+    ctx->out_f32 = GEMV_OUT_RESIDUAL_NORM;
+    ctx->gemv_ends = &ends;
+    // y is not written in this mode; the residual buffer stands in for the (unused) output pointer
+    const int32_t st = scr_linear_affine_b4(ctx, packed, x, M, N, K, group, residual, nullptr, 0, stream_);
+    ctx->out_f32 = 0;
+    ctx->gemv_ends = nullptr;
+    return st;
 }
 
 extern "C" int32_t scr_linear_affine_b4_silu_mul(scr_ctx* ctx, const void* packed, const uint16_t* x, int32_t M, int32_t N2,

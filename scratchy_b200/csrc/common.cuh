@@ -15,7 +15,8 @@ struct scr_ctx {
     int sm_count = 0;
     int cc_major = 0, cc_minor = 0;
     std::atomic<long long> launches{0};
-    int out_f32 = 0;                // set by the *_partial entry points for the duration of a call
+    int out_f32 = 0;                // output mode of the matvec epilogue, set by the variant entry points for one call
+    const void* gemv_ends = nullptr;    // arguments of the residual + norm epilogue for the same call
     int* dev_status = nullptr;      // device word: first bounded wait that ran out (0 = none)
     char err[256] = {0};
 };

@@ -642,7 +642,10 @@ __global__ void __launch_bounds__(ATTB_THREADS) attention_decode_tc_kernel(
         fence_mbar_init();
     }
     __syncthreads();
-    pdl_wait();                                      // q and the newest cache slot come from the previous kernels
+    // What the previous kernels of the stream produce for this one is q and the cache slot of the newest token
+    // (position kv_len - 1, in the sequence's last block).  Every other cache block was written in earlier steps,
+    // so the producer starts streaming them at once and only the last block, and the consumers' q, wait.
+    const int newest_blk = total_blk - 1;
 
     if (warp == nwarps) {
         // ---------------- producer: lane s owns ring stage s and issues, in order, every block that passes
@@ -655,9 +658,14 @@ __global__ void __launch_bounds__(ATTB_THREADS) attention_decode_tc_kernel(
             const int w = lane / spw, r = lane - w * spw;
             const uint32_t full = smem_u32(&bars[lane]);
             const uint32_t dst = smem_u32(ring + size_t(lane) * 2 * chunk);
+            bool waited = false;
             for (int n = 0;; ++n) {
                 const int i = w + nwarps * (r + spw * n);
                 if (i >= nblk) break;
+                if (!waited && first_blk + i >= newest_blk) {
+                    pdl_wait();
+                    waited = true;
+                }
                 if (n >= 1 && !mbar_wait(smem_u32(&bars[stages + lane]), uint32_t((n - 1) & 1), status, ATT_ERR_EMPTY)) break;
                 const int token0 = int((blocks[i] * uint32_t(num_kv_heads) + uint32_t(kvh)) * uint32_t(block_size));
                 mbar_arrive_expect_tx(full, 2 * chunk);
@@ -671,6 +679,7 @@ __global__ void __launch_bounds__(ATTB_THREADS) attention_decode_tc_kernel(
         __syncwarp();
     } else {
         // ---------------- consumers: warp w owns blocks w, w+8, ...
+        pdl_wait();
         const int row = lane >> 2, quad = lane & 3;
         uint32_t qa0[KSTEPS], qa2[KSTEPS];             // A fragments of Q: row = query head (zero beyond G), 16 dims per step
 #pragma unroll

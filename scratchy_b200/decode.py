@@ -2,7 +2,10 @@
 
 Host-side mirror of the reference's decode program (embed -> per layer [rmsnorm, fused QKV, RoPE +
 paged-KV append, paged decode attention, o, residual add + rmsnorm, fused gate/up, silu*up, down] ->
-final norm -> lm_head -> greedy argmax).  Each operator wrapper names the reference host golden it is
+final norm -> lm_head -> greedy argmax).  Up to 16 tokens silu*up runs as the epilogue of the gate/up matvec.
+The residual add + rmsnorm can run as the epilogue of the o / down matvecs too (`fuse_residual_norm=True`), but
+that measured slower than the separate kernel (the ticket and the last CTA's serial pass cost more than the
+launch they save), so it is off by default.  Each operator wrapper names the reference host golden it is
 checked against (crates/targets/metal/src/cpu_golden.rs); the fused QKV and gate/up projections are
 built with the reference's `load_rows_concat` law (crates/targets/metal/src/layers_quant.rs:363-450).
 
@@ -293,17 +296,20 @@ class DecodeBuffers:
         self.logits = torch.empty((batch, cfg.vocab), dtype=bf, device=device)
         self.next_ids = torch.zeros(batch, dtype=i32, device=device)
         self.workspace = torch.empty(max(workspace_bytes, 16), dtype=torch.uint8, device=device)
+        # ticket counter + per-CTA sums of the fused residual/norm epilogue: zero once, the kernel keeps it zero
+        self.ends_scratch = torch.zeros(AffineQuantLinear.ENDS_SCRATCH_BYTES, dtype=torch.uint8, device=device)
 
 
 class LlamaDecoder:
     """Random-init or checkpoint-loaded Llama decoder whose every linear is MLX affine int4 g64."""
 
-    def __init__(self, cfg: LlamaConfig, checkpoint, device, max_pos: int = 4096):
+    def __init__(self, cfg: LlamaConfig, checkpoint, device, max_pos: int = 4096, fuse_residual_norm: bool = False):
         """`checkpoint`: a `GpuWeights` (e.g. `CheckpointWeights.from_dir(...)`) or a dict of host / device
         tensors with the HF Llama names."""
         if not torch.cuda.is_available():
             raise _lib.ScratchyCudaError(-5, "LlamaDecoder needs a CUDA device (there is no CPU path)")
         self.cfg, self.device = cfg, torch.device(device)
+        self.fuse_residual_norm = fuse_residual_norm
         dev = self.device
         gw = checkpoint if isinstance(checkpoint, GpuWeights) else GpuWeights({k: _to_device(v, dev)
                                                                               for k, v in checkpoint.items()})
@@ -359,12 +365,19 @@ class LlamaDecoder:
                         cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, cache.block_size)
             attention_via_cache(q, cache.k[i], cache.v[i], buf.block_table, buf.seq_used_k, cfg.n_q_heads,
                                 cfg.n_kv_heads, cfg.head_dim, cache.block_size, self.attn_scale, out=buf.attn)
-            layer.o.forward(buf.attn, out=buf.delta, workspace=buf.workspace)
-            fused_add_rmsnorm(buf.residual, buf.delta, layer.post_norm, cfg.rms_eps, out=buf.normed)
-            layer.gate_up.forward_silu_mul(buf.normed, out=buf.act, scratch=buf.gate_up, workspace=buf.workspace)
-            layer.down.forward(buf.act, out=buf.delta, workspace=buf.workspace)
             nxt = self.layers[i + 1].input_norm if i + 1 < len(self.layers) else self.final_norm
-            fused_add_rmsnorm(buf.residual, buf.delta, nxt, cfg.rms_eps, out=buf.normed)
+            if self.fuse_residual_norm:
+                layer.o.forward_residual_rmsnorm(buf.attn, buf.residual, layer.post_norm, cfg.rms_eps, buf.normed,
+                                                 buf.ends_scratch, delta=buf.delta, workspace=buf.workspace)
+                layer.gate_up.forward_silu_mul(buf.normed, out=buf.act, scratch=buf.gate_up, workspace=buf.workspace)
+                layer.down.forward_residual_rmsnorm(buf.act, buf.residual, nxt, cfg.rms_eps, buf.normed, buf.ends_scratch,
+                                                    delta=buf.delta, workspace=buf.workspace)
+            else:
+                layer.o.forward(buf.attn, out=buf.delta, workspace=buf.workspace)
+                fused_add_rmsnorm(buf.residual, buf.delta, layer.post_norm, cfg.rms_eps, out=buf.normed)
+                layer.gate_up.forward_silu_mul(buf.normed, out=buf.act, scratch=buf.gate_up, workspace=buf.workspace)
+                layer.down.forward(buf.act, out=buf.delta, workspace=buf.workspace)
+                fused_add_rmsnorm(buf.residual, buf.delta, nxt, cfg.rms_eps, out=buf.normed)
         self.lm_head.forward(buf.normed, out=buf.logits, workspace=buf.workspace)
         argmax(buf.logits, out=buf.next_ids)
         return buf.logits

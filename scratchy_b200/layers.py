@@ -260,6 +260,29 @@ class AffineQuantLinear:
             _stream(dev)))
         return out.reshape(*x.shape[:-1], self.out_features)
 
+    ENDS_SCRATCH_BYTES = 65536      # SCR_ENDS_SCRATCH_BYTES
+
+    def forward_residual_rmsnorm(self, x: torch.Tensor, residual: torch.Tensor, gain: torch.Tensor, eps: float,
+                                 normed: torch.Tensor, scratch: torch.Tensor,
+                                 delta: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """`residual += x @ W^T` (in place, bf16) and `normed = rmsnorm(residual, gain)`: one launch up to 16 tokens
+        (`scr_linear_affine_b4_residual_rmsnorm`; `scratch` = ENDS_SCRATCH_BYTES, zeroed once by the caller), the
+        linear into `delta` followed by `scr_fused_add_rmsnorm_bf16` above."""
+        x2 = x.reshape(-1, self.in_features).contiguous()
+        M = int(x2.shape[0])
+        dev = x2.device
+        ctx = _lib.context(_dev_index(dev))
+        if M <= 16:
+            ctx.check(_lib.lib().scr_linear_affine_b4_residual_rmsnorm(
+                ctx.handle, _ptr(self.packed), _ptr(x2), M, self.out_features, self.in_features, self.group_size,
+                _ptr(residual), _ptr(gain), ctypes.c_float(eps), _ptr(normed), _ptr(scratch),
+                ctypes.c_size_t(scratch.numel() * scratch.element_size()), _stream(dev)))
+            return normed
+        delta = self.forward(x2, out=delta, workspace=workspace)
+        ctx.check(_lib.lib().scr_fused_add_rmsnorm_bf16(ctx.handle, _ptr(residual), _ptr(delta), _ptr(gain), _ptr(normed), M,
+                                                        self.out_features, ctypes.c_float(eps), _stream(dev)))
+        return normed
+
     def forward_partial(self, x: torch.Tensor, out: Optional[torch.Tensor] = None,
                         workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Row-parallel use: unrounded f32 sums over this rank's K-slice (`scr_linear_affine_b4_partial`)."""

@@ -286,3 +286,52 @@ def test_gate_up_with_fused_silu_mul(M, inter, K):
                                                       None))
         torch.cuda.synchronize()
         assert np.array_equal(got, bits_of(two_step).reshape(M, inter))
+
+
+@pytest.mark.parametrize("M", [1, 5, 16, 40])
+@pytest.mark.parametrize("N,K", [(3072, 3072), (3072, 8192), (8192, 3072), (24, 192), (136, 320)])
+def test_residual_add_and_rmsnorm_in_the_epilogue(N, K, M):
+    """`fused_add_rmsnorm` (crates/targets/metal/src/cpu_golden.rs:171-200) folded into the o / down matvec: the stored
+    residual must equal the two-kernel path bit for bit (same matvec sums, same roundings), the norm must meet the
+    oracle bar; repeated calls and graph replays must keep working (the ticket counter resets itself)."""
+    import torch
+    from scratchy_b200 import AffineQuantLinear, decode
+    from util import bf16_to_f32
+    w, s, b = synth.affine_int4_weights(N, K, 64, synth.seed_for("ends", N, K))
+    lin = make_layer(w, s, b)
+    rng = np.random.default_rng(M)
+    xb = synth.activations_bf16(M, K, 91)
+    res0 = synth.f32_to_bf16_bits(rng.standard_normal((M, N)).astype(np.float32))
+    gain = synth.f32_to_bf16_bits((1.0 + 0.1 * rng.standard_normal(N)).astype(np.float32))
+    x, g = bf16_dev(xb).reshape(M, K), bf16_dev(gain)
+    # two kernels: linear, then add + norm
+    res_a = bf16_dev(res0)
+    normed_a = decode.fused_add_rmsnorm(res_a, lin.forward(x), g, 1e-5)
+    # one launch (up to 16 tokens)
+    scratch = torch.zeros(AffineQuantLinear.ENDS_SCRATCH_BYTES, dtype=torch.uint8, device="cuda")
+    res_b = bf16_dev(res0)
+    normed_b = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    lin.forward_residual_rmsnorm(x, res_b, g, 1e-5, normed_b, scratch)
+    torch.cuda.synchronize()
+    assert np.array_equal(bits_of(res_b), bits_of(res_a)), "residual after the add"
+    assert rel_l2(bits_of(normed_b), bits_of(normed_a)) <= 1e-4 and np.mean(bits_of(normed_b) == bits_of(normed_a)) > 0.98
+    y = oracle.affine_qmm_t_b4(w.view(np.uint8).reshape(-1), s, b, xb, M, N, K, 64)
+    want_res, want = oracle.fused_add_rmsnorm(bf16_to_f32(res0), bf16_to_f32(y), bf16_to_f32(gain), 1e-5, round_residual_bf16=True)
+    assert rel_l2(bits_of(normed_b), synth.f32_to_bf16_bits(want)) <= REL_L2_TOL
+    assert rel_l2(bits_of(res_b), synth.f32_to_bf16_bits(want_res)) <= REL_L2_TOL
+    assert int(scratch.view(torch.int32)[0]) == 0, "the ticket counter is left at zero"
+    if M <= 16:
+        # again, eagerly and from a graph: same inputs, same outputs
+        side = torch.cuda.Stream()
+        res_c = bf16_dev(res0)
+        normed_c = torch.empty_like(normed_b)
+        lin.forward_residual_rmsnorm(x, res_c, g, 1e-5, normed_c, scratch)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            lin.forward_residual_rmsnorm(x, res_c, g, 1e-5, normed_c, scratch)
+        for _ in range(3):
+            res_c.copy_(bf16_dev(res0))
+            graph.replay()
+            torch.cuda.synchronize()
+            assert np.array_equal(bits_of(res_c), bits_of(res_b)) and np.array_equal(bits_of(normed_c), bits_of(normed_b))
