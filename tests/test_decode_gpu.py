@@ -267,21 +267,27 @@ def _oracle_step(cfg, ck, ids, pos, slots, table, used, cache_k, cache_v, cos, s
     return _oracle_linear(ck, ["lm_head"], normed, cfg.hidden)
 
 
-@pytest.mark.parametrize("batch", [1, 3, 20])
-def test_decode_step_matches_oracle_chain(batch):
+@pytest.mark.parametrize("batch,fuse_residual_norm,head_dim,bs,max_ctx", [
+    (1, False, 64, 4, 20), (3, False, 64, 4, 20), (20, False, 64, 4, 20), (3, True, 64, 4, 20),
+    # 16-token blocks and head_dim 128: the TMA + tensor-core attention, which streams the old cache blocks
+    # while the RoPE/append kernel before it is still running and waits only for the newest block
+    (2, False, 128, 16, 100), (9, False, 128, 16, 100)])
+def test_decode_step_matches_oracle_chain(batch, fuse_residual_norm, head_dim, bs, max_ctx):
     """Two consecutive steps of a small random-init decoder (eager, then the same step replayed from a
     CUDA graph) against the oracle chain; batch 20 takes the tensor-core linear path."""
     import torch
     from scratchy_b200 import decode
-    cfg = decode.LlamaConfig(hidden=256, n_layers=2, n_q_heads=4, n_kv_heads=2, head_dim=64, intermediate=512,
+    cfg = decode.LlamaConfig(hidden=256, n_layers=2, n_q_heads=4, n_kv_heads=2, head_dim=head_dim, intermediate=512,
                              vocab=1024, rope_theta=10000.0)
     ck = decode.synthetic_checkpoint(cfg, seed=batch)
-    dec = decode.LlamaDecoder(cfg, ck, "cuda:0", max_pos=128)
-    bs, max_blocks = 4, 8
+    dec = decode.LlamaDecoder(cfg, ck, "cuda:0", max_pos=128, fuse_residual_norm=fuse_residual_norm)
+    max_blocks = 8
     nblk = batch * max_blocks
     cache = decode.PagedKvCache(cfg, nblk, bs, "cuda:0")
     rng = np.random.default_rng(batch)
-    ctx_len = rng.integers(3, 20, size=batch)
+    ctx_len = rng.integers(3, max_ctx, size=batch)
+    if head_dim == 128:
+        ctx_len[0] = 2 * bs - 1                      # the second step's token opens a new block
     table = rng.permutation(nblk).reshape(batch, max_blocks).astype(np.uint32)
     # pre-fill the caches with random history
     hist_k = [rbits(rng.standard_normal((nblk, cfg.n_kv_heads, bs, cfg.head_dim))) for _ in range(cfg.n_layers)]
