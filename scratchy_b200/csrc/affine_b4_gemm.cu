@@ -21,11 +21,8 @@
 #include "tc_common.cuh"
 
 bool affine_b4_gemm_tc_enabled() { return true; }
-static int affine_gemm_ksplit(int M, int N, int K, int sms);
-size_t affine_b4_gemm_tc_workspace(int M, int N, int K) {
-    const int ks = affine_gemm_ksplit(M, N, K, tc_sm_count());
-    return ks > 1 ? (size_t)ks * M * N * sizeof(float) : 0;
-}
+size_t affine_b4_gemm_tc_workspace_plan(int M, int N, int K);
+size_t affine_b4_gemm_tc_workspace(int M, int N, int K) { return affine_b4_gemm_tc_workspace_plan(M, N, K); }
 
 #define A4G_THREADS 704
 #define A4G_DQ_WARPS 16
@@ -64,11 +61,60 @@ __device__ __forceinline__ uint32_t ld_shared_u32(uint32_t addr) {
     return v;
 }
 
+// Unit -> (tile, k range).  Units [0, full) are whole tiles; the rest split each tail tile's k extent ks_tail ways.
+__device__ __forceinline__ void a4g_unit(int unit, int full, int ks_tail, int KC, int& tile, int& ks, int& kc_lo, int& kc_hi) {
+    if (unit < full) {
+        tile = unit;
+        ks = 0;
+        kc_lo = 0;
+        kc_hi = KC;
+        return;
+    }
+    const int v = unit - full;
+    tile = full + v / ks_tail;
+    ks = v - (v / ks_tail) * ks_tail;
+    const int per = (KC + ks_tail - 1) / ks_tail;
+    kc_lo = ks * per;
+    kc_hi = min(KC, kc_lo + per);
+}
+
+// Finishes the split tiles: sums a tile's ks_tail partial tiles in slab order (deterministic) and stores the
+// result, rounded once (or as f32 partials).  One CTA per (tail tile, 8 rows), one float4 per thread.
+__global__ void __launch_bounds__(256) affine_b4_gemm_tail_finish_kernel(const float* __restrict__ slabs, int ks_tail, int n_tail,
+                                                                         int full, int MT, int tile_rows, int M, int N,
+                                                                         uint16_t* __restrict__ y, int out_f32) {
+    const int groups = tile_rows / 8;
+    const int tt = blockIdx.x / groups, grp = blockIdx.x - tt * groups;
+    const int tile = full + tt;
+    const int mt = tile % MT, nb = tile / MT;
+    const size_t tile_elems = (size_t)tile_rows * A4G_BN;
+    const int rl = grp * 8 + threadIdx.x / (A4G_BN / 4), c4 = (threadIdx.x % (A4G_BN / 4)) * 4;
+    const int m = mt * tile_rows + rl, n = nb * A4G_BN + c4;
+    if (m >= M || n >= N) return;
+    const float* p = slabs + (size_t)tt * tile_elems + (size_t)rl * A4G_BN + c4;
+    float4 a = *reinterpret_cast<const float4*>(p);
+    for (int k = 1; k < ks_tail; ++k) {
+        const float4 b = *reinterpret_cast<const float4*>(p + (size_t)k * n_tail * tile_elems);
+        a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+    }
+    const float v[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        if (n + j >= N) break;
+        if (out_f32) {
+            reinterpret_cast<float*>(y)[(size_t)m * N + n + j] = v[j];
+        } else {
+            const __nv_bfloat16 o = __float2bfloat16_rn(v[j]);
+            y[(size_t)m * N + n + j] = *reinterpret_cast<const uint16_t*>(&o);
+        }
+    }
+}
+
 template <int TM>
 __global__ void __launch_bounds__(A4G_THREADS, 1)
 affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_t* __restrict__ packed,
                          uint16_t* __restrict__ y, int M, int N, int RB, int KC, int MT, int out_f32,
-                         int ksplit, float* __restrict__ slabs, int* __restrict__ status) {
+                         int full, int ks_tail, float* __restrict__ slabs, int* __restrict__ status) {
     using S = A4GSmem<TM>;
     constexpr int SX = S::kSX;
     constexpr int BN = A4G_BN;
@@ -90,8 +136,10 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int NTB = RB * 16 / BN;                        // RB is a multiple of 8 (N padded to 128)
-    const int tiles = MT * NTB * ksplit;                 // MT = token tiles of 128 * TM; ksplit CTAs share a tile's k
-    const int kc_per = (KC + ksplit - 1) / ksplit;
+    // Work units: the first `full` tiles whole; each of the remaining (tail) tiles as ks_tail units that share its k
+    // extent and leave f32 partial tiles in `slabs` for the finishing kernel (MT = token tiles of 128 * TM).
+    const int n_tail = MT * NTB - full;
+    const int tiles = full + n_tail * ks_tail;
     constexpr uint32_t kAccCols = (uint32_t)(TM * BN);   // TMEM columns per accumulator buffer
 
     if (threadIdx.x == 0) {
@@ -115,11 +163,11 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
         if (lane == 0) {
             int sx = 0, sp = 0;
             uint32_t phx = 0, php = 0;
-            for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
-                const int ks = tile % ksplit, t2 = tile / ksplit;
+            for (int unit = blockIdx.x; unit < tiles; unit += gridDim.x) {
+                int t2, ks, kc_lo, kc_hi;
+                a4g_unit(unit, full, ks_tail, KC, t2, ks, kc_lo, kc_hi);
                 const int mt = t2 % MT, nb = t2 / MT;
                 const int rb0 = nb * (BN / 16);
-                const int kc_lo = ks * kc_per, kc_hi = min(KC, kc_lo + kc_per);
                 for (int kc = kc_lo; kc < kc_hi; ++kc) {
                     mbar_wait(pempty(sp), php ^ 1u, status, TC_ERR_EMPTY_WAIT);
                     mbar_arrive_expect_tx(pfull(sp), S::kPStage);
@@ -147,12 +195,13 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
             uint32_t phx = 0, phd = 0;
             int it = 0;
             const uint32_t idesc = umma_idesc(1, 1, 128, BN);
-            for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
+            for (int unit = blockIdx.x; unit < tiles; unit += gridDim.x, ++it) {
                 const int buf = it & 1;
                 mbar_wait(acce(buf), ((uint32_t)(it >> 1) & 1u) ^ 1u, status, TC_ERR_ACC_EMPTY);
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)buf * kAccCols;
-                const int kc_lo = (tile % ksplit) * kc_per, kc_hi = min(KC, kc_lo + kc_per);
+                int t2, ks, kc_lo, kc_hi;
+                a4g_unit(unit, full, ks_tail, KC, t2, ks, kc_lo, kc_hi);
                 for (int kc = kc_lo; kc < kc_hi; ++kc) {
                     mbar_wait(xfull(sx), phx, status, TC_ERR_FULL_WAIT);
                     mbar_wait(dfull(sd), phd, status, TC_ERR_DEQ_WAIT);
@@ -190,8 +239,9 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
         const bool check = *reinterpret_cast<const unsigned int*>(packed + (size_t)RB * KC * AFF_BLOCK_BYTES) != 0;
         int sp = 0, sd = 0;
         uint32_t php = 0, phd = 0;
-        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
-            const int kc_lo = (tile % ksplit) * kc_per, kc_hi = min(KC, kc_lo + kc_per);
+        for (int unit = blockIdx.x; unit < tiles; unit += gridDim.x) {
+            int t2, ks, kc_lo, kc_hi;
+            a4g_unit(unit, full, ks_tail, KC, t2, ks, kc_lo, kc_hi);
             for (int kc = kc_lo; kc < kc_hi; ++kc) {
                 mbar_wait(pfull(sp), php, status, TC_ERR_FULL_WAIT);
                 mbar_wait(dempty(sd), phd ^ 1u, status, TC_ERR_EMPTY_WAIT);
@@ -240,14 +290,17 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
         const float out_scale =
             (*reinterpret_cast<const unsigned int*>(packed + (size_t)RB * KC * AFF_BLOCK_BYTES) != 0) ? 1.0f : AFF_SCALED_FACTOR;
         int it = 0;
-        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
-            const int ks = tile % ksplit, t2 = tile / ksplit;
+        for (int unit = blockIdx.x; unit < tiles; unit += gridDim.x, ++it) {
+            int t2, ks, kc_lo, kc_hi;
+            a4g_unit(unit, full, ks_tail, KC, t2, ks, kc_lo, kc_hi);
             const int mt = t2 % MT, nb = t2 / MT;
             const int n0 = nb * BN;
             const int buf = it & 1;
-            // split-K: every CTA of a tile writes f32 into its own slab, summed afterwards
-            const bool f32mode = out_f32 || ksplit > 1;
-            float* fbase = ksplit > 1 ? slabs + (size_t)ks * M * N : reinterpret_cast<float*>(y);
+            // a split unit writes its f32 partial tile (TM*128 x 128, padding included) into its own slab
+            const bool split = unit >= full && ks_tail > 1;
+            const bool f32mode = out_f32 != 0;
+            float* fbase = reinterpret_cast<float*>(y);
+            float* slab = split ? slabs + ((size_t)ks * n_tail + (t2 - full)) * (size_t)(TM * 128 * BN) : nullptr;
             mbar_wait(accf(buf), (uint32_t)(it >> 1) & 1u, status, TC_ERR_ACC_FULL);
             tc_fence_after();
 #pragma unroll 1
@@ -259,7 +312,14 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
                     tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)buf * kAccCols + (uint32_t)(h * BN + c * 32), r);
                     tmem_ld_wait();
                     const int nc = n0 + c * 32;
-                    if (m < M && nc < N && f32mode) {
+                    if (split) {
+                        if (m >= M) continue;          // rows of padding are never read back
+                        float4* dst = reinterpret_cast<float4*>(slab + (size_t)(h * 128 + q * 32 + lane) * BN + c * 32);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            dst[j] = make_float4(__uint_as_float(r[4 * j]) * out_scale, __uint_as_float(r[4 * j + 1]) * out_scale,
+                                                 __uint_as_float(r[4 * j + 2]) * out_scale, __uint_as_float(r[4 * j + 3]) * out_scale);
+                    } else if (m < M && nc < N && f32mode) {
                         // unrounded f32 (row-parallel partials, or a split-K slab)
                         float* frow = fbase + (size_t)m * N + nc;
                         const bool v4 = (N % 4) == 0 && nc + 32 <= N;
@@ -317,27 +377,65 @@ static int affine_gemm_tm(int M, int N, int K, int sms) {
     const int tiles2 = scr_ceil_div(M, 256) * (g.RB * 16 / A4G_BN);
     return (M > 128 && tiles2 >= sms / 2) ? 2 : 1;
 }
-static int affine_gemm_ksplit(int M, int N, int K, int sms) {
+// How the tiles are cut into work units.  Few tiles (less than half the SMs): every tile is split along k.
+// Otherwise the persistent CTAs take whole tiles round by round, and when the last round would leave more than
+// half the machine idle its tiles (the tail) are split along k so that the round is about full again.
+struct AffineGemmPlan {
+    int tm, mt, tiles, full, ks_tail;
+    int n_tail() const { return tiles - full; }
+    size_t slab_floats() const { return ks_tail > 1 ? (size_t)ks_tail * n_tail() * (size_t)(tm * 128 * A4G_BN) : 0; }
+};
+static AffineGemmPlan affine_gemm_plan(int M, int N, int K, int sms) {
     const AffineGeom g = affine_geom(N, K);
-    const int tm = affine_gemm_tm(M, N, K, sms);
-    return tc_pick_ksplit(scr_ceil_div(M, 128 * tm) * (g.RB * 16 / A4G_BN), g.KC, sms);
+    AffineGemmPlan p;
+    p.tm = affine_gemm_tm(M, N, K, sms);
+    p.mt = scr_ceil_div(M, 128 * p.tm);
+    p.tiles = p.mt * (g.RB * 16 / A4G_BN);
+    p.full = p.tiles;
+    p.ks_tail = 1;
+    // Estimated duration in tile-times: rounds of whole tiles, a split unit costing 1/ks of a tile plus its own
+    // accumulator drain and f32 slab write (8 % per way, measured on the 3B shapes), and the finishing kernel.  Candidates: no split, every tile split ks ways, or only the
+    // tiles of the last (partial) round split.
+    const int max_ks = std::min(8, g.KC / 4);
+    float best = (float)scr_ceil_div(p.tiles, sms);
+    for (int ks = 2; ks <= max_ks; ++ks) {
+        const float all = (float)scr_ceil_div(p.tiles * ks, sms) / ks * (1.0f + 0.08f * ks) + 0.2f;
+        if (all < best - 1e-3f) {
+            best = all;
+            p.full = 0;
+            p.ks_tail = ks;
+        }
+        const int rem = p.tiles % sms;
+        if (p.tiles > sms && rem > 0 && rem * ks <= sms) {
+            const float tail = (float)(p.tiles / sms) + (1.0f + 0.08f * ks) / ks + 0.1f;
+            if (tail < best - 1e-3f) {
+                best = tail;
+                p.full = p.tiles - rem;
+                p.ks_tail = ks;
+            }
+        }
+    }
+    return p;
 }
+size_t affine_b4_gemm_tc_workspace_plan(int M, int N, int K) { return affine_gemm_plan(M, N, K, tc_sm_count()).slab_floats() * sizeof(float); }
 
 template <int TM>
 static int32_t affine_gemm_launch_tm(scr_ctx* ctx, const CUtensorMap& map, const uint8_t* packed, uint16_t* y, int M, int N,
-                                     int K, int ksplit, float* slabs, cudaStream_t stream) {
+                                     int K, const AffineGemmPlan& p, float* slabs, cudaStream_t stream) {
     const AffineGeom g = affine_geom(N, K);
-    const int MT = scr_ceil_div(M, 128 * TM);
-    const int tiles = MT * (g.RB * 16 / A4G_BN) * ksplit;
-    const int grid = std::min(tiles, ctx->sm_count);
+    const int units = p.full + p.n_tail() * p.ks_tail;
+    const int grid = std::min(units, ctx->sm_count);
     cudaError_t e = cudaFuncSetAttribute(affine_b4_gemm_tc_kernel<TM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)A4GSmem<TM>::kTotal);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine gemm smem attribute: %s", cudaGetErrorString(e));
-    affine_b4_gemm_tc_kernel<TM><<<grid, A4G_THREADS, A4GSmem<TM>::kTotal, stream>>>(map, packed, y, M, N, g.RB, g.KC, MT,
-                                                                                    ctx->out_f32, ksplit, slabs, ctx->dev_status);
+    affine_b4_gemm_tc_kernel<TM><<<grid, A4G_THREADS, A4GSmem<TM>::kTotal, stream>>>(map, packed, y, M, N, g.RB, g.KC, p.mt,
+                                                                                    ctx->out_f32, p.full, p.ks_tail, slabs,
+                                                                                    ctx->dev_status);
     int32_t st = scr_check_launch(ctx, "affine_b4_gemm_tc");
-    if (st || ksplit == 1) return st;
-    return tc_splitk_finish(ctx, slabs, ksplit, (long long)M * N, y, stream);
+    if (st || p.ks_tail == 1) return st;
+    affine_b4_gemm_tail_finish_kernel<<<p.n_tail() * (TM * 128 / 8), 256, 0, stream>>>(slabs, p.ks_tail, p.n_tail(), p.full, p.mt,
+                                                                                       TM * 128, M, N, y, ctx->out_f32);
+    return scr_check_launch(ctx, "affine_b4_gemm_tail_finish");
 }
 
 int32_t affine_b4_gemm_tc_launch(scr_ctx* ctx, const uint8_t* packed, const uint16_t* x, uint16_t* y, int M, int N, int K,
@@ -354,10 +452,9 @@ int32_t affine_b4_gemm_tc_launch(scr_ctx* ctx, const uint8_t* packed, const uint
     CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)x, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return scr_fail(ctx, SCR_E_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
-    const int ksplit = affine_gemm_ksplit(M, N, K, ctx->sm_count);
+    const AffineGemmPlan plan = affine_gemm_plan(M, N, K, ctx->sm_count);
     float* slabs = reinterpret_cast<float*>(workspace);
-    if (ksplit > 1 && (!slabs || !scr_aligned16(slabs))) return scr_fail(ctx, SCR_E_WORKSPACE, "split-K needs an aligned workspace");
-    if (affine_gemm_tm(M, N, K, ctx->sm_count) == 2)
-        return affine_gemm_launch_tm<2>(ctx, map, packed, y, M, N, K, ksplit, slabs, stream);
-    return affine_gemm_launch_tm<1>(ctx, map, packed, y, M, N, K, ksplit, slabs, stream);
+    if (plan.ks_tail > 1 && (!slabs || !scr_aligned16(slabs))) return scr_fail(ctx, SCR_E_WORKSPACE, "split-K needs an aligned workspace");
+    if (plan.tm == 2) return affine_gemm_launch_tm<2>(ctx, map, packed, y, M, N, K, plan, slabs, stream);
+    return affine_gemm_launch_tm<1>(ctx, map, packed, y, M, N, K, plan, slabs, stream);
 }
