@@ -141,25 +141,3 @@ extern "C" int32_t scr_partial_to_bf16(scr_ctx* ctx, const float* in, int64_t co
     partial_to_bf16_kernel<<<blocks, threads, 0, (cudaStream_t)stream>>>(in, (long long)count, out);
     return scr_check_launch(ctx, "partial_to_bf16");
 }
-
-// ---- split-K finish: sum the slabs in slab order, round once ---------------------------------
-__global__ void splitk_finish_kernel(const float* __restrict__ slabs, int ksplit, long long count, uint16_t* __restrict__ y,
-                                     int out_f32) {
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
-        float s = slabs[i];
-        for (int k = 1; k < ksplit; ++k) s += slabs[(size_t)k * count + i];
-        if (out_f32) {
-            reinterpret_cast<float*>(y)[i] = s;
-        } else {
-            const __nv_bfloat16 v = __float2bfloat16_rn(s);
-            y[i] = *reinterpret_cast<const uint16_t*>(&v);
-        }
-    }
-}
-
-int32_t tc_splitk_finish(scr_ctx* ctx, const float* slabs, int ksplit, long long count, uint16_t* y, cudaStream_t stream) {
-    const int threads = 256;
-    const int blocks = (int)std::min<long long>((count + threads - 1) / threads, (long long)ctx->sm_count * 8);
-    splitk_finish_kernel<<<blocks, threads, 0, stream>>>(slabs, ksplit, count, y, ctx->out_f32);
-    return scr_check_launch(ctx, "splitk_finish");
-}

@@ -61,23 +61,6 @@ __device__ __forceinline__ uint32_t ld_shared_u32(uint32_t addr) {
     return v;
 }
 
-// Unit -> (tile, k range).  Units [0, full) are whole tiles; the rest split each tail tile's k extent ks_tail ways.
-__device__ __forceinline__ void a4g_unit(int unit, int full, int ks_tail, int KC, int& tile, int& ks, int& kc_lo, int& kc_hi) {
-    if (unit < full) {
-        tile = unit;
-        ks = 0;
-        kc_lo = 0;
-        kc_hi = KC;
-        return;
-    }
-    const int v = unit - full;
-    tile = full + v / ks_tail;
-    ks = v - (v / ks_tail) * ks_tail;
-    const int per = (KC + ks_tail - 1) / ks_tail;
-    kc_lo = ks * per;
-    kc_hi = min(KC, kc_lo + per);
-}
-
 // Finishes the split tiles: sums a tile's ks_tail partial tiles in slab order (deterministic) and stores the
 // result, rounded once (or as f32 partials).  One CTA per (tail tile, 8 rows), one float4 per thread.
 __global__ void __launch_bounds__(256) affine_b4_gemm_tail_finish_kernel(const float* __restrict__ slabs, int ks_tail, int n_tail,
@@ -165,7 +148,7 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
             uint32_t phx = 0, php = 0;
             for (int unit = blockIdx.x; unit < tiles; unit += gridDim.x) {
                 int t2, ks, kc_lo, kc_hi;
-                a4g_unit(unit, full, ks_tail, KC, t2, ks, kc_lo, kc_hi);
+                tc_unit(unit, full, ks_tail, KC, t2, ks, kc_lo, kc_hi);
                 const int mt = t2 % MT, nb = t2 / MT;
                 const int rb0 = nb * (BN / 16);
                 for (int kc = kc_lo; kc < kc_hi; ++kc) {
@@ -201,7 +184,7 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)buf * kAccCols;
                 int t2, ks, kc_lo, kc_hi;
-                a4g_unit(unit, full, ks_tail, KC, t2, ks, kc_lo, kc_hi);
+                tc_unit(unit, full, ks_tail, KC, t2, ks, kc_lo, kc_hi);
                 for (int kc = kc_lo; kc < kc_hi; ++kc) {
                     mbar_wait(xfull(sx), phx, status, TC_ERR_FULL_WAIT);
                     mbar_wait(dfull(sd), phd, status, TC_ERR_DEQ_WAIT);
@@ -241,7 +224,7 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
         uint32_t php = 0, phd = 0;
         for (int unit = blockIdx.x; unit < tiles; unit += gridDim.x) {
             int t2, ks, kc_lo, kc_hi;
-            a4g_unit(unit, full, ks_tail, KC, t2, ks, kc_lo, kc_hi);
+            tc_unit(unit, full, ks_tail, KC, t2, ks, kc_lo, kc_hi);
             for (int kc = kc_lo; kc < kc_hi; ++kc) {
                 mbar_wait(pfull(sp), php, status, TC_ERR_FULL_WAIT);
                 mbar_wait(dempty(sd), phd ^ 1u, status, TC_ERR_EMPTY_WAIT);
@@ -292,7 +275,7 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
         int it = 0;
         for (int unit = blockIdx.x; unit < tiles; unit += gridDim.x, ++it) {
             int t2, ks, kc_lo, kc_hi;
-            a4g_unit(unit, full, ks_tail, KC, t2, ks, kc_lo, kc_hi);
+            tc_unit(unit, full, ks_tail, KC, t2, ks, kc_lo, kc_hi);
             const int mt = t2 % MT, nb = t2 / MT;
             const int n0 = nb * BN;
             const int buf = it & 1;
@@ -391,30 +374,7 @@ static AffineGemmPlan affine_gemm_plan(int M, int N, int K, int sms) {
     p.tm = affine_gemm_tm(M, N, K, sms);
     p.mt = scr_ceil_div(M, 128 * p.tm);
     p.tiles = p.mt * (g.RB * 16 / A4G_BN);
-    p.full = p.tiles;
-    p.ks_tail = 1;
-    // Estimated duration in tile-times: rounds of whole tiles, a split unit costing 1/ks of a tile plus its own
-    // accumulator drain and f32 slab write (8 % per way, measured on the 3B shapes), and the finishing kernel.  Candidates: no split, every tile split ks ways, or only the
-    // tiles of the last (partial) round split.
-    const int max_ks = std::min(8, g.KC / 4);
-    float best = (float)scr_ceil_div(p.tiles, sms);
-    for (int ks = 2; ks <= max_ks; ++ks) {
-        const float all = (float)scr_ceil_div(p.tiles * ks, sms) / ks * (1.0f + 0.08f * ks) + 0.2f;
-        if (all < best - 1e-3f) {
-            best = all;
-            p.full = 0;
-            p.ks_tail = ks;
-        }
-        const int rem = p.tiles % sms;
-        if (p.tiles > sms && rem > 0 && rem * ks <= sms) {
-            const float tail = (float)(p.tiles / sms) + (1.0f + 0.08f * ks) / ks + 0.1f;
-            if (tail < best - 1e-3f) {
-                best = tail;
-                p.full = p.tiles - rem;
-                p.ks_tail = ks;
-            }
-        }
-    }
+    tc_plan_units(p.tiles, g.KC, sms, 1.0f * p.tm, &p.full, &p.ks_tail);      // ~1 us per 128-k step and 128 tokens (measured)
     return p;
 }
 size_t affine_b4_gemm_tc_workspace_plan(int M, int N, int K) { return affine_gemm_plan(M, N, K, tc_sm_count()).slab_floats() * sizeof(float); }

@@ -17,19 +17,66 @@
 #include "tc_common.cuh"
 
 bool fp8_gemm_tc_enabled() { return true; }
-static int fp8_gemm_bn(int M, int N, int K, int sms) {
-    // wide channel tiles when there are enough of them to fill the machine, narrow otherwise
+// Channel-tile width and work units.  Wide (256-channel) tiles reuse every activation tile twice and are preferred;
+// a 128-channel tile does half the work in about three quarters of the time (measured), which can still win
+// when it quantises better over the SMs.  Units as in `tc_plan_units`.
+struct Fp8GemmPlan {
+    int bn, mt, tiles, full, ks_tail;
+    int n_tail() const { return tiles - full; }
+    size_t slab_floats() const { return ks_tail > 1 ? (size_t)ks_tail * n_tail() * (size_t)(128 * bn) : 0; }
+};
+static Fp8GemmPlan fp8_gemm_plan(int M, int N, int K, int sms) {
     const Fp8Geom g = fp8_geom(N, K);
-    return (scr_ceil_div(M, 128) * scr_ceil_div(g.NT, 2) >= sms) ? 256 : 128;
+    Fp8GemmPlan best{};
+    float best_est = 0.f;
+    for (int bn = 256; bn >= 128; bn -= 128) {
+        Fp8GemmPlan p;
+        p.bn = bn;
+        p.mt = scr_ceil_div(M, 128);
+        p.tiles = p.mt * ((g.NT * 128 + bn - 1) / bn);
+        // one k-step of a 128 x 256 tile takes ~0.5 us, of a 128 x 128 tile ~0.37 us (measured)
+        const float est = tc_plan_units(p.tiles, g.KT, sms, bn == 256 ? 0.5f : 0.37f, &p.full, &p.ks_tail) * (bn == 256 ? 1.0f : 0.75f);
+        if (bn == 256 || est < best_est * 0.97f) {
+            best = p;
+            best_est = est;
+        }
+        if (g.NT < 2) break;                 // a single 128-channel tile row: nothing to widen
+    }
+    return best;
 }
-static int fp8_gemm_ksplit(int M, int N, int K, int sms) {
-    const Fp8Geom g = fp8_geom(N, K);
-    const int bn = fp8_gemm_bn(M, N, K, sms);
-    return tc_pick_ksplit(scr_ceil_div(M, 128) * ((g.NT * 128 + bn - 1) / bn), g.KT, sms);
-}
-size_t fp8_gemm_tc_workspace(int M, int N, int K) {
-    const int ks = fp8_gemm_ksplit(M, N, K, tc_sm_count());
-    return ks > 1 ? (size_t)ks * M * N * sizeof(float) : 0;
+size_t fp8_gemm_tc_workspace(int M, int N, int K) { return fp8_gemm_plan(M, N, K, tc_sm_count()).slab_floats() * sizeof(float); }
+
+// Finishes the split tiles: sums a tile's partial tiles in slab order (deterministic), one rounding (or f32 out).
+// One CTA per (tail tile, 1024 / BN rows), one float4 per thread.
+__global__ void __launch_bounds__(256) fp8_gemm_tail_finish_kernel(const float* __restrict__ slabs, int ks_tail, int n_tail, int full,
+                                                                   int MT, int bn, int M, int N, uint16_t* __restrict__ y,
+                                                                   int out_f32) {
+    const int rows_per_cta = 1024 / bn;                  // 256 threads x 4 columns
+    const int groups = 128 / rows_per_cta;
+    const int tt = blockIdx.x / groups, grp = blockIdx.x - tt * groups;
+    const int tile = full + tt;
+    const int mt = tile % MT, nb = tile / MT;
+    const size_t tile_elems = (size_t)128 * bn;
+    const int rl = grp * rows_per_cta + threadIdx.x / (bn / 4), c4 = (threadIdx.x % (bn / 4)) * 4;
+    const int m = mt * 128 + rl, n = nb * bn + c4;
+    if (m >= M || n >= N) return;
+    const float* p = slabs + (size_t)tt * tile_elems + (size_t)rl * bn + c4;
+    float4 a = *reinterpret_cast<const float4*>(p);
+    for (int k = 1; k < ks_tail; ++k) {
+        const float4 b = *reinterpret_cast<const float4*>(p + (size_t)k * n_tail * tile_elems);
+        a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+    }
+    const float v[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        if (n + j >= N) break;
+        if (out_f32) {
+            reinterpret_cast<float*>(y)[(size_t)m * N + n + j] = v[j];
+        } else {
+            const __nv_bfloat16 o = __float2bfloat16_rn(v[j]);
+            y[(size_t)m * N + n + j] = *reinterpret_cast<const uint16_t*>(&o);
+        }
+    }
 }
 
 #define F8G_STAGES 4
@@ -46,7 +93,7 @@ template <int BN>
 __global__ void __launch_bounds__(F8G_THREADS, 1)
 fp8_gemm_tc_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_scale, const uint8_t* __restrict__ xq,
                    const float* __restrict__ a_scale, uint16_t* __restrict__ y, int M, int N, int KT, int NT, int MT,
-                   int M_pad, int out_f32, int ksplit, float* __restrict__ slabs, int* __restrict__ status) {
+                   int M_pad, int out_f32, int full, int ks_tail, float* __restrict__ slabs, int* __restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -60,8 +107,8 @@ fp8_gemm_tc_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ 
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int NTB = (NT * 128 + BN - 1) / BN;            // channel tiles of BN
-    const int tiles = MT * NTB * ksplit;                 // ksplit CTAs share a tile's k extent
-    const int kt_per = (KT + ksplit - 1) / ksplit;
+    const int n_tail = MT * NTB - full;                  // tiles whose k extent is split ks_tail ways (see tc_plan_units)
+    const int tiles = full + n_tail * ks_tail;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < F8G_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -82,12 +129,12 @@ fp8_gemm_tc_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ 
         if (lane == 0) {
             int s = 0;
             uint32_t ph = 0;
-            for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
-                const int ks = tile % ksplit, t2 = tile / ksplit;
+            for (int unit = blockIdx.x; unit < tiles; unit += gridDim.x) {
+                int t2, ks, kt_lo, kt_hi;
+                tc_unit(unit, full, ks_tail, KT, t2, ks, kt_lo, kt_hi);
                 const int mt = t2 % MT, nb = t2 / MT;
                 const int nt0 = nb * (BN / 128);
                 const int ntn = min(BN / 128, NT - nt0);                  // 128-row weight tiles in this channel tile
-                const int kt_lo = ks * kt_per, kt_hi = min(KT, kt_lo + kt_per);
                 for (int kt = kt_lo; kt < kt_hi; ++kt) {
                     mbar_wait(empty_bar(s), ph ^ 1u, status, TC_ERR_EMPTY_WAIT);
                     const uint32_t sa = smem_base + s * F8GSmem<BN>::kStageBytes;
@@ -106,11 +153,12 @@ fp8_gemm_tc_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ 
             int s = 0;
             uint32_t ph = 0;
             int it = 0;
-            for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
-                const int nb = (tile / ksplit) / MT;
+            for (int unit = blockIdx.x; unit < tiles; unit += gridDim.x, ++it) {
+                int t2, ks, kt_lo, kt_hi;
+                tc_unit(unit, full, ks_tail, KT, t2, ks, kt_lo, kt_hi);
+                const int nb = t2 / MT;
                 const int nt0 = nb * (BN / 128);
                 const int ntn = min(BN / 128, NT - nt0);
-                const int kt_lo = (tile % ksplit) * kt_per, kt_hi = min(KT, kt_lo + kt_per);
                 const uint32_t idesc = umma_idesc(0, 0, 128, 128u * ntn);
                 const int buf = it & 1;
                 mbar_wait(acce_bar(buf), ((uint32_t)(it >> 1) & 1u) ^ 1u, status, TC_ERR_ACC_EMPTY);
@@ -136,15 +184,18 @@ fp8_gemm_tc_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ 
         const int q = warp & 3;                                   // TMEM lane quadrant this warp may read
         const bool vec_ok = (N % 8) == 0;
         int it = 0;
-        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
-            const int ks = tile % ksplit, t2 = tile / ksplit;
+        for (int unit = blockIdx.x; unit < tiles; unit += gridDim.x, ++it) {
+            int t2, ks, kt_lo, kt_hi;
+            tc_unit(unit, full, ks_tail, KT, t2, ks, kt_lo, kt_hi);
             const int mt = t2 % MT, nb = t2 / MT;
             const int n0 = nb * BN;
             const int bn_cur = min(BN, NT * 128 - n0);
             const int buf = it & 1;
-            // split-K: every CTA of a tile writes f32 into its own slab, summed afterwards
-            const bool f32mode = out_f32 || ksplit > 1;
-            float* fbase = ksplit > 1 ? slabs + (size_t)ks * M * N : reinterpret_cast<float*>(y);
+            // a split unit writes its scaled f32 partial tile (128 x BN, padding columns included) into its own slab
+            const bool split = unit >= full && ks_tail > 1;
+            const bool f32mode = out_f32 != 0;
+            float* fbase = reinterpret_cast<float*>(y);
+            float* slab = split ? slabs + ((size_t)ks * n_tail + (t2 - full)) * (size_t)(128 * BN) : nullptr;
             mbar_wait(accf_bar(buf), (uint32_t)(it >> 1) & 1u, status, TC_ERR_ACC_FULL);
             tc_fence_after();
             const int m = mt * 128 + q * 32 + lane;
@@ -155,7 +206,18 @@ fp8_gemm_tc_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ 
                 tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + c * 32), r);
                 tmem_ld_wait();
                 const int nc = n0 + c * 32;
-                if (m < M && nc < N && f32mode) {
+                if (split) {
+                    if (m >= M) continue;              // rows of padding are never read back
+                    float4* dst = reinterpret_cast<float4*>(slab + (size_t)(q * 32 + lane) * BN + c * 32);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float4 ws = __ldg(reinterpret_cast<const float4*>(w_scale + nc) + j);
+                        dst[j] = make_float4(__fmul_rn(__fmul_rn(__uint_as_float(r[4 * j + 0]), as), ws.x),
+                                             __fmul_rn(__fmul_rn(__uint_as_float(r[4 * j + 1]), as), ws.y),
+                                             __fmul_rn(__fmul_rn(__uint_as_float(r[4 * j + 2]), as), ws.z),
+                                             __fmul_rn(__fmul_rn(__uint_as_float(r[4 * j + 3]), as), ws.w));
+                    }
+                } else if (m < M && nc < N && f32mode) {
                     // unrounded f32 (row-parallel partials, or a split-K slab)
                     float* frow = fbase + (size_t)m * N + nc;
                     const bool v4 = (N % 4) == 0 && nc + 32 <= N;
@@ -216,23 +278,24 @@ fp8_gemm_tc_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ 
 
 template <int BN>
 static int32_t fp8_gemm_launch_bn(scr_ctx* ctx, const uint8_t* wpack, const uint8_t* act, uint16_t* y, int M, int N, int K,
-                                  int ksplit, float* slabs, cudaStream_t stream) {
+                                  const Fp8GemmPlan& p, float* slabs, cudaStream_t stream) {
     const Fp8Geom g = fp8_geom(N, K);
     const float* w_scale = reinterpret_cast<const float*>(wpack + (size_t)g.NT * g.KT * FP8_TILE_BYTES);
     const float* a_scale = reinterpret_cast<const float*>(act);
     const uint8_t* xq = act + fp8_act_scale_bytes(M);
-    const int MT = scr_ceil_div(M, 128);
-    const int NTB = (g.NT * 128 + BN - 1) / BN;
-    const int tiles = MT * NTB * ksplit;
-    const int grid = std::min(tiles, ctx->sm_count);
+    const int units = p.full + p.n_tail() * p.ks_tail;
+    const int grid = std::min(units, ctx->sm_count);
     cudaError_t e = cudaFuncSetAttribute(fp8_gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)F8GSmem<BN>::kTotal);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "fp8_gemm smem attribute: %s", cudaGetErrorString(e));
     fp8_gemm_tc_kernel<BN><<<grid, F8G_THREADS, F8GSmem<BN>::kTotal, stream>>>(wpack, w_scale, xq, a_scale, y, M, N, g.KT,
-                                                                              g.NT, MT, MT * 128, ctx->out_f32, ksplit, slabs, ctx->dev_status);
+                                                                              g.NT, p.mt, p.mt * 128, ctx->out_f32, p.full,
+                                                                              p.ks_tail, slabs, ctx->dev_status);
     int32_t st = scr_check_launch(ctx, "fp8_gemm_tc");
-    if (st || ksplit == 1) return st;
-    return tc_splitk_finish(ctx, slabs, ksplit, (long long)M * N, y, stream);
+    if (st || p.ks_tail == 1) return st;
+    fp8_gemm_tail_finish_kernel<<<p.n_tail() * (128 / (1024 / BN)), 256, 0, stream>>>(slabs, p.ks_tail, p.n_tail(), p.full, p.mt, BN,
+                                                                                     M, N, y, ctx->out_f32);
+    return scr_check_launch(ctx, "fp8_gemm_tail_finish");
 }
 
 int32_t fp8_gemm_tc_launch(scr_ctx* ctx, const uint8_t* wpack, const uint8_t* act, uint16_t* y, int M, int N, int K,
@@ -240,9 +303,9 @@ int32_t fp8_gemm_tc_launch(scr_ctx* ctx, const uint8_t* wpack, const uint8_t* ac
     if (((uintptr_t)(act + fp8_act_scale_bytes(M)) & 127u) != 0 || ((uintptr_t)wpack & 127u) != 0)
         return scr_fail(ctx, SCR_E_ALIGN, "weight pack and activation pack must be 128-byte aligned for the GEMM path");
     if (!scr_aligned16(y)) return scr_fail(ctx, SCR_E_ALIGN, "y must be 16-byte aligned");
-    const int ksplit = fp8_gemm_ksplit(M, N, K, ctx->sm_count);
+    const Fp8GemmPlan plan = fp8_gemm_plan(M, N, K, ctx->sm_count);
     float* slabs = reinterpret_cast<float*>(workspace);
-    if (ksplit > 1 && (!slabs || !scr_aligned16(slabs))) return scr_fail(ctx, SCR_E_WORKSPACE, "split-K needs an aligned workspace");
-    if (fp8_gemm_bn(M, N, K, ctx->sm_count) == 256) return fp8_gemm_launch_bn<256>(ctx, wpack, act, y, M, N, K, ksplit, slabs, stream);
-    return fp8_gemm_launch_bn<128>(ctx, wpack, act, y, M, N, K, ksplit, slabs, stream);
+    if (plan.ks_tail > 1 && (!slabs || !scr_aligned16(slabs))) return scr_fail(ctx, SCR_E_WORKSPACE, "split-K needs an aligned workspace");
+    if (plan.bn == 256) return fp8_gemm_launch_bn<256>(ctx, wpack, act, y, M, N, K, plan, slabs, stream);
+    return fp8_gemm_launch_bn<128>(ctx, wpack, act, y, M, N, K, plan, slabs, stream);
 }

@@ -127,15 +127,54 @@ __host__ __device__ __forceinline__ uint32_t umma_idesc(uint32_t a_fmt, uint32_t
     return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | ((N >> 3) << 17) | ((M >> 4) << 24);
 }
 
-// Split-K for launches with too few output tiles to fill the machine: `ksplit` CTAs share a tile's
-// k extent, each writes its f32 partial tile into its own slab [ks][M][N] of the workspace and a
-// finishing kernel sums the slabs in slab order (deterministic) and rounds once.
-static inline int tc_pick_ksplit(int tiles, int k_steps, int sms) {
-    if (tiles * 2 > sms) return 1;
-    int ks = sms / tiles;
-    if (ks > 8) ks = 8;
-    if (ks > k_steps / 4) ks = k_steps / 4;
-    return ks < 1 ? 1 : ks;
+// Work units of a persistent GEMM with `tiles` output tiles of `k_steps` k-steps on `sms` SMs.  Candidates: whole
+// tiles only; every tile split ks ways along k; or whole tiles round by round with only the last, partial round
+// split (units [0, full) are whole tiles, the other tiles - full are split ks_tail ways).  The estimate is in
+// tile-times.  A split unit costs 1/ks of a tile plus a fixed ~3 us (its own accumulator drain and f32 slab
+// write), and split work needs the finishing kernel (~4 us); `us_per_kstep` (how long one k-step of one tile
+// takes, measured per kernel) turns those into tile-times.  Returns the estimate.
+static inline float tc_plan_units(int tiles, int k_steps, int sms, float us_per_kstep, int* full, int* ks_tail) {
+    *full = tiles;
+    *ks_tail = 1;
+    const int max_ks = k_steps / 4 < 8 ? k_steps / 4 : 8;
+    const float tile_us = k_steps * us_per_kstep;
+    const float unit_ovh = 3.0f / tile_us, finish = 4.0f / tile_us;
+    float best = (float)((tiles + sms - 1) / sms);
+    for (int ks = 2; ks <= max_ks; ++ks) {
+        const float all = (float)((tiles * ks + sms - 1) / sms) * (1.0f / ks + unit_ovh) + finish;
+        // splitting everything only pays clearly when the tiles do not fill one round; beyond that it has to win by 10 %
+        if (all < best * (tiles <= sms ? 0.97f : 0.90f)) {
+            best = all;
+            *full = 0;
+            *ks_tail = ks;
+        }
+        const int rem = tiles % sms;
+        if (tiles > sms && rem > 0 && rem * ks <= sms) {
+            const float tail = (float)(tiles / sms) + 1.0f / ks + unit_ovh + finish;
+            if (tail < best * 0.97f) {
+                best = tail;
+                *full = tiles - rem;
+                *ks_tail = ks;
+            }
+        }
+    }
+    return best;
+}
+// Unit -> (tile, k range) for such a plan.
+__device__ __forceinline__ void tc_unit(int unit, int full, int ks_tail, int k_steps, int& tile, int& ks, int& k_lo, int& k_hi) {
+    if (unit < full) {
+        tile = unit;
+        ks = 0;
+        k_lo = 0;
+        k_hi = k_steps;
+        return;
+    }
+    const int v = unit - full;
+    tile = full + v / ks_tail;
+    ks = v - (v / ks_tail) * ks_tail;
+    const int per = (k_steps + ks_tail - 1) / ks_tail;
+    k_lo = ks * per;
+    k_hi = min(k_steps, k_lo + per);
 }
 static inline int tc_sm_count() {
     static int sms = 0;
@@ -148,7 +187,6 @@ static inline int tc_sm_count() {
     }
     return sms;
 }
-int32_t tc_splitk_finish(scr_ctx* ctx, const float* slabs, int ksplit, long long count, uint16_t* y, cudaStream_t stream);
 
 __device__ __forceinline__ bool elect_one() {
     uint32_t pred;
