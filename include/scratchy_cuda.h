@@ -139,6 +139,13 @@ int32_t scr_fp8_repack(scr_ctx* ctx, const uint8_t* w_e4m3, const float* w_scale
 int32_t scr_fp8_act_size(int32_t M, int32_t K, size_t* bytes);
 int32_t scr_fp8_quant_per_token(scr_ctx* ctx, const uint16_t* x_bf16, int32_t M, int32_t K,
                                 void* act, void* stream);
+/* RMSNorm fused with the quantisation: the activation pack of a W8A8 linear straight from the residual
+ * stream (the reference quantises on the norm side for its W4A8 path,
+ * crates/targets/metal/src/shaders/norm_w4a8_quant.h:1-12; norm golden cpu_golden.rs:25-37).  The codes and
+ * a_scale are those `scr_fp8_quant_per_token` computes from bf16(rmsnorm(x)); `normed_bf16` (may be NULL)
+ * receives that bf16 row as well, for consumers that are not quantised linears. */
+int32_t scr_rmsnorm_fp8_quant(scr_ctx* ctx, const uint16_t* x_bf16, const uint16_t* gain, float eps,
+                              int32_t M, int32_t K, void* act, uint16_t* normed_bf16, void* stream);
 /* Test hook: unpack an activation pack to plain x_q [M,K] bytes and a_scale [M]. */
 int32_t scr_fp8_act_unpack(scr_ctx* ctx, const void* act, int32_t M, int32_t K, uint8_t* xq,
                            float* a_scale, void* stream);

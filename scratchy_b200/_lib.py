@@ -49,6 +49,7 @@ SIGNATURES = {
     "scr_fp8_repack": (_i32, [_vp, _vp, _vp, _i32, _i32, _vp, _vp]),
     "scr_fp8_act_size": (_i32, [_i32, _i32, _psz]),
     "scr_fp8_quant_per_token": (_i32, [_vp, _vp, _i32, _i32, _vp, _vp]),
+    "scr_rmsnorm_fp8_quant": (_i32, [_vp, _vp, _vp, ctypes.c_float, _i32, _i32, _vp, _vp, _vp]),
     "scr_fp8_act_unpack": (_i32, [_vp, _vp, _i32, _i32, _vp, _vp, _vp]),
     "scr_e4m3_encode": (_i32, [_vp, _vp, _i64, _vp, _vp]),
     "scr_linear_fp8": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _sz, _vp]),

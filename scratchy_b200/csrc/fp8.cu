@@ -110,6 +110,104 @@ fp8_quant_per_token_kernel(const uint16_t* __restrict__ x, int M, int K, int til
     }
 }
 
+// RMSNorm fused with the per-token quantisation: the producer of a W8A8 linear's activation pack straight from
+// the residual stream (the reference quantises on the norm side for its W4A8 path,
+// crates/targets/metal/src/shaders/norm_w4a8_quant.h:1-12; golden of the norm crates/targets/metal/src/cpu_golden.rs:25-37).
+// Per token: inv_rms from the sum of squares, normed = bf16((x * inv_rms) * gain) — the value the stand-alone norm
+// kernel would have stored — then absmax, a_scale and the e4m3 codes exactly as the quantise kernel computes them
+// from those bf16 values.  One CTA per token; the normed row lives in shared memory between the passes.
+__global__ void __launch_bounds__(QUANT_THREADS)
+fp8_rmsnorm_quant_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ gain, float eps, int M, int K, int tiled,
+                         int M_pad, uint8_t* __restrict__ act, uint16_t* __restrict__ normed_out) {
+    extern __shared__ float nrow[];                       // K floats: the bf16-rounded normed row
+    __shared__ float warp_red[QUANT_THREADS / 32];
+    __shared__ float s_bcast;
+    const int m = blockIdx.x;
+    const uint16_t* xr = x + (size_t)m * K;
+    const int nvec = K / 8;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+    float sq = 0.f;
+    for (int v = threadIdx.x; v < nvec; v += QUANT_THREADS) {
+        const uint4 q = ld_nc_v4(xr + v * 8);
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float lo = __uint_as_float(w[i] << 16), hi = __uint_as_float(w[i] & 0xFFFF0000u);
+            sq = __fadd_rn(sq, __fmul_rn(lo, lo));
+            sq = __fadd_rn(sq, __fmul_rn(hi, hi));
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xFFFFFFFFu, sq, o);
+    if (lane == 0) warp_red[warp] = sq;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+#pragma unroll
+        for (int i = 0; i < QUANT_THREADS / 32; ++i) t += warp_red[i];
+        s_bcast = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)K), eps)));
+    }
+    __syncthreads();
+    const float inv_rms = s_bcast;
+
+    float amax = 0.f;
+    for (int v = threadIdx.x; v < nvec; v += QUANT_THREADS) {
+        const uint4 q = ld_nc_v4(xr + v * 8);
+        const uint4 gq = ld_nc_v4(gain + v * 8);
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w}, gw[4] = {gq.x, gq.y, gq.z, gq.w};
+        uint32_t ow[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float lo = __fmul_rn(__fmul_rn(__uint_as_float(w[i] << 16), inv_rms), __uint_as_float(gw[i] << 16));
+            const float hi = __fmul_rn(__fmul_rn(__uint_as_float(w[i] & 0xFFFF0000u), inv_rms), __uint_as_float(gw[i] & 0xFFFF0000u));
+            const __nv_bfloat162 pk = __floats2bfloat162_rn(lo, hi);
+            ow[i] = *reinterpret_cast<const uint32_t*>(&pk);
+            const float rlo = __uint_as_float(ow[i] << 16), rhi = __uint_as_float(ow[i] & 0xFFFF0000u);
+            nrow[v * 8 + 2 * i] = rlo;
+            nrow[v * 8 + 2 * i + 1] = rhi;
+            amax = fmaxf(amax, fmaxf(fabsf(rlo), fabsf(rhi)));
+        }
+        if (normed_out) *reinterpret_cast<uint4*>(normed_out + (size_t)m * K + v * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+    __syncthreads();                                      // s_bcast and warp_red are reused
+    if (lane == 0) warp_red[warp] = amax;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float a = 0.f;
+#pragma unroll
+        for (int i = 0; i < QUANT_THREADS / 32; ++i) a = fmaxf(a, warp_red[i]);
+        const float sc = fminf(fmaxf(__fmul_rn(a, 1.0f / 448.0f), 1.0f / 448.0f / 448.0f), 448.0f);
+        reinterpret_cast<float*>(act)[m] = sc;
+        s_bcast = __fdiv_rn(1.0f, sc);
+    }
+    __syncthreads();
+    const float inv = s_bcast;
+
+    const size_t scale_bytes = ((size_t)M * 4 + 127) / 128 * 128;
+    uint8_t* xq = act + scale_bytes;
+    const int K16 = (K + 15) / 16 * 16;
+    const int kspan = tiled ? (K + 127) / 128 * 128 : K16;
+    for (int c = threadIdx.x; c < kspan / 16; c += QUANT_THREADS) {
+        const int k0 = c * 16;
+        uint32_t out[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int kk = k0 + j;
+            if (kk < K) {
+                const float v = fminf(fmaxf(__fmul_rn(nrow[kk], inv), -448.0f), 448.0f);
+                out[j >> 2] |= e4m3_encode_ref(v) << ((j & 3) * 8);
+            }
+        }
+        size_t off;
+        if (tiled) off = (size_t)(k0 >> 7) * ((size_t)M_pad * 128) + fp8_swizzled_offset(m, k0 & 127);
+        else off = (size_t)m * K16 + k0;
+        *reinterpret_cast<uint4*>(xq + off) = make_uint4(out[0], out[1], out[2], out[3]);
+    }
+}
+
 __global__ void fp8_act_unpack_kernel(const uint8_t* __restrict__ act, int M, int K, int tiled, int M_pad,
                                       uint8_t* __restrict__ xq_out, float* __restrict__ a_scale) {
     const size_t scale_bytes = ((size_t)M * 4 + 127) / 128 * 128;
@@ -504,6 +602,27 @@ extern "C" int32_t scr_fp8_quant_per_token(scr_ctx* ctx, const uint16_t* x, int3
     const int M_pad = scr_ceil_div(M, FP8_TILE) * FP8_TILE;
     fp8_quant_per_token_kernel<<<M, QUANT_THREADS, 0, (cudaStream_t)stream>>>(x, M, K, tiled, M_pad, (uint8_t*)act);
     return scr_check_launch(ctx, "fp8_quant_per_token");
+}
+
+extern "C" int32_t scr_rmsnorm_fp8_quant(scr_ctx* ctx, const uint16_t* x, const uint16_t* gain, float eps, int32_t M, int32_t K,
+                                         void* act, uint16_t* normed_out, void* stream) {
+    SCR_REQUIRE_CTX(ctx);
+    if (!x || !gain || !act) return scr_fail(ctx, SCR_E_ARG, "null pointer");
+    if (M <= 0 || K <= 0) return scr_fail(ctx, SCR_E_SHAPE, "M=%d K=%d must be positive", M, K);
+    if (K % 8 != 0) return scr_fail(ctx, SCR_E_SHAPE, "K=%d must be a multiple of 8", K);
+    if (!scr_aligned16(x) || !scr_aligned16(gain) || !scr_aligned16(act) || (normed_out && !scr_aligned16(normed_out)))
+        return scr_fail(ctx, SCR_E_ALIGN, "x/gain/act/normed must be 16-byte aligned");
+    const size_t smem = (size_t)K * sizeof(float);
+    if (smem > 200 * 1024) return scr_fail(ctx, SCR_E_UNSUPPORTED, "K=%d exceeds the shared-memory row buffer", K);
+    if (smem > 48 * 1024) {
+        const cudaError_t e = cudaFuncSetAttribute(fp8_rmsnorm_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "rmsnorm_fp8_quant smem attribute: %s", cudaGetErrorString(e));
+    }
+    const int tiled = fp8_act_tiled(M) ? 1 : 0;
+    const int M_pad = scr_ceil_div(M, FP8_TILE) * FP8_TILE;
+    fp8_rmsnorm_quant_kernel<<<M, QUANT_THREADS, smem, (cudaStream_t)stream>>>(x, gain, eps, M, K, tiled, M_pad, (uint8_t*)act,
+                                                                              normed_out);
+    return scr_check_launch(ctx, "rmsnorm_fp8_quant");
 }
 
 extern "C" int32_t scr_fp8_act_unpack(scr_ctx* ctx, const void* act, int32_t M, int32_t K, uint8_t* xq, float* a_scale,

@@ -392,6 +392,24 @@ class Fp8Linear:
         ctx.check(L.scr_fp8_quant_per_token(ctx.handle, _ptr(x2), M, K, _ptr(buf), _stream(dev)))
         return Fp8ActPack(buf, M, K)
 
+    @staticmethod
+    def quantize_rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float,
+                         normed_out: Optional[torch.Tensor] = None) -> Fp8ActPack:
+        """RMSNorm and the per-token quantisation in one launch (`scr_rmsnorm_fp8_quant`): the pack that
+        `quantize_activation(rmsnorm(x))` would give, plus (optionally) the bf16 normed rows."""
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        M, K = int(x2.shape[0]), int(x2.shape[1])
+        dev = x2.device
+        size = ctypes.c_size_t(0)
+        st = _lib.lib().scr_fp8_act_size(M, K, ctypes.byref(size))
+        if st:
+            raise ScratchyCudaError(st, "scr_fp8_act_size")
+        buf = torch.empty(size.value, dtype=torch.uint8, device=dev)
+        ctx = _lib.context(_dev_index(dev))
+        ctx.check(_lib.lib().scr_rmsnorm_fp8_quant(ctx.handle, _ptr(x2), _ptr(gain), ctypes.c_float(eps), M, K, _ptr(buf),
+                                                   _ptr(normed_out), _stream(dev)))
+        return Fp8ActPack(buf, M, K)
+
     def workspace_bytes(self, M: int) -> int:
         size = ctypes.c_size_t(0)
         st = _lib.lib().scr_linear_workspace_size(KIND_FP8_DYNAMIC, M, self.out_features, self.in_features,

@@ -217,3 +217,31 @@ def test_matvec_quantises_by_itself_with_the_same_bits(N, K, M):
     assert np.array_equal(bits_of(part.to(torch.bfloat16)), bits_of(fused))
     want = oracle.fp8_dynamic_linear(bits_of(x).reshape(M, K), wq, ws, M, N, K)
     assert rel_l2(bits_of(fused).reshape(M, N), want) <= REL_L2_TOL
+
+
+@pytest.mark.parametrize("M,K", [(1, 3584), (16, 8192), (40, 3584), (300, 256), (3, 72)])
+def test_rmsnorm_fused_with_the_quantisation(M, K):
+    """The W8A8 activation producer straight from the residual stream (norm-side quantisation,
+    crates/targets/metal/src/shaders/norm_w4a8_quant.h:1-12): codes, scales and the bf16 normed rows must equal the
+    two-kernel path (rmsnorm, then quantise) bit for bit, and the oracle within its bars."""
+    import torch
+    from scratchy_b200 import Fp8Linear, decode
+    from util import bf16_to_f32
+    rng = np.random.default_rng(synth.seed_for("normq", M, K))
+    xb = synth.f32_to_bf16_bits((rng.standard_normal((M, K)) * 2.0).astype(np.float32))
+    gb = synth.f32_to_bf16_bits((1.0 + 0.1 * rng.standard_normal(K)).astype(np.float32))
+    x, g = bf16_dev(xb).reshape(M, K), bf16_dev(gb)
+    normed = torch.empty((M, K), dtype=torch.bfloat16, device="cuda")
+    fused = Fp8Linear.quantize_rmsnorm(x, g, 1e-5, normed_out=normed)
+    two_norm = decode.rmsnorm(x, g, 1e-5)
+    two = Fp8Linear.quantize_activation(two_norm)
+    xq_a, sc_a = fused.unpack()
+    xq_b, sc_b = two.unpack()
+    torch.cuda.synchronize()
+    assert np.array_equal(bits_of(normed), bits_of(two_norm))
+    assert torch.equal(xq_a, xq_b) and torch.equal(sc_a, sc_b)
+    want_norm = synth.f32_to_bf16_bits(oracle.rmsnorm(bf16_to_f32(xb), bf16_to_f32(gb), 1e-5))
+    assert rel_l2(bits_of(normed).reshape(M, K), want_norm) <= REL_L2_TOL
+    want_q, want_s = oracle.fp8_quant_per_token(want_norm, M, K)
+    assert np.allclose(sc_a.cpu().numpy(), want_s, rtol=1e-2)
+    assert np.mean(xq_a.cpu().numpy().reshape(M, K) == want_q) > 0.97
