@@ -7,7 +7,9 @@
  * `int32_t` status (0 = OK, negative = error), never throws, never aborts and
  * allocates nothing on the step path.  All device pointers must be 16-byte
  * aligned unless stated otherwise.  One caller thread drives one stream; the
- * library keeps no global mutable state besides the per-device context.
+ * library keeps no global mutable state besides the per-device context, and a
+ * context serves one host thread at a time (a call parks its variant's options
+ * in the context while it runs): give each worker thread its own context.
  *
  * Each declaration cites the reference interface it replaces (paths relative to
  * the reference project's root).
