@@ -110,63 +110,6 @@ fp8_quant_per_token_kernel(const uint16_t* __restrict__ x, int M, int K, int til
     }
 }
 
-// The same quantisation with one WARP per token, for many tokens of K <= 4096: the row stays in registers between
-// the absmax and the encode (one read of x, no block barrier).  Lane l holds the 16-byte vectors l, l+32, ...; an
-// even lane and its odd neighbour together own one 16-code output chunk.  Same arithmetic, same bits.
-#define QUANT_WARP_VECS 16
-__global__ void __launch_bounds__(QUANT_THREADS, 2)
-fp8_quant_per_token_warp_kernel(const uint16_t* __restrict__ x, int M, int K, int tiled, int M_pad, uint8_t* __restrict__ act) {
-    const int lane = threadIdx.x & 31;
-    const int m = blockIdx.x * (QUANT_THREADS / 32) + (threadIdx.x >> 5);
-    if (m >= M) return;                                   // warp-uniform
-    const uint16_t* xr = x + (size_t)m * K;
-    const int nvec = K / 8;
-    uint4 v[QUANT_WARP_VECS];
-    float amax = 0.f;
-#pragma unroll
-    for (int i = 0; i < QUANT_WARP_VECS; ++i) {
-        const int idx = lane + 32 * i;
-        v[i] = idx < nvec ? ld_nc_v4(xr + idx * 8) : make_uint4(0, 0, 0, 0);
-        const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            amax = fmaxf(amax, fabsf(__uint_as_float(w[j] << 16)));
-            amax = fmaxf(amax, fabsf(__uint_as_float(w[j] & 0xFFFF0000u)));
-        }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-    const float sc = fminf(fmaxf(__fmul_rn(amax, 1.0f / 448.0f), 1.0f / 448.0f / 448.0f), 448.0f);
-    const float inv = __fdiv_rn(1.0f, sc);
-    if (lane == 0) reinterpret_cast<float*>(act)[m] = sc;
-
-    const size_t scale_bytes = ((size_t)M * 4 + 127) / 128 * 128;
-    uint8_t* xq = act + scale_bytes;
-    const int K16 = (K + 15) / 16 * 16;
-    const int kspan = tiled ? (K + 127) / 128 * 128 : K16;
-#pragma unroll
-    for (int i = 0; i < QUANT_WARP_VECS; ++i) {
-        const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
-        uint32_t lo = 0, hi = 0;                          // 8 codes of this lane's vector
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const float a = fminf(fmaxf(__fmul_rn(__uint_as_float(w[j] << 16), inv), -448.0f), 448.0f);
-            const float b = fminf(fmaxf(__fmul_rn(__uint_as_float(w[j] & 0xFFFF0000u), inv), -448.0f), 448.0f);
-            const uint32_t two = e4m3_encode_ref(a) | (e4m3_encode_ref(b) << 8);
-            if (j < 2) lo |= two << (j * 16);
-            else hi |= two << ((j - 2) * 16);
-        }
-        const uint32_t nlo = __shfl_down_sync(0xFFFFFFFFu, lo, 1), nhi = __shfl_down_sync(0xFFFFFFFFu, hi, 1);
-        const int k0 = (lane + 32 * i) * 8;               // first k of this lane's vector; even lanes start a chunk
-        if ((lane & 1) == 0 && k0 < kspan) {
-            size_t off;
-            if (tiled) off = (size_t)(k0 >> 7) * ((size_t)M_pad * 128) + fp8_swizzled_offset(m, k0 & 127);
-            else off = (size_t)m * K16 + k0;
-            *reinterpret_cast<uint4*>(xq + off) = make_uint4(lo, hi, nlo, nhi);
-        }
-    }
-}
-
 // RMSNorm fused with the per-token quantisation: the producer of a W8A8 linear's activation pack straight from
 // the residual stream (the reference quantises on the norm side for its W4A8 path,
 // crates/targets/metal/src/shaders/norm_w4a8_quant.h:1-12; golden of the norm crates/targets/metal/src/cpu_golden.rs:25-37).
@@ -657,11 +600,7 @@ extern "C" int32_t scr_fp8_quant_per_token(scr_ctx* ctx, const uint16_t* x, int3
     if (!scr_aligned16(x) || !scr_aligned16(act)) return scr_fail(ctx, SCR_E_ALIGN, "x/act must be 16-byte aligned");
     const int tiled = fp8_act_tiled(M) ? 1 : 0;
     const int M_pad = scr_ceil_div(M, FP8_TILE) * FP8_TILE;
-    if (M >= 64 && K <= QUANT_WARP_VECS * 32 * 8)          // many tokens of a row that fits a warp's registers
-        fp8_quant_per_token_warp_kernel<<<scr_ceil_div(M, QUANT_THREADS / 32), QUANT_THREADS, 0, (cudaStream_t)stream>>>(
-            x, M, K, tiled, M_pad, (uint8_t*)act);
-    else
-        fp8_quant_per_token_kernel<<<M, QUANT_THREADS, 0, (cudaStream_t)stream>>>(x, M, K, tiled, M_pad, (uint8_t*)act);
+    fp8_quant_per_token_kernel<<<M, QUANT_THREADS, 0, (cudaStream_t)stream>>>(x, M, K, tiled, M_pad, (uint8_t*)act);
     return scr_check_launch(ctx, "fp8_quant_per_token");
 }
 
