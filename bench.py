@@ -174,13 +174,16 @@ def run_reference(args):
 
 
 # ------------------------------------------------------------------------------------ GPU arm
-def build_int4_model(device, n_layers):
+def build_int4_model(device, n_layers, fused=False):
+    """The 7 linears of every layer (synthetic, seeded per layer and shape).  With `fused`, also the same weights as
+    the reference's fused projections (`load_rows_concat`: q|k|v and gate|up as one matrix each), for the extra
+    4-launches-per-layer measurement."""
     import torch
     from scratchy_b200 import AffineQuantLinear
-    layers = []
+    layers, fused_layers = [], []
     # one set of synthetic checkpoint tensors per shape, re-drawn per layer on the device
     for li in range(n_layers):
-        row = []
+        row, raw = [], []
         for name in LAYER_ORDER:
             K, N = synth.LLAMA_3_2_3B[name]
             g = torch.Generator(device=device)
@@ -189,9 +192,14 @@ def build_int4_model(device, n_layers):
             s = (torch.randn((N, K // 64), device=device, generator=g) * 0.02).abs().add(1e-3).to(torch.bfloat16)
             b = (-8.0 * s.float() + torch.randn((N, K // 64), device=device, generator=g) * 1e-3).to(torch.bfloat16)
             row.append(AffineQuantLinear.from_tensors(w, s, b, 64, 4))
+            raw.append((w, s, b))
         layers.append(row)
+        if fused:
+            def cat(idxs):
+                return AffineQuantLinear.from_tensors(*(torch.cat([raw[i][j] for i in idxs], 0) for j in range(3)), 64, 4)
+            fused_layers.append([cat([0, 1, 2]), row[3], cat([4, 5]), row[6]])
     torch.cuda.synchronize(device)
-    return layers
+    return (layers, fused_layers) if fused else layers
 
 
 def run_gpu(args):
@@ -212,7 +220,7 @@ def run_gpu(args):
     peaks = measured_peaks()
 
     M = 1
-    layers = build_int4_model(device, N_LAYERS)
+    layers, fused_layers = build_int4_model(device, N_LAYERS, fused=True)
     shapes = [synth.LLAMA_3_2_3B[n] for n in LAYER_ORDER]
     step_bytes = N_LAYERS * sum(affine_alg_bytes(M, N, K) for K, N in shapes)
     xs = [torch.randn((M, K), device=device).to(torch.bfloat16) for K, _ in shapes]
@@ -277,6 +285,38 @@ def run_gpu(args):
     ms = ev0.elapsed_time(ev1)
     launches = launches_per_step * args.steps
     clocks = sampler.stop() if sampler else None
+
+    # ---- extra, not the headline: the same weights as the reference's fused projections, 4 launches per layer
+    fused_info = None
+    if world == 1:
+        fx = [xs[0], xs[3], xs[4], xs[6]]
+        fy = [torch.empty((M, l.out_features), dtype=torch.bfloat16, device=device) for l in fused_layers[0]]
+
+        def step_fused():
+            for row in fused_layers:
+                for i in range(4):
+                    row[i].forward(fx[i], out=fy[i])
+        step_fused()
+        torch.cuda.synchronize(device)
+        graph_f = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph_f, stream=side):
+            step_fused()
+        for _ in range(max(3, args.warmup)):
+            graph_f.replay()
+        torch.cuda.synchronize(device)
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        for _ in range(args.steps):
+            graph_f.replay()
+        f1.record()
+        torch.cuda.synchronize(device)
+        ms_f = f0.elapsed_time(f1)
+        fused_info = {"value": step_bytes * args.steps / (ms_f * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": ms_f / args.steps,
+                      "launches_per_step": 4 * N_LAYERS,
+                      "workload": "the same 7 linears per layer as q|k|v and gate|up rows-concat fused projections "
+                                  "(the reference's load_rows_concat): 4 dependent launches per layer"}
+        del graph_f
+    fused_layers = None
 
     # ---- end to end: host (pinned) activations in, host results out, through the public API.
     # Every linear's input is copied from pinned host memory and its output copied back inside
@@ -347,6 +387,8 @@ def run_gpu(args):
     achieved = step_bytes * args.steps / (ms * 1e-3) / 1e9          # one GPU's kernel stream
 
     extra = {}
+    if fused_info:
+        extra["fused_projections"] = fused_info
     if world == 1 and not args.no_decode:
         del layers, graph, graph_e2e
         layers = graph = graph_e2e = None
