@@ -220,7 +220,10 @@ def run_gpu(args):
     peaks = measured_peaks()
 
     M = 1
-    layers, fused_layers = build_int4_model(device, N_LAYERS, fused=True)
+    if world == 1:
+        layers, fused_layers = build_int4_model(device, N_LAYERS, fused=True)
+    else:
+        layers, fused_layers = build_int4_model(device, N_LAYERS), None
     shapes = [synth.LLAMA_3_2_3B[n] for n in LAYER_ORDER]
     step_bytes = N_LAYERS * sum(affine_alg_bytes(M, N, K) for K, N in shapes)
     xs = [torch.randn((M, K), device=device).to(torch.bfloat16) for K, _ in shapes]
