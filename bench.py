@@ -538,7 +538,7 @@ def run_sweep(device, ctx):
     return out
 
 
-def run_decode(device, steps=20, batches=(1, 8, 32), context=2048, block_size=16):
+def run_decode(device, steps=20, batches=(1, 8, 32), context=2048, block_size=16, fuse_rope=True):
     """BASELINE config 3: random-init Llama-3.2-3B, every linear MLX int4 g64 (lm_head too), one decode
     step at context `context` with a bf16 paged KV cache, the whole step one CUDA graph.
     tok/s = batch / step time.  The step streams all packed weights (larger than L2) plus the batch's KV."""
@@ -546,7 +546,8 @@ def run_decode(device, steps=20, batches=(1, 8, 32), context=2048, block_size=16
     from scratchy_b200 import _lib, decode
     peaks = measured_peaks()
     cfg = decode.LLAMA_3_2_3B
-    dec = decode.LlamaDecoder(cfg, decode.synthetic_checkpoint_on_device(cfg, device, 0), device, max_pos=context + 64)
+    dec = decode.LlamaDecoder(cfg, decode.synthetic_checkpoint_on_device(cfg, device, 0), device, max_pos=context + 64,
+                              fuse_rope=fuse_rope)
     ctx = _lib.context(device.index)
     out = []
     blocks_per_seq = (context + 1 + block_size - 1) // block_size
@@ -801,6 +802,7 @@ def main():
     ap.add_argument("--no-decode", action="store_true", help="skip the whole-decode-step section (config 3)")
     ap.add_argument("--decode-only", action="store_true", help="run only the whole-decode-step section and print it")
     ap.add_argument("--decode-batches", default="1,8,32")
+    ap.add_argument("--no-fuse-rope", action="store_true", help="decode step with RoPE + append as a kernel of their own")
     ap.add_argument("--case", default=None, help="kind,shape,M e.g. int4,gate,2048: time one linear alone")
     args = ap.parse_args()
     if args.case:
@@ -810,7 +812,8 @@ def main():
         import torch
         device = torch.device("cuda", 0)
         torch.cuda.set_device(device)
-        cases = run_decode(device, steps=args.steps, batches=tuple(int(b) for b in args.decode_batches.split(",")))
+        cases = run_decode(device, steps=args.steps, batches=tuple(int(b) for b in args.decode_batches.split(",")),
+                           fuse_rope=not args.no_fuse_rope)
         print(json.dumps({"decode": cases}))
         return
     if args.impl == "reference":

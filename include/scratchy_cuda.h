@@ -244,6 +244,25 @@ int32_t scr_attention_via_cache_bf16(scr_ctx* ctx, const uint16_t* q, int64_t ld
                                      int32_t batch, int32_t num_q_heads, int32_t num_kv_heads,
                                      int32_t head_dim, int32_t block_size,
                                      int32_t max_blocks_per_seq, float attn_scale, void* stream);
+/* `rope_append` (cpu_golden.rs:289-362) followed by `attention_via_cache` (cpu_golden.rs:386-460) as
+ * ONE launch for a decode step: q, k, v are the unrotated outputs of the QKV projection (one token
+ * per sequence); the kernel rotates q in registers, rotates k and stores it and v into the cache
+ * slot of token seq_used_k[b] - 1 of sequence b (block block_table[b][(seq_used_k[b]-1) /
+ * block_size], i.e. the slot the reference's slot_mapping names for that token), and attends over
+ * the seq_used_k[b] tokens including it.  q is left unrotated.  The cache contents and `out` are
+ * the same bits as the two separate calls give.  Needs block_size a multiple of 16 (<= 256);
+ * SCR_E_UNSUPPORTED otherwise — call the two operators separately then. */
+int32_t scr_rope_attention_via_cache_bf16(scr_ctx* ctx, const uint16_t* q, int64_t ld_q,
+                                          const uint16_t* k, int64_t ld_k, const uint16_t* v,
+                                          int64_t ld_v, const uint32_t* positions,
+                                          const float* cos_table, const float* sin_table,
+                                          int32_t max_pos, uint16_t* cache_k, uint16_t* cache_v,
+                                          int32_t num_blocks, const uint32_t* block_table,
+                                          const uint32_t* seq_used_k, uint16_t* out, int64_t ld_o,
+                                          int32_t batch, int32_t num_q_heads, int32_t num_kv_heads,
+                                          int32_t head_dim, int32_t block_size,
+                                          int32_t max_blocks_per_seq, float attn_scale,
+                                          void* stream);
 /* Greedy sampling (crates/targets/metal/tests/argmax_split_test.rs:24-33): per row the id of the
  * largest value, the smallest id among equal ones, NaN never. */
 int32_t scr_argmax_bf16(scr_ctx* ctx, const uint16_t* logits, int64_t ld, int32_t rows,

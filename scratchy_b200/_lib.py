@@ -72,6 +72,9 @@ SIGNATURES = {
                                     _i32, _i32, _i32, _i32, _i32, _i32, _vp]),
     "scr_attention_via_cache_bf16": (_i32, [_vp, _vp, _i64, _vp, _vp, _i32, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32,
                                             _i32, _i32, ctypes.c_float, _vp]),
+    "scr_rope_attention_via_cache_bf16": (_i32, [_vp, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _i32, _vp, _vp, _i32,
+                                                 _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _i32, ctypes.c_float,
+                                                 _vp]),
     "scr_argmax_bf16": (_i32, [_vp, _vp, _i64, _i32, _i32, _vp, _vp]),
 }
 

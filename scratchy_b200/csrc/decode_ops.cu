@@ -583,12 +583,45 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) { return f32_to_bf16_bits(lo) | (f32_to_bf16_bits(hi) << 16); }
 
+// RoPE + append folded into the attention (`enabled`): q, k_new, v_new are the UNrotated outputs of the QKV
+// projection; the kernel rotates q in registers, and the CTA that owns the sequence's newest block rotates k_new,
+// writes it and v_new into the token's cache slot (for later steps) and patches them into its shared-memory tile
+// (for this one).  Products and sums are rounded as in the stand-alone kernel, so q, the cache and the attention
+// output are the same bits as `rope_append` followed by the plain attention.
+struct AttRope {
+    const uint16_t* k_new;
+    const uint16_t* v_new;
+    const uint32_t* positions;
+    const float* cos_table;
+    const float* sin_table;
+    uint16_t* cache_k;
+    uint16_t* cache_v;
+    long long ld_k, ld_v;
+    uint32_t max_pos;
+    int enabled;
+};
+
+__device__ __forceinline__ uint32_t att_rope_pair(uint32_t x0w, uint32_t x1w, const float* c, const float* s, bool first) {
+    // two adjacent dims: lo/hi halves of the words; `first` selects the output for d (x0*c - x1*s) or d + half (x1*c + x0*s)
+    const float x0l = __uint_as_float(x0w << 16), x0h = __uint_as_float(x0w & 0xFFFF0000u);
+    const float x1l = __uint_as_float(x1w << 16), x1h = __uint_as_float(x1w & 0xFFFF0000u);
+    float rl, rh;
+    if (first) {
+        rl = __fsub_rn(__fmul_rn(x0l, c[0]), __fmul_rn(x1l, s[0]));
+        rh = __fsub_rn(__fmul_rn(x0h, c[1]), __fmul_rn(x1h, s[1]));
+    } else {
+        rl = __fadd_rn(__fmul_rn(x1l, c[0]), __fmul_rn(x0l, s[0]));
+        rh = __fadd_rn(__fmul_rn(x1h, c[1]), __fmul_rn(x0h, s[1]));
+    }
+    return pack_bf16x2(rl, rh);
+}
+
 template <int D>
 __global__ void __launch_bounds__(ATTB_THREADS) attention_decode_tc_kernel(
     const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map, const uint16_t* __restrict__ q,
     long long ld_q, const uint32_t* __restrict__ block_table, const uint32_t* __restrict__ seq_used_k,
     uint16_t* __restrict__ out, long long ld_o, int G, int num_kv_heads, int block_size, int max_blocks_per_seq,
-    uint32_t num_blocks, int table_cap, int stages, float scale, int* status) {
+    uint32_t num_blocks, int table_cap, int stages, float scale, int* status, AttRope rope) {
     constexpr int NH = D / 64;                       // 128-byte rows per token
     constexpr int STATE = D + 2;
     constexpr int KSTEPS = D / 16;
@@ -662,8 +695,8 @@ __global__ void __launch_bounds__(ATTB_THREADS) attention_decode_tc_kernel(
             for (int n = 0;; ++n) {
                 const int i = w + nwarps * (r + spw * n);
                 if (i >= nblk) break;
-                if (!waited && first_blk + i >= newest_blk) {
-                    pdl_wait();
+                if (!rope.enabled && !waited && first_blk + i >= newest_blk) {
+                    pdl_wait();                    // (with the append folded in, no preceding kernel writes the cache)
                     waited = true;
                 }
                 if (n >= 1 && !mbar_wait(smem_u32(&bars[stages + lane]), uint32_t((n - 1) & 1), status, ATT_ERR_EMPTY)) break;
@@ -691,6 +724,24 @@ __global__ void __launch_bounds__(ATTB_THREADS) attention_decode_tc_kernel(
                 qa2[kk] = *reinterpret_cast<const uint32_t*>(qp + 8);
             }
         }
+        if (rope.enabled) {
+            const uint32_t pos = rope.positions[b];
+            if (pos >= rope.max_pos) {
+                if (lane == 0) atomicCAS(status, 0, DEV_BAD_POSITION);
+            } else if (row < G) {
+                const float* cs = rope.cos_table + size_t(pos) * D;
+                const float* sn = rope.sin_table + size_t(pos) * D;
+#pragma unroll
+                for (int kk = 0; kk < KSTEPS / 2; ++kk) {
+                    const int d = kk * 16 + quad * 2;                      // < D/2; partner dim d + D/2 sits KSTEPS/2 steps on
+                    const uint32_t a0 = qa0[kk], b0 = qa0[kk + KSTEPS / 2], a2 = qa2[kk], b2 = qa2[kk + KSTEPS / 2];
+                    qa0[kk] = att_rope_pair(a0, b0, cs + d, sn + d, true);
+                    qa0[kk + KSTEPS / 2] = att_rope_pair(a0, b0, cs + d, sn + d, false);
+                    qa2[kk] = att_rope_pair(a2, b2, cs + d + 8, sn + d + 8, true);
+                    qa2[kk + KSTEPS / 2] = att_rope_pair(a2, b2, cs + d + 8, sn + d + 8, false);
+                }
+            }
+        }
         const float sl2 = scale * 1.4426950408889634f;                     // scores live in the log2 domain
         float m2 = -INFINITY, lsum = 0.0f;                                 // this lane's row; lsum is the lane's share of the row sum
         float o[NTILES][2];
@@ -708,6 +759,42 @@ __global__ void __launch_bounds__(ATTB_THREADS) attention_decode_tc_kernel(
             const uint32_t kst = smem_u32(ring + size_t(s) * 2 * chunk);
             const uint32_t vst = kst + chunk;
             const int t0 = (first_blk + i) * block_size;
+            if (rope.enabled && first_blk + i == newest_blk) {
+                // the newest token: rotate k_new, write it and v_new to the cache slot and into this tile
+                const int slot = kv_len - 1 - t0;
+                const uint32_t pos = rope.positions[b];
+                const size_t cache_off = ((size_t(blocks[i]) * num_kv_heads + kvh) * block_size + slot) * D;
+                unsigned char* ktile = ring + size_t(s) * 2 * chunk;
+                // a block id outside the cache was replaced by 0 for the loads (and reported): never append there
+                const bool slot_ok = pos < rope.max_pos && block_table[size_t(b) * max_blocks_per_seq + newest_blk] < num_blocks;
+                if (slot_ok && lane < D / 16) {
+                    const int d = lane * 8;                                // dims d..d+7 pair with d + D/2 ..
+                    const uint16_t* kp = rope.k_new + b * rope.ld_k + size_t(kvh) * D;
+                    const uint4 x0 = *reinterpret_cast<const uint4*>(kp + d), x1 = *reinterpret_cast<const uint4*>(kp + d + D / 2);
+                    const float* cs = rope.cos_table + size_t(pos) * D + d;
+                    const float* sn = rope.sin_table + size_t(pos) * D + d;
+                    const uint32_t xw0[4] = {x0.x, x0.y, x0.z, x0.w}, xw1[4] = {x1.x, x1.y, x1.z, x1.w};
+                    uint32_t r0[4], r1[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        r0[j] = att_rope_pair(xw0[j], xw1[j], cs + 2 * j, sn + 2 * j, true);
+                        r1[j] = att_rope_pair(xw0[j], xw1[j], cs + 2 * j, sn + 2 * j, false);
+                    }
+                    const uint4 o0 = make_uint4(r0[0], r0[1], r0[2], r0[3]), o1 = make_uint4(r1[0], r1[1], r1[2], r1[3]);
+                    *reinterpret_cast<uint4*>(rope.cache_k + cache_off + d) = o0;
+                    *reinterpret_cast<uint4*>(rope.cache_k + cache_off + d + D / 2) = o1;
+                    const int d1 = d + D / 2;
+                    *reinterpret_cast<uint4*>(ktile + (d >> 6) * half_bytes + slot * 128 + ((((d & 63) >> 3) ^ (slot & 7)) << 4)) = o0;
+                    *reinterpret_cast<uint4*>(ktile + (d1 >> 6) * half_bytes + slot * 128 + ((((d1 & 63) >> 3) ^ (slot & 7)) << 4)) = o1;
+                }
+                if (slot_ok && lane >= 16 && lane < 16 + D / 8) {
+                    const int d = (lane - 16) * 8;
+                    const uint4 vv = *reinterpret_cast<const uint4*>(rope.v_new + b * rope.ld_v + size_t(kvh) * D + d);
+                    *reinterpret_cast<uint4*>(rope.cache_v + cache_off + d) = vv;
+                    *reinterpret_cast<uint4*>(ktile + chunk + (d >> 6) * half_bytes + slot * 128 + ((((d & 63) >> 3) ^ (slot & 7)) << 4)) = vv;
+                }
+                __syncwarp();                                              // the patched tile is read by this warp's ldmatrix
+            }
             for (int sub = 0; sub < block_size; sub += 16) {
                 if (t0 + sub >= kv_len) break;
                 // S[16 x 16 tokens] = Q K^T
@@ -808,7 +895,7 @@ template <int D, int G>
 cudaError_t attention_launch(const uint16_t* q, long long ld_q, const uint16_t* cache_k, const uint16_t* cache_v,
                              const uint32_t* block_table, const uint32_t* seq_used_k, uint16_t* out, long long ld_o, int batch,
                              int num_kv_heads, int block_size, int max_blocks_per_seq, uint32_t num_blocks, float scale,
-                             int sm_count, int* status, cudaStream_t stream) {
+                             int sm_count, int* status, cudaStream_t stream, const AttRope& rope) {
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -868,8 +955,9 @@ cudaError_t attention_launch(const uint16_t* q, long long ld_q, const uint16_t* 
         cfg.dynamicSmemBytes = smem;
         attr[0].val.clusterDim.x = nsplit;
         return cudaLaunchKernelEx(&cfg, kernel, maps[0], maps[1], q, ld_q, block_table, seq_used_k, out, ld_o, G, num_kv_heads,
-                                  block_size, max_blocks_per_seq, num_blocks, table_cap, stages, scale, status);
+                                  block_size, max_blocks_per_seq, num_blocks, table_cap, stages, scale, status, rope);
     }
+    if (rope.enabled) return cudaErrorNotSupported;  // the rotation and the append are folded into the streaming variant only
     // small or odd blocks: per-token loads
     const int cap1 = max_blocks_per_seq / ATT_SPLITS + 3;
     const size_t smem = warp_part + part + size_t(cap1) * sizeof(uint32_t);
@@ -887,9 +975,10 @@ cudaError_t attention_launch(const uint16_t* q, long long ld_q, const uint16_t* 
 template <int D>
 cudaError_t attention_dispatch_g(int G, const uint16_t* q, long long ld_q, const uint16_t* ck, const uint16_t* cv,
                                  const uint32_t* bt, const uint32_t* used, uint16_t* out, long long ld_o, int batch, int hkv,
-                                 int bs, int mb, uint32_t nb, float scale, int sms, int* status, cudaStream_t st) {
+                                 int bs, int mb, uint32_t nb, float scale, int sms, int* status, cudaStream_t st,
+                                 const AttRope& rope) {
     switch (G) {
-#define ATT_CASE(GG) case GG: return attention_launch<D, GG>(q, ld_q, ck, cv, bt, used, out, ld_o, batch, hkv, bs, mb, nb, scale, sms, status, st)
+#define ATT_CASE(GG) case GG: return attention_launch<D, GG>(q, ld_q, ck, cv, bt, used, out, ld_o, batch, hkv, bs, mb, nb, scale, sms, status, st, rope)
         ATT_CASE(1); ATT_CASE(2); ATT_CASE(3); ATT_CASE(4); ATT_CASE(5); ATT_CASE(6); ATT_CASE(7); ATT_CASE(8);
 #undef ATT_CASE
         default: return cudaErrorInvalidValue;
@@ -1030,17 +1119,74 @@ extern "C" int32_t scr_attention_via_cache_bf16(scr_ctx* ctx, const uint16_t* q,
                 "attention: q / cache not 16-byte aligned");
     DEC_REQUIRE(max_blocks_per_seq <= (1 << 20), SCR_E_UNSUPPORTED, "attention: block table wider than 2^20 blocks");
     if (batch == 0) return SCR_OK;
+    AttRope rope = {};
     cudaError_t e;
     if (head_dim == 128)
         e = attention_dispatch_g<128>(G, q, ld_q, cache_k, cache_v, block_table, seq_used_k, out, ld_o, batch, num_kv_heads,
                                       block_size, max_blocks_per_seq, uint32_t(num_blocks), attn_scale, ctx->sm_count, ctx->dev_status,
-                                      (cudaStream_t)stream);
+                                      (cudaStream_t)stream, rope);
     else
         e = attention_dispatch_g<64>(G, q, ld_q, cache_k, cache_v, block_table, seq_used_k, out, ld_o, batch, num_kv_heads,
                                      block_size, max_blocks_per_seq, uint32_t(num_blocks), attn_scale, ctx->sm_count, ctx->dev_status,
-                                     (cudaStream_t)stream);
+                                     (cudaStream_t)stream, rope);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "attention: %s", cudaGetErrorString(e));
     return scr_check_launch(ctx, "attention_via_cache");
+}
+
+extern "C" int32_t scr_rope_attention_via_cache_bf16(scr_ctx* ctx, const uint16_t* q, int64_t ld_q, const uint16_t* k, int64_t ld_k,
+                                                     const uint16_t* v, int64_t ld_v, const uint32_t* positions,
+                                                     const float* cos_table, const float* sin_table, int32_t max_pos,
+                                                     uint16_t* cache_k, uint16_t* cache_v, int32_t num_blocks,
+                                                     const uint32_t* block_table, const uint32_t* seq_used_k, uint16_t* out,
+                                                     int64_t ld_o, int32_t batch, int32_t num_q_heads, int32_t num_kv_heads,
+                                                     int32_t head_dim, int32_t block_size, int32_t max_blocks_per_seq,
+                                                     float attn_scale, void* stream) {
+    SCR_REQUIRE_CTX(ctx);
+    DEC_REQUIRE(q && k && v && positions && cos_table && sin_table && cache_k && cache_v && block_table && seq_used_k && out, SCR_E_ARG,
+                "rope_attention: null pointer");
+    DEC_REQUIRE(batch >= 0 && num_q_heads > 0 && num_kv_heads > 0 && num_q_heads % num_kv_heads == 0 && block_size > 0 &&
+                    max_blocks_per_seq > 0 && num_blocks > 0 && max_pos > 0,
+                SCR_E_SHAPE, "rope_attention: bad head / block geometry");
+    const int G = num_q_heads / num_kv_heads;
+    DEC_REQUIRE(head_dim == 64 || head_dim == 128, SCR_E_UNSUPPORTED, "rope_attention: head_dim=%d (64 and 128 are built)", head_dim);
+    DEC_REQUIRE(G <= 8, SCR_E_UNSUPPORTED, "rope_attention: %d query heads per kv head (up to 8 are built)", G);
+    DEC_REQUIRE(block_size % 16 == 0 && block_size <= 256, SCR_E_UNSUPPORTED,
+                "rope_attention: block_size=%d (multiples of 16 up to 256; use rope_append + attention_via_cache otherwise)", block_size);
+    DEC_REQUIRE(batch <= 65535 && num_kv_heads <= 65535, SCR_E_SHAPE, "rope_attention: batch / kv heads exceed the grid limits");
+    const int64_t qd = (int64_t)num_q_heads * head_dim, kd = (int64_t)num_kv_heads * head_dim;
+    DEC_REQUIRE(ld_q >= qd && ld_o >= qd && ld_k >= kd && ld_v >= kd && ld_q % 8 == 0 && ld_k % 8 == 0 && ld_v % 8 == 0, SCR_E_SHAPE,
+                "rope_attention: a row stride is shorter than its row or not a multiple of 8");
+    DEC_REQUIRE(scr_aligned16(q) && scr_aligned16(k) && scr_aligned16(v) && scr_aligned16(cache_k) && scr_aligned16(cache_v), SCR_E_ALIGN,
+                "rope_attention: q / k / v / cache not 16-byte aligned");
+    DEC_REQUIRE(max_blocks_per_seq <= (1 << 20), SCR_E_UNSUPPORTED, "rope_attention: block table wider than 2^20 blocks");
+    if (batch == 0) return SCR_OK;
+    AttRope rope = {};
+    rope.k_new = k;
+    rope.v_new = v;
+    rope.positions = positions;
+    rope.cos_table = cos_table;
+    rope.sin_table = sin_table;
+    rope.cache_k = cache_k;
+    rope.cache_v = cache_v;
+    rope.ld_k = ld_k;
+    rope.ld_v = ld_v;
+    rope.max_pos = uint32_t(max_pos);
+    rope.enabled = 1;
+    cudaError_t e;
+    if (head_dim == 128)
+        e = attention_dispatch_g<128>(G, q, ld_q, cache_k, cache_v, block_table, seq_used_k, out, ld_o, batch, num_kv_heads,
+                                      block_size, max_blocks_per_seq, uint32_t(num_blocks), attn_scale, ctx->sm_count, ctx->dev_status,
+                                      (cudaStream_t)stream, rope);
+    else
+        e = attention_dispatch_g<64>(G, q, ld_q, cache_k, cache_v, block_table, seq_used_k, out, ld_o, batch, num_kv_heads,
+                                     block_size, max_blocks_per_seq, uint32_t(num_blocks), attn_scale, ctx->sm_count, ctx->dev_status,
+                                     (cudaStream_t)stream, rope);
+    if (e == cudaErrorNotSupported) {
+        (void)cudaGetLastError();
+        return scr_fail(ctx, SCR_E_UNSUPPORTED, "rope_attention: this geometry has no streaming variant (use rope_append + attention_via_cache)");
+    }
+    if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "rope_attention: %s", cudaGetErrorString(e));
+    return scr_check_launch(ctx, "rope_attention_via_cache");
 }
 
 extern "C" int32_t scr_argmax_bf16(scr_ctx* ctx, const uint16_t* logits, int64_t ld, int32_t rows, int32_t width, uint32_t* out,

@@ -2,7 +2,8 @@
 
 Host-side mirror of the reference's decode program (embed -> per layer [rmsnorm, fused QKV, RoPE +
 paged-KV append, paged decode attention, o, residual add + rmsnorm, fused gate/up, silu*up, down] ->
-final norm -> lm_head -> greedy argmax).  Up to 16 tokens silu*up runs as the epilogue of the gate/up matvec.
+final norm -> lm_head -> greedy argmax).  Up to 16 tokens silu*up runs as the epilogue of the gate/up matvec,
+and RoPE + the cache append run inside the attention launch when the cache's blocks are multiples of 16 tokens.
 The residual add + rmsnorm can run as the epilogue of the o / down matvecs too (`fuse_residual_norm=True`), but
 that measured slower than the separate kernel (the ticket and the last CTA's serial pass cost more than the
 launch they save), so it is off by default.  Each operator wrapper names the reference host golden it is
@@ -122,6 +123,33 @@ def attention_via_cache(q: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.T
         _ptr(out), _rows(out), batch, num_q_heads, num_kv_heads, head_dim, block_size, int(block_table.shape[1]),
         ctypes.c_float(attn_scale), _stream(dev)))
     return out
+
+
+def rope_attention_via_cache(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, positions: torch.Tensor,
+                             cos_table: torch.Tensor, sin_table: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tensor,
+                             block_table: torch.Tensor, seq_used_k: torch.Tensor, num_q_heads: int, num_kv_heads: int,
+                             head_dim: int, block_size: int, attn_scale: float,
+                             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """`rope_append` then `attention_via_cache` (cpu_golden.rs:289-362, 386-460) in one launch for a decode step.
+    The new token of sequence b lands in the slot of token seq_used_k[b] - 1 (what the reference's slot_mapping
+    names for it); q is left unrotated.  Raises SCR_E_UNSUPPORTED unless block_size is a multiple of 16 (<= 256)."""
+    dev = q.device
+    batch = int(q.shape[0])
+    if out is None:
+        out = torch.empty((batch, num_q_heads * head_dim), dtype=torch.bfloat16, device=dev)
+    num_blocks = cache_k.numel() // (num_kv_heads * block_size * head_dim)
+    c = _ctx(dev)
+    c.check(_lib.lib().scr_rope_attention_via_cache_bf16(
+        c.handle, _ptr(q), _rows(q), _ptr(k), _rows(k), _ptr(v), _rows(v), _ptr(positions), _ptr(cos_table), _ptr(sin_table),
+        int(cos_table.shape[0]), _ptr(cache_k), _ptr(cache_v), int(num_blocks), _ptr(block_table), _ptr(seq_used_k),
+        _ptr(out), _rows(out), batch, num_q_heads, num_kv_heads, head_dim, block_size, int(block_table.shape[1]),
+        ctypes.c_float(attn_scale), _stream(dev)))
+    return out
+
+
+def rope_attention_supported(block_size: int) -> bool:
+    """Geometries for which the one-launch RoPE + append + attention exists."""
+    return block_size % 16 == 0 and block_size <= 256
 
 
 def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -303,13 +331,17 @@ class DecodeBuffers:
 class LlamaDecoder:
     """Random-init or checkpoint-loaded Llama decoder whose every linear is MLX affine int4 g64."""
 
-    def __init__(self, cfg: LlamaConfig, checkpoint, device, max_pos: int = 4096, fuse_residual_norm: bool = False):
+    def __init__(self, cfg: LlamaConfig, checkpoint, device, max_pos: int = 4096, fuse_residual_norm: bool = False,
+                 fuse_rope: bool = True):
         """`checkpoint`: a `GpuWeights` (e.g. `CheckpointWeights.from_dir(...)`) or a dict of host / device
-        tensors with the HF Llama names."""
+        tensors with the HF Llama names.  `fuse_rope`: run RoPE + cache append inside the attention launch where
+        the cache geometry allows it (the new token's slot is then taken from block_table / seq_used_k, which a
+        decode step keeps consistent with slot_mapping)."""
         if not torch.cuda.is_available():
             raise _lib.ScratchyCudaError(-5, "LlamaDecoder needs a CUDA device (there is no CPU path)")
         self.cfg, self.device = cfg, torch.device(device)
         self.fuse_residual_norm = fuse_residual_norm
+        self.fuse_rope = fuse_rope
         dev = self.device
         gw = checkpoint if isinstance(checkpoint, GpuWeights) else GpuWeights({k: _to_device(v, dev)
                                                                               for k, v in checkpoint.items()})
@@ -361,10 +393,15 @@ class LlamaDecoder:
         for i, layer in enumerate(self.layers):
             layer.qkv.forward(buf.normed, out=buf.qkv, workspace=buf.workspace)
             q, k, v = buf.qkv[:, :qd], buf.qkv[:, qd:qd + kd], buf.qkv[:, qd + kd:]
-            rope_append(q, k, v, buf.positions, buf.slot_mapping, self.cos, self.sin, cache.k[i], cache.v[i],
-                        cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, cache.block_size)
-            attention_via_cache(q, cache.k[i], cache.v[i], buf.block_table, buf.seq_used_k, cfg.n_q_heads,
-                                cfg.n_kv_heads, cfg.head_dim, cache.block_size, self.attn_scale, out=buf.attn)
+            if self.fuse_rope and rope_attention_supported(cache.block_size):
+                rope_attention_via_cache(q, k, v, buf.positions, self.cos, self.sin, cache.k[i], cache.v[i], buf.block_table,
+                                         buf.seq_used_k, cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, cache.block_size,
+                                         self.attn_scale, out=buf.attn)
+            else:
+                rope_append(q, k, v, buf.positions, buf.slot_mapping, self.cos, self.sin, cache.k[i], cache.v[i],
+                            cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, cache.block_size)
+                attention_via_cache(q, cache.k[i], cache.v[i], buf.block_table, buf.seq_used_k, cfg.n_q_heads,
+                                    cfg.n_kv_heads, cfg.head_dim, cache.block_size, self.attn_scale, out=buf.attn)
             nxt = self.layers[i + 1].input_norm if i + 1 < len(self.layers) else self.final_norm
             if self.fuse_residual_norm:
                 layer.o.forward_residual_rmsnorm(buf.attn, buf.residual, layer.post_norm, cfg.rms_eps, buf.normed,

@@ -207,6 +207,77 @@ def test_attention_sharp_softmax():
     assert rel_l2(got, want) <= REL_L2_TOL
 
 
+@pytest.mark.parametrize("lens,hq,hkv,d,bs", [
+    ([2049], 24, 8, 128, 16),                 # the newest token opens a block of its own (slot 0), clusters of 8
+    ([2048, 77, 1, 300, 16, 17, 128, 640], 24, 8, 128, 16),   # last slot of a block, a one-token sequence, ...
+    ([700 - 13 * i for i in range(10)], 24, 8, 128, 16),      # clusters of 4
+    ([1 + 11 * i for i in range(40)], 24, 8, 128, 16),        # one CTA per pair
+    ([200, 33, 16], 8, 8, 64, 16),            # head_dim 64
+    ([1000, 65], 16, 2, 64, 64),              # 8 query heads per kv head, 64-token blocks
+    ([5000, 33], 8, 2, 128, 32),              # the ring wraps before the newest block arrives
+])
+def test_rope_attention_one_launch_equals_the_two_operators(lens, hq, hkv, d, bs):
+    """RoPE + append folded into the attention launch: the cache and the output are the bits that
+    `rope_append` followed by `attention_via_cache` produce, and both match the oracle."""
+    import torch
+    from scratchy_b200 import _lib, decode
+    rng = np.random.default_rng(synth.seed_for("ropeattn", len(lens), hq, hkv, d, bs))
+    batch = len(lens)
+    max_blocks = max((n + bs - 1) // bs for n in lens) + 1
+    nblk = batch * max_blocks + 3
+    table = rng.permutation(nblk)[:batch * max_blocks].reshape(batch, max_blocks).astype(np.uint32)
+    ck = rbits(rng.standard_normal((nblk, hkv, bs, d)))
+    cv = rbits(rng.standard_normal((nblk, hkv, bs, d)))
+    qkv = rbits(rng.standard_normal((batch, (hq + 2 * hkv) * d)))
+    cos, sin = (rng.uniform(-1, 1, size=(64, d)).astype(np.float32) for _ in range(2))
+    pos = rng.integers(0, 64, size=batch).astype(np.uint32)
+    used = np.array(lens, np.uint32)
+    slots = np.array([table[b, (lens[b] - 1) // bs] * bs + (lens[b] - 1) % bs for b in range(batch)], np.uint32)
+    qd, kd = hq * d, hkv * d
+    scale = 1.0 / math.sqrt(d)
+    # the two operators
+    t = bf16_dev(qkv)
+    k2, v2 = bf16_dev(ck), bf16_dev(cv)
+    decode.rope_append(t[:, :qd], t[:, qd:qd + kd], t[:, qd + kd:], i32_dev(pos), i32_dev(slots), to_dev(cos), to_dev(sin),
+                       k2, v2, hq, hkv, d, bs)
+    two = decode.attention_via_cache(t[:, :qd], k2, v2, i32_dev(table), i32_dev(used), hq, hkv, d, bs, scale)
+    # one launch
+    u = bf16_dev(qkv)
+    k1, v1 = bf16_dev(ck), bf16_dev(cv)
+    one = decode.rope_attention_via_cache(u[:, :qd], u[:, qd:qd + kd], u[:, qd + kd:], i32_dev(pos), to_dev(cos), to_dev(sin),
+                                          k1, v1, i32_dev(table), i32_dev(used), hq, hkv, d, bs, scale)
+    torch.cuda.synchronize()
+    _lib.context(0).device_status(None)
+    assert np.array_equal(bits_of(u), qkv), "the fused call leaves q, k, v as the projection wrote them"
+    assert np.array_equal(bits_of(k1), bits_of(k2)) and np.array_equal(bits_of(v1), bits_of(v2)), "cache contents"
+    assert np.array_equal(bits_of(one), bits_of(two)), "attention output"
+    f = bf16_to_f32(qkv)
+    ok, ov = bf16_to_f32(ck).copy(), bf16_to_f32(cv).copy()
+    q_rot = oracle.rope_append(f[:, :qd], f[:, qd:qd + kd], f[:, qd + kd:], pos, slots, cos, sin, ok, ov, hq, hkv, d, bs)
+    assert np.array_equal(bits_of(k1), rbits(ok)) and np.array_equal(bits_of(v1), rbits(ov))
+    want = oracle.attention_via_cache(bf16_to_f32(rbits(q_rot)), bf16_to_f32(rbits(ok)), ov, table, used, hq, hkv, d, bs,
+                                      np.float32(scale))
+    assert rel_l2(bits_of(one), rbits(want)) <= REL_L2_TOL
+
+
+def test_rope_attention_refuses_what_it_cannot_stream():
+    """Blocks that are not a multiple of 16 tokens have no one-launch form: the call says so and touches nothing."""
+    import torch
+    from scratchy_b200 import _lib, decode
+    rng = np.random.default_rng(4)
+    hq, hkv, d, bs = 4, 2, 64, 4
+    ck = rbits(rng.standard_normal((6, hkv, bs, d)))
+    k1, v1 = bf16_dev(ck), bf16_dev(ck)
+    u = bf16_dev(rbits(rng.standard_normal((1, (hq + 2 * hkv) * d))))
+    tab = to_dev(np.zeros((64, d), np.float32))
+    with pytest.raises(_lib.ScratchyCudaError) as e:
+        decode.rope_attention_via_cache(u[:, :hq * d], u[:, hq * d:(hq + hkv) * d], u[:, (hq + hkv) * d:], i32_dev(np.array([3])),
+                                        tab, tab, k1, v1, i32_dev(np.array([[1, 2]])), i32_dev(np.array([4])), hq, hkv, d, bs, 0.125)
+    assert e.value.status == -7
+    torch.cuda.synchronize()
+    assert np.array_equal(bits_of(k1), ck) and not decode.rope_attention_supported(bs)
+
+
 def test_argmax_bit_exact():
     import torch
     from scratchy_b200 import decode
@@ -267,12 +338,14 @@ def _oracle_step(cfg, ck, ids, pos, slots, table, used, cache_k, cache_v, cos, s
     return _oracle_linear(ck, ["lm_head"], normed, cfg.hidden)
 
 
-@pytest.mark.parametrize("batch,fuse_residual_norm,head_dim,bs,max_ctx", [
-    (1, False, 64, 4, 20), (3, False, 64, 4, 20), (20, False, 64, 4, 20), (3, True, 64, 4, 20),
-    # 16-token blocks and head_dim 128: the TMA + tensor-core attention, which streams the old cache blocks
-    # while the RoPE/append kernel before it is still running and waits only for the newest block
-    (2, False, 128, 16, 100), (9, False, 128, 16, 100)])
-def test_decode_step_matches_oracle_chain(batch, fuse_residual_norm, head_dim, bs, max_ctx):
+@pytest.mark.parametrize("batch,fuse_residual_norm,head_dim,bs,max_ctx,fuse_rope", [
+    (1, False, 64, 4, 20, True), (3, False, 64, 4, 20, True), (20, False, 64, 4, 20, True), (3, True, 64, 4, 20, True),
+    # 16-token blocks and head_dim 128: the TMA + tensor-core attention.  With RoPE + append as a kernel of their
+    # own it streams the old cache blocks while that kernel is still running and waits only for the newest block;
+    # with them folded in (the default) it patches the newest token into its shared-memory tile itself.
+    (2, False, 128, 16, 100, False), (9, False, 128, 16, 100, False),
+    (2, False, 128, 16, 100, True), (9, False, 128, 16, 100, True), (20, False, 64, 16, 100, True)])
+def test_decode_step_matches_oracle_chain(batch, fuse_residual_norm, head_dim, bs, max_ctx, fuse_rope):
     """Two consecutive steps of a small random-init decoder (eager, then the same step replayed from a
     CUDA graph) against the oracle chain; batch 20 takes the tensor-core linear path."""
     import torch
@@ -280,13 +353,13 @@ def test_decode_step_matches_oracle_chain(batch, fuse_residual_norm, head_dim, b
     cfg = decode.LlamaConfig(hidden=256, n_layers=2, n_q_heads=4, n_kv_heads=2, head_dim=head_dim, intermediate=512,
                              vocab=1024, rope_theta=10000.0)
     ck = decode.synthetic_checkpoint(cfg, seed=batch)
-    dec = decode.LlamaDecoder(cfg, ck, "cuda:0", max_pos=128, fuse_residual_norm=fuse_residual_norm)
+    dec = decode.LlamaDecoder(cfg, ck, "cuda:0", max_pos=128, fuse_residual_norm=fuse_residual_norm, fuse_rope=fuse_rope)
     max_blocks = 8
     nblk = batch * max_blocks
     cache = decode.PagedKvCache(cfg, nblk, bs, "cuda:0")
     rng = np.random.default_rng(batch)
     ctx_len = rng.integers(3, max_ctx, size=batch)
-    if head_dim == 128:
+    if bs == 16:
         ctx_len[0] = 2 * bs - 1                      # the second step's token opens a new block
     table = rng.permutation(nblk).reshape(batch, max_blocks).astype(np.uint32)
     # pre-fill the caches with random history
