@@ -120,6 +120,32 @@ int32_t scr_linear_affine_b4_residual_rmsnorm(scr_ctx* ctx, const void* packed, 
                                               uint16_t* normed, void* scratch, size_t scratch_bytes,
                                               void* stream);
 
+/* ---- a tape of matvecs in one launch ----------------------------------------
+ * The reference runs a decode step as a tape of operators that is fixed at build time
+ * (crates/targets/metal/src/tape/step.rs: one `Step` per dispatch, encoded back to back into one
+ * command buffer).  `scr_affine_b4_tape_create` takes the int4 linears of such a tape — for each its
+ * repacked matrix, x [max_rows, K] and y [max_rows, N] (bf16, device, fixed for the life of the
+ * tape) and up to three earlier jobs it must wait for — and `scr_linear_affine_b4_tape` runs all of
+ * them, M <= max_rows <= 16 rows each, inside ONE persistent kernel: y_j = x_j @ W_j^T in tape
+ * order, a job starting once the jobs in dep[] have stored their outputs.  The caller names every
+ * dependency: the producer of a job's x, and — when a buffer is reused — the earlier readers and
+ * writers of its y.  Results are deterministic (fixed summation order) and within the matvec's
+ * tolerance of `scr_linear_affine_b4`; create allocates and synchronises (load time), the run call
+ * allocates nothing and can be captured in a CUDA graph.  A matrix repacked after create needs a
+ * new tape.  Runs of one tape must not overlap on the GPU. */
+typedef struct scr_tape scr_tape;
+typedef struct scr_tape_linear {
+    const void* packed;     /* scr_affine_b4_repack output */
+    const uint16_t* x;      /* [max_rows, K] bf16 */
+    uint16_t* y;            /* [max_rows, N] bf16 */
+    int32_t N, K, group;
+    int32_t dep[3];         /* indices of earlier jobs, -1 = none */
+} scr_tape_linear;
+int32_t scr_affine_b4_tape_create(scr_ctx* ctx, const scr_tape_linear* jobs, int32_t n_jobs,
+                                  int32_t max_rows, scr_tape** out);
+int32_t scr_linear_affine_b4_tape(scr_ctx* ctx, scr_tape* tape, int32_t M, void* stream);
+int32_t scr_tape_destroy(scr_tape* tape);
+
 /* ---- fp8-dynamic-per-channel: load-time repack ----------------------------
  * Replaces the `load_layered_fp8...` loaders the reference's codegen names but no live
  * target implements (Metal refuses fp8: crates/targets/metal/compiler/src/steps_from_tape.rs:2009).

@@ -45,6 +45,9 @@ SIGNATURES = {
     "scr_linear_affine_b4_silu_mul": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp]),
     "scr_linear_affine_b4_residual_rmsnorm": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, ctypes.c_float, _vp,
                                                      _vp, _sz, _vp]),
+    "scr_affine_b4_tape_create": (_i32, [_vp, _vp, _i32, _i32, ctypes.POINTER(_vp)]),
+    "scr_linear_affine_b4_tape": (_i32, [_vp, _vp, _i32, _vp]),
+    "scr_tape_destroy": (_i32, [_vp]),
     "scr_fp8_repack_size": (_i32, [_i32, _i32, _psz]),
     "scr_fp8_repack": (_i32, [_vp, _vp, _vp, _i32, _i32, _vp, _vp]),
     "scr_fp8_act_size": (_i32, [_i32, _i32, _psz]),
@@ -77,6 +80,13 @@ SIGNATURES = {
                                                  _vp]),
     "scr_argmax_bf16": (_i32, [_vp, _vp, _i64, _i32, _i32, _vp, _vp]),
 }
+
+
+
+class TapeLinear(ctypes.Structure):
+    """`scr_tape_linear` of include/scratchy_cuda.h."""
+    _fields_ = [("packed", _vp), ("x", _vp), ("y", _vp), ("N", _i32), ("K", _i32), ("group", _i32), ("dep", _i32 * 3)]
+
 
 _lib = None
 _lock = threading.Lock()

@@ -1,6 +1,10 @@
 // MLX affine int4 (group 64): load-time repack, dequant dump hook and the decode matvec.
 #include "affine_b4.cuh"
 
+#include <algorithm>
+#include <new>
+#include <vector>
+
 // ------------------------------------------------------------------------------------
 // Repack: checkpoint layout -> streaming blocks (layout in affine_b4.cuh).
 // One thread per 16-byte piece plus one thread per 8-byte scale entry.
@@ -740,4 +744,336 @@ extern "C" int32_t scr_linear_affine_b4_silu_mul(scr_ctx* ctx, const void* packe
     const int32_t st = scr_linear_affine_b4(ctx, packed, x, M, N2, K, group, out, nullptr, 0, stream_);
     ctx->out_f32 = 0;
     return st;
+}
+
+// ------------------------------------------------------------------------------------
+// Matvec tape: a static list of M <= 16 linears with declared dependencies, one launch.
+//
+// The reference runs a decode step as a tape of operators fixed at build time
+// (crates/targets/metal/src/tape/step.rs); here the linears of such a tape run inside ONE
+// persistent cooperative kernel, so that no launch boundary (about 3 us of fixed cost each at these
+// sizes) sits between dependent matvecs.  Every CTA walks the jobs in tape order.  Row-blocks are
+// dealt round-robin, continuing across jobs, so that small jobs land on different CTAs.  The
+// producer lane never waits for anything but ring space: weights are load-time constants, and it
+// streams the next jobs' weights while the consumers wait for a dependency.  Consumers wait
+// (bounded) until the jobs named in dep[] have stored all their row-blocks — a counter per job,
+// bumped with release semantics once per CTA and job — and read activations with ordinary coherent
+// loads, never the read-only path (another CTA of this launch may have written them).  The last CTA to leave zeroes the counters,
+// so the tape can be replayed from a CUDA graph.  Summation order is fixed: results are
+// deterministic and do not depend on which CTA took which row-block.
+// ------------------------------------------------------------------------------------
+#define TAPE_MAX_DEPS 3
+#define TAPE_WAIT_LIMIT (1u << 22)
+#define TAPE_ERR_DEP_WAIT 0x0D000001
+
+struct TapeJob {
+    const uint8_t* packed;
+    const uint16_t* x;
+    uint16_t* y;
+    int N, K, KC, rb_real;
+    int unit_base;                 // row-blocks of all earlier jobs (where the round-robin deal continues)
+    int check;                     // the matrix has groups that need the exact (two-step rounding) path
+    int dep[TAPE_MAX_DEPS];        // earlier jobs this one waits for (-1 = none)
+    int dep_need[TAPE_MAX_DEPS];   // their row-block counts
+    int pad[2];
+};
+static_assert(sizeof(TapeJob) % 16 == 0, "the job table is copied into shared memory 16 bytes at a time");
+
+struct scr_tape {
+    scr_ctx* ctx = nullptr;
+    int n_jobs = 0;
+    int max_rows = 0;              // largest M the x / y buffers were declared for
+    TapeJob* jobs = nullptr;       // device
+    unsigned int* done = nullptr;  // device: [n_jobs] row-blocks stored per job, [n_jobs] = CTAs that left
+    int grid[2] = {0, 0};          // co-resident CTAs: up to 8 rows, up to 16 rows
+};
+
+// Activations another CTA of this launch may have written: an ordinary (coherent, L1-allocating) load — never
+// the read-only path — issued after the job's acquire fence and the CTA barrier that follows it.
+__device__ __forceinline__ uint4 tape_ld_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void tape_red_release(unsigned int* p, unsigned int v) {
+    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// One row-block of one job: the k loop over the ring, the cross-warp sum and the bf16 store.
+template <int MT, bool CHECK>
+__device__ __forceinline__ void tape_row_block(uint16_t* __restrict__ y, int N, int K, int KC, int rb, int M, int nstage, uint32_t& n_it, int buf,
+                                               const uint16_t* const (&xrow)[MT], int* __restrict__ status, uint32_t ring_base,
+                                               uint32_t full_base, uint32_t empty_base, float (*red)[GEMV_CWARPS][32][MT * 4]) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = lane & 3;
+    float acc[2][MT][4];
+#pragma unroll
+    for (int a = 0; a < 2; ++a)
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[a][mt][i] = 0.f;
+#pragma unroll 1
+    for (int j = 0; j < nstage; ++j, ++n_it) {
+        const int kc = j * GEMV_CWARPS + warp;
+        const bool active = kc < KC;
+        const uint32_t slot = n_it & (GEMV_STAGES - 1);
+        uint4 xv[MT][4];
+        int k0 = kc * 128 + t * 32;
+        if (k0 >= K) k0 = 0;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) xv[mt][i] = tape_ld_v4(xrow[mt] + k0 + 8 * i);
+        gemv_wait(full_base + 8u * slot, (n_it / GEMV_STAGES) & 1u, status);
+        if (active) gemv_block_compute<MT, CHECK>(ring_base + slot * GEMV_STAGE_BYTES + warp * AFF_BLOCK_BYTES, acc, xv, lane);
+        __syncwarp();
+        if (lane == 0) gemv_mbar_arrive(empty_base + 8u * slot);
+    }
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            red[buf][warp][lane][mt * 4 + i] = (acc[0][mt][i] + acc[1][mt][i]) * (CHECK ? 1.0f : AFF_SCALED_FACTOR);
+    gemv_consumer_sync();
+    constexpr int SLOTS = 32 * MT * 4;
+    const int e = threadIdx.x;
+    if (e < SLOTS) {
+        const int ln = e / (MT * 4), idx = e % (MT * 4);
+        const int row = (ln >> 2) + (((idx & 3) >> 1) ? 8 : 0);
+        const int tok = (idx >> 2) * 8 + (ln & 3) * 2 + (idx & 1);
+        const int n = rb * 16 + row;
+        float total = 0.f;
+#pragma unroll
+        for (int wdx = 0; wdx < GEMV_CWARPS; ++wdx) total += red[buf][wdx][ln][idx];
+        if (tok < M && n < N) {
+            const __nv_bfloat16 v = __float2bfloat16_rn(total);
+            y[(size_t)tok * N + n] = *reinterpret_cast<const uint16_t*>(&v);
+        }
+    }
+}
+
+// The job table is copied into shared memory once (a record read from global memory at every job boundary
+// stalls the single producer lane for a memory round trip while the ring behind it drains).
+template <int MT>
+__global__ void __launch_bounds__(GEMV_THREADS, (MT == 1 ? 3 : 2))
+affine_b4_tape_kernel(const TapeJob* __restrict__ jobs_g, int n_jobs, int M, unsigned int* done, int* __restrict__ status) {
+    extern __shared__ __align__(128) uint8_t gemv_ring[];          // [GEMV_STAGES][8 blocks], then the job table
+    __shared__ __align__(8) uint64_t full_bar[GEMV_STAGES];
+    __shared__ __align__(8) uint64_t empty_bar[GEMV_STAGES];
+    __shared__ float red[2][GEMV_CWARPS][32][MT * 4];
+    __shared__ int s_last;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    TapeJob* jobs = reinterpret_cast<TapeJob*>(gemv_ring + GEMV_STAGES * GEMV_STAGE_BYTES);
+    {
+        const uint4* src = reinterpret_cast<const uint4*>(jobs_g);
+        uint4* dst = reinterpret_cast<uint4*>(jobs);
+        const int n16 = n_jobs * int(sizeof(TapeJob) / 16);
+        for (int i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = src[i];
+    }
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int d = 0; d < GEMV_STAGES; ++d) {
+            gemv_mbar_init(gemv_smem_u32(&full_bar[d]), 1);
+            gemv_mbar_init(gemv_smem_u32(&empty_bar[d]), GEMV_CWARPS);
+        }
+        s_last = 0;
+    }
+    gemv_fence_mbar_init();
+    __syncthreads();
+    const uint32_t ring_base = gemv_smem_u32(gemv_ring);
+    const uint32_t full_base = gemv_smem_u32(&full_bar[0]);
+    const uint32_t empty_base = gemv_smem_u32(&empty_bar[0]);
+    const int G = int(gridDim.x), c = int(blockIdx.x);
+
+    if (warp == GEMV_CWARPS) {
+        if (lane == 0) {
+            // ---- weights: never waits for anything but ring space
+            uint32_t n_it = 0;
+            for (int j = 0; j < n_jobs; ++j) {
+                const TapeJob& job = jobs[j];
+                const int KC = job.KC, rb_real = job.rb_real;
+                const int nstage = (KC + GEMV_CWARPS - 1) / GEMV_CWARPS;
+                const int first = (c - job.unit_base % G + G) % G;
+                for (int rb = first; rb < rb_real; rb += G) {
+                    const uint8_t* src = job.packed + (size_t)rb * KC * AFF_BLOCK_BYTES;
+                    for (int s = 0; s < nstage; ++s, ++n_it) {
+                        const uint32_t slot = n_it & (GEMV_STAGES - 1);
+                        gemv_wait(empty_base + 8u * slot, ((n_it / GEMV_STAGES) & 1u) ^ 1u, status);
+                        const uint32_t bytes = (uint32_t)min(GEMV_CWARPS, KC - s * GEMV_CWARPS) * AFF_BLOCK_BYTES;
+                        gemv_arrive_expect_tx(full_base + 8u * slot, bytes);
+                        gemv_bulk_g2s(ring_base + slot * GEMV_STAGE_BYTES, src + (size_t)s * GEMV_STAGE_BYTES, bytes,
+                                      full_base + 8u * slot);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        const int g = lane >> 2;
+        uint32_t n_it = 0;
+        int it = 0;
+        for (int j = 0; j < n_jobs; ++j) {
+            const TapeJob& job = jobs[j];
+            const int rb_real = job.rb_real;
+            const int first = (c - job.unit_base % G + G) % G;
+            if (first >= rb_real) continue;                    // no row-block of this job here: nothing to wait for or to report
+            const int N = job.N, K = job.K, KC = job.KC;
+            const bool has_dep = job.dep[0] >= 0 || job.dep[1] >= 0 || job.dep[2] >= 0;
+            // one poller per CTA (thousands of pollers on one word starve the writers), with a short back-off
+            if (threadIdx.x == 0 && has_dep) {
+#pragma unroll 1
+                for (int d = 0; d < TAPE_MAX_DEPS; ++d) {
+                    const int dep = job.dep[d];
+                    if (dep < 0) continue;
+                    const unsigned int need = (unsigned int)job.dep_need[d];
+                    const volatile unsigned int* ctr = done + dep;
+                    bool seen = false;
+                    for (unsigned int p = 0; p < TAPE_WAIT_LIMIT; ++p) {
+                        if (*ctr >= need) {
+                            seen = true;
+                            break;
+                        }
+                        if ((p & 1023u) == 1023u && *reinterpret_cast<volatile int*>(status) != 0) break;
+                        __nanosleep(20);
+                    }
+                    if (!seen) atomicCAS(status, 0, TAPE_ERR_DEP_WAIT);
+                }
+                __threadfence();                               // acquire: the producers' stores are visible from here on
+            }
+            if (has_dep) gemv_consumer_sync();
+            const bool check = job.check != 0;
+            uint16_t* y = job.y;
+            const uint16_t* xrow[MT];
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) xrow[mt] = job.x + (size_t)min(mt * 8 + g, M - 1) * K;
+            const int nstage = (KC + GEMV_CWARPS - 1) / GEMV_CWARPS;
+            unsigned int units = 0;
+            for (int rb = first; rb < rb_real; rb += G, ++it, ++units) {
+                if (check)
+                    tape_row_block<MT, true>(y, N, K, KC, rb, M, nstage, n_it, it & 1, xrow, status, ring_base, full_base, empty_base, red);
+                else
+                    tape_row_block<MT, false>(y, N, K, KC, rb, M, nstage, n_it, it & 1, xrow, status, ring_base, full_base, empty_base, red);
+            }
+            gemv_consumer_sync();                              // every store of this CTA's row-blocks has been issued ...
+            if (threadIdx.x == 0) tape_red_release(done + j, units);      // ... and is released, cumulatively, by this one
+        }
+    }
+    // the last CTA to leave clears the counters for the next replay
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(done + n_jobs, 1u) == (unsigned int)(G - 1)) s_last = 1;
+    }
+    __syncthreads();
+    if (s_last) {
+        for (int i = threadIdx.x; i <= n_jobs; i += blockDim.x) done[i] = 0u;
+    }
+}
+
+#define TAPE_MAX_JOBS 320          // the job table sits in shared memory beside the ring
+
+static size_t tape_smem_bytes(int n_jobs) { return (size_t)GEMV_STAGES * GEMV_STAGE_BYTES + (size_t)n_jobs * sizeof(TapeJob); }
+
+template <int MT>
+static int tape_resident_ctas(int sms, int n_jobs) {
+    int per_sm = 0;
+    const size_t kRingBytes = tape_smem_bytes(n_jobs);
+    if (cudaFuncSetAttribute(affine_b4_tape_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tape_smem_bytes(TAPE_MAX_JOBS)) !=
+        cudaSuccess)
+        return 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, affine_b4_tape_kernel<MT>, GEMV_THREADS, kRingBytes) != cudaSuccess)
+        return 0;
+    return std::min(per_sm, MT == 1 ? 3 : 2) * sms;
+}
+
+extern "C" int32_t scr_affine_b4_tape_create(scr_ctx* ctx, const scr_tape_linear* jobs, int32_t n_jobs, int32_t max_rows,
+                                             scr_tape** out) {
+    SCR_REQUIRE_CTX(ctx);
+    if (!jobs || !out) return scr_fail(ctx, SCR_E_ARG, "tape: null pointer");
+    *out = nullptr;
+    if (n_jobs <= 0) return scr_fail(ctx, SCR_E_SHAPE, "tape: %d jobs", n_jobs);
+    if (n_jobs > TAPE_MAX_JOBS) return scr_fail(ctx, SCR_E_UNSUPPORTED, "tape: %d jobs (up to %d per tape; chain several)", n_jobs, TAPE_MAX_JOBS);
+    if (max_rows <= 0 || max_rows > 16) return scr_fail(ctx, SCR_E_UNSUPPORTED, "tape: max_rows=%d (the matvec path, 1..16 rows)", max_rows);
+    std::vector<TapeJob> host((size_t)n_jobs);
+    long long unit_base = 0;
+    for (int j = 0; j < n_jobs; ++j) {
+        const scr_tape_linear& s = jobs[j];
+        if (!s.packed || !s.x || !s.y) return scr_fail(ctx, SCR_E_ARG, "tape job %d: null pointer", j);
+        int32_t st = affine_check_shape(ctx, s.N, s.K, s.group);
+        if (st) return st;
+        if (!scr_aligned16(s.packed) || !scr_aligned16(s.x)) return scr_fail(ctx, SCR_E_ALIGN, "tape job %d: packed/x must be 16-byte aligned", j);
+        const AffineGeom g = affine_geom(s.N, s.K);
+        TapeJob& t = host[(size_t)j];
+        t.packed = static_cast<const uint8_t*>(s.packed);
+        t.x = s.x;
+        t.y = s.y;
+        t.N = s.N;
+        t.K = s.K;
+        t.KC = g.KC;
+        t.rb_real = scr_ceil_div(s.N, 16);
+        t.unit_base = int(unit_base % (1 << 30));
+        unit_base += t.rb_real;
+        unsigned int flag = 0;
+        cudaError_t e = cudaMemcpy(&flag, t.packed + affine_blocks_bytes(g), sizeof(flag), cudaMemcpyDeviceToHost);
+        if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "tape job %d: reading the matrix trailer: %s", j, cudaGetErrorString(e));
+        t.check = flag != 0;
+        for (int d = 0; d < TAPE_MAX_DEPS; ++d) {
+            const int dep = s.dep[d];
+            if (dep >= j) return scr_fail(ctx, SCR_E_ARG, "tape job %d: dependency %d is not an earlier job", j, dep);
+            t.dep[d] = dep < 0 ? -1 : dep;
+            t.dep_need[d] = dep < 0 ? 0 : host[(size_t)dep].rb_real;
+        }
+    }
+    scr_tape* tp = new (std::nothrow) scr_tape();
+    if (!tp) return scr_fail(ctx, SCR_E_CUDA, "tape: out of host memory");
+    tp->ctx = ctx;
+    tp->n_jobs = n_jobs;
+    tp->max_rows = max_rows;
+    tp->grid[0] = tape_resident_ctas<1>(ctx->sm_count, n_jobs);
+    tp->grid[1] = tape_resident_ctas<2>(ctx->sm_count, n_jobs);
+    cudaError_t e = tp->grid[0] > 0 && tp->grid[1] > 0 ? cudaSuccess : cudaErrorLaunchOutOfResources;
+    if (e == cudaSuccess) e = cudaMalloc(&tp->jobs, sizeof(TapeJob) * (size_t)n_jobs);
+    if (e == cudaSuccess) e = cudaMalloc(&tp->done, sizeof(unsigned int) * ((size_t)n_jobs + 1));
+    if (e == cudaSuccess) e = cudaMemcpy(tp->jobs, host.data(), sizeof(TapeJob) * (size_t)n_jobs, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemset(tp->done, 0, sizeof(unsigned int) * ((size_t)n_jobs + 1));
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        if (tp->jobs) cudaFree(tp->jobs);
+        if (tp->done) cudaFree(tp->done);
+        delete tp;
+        return scr_fail(ctx, SCR_E_CUDA, "tape: %s", cudaGetErrorString(e));
+    }
+    *out = tp;
+    return SCR_OK;
+}
+
+extern "C" int32_t scr_tape_destroy(scr_tape* tape) {
+    if (!tape) return SCR_OK;
+    if (tape->jobs) cudaFree(tape->jobs);
+    if (tape->done) cudaFree(tape->done);
+    delete tape;
+    return SCR_OK;
+}
+
+extern "C" int32_t scr_linear_affine_b4_tape(scr_ctx* ctx, scr_tape* tape, int32_t M, void* stream_) {
+    SCR_REQUIRE_CTX(ctx);
+    if (!tape || tape->ctx != ctx) return scr_fail(ctx, SCR_E_ARG, "tape: null handle or a handle of another context");
+    if (M <= 0 || M > tape->max_rows) return scr_fail(ctx, SCR_E_SHAPE, "tape: M=%d outside 1..%d", M, tape->max_rows);
+    const size_t kRingBytes = tape_smem_bytes(tape->n_jobs);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(tape->grid[M > 8 ? 1 : 0], 1, 1);
+    cfg.blockDim = dim3(GEMV_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = kRingBytes;
+    cfg.stream = (cudaStream_t)stream_;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;       // every CTA resident: a CTA may wait for any other
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const TapeJob* jobs = tape->jobs;
+    cudaError_t e = M <= 8 ? cudaLaunchKernelEx(&cfg, affine_b4_tape_kernel<1>, jobs, tape->n_jobs, (int)M, tape->done, ctx->dev_status)
+                           : cudaLaunchKernelEx(&cfg, affine_b4_tape_kernel<2>, jobs, tape->n_jobs, (int)M, tape->done, ctx->dev_status);
+    if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine_b4_tape launch: %s", cudaGetErrorString(e));
+    return scr_check_launch(ctx, "affine_b4_tape");
 }

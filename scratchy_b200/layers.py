@@ -311,6 +311,58 @@ class AffineQuantLinear:
         return w
 
 
+class AffineTape:
+    """A static tape of int4 matvecs that runs as ONE launch (`scr_linear_affine_b4_tape`), the way the
+    reference's decode step is a tape of dispatches fixed at build time
+    (crates/targets/metal/src/tape/step.rs).  `jobs`: (linear, x [max_rows, K], y [max_rows, N], deps) in
+    tape order; `deps` lists up to three earlier jobs that must have stored their output before this
+    one starts — the producer of x and, when a buffer is reused, its earlier readers and writers.
+    The tensors are bound for the life of the tape."""
+
+    def __init__(self, jobs, max_rows: int = 1):
+        if not jobs:
+            raise ValueError("an empty tape")
+        dev = jobs[0][1].device
+        self._keep = []
+        arr = (_lib.TapeLinear * len(jobs))()
+        for j, (lin, x, y, deps) in enumerate(jobs):
+            if x.dtype != torch.bfloat16 or y.dtype != torch.bfloat16 or not x.is_contiguous() or not y.is_contiguous():
+                raise ValueError(f"tape job {j}: x and y must be contiguous bf16 tensors")
+            if tuple(x.shape) != (max_rows, lin.in_features) or tuple(y.shape) != (max_rows, lin.out_features):
+                raise ValueError(f"tape job {j}: x {tuple(x.shape)} / y {tuple(y.shape)} do not match "
+                                 f"[{max_rows}, {lin.in_features}] / [{max_rows}, {lin.out_features}]")
+            deps = list(deps)
+            if len(deps) > 3:
+                raise ValueError(f"tape job {j}: at most three dependencies")
+            arr[j].packed, arr[j].x, arr[j].y = lin.packed.data_ptr(), x.data_ptr(), y.data_ptr()
+            arr[j].N, arr[j].K, arr[j].group = lin.out_features, lin.in_features, lin.group_size
+            for d in range(3):
+                arr[j].dep[d] = int(deps[d]) if d < len(deps) else -1
+            self._keep.append((lin, x, y))
+        self.device, self.max_rows, self.n_jobs = dev, int(max_rows), len(jobs)
+        self._ctx = _lib.context(_dev_index(dev))
+        self._h = ctypes.c_void_p()
+        torch.cuda.synchronize(dev)
+        self._ctx.check(_lib.lib().scr_affine_b4_tape_create(self._ctx.handle, ctypes.cast(arr, ctypes.c_void_p), len(jobs),
+                                                             int(max_rows), ctypes.byref(self._h)))
+
+    def run(self, M: Optional[int] = None) -> None:
+        """y_j = x_j @ W_j^T for every job, rows 0..M-1 (M defaults to max_rows), on the current stream."""
+        self._ctx.check(_lib.lib().scr_linear_affine_b4_tape(self._ctx.handle, self._h, int(M or self.max_rows),
+                                                             _stream(self.device)))
+
+    def close(self) -> None:
+        if self._h:
+            _lib.lib().scr_tape_destroy(self._h)
+            self._h = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 def _take_affine_scales(weights: GpuWeights, name: str) -> torch.Tensor:
     """`take_affine_scales` (layers_quant.rs:270-285): refuse scales that are not the pinned dtype."""
     compiled = weights.rmsnorm_scale_dtype()
