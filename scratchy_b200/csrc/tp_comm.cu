@@ -70,6 +70,11 @@ __global__ void __launch_bounds__(TPC_THREADS) tp_allreduce_kernel(TpcPeers peer
                                                                    unsigned int* state, int* status) {
     __shared__ unsigned int s_epoch;
     const int c = blockIdx.x, tid = threadIdx.x;
+    // Programmatic dependent launch: the next kernel of the stream (a matvec that prefetches its load-time
+    // weights before its own dependency wait) may start while this exchange is in flight; this kernel itself
+    // touches nothing before the kernels ahead of it have completed.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (tid == 0) s_epoch = *reinterpret_cast<volatile unsigned int*>(&state[0]) + 1u;
     __syncthreads();
     const unsigned int e = s_epoch;
@@ -83,9 +88,9 @@ __global__ void __launch_bounds__(TPC_THREADS) tp_allreduce_kernel(TpcPeers peer
             for (int p = 0; p < world; ++p) *reinterpret_cast<float4*>(peers.recv[p] + (half + rank) * max_elems + i) = v;
         }
     }
-    __threadfence_system();
     __syncthreads();
-    // 2. publish, 3. wait for every rank's copy of my slices (bounded)
+    // 2. publish (the release is cumulative over the stores the barrier ordered before it: one system-scope fence
+    //    per publishing thread, not one per storing thread), 3. wait for every rank's copy of my slices (bounded)
     if (tid < world) {
         st_release_sys(peers.flags[tid] + (half + rank) * TPC_MAX_CTAS + c, e);
         const unsigned int* mine = peers.flags[rank] + (half + tid) * TPC_MAX_CTAS + c;
@@ -209,9 +214,18 @@ extern "C" int32_t scr_tp_allreduce_partial(scr_tp_comm* comm, const float* part
         peers.flags[p] = reinterpret_cast<unsigned int*>(base + comm->flags_off);
     }
     const int grid = (int)std::min<long long>((count + TPC_SLICE - 1) / TPC_SLICE, TPC_MAX_CTAS);
-    tp_allreduce_kernel<<<grid, TPC_THREADS, 0, (cudaStream_t)stream>>>(peers, comm->world, comm->rank, comm->max_elems, partial,
-                                                                        (long long)count, y_bf16, y_f32, comm->state,
-                                                                        ctx->dev_status);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(TPC_THREADS);
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, tp_allreduce_kernel, peers, comm->world, comm->rank, (long long)comm->max_elems, partial,
+                                       (long long)count, y_bf16, y_f32, comm->state, ctx->dev_status);
+    if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "tp all-reduce launch: %s", cudaGetErrorString(e));
     return scr_check_launch(ctx, "tp_allreduce");
 }
 
