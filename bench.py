@@ -439,7 +439,7 @@ def run_gpu(args):
     if world > 1 or args.sweep:
         del layers, graph, graph_e2e
         torch.cuda.empty_cache()
-        tp_res = run_tp(device, world, rank)
+        tp_res = run_tp(device, world, rank, fuse_exchange=args.tp_fused_exchange)
         if rank == 0:
             extra["tp"] = tp_res
 
@@ -625,7 +625,7 @@ def run_decode(device, steps=20, batches=(1, 8, 32), context=2048, block_size=16
     return out
 
 
-def run_tp(device, world, rank):
+def run_tp(device, world, rank, fuse_exchange=False):
     """BASELINE config 4: Llama-3-70B-shaped fp8 per-channel linears, tensor parallel over `world`
     GPUs: column-parallel qkv and gate/up, row-parallel o and down, each followed by the all-reduce
     of the f32 partials [M, 8192] and one rounding to bf16 — the one-shot peer-memory kernel
@@ -690,11 +690,20 @@ def run_tp(device, world, rank):
                 dst.copy_(tpmod.partial_to_bf16(part))
             return dst
 
+        # a few tokens: the row-parallel matvec pushes its partials to the peers and sums in its own epilogue
+        fused = (use_one_shot and fuse_exchange and one.fp8_linear_all_reduce_supported(layers[0]["o"], M)
+                 and one.fp8_linear_all_reduce_supported(layers[0]["down"], M))
+
         def layer_step(L):
             L["qkv"].forward(x, out=bufs["qkv"], workspace=ws)
-            L["o"].forward_partial(bufs["attn"], out=bufs["po"], workspace=ws)
-            h = reduce_round(bufs["po"], bufs["h"])
+            if fused:
+                h = one.fp8_linear_all_reduce(L["o"], bufs["attn"], out=bufs["h"])
+            else:
+                L["o"].forward_partial(bufs["attn"], out=bufs["po"], workspace=ws)
+                h = reduce_round(bufs["po"], bufs["h"])
             L["gate_up"].forward(h, out=bufs["gu"], workspace=ws)
+            if fused:
+                return one.fp8_linear_all_reduce(L["down"], bufs["act"], out=bufs["y"])
             L["down"].forward_partial(bufs["act"], out=bufs["pd"], workspace=ws)
             return reduce_round(bufs["pd"], bufs["y"])
 
@@ -734,6 +743,8 @@ def run_tp(device, world, rank):
                     "tok_per_s_per_layer": M * 1e6 / us_layer, "TFLOPs_all_gpus": flops / us_layer / 1e6,
                     "weight_GBps_per_gpu": (H * (QKV + H + 3 * FF) / world) / us_layer / 1e3, "launch": mode,
                     "allreduce": ("none (one rank)" if world == 1 else
+                                  "f32 [M,8192] x2 per layer, pushed and summed in the row-parallel matvec's epilogue over peer "
+                                  "memory (rank-ordered sum, one launch with the matvec)" if fused else
                                   "f32 [M,8192] x2 per layer, one-shot peer-memory kernel (rank-ordered sum)" if use_one_shot
                                   else "f32 [M,8192] x2 per layer (NCCL)")})
         del gr
@@ -839,6 +850,9 @@ def main():
     ap.add_argument("--decode-only", action="store_true", help="run only the whole-decode-step section and print it")
     ap.add_argument("--decode-batches", default="1,8,32")
     ap.add_argument("--no-fuse-rope", action="store_true", help="decode step with RoPE + append as a kernel of their own")
+    ap.add_argument("--tp-fused-exchange", action="store_true",
+                    help="tensor-parallel section: row-parallel matvec and all-reduce as ONE launch "
+                         "(scr_linear_fp8_dynamic_allreduce; measured a few percent slower than the two launches)")
     ap.add_argument("--case", default=None, help="kind,shape,M e.g. int4,gate,2048: time one linear alone")
     args = ap.parse_args()
     if args.case:

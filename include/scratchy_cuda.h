@@ -312,6 +312,16 @@ int32_t scr_tp_comm_connect(scr_tp_comm* comm, const uint8_t* handles /* world x
 int32_t scr_tp_allreduce_partial(scr_tp_comm* comm, const float* partial, int64_t count,
                                  uint16_t* y_bf16, float* y_f32, void* stream);
 int32_t scr_tp_comm_destroy(scr_tp_comm* comm);
+/* A row-parallel fp8-dynamic linear and its all-reduce as ONE launch, for decode sizes: the matvec's
+ * epilogue stores its f32 partial sums straight into every rank's receive buffer over NVLink, and
+ * each CTA then sums the ranks' copies of its own rows in rank order and rounds once
+ *   y[M,N] (bf16) = round( sum over ranks r, in order, of  x_r[M,K_r] @ W_r^T ).
+ * Same bits as `scr_linear_fp8_dynamic_partial` followed by `scr_tp_allreduce_partial`.  Every rank
+ * calls it with the same M and N, in the same order as its other calls on `comm`; M * N <= the
+ * communicator's max_elems.  Covers what the self-quantising matvec covers (M <= 4 and M * K16 <=
+ * 14 KiB); SCR_E_UNSUPPORTED otherwise — run the two calls then. */
+int32_t scr_linear_fp8_dynamic_allreduce(scr_tp_comm* comm, const void* packed, const uint16_t* x_bf16,
+                                         int32_t M, int32_t N, int32_t K, uint16_t* y_bf16, void* stream);
 
 /* No counterpart in the reference.  The same linear as `scr_linear_fp8_dynamic` for callers
  * that cannot allocate device memory on the step path (an arena-owning runtime, code inside a

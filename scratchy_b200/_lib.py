@@ -65,6 +65,7 @@ SIGNATURES = {
     "scr_tp_comm_connect": (_i32, [_vp, _vp]),
     "scr_tp_allreduce_partial": (_i32, [_vp, _vp, _i64, _vp, _vp, _vp]),
     "scr_tp_comm_destroy": (_i32, [_vp]),
+    "scr_linear_fp8_dynamic_allreduce": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp]),
     "scr_linear_fp8_dynamic_static": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp]),
     "scr_embed_bf16": (_i32, [_vp, _vp, _i32, _vp, _i32, _i32, _vp, _vp]),
     "scr_rmsnorm_bf16": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, ctypes.c_float, _vp]),

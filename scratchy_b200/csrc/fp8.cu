@@ -1,6 +1,7 @@
 // fp8-dynamic-per-channel: weight repack, per-token activation quantisation, test hooks and
 // the decode matvec (M <= 16).  Layouts are described in fp8.cuh.
 #include "fp8.cuh"
+#include "tp_comm.cuh"
 
 // ------------------------------------------------------------------------------------
 // Weight repack: [N, K] e4m3 row-major -> swizzled 128x128 tiles + padded scales.
@@ -319,11 +320,17 @@ __device__ __forceinline__ void f8_block_compute(uint32_t blk, float acc[2][MT][
 // FUSE_Q: the kernel takes the bf16 activations and quantises them itself (every CTA repeats the
 // per-token absmax and the encode into its own shared memory: a few KB from L2, one launch saved);
 // the arithmetic is the quantise kernel's, statement for statement, so x_q and a_scale are the same bits.
-template <int MT, int SPLIT_CLUSTER, int FUSE_Q>
+//
+// EXCH: a row-parallel linear under tensor parallelism.  The f32 partial sums do not go to y: the epilogue stores
+// them straight into this rank's slot of EVERY rank's receive buffer (plain peer stores over NVLink) as 8-byte
+// {value, call number} packets; at its end each CTA reads — bounded polls — the W ranks' packets of its own rows,
+// sums them in rank order and rounds once: matvec and all-reduce in one launch, no flag array and no system-scope
+// fence, the same bits as the partial matvec followed by the stand-alone exchange.
+template <int MT, int SPLIT_CLUSTER, int FUSE_Q, int EXCH>
 __global__ void __launch_bounds__(F8V_THREADS, (MT == 1 ? 3 : 2))
 fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_scale, const uint8_t* __restrict__ xq,
                 const float* __restrict__ a_scale, const uint16_t* __restrict__ x_bf16, int K, uint16_t* __restrict__ y, int M,
-                int N, int K16, int KT, int rb_real, int split, int out_f32, int* __restrict__ status) {
+                int N, int K16, int KT, int rb_real, int split, int out_f32, int* __restrict__ status, TpcExchange ex) {
     extern __shared__ __align__(128) uint8_t f8v_ring[];           // [F8V_STAGES][8 blocks of 2 KB] (+ x_q [M][K16] when FUSE_Q)
     __shared__ __align__(8) uint64_t full_bar[F8V_STAGES];
     __shared__ __align__(8) uint64_t empty_bar[F8V_STAGES];
@@ -331,6 +338,7 @@ fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_s
     __shared__ float cl_part[SPLIT_CLUSTER ? F8V_MAX_SPLIT : 1][16][MT * 8];
     __shared__ float q_wmax[F8V_CWARPS];
     __shared__ float q_scale[8];
+    __shared__ unsigned int s_epoch;                               // EXCH: the call number of this exchange
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -385,6 +393,8 @@ fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_s
         __syncwarp();
     } else {
         asm volatile("griddepcontrol.wait;" ::: "memory");        // the activations are settled
+        // (read by the other threads after the consumer barriers of the quantise / the first cross-warp sum)
+        if (EXCH && threadIdx.x == 0) s_epoch = *reinterpret_cast<volatile unsigned int*>(&ex.state[0]) + 1u;
         const uint32_t xs_base = ring_base + F8V_STAGES * F8V_STAGE_BYTES;
         if (FUSE_Q) {
             uint8_t* xs = f8v_ring + F8V_STAGES * F8V_STAGE_BYTES;
@@ -510,7 +520,11 @@ fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_s
                 } else if (n < N) {
                     // (raw * a_scale[m]) * w_scale[n], in that order (ktir_matmul_fp8.rs:676-712)
                     const float o = __fmul_rn(__fmul_rn(total, a_scale_eff[tok]), ws_mine);
-                    if (out_f32) {
+                    if (EXCH) {
+                        const unsigned int e_call = s_epoch;
+                        const long long at = tpc_slot(e_call, ex.world, ex.rank, ex.max_elems, (long long)tok * N + n);
+                        for (int p = 0; p < ex.world; ++p) tpc_ll_store(ex.peers.ll[p] + at, o, e_call);
+                    } else if (out_f32) {
                         reinterpret_cast<float*>(y)[(size_t)tok * N + n] = o;
                     } else {
                         const __nv_bfloat16 v = __float2bfloat16_rn(o);
@@ -534,13 +548,41 @@ fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_s
             float s = 0.f;
             for (int r = 0; r < split; ++r) s += cl_part[r][row][tok];
             const float o = __fmul_rn(__fmul_rn(s, (FUSE_Q ? q_scale : a_scale)[tok]), ws_final);
-            if (out_f32) {
+            if (EXCH) {
+                const unsigned int e_call = s_epoch;
+                const long long at = tpc_slot(e_call, ex.world, ex.rank, ex.max_elems, (long long)tok * N + n);
+                for (int p = 0; p < ex.world; ++p) tpc_ll_store(ex.peers.ll[p] + at, o, e_call);
+            } else if (out_f32) {
                 reinterpret_cast<float*>(y)[(size_t)tok * N + n] = o;
             } else {
                 const __nv_bfloat16 v = __float2bfloat16_rn(o);
                 y[(size_t)tok * N + n] = *reinterpret_cast<const uint16_t*>(&v);
             }
         }
+    }
+
+    if (EXCH) {
+        if (SPLIT_CLUSTER && sp != 0) return;                      // the cluster's CTA 0 owns the row-block (block-uniform exit)
+        __syncthreads();                                           // (the producer warp learns the call number)
+        const unsigned int e_call = s_epoch;
+        constexpr int SLOTS = 32 * MT * 4;
+        const int e = threadIdx.x;
+        const int ln = e / (MT * 4), idx = e % (MT * 4);
+        const int row = (ln >> 2) + (((idx & 3) >> 1) ? 8 : 0);
+        const int tok = (idx >> 2) * 8 + (ln & 3) * 2 + (idx & 1);
+        const uint2* mine = ex.peers.ll[ex.rank];
+        for (int rb = blockIdx.x; rb < rb_real; rb += (SPLIT_CLUSTER ? rb_real : int(gridDim.x))) {
+            const int n = rb * 16 + row;
+            if (e < SLOTS && tok < M && n < N) {
+                const long long at = (long long)tok * N + n;
+                float s = tpc_ll_wait(mine + tpc_slot(e_call, ex.world, 0, ex.max_elems, at), e_call, status);
+                for (int q = 1; q < ex.world; ++q)
+                    s = __fadd_rn(s, tpc_ll_wait(mine + tpc_slot(e_call, ex.world, q, ex.max_elems, at), e_call, status));
+                const __nv_bfloat16 v = __float2bfloat16_rn(s);
+                ex.y_bf16[at] = *reinterpret_cast<const uint16_t*>(&v);
+            }
+        }
+        tpc_finish_call(ex.state, e_call, gridDim.x);
     }
 }
 
@@ -674,7 +716,8 @@ static bool fp8_gemv_fuses_quant(int M, int K) {
 
 template <int MT>
 static int32_t fp8_gemv_launch(scr_ctx* ctx, const uint8_t* wpack, const uint8_t* xq, const float* a_scale, uint16_t* y,
-                               int M, int N, int K, cudaStream_t stream, const uint16_t* x_bf16 = nullptr) {
+                               int M, int N, int K, cudaStream_t stream, const uint16_t* x_bf16 = nullptr,
+                               const TpcExchange* exchange = nullptr) {
     const Fp8Geom g = fp8_geom(N, K);
     const float* w_scale = reinterpret_cast<const float*>(wpack + (size_t)g.NT * g.KT * FP8_TILE_BYTES);
     const int K16 = scr_ceil_div(K, 16) * 16;
@@ -683,8 +726,10 @@ static int32_t fp8_gemv_launch(scr_ctx* ctx, const uint8_t* wpack, const uint8_t
     fp8_gemv_shape(rb_real, g.KT, ctx->sm_count, &grid_x, &split);
     const bool fuse = (MT == 1) && x_bf16 != nullptr;
     const int kRingBytes = F8V_STAGES * F8V_STAGE_BYTES + (fuse ? M * K16 : 0);
-    auto kernel = fuse ? ((split == 1) ? fp8_gemv_kernel<1, 0, 1> : fp8_gemv_kernel<1, 1, 1>)
-                       : ((split == 1) ? fp8_gemv_kernel<MT, 0, 0> : fp8_gemv_kernel<MT, 1, 0>);
+    if (exchange && !fuse) return scr_fail(ctx, SCR_E_UNSUPPORTED, "fp8 matvec + exchange: needs the self-quantising matvec");
+    auto kernel = exchange ? ((split == 1) ? fp8_gemv_kernel<1, 0, 1, 1> : fp8_gemv_kernel<1, 1, 1, 1>)
+                  : fuse   ? ((split == 1) ? fp8_gemv_kernel<1, 0, 1, 0> : fp8_gemv_kernel<1, 1, 1, 0>)
+                           : ((split == 1) ? fp8_gemv_kernel<MT, 0, 0, 0> : fp8_gemv_kernel<MT, 1, 0, 0>);
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "fp8_gemv smem attribute: %s", cudaGetErrorString(e));
     cudaLaunchConfig_t cfg = {};
@@ -706,8 +751,17 @@ static int32_t fp8_gemv_launch(scr_ctx* ctx, const uint8_t* wpack, const uint8_t
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
+    TpcExchange ex = {};
+    if (exchange) {
+        // CTAs of this launch wait for their peers on the other ranks: every one of them has to be resident
+        int per_sm = 0;
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, F8V_THREADS, kRingBytes);
+        if (e != cudaSuccess || (long long)per_sm * ctx->sm_count < (long long)grid_x * split)
+            return scr_fail(ctx, SCR_E_UNSUPPORTED, "fp8 matvec + exchange: %d CTAs cannot all be resident", grid_x * split);
+        ex = *exchange;
+    }
     e = cudaLaunchKernelEx(&cfg, kernel, wpack, w_scale, xq, a_scale, x_bf16, K, y, M, N, K16, g.KT, rb_real, split, ctx->out_f32,
-                           ctx->dev_status);
+                           ctx->dev_status, ex);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "fp8_gemv launch: %s", cudaGetErrorString(e));
     return scr_check_launch(ctx, "fp8_gemv");
 }
@@ -775,6 +829,36 @@ extern "C" int32_t scr_linear_fp8_dynamic(scr_ctx* ctx, const void* packed, cons
     const size_t act_bytes = (fp8_act_bytes(M, K) + 127) / 128 * 128;
     return fp8_linear_from_pack(ctx, (const uint8_t*)packed, (const uint8_t*)workspace, M, N, K, y,
                                 (uint8_t*)workspace + act_bytes, workspace_bytes - act_bytes, (cudaStream_t)stream);
+}
+
+// Row-parallel fp8 linear + all-reduce in one launch (decode sizes): see EXCH above.
+extern "C" int32_t scr_linear_fp8_dynamic_allreduce(scr_tp_comm* comm, const void* packed, const uint16_t* x, int32_t M,
+                                                    int32_t N, int32_t K, uint16_t* y, void* stream) {
+    if (!comm) return SCR_E_ARG;
+    scr_ctx* ctx = comm->ctx;
+    SCR_REQUIRE_CTX(ctx);
+    if (!packed || !x || !y) return scr_fail(ctx, SCR_E_ARG, "null pointer");
+    if (!comm->connected) return scr_fail(ctx, SCR_E_COMM, "fp8 matvec + exchange: peers are not connected");
+    int32_t st = fp8_check_shape(ctx, N, K);
+    if (st) return st;
+    if (M <= 0) return scr_fail(ctx, SCR_E_SHAPE, "M=%d must be positive", M);
+    if ((long long)M * N > comm->max_elems)
+        return scr_fail(ctx, SCR_E_SHAPE, "fp8 matvec + exchange: %lld outputs exceed the communicator's %lld", (long long)M * N,
+                        comm->max_elems);
+    if (!fp8_gemv_fuses_quant(M, K))
+        return scr_fail(ctx, SCR_E_UNSUPPORTED,
+                        "fp8 matvec + exchange: M=%d K=%d is beyond the self-quantising matvec (use scr_linear_fp8_dynamic_partial "
+                        "and scr_tp_allreduce_partial)", M, K);
+    if (!scr_aligned16(packed) || !scr_aligned16(x)) return scr_fail(ctx, SCR_E_ALIGN, "packed/x must be 16-byte aligned");
+    if (ctx->out_f32 != 0) return scr_fail(ctx, SCR_E_ARG, "fp8 matvec + exchange: another output mode is active");
+    TpcExchange ex = {};
+    ex.peers = tpc_peer_table(comm);
+    ex.world = comm->world;
+    ex.rank = comm->rank;
+    ex.max_elems = comm->max_elems;
+    ex.state = comm->state;
+    ex.y_bf16 = y;
+    return fp8_gemv_launch<1>(ctx, (const uint8_t*)packed, nullptr, nullptr, y, M, N, K, (cudaStream_t)stream, x, &ex);
 }
 
 // ------------------------------------------------------------------------------------

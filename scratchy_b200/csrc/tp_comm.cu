@@ -4,10 +4,12 @@
 // meaning of the collective that follows is "sum the ranks' operands in rank order"
 // (crates/compiler/subtile/src/tensor_parallel.rs:1350-1362), then round once.  For the few tokens of
 // a decode step the exchange is latency, not bandwidth: one kernel per rank
-//   1. stores its partials into a receive slot it owns in EVERY rank's buffer (plain peer stores),
-//   2. publishes a per-CTA flag on every rank (release, system scope),
-//   3. waits — bounded — for the flags of all ranks for the slices it owns,
-//   4. sums the W received copies in rank order 0..W-1 and rounds to bf16.
+//   1. stores its partials into a receive slot it owns in EVERY rank's buffer (plain peer stores), each value
+//      as an 8-byte packet {f32 bits, call number} — an aligned 8-byte store is single-copy atomic, so the
+//      call number doubles as the "value has arrived" flag and neither side needs a system-scope fence
+//      (measured: a fence.sys per side cost ~3 us each, twice the rest of the exchange),
+//   2. reads — bounded polls — every rank's packets for the elements it owns,
+//   3. sums the W received copies in rank order 0..W-1 and rounds to bf16.
 // The result is the rank-ordered sum bit for bit on every rank (a library all-reduce promises no
 // order).  Buffers are cudaMalloc'd per rank and mapped into the peers through CUDA IPC handles that
 // the host exchanges once at start-up; the step path allocates nothing.  No multicast, no TMA here:
@@ -17,52 +19,14 @@
 // enough: a rank can start call e+1 only after every rank has pushed for call e, i.e. after every rank
 // has finished reading call e-1.  The call counter lives on the device and is advanced by the last CTA
 // of a launch, so a captured CUDA graph replays correctly.
-#include "common.cuh"
+#include "tp_comm.cuh"
 
 #include <string.h>
 
 #include <algorithm>
 #include <new>
 
-#define TPC_MAX_WORLD 8
-#define TPC_MAX_CTAS 256
-#define TPC_THREADS 256
-#define TPC_SLICE (TPC_THREADS * 4)          // f32 elements one CTA moves per pass
-#define TPC_WAIT_LIMIT (1u << 22)
-#define TPC_ERR_FLAG_WAIT 0x0C000001
-
-struct TpcPeers {
-    float* recv[TPC_MAX_WORLD];              // base of each rank's receive area  [2][W][max_elems]
-    unsigned int* flags[TPC_MAX_WORLD];      // base of each rank's flag area     [2][W][TPC_MAX_CTAS]
-};
-
-struct scr_tp_comm {
-    scr_ctx* ctx = nullptr;
-    int world = 1, rank = 0;
-    long long max_elems = 0;
-    size_t bytes = 0, flags_off = 0;
-    unsigned char* local = nullptr;
-    unsigned char* peer[TPC_MAX_WORLD] = {nullptr};
-    bool opened[TPC_MAX_WORLD] = {false};
-    unsigned int* state = nullptr;           // device: [0] = call counter, [1] = CTAs finished in the running call
-    bool connected = false;
-};
-
 namespace {
-
-__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
-    unsigned int v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ float4 ld_cg_f4(const float* p) {
-    float4 v;
-    asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
-    return v;
-}
 
 __global__ void __launch_bounds__(TPC_THREADS) tp_allreduce_kernel(TpcPeers peers, int world, int rank, long long max_elems,
                                                                    const float* __restrict__ partial, long long count,
@@ -78,65 +42,43 @@ __global__ void __launch_bounds__(TPC_THREADS) tp_allreduce_kernel(TpcPeers peer
     if (tid == 0) s_epoch = *reinterpret_cast<volatile unsigned int*>(&state[0]) + 1u;
     __syncthreads();
     const unsigned int e = s_epoch;
-    const long long half = (long long)(e & 1u) * world;
 
-    // 1. my partials -> my slot in every rank's receive area
+    // 1. my partials, as packets, -> my slot in every rank's receive area
     for (long long base = (long long)c * TPC_SLICE; base < count; base += (long long)gridDim.x * TPC_SLICE) {
         const long long i = base + tid * 4;
         if (i < count) {
             const float4 v = *reinterpret_cast<const float4*>(partial + i);
-            for (int p = 0; p < world; ++p) *reinterpret_cast<float4*>(peers.recv[p] + (half + rank) * max_elems + i) = v;
-        }
-    }
-    __syncthreads();
-    // 2. publish (the release is cumulative over the stores the barrier ordered before it: one system-scope fence
-    //    per publishing thread, not one per storing thread), 3. wait for every rank's copy of my slices (bounded)
-    if (tid < world) {
-        st_release_sys(peers.flags[tid] + (half + rank) * TPC_MAX_CTAS + c, e);
-        const unsigned int* mine = peers.flags[rank] + (half + tid) * TPC_MAX_CTAS + c;
-        bool seen = false;
-        for (unsigned int it = 0; it < TPC_WAIT_LIMIT; ++it) {
-            if ((int)(ld_acquire_sys(mine) - e) >= 0) {
-                seen = true;
-                break;
+            const float f[4] = {v.x, v.y, v.z, v.w};
+            for (int p = 0; p < world; ++p) {
+                uint2* dst = peers.ll[p] + tpc_slot(e, world, rank, max_elems, i);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) tpc_ll_store(dst + k, f[k], e);
             }
-            if ((it & 1023u) == 1023u && *reinterpret_cast<volatile int*>(status) != 0) break;
         }
-        if (!seen) atomicCAS(status, 0, TPC_ERR_FLAG_WAIT);
     }
-    __syncthreads();
-    // 4. rank-ordered sum, one rounding
-    const float* mine_recv = peers.recv[rank];
+    // 2. every rank's packets for my elements (bounded waits), summed in rank order, one rounding
+    const uint2* mine = peers.ll[rank];
     for (long long base = (long long)c * TPC_SLICE; base < count; base += (long long)gridDim.x * TPC_SLICE) {
         const long long i = base + tid * 4;
         if (i < count) {
-            float4 s = ld_cg_f4(mine_recv + half * max_elems + i);
+            float s[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) s[k] = tpc_ll_wait(mine + tpc_slot(e, world, 0, max_elems, i) + k, e, status);
             for (int q = 1; q < world; ++q) {
-                const float4 v = ld_cg_f4(mine_recv + (half + q) * max_elems + i);
-                s.x = __fadd_rn(s.x, v.x);
-                s.y = __fadd_rn(s.y, v.y);
-                s.z = __fadd_rn(s.z, v.z);
-                s.w = __fadd_rn(s.w, v.w);
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    s[k] = __fadd_rn(s[k], tpc_ll_wait(mine + tpc_slot(e, world, q, max_elems, i) + k, e, status));
             }
-            if (y_f32) *reinterpret_cast<float4*>(y_f32 + i) = s;
+            if (y_f32) *reinterpret_cast<float4*>(y_f32 + i) = make_float4(s[0], s[1], s[2], s[3]);
             if (y_bf16) {
-                const __nv_bfloat162 lo = __floats2bfloat162_rn(s.x, s.y), hi = __floats2bfloat162_rn(s.z, s.w);
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(s[0], s[1]), hi = __floats2bfloat162_rn(s[2], s[3]);
                 *reinterpret_cast<uint2*>(y_bf16 + i) =
                     make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
             }
         }
     }
-    // 5. the last CTA to finish advances the call counter (every CTA has read it by then)
-    __syncthreads();
-    if (tid == 0) {
-        __threadfence();
-        const unsigned int done = atomicAdd(&state[1], 1u);
-        if (done == gridDim.x - 1) {
-            state[1] = 0;
-            __threadfence();
-            *reinterpret_cast<volatile unsigned int*>(&state[0]) = e;
-        }
-    }
+    // 3. the last CTA to finish advances the call counter (every CTA has read it by then)
+    tpc_finish_call(state, e, gridDim.x);
 }
 
 }  // namespace
@@ -156,8 +98,7 @@ extern "C" int32_t scr_tp_comm_create(scr_ctx* ctx, int32_t world, int32_t rank,
     c->world = world;
     c->rank = rank;
     c->max_elems = max_elems;
-    c->flags_off = ((size_t)2 * world * max_elems * sizeof(float) + 255) & ~(size_t)255;
-    c->bytes = c->flags_off + (size_t)2 * world * TPC_MAX_CTAS * sizeof(unsigned int);
+    c->bytes = (size_t)2 * world * max_elems * sizeof(uint2);      // zeroed: call numbers start at 1
     cudaError_t e = cudaMalloc((void**)&c->local, c->bytes);
     if (e == cudaSuccess) e = cudaMemset(c->local, 0, c->bytes);
     if (e == cudaSuccess) e = cudaMalloc((void**)&c->state, 2 * sizeof(unsigned int));
@@ -207,13 +148,8 @@ extern "C" int32_t scr_tp_allreduce_partial(scr_tp_comm* comm, const float* part
                         comm->max_elems);
     if (!scr_aligned16(partial) || (y_f32 && !scr_aligned16(y_f32)) || (y_bf16 && ((uintptr_t)y_bf16 & 7u)))
         return scr_fail(ctx, SCR_E_ALIGN, "tp all-reduce: buffers must be 16-byte aligned");
-    TpcPeers peers;
-    for (int p = 0; p < TPC_MAX_WORLD; ++p) {
-        unsigned char* base = comm->peer[p < comm->world ? p : comm->rank];
-        peers.recv[p] = reinterpret_cast<float*>(base);
-        peers.flags[p] = reinterpret_cast<unsigned int*>(base + comm->flags_off);
-    }
-    const int grid = (int)std::min<long long>((count + TPC_SLICE - 1) / TPC_SLICE, TPC_MAX_CTAS);
+    const TpcPeers peers = tpc_peer_table(comm);
+    const int grid = (int)std::min<long long>((count + TPC_SLICE - 1) / TPC_SLICE, TPC_MAX_GRID);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(TPC_THREADS);

@@ -1,0 +1,79 @@
+// Shared pieces of the tensor-parallel exchange over NVLink peer memory: the communicator object, the peer
+// pointer table a kernel receives, and the system-scope publish / poll helpers.  Used by the stand-alone
+// all-reduce kernel (tp_comm.cu) and by the row-parallel matvec that pushes and sums in its own epilogue (fp8.cu).
+#pragma once
+#include "common.cuh"
+
+#define TPC_MAX_WORLD 8
+#define TPC_MAX_GRID 256                     // grid of the stand-alone all-reduce kernel
+#define TPC_THREADS 256
+#define TPC_SLICE (TPC_THREADS * 4)          // f32 elements one CTA moves per pass
+#define TPC_WAIT_LIMIT (1u << 22)
+#define TPC_ERR_FLAG_WAIT 0x0C000001
+
+// Every exchanged value travels as an 8-byte packet {f32 bits, call number}: an aligned 8-byte store is
+// single-copy atomic, so a receiver that reads the expected call number has the value with it — no
+// system-scope fence and no separate flag on either side (a fence.sys costs microseconds; measured).
+struct TpcPeers {
+    uint2* ll[TPC_MAX_WORLD];                // base of each rank's receive area  [2][W][max_elems] packets
+};
+
+struct scr_tp_comm {
+    scr_ctx* ctx = nullptr;
+    int world = 1, rank = 0;
+    long long max_elems = 0;
+    size_t bytes = 0;
+    unsigned char* local = nullptr;
+    unsigned char* peer[TPC_MAX_WORLD] = {nullptr};
+    bool opened[TPC_MAX_WORLD] = {false};
+    unsigned int* state = nullptr;           // device: [0] = call counter, [1] = CTAs finished in the running call
+    bool connected = false;
+};
+
+// What a kernel that exchanges in its own epilogue needs (passed by value).
+struct TpcExchange {
+    TpcPeers peers;
+    int world, rank;
+    long long max_elems;
+    unsigned int* state;
+    uint16_t* y_bf16;                        // the reduced, rounded result [M, N]
+};
+
+static inline TpcPeers tpc_peer_table(const scr_tp_comm* comm) {
+    TpcPeers peers;
+    for (int p = 0; p < TPC_MAX_WORLD; ++p) peers.ll[p] = reinterpret_cast<uint2*>(comm->peer[p < comm->world ? p : comm->rank]);
+    return peers;
+}
+
+// Slot of (call e, sending rank r, element i) in a receive area: calls alternate between two halves.
+__device__ __forceinline__ long long tpc_slot(unsigned int e, int world, int r, long long max_elems, long long i) {
+    return ((long long)(e & 1u) * world + r) * max_elems + i;
+}
+__device__ __forceinline__ void tpc_ll_store(uint2* p, float v, unsigned int e) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(e) : "memory");
+}
+// Bounded wait for the packet of call e; gives up (recording the code) after TPC_WAIT_LIMIT polls or as soon as
+// another waiter has recorded a failure, and returns 0 then.
+__device__ __forceinline__ float tpc_ll_wait(const uint2* p, unsigned int e, int* status) {
+    for (unsigned int it = 0; it < TPC_WAIT_LIMIT; ++it) {
+        uint32_t v, f;
+        asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v), "=r"(f) : "l"(p) : "memory");
+        if (f == e) return __uint_as_float(v);
+        if ((it & 1023u) == 1023u && *reinterpret_cast<volatile int*>(status) != 0) return 0.f;
+    }
+    atomicCAS(status, 0, TPC_ERR_FLAG_WAIT);
+    return 0.f;
+}
+// The last CTA of a launch advances the call counter (every CTA has read it by then).
+__device__ __forceinline__ void tpc_finish_call(unsigned int* state, unsigned int e, unsigned int ctas) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const unsigned int done = atomicAdd(&state[1], 1u);
+        if (done == ctas - 1) {
+            state[1] = 0;
+            __threadfence();
+            *reinterpret_cast<volatile unsigned int*>(&state[0]) = e;
+        }
+    }
+}

@@ -148,6 +148,25 @@ class OneShotAllReduce:
             ctypes.c_void_p(torch.cuda.current_stream(part.device).cuda_stream)))
         return out_bf16 if out_bf16 is not None else out_f32
 
+    def fp8_linear_all_reduce(self, linear, x_local: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """A row-parallel `Fp8Linear` and its all-reduce as one launch (`scr_linear_fp8_dynamic_allreduce`):
+        the same bits as `linear.forward_partial` followed by `all_reduce`.  Raises SCR_E_UNSUPPORTED beyond
+        the self-quantising matvec (a few tokens); see `fp8_linear_all_reduce_supported`."""
+        import ctypes
+        x2 = x_local.reshape(-1, linear.in_features).contiguous()
+        M = int(x2.shape[0])
+        if out is None:
+            out = torch.empty((M, linear.out_features), dtype=torch.bfloat16, device=x2.device)
+        self._ctx.check(self._lib.lib().scr_linear_fp8_dynamic_allreduce(
+            self._h, ctypes.c_void_p(linear.packed.data_ptr()), ctypes.c_void_p(x2.data_ptr()), M, linear.out_features,
+            linear.in_features, ctypes.c_void_p(out.data_ptr()),
+            ctypes.c_void_p(torch.cuda.current_stream(x2.device).cuda_stream)))
+        return out
+
+    def fp8_linear_all_reduce_supported(self, linear, M: int) -> bool:
+        k16 = (linear.in_features + 15) // 16 * 16
+        return M <= 4 and linear.in_features % 8 == 0 and M * k16 <= 14 * 1024 and M * linear.out_features <= self.max_elems
+
     def close(self) -> None:
         if self._h:
             if self.tp.world > 1 and dist.is_initialized():

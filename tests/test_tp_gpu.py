@@ -110,6 +110,34 @@ def _nccl_worker(rank, world, port, q):
             ok &= bool(np.array_equal(got32.cpu().numpy(), oracle.allreduce_rank_order(parts)))
         y = tpmod.RowParallel(flin, comm, one_shot=one).forward(tpmod.slice_cols(xt, tp))
         ok &= rel_l2(y.view(torch.int16).cpu().numpy().view(np.uint16), want) <= REL_L2_TOL
+        # matvec + exchange in one launch: the bits of the partial matvec followed by the one-shot exchange,
+        # for a persistent grid (N = 8192: more row-blocks than CTAs) and a cluster-split one (N = 512),
+        # interleaved with stand-alone exchanges on the same communicator, eagerly and from a graph
+        for n_out, m_rows in [(512, 3), (8192, 1), (8192, 2)]:
+            wq2, ws2 = oracle.fp8_quantize_weight_per_channel(synth.fp8_weights_f32(n_out, K, 50 + m_rows))
+            f2 = Fp8Linear.from_tensors(*tpmod.shard_fp8_row_parallel(torch.from_numpy(wq2).to(dev),
+                                                                      torch.from_numpy(ws2).to(dev), tp))
+            xl = tpmod.slice_cols(xt[:m_rows], tp).contiguous()
+            ref = one.all_reduce(f2.forward_partial(xl))
+            ok &= one.fp8_linear_all_reduce_supported(f2, m_rows)
+            for _ in range(3):
+                got = one.fp8_linear_all_reduce(f2, xl)
+                ok &= bool(torch.equal(got.view(torch.int16), ref.view(torch.int16)))
+            fused_out = torch.empty_like(ref)
+            torch.cuda.synchronize()
+            dist.barrier()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                one.fp8_linear_all_reduce(f2, xl, out=fused_out)
+                one.all_reduce(mine, out_bf16=got16)
+            for _ in range(3):
+                fused_out.zero_()
+                graph.replay()
+                torch.cuda.synchronize()
+                ok &= bool(torch.equal(fused_out.view(torch.int16), ref.view(torch.int16)))
+                ok &= bool(np.array_equal(got16.view(torch.int16).cpu().numpy().view(np.uint16), want_bits))
+            want2, _ = lockstep_fp8_row_parallel(wq2, ws2, x[:m_rows], world)
+            ok &= rel_l2(fused_out.view(torch.int16).cpu().numpy().view(np.uint16), want2) <= REL_L2_TOL
         torch.cuda.synchronize()
         _lib_ctx = __import__("scratchy_b200")._lib.context(rank)
         _lib_ctx.device_status(None)                         # no bounded flag wait ran out
@@ -170,4 +198,57 @@ def test_one_shot_all_reduce_single_rank():
         one.all_reduce(torch.zeros(301 * 1024, device=dev))                    # beyond max_elems
     with pytest.raises(_lib.ScratchyCudaError):
         one.all_reduce(torch.zeros(6, device=dev))                             # not a multiple of 4
+    one.close()
+
+
+@pytest.mark.parametrize("N,K,M", [(8192, 1024, 1), (8192, 3584, 4), (512, 4096, 3), (72, 1024, 2), (8192, 14336, 1)])
+def test_fp8_matvec_with_exchange_single_rank(N, K, M):
+    """World size 1 runs the whole fused kernel on one GPU (push to itself, flag, wait, sum of one operand):
+    the result is the rounded partial, bit for bit, for persistent and cluster-split grids, eagerly,
+    interleaved with stand-alone exchanges, and replayed from a CUDA graph."""
+    import torch
+    from scratchy_b200 import Fp8Linear, _lib, tp as tpmod
+    dev = torch.device("cuda", 0)
+    one = tpmod.OneShotAllReduce(tpmod.TpWorld(1, 0), dev, max_elems=4 * 8192)
+    wq, ws = oracle.fp8_quantize_weight_per_channel(synth.fp8_weights_f32(N, K, N + K))
+    lin = Fp8Linear.from_tensors(to_dev(wq), to_dev(ws))
+    x = bf16_dev(synth.activations_bf16(M, K, 5)).reshape(M, K)
+    want = tpmod.partial_to_bf16(lin.forward_partial(x))
+    assert one.fp8_linear_all_reduce_supported(lin, M)
+    for i in range(3):
+        got = one.fp8_linear_all_reduce(lin, x)
+        if i == 1:
+            one.all_reduce(torch.zeros(8, device=dev))            # a stand-alone call in between: the halves keep alternating
+        torch.cuda.synchronize()
+        assert np.array_equal(bits_of(got), bits_of(want)), f"call {i}"
+    out = torch.zeros_like(want)
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        one.fp8_linear_all_reduce(lin, x, out=out)
+    for i in range(3):
+        out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert np.array_equal(bits_of(out), bits_of(want)), f"replay {i}"
+    _lib.context(0).device_status(None)
+    one.close()
+
+
+def test_fp8_matvec_with_exchange_refuses_what_it_cannot_fuse():
+    import torch
+    from scratchy_b200 import Fp8Linear, _lib, tp as tpmod
+    dev = torch.device("cuda", 0)
+    one = tpmod.OneShotAllReduce(tpmod.TpWorld(1, 0), dev, max_elems=8192)
+    wq, ws = oracle.fp8_quantize_weight_per_channel(synth.fp8_weights_f32(256, 1024, 1))
+    lin = Fp8Linear.from_tensors(to_dev(wq), to_dev(ws))
+    with pytest.raises(_lib.ScratchyCudaError) as e:
+        one.fp8_linear_all_reduce(lin, torch.zeros((8, 1024), dtype=torch.bfloat16, device=dev))     # 8 rows: not self-quantising
+    assert e.value.status == -7
+    big = Fp8Linear.from_tensors(to_dev(np.repeat(wq, 64, axis=0)), to_dev(np.repeat(ws, 64)))       # 16384 outputs > max_elems
+    with pytest.raises(_lib.ScratchyCudaError) as e:
+        one.fp8_linear_all_reduce(big, torch.zeros((1, 1024), dtype=torch.bfloat16, device=dev))
+    assert e.value.status == -2
+    assert not one.fp8_linear_all_reduce_supported(lin, 8)
     one.close()
