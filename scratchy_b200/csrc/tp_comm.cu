@@ -81,6 +81,75 @@ __global__ void __launch_bounds__(TPC_THREADS) tp_allreduce_kernel(TpcPeers peer
     tpc_finish_call(state, e, gridDim.x);
 }
 
+// The same exchange for larger payloads: dense f32 stores, then one flag per CTA and rank.
+__device__ __forceinline__ float4 ld_cg_f4(const float* p) {
+    float4 v;
+    asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+    return v;
+}
+
+__global__ void __launch_bounds__(TPC_THREADS) tp_allreduce_flags_kernel(TpcPeers peers, int world, int rank, long long max_elems,
+                                                                         const float* __restrict__ partial, long long count,
+                                                                         uint16_t* __restrict__ y_bf16, float* __restrict__ y_f32,
+                                                                         unsigned int* state, int* status) {
+    __shared__ unsigned int s_epoch;
+    const int c = blockIdx.x, tid = threadIdx.x;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (tid == 0) s_epoch = *reinterpret_cast<volatile unsigned int*>(&state[0]) + 1u;
+    __syncthreads();
+    const unsigned int e = s_epoch;
+    const long long half = (long long)(e & 1u) * world;
+
+    // 1. my partials -> my slot in every rank's dense receive area
+    for (long long base = (long long)c * TPC_SLICE; base < count; base += (long long)gridDim.x * TPC_SLICE) {
+        const long long i = base + tid * 4;
+        if (i < count) {
+            const float4 v = *reinterpret_cast<const float4*>(partial + i);
+            for (int p = 0; p < world; ++p) *reinterpret_cast<float4*>(peers.recv[p] + (half + rank) * max_elems + i) = v;
+        }
+    }
+    __syncthreads();
+    // 2. publish (the release is cumulative over the stores the barrier ordered before it: one system-scope fence
+    //    per publishing thread, not one per storing thread), 3. wait for every rank's copy of my slices (bounded)
+    if (tid < world) {
+        tpc_st_release_sys(peers.flags[tid] + (half + rank) * TPC_MAX_CTAS + c, e);
+        const unsigned int* mine = peers.flags[rank] + (half + tid) * TPC_MAX_CTAS + c;
+        bool seen = false;
+        for (unsigned int it = 0; it < TPC_WAIT_LIMIT; ++it) {
+            if ((int)(tpc_ld_acquire_sys(mine) - e) >= 0) {
+                seen = true;
+                break;
+            }
+            if ((it & 1023u) == 1023u && *reinterpret_cast<volatile int*>(status) != 0) break;
+        }
+        if (!seen) atomicCAS(status, 0, TPC_ERR_FLAG_WAIT);
+    }
+    __syncthreads();
+    // 4. rank-ordered sum, one rounding
+    const float* mine_recv = peers.recv[rank];
+    for (long long base = (long long)c * TPC_SLICE; base < count; base += (long long)gridDim.x * TPC_SLICE) {
+        const long long i = base + tid * 4;
+        if (i < count) {
+            float4 s = ld_cg_f4(mine_recv + half * max_elems + i);
+            for (int q = 1; q < world; ++q) {
+                const float4 v = ld_cg_f4(mine_recv + (half + q) * max_elems + i);
+                s.x = __fadd_rn(s.x, v.x);
+                s.y = __fadd_rn(s.y, v.y);
+                s.z = __fadd_rn(s.z, v.z);
+                s.w = __fadd_rn(s.w, v.w);
+            }
+            if (y_f32) *reinterpret_cast<float4*>(y_f32 + i) = s;
+            if (y_bf16) {
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(s.x, s.y), hi = __floats2bfloat162_rn(s.z, s.w);
+                *reinterpret_cast<uint2*>(y_bf16 + i) =
+                    make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+            }
+        }
+    }
+    tpc_finish_call(state, e, gridDim.x);
+}
+
 }  // namespace
 
 extern "C" int32_t scr_tp_comm_create(scr_ctx* ctx, int32_t world, int32_t rank, int64_t max_elems, scr_tp_comm** out,
@@ -98,7 +167,10 @@ extern "C" int32_t scr_tp_comm_create(scr_ctx* ctx, int32_t world, int32_t rank,
     c->world = world;
     c->rank = rank;
     c->max_elems = max_elems;
-    c->bytes = (size_t)2 * world * max_elems * sizeof(uint2);      // zeroed: call numbers start at 1
+    // packets | dense f32 | flags; zeroed: call numbers start at 1
+    c->recv_off = ((size_t)2 * world * max_elems * sizeof(uint2) + 255) & ~(size_t)255;
+    c->flags_off = (c->recv_off + (size_t)2 * world * max_elems * sizeof(float) + 255) & ~(size_t)255;
+    c->bytes = c->flags_off + (size_t)2 * world * TPC_MAX_CTAS * sizeof(unsigned int);
     cudaError_t e = cudaMalloc((void**)&c->local, c->bytes);
     if (e == cudaSuccess) e = cudaMemset(c->local, 0, c->bytes);
     if (e == cudaSuccess) e = cudaMalloc((void**)&c->state, 2 * sizeof(unsigned int));
@@ -159,7 +231,9 @@ extern "C" int32_t scr_tp_allreduce_partial(scr_tp_comm* comm, const float* part
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, tp_allreduce_kernel, peers, comm->world, comm->rank, (long long)comm->max_elems, partial,
+    // every rank takes the same branch: count and world are the same everywhere
+    auto kernel = (long long)count * comm->world <= TPC_PACKET_MAX ? tp_allreduce_kernel : tp_allreduce_flags_kernel;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, peers, comm->world, comm->rank, (long long)comm->max_elems, partial,
                                        (long long)count, y_bf16, y_f32, comm->state, ctx->dev_status);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "tp all-reduce launch: %s", cudaGetErrorString(e));
     return scr_check_launch(ctx, "tp_allreduce");

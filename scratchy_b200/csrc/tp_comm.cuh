@@ -14,15 +14,23 @@
 // Every exchanged value travels as an 8-byte packet {f32 bits, call number}: an aligned 8-byte store is
 // single-copy atomic, so a receiver that reads the expected call number has the value with it — no
 // system-scope fence and no separate flag on either side (a fence.sys costs microseconds; measured).
+// Larger payloads (more than TPC_PACKET_MAX values summed over the ranks) go the other way: dense f32 stores into
+// a second receive area, then one flag per CTA and rank with release / acquire at system scope — half the bytes
+// and 16-byte stores; the two fences are then small against the transfer (TP=8, 32 tokens: 156 us per layer
+// against 332 us with packets).
+#define TPC_PACKET_MAX 32768
+#define TPC_MAX_CTAS 256                     // flag slots per (half, rank)
 struct TpcPeers {
-    uint2* ll[TPC_MAX_WORLD];                // base of each rank's receive area  [2][W][max_elems] packets
+    uint2* ll[TPC_MAX_WORLD];                // base of each rank's packet area   [2][W][max_elems] packets
+    float* recv[TPC_MAX_WORLD];              // base of each rank's dense area    [2][W][max_elems] f32
+    unsigned int* flags[TPC_MAX_WORLD];      // base of each rank's flag area     [2][W][TPC_MAX_CTAS]
 };
 
 struct scr_tp_comm {
     scr_ctx* ctx = nullptr;
     int world = 1, rank = 0;
     long long max_elems = 0;
-    size_t bytes = 0;
+    size_t bytes = 0, recv_off = 0, flags_off = 0;
     unsigned char* local = nullptr;
     unsigned char* peer[TPC_MAX_WORLD] = {nullptr};
     bool opened[TPC_MAX_WORLD] = {false};
@@ -41,7 +49,12 @@ struct TpcExchange {
 
 static inline TpcPeers tpc_peer_table(const scr_tp_comm* comm) {
     TpcPeers peers;
-    for (int p = 0; p < TPC_MAX_WORLD; ++p) peers.ll[p] = reinterpret_cast<uint2*>(comm->peer[p < comm->world ? p : comm->rank]);
+    for (int p = 0; p < TPC_MAX_WORLD; ++p) {
+        unsigned char* base = comm->peer[p < comm->world ? p : comm->rank];
+        peers.ll[p] = reinterpret_cast<uint2*>(base);
+        peers.recv[p] = reinterpret_cast<float*>(base + comm->recv_off);
+        peers.flags[p] = reinterpret_cast<unsigned int*>(base + comm->flags_off);
+    }
     return peers;
 }
 
@@ -63,6 +76,14 @@ __device__ __forceinline__ float tpc_ll_wait(const uint2* p, unsigned int e, int
     }
     atomicCAS(status, 0, TPC_ERR_FLAG_WAIT);
     return 0.f;
+}
+__device__ __forceinline__ void tpc_st_release_sys(unsigned int* p, unsigned int v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int tpc_ld_acquire_sys(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
 }
 // The last CTA of a launch advances the call counter (every CTA has read it by then).
 __device__ __forceinline__ void tpc_finish_call(unsigned int* state, unsigned int e, unsigned int ctas) {

@@ -86,12 +86,21 @@ def _nccl_worker(rank, world, port, q):
         want, _ = lockstep_fp8_row_parallel(wq, ws, x, world)
         ok &= rel_l2(y.view(torch.int16).cpu().numpy().view(np.uint16), want) <= REL_L2_TOL
         # the one-shot exchange over peer memory: rank-ordered sum, bit for bit, eagerly and replayed from a graph
-        one = tpmod.OneShotAllReduce(tp, dev, max_elems=16 * 1024)
+        one = tpmod.OneShotAllReduce(tp, dev, max_elems=40 * 1024)
         rng = np.random.default_rng(7)
         parts = [rng.standard_normal((5, 1024)).astype(np.float32) * (1.0 + r) for r in range(world)]
         want_bits = oracle.f32_to_bf16_bits(oracle.allreduce_rank_order(parts))
         mine = torch.from_numpy(parts[rank]).to(dev)
         for _ in range(3):                                   # consecutive calls alternate the receive halves
+            got = one.all_reduce(mine)
+            ok &= bool(np.array_equal(got.view(torch.int16).cpu().numpy().view(np.uint16), want_bits))
+        # a payload beyond the packet form (dense stores + one flag per CTA and rank), interleaved with the small one
+        big = [rng.standard_normal((40, 1024)).astype(np.float32) * (1.0 + r) for r in range(world)]
+        big_bits = oracle.f32_to_bf16_bits(oracle.allreduce_rank_order(big))
+        big_mine = torch.from_numpy(big[rank]).to(dev)
+        for _ in range(3):
+            got = one.all_reduce(big_mine)
+            ok &= bool(np.array_equal(got.view(torch.int16).cpu().numpy().view(np.uint16), big_bits))
             got = one.all_reduce(mine)
             ok &= bool(np.array_equal(got.view(torch.int16).cpu().numpy().view(np.uint16), want_bits))
         got16 = torch.empty((5, 1024), dtype=torch.bfloat16, device=dev)
