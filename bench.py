@@ -439,7 +439,7 @@ def run_gpu(args):
     if world > 1 or args.sweep:
         del layers, graph, graph_e2e
         torch.cuda.empty_cache()
-        tp_res = run_tp(device, world, rank, fuse_exchange=args.tp_fused_exchange)
+        tp_res = run_tp(device, world, rank, fuse_exchange=not args.tp_separate_exchange)
         if rank == 0:
             extra["tp"] = tp_res
 
@@ -625,7 +625,7 @@ def run_decode(device, steps=20, batches=(1, 8, 32), context=2048, block_size=16
     return out
 
 
-def run_tp(device, world, rank, fuse_exchange=False):
+def run_tp(device, world, rank, fuse_exchange=True):
     """BASELINE config 4: Llama-3-70B-shaped fp8 per-channel linears, tensor parallel over `world`
     GPUs: column-parallel qkv and gate/up, row-parallel o and down, each followed by the all-reduce
     of the f32 partials [M, 8192] and one rounding to bf16 — the one-shot peer-memory kernel
@@ -850,9 +850,9 @@ def main():
     ap.add_argument("--decode-only", action="store_true", help="run only the whole-decode-step section and print it")
     ap.add_argument("--decode-batches", default="1,8,32")
     ap.add_argument("--no-fuse-rope", action="store_true", help="decode step with RoPE + append as a kernel of their own")
-    ap.add_argument("--tp-fused-exchange", action="store_true",
-                    help="tensor-parallel section: row-parallel matvec and all-reduce as ONE launch "
-                         "(scr_linear_fp8_dynamic_allreduce; measured a few percent slower than the two launches)")
+    ap.add_argument("--tp-separate-exchange", action="store_true",
+                    help="tensor-parallel section: row-parallel matvec and all-reduce as two launches instead of "
+                         "scr_linear_fp8_dynamic_allreduce (measured: equal at TP=2, 9 %% slower at TP=8)")
     ap.add_argument("--case", default=None, help="kind,shape,M e.g. int4,gate,2048: time one linear alone")
     args = ap.parse_args()
     if args.case:
