@@ -575,7 +575,7 @@ def run_sweep(device, ctx):
 
 
 def run_decode(device, steps=20, batches=(1, 8, 32), context=2048, block_size=16, fuse_rope=True):
-    """BASELINE config 3: random-init Llama-3.2-3B, every linear MLX int4 g64 (lm_head too), one decode
+    """Benchmark configuration 3: random-init Llama-3.2-3B, every linear MLX int4 g64 (lm_head too), one decode
     step at context `context` with a bf16 paged KV cache, the whole step one CUDA graph.
     tok/s = batch / step time.  The step streams all packed weights (larger than L2) plus the batch's KV."""
     import torch
@@ -626,7 +626,7 @@ def run_decode(device, steps=20, batches=(1, 8, 32), context=2048, block_size=16
 
 
 def run_tp(device, world, rank, fuse_exchange=True):
-    """BASELINE config 4: Llama-3-70B-shaped fp8 per-channel linears, tensor parallel over `world`
+    """Benchmark configuration 4: Llama-3-70B-shaped fp8 per-channel linears, tensor parallel over `world`
     GPUs: column-parallel qkv and gate/up, row-parallel o and down, each followed by the all-reduce
     of the f32 partials [M, 8192] and one rounding to bf16 — the one-shot peer-memory kernel
     (`scr_tp_allreduce_partial`) up to M = 64, the process group's NCCL all-reduce above.  One

@@ -96,7 +96,7 @@ def test_dequant_bit_exact_adversarial_scales():
 
 
 def test_config0_single_linear_m1():
-    """BASELINE config 0: M=1, K=3072, N=8192, seed 0."""
+    """Benchmark configuration 0: M=1, K=3072, N=8192, seed 0."""
     w, s, b = synth.affine_int4_weights(8192, 3072, 64, 0)
     x = synth.activations_bf16(1, 3072, 1)
     got, want = run_case(8192, 3072, 1, 0, w, s, b, x)
@@ -194,7 +194,7 @@ def test_prefill_gemm_llama_shapes_full_oracle(name, M):
 
 @pytest.mark.parametrize("name,M", [("gate", 2048), ("down", 2048), ("q", 512)])
 def test_prefill_gemm_full_size_sampled_rows(name, M):
-    """Full BASELINE sizes: the oracle evaluates a seeded subset of 24 token rows (each output row
+    """Full benchmark sizes: the oracle evaluates a seeded subset of 24 token rows (each output row
     depends only on its own activation row), and the whole output must be finite."""
     import torch
     K, N = synth.LLAMA_3_2_3B[name]

@@ -170,7 +170,7 @@ def test_prefill_gemm_qwen_shapes_full_oracle(name, M):
 
 @pytest.mark.parametrize("name,M", [("gate", 2048), ("down", 2048), ("gate", 8192)])
 def test_prefill_gemm_full_size_sampled_rows(name, M):
-    """Full BASELINE sizes: oracle on a seeded subset of 16 token rows; x_q and a_scale of those rows
+    """Full benchmark sizes: oracle on a seeded subset of 16 token rows; x_q and a_scale of those rows
     must be bit-exact and the outputs within tolerance; the whole output must be finite."""
     import torch
     from scratchy_b200 import Fp8Linear
