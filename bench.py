@@ -770,6 +770,8 @@ def run_case(args):
     torch.cuda.set_device(0)
     if kind == "attn":
         return run_case_attention(device, batch=int(name), context=M, reps=args.steps)
+    # kind "fp8x": the fp8 matvec with the tensor-parallel exchange in its epilogue, on a one-rank communicator
+    # (pushes to itself: the whole kernel runs on one GPU)
     K, N = (synth.LLAMA_3_2_3B if kind == "int4" else synth.QWEN_2_5_7B)[name]
     copies = max(2, int((256 << 20) // (N * K)) + 1)
     lins = []
@@ -784,14 +786,23 @@ def run_case(args):
     x = torch.randn((M, K), device=device).to(torch.bfloat16)
     y = torch.empty((M, N), dtype=torch.bfloat16, device=device)
     ws = torch.empty(max(16, lins[0].workspace_bytes(M)), dtype=torch.uint8, device=device)
+    if kind == "fp8x":
+        from scratchy_b200 import tp as tpmod
+        one = tpmod.OneShotAllReduce(tpmod.TpWorld(1, 0), device, max_elems=(M * N + 3) // 4 * 4)
+
+        def call(l):
+            one.fp8_linear_all_reduce(l, x, out=y)
+    else:
+        def call(l):
+            l.forward(x, out=y, workspace=ws)
     for l in lins[:2]:
-        l.forward(x, out=y, workspace=ws)
+        call(l)
     torch.cuda.synchronize()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     reps = args.steps
     a.record()
     for i in range(reps):
-        lins[i % copies].forward(x, out=y, workspace=ws)
+        call(lins[i % copies])
     b.record()
     torch.cuda.synchronize()
     dt = a.elapsed_time(b) * 1e-3 / reps
