@@ -89,12 +89,17 @@ int32_t scr_affine_b4_dequant_dump(scr_ctx* ctx, const void* packed, int32_t N, 
  *   y[M,N] (bf16) = x[M,K] (bf16) @ dequant(W)[N,K]^T, f32 accumulation, one rounding,
  * the contraction of `cpu_reference::affine_qmm_t_b4` (crates/targets/metal/src/cpu_reference.rs:107-137).
  * The kernel is chosen from M (matvec for M <= 16, tensor-core GEMM above).
+ * `bias_bf16` (may be NULL) is the linear's own bias [N], the `{prefix}.bias` tensor the loader
+ * takes (crates/targets/metal/src/layers_quant.rs:318-351): it is added in f32 before the one
+ * rounding, as the reference's matvec epilogue does (the `QmvEnds.bias` end,
+ * crates/targets/metal/src/tape/step.rs:472-482, shaders/quantized_qmv.metal:104-112).
  * `workspace` may be NULL when `scr_linear_workspace_size` reports 0 bytes. */
 #define SCR_KIND_AFFINE_B4   0
 #define SCR_KIND_FP8_DYNAMIC 1
 int32_t scr_linear_workspace_size(int32_t kind, int32_t M, int32_t N, int32_t K, size_t* bytes);
 int32_t scr_linear_affine_b4(scr_ctx* ctx, const void* packed, const uint16_t* x_bf16,
-                             int32_t M, int32_t N, int32_t K, int32_t group, uint16_t* y_bf16,
+                             int32_t M, int32_t N, int32_t K, int32_t group,
+                             const uint16_t* bias_bf16, uint16_t* y_bf16,
                              void* workspace, size_t workspace_bytes, void* stream);
 /* The fused gate/up projection with its activation, the `FusedGateUpSiluMul` end of the reference's
  * matvec (`QmvEnds`, crates/targets/metal/src/tape/step.rs:472-482; golden cpu_golden.rs:211-219):
@@ -187,13 +192,15 @@ int32_t scr_e4m3_encode(scr_ctx* ctx, const float* v, int64_t count, uint8_t* ou
  * `scr_linear_fp8` consumes an activation pack; `scr_linear_fp8_dynamic` is the whole
  * generated Linear (quantise, then contract) and needs a workspace that holds the pack.  For
  * M <= 4 (and M*K <= 16 KiB of codes) the matvec quantises the activations itself — same x_q and
- * a_scale bits, one launch, the workspace is not touched. */
+ * a_scale bits, one launch, the workspace is not touched.  `bias_bf16` (may be NULL) is the linear's
+ * own bias [N] (`{prefix}.bias`; the q/k/v projections of Qwen2.5 carry one), added in f32 to the
+ * dequantised sum before the one rounding. */
 int32_t scr_linear_fp8(scr_ctx* ctx, const void* packed, const void* act, int32_t M, int32_t N,
-                       int32_t K, uint16_t* y_bf16, void* workspace, size_t workspace_bytes,
-                       void* stream);
+                       int32_t K, const uint16_t* bias_bf16, uint16_t* y_bf16, void* workspace,
+                       size_t workspace_bytes, void* stream);
 int32_t scr_linear_fp8_dynamic(scr_ctx* ctx, const void* packed, const uint16_t* x_bf16, int32_t M,
-                               int32_t N, int32_t K, uint16_t* y_bf16, void* workspace,
-                               size_t workspace_bytes, void* stream);
+                               int32_t N, int32_t K, const uint16_t* bias_bf16, uint16_t* y_bf16,
+                               void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---- tensor parallel: row-parallel partials --------------------------------
  * A row-parallel linear (o, down) holds a K-slice of the weight and yields a `Partial`

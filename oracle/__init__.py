@@ -108,6 +108,14 @@ def affine_qmm_t_b4(packed_bytes, scales, biases, x, m, n, k, group_size, scale_
     return (y, yf) if want_f32 else y
 
 
+def affine_qmm_t_b4_bias(packed_bytes, scales, biases, x, linear_bias, m, n, k, group_size, scale_dt=BF16):
+    """The linear with its own bias [n] (bf16 patterns): the reference's matvec adds `float(bias[n])` to the f32
+    dot and rounds once (crates/targets/metal/shaders/quantized_qmv.metal:104-112, `qmv_store`)."""
+    _, acc = affine_qmm_t_b4(packed_bytes, scales, biases, x, m, n, k, group_size, scale_dt=scale_dt, want_f32=True)
+    bias = bf16_bits_to_f32(_c(linear_bias, np.uint16).reshape(1, n))
+    return f32_to_bf16_bits(acc.astype(np.float32) + bias.astype(np.float32))
+
+
 # --------------------------------------------------------------------------- e4m3 / fp8
 def e4m3_to_f32(b) -> np.ndarray:
     b = _c(b, np.uint8)
@@ -151,6 +159,15 @@ def fp8_dynamic_linear(x_bf16, wq, w_scale, m, n, k, rne=False, want_f32=False):
     """The whole generated Linear for fp8-dynamic-per-channel: quantise per token, contract, dequantise."""
     xq, a = fp8_quant_per_token(x_bf16, m, k, rne=rne)
     return fp8_linear(xq, a, wq, w_scale, m, n, k, want_f32=want_f32)
+
+
+def fp8_dynamic_linear_bias(x_bf16, wq, w_scale, linear_bias, m, n, k) -> np.ndarray:
+    """The fp8 dynamic linear with the linear's own bias [n] (bf16 patterns): the bias is added in f32 to the
+    dequantised sum and the result rounded once, the order of the reference's matvec epilogue
+    (crates/targets/metal/shaders/quantized_qmv.metal:104-112, `qmv_store`)."""
+    _, acc = fp8_dynamic_linear(x_bf16, wq, w_scale, m, n, k, want_f32=True)
+    bias = bf16_bits_to_f32(_c(linear_bias, np.uint16).reshape(1, n))
+    return f32_to_bf16_bits(acc.astype(np.float32) + bias.astype(np.float32))
 
 
 def fp8_weight_only_linear(a, wq, ws, m, n, k) -> np.ndarray:

@@ -41,7 +41,7 @@ SIGNATURES = {
     "scr_affine_b4_repack": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp]),
     "scr_affine_b4_dequant_dump": (_i32, [_vp, _vp, _i32, _i32, _i32, _vp, _vp]),
     "scr_linear_workspace_size": (_i32, [_i32, _i32, _i32, _i32, _psz]),
-    "scr_linear_affine_b4": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _sz, _vp]),
+    "scr_linear_affine_b4": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _sz, _vp]),
     "scr_linear_affine_b4_silu_mul": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp]),
     "scr_linear_affine_b4_residual_rmsnorm": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, ctypes.c_float, _vp,
                                                      _vp, _sz, _vp]),
@@ -55,8 +55,8 @@ SIGNATURES = {
     "scr_rmsnorm_fp8_quant": (_i32, [_vp, _vp, _vp, ctypes.c_float, _i32, _i32, _vp, _vp, _vp]),
     "scr_fp8_act_unpack": (_i32, [_vp, _vp, _i32, _i32, _vp, _vp, _vp]),
     "scr_e4m3_encode": (_i32, [_vp, _vp, _i64, _vp, _vp]),
-    "scr_linear_fp8": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _sz, _vp]),
-    "scr_linear_fp8_dynamic": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _sz, _vp]),
+    "scr_linear_fp8": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _sz, _vp]),
+    "scr_linear_fp8_dynamic": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _sz, _vp]),
     "scr_linear_affine_b4_partial": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _sz, _vp]),
     "scr_linear_fp8_partial": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _sz, _vp]),
     "scr_linear_fp8_dynamic_partial": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _sz, _vp]),

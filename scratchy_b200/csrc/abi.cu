@@ -82,49 +82,6 @@ extern "C" int32_t scr_device_status(scr_ctx* ctx, void* stream, int32_t* code) 
     return SCR_OK;
 }
 
-// ---- row-parallel partials ----------------------------------------------------------------
-// A row-parallel linear (o, down) yields a `Partial` in the reference's placement lattice
-// (crates/compiler/subtile/src/tensor_parallel.rs:1-63): unrounded f32 sums over the rank's
-// K-slice, to be summed over ranks by the all-reduce and rounded to bf16 once afterwards.
-extern "C" int32_t scr_linear_affine_b4(scr_ctx*, const void*, const uint16_t*, int32_t, int32_t, int32_t, int32_t, uint16_t*,
-                                        void*, size_t, void*);
-extern "C" int32_t scr_linear_fp8(scr_ctx*, const void*, const void*, int32_t, int32_t, int32_t, uint16_t*, void*, size_t, void*);
-
-extern "C" int32_t scr_linear_affine_b4_partial(scr_ctx* ctx, const void* packed, const uint16_t* x, int32_t M, int32_t N,
-                                                int32_t K, int32_t group, float* y_f32, void* workspace,
-                                                size_t workspace_bytes, void* stream) {
-    if (!ctx) return SCR_E_ARG;
-    ctx->out_f32 = 1;
-    const int32_t st = scr_linear_affine_b4(ctx, packed, x, M, N, K, group, reinterpret_cast<uint16_t*>(y_f32), workspace,
-                                            workspace_bytes, stream);
-    ctx->out_f32 = 0;
-    return st;
-}
-
-extern "C" int32_t scr_linear_fp8_partial(scr_ctx* ctx, const void* packed, const void* act, int32_t M, int32_t N, int32_t K,
-                                          float* y_f32, void* workspace, size_t workspace_bytes, void* stream) {
-    if (!ctx) return SCR_E_ARG;
-    ctx->out_f32 = 1;
-    const int32_t st = scr_linear_fp8(ctx, packed, act, M, N, K, reinterpret_cast<uint16_t*>(y_f32), workspace, workspace_bytes,
-                                      stream);
-    ctx->out_f32 = 0;
-    return st;
-}
-
-extern "C" int32_t scr_linear_fp8_dynamic(scr_ctx*, const void*, const uint16_t*, int32_t, int32_t, int32_t, uint16_t*, void*, size_t,
-                                          void*);
-
-extern "C" int32_t scr_linear_fp8_dynamic_partial(scr_ctx* ctx, const void* packed, const uint16_t* x, int32_t M, int32_t N,
-                                                  int32_t K, float* y_f32, void* workspace, size_t workspace_bytes,
-                                                  void* stream) {
-    if (!ctx) return SCR_E_ARG;
-    ctx->out_f32 = 1;
-    const int32_t st = scr_linear_fp8_dynamic(ctx, packed, x, M, N, K, reinterpret_cast<uint16_t*>(y_f32), workspace,
-                                              workspace_bytes, stream);
-    ctx->out_f32 = 0;
-    return st;
-}
-
 __global__ void partial_to_bf16_kernel(const float* __restrict__ in, long long count, uint16_t* __restrict__ out) {
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
         const __nv_bfloat16 v = __float2bfloat16_rn(in[i]);

@@ -1,5 +1,6 @@
 // MLX affine int4 (group 64): load-time repack, dequant dump hook and the decode matvec.
 #include "affine_b4.cuh"
+#include "gemv_common.cuh"
 
 #include <algorithm>
 #include <new>
@@ -110,58 +111,6 @@ __global__ void affine_b4_dump_kernel(const uint8_t* __restrict__ packed, int N,
     }
 }
 
-// ---- small PTX helpers for the matvec kernels ------------------------------------------
-__device__ __forceinline__ uint32_t gemv_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void gemv_mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void gemv_fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
-__device__ __forceinline__ void gemv_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void gemv_bulk_g2s(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
-// Bounded wait on a stage barrier: gives up after 2^20 polls (or as soon as another waiter has
-// recorded a failure), records code 6 in the status word and lets the kernel run to its end.
-__device__ __forceinline__ void gemv_wait(uint32_t bar, uint32_t parity, int* status) {
-#pragma unroll 1
-    for (uint32_t i = 0; i < (1u << 20); ++i) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return;
-        if ((i & 255u) == 255u && *reinterpret_cast<volatile int*>(status) != 0) return;
-    }
-    atomicCAS(status, 0, 6);
-}
-__device__ __forceinline__ uint4 gemv_lds_v4(uint32_t addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ uint2 gemv_lds_v2(uint32_t addr) {
-    uint2 v;
-    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ uint32_t gemv_cluster_ctarank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ void gemv_cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void gemv_st_cluster_rank0_f32(const float* local_ptr, float v) {
-    const uint32_t local = (uint32_t)__cvta_generic_to_shared(local_ptr);
-    uint32_t remote;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(0));
-    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
-}
-
 // ------------------------------------------------------------------------------------
 // Decode matvec, M <= 16.
 //
@@ -181,94 +130,6 @@ __device__ __forceinline__ void gemv_st_cluster_rank0_f32(const float* local_ptr
 // cluster that splits the k extent and reduces through distributed shared memory in rank
 // order.  Every wait is bounded (gemv_wait).
 // ------------------------------------------------------------------------------------
-__device__ __forceinline__ void mma_bf16_16816(float d[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                               uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void gemv_mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void gemv_consumer_sync() {          // the 8 consumer warps only
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-}
-
-#define GEMV_CWARPS 8
-#define GEMV_THREADS ((GEMV_CWARPS + 1) * 32)
-#define GEMV_STAGES 4
-#define GEMV_STAGE_BYTES (GEMV_CWARPS * AFF_BLOCK_BYTES)
-#define GEMV_MAX_SPLIT 8
-
-// One 1152-byte block from shared memory against pre-loaded activations (xv: this lane's 32
-// activations per token tile, in k order).
-template <int MT, bool CHECK>
-__device__ __forceinline__ void gemv_block_compute(uint32_t blk, float acc[2][MT][4], const uint4 xv[MT][4], int lane) {
-    const uint4 p0 = gemv_lds_v4(blk + lane * 16);
-    const uint4 p1 = gemv_lds_v4(blk + 512 + lane * 16);
-    const uint2 sb = gemv_lds_v2(blk + 1024 + ((lane >> 2) * 2 + ((lane & 3) >> 1)) * 8);
-    const uint32_t wa[4] = {p0.x, p0.y, p0.z, p0.w};
-    const uint32_t wb[4] = {p1.x, p1.y, p1.z, p1.w};
-    if (CHECK) {
-        // generic variant: per-group test for the exact path; weights unscaled
-        const uint32_t s2a = __byte_perm(sb.x, sb.x, 0x1010), b2a = __byte_perm(sb.x, sb.x, 0x3232);
-        const uint32_t s2b = __byte_perm(sb.y, sb.y, 0x1010), b2b = __byte_perm(sb.y, sb.y, 0x3232);
-        const bool slow_a = affine_slow_group(sb.x);
-        const bool slow_b = affine_slow_group(sb.y);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            uint32_t w0[4], w1[4];
-            affine_dequant_word<true>(wa[i], sb.x, s2a, b2a, slow_a, w0);
-            affine_dequant_word<true>(wb[i], sb.y, s2b, b2b, slow_b, w1);
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                mma_bf16_16816(acc[0][mt], w0[0], w1[0], w0[1], w1[1], xv[mt][i].x, xv[mt][i].y);
-                mma_bf16_16816(acc[1][mt], w0[2], w1[2], w0[3], w1[3], xv[mt][i].z, xv[mt][i].w);
-            }
-        }
-    } else {
-        // scaled variant: weights carry a factor 2^-7 that the caller removes from the accumulators
-        const AffineScaled ca = affine_scaled_consts(sb.x);
-        const AffineScaled cb = affine_scaled_consts(sb.y);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            uint32_t w0[4], w1[4];
-            affine_dequant_word_scaled(wa[i], ca, w0);
-            affine_dequant_word_scaled(wb[i], cb, w1);
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                // two independent accumulator sets halve the dependent-MMA chain
-                mma_bf16_16816(acc[0][mt], w0[0], w1[0], w0[1], w1[1], xv[mt][i].x, xv[mt][i].y);
-                mma_bf16_16816(acc[1][mt], w0[2], w1[2], w0[3], w1[3], xv[mt][i].z, xv[mt][i].w);
-            }
-        }
-    }
-}
-
-// Output modes of the matvec epilogue (the `out_f32` argument): bf16, unrounded f32 partials, or the
-// gate/up pairing: the matrix holds, per 16-row block, 8 gate rows then the 8 up rows of the same
-// channels (the loader's `load_rows_interleave8`), so gate_i and up_i end up in the same lane two
-// accumulator slots apart; the lane holding the gate sum takes the up sum by shuffle and stores
-// bf16(silu(bf16(gate)) * bf16(up)) — the value the separate silu*up kernel computes from the two
-// bf16 outputs (crates/targets/metal/src/cpu_golden.rs:211-219), one launch saved.
-#define GEMV_OUT_BF16 0
-#define GEMV_OUT_F32 1
-#define GEMV_OUT_SILU_PAIRS 2
-
-// Called by all 32 lanes of a warp.  `total` is this lane's (row, token) sum; bit 1 of `idx` says
-// whether the row is a gate row (0) or the up row 8 below it (1).
-__device__ __forceinline__ void gemv_store_silu_pair(float total, int idx, int tok, int M, int channel, int channels,
-                                                     uint16_t* __restrict__ y) {
-    const float other = __shfl_xor_sync(0xffffffffu, total, 2);
-    if ((idx & 2) == 0 && tok < M && channel < channels) {
-        const float g = __bfloat162float(__float2bfloat16_rn(total));
-        const float u = __bfloat162float(__float2bfloat16_rn(other));
-        const __nv_bfloat16 v = __float2bfloat16_rn(__fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u));
-        y[(size_t)tok * channels + channel] = *reinterpret_cast<const uint16_t*>(&v);
-    }
-}
-
 // GEMV_OUT_RESIDUAL_NORM: the o / down projection with the ends the reference folds around its matvec
 // (`QmvEnds`, crates/targets/metal/src/tape/step.rs:472-482), i.e. `fused_add_rmsnorm`
 // (crates/targets/metal/src/cpu_golden.rs:171-200) without a kernel of its own:
@@ -347,10 +208,19 @@ __device__ __forceinline__ void gemv_norm_tail(float my_sq, int M, int N, int nc
     }
 }
 
+// Activations the preceding kernel of the stream (or, in the tape, another CTA of this launch) has written: an ordinary
+// (coherent, L1-allocating) load — never the read-only path, whose contract is data that stays constant for the
+// kernel's lifetime, and this kernel is alive before its producer has finished.
+__device__ __forceinline__ uint4 tape_ld_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
 template <int MT, int SPLIT_CLUSTER, bool CHECK>
 __device__ __forceinline__ void gemv_consumer(const uint16_t* __restrict__ x, uint16_t* __restrict__ y, int M, int N,
                                               int K, int kc_lo, int kc_hi, int nstage, int rb_real, int split, int sp,
-                                              int out_f32, int* __restrict__ status, uint32_t ring_base, uint32_t full_base,
+                                              int out_f32, const uint16_t* __restrict__ bias, int* __restrict__ status, uint32_t ring_base, uint32_t full_base,
                                               uint32_t empty_base, float (*red)[GEMV_CWARPS][32][MT * 4],
                                               float (*cl_part)[16][MT * 8], const GemvEnds& ends, float (*sq_s)[16][16]) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -385,7 +255,7 @@ __device__ __forceinline__ void gemv_consumer(const uint16_t* __restrict__ x, ui
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) xv[mt][i] = ld_nc_v4(xrow[mt] + k0 + 8 * i);
+                for (int i = 0; i < 4; ++i) xv[mt][i] = tape_ld_v4(xrow[mt] + k0 + 8 * i);      // coherent: the preceding kernel wrote x
             gemv_wait(full_base + 8u * slot, (n_it / GEMV_STAGES) & 1u, status);
             if (active) gemv_block_compute<MT, CHECK>(ring_base + slot * GEMV_STAGE_BYTES + warp * AFF_BLOCK_BYTES, acc, xv, lane);
             __syncwarp();                                         // every lane has consumed the stage
@@ -419,6 +289,7 @@ __device__ __forceinline__ void gemv_consumer(const uint16_t* __restrict__ x, ui
             } else if (out_f32 == GEMV_OUT_RESIDUAL_NORM) {
                 sq_s[buf][tok][row] = gemv_residual_update(total, tok, M, n, N, ends);
             } else if (tok < M && n < N) {
+                if (bias) total += __uint_as_float(uint32_t(bias[n]) << 16);
                 if (out_f32) {
                     reinterpret_cast<float*>(y)[(size_t)tok * N + n] = total;
                 } else {
@@ -443,7 +314,7 @@ template <int MT, int SPLIT_CLUSTER>
 __global__ void __launch_bounds__(GEMV_THREADS, (MT == 1 ? 3 : 2))
 affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __restrict__ x, uint16_t* __restrict__ y,
                       int M, int N, int K, int RB, int KC, int rb_real, int split, int out_f32,
-                      int* __restrict__ status, GemvEnds ends) {
+                      const uint16_t* __restrict__ bias, int* __restrict__ status, GemvEnds ends) {
     extern __shared__ __align__(128) uint8_t gemv_ring[];          // [GEMV_STAGES][8 blocks]
     __shared__ float sq_s[2][16][16];                              // RESIDUAL_NORM: squares of the stored residuals [token][row]
     __shared__ __align__(8) uint64_t full_bar[GEMV_STAGES];
@@ -500,10 +371,10 @@ affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __rest
         asm volatile("griddepcontrol.wait;" ::: "memory");        // x (and y's previous readers) are settled
         const bool check = trailer_flag != 0;
         if (check)
-            gemv_consumer<MT, SPLIT_CLUSTER, true>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, out_f32, status, ring_base,
+            gemv_consumer<MT, SPLIT_CLUSTER, true>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, out_f32, bias, status, ring_base,
                                                    full_base, empty_base, red, cl_part, ends, sq_s);
         else
-            gemv_consumer<MT, SPLIT_CLUSTER, false>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, out_f32, status, ring_base,
+            gemv_consumer<MT, SPLIT_CLUSTER, false>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, out_f32, bias, status, ring_base,
                                                     full_base, empty_base, red, cl_part, ends, sq_s);
     }
 
@@ -539,6 +410,7 @@ affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __rest
         } else if (sp == 0 && e < SLOTS && tok < M && n < N) {
             float s = 0.f;
             for (int r = 0; r < split; ++r) s += cl_part[r][row][tok];
+            if (bias) s += __uint_as_float(uint32_t(bias[n]) << 16);
             if (out_f32) {
                 reinterpret_cast<float*>(y)[(size_t)tok * N + n] = s;
             } else {
@@ -629,9 +501,17 @@ static void affine_gemv_shape(int rb_real, int KC, int sms, int* grid_x, int* sp
     *split = best;
 }
 
+// What a forward call asks of the epilogue, passed down as an argument (never parked in the context: a
+// context may serve two streams).
+struct AffineFwd {
+    int out_mode = GEMV_OUT_BF16;            // GEMV_OUT_*
+    const uint16_t* bias = nullptr;          // the linear's own bias [N] (bf16), added in f32 before the one rounding
+    const GemvEnds* ends = nullptr;          // GEMV_OUT_RESIDUAL_NORM only
+};
+
 template <int MT>
 static int32_t affine_gemv_launch(scr_ctx* ctx, const uint8_t* packed, const uint16_t* x, uint16_t* y, int M, int N,
-                                  int K, cudaStream_t stream) {
+                                  int K, const AffineFwd& f, cudaStream_t stream) {
     const AffineGeom g = affine_geom(N, K);
     const int rb_real = scr_ceil_div(N, 16);
     int grid_x = 1, split = 1;
@@ -660,20 +540,21 @@ static int32_t affine_gemv_launch(scr_ctx* ctx, const uint8_t* packed, const uin
     cfg.attrs = attr;
     cfg.numAttrs = na;
     GemvEnds ends = {};
-    if (ctx->out_f32 == GEMV_OUT_RESIDUAL_NORM) {
-        if (!ctx->gemv_ends) return scr_fail(ctx, SCR_E_ARG, "residual + norm epilogue requested without its arguments");
-        ends = *static_cast<const GemvEnds*>(ctx->gemv_ends);
+    if (f.out_mode == GEMV_OUT_RESIDUAL_NORM) {
+        if (!f.ends) return scr_fail(ctx, SCR_E_ARG, "residual + norm epilogue requested without its arguments");
+        ends = *f.ends;
         if ((size_t)(16 + grid_x * 16) * sizeof(float) > SCR_ENDS_SCRATCH_BYTES)
             return scr_fail(ctx, SCR_E_WORKSPACE, "residual + norm epilogue: %d CTAs exceed the scratch", grid_x);
     }
-    e = cudaLaunchKernelEx(&cfg, kernel, packed, x, y, M, N, K, g.RB, g.KC, rb_real, split, ctx->out_f32, ctx->dev_status, ends);
+    e = cudaLaunchKernelEx(&cfg, kernel, packed, x, y, M, N, K, g.RB, g.KC, rb_real, split, f.out_mode, f.bias, ctx->dev_status, ends);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine_b4_gemv launch: %s", cudaGetErrorString(e));
     return scr_check_launch(ctx, "affine_b4_gemv");
 }
 
 // Defined in affine_b4_gemm.cu
 int32_t affine_b4_gemm_tc_launch(scr_ctx* ctx, const uint8_t* packed, const uint16_t* x, uint16_t* y, int M, int N,
-                                 int K, void* workspace, size_t workspace_bytes, cudaStream_t stream);
+                                 int K, int out_f32, const uint16_t* bias, void* workspace, size_t workspace_bytes,
+                                 cudaStream_t stream);
 size_t affine_b4_gemm_tc_workspace(int M, int N, int K);
 bool affine_b4_gemm_tc_enabled();
 
@@ -682,33 +563,61 @@ size_t affine_workspace_bytes(int M, int N, int K) {
     return affine_b4_gemm_tc_workspace(M, N, K);
 }
 
-extern "C" int32_t scr_linear_affine_b4(scr_ctx* ctx, const void* packed, const uint16_t* x, int32_t M, int32_t N,
-                                        int32_t K, int32_t group, uint16_t* y, void* workspace, size_t workspace_bytes,
-                                        void* stream_) {
-    SCR_REQUIRE_CTX(ctx);
-    if (!packed || !x || !y) return scr_fail(ctx, SCR_E_ARG, "null pointer");
+// The forward dispatch every int4 entry point goes through: the balanced matvec up to 8 tokens, the
+// two-tile matvec up to 16, the tensor-core GEMM above.
+static int32_t affine_forward(scr_ctx* ctx, const void* packed, const uint16_t* x, int M, int N, int K, int group, void* y_,
+                              const AffineFwd& f, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+    if (!packed || !x || !y_) return scr_fail(ctx, SCR_E_ARG, "null pointer");
     int32_t st = affine_check_shape(ctx, N, K, group);
     if (st) return st;
     if (M <= 0) return scr_fail(ctx, SCR_E_SHAPE, "M=%d must be positive", M);
     if (!scr_aligned16(packed) || !scr_aligned16(x)) return scr_fail(ctx, SCR_E_ALIGN, "packed/x must be 16-byte aligned");
-    cudaStream_t stream = (cudaStream_t)stream_;
+    if (f.bias && (f.out_mode == GEMV_OUT_SILU_PAIRS || f.out_mode == GEMV_OUT_RESIDUAL_NORM))
+        return scr_fail(ctx, SCR_E_UNSUPPORTED, "a linear bias cannot be combined with this fused epilogue");
     const uint8_t* pk = (const uint8_t*)packed;
-    if (M <= 8) return affine_gemv_launch<1>(ctx, pk, x, y, M, N, K, stream);
-    if (M <= 16) return affine_gemv_launch<2>(ctx, pk, x, y, M, N, K, stream);
+    uint16_t* y = static_cast<uint16_t*>(y_);
+    if (M <= 8) return affine_gemv_launch<1>(ctx, pk, x, y, M, N, K, f, stream);
+    if (M <= 16) return affine_gemv_launch<2>(ctx, pk, x, y, M, N, K, f, stream);
+    if (f.out_mode != GEMV_OUT_BF16 && f.out_mode != GEMV_OUT_F32)
+        return scr_fail(ctx, SCR_E_UNSUPPORTED, "this fused epilogue exists on the matvec path only (M <= 16)");
     if (affine_b4_gemm_tc_enabled()) {
         const size_t need = affine_b4_gemm_tc_workspace(M, N, K);
         if (need > 0 && (!workspace || workspace_bytes < need))
             return scr_fail(ctx, SCR_E_WORKSPACE, "workspace %zu bytes < required %zu", workspace_bytes, need);
-        return affine_b4_gemm_tc_launch(ctx, pk, x, y, M, N, K, workspace, workspace_bytes, stream);
+        return affine_b4_gemm_tc_launch(ctx, pk, x, y, M, N, K, f.out_mode == GEMV_OUT_F32, f.bias, workspace, workspace_bytes, stream);
     }
     // Token tiles of 16 through the matvec kernel (weights re-streamed per tile).
+    const size_t ystride = f.out_mode == GEMV_OUT_F32 ? 2 : 1;
     for (int m0 = 0; m0 < M; m0 += 16) {
         const int mt = std::min(16, M - m0);
-        st = (mt <= 8) ? affine_gemv_launch<1>(ctx, pk, x + (size_t)m0 * K, y + (size_t)m0 * N, mt, N, K, stream)
-                       : affine_gemv_launch<2>(ctx, pk, x + (size_t)m0 * K, y + (size_t)m0 * N, mt, N, K, stream);
+        uint16_t* yt = y + (size_t)m0 * N * ystride;
+        st = (mt <= 8) ? affine_gemv_launch<1>(ctx, pk, x + (size_t)m0 * K, yt, mt, N, K, f, stream)
+                       : affine_gemv_launch<2>(ctx, pk, x + (size_t)m0 * K, yt, mt, N, K, f, stream);
         if (st) return st;
     }
     return SCR_OK;
+}
+
+extern "C" int32_t scr_linear_affine_b4(scr_ctx* ctx, const void* packed, const uint16_t* x, int32_t M, int32_t N,
+                                        int32_t K, int32_t group, const uint16_t* bias, uint16_t* y, void* workspace,
+                                        size_t workspace_bytes, void* stream_) {
+    SCR_REQUIRE_CTX(ctx);
+    AffineFwd f;
+    f.bias = bias;
+    return affine_forward(ctx, packed, x, M, N, K, group, y, f, workspace, workspace_bytes, (cudaStream_t)stream_);
+}
+
+// A row-parallel linear (o, down) yields a `Partial` in the reference's placement lattice
+// (crates/compiler/subtile/src/tensor_parallel.rs:1-63): unrounded f32 sums over the rank's K-slice, to be
+// summed over ranks by the all-reduce and rounded to bf16 once afterwards (the bias, if any, is added after
+// the sum by whoever rounds).
+extern "C" int32_t scr_linear_affine_b4_partial(scr_ctx* ctx, const void* packed, const uint16_t* x, int32_t M, int32_t N,
+                                                int32_t K, int32_t group, float* y_f32, void* workspace,
+                                                size_t workspace_bytes, void* stream_) {
+    SCR_REQUIRE_CTX(ctx);
+    AffineFwd f;
+    f.out_mode = GEMV_OUT_F32;
+    return affine_forward(ctx, packed, x, M, N, K, group, y_f32, f, workspace, workspace_bytes, (cudaStream_t)stream_);
 }
 
 extern "C" int32_t scr_linear_affine_b4_residual_rmsnorm(scr_ctx* ctx, const void* packed, const uint16_t* x, int32_t M,
@@ -723,15 +632,12 @@ extern "C" int32_t scr_linear_affine_b4_residual_rmsnorm(scr_ctx* ctx, const voi
         return scr_fail(ctx, SCR_E_WORKSPACE, "fused residual + norm epilogue: scratch %zu bytes < %d", scratch_bytes, SCR_ENDS_SCRATCH_BYTES);
     if (!scr_aligned16(residual) || !scr_aligned16(gain) || !scr_aligned16(normed) || !scr_aligned16(scratch))
         return scr_fail(ctx, SCR_E_ALIGN, "fused residual + norm epilogue: pointers must be 16-byte aligned");
-    if (ctx->out_f32 != 0) return scr_fail(ctx, SCR_E_ARG, "fused residual + norm epilogue: another output mode is active");
     const GemvEnds ends = {residual, gain, normed, static_cast<float*>(scratch), eps};
-    ctx->out_f32 = GEMV_OUT_RESIDUAL_NORM;
-    ctx->gemv_ends = &ends;
+    AffineFwd f;
+    f.out_mode = GEMV_OUT_RESIDUAL_NORM;
+    f.ends = &ends;
     // y is not written in this mode; the residual buffer stands in for the (unused) output pointer
-    const int32_t st = scr_linear_affine_b4(ctx, packed, x, M, N, K, group, residual, nullptr, 0, stream_);
-    ctx->out_f32 = 0;
-    ctx->gemv_ends = nullptr;
-    return st;
+    return affine_forward(ctx, packed, x, M, N, K, group, residual, f, nullptr, 0, (cudaStream_t)stream_);
 }
 
 extern "C" int32_t scr_linear_affine_b4_silu_mul(scr_ctx* ctx, const void* packed, const uint16_t* x, int32_t M, int32_t N2,
@@ -739,11 +645,9 @@ extern "C" int32_t scr_linear_affine_b4_silu_mul(scr_ctx* ctx, const void* packe
     SCR_REQUIRE_CTX(ctx);
     if (M > 16) return scr_fail(ctx, SCR_E_UNSUPPORTED, "fused silu*up epilogue: M=%d (the matvec path, M <= 16, has it)", M);
     if (N2 <= 0 || N2 % 16 != 0) return scr_fail(ctx, SCR_E_SHAPE, "fused silu*up epilogue: %d fused rows (8 gate + 8 up per block)", N2);
-    if (ctx->out_f32 != 0) return scr_fail(ctx, SCR_E_ARG, "fused silu*up epilogue: partial output requested at the same time");
-    ctx->out_f32 = GEMV_OUT_SILU_PAIRS;
-    const int32_t st = scr_linear_affine_b4(ctx, packed, x, M, N2, K, group, out, nullptr, 0, stream_);
-    ctx->out_f32 = 0;
-    return st;
+    AffineFwd f;
+    f.out_mode = GEMV_OUT_SILU_PAIRS;
+    return affine_forward(ctx, packed, x, M, N2, K, group, out, f, nullptr, 0, (cudaStream_t)stream_);
 }
 
 // ------------------------------------------------------------------------------------
@@ -788,13 +692,6 @@ struct scr_tape {
     int grid[2] = {0, 0};          // co-resident CTAs: up to 8 rows, up to 16 rows
 };
 
-// Activations another CTA of this launch may have written: an ordinary (coherent, L1-allocating) load — never
-// the read-only path — issued after the job's acquire fence and the CTA barrier that follows it.
-__device__ __forceinline__ uint4 tape_ld_v4(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-    return v;
-}
 __device__ __forceinline__ void tape_red_release(unsigned int* p, unsigned int v) {
     asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }

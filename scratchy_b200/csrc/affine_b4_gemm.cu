@@ -65,7 +65,8 @@ __device__ __forceinline__ uint32_t ld_shared_u32(uint32_t addr) {
 // result, rounded once (or as f32 partials).  One CTA per (tail tile, 8 rows), one float4 per thread.
 __global__ void __launch_bounds__(256) affine_b4_gemm_tail_finish_kernel(const float* __restrict__ slabs, int ks_tail, int n_tail,
                                                                          int full, int MT, int tile_rows, int M, int N,
-                                                                         uint16_t* __restrict__ y, int out_f32) {
+                                                                         uint16_t* __restrict__ y, int out_f32,
+                                                                         const uint16_t* __restrict__ bias) {
     const int groups = tile_rows / 8;
     const int tt = blockIdx.x / groups, grp = blockIdx.x - tt * groups;
     const int tile = full + tt;
@@ -87,7 +88,7 @@ __global__ void __launch_bounds__(256) affine_b4_gemm_tail_finish_kernel(const f
         if (out_f32) {
             reinterpret_cast<float*>(y)[(size_t)m * N + n + j] = v[j];
         } else {
-            const __nv_bfloat16 o = __float2bfloat16_rn(v[j]);
+            const __nv_bfloat16 o = __float2bfloat16_rn(bias ? v[j] + __uint_as_float(uint32_t(bias[n + j]) << 16) : v[j]);
             y[(size_t)m * N + n + j] = *reinterpret_cast<const uint16_t*>(&o);
         }
     }
@@ -97,7 +98,8 @@ template <int TM>
 __global__ void __launch_bounds__(A4G_THREADS, 1)
 affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_t* __restrict__ packed,
                          uint16_t* __restrict__ y, int M, int N, int RB, int KC, int MT, int out_f32,
-                         int full, int ks_tail, float* __restrict__ slabs, int* __restrict__ status) {
+                         const uint16_t* __restrict__ bias, int full, int ks_tail, float* __restrict__ slabs,
+                         int* __restrict__ status) {
     using S = A4GSmem<TM>;
     constexpr int SX = S::kSX;
     constexpr int BN = A4G_BN;
@@ -323,8 +325,13 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
                         uint32_t o[16];
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
-                            const __nv_bfloat162 pk = __floats2bfloat162_rn(__uint_as_float(r[2 * j]) * out_scale,
-                                                                             __uint_as_float(r[2 * j + 1]) * out_scale);
+                            float lo = __uint_as_float(r[2 * j]) * out_scale, hi = __uint_as_float(r[2 * j + 1]) * out_scale;
+                            if (bias) {                // the linear's own bias, added in f32 before the one rounding
+                                const int n2 = nc + 2 * j;
+                                if (n2 < N) lo += __uint_as_float(uint32_t(bias[n2]) << 16);
+                                if (n2 + 1 < N) hi += __uint_as_float(uint32_t(bias[n2 + 1]) << 16);
+                            }
+                            const __nv_bfloat162 pk = __floats2bfloat162_rn(lo, hi);
                             o[j] = *reinterpret_cast<const uint32_t*>(&pk);
                         }
                         if (vec_ok && nc + 32 <= N) {
@@ -381,7 +388,8 @@ size_t affine_b4_gemm_tc_workspace_plan(int M, int N, int K) { return affine_gem
 
 template <int TM>
 static int32_t affine_gemm_launch_tm(scr_ctx* ctx, const CUtensorMap& map, const uint8_t* packed, uint16_t* y, int M, int N,
-                                     int K, const AffineGemmPlan& p, float* slabs, cudaStream_t stream) {
+                                     int K, int out_f32, const uint16_t* bias, const AffineGemmPlan& p, float* slabs,
+                                     cudaStream_t stream) {
     const AffineGeom g = affine_geom(N, K);
     const int units = p.full + p.n_tail() * p.ks_tail;
     const int grid = std::min(units, ctx->sm_count);
@@ -389,17 +397,17 @@ static int32_t affine_gemm_launch_tm(scr_ctx* ctx, const CUtensorMap& map, const
                                          (int)A4GSmem<TM>::kTotal);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine gemm smem attribute: %s", cudaGetErrorString(e));
     affine_b4_gemm_tc_kernel<TM><<<grid, A4G_THREADS, A4GSmem<TM>::kTotal, stream>>>(map, packed, y, M, N, g.RB, g.KC, p.mt,
-                                                                                    ctx->out_f32, p.full, p.ks_tail, slabs,
+                                                                                    out_f32, bias, p.full, p.ks_tail, slabs,
                                                                                     ctx->dev_status);
     int32_t st = scr_check_launch(ctx, "affine_b4_gemm_tc");
     if (st || p.ks_tail == 1) return st;
     affine_b4_gemm_tail_finish_kernel<<<p.n_tail() * (TM * 128 / 8), 256, 0, stream>>>(slabs, p.ks_tail, p.n_tail(), p.full, p.mt,
-                                                                                       TM * 128, M, N, y, ctx->out_f32);
+                                                                                       TM * 128, M, N, y, out_f32, bias);
     return scr_check_launch(ctx, "affine_b4_gemm_tail_finish");
 }
 
 int32_t affine_b4_gemm_tc_launch(scr_ctx* ctx, const uint8_t* packed, const uint16_t* x, uint16_t* y, int M, int N, int K,
-                                 void* workspace, size_t, cudaStream_t stream) {
+                                 int out_f32, const uint16_t* bias, void* workspace, size_t, cudaStream_t stream) {
     if (((uintptr_t)packed & 127u) != 0) return scr_fail(ctx, SCR_E_ALIGN, "packed weights must be 128-byte aligned for the GEMM path");
     if (!scr_aligned16(y)) return scr_fail(ctx, SCR_E_ALIGN, "y must be 16-byte aligned");
     tc_encode_tiled_fn enc = tc_tensor_map_encoder();
@@ -415,6 +423,6 @@ int32_t affine_b4_gemm_tc_launch(scr_ctx* ctx, const uint8_t* packed, const uint
     const AffineGemmPlan plan = affine_gemm_plan(M, N, K, ctx->sm_count);
     float* slabs = reinterpret_cast<float*>(workspace);
     if (plan.ks_tail > 1 && (!slabs || !scr_aligned16(slabs))) return scr_fail(ctx, SCR_E_WORKSPACE, "split-K needs an aligned workspace");
-    if (plan.tm == 2) return affine_gemm_launch_tm<2>(ctx, map, packed, y, M, N, K, plan, slabs, stream);
-    return affine_gemm_launch_tm<1>(ctx, map, packed, y, M, N, K, plan, slabs, stream);
+    if (plan.tm == 2) return affine_gemm_launch_tm<2>(ctx, map, packed, y, M, N, K, out_f32, bias, plan, slabs, stream);
+    return affine_gemm_launch_tm<1>(ctx, map, packed, y, M, N, K, out_f32, bias, plan, slabs, stream);
 }

@@ -10,13 +10,18 @@
 
 #include "../../include/scratchy_cuda.h"
 
+// What a forward call asks of a linear's epilogue, passed down as an argument (never parked in the context: a
+// context may serve two streams).
+struct LinearEnds {
+    int out_f32 = 0;                         // unrounded f32 partial sums instead of bf16 (row-parallel linears)
+    const uint16_t* bias = nullptr;          // the linear's own bias [N] (bf16), added in f32 before the one rounding
+};
+
 struct scr_ctx {
     int device = 0;
     int sm_count = 0;
     int cc_major = 0, cc_minor = 0;
     std::atomic<long long> launches{0};
-    int out_f32 = 0;                // output mode of the matvec epilogue, set by the variant entry points for one call
-    const void* gemv_ends = nullptr;    // arguments of the residual + norm epilogue for the same call
     int* dev_status = nullptr;      // device word: first bounded wait that ran out (0 = none)
     char err[256] = {0};
 };
@@ -60,7 +65,15 @@ __device__ __forceinline__ uint2 ld_stream_v2(const void* p) {
     asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
     return v;
 }
-// Cached read-only 128-bit load (activations, re-read by every warp).
+// Activations: an ordinary (coherent, L1-allocating) 128-bit load.  They are written by the preceding kernel of the
+// stream, and under programmatic dependent launch the reading kernel is alive before that kernel has finished, so
+// the read-only path (whose contract is data constant for the kernel's lifetime) is not used for them.
+__device__ __forceinline__ uint4 ld_act_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+// Cached read-only 128-bit load: load-time constants only (norm gains, tables).
 __device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
     uint4 v;
     asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];"

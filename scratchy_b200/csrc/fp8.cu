@@ -57,7 +57,7 @@ fp8_quant_per_token_kernel(const uint16_t* __restrict__ x, int M, int K, int til
 
     float amax = 0.f;
     for (int v = threadIdx.x; v < nvec; v += QUANT_THREADS) {
-        const uint4 q = ld_nc_v4(xr + v * 8);
+        const uint4 q = ld_act_v4(xr + v * 8);
         const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -93,7 +93,7 @@ fp8_quant_per_token_kernel(const uint16_t* __restrict__ x, int M, int K, int til
         for (int h = 0; h < 2; ++h) {
             const int kk = k0 + h * 8;
             if (kk < K) {                                     // K % 8 == 0: a vector is all in or all out
-                const uint4 q = ld_nc_v4(xr + kk);
+                const uint4 q = ld_act_v4(xr + kk);
                 const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -130,7 +130,7 @@ fp8_rmsnorm_quant_kernel(const uint16_t* __restrict__ x, const uint16_t* __restr
 
     float sq = 0.f;
     for (int v = threadIdx.x; v < nvec; v += QUANT_THREADS) {
-        const uint4 q = ld_nc_v4(xr + v * 8);
+        const uint4 q = ld_act_v4(xr + v * 8);
         const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -154,7 +154,7 @@ fp8_rmsnorm_quant_kernel(const uint16_t* __restrict__ x, const uint16_t* __restr
 
     float amax = 0.f;
     for (int v = threadIdx.x; v < nvec; v += QUANT_THREADS) {
-        const uint4 q = ld_nc_v4(xr + v * 8);
+        const uint4 q = ld_act_v4(xr + v * 8);
         const uint4 gq = ld_nc_v4(gain + v * 8);
         const uint32_t w[4] = {q.x, q.y, q.z, q.w}, gw[4] = {gq.x, gq.y, gq.z, gq.w};
         uint32_t ow[4];
@@ -330,7 +330,8 @@ template <int MT, int SPLIT_CLUSTER, int FUSE_Q, int EXCH>
 __global__ void __launch_bounds__(F8V_THREADS, (MT == 1 ? 3 : 2))
 fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_scale, const uint8_t* __restrict__ xq,
                 const float* __restrict__ a_scale, const uint16_t* __restrict__ x_bf16, int K, uint16_t* __restrict__ y, int M,
-                int N, int K16, int KT, int rb_real, int split, int out_f32, int* __restrict__ status, TpcExchange ex) {
+                int N, int K16, int KT, int rb_real, int split, int out_f32, const uint16_t* __restrict__ bias,
+                int* __restrict__ status, TpcExchange ex) {
     extern __shared__ __align__(128) uint8_t f8v_ring[];           // [F8V_STAGES][8 blocks of 2 KB] (+ x_q [M][K16] when FUSE_Q)
     __shared__ __align__(8) uint64_t full_bar[F8V_STAGES];
     __shared__ __align__(8) uint64_t empty_bar[F8V_STAGES];
@@ -403,7 +404,7 @@ fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_s
                 const uint16_t* xr = x_bf16 + (size_t)m * K;
                 float amax = 0.f;
                 for (int v = tid; v < K / 8; v += F8V_CWARPS * 32) {
-                    const uint4 q = ld_nc_v4(xr + v * 8);
+                    const uint4 q = ld_act_v4(xr + v * 8);
                     const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
@@ -428,7 +429,7 @@ fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_s
                     for (int h = 0; h < 2; ++h) {
                         const int kk = k0 + h * 8;
                         if (kk < K) {
-                            const uint4 q = ld_nc_v4(xr + kk);
+                            const uint4 q = ld_act_v4(xr + kk);
                             const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
                             for (int i = 0; i < 4; ++i) {
@@ -488,8 +489,8 @@ fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_s
                         xlo[mt] = f8v_lds_v4(xrow_s[mt] + klo);
                         xhi[mt] = f8v_lds_v4(xrow_s[mt] + khi);
                     } else {
-                        xlo[mt] = ld_nc_v4(xrow[mt] + klo);
-                        xhi[mt] = ld_nc_v4(xrow[mt] + khi);
+                        xlo[mt] = ld_act_v4(xrow[mt] + klo);
+                        xhi[mt] = ld_act_v4(xrow[mt] + khi);
                     }
                 }
                 f8v_wait(full_base + 8u * slot, (n_it / F8V_STAGES) & 1u, status);
@@ -519,7 +520,8 @@ fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_s
                     fp8_st_cluster_rank0_f32(&cl_part[sp][row][tok], total);
                 } else if (n < N) {
                     // (raw * a_scale[m]) * w_scale[n], in that order (ktir_matmul_fp8.rs:676-712)
-                    const float o = __fmul_rn(__fmul_rn(total, a_scale_eff[tok]), ws_mine);
+                    float o = __fmul_rn(__fmul_rn(total, a_scale_eff[tok]), ws_mine);
+                    if (!EXCH && bias) o += __uint_as_float(uint32_t(bias[n]) << 16);      // the linear's own bias, before the one rounding
                     if (EXCH) {
                         const unsigned int e_call = s_epoch;
                         const long long at = tpc_slot(e_call, ex.world, ex.rank, ex.max_elems, (long long)tok * N + n);
@@ -547,7 +549,8 @@ fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_s
         if (sp == 0 && e < SLOTS && tok < M && n < N) {
             float s = 0.f;
             for (int r = 0; r < split; ++r) s += cl_part[r][row][tok];
-            const float o = __fmul_rn(__fmul_rn(s, (FUSE_Q ? q_scale : a_scale)[tok]), ws_final);
+            float o = __fmul_rn(__fmul_rn(s, (FUSE_Q ? q_scale : a_scale)[tok]), ws_final);
+            if (!EXCH && bias) o += __uint_as_float(uint32_t(bias[n]) << 16);
             if (EXCH) {
                 const unsigned int e_call = s_epoch;
                 const long long at = tpc_slot(e_call, ex.world, ex.rank, ex.max_elems, (long long)tok * N + n);
@@ -591,7 +594,7 @@ fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_s
 // ------------------------------------------------------------------------------------
 // Defined in fp8_gemm.cu
 int32_t fp8_gemm_tc_launch(scr_ctx* ctx, const uint8_t* wpack, const uint8_t* act, uint16_t* y, int M, int N, int K,
-                           void* workspace, size_t workspace_bytes, cudaStream_t stream);
+                           const LinearEnds& ends, void* workspace, size_t workspace_bytes, cudaStream_t stream);
 size_t fp8_gemm_tc_workspace(int M, int N, int K);
 
 static int32_t fp8_check_shape(scr_ctx* ctx, int N, int K) {
@@ -716,7 +719,7 @@ static bool fp8_gemv_fuses_quant(int M, int K) {
 
 template <int MT>
 static int32_t fp8_gemv_launch(scr_ctx* ctx, const uint8_t* wpack, const uint8_t* xq, const float* a_scale, uint16_t* y,
-                               int M, int N, int K, cudaStream_t stream, const uint16_t* x_bf16 = nullptr,
+                               int M, int N, int K, const LinearEnds& ends, cudaStream_t stream, const uint16_t* x_bf16 = nullptr,
                                const TpcExchange* exchange = nullptr) {
     const Fp8Geom g = fp8_geom(N, K);
     const float* w_scale = reinterpret_cast<const float*>(wpack + (size_t)g.NT * g.KT * FP8_TILE_BYTES);
@@ -760,8 +763,8 @@ static int32_t fp8_gemv_launch(scr_ctx* ctx, const uint8_t* wpack, const uint8_t
             return scr_fail(ctx, SCR_E_UNSUPPORTED, "fp8 matvec + exchange: %d CTAs cannot all be resident", grid_x * split);
         ex = *exchange;
     }
-    e = cudaLaunchKernelEx(&cfg, kernel, wpack, w_scale, xq, a_scale, x_bf16, K, y, M, N, K16, g.KT, rb_real, split, ctx->out_f32,
-                           ctx->dev_status, ex);
+    e = cudaLaunchKernelEx(&cfg, kernel, wpack, w_scale, xq, a_scale, x_bf16, K, y, M, N, K16, g.KT, rb_real, split, ends.out_f32,
+                           ends.bias, ctx->dev_status, ex);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "fp8_gemv launch: %s", cudaGetErrorString(e));
     return scr_check_launch(ctx, "fp8_gemv");
 }
@@ -774,51 +777,56 @@ size_t fp8_workspace_bytes(int M, int N, int K) {
 }
 
 static int32_t fp8_linear_from_pack(scr_ctx* ctx, const uint8_t* wpack, const uint8_t* act, int M, int N, int K,
-                                    uint16_t* y, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+                                    uint16_t* y, const LinearEnds& ends, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+    // every path below streams the weight pack with bulk copies and reads the activation pack 16 bytes at a time: a
+    // misaligned pointer is refused here, on the host, and never reaches a kernel
+    if (!scr_aligned16(wpack) || !scr_aligned16(act)) return scr_fail(ctx, SCR_E_ALIGN, "weight pack and activation pack must be 16-byte aligned");
+    if (ends.bias && ends.out_f32) return scr_fail(ctx, SCR_E_ARG, "a bias is added after the partial sums have been reduced, not to a partial");
     const float* a_scale = reinterpret_cast<const float*>(act);
     const uint8_t* xq = act + fp8_act_scale_bytes(M);
-    if (M <= 8) return fp8_gemv_launch<1>(ctx, wpack, xq, a_scale, y, M, N, K, stream);
-    if (M <= 16) return fp8_gemv_launch<2>(ctx, wpack, xq, a_scale, y, M, N, K, stream);
-    if (fp8_act_tiled(M)) return fp8_gemm_tc_launch(ctx, wpack, act, y, M, N, K, workspace, workspace_bytes, stream);
+    if (M <= 8) return fp8_gemv_launch<1>(ctx, wpack, xq, a_scale, y, M, N, K, ends, stream);
+    if (M <= 16) return fp8_gemv_launch<2>(ctx, wpack, xq, a_scale, y, M, N, K, ends, stream);
+    if (fp8_act_tiled(M)) return fp8_gemm_tc_launch(ctx, wpack, act, y, M, N, K, ends, workspace, workspace_bytes, stream);
     const int K16 = scr_ceil_div(K, 16) * 16;
+    const size_t ystride = ends.out_f32 ? 2 : 1;
     for (int m0 = 0; m0 < M; m0 += 16) {
         const int mt = std::min(16, M - m0);
+        uint16_t* yt = y + (size_t)m0 * N * ystride;
         int32_t st = (mt <= 8)
-            ? fp8_gemv_launch<1>(ctx, wpack, xq + (size_t)m0 * K16, a_scale + m0, y + (size_t)m0 * N, mt, N, K, stream)
-            : fp8_gemv_launch<2>(ctx, wpack, xq + (size_t)m0 * K16, a_scale + m0, y + (size_t)m0 * N, mt, N, K, stream);
+            ? fp8_gemv_launch<1>(ctx, wpack, xq + (size_t)m0 * K16, a_scale + m0, yt, mt, N, K, ends, stream)
+            : fp8_gemv_launch<2>(ctx, wpack, xq + (size_t)m0 * K16, a_scale + m0, yt, mt, N, K, ends, stream);
         if (st) return st;
     }
     return SCR_OK;
 }
 
-extern "C" int32_t scr_linear_fp8(scr_ctx* ctx, const void* packed, const void* act, int32_t M, int32_t N, int32_t K,
-                                  uint16_t* y, void* workspace, size_t workspace_bytes, void* stream) {
-    SCR_REQUIRE_CTX(ctx);
+static int32_t fp8_linear(scr_ctx* ctx, const void* packed, const void* act, int M, int N, int K, void* y, const LinearEnds& ends,
+                          void* workspace, size_t workspace_bytes, cudaStream_t stream) {
     if (!packed || !act || !y) return scr_fail(ctx, SCR_E_ARG, "null pointer");
     int32_t st = fp8_check_shape(ctx, N, K);
     if (st) return st;
     if (M <= 0) return scr_fail(ctx, SCR_E_SHAPE, "M=%d must be positive", M);
-    if (!scr_aligned16(packed) || !scr_aligned16(act)) return scr_fail(ctx, SCR_E_ALIGN, "packed/act must be 16-byte aligned");
     if (fp8_act_tiled(M)) {
         const size_t need = fp8_gemm_tc_workspace(M, N, K);
         if (need > 0 && (!workspace || workspace_bytes < need))
             return scr_fail(ctx, SCR_E_WORKSPACE, "workspace %zu bytes < required %zu", workspace_bytes, need);
     }
-    return fp8_linear_from_pack(ctx, (const uint8_t*)packed, (const uint8_t*)act, M, N, K, y, workspace, workspace_bytes,
-                                (cudaStream_t)stream);
+    return fp8_linear_from_pack(ctx, (const uint8_t*)packed, (const uint8_t*)act, M, N, K, static_cast<uint16_t*>(y), ends, workspace,
+                                workspace_bytes, stream);
 }
 
-extern "C" int32_t scr_linear_fp8_dynamic(scr_ctx* ctx, const void* packed, const uint16_t* x, int32_t M, int32_t N,
-                                          int32_t K, uint16_t* y, void* workspace, size_t workspace_bytes, void* stream) {
-    SCR_REQUIRE_CTX(ctx);
+static int32_t fp8_linear_dynamic(scr_ctx* ctx, const void* packed, const uint16_t* x, int M, int N, int K, void* y,
+                                  const LinearEnds& ends, void* workspace, size_t workspace_bytes, void* stream) {
     if (!packed || !x || !y) return scr_fail(ctx, SCR_E_ARG, "null pointer");
     int32_t st = fp8_check_shape(ctx, N, K);
     if (st) return st;
     if (M <= 0) return scr_fail(ctx, SCR_E_SHAPE, "M=%d must be positive", M);
+    if (!scr_aligned16(packed) || !scr_aligned16(x)) return scr_fail(ctx, SCR_E_ALIGN, "packed/x must be 16-byte aligned");
+    if (ends.bias && ends.out_f32) return scr_fail(ctx, SCR_E_ARG, "a bias is added after the partial sums have been reduced, not to a partial");
     if (fp8_gemv_fuses_quant(M, K)) {
         // few tokens: the matvec quantises the activations itself, no pack and no second launch
-        if (!scr_aligned16(packed) || !scr_aligned16(x)) return scr_fail(ctx, SCR_E_ALIGN, "packed/x must be 16-byte aligned");
-        return fp8_gemv_launch<1>(ctx, (const uint8_t*)packed, nullptr, nullptr, y, M, N, K, (cudaStream_t)stream, x);
+        return fp8_gemv_launch<1>(ctx, (const uint8_t*)packed, nullptr, nullptr, static_cast<uint16_t*>(y), M, N, K, ends,
+                                  (cudaStream_t)stream, x);
     }
     const size_t need = fp8_workspace_bytes(M, N, K);
     if (!workspace || workspace_bytes < need)
@@ -827,8 +835,44 @@ extern "C" int32_t scr_linear_fp8_dynamic(scr_ctx* ctx, const void* packed, cons
     st = scr_fp8_quant_per_token(ctx, x, M, K, workspace, stream);
     if (st) return st;
     const size_t act_bytes = (fp8_act_bytes(M, K) + 127) / 128 * 128;
-    return fp8_linear_from_pack(ctx, (const uint8_t*)packed, (const uint8_t*)workspace, M, N, K, y,
+    return fp8_linear_from_pack(ctx, (const uint8_t*)packed, (const uint8_t*)workspace, M, N, K, static_cast<uint16_t*>(y), ends,
                                 (uint8_t*)workspace + act_bytes, workspace_bytes - act_bytes, (cudaStream_t)stream);
+}
+
+extern "C" int32_t scr_linear_fp8(scr_ctx* ctx, const void* packed, const void* act, int32_t M, int32_t N, int32_t K,
+                                  const uint16_t* bias, uint16_t* y, void* workspace, size_t workspace_bytes, void* stream) {
+    SCR_REQUIRE_CTX(ctx);
+    LinearEnds ends;
+    ends.bias = bias;
+    return fp8_linear(ctx, packed, act, M, N, K, y, ends, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+extern "C" int32_t scr_linear_fp8_dynamic(scr_ctx* ctx, const void* packed, const uint16_t* x, int32_t M, int32_t N,
+                                          int32_t K, const uint16_t* bias, uint16_t* y, void* workspace, size_t workspace_bytes,
+                                          void* stream) {
+    SCR_REQUIRE_CTX(ctx);
+    LinearEnds ends;
+    ends.bias = bias;
+    return fp8_linear_dynamic(ctx, packed, x, M, N, K, y, ends, workspace, workspace_bytes, stream);
+}
+
+// Row-parallel partials (crates/compiler/subtile/src/tensor_parallel.rs:1-63): the UNROUNDED f32 sums over this
+// rank's K-slice; the all-reduce sums them over the ranks and rounds once.
+extern "C" int32_t scr_linear_fp8_partial(scr_ctx* ctx, const void* packed, const void* act, int32_t M, int32_t N, int32_t K,
+                                          float* y_f32, void* workspace, size_t workspace_bytes, void* stream) {
+    SCR_REQUIRE_CTX(ctx);
+    LinearEnds ends;
+    ends.out_f32 = 1;
+    return fp8_linear(ctx, packed, act, M, N, K, y_f32, ends, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+extern "C" int32_t scr_linear_fp8_dynamic_partial(scr_ctx* ctx, const void* packed, const uint16_t* x, int32_t M, int32_t N,
+                                                  int32_t K, float* y_f32, void* workspace, size_t workspace_bytes,
+                                                  void* stream) {
+    SCR_REQUIRE_CTX(ctx);
+    LinearEnds ends;
+    ends.out_f32 = 1;
+    return fp8_linear_dynamic(ctx, packed, x, M, N, K, y_f32, ends, workspace, workspace_bytes, stream);
 }
 
 // Row-parallel fp8 linear + all-reduce in one launch (decode sizes): see EXCH above.
@@ -850,7 +894,6 @@ extern "C" int32_t scr_linear_fp8_dynamic_allreduce(scr_tp_comm* comm, const voi
                         "fp8 matvec + exchange: M=%d K=%d is beyond the self-quantising matvec (use scr_linear_fp8_dynamic_partial "
                         "and scr_tp_allreduce_partial)", M, K);
     if (!scr_aligned16(packed) || !scr_aligned16(x)) return scr_fail(ctx, SCR_E_ALIGN, "packed/x must be 16-byte aligned");
-    if (ctx->out_f32 != 0) return scr_fail(ctx, SCR_E_ARG, "fp8 matvec + exchange: another output mode is active");
     TpcExchange ex = {};
     ex.peers = tpc_peer_table(comm);
     ex.world = comm->world;
@@ -858,7 +901,7 @@ extern "C" int32_t scr_linear_fp8_dynamic_allreduce(scr_tp_comm* comm, const voi
     ex.max_elems = comm->max_elems;
     ex.state = comm->state;
     ex.y_bf16 = y;
-    return fp8_gemv_launch<1>(ctx, (const uint8_t*)packed, nullptr, nullptr, y, M, N, K, (cudaStream_t)stream, x, &ex);
+    return fp8_gemv_launch<1>(ctx, (const uint8_t*)packed, nullptr, nullptr, y, M, N, K, LinearEnds(), (cudaStream_t)stream, x, &ex);
 }
 
 // ------------------------------------------------------------------------------------
@@ -915,6 +958,7 @@ extern "C" int32_t scr_linear_fp8_dynamic_static(scr_ctx* ctx, const void* packe
     int32_t st = fp8_check_shape(ctx, N, K);
     if (st) return st;
     if (M <= 0) return scr_fail(ctx, SCR_E_SHAPE, "M=%d must be positive", M);
+    if (!scr_aligned16(packed) || !scr_aligned16(x)) return scr_fail(ctx, SCR_E_ALIGN, "packed/x must be 16-byte aligned");
     const size_t need = fp8_workspace_bytes(M, N, K);
     if (need > (size_t)SCR_STATIC_SCRATCH_BYTES)
         return scr_fail(ctx, SCR_E_WORKSPACE,
@@ -926,6 +970,6 @@ extern "C" int32_t scr_linear_fp8_dynamic_static(scr_ctx* ctx, const void* packe
     st = scr_fp8_quant_per_token(ctx, x, M, K, scratch, stream);
     if (st) return st;
     const size_t act_bytes = (fp8_act_bytes(M, K) + 127) / 128 * 128;
-    return fp8_linear_from_pack(ctx, (const uint8_t*)packed, (const uint8_t*)scratch, M, N, K, y, (uint8_t*)scratch + act_bytes,
-                                (size_t)SCR_STATIC_SCRATCH_BYTES - act_bytes, (cudaStream_t)stream);
+    return fp8_linear_from_pack(ctx, (const uint8_t*)packed, (const uint8_t*)scratch, M, N, K, y, LinearEnds(),
+                                (uint8_t*)scratch + act_bytes, (size_t)SCR_STATIC_SCRATCH_BYTES - act_bytes, (cudaStream_t)stream);
 }

@@ -50,7 +50,7 @@ size_t fp8_gemm_tc_workspace(int M, int N, int K) { return fp8_gemm_plan(M, N, K
 // One CTA per (tail tile, 1024 / BN rows), one float4 per thread.
 __global__ void __launch_bounds__(256) fp8_gemm_tail_finish_kernel(const float* __restrict__ slabs, int ks_tail, int n_tail, int full,
                                                                    int MT, int bn, int M, int N, uint16_t* __restrict__ y,
-                                                                   int out_f32) {
+                                                                   int out_f32, const uint16_t* __restrict__ bias) {
     const int rows_per_cta = 1024 / bn;                  // 256 threads x 4 columns
     const int groups = 128 / rows_per_cta;
     const int tt = blockIdx.x / groups, grp = blockIdx.x - tt * groups;
@@ -73,7 +73,7 @@ __global__ void __launch_bounds__(256) fp8_gemm_tail_finish_kernel(const float* 
         if (out_f32) {
             reinterpret_cast<float*>(y)[(size_t)m * N + n + j] = v[j];
         } else {
-            const __nv_bfloat16 o = __float2bfloat16_rn(v[j]);
+            const __nv_bfloat16 o = __float2bfloat16_rn(bias ? v[j] + __uint_as_float(uint32_t(bias[n + j]) << 16) : v[j]);
             y[(size_t)m * N + n + j] = *reinterpret_cast<const uint16_t*>(&o);
         }
     }
@@ -93,7 +93,8 @@ template <int BN>
 __global__ void __launch_bounds__(F8G_THREADS, 1)
 fp8_gemm_tc_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_scale, const uint8_t* __restrict__ xq,
                    const float* __restrict__ a_scale, uint16_t* __restrict__ y, int M, int N, int KT, int NT, int MT,
-                   int M_pad, int out_f32, int full, int ks_tail, float* __restrict__ slabs, int* __restrict__ status) {
+                   int M_pad, int out_f32, const uint16_t* __restrict__ bias, int full, int ks_tail, float* __restrict__ slabs,
+                   int* __restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -243,10 +244,17 @@ fp8_gemm_tc_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ 
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         const float4 ws = __ldg(reinterpret_cast<const float4*>(w_scale + nc) + j);   // scales are padded to NT*128
-                        const float v0 = __fmul_rn(__fmul_rn(__uint_as_float(r[4 * j + 0]), as), ws.x);
-                        const float v1 = __fmul_rn(__fmul_rn(__uint_as_float(r[4 * j + 1]), as), ws.y);
-                        const float v2 = __fmul_rn(__fmul_rn(__uint_as_float(r[4 * j + 2]), as), ws.z);
-                        const float v3 = __fmul_rn(__fmul_rn(__uint_as_float(r[4 * j + 3]), as), ws.w);
+                        float v0 = __fmul_rn(__fmul_rn(__uint_as_float(r[4 * j + 0]), as), ws.x);
+                        float v1 = __fmul_rn(__fmul_rn(__uint_as_float(r[4 * j + 1]), as), ws.y);
+                        float v2 = __fmul_rn(__fmul_rn(__uint_as_float(r[4 * j + 2]), as), ws.z);
+                        float v3 = __fmul_rn(__fmul_rn(__uint_as_float(r[4 * j + 3]), as), ws.w);
+                        if (bias) {                    // the linear's own bias, added in f32 before the one rounding
+                            const int n4 = nc + 4 * j;
+                            if (n4 + 0 < N) v0 += __uint_as_float(uint32_t(bias[n4 + 0]) << 16);
+                            if (n4 + 1 < N) v1 += __uint_as_float(uint32_t(bias[n4 + 1]) << 16);
+                            if (n4 + 2 < N) v2 += __uint_as_float(uint32_t(bias[n4 + 2]) << 16);
+                            if (n4 + 3 < N) v3 += __uint_as_float(uint32_t(bias[n4 + 3]) << 16);
+                        }
                         const __nv_bfloat162 p0 = __floats2bfloat162_rn(v0, v1);
                         const __nv_bfloat162 p1 = __floats2bfloat162_rn(v2, v3);
                         o[2 * j] = *reinterpret_cast<const uint32_t*>(&p0);
@@ -278,7 +286,7 @@ fp8_gemm_tc_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ 
 
 template <int BN>
 static int32_t fp8_gemm_launch_bn(scr_ctx* ctx, const uint8_t* wpack, const uint8_t* act, uint16_t* y, int M, int N, int K,
-                                  const Fp8GemmPlan& p, float* slabs, cudaStream_t stream) {
+                                  const LinearEnds& ends, const Fp8GemmPlan& p, float* slabs, cudaStream_t stream) {
     const Fp8Geom g = fp8_geom(N, K);
     const float* w_scale = reinterpret_cast<const float*>(wpack + (size_t)g.NT * g.KT * FP8_TILE_BYTES);
     const float* a_scale = reinterpret_cast<const float*>(act);
@@ -289,23 +297,23 @@ static int32_t fp8_gemm_launch_bn(scr_ctx* ctx, const uint8_t* wpack, const uint
                                          (int)F8GSmem<BN>::kTotal);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "fp8_gemm smem attribute: %s", cudaGetErrorString(e));
     fp8_gemm_tc_kernel<BN><<<grid, F8G_THREADS, F8GSmem<BN>::kTotal, stream>>>(wpack, w_scale, xq, a_scale, y, M, N, g.KT,
-                                                                              g.NT, p.mt, p.mt * 128, ctx->out_f32, p.full,
+                                                                              g.NT, p.mt, p.mt * 128, ends.out_f32, ends.bias, p.full,
                                                                               p.ks_tail, slabs, ctx->dev_status);
     int32_t st = scr_check_launch(ctx, "fp8_gemm_tc");
     if (st || p.ks_tail == 1) return st;
     fp8_gemm_tail_finish_kernel<<<p.n_tail() * (128 / (1024 / BN)), 256, 0, stream>>>(slabs, p.ks_tail, p.n_tail(), p.full, p.mt, BN,
-                                                                                     M, N, y, ctx->out_f32);
+                                                                                     M, N, y, ends.out_f32, ends.bias);
     return scr_check_launch(ctx, "fp8_gemm_tail_finish");
 }
 
 int32_t fp8_gemm_tc_launch(scr_ctx* ctx, const uint8_t* wpack, const uint8_t* act, uint16_t* y, int M, int N, int K,
-                           void* workspace, size_t, cudaStream_t stream) {
+                           const LinearEnds& ends, void* workspace, size_t, cudaStream_t stream) {
     if (((uintptr_t)(act + fp8_act_scale_bytes(M)) & 127u) != 0 || ((uintptr_t)wpack & 127u) != 0)
         return scr_fail(ctx, SCR_E_ALIGN, "weight pack and activation pack must be 128-byte aligned for the GEMM path");
     if (!scr_aligned16(y)) return scr_fail(ctx, SCR_E_ALIGN, "y must be 16-byte aligned");
     const Fp8GemmPlan plan = fp8_gemm_plan(M, N, K, ctx->sm_count);
     float* slabs = reinterpret_cast<float*>(workspace);
     if (plan.ks_tail > 1 && (!slabs || !scr_aligned16(slabs))) return scr_fail(ctx, SCR_E_WORKSPACE, "split-K needs an aligned workspace");
-    if (plan.bn == 256) return fp8_gemm_launch_bn<256>(ctx, wpack, act, y, M, N, K, plan, slabs, stream);
-    return fp8_gemm_launch_bn<128>(ctx, wpack, act, y, M, N, K, plan, slabs, stream);
+    if (plan.bn == 256) return fp8_gemm_launch_bn<256>(ctx, wpack, act, y, M, N, K, ends, plan, slabs, stream);
+    return fp8_gemm_launch_bn<128>(ctx, wpack, act, y, M, N, K, ends, plan, slabs, stream);
 }

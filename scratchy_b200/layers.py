@@ -219,6 +219,11 @@ class AffineQuantLinear:
             raise ScratchyCudaError(-5, "weights must be on a CUDA device (there is no CPU path)")
         dev = weight.device
         N, K = int(weight.shape[0]), int(weight.shape[1]) * 8
+        if linear_bias is not None:
+            # `{prefix}.bias` (layers_quant.rs:318-351): one value per output channel, in the activation dtype
+            if linear_bias.dtype != torch.bfloat16 or tuple(linear_bias.shape) != (N,):
+                raise ValueError(f"`.bias` must be bf16 [{N}], got {linear_bias.dtype} {tuple(linear_bias.shape)}")
+            linear_bias = linear_bias.to(dev).contiguous()
         ctx = _lib.context(_dev_index(dev))
         L = _lib.lib()
         size = ctypes.c_size_t(0)
@@ -256,7 +261,7 @@ class AffineQuantLinear:
             workspace = torch.empty(need, dtype=torch.uint8, device=dev)
         ctx.check(_lib.lib().scr_linear_affine_b4(
             ctx.handle, _ptr(self.packed), _ptr(x2), M, self.out_features, self.in_features, self.group_size,
-            _ptr(out), _ptr(workspace), ctypes.c_size_t(workspace.numel() if workspace is not None else 0),
+            _ptr(self.linear_bias), _ptr(out), _ptr(workspace), ctypes.c_size_t(workspace.numel() if workspace is not None else 0),
             _stream(dev)))
         return out.reshape(*x.shape[:-1], self.out_features)
 
@@ -399,18 +404,21 @@ class Fp8Linear:
     packed: torch.Tensor
     in_features: int
     out_features: int
+    linear_bias: Optional[torch.Tensor] = None      # `{prefix}.bias` [N] bf16 (the q/k/v projections of Qwen2.5 carry one)
 
     @classmethod
     def load(cls, weights: GpuWeights, prefix: str, expected_in_features: int) -> "Fp8Linear":
         weight = weights.take(f"{prefix}.weight")
         scale = weights.take(f"{prefix}.weight_scale")
+        linear_bias = weights.take(f"{prefix}.bias") if weights.contains(f"{prefix}.bias") else None
         if weight.dim() != 2 or int(weight.shape[1]) != expected_in_features:
             raise ValueError(f"`{prefix}.weight` is {tuple(weight.shape)}; this build expects "
                              f"in_features={expected_in_features}")
-        return cls.from_tensors(weight, scale)
+        return cls.from_tensors(weight, scale, linear_bias)
 
     @classmethod
-    def from_tensors(cls, weight_e4m3: torch.Tensor, weight_scale: torch.Tensor) -> "Fp8Linear":
+    def from_tensors(cls, weight_e4m3: torch.Tensor, weight_scale: torch.Tensor,
+                     linear_bias: Optional[torch.Tensor] = None) -> "Fp8Linear":
         if weight_e4m3.dtype not in (torch.uint8, torch.float8_e4m3fn):
             raise ValueError(f"`.weight` must be FP8 E4M3 bytes, got {weight_e4m3.dtype}")
         if not weight_e4m3.is_cuda:
@@ -427,7 +435,11 @@ class Fp8Linear:
         packed = torch.empty(size.value, dtype=torch.uint8, device=dev)
         w = weight_e4m3.contiguous().view(torch.uint8)
         ctx.check(L.scr_fp8_repack(ctx.handle, _ptr(w), _ptr(scale), N, K, _ptr(packed), _stream(dev)))
-        return cls(packed, K, N)
+        if linear_bias is not None:
+            if linear_bias.dtype != torch.bfloat16 or tuple(linear_bias.shape) != (N,):
+                raise ValueError(f"`.bias` must be bf16 [{N}], got {linear_bias.dtype} {tuple(linear_bias.shape)}")
+            linear_bias = linear_bias.to(dev).contiguous()
+        return cls(packed, K, N, linear_bias)
 
     @staticmethod
     def quantize_activation(x: torch.Tensor) -> Fp8ActPack:
@@ -482,7 +494,7 @@ class Fp8Linear:
         if workspace is None or workspace.numel() < need:
             workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
         ctx.check(_lib.lib().scr_linear_fp8(ctx.handle, _ptr(self.packed), _ptr(act.buf), act.M, self.out_features,
-                                            self.in_features, _ptr(out), _ptr(workspace),
+                                            self.in_features, _ptr(self.linear_bias), _ptr(out), _ptr(workspace),
                                             ctypes.c_size_t(workspace.numel()), _stream(dev)))
         return out
 
@@ -521,7 +533,7 @@ class Fp8Linear:
         if workspace is None or workspace.numel() < need:
             workspace = torch.empty(need, dtype=torch.uint8, device=dev)
         ctx.check(_lib.lib().scr_linear_fp8_dynamic(ctx.handle, _ptr(self.packed), _ptr(x2), M, self.out_features,
-                                                    self.in_features, _ptr(out), _ptr(workspace),
+                                                    self.in_features, _ptr(self.linear_bias), _ptr(out), _ptr(workspace),
                                                     ctypes.c_size_t(workspace.numel()), _stream(dev)))
         return out.reshape(*x.shape[:-1], self.out_features)
 

@@ -69,7 +69,7 @@ def test_fp8_sizes():
 
 def test_null_context_is_an_argument_error_not_a_crash():
     L = _lib.lib()
-    assert L.scr_linear_affine_b4(None, None, None, 1, 16, 64, 64, None, None, 0, None) == -1
+    assert L.scr_linear_affine_b4(None, None, None, 1, 16, 64, 64, None, None, None, 0, None) == -1
     assert L.scr_fp8_quant_per_token(None, None, 1, 64, None, None) == -1
     assert L.scr_cuda_destroy(None) == -1
     assert L.scr_launch_count(None) == 0

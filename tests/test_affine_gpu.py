@@ -158,12 +158,12 @@ def test_error_codes_through_the_abi():
     L = _lib.lib()
     buf = torch.zeros(4096, dtype=torch.uint8, device="cuda")
     p = ctypes.c_void_p(buf.data_ptr())
-    assert L.scr_linear_affine_b4(ctx.handle, p, p, 1, 16, 96, 64, p, None, 0, None) == -2     # K % group
-    assert L.scr_linear_affine_b4(ctx.handle, p, p, 1, 16, 128, 32, p, None, 0, None) == -4    # group 32
-    assert L.scr_linear_affine_b4(ctx.handle, p, p, 0, 16, 128, 64, p, None, 0, None) == -2    # M
-    assert L.scr_linear_affine_b4(ctx.handle, None, p, 1, 16, 128, 64, p, None, 0, None) == -1
+    assert L.scr_linear_affine_b4(ctx.handle, p, p, 1, 16, 96, 64, None, p, None, 0, None) == -2     # K % group
+    assert L.scr_linear_affine_b4(ctx.handle, p, p, 1, 16, 128, 32, None, p, None, 0, None) == -4    # group 32
+    assert L.scr_linear_affine_b4(ctx.handle, p, p, 0, 16, 128, 64, None, p, None, 0, None) == -2    # M
+    assert L.scr_linear_affine_b4(ctx.handle, None, p, 1, 16, 128, 64, None, p, None, 0, None) == -1
     mis = ctypes.c_void_p(buf.data_ptr() + 4)
-    assert L.scr_linear_affine_b4(ctx.handle, mis, p, 1, 16, 128, 64, p, None, 0, None) == -3
+    assert L.scr_linear_affine_b4(ctx.handle, mis, p, 1, 16, 128, 64, None, p, None, 0, None) == -3
     assert b"aligned" in L.scr_last_error(ctx.handle)
 
 
@@ -335,3 +335,40 @@ def test_residual_add_and_rmsnorm_in_the_epilogue(N, K, M):
             graph.replay()
             torch.cuda.synchronize()
             assert np.array_equal(bits_of(res_c), bits_of(res_b)) and np.array_equal(bits_of(normed_c), bits_of(normed_b))
+
+
+@pytest.mark.parametrize("N,K,M", [(3584, 3584, 1), (512, 3584, 1), (512, 3584, 16), (1000, 1088, 3), (3584, 3584, 64),
+                                   (512, 3584, 2048)])
+def test_linear_bias_in_the_epilogue(N, K, M):
+    """`{prefix}.bias` (the q/k/v projections of Qwen2.5 carry one): added in f32 to the sum before the one rounding,
+    as the reference's matvec epilogue does (crates/targets/metal/shaders/quantized_qmv.metal:104-112), on the
+    matvec (M <= 16) and on the tensor-core GEMM, split-K tiles included."""
+    import torch
+    from scratchy_b200 import AffineQuantLinear
+    w, s, b = synth.affine_int4_weights(N, K, 64, synth.seed_for("bias", N, K, M))
+    x = synth.activations_bf16(M, K, synth.seed_for("biasx", N, K, M))
+    rng = np.random.default_rng(synth.seed_for("biasb", N, K, M))
+    bias = synth.f32_to_bf16_bits(rng.normal(0.0, 2.0, N).astype(np.float32))
+    layer = AffineQuantLinear.from_tensors(u32_dev(w), bf16_dev(s), bf16_dev(b), 64, 4, linear_bias=bf16_dev(bias))
+    y = bits_of(layer.forward(bf16_dev(x).reshape(M, K))).reshape(M, N)
+    torch.cuda.synchronize()
+    rows = np.arange(M) if M <= 64 else np.sort(np.random.default_rng(1).choice(M, 48, replace=False))
+    xs = x.reshape(M, K)[rows]
+    want = oracle.affine_qmm_t_b4_bias(w.view(np.uint8).reshape(-1), s, b, xs, bias, len(rows), N, K, 64)
+    plain = oracle.affine_qmm_t_b4(w.view(np.uint8).reshape(-1), s, b, xs, len(rows), N, K, 64)
+    r = rel_l2(y[rows], want)
+    print(f"bias N={N} K={K} M={M} rel_l2={r:.3e} max_abs={max_abs(y[rows], want):.3e}")
+    assert r <= REL_L2_TOL
+    assert rel_l2(y[rows], plain) > 0.1, "the bias must have been applied"
+
+
+def test_bias_is_refused_where_no_epilogue_has_it():
+    """A fused gate/up pairing has no bias end: the call is refused, never silently dropped."""
+    import torch
+    from scratchy_b200 import AffineQuantLinear, ScratchyCudaError
+    w, s, b = synth.affine_int4_weights(64, 128, 64, 5)
+    bias = synth.f32_to_bf16_bits(np.ones(64, np.float32))
+    layer = AffineQuantLinear.from_tensors(u32_dev(w), bf16_dev(s), bf16_dev(b), 64, 4, linear_bias=bf16_dev(bias))
+    layer.pairs8 = True
+    with pytest.raises((ScratchyCudaError, ValueError)):
+        layer.forward_silu_mul(torch.zeros((1, 128), dtype=torch.bfloat16, device="cuda"))

@@ -245,3 +245,54 @@ def test_rmsnorm_fused_with_the_quantisation(M, K):
     want_q, want_s = oracle.fp8_quant_per_token(want_norm, M, K)
     assert np.allclose(sc_a.cpu().numpy(), want_s, rtol=1e-2)
     assert np.mean(xq_a.cpu().numpy().reshape(M, K) == want_q) > 0.97
+
+
+@pytest.mark.parametrize("N,K,M", [(3584, 3584, 1), (512, 3584, 1), (512, 3584, 16), (512, 3584, 64), (3584, 3584, 2048),
+                                   (1000, 1088, 3)])
+def test_linear_bias_in_the_epilogue(N, K, M):
+    """`{prefix}.bias` on the fp8 path (Qwen2.5's q/k/v carry one): added in f32 to the dequantised sum before the one
+    rounding (the order of crates/targets/metal/shaders/quantized_qmv.metal:104-112), on the self-quantising matvec,
+    the pack matvec and the tensor-core GEMM."""
+    import torch
+    from scratchy_b200 import Fp8Linear
+    wq, ws = oracle.fp8_quantize_weight_per_channel(synth.fp8_weights_f32(N, K, synth.seed_for("f8bias", N, K, M)))
+    x = synth.activations_bf16(M, K, synth.seed_for("f8biasx", N, K, M))
+    rng = np.random.default_rng(synth.seed_for("f8biasb", N, K, M))
+    bias = synth.f32_to_bf16_bits(rng.normal(0.0, 2.0, N).astype(np.float32))
+    layer = Fp8Linear.from_tensors(to_dev(wq), to_dev(ws), linear_bias=bf16_dev(bias))
+    y = bits_of(layer.forward(bf16_dev(x).reshape(M, K))).reshape(M, N)
+    torch.cuda.synchronize()
+    rows = np.arange(M) if M <= 64 else np.sort(np.random.default_rng(1).choice(M, 48, replace=False))
+    xs = x.reshape(M, K)[rows]
+    want = oracle.fp8_dynamic_linear_bias(xs, wq, ws, bias, len(rows), N, K)
+    plain = oracle.fp8_dynamic_linear(xs, wq, ws, len(rows), N, K)
+    r = rel_l2(y[rows], want)
+    print(f"fp8 bias N={N} K={K} M={M} rel_l2={r:.3e} max_abs={max_abs(y[rows], want):.3e}")
+    assert r <= REL_L2_TOL
+    assert rel_l2(y[rows], plain) > 0.1, "the bias must have been applied"
+
+
+def test_misaligned_pointers_are_refused_on_the_host():
+    """Every fp8 forward entry point refuses a pointer that is not 16-byte aligned with SCR_E_ALIGN before anything
+    is launched: the matvec's bulk copies would otherwise fault on the device."""
+    import torch
+    from scratchy_b200 import _lib
+    ctx = _lib.context(0)
+    L = _lib.lib()
+    N, K = 64, 128
+    wq, ws = oracle.fp8_quantize_weight_per_channel(synth.fp8_weights_f32(N, K, 3))
+    layer = make_layer(wq, ws)
+    x = torch.zeros((17, K), dtype=torch.bfloat16, device="cuda")
+    y = torch.empty((17, N), dtype=torch.bfloat16, device="cuda")
+    wsz = layer.workspace_bytes(17)
+    wsb = torch.empty(wsz + 64, dtype=torch.uint8, device="cuda")
+    p, xp, yp, wp = layer.packed.data_ptr(), x.data_ptr(), y.data_ptr(), wsb.data_ptr()
+    before = ctx.launch_count()
+    for M in (1, 17):
+        assert L.scr_linear_fp8_dynamic(ctx.handle, p + 2, xp, M, N, K, None, yp, wp, wsb.numel(), None) == -3
+        assert L.scr_linear_fp8_dynamic(ctx.handle, p, xp + 2, M, N, K, None, yp, wp, wsb.numel(), None) == -3
+        assert L.scr_linear_fp8_dynamic_static(ctx.handle, p + 2, xp, M, N, K, yp, None) == -3
+        assert L.scr_linear_fp8_dynamic_static(ctx.handle, p, xp + 2, M, N, K, yp, None) == -3
+        assert L.scr_linear_fp8(ctx.handle, p + 2, wp, M, N, K, None, yp, wp, wsb.numel(), None) == -3
+        assert L.scr_linear_fp8(ctx.handle, p, wp + 2, M, N, K, None, yp, wp, wsb.numel(), None) == -3
+    assert ctx.launch_count() == before, "a refused call must not launch anything"
