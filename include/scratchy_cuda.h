@@ -65,16 +65,22 @@ int32_t scr_device_status(scr_ctx* ctx, void* stream, int32_t* code);
  * + `load_layered_linear_affine_quant` (crates/targets/metal/src/loaders.rs:96-116): the
  * checkpoint tensors of `AffineQuantLinear` (crates/models/quantization/src/layers_quant.rs:33-52)
  *   w       U32  [N, K/8]   element i of a word at bits [4i, 4i+4)
- *   scales  BF16 [N, K/64]
- *   biases  BF16 [N, K/64]
+ *   scales  F16 or BF16 [N, K/64]   (`scale_dtype`: the model's SCALE_DTYPE the loader pins,
+ *   biases  F16 or BF16 [N, K/64]    crates/targets/metal/src/layers_quant.rs:238-285)
  * already resident on the device, are rewritten once into the kernels' streaming
- * layout (`dst`, `scr_affine_b4_repack_size` bytes, 128-byte aligned).
+ * layout (`dst`, `scr_affine_b4_repack_size` bytes, 128-byte aligned).  F16 scales and biases —
+ * what every mlx-community 4-bit checkpoint ships — are narrowed to the bf16 activation type here,
+ * exactly as the reference narrows them before it multiplies (`TAct::from_f32(scale.to_f32())`,
+ * crates/targets/metal/src/cpu_reference.rs:63-68,90-92), so the kernels see one layout.
  * Validation follows layers_quant.rs:310-338: bits == 4, K % group == 0; this build
  * implements group == 64 only (SCR_E_DTYPE otherwise). */
 int32_t scr_affine_b4_repack_size(int32_t N, int32_t K, int32_t group, size_t* bytes);
-int32_t scr_affine_b4_repack(scr_ctx* ctx, const uint32_t* w, const uint16_t* scales_bf16,
-                             const uint16_t* biases_bf16, int32_t N, int32_t K, int32_t group,
-                             void* dst, void* stream);
+/* The reference's `DType` discriminants (crates/tensors/src/dtype.rs:7-16). */
+#define SCR_DTYPE_F16  0
+#define SCR_DTYPE_BF16 1
+int32_t scr_affine_b4_repack(scr_ctx* ctx, const uint32_t* w, const uint16_t* scales,
+                             const uint16_t* biases, int32_t scale_dtype, int32_t N, int32_t K,
+                             int32_t group, void* dst, void* stream);
 
 /* Test hook: dequantise the *repacked* buffer back to dense bf16 [N, K] with the very
  * device code the matvec and the GEMM use.  Must equal, bit for bit,
@@ -315,6 +321,21 @@ typedef struct scr_tp_comm scr_tp_comm;
 int32_t scr_tp_comm_create(scr_ctx* ctx, int32_t world, int32_t rank, int64_t max_elems,
                            scr_tp_comm** out, uint8_t* handle_out /* SCR_TP_HANDLE_BYTES */);
 int32_t scr_tp_comm_connect(scr_tp_comm* comm, const uint8_t* handles /* world x SCR_TP_HANDLE_BYTES */);
+/* The same for ranks that are THREADS OF ONE PROCESS — how the reference's executor drives its ranks
+ * (crates/serving/worker/src/threadpool.rs:1-16, crates/serving/worker/src/parallel.rs:103-150): an IPC handle
+ * opens only in another process, so such ranks exchange raw device pointers.  Every rank reads its own
+ * `scr_tp_comm_base`; each then calls `scr_tp_comm_connect_local` with all `world` bases and the devices they
+ * live on, its own device current (peer access is enabled here). */
+int32_t scr_tp_comm_base(scr_tp_comm* comm, void** base);
+int32_t scr_tp_comm_connect_local(scr_tp_comm* comm, void* const* peer_bases /* world */,
+                                  const int32_t* peer_devices /* world */);
+/* Failure detection, the device half of the executor's health check (crates/serving/engine/src/executor.rs:454):
+ * a kernel of this communicator polls at most `polls` times for a peer's data, then records a code in the
+ * context's status word (`scr_device_status` reports SCR_E_TIMEOUT) and runs to its end — nothing hangs, the
+ * call's results are garbage, the call counter still advances and the next call works.  While the status word
+ * is set every bounded wait on this context gives up early, so read (and thereby clear) it with
+ * `scr_device_status` once per step, after the host has synchronised on the step's result anyway. */
+int32_t scr_tp_comm_set_wait_limit(scr_tp_comm* comm, uint32_t polls);
 /* y_bf16 and/or y_f32 receive the reduced [count] values (either may be NULL, not both). */
 int32_t scr_tp_allreduce_partial(scr_tp_comm* comm, const float* partial, int64_t count,
                                  uint16_t* y_bf16, float* y_f32, void* stream);

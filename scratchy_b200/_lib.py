@@ -11,6 +11,7 @@ _LIB_PATH = os.path.join(_HERE, "libscratchy_cuda.so")
 OK = 0
 STATUS = {0: "SCR_OK", -1: "SCR_E_ARG", -2: "SCR_E_SHAPE", -3: "SCR_E_ALIGN", -4: "SCR_E_DTYPE", -5: "SCR_E_CUDA",
           -6: "SCR_E_WORKSPACE", -7: "SCR_E_UNSUPPORTED", -8: "SCR_E_TIMEOUT", -9: "SCR_E_COMM"}
+DTYPE_F16, DTYPE_BF16 = 0, 1     # the reference's DType discriminants (crates/tensors/src/dtype.rs:7-16)
 KIND_AFFINE_B4 = 0
 KIND_FP8_DYNAMIC = 1
 
@@ -38,7 +39,7 @@ SIGNATURES = {
     "scr_launch_count": (_i64, [_vp]),
     "scr_device_status": (_i32, [_vp, _vp, ctypes.POINTER(_i32)]),
     "scr_affine_b4_repack_size": (_i32, [_i32, _i32, _i32, _psz]),
-    "scr_affine_b4_repack": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp]),
+    "scr_affine_b4_repack": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp]),
     "scr_affine_b4_dequant_dump": (_i32, [_vp, _vp, _i32, _i32, _i32, _vp, _vp]),
     "scr_linear_workspace_size": (_i32, [_i32, _i32, _i32, _i32, _psz]),
     "scr_linear_affine_b4": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _sz, _vp]),
@@ -63,6 +64,9 @@ SIGNATURES = {
     "scr_partial_to_bf16": (_i32, [_vp, _vp, _i64, _vp, _vp]),
     "scr_tp_comm_create": (_i32, [_vp, _i32, _i32, _i64, ctypes.POINTER(_vp), _vp]),
     "scr_tp_comm_connect": (_i32, [_vp, _vp]),
+    "scr_tp_comm_base": (_i32, [_vp, ctypes.POINTER(_vp)]),
+    "scr_tp_comm_connect_local": (_i32, [_vp, ctypes.POINTER(_vp), ctypes.POINTER(_i32)]),
+    "scr_tp_comm_set_wait_limit": (_i32, [_vp, ctypes.c_uint32]),
     "scr_tp_allreduce_partial": (_i32, [_vp, _vp, _i64, _vp, _vp, _vp]),
     "scr_tp_comm_destroy": (_i32, [_vp]),
     "scr_linear_fp8_dynamic_allreduce": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp]),

@@ -2,6 +2,8 @@
 #include "affine_b4.cuh"
 #include "gemv_common.cuh"
 
+#include <cuda_fp16.h>
+
 #include <algorithm>
 #include <new>
 #include <vector>
@@ -21,8 +23,19 @@ __device__ __forceinline__ uint32_t affine_interleave_word(uint32_t src) {
     return dst;
 }
 
+// A scale or bias as the kernels keep it: bf16 bits.  F16 storage (what every mlx-community 4-bit checkpoint ships)
+// is narrowed to the bf16 activation type exactly as the reference does before it multiplies
+// (`TAct::from_f32(scales[g].to_f32())`, crates/targets/metal/src/cpu_reference.rs:90-92): f16 -> f32 is exact, f32 -> bf16
+// rounds to nearest even.
+__device__ __forceinline__ uint32_t affine_scale_bits(uint16_t raw, int f16) {
+    if (!f16) return raw;
+    const float f = __half2float(__ushort_as_half(raw));
+    const __nv_bfloat16 b = __float2bfloat16_rn(f);
+    return *reinterpret_cast<const uint16_t*>(&b);
+}
+
 __global__ void affine_b4_repack_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict__ scales,
-                                        const uint16_t* __restrict__ biases, int N, int K, int RB, int KC,
+                                        const uint16_t* __restrict__ biases, int f16, int N, int K, int RB, int KC,
                                         uint8_t* __restrict__ dst, unsigned int* __restrict__ slow_flag) {
     const long long nblocks = (long long)RB * KC;
     const long long items = nblocks * 80;               // 64 pieces + 16 scale entries per block
@@ -52,8 +65,8 @@ __global__ void affine_b4_repack_kernel(const uint32_t* __restrict__ w, const ui
             if (grp * 64 < K) {
                 const int G = K / 64;
                 const int r0 = rb * 16 + g, r1 = r0 + 8;
-                if (r0 < N) v.x = uint32_t(scales[(size_t)r0 * G + grp]) | (uint32_t(biases[(size_t)r0 * G + grp]) << 16);
-                if (r1 < N) v.y = uint32_t(scales[(size_t)r1 * G + grp]) | (uint32_t(biases[(size_t)r1 * G + grp]) << 16);
+                if (r0 < N) v.x = affine_scale_bits(scales[(size_t)r0 * G + grp], f16) | (affine_scale_bits(biases[(size_t)r0 * G + grp], f16) << 16);
+                if (r1 < N) v.y = affine_scale_bits(scales[(size_t)r1 * G + grp], f16) | (affine_scale_bits(biases[(size_t)r1 * G + grp], f16) << 16);
             }
             *reinterpret_cast<uint2*>(out + 1024 + e * 8) = v;
             if (affine_group_needs_generic(v.x) || affine_group_needs_generic(v.y)) atomicOr(slow_flag, 1u);
@@ -442,9 +455,11 @@ extern "C" int32_t scr_affine_b4_repack_size(int32_t N, int32_t K, int32_t group
 }
 
 extern "C" int32_t scr_affine_b4_repack(scr_ctx* ctx, const uint32_t* w, const uint16_t* scales, const uint16_t* biases,
-                                        int32_t N, int32_t K, int32_t group, void* dst, void* stream) {
+                                        int32_t scale_dtype, int32_t N, int32_t K, int32_t group, void* dst, void* stream) {
     SCR_REQUIRE_CTX(ctx);
     if (!w || !scales || !biases || !dst) return scr_fail(ctx, SCR_E_ARG, "null pointer");
+    if (scale_dtype != SCR_DTYPE_F16 && scale_dtype != SCR_DTYPE_BF16)
+        return scr_fail(ctx, SCR_E_DTYPE, "scales/biases must be F16 or BF16 (dtype %d)", scale_dtype);
     int32_t st = affine_check_shape(ctx, N, K, group);
     if (st) return st;
     if (!scr_aligned16(w) || !scr_aligned16(dst)) return scr_fail(ctx, SCR_E_ALIGN, "w/dst must be 16-byte aligned");
@@ -455,7 +470,7 @@ extern "C" int32_t scr_affine_b4_repack(scr_ctx* ctx, const uint32_t* w, const u
     unsigned int* flag = reinterpret_cast<unsigned int*>((uint8_t*)dst + affine_blocks_bytes(g));
     cudaError_t e = cudaMemsetAsync(flag, 0, AFF_TRAILER_BYTES, (cudaStream_t)stream);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine_b4_repack memset: %s", cudaGetErrorString(e));
-    affine_b4_repack_kernel<<<blocks, threads, 0, (cudaStream_t)stream>>>(w, scales, biases, N, K, g.RB, g.KC,
+    affine_b4_repack_kernel<<<blocks, threads, 0, (cudaStream_t)stream>>>(w, scales, biases, scale_dtype == SCR_DTYPE_F16, N, K, g.RB, g.KC,
                                                                          (uint8_t*)dst, flag);
     int32_t st2 = scr_check_launch(ctx, "affine_b4_repack");
     if (st2) return st2;

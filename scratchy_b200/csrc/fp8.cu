@@ -578,9 +578,9 @@ fp8_gemv_kernel(const uint8_t* __restrict__ wpack, const float* __restrict__ w_s
             const int n = rb * 16 + row;
             if (e < SLOTS && tok < M && n < N) {
                 const long long at = (long long)tok * N + n;
-                float s = tpc_ll_wait(mine + tpc_slot(e_call, ex.world, 0, ex.max_elems, at), e_call, status);
+                float s = tpc_ll_wait(mine + tpc_slot(e_call, ex.world, 0, ex.max_elems, at), e_call, status, ex.wait_limit);
                 for (int q = 1; q < ex.world; ++q)
-                    s = __fadd_rn(s, tpc_ll_wait(mine + tpc_slot(e_call, ex.world, q, ex.max_elems, at), e_call, status));
+                    s = __fadd_rn(s, tpc_ll_wait(mine + tpc_slot(e_call, ex.world, q, ex.max_elems, at), e_call, status, ex.wait_limit));
                 const __nv_bfloat16 v = __float2bfloat16_rn(s);
                 ex.y_bf16[at] = *reinterpret_cast<const uint16_t*>(&v);
             }
@@ -901,6 +901,7 @@ extern "C" int32_t scr_linear_fp8_dynamic_allreduce(scr_tp_comm* comm, const voi
     ex.max_elems = comm->max_elems;
     ex.state = comm->state;
     ex.y_bf16 = y;
+    ex.wait_limit = comm->wait_limit;
     return fp8_gemv_launch<1>(ctx, (const uint8_t*)packed, nullptr, nullptr, y, M, N, K, LinearEnds(), (cudaStream_t)stream, x, &ex);
 }
 

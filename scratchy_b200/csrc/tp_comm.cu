@@ -31,7 +31,7 @@ namespace {
 __global__ void __launch_bounds__(TPC_THREADS) tp_allreduce_kernel(TpcPeers peers, int world, int rank, long long max_elems,
                                                                    const float* __restrict__ partial, long long count,
                                                                    uint16_t* __restrict__ y_bf16, float* __restrict__ y_f32,
-                                                                   unsigned int* state, int* status) {
+                                                                   unsigned int* state, int* status, unsigned int wait_limit) {
     __shared__ unsigned int s_epoch;
     const int c = blockIdx.x, tid = threadIdx.x;
     // Programmatic dependent launch: the next kernel of the stream (a matvec that prefetches its load-time
@@ -63,11 +63,11 @@ __global__ void __launch_bounds__(TPC_THREADS) tp_allreduce_kernel(TpcPeers peer
         if (i < count) {
             float s[4];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) s[k] = tpc_ll_wait(mine + tpc_slot(e, world, 0, max_elems, i) + k, e, status);
+            for (int k = 0; k < 4; ++k) s[k] = tpc_ll_wait(mine + tpc_slot(e, world, 0, max_elems, i) + k, e, status, wait_limit);
             for (int q = 1; q < world; ++q) {
 #pragma unroll
                 for (int k = 0; k < 4; ++k)
-                    s[k] = __fadd_rn(s[k], tpc_ll_wait(mine + tpc_slot(e, world, q, max_elems, i) + k, e, status));
+                    s[k] = __fadd_rn(s[k], tpc_ll_wait(mine + tpc_slot(e, world, q, max_elems, i) + k, e, status, wait_limit));
             }
             if (y_f32) *reinterpret_cast<float4*>(y_f32 + i) = make_float4(s[0], s[1], s[2], s[3]);
             if (y_bf16) {
@@ -91,7 +91,7 @@ __device__ __forceinline__ float4 ld_cg_f4(const float* p) {
 __global__ void __launch_bounds__(TPC_THREADS) tp_allreduce_flags_kernel(TpcPeers peers, int world, int rank, long long max_elems,
                                                                          const float* __restrict__ partial, long long count,
                                                                          uint16_t* __restrict__ y_bf16, float* __restrict__ y_f32,
-                                                                         unsigned int* state, int* status) {
+                                                                         unsigned int* state, int* status, unsigned int wait_limit) {
     __shared__ unsigned int s_epoch;
     const int c = blockIdx.x, tid = threadIdx.x;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -116,7 +116,7 @@ __global__ void __launch_bounds__(TPC_THREADS) tp_allreduce_flags_kernel(TpcPeer
         tpc_st_release_sys(peers.flags[tid] + (half + rank) * TPC_MAX_CTAS + c, e);
         const unsigned int* mine = peers.flags[rank] + (half + tid) * TPC_MAX_CTAS + c;
         bool seen = false;
-        for (unsigned int it = 0; it < TPC_WAIT_LIMIT; ++it) {
+        for (unsigned int it = 0; it < wait_limit; ++it) {
             if ((int)(tpc_ld_acquire_sys(mine) - e) >= 0) {
                 seen = true;
                 break;
@@ -208,11 +208,59 @@ extern "C" int32_t scr_tp_comm_connect(scr_tp_comm* comm, const uint8_t* handles
     return SCR_OK;
 }
 
+// Ranks that are threads of ONE process (the reference's executor runs one OS thread per rank inside one process:
+// crates/serving/worker/src/threadpool.rs:1-16, parallel.rs:103-150) cannot open each other's IPC handles — an IPC
+// handle only opens in another process.  They connect with raw device pointers instead: every rank publishes
+// `scr_tp_comm_base`, and each calls this with all W bases and the devices they live on, with its own device
+// current.  Peer access is enabled here (an already-enabled pair is fine).
+extern "C" int32_t scr_tp_comm_base(scr_tp_comm* comm, void** base) {
+    if (!comm || !base) return SCR_E_ARG;
+    *base = comm->local;
+    return SCR_OK;
+}
+
+extern "C" int32_t scr_tp_comm_connect_local(scr_tp_comm* comm, void* const* peer_bases, const int32_t* peer_devices) {
+    if (!comm || !peer_bases || !peer_devices) return SCR_E_ARG;
+    scr_ctx* ctx = comm->ctx;
+    SCR_REQUIRE_CTX(ctx);
+    int cur = -1;
+    if (cudaGetDevice(&cur) != cudaSuccess || cur != ctx->device)
+        return scr_fail(ctx, SCR_E_ARG, "tp comm: device %d must be current (current is %d)", ctx->device, cur);
+    for (int p = 0; p < comm->world; ++p) {
+        if (p == comm->rank) continue;
+        if (!peer_bases[p]) return scr_fail(ctx, SCR_E_ARG, "tp comm: rank %d has no base pointer", p);
+        if (peer_devices[p] != ctx->device) {
+            int can = 0;
+            cudaError_t e = cudaDeviceCanAccessPeer(&can, ctx->device, peer_devices[p]);
+            if (e != cudaSuccess || !can)
+                return scr_fail(ctx, SCR_E_COMM, "tp comm: device %d cannot reach device %d", ctx->device, peer_devices[p]);
+            e = cudaDeviceEnablePeerAccess(peer_devices[p], 0);
+            if (e == cudaErrorPeerAccessAlreadyEnabled) {
+                (void)cudaGetLastError();
+            } else if (e != cudaSuccess) {
+                return scr_fail(ctx, SCR_E_COMM, "tp comm: enabling peer access to device %d: %s", peer_devices[p], cudaGetErrorString(e));
+            }
+        }
+        comm->peer[p] = static_cast<unsigned char*>(peer_bases[p]);
+    }
+    comm->connected = true;
+    return SCR_OK;
+}
+
+// How many times a kernel polls for a peer's packet or flag before it gives up, records SCR_E_TIMEOUT's code in the
+// context's status word and runs to its end (results of that call are garbage; the call counter still advances, so
+// the next call works).  The default is generous; health checks and tests set it short.
+extern "C" int32_t scr_tp_comm_set_wait_limit(scr_tp_comm* comm, uint32_t polls) {
+    if (!comm || polls == 0) return SCR_E_ARG;
+    comm->wait_limit = polls;
+    return SCR_OK;
+}
+
 extern "C" int32_t scr_tp_allreduce_partial(scr_tp_comm* comm, const float* partial, int64_t count, uint16_t* y_bf16,
                                             float* y_f32, void* stream) {
     if (!comm) return SCR_E_ARG;
     scr_ctx* ctx = comm->ctx;
-    ctx->err[0] = 0;
+    SCR_REQUIRE_CTX(ctx);
     if (!partial || (!y_bf16 && !y_f32)) return scr_fail(ctx, SCR_E_ARG, "tp all-reduce: null pointer");
     if (!comm->connected) return scr_fail(ctx, SCR_E_COMM, "tp all-reduce: peers are not connected");
     if (count <= 0 || count % 4 != 0 || count > comm->max_elems)
@@ -234,7 +282,7 @@ extern "C" int32_t scr_tp_allreduce_partial(scr_tp_comm* comm, const float* part
     // every rank takes the same branch: count and world are the same everywhere
     auto kernel = (long long)count * comm->world <= TPC_PACKET_MAX ? tp_allreduce_kernel : tp_allreduce_flags_kernel;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, peers, comm->world, comm->rank, (long long)comm->max_elems, partial,
-                                       (long long)count, y_bf16, y_f32, comm->state, ctx->dev_status);
+                                       (long long)count, y_bf16, y_f32, comm->state, ctx->dev_status, comm->wait_limit);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "tp all-reduce launch: %s", cudaGetErrorString(e));
     return scr_check_launch(ctx, "tp_allreduce");
 }

@@ -35,6 +35,7 @@ struct scr_tp_comm {
     unsigned char* peer[TPC_MAX_WORLD] = {nullptr};
     bool opened[TPC_MAX_WORLD] = {false};
     unsigned int* state = nullptr;           // device: [0] = call counter, [1] = CTAs finished in the running call
+    unsigned int wait_limit = TPC_WAIT_LIMIT;    // polls a kernel waits for a peer's packet or flag before it gives up
     bool connected = false;
 };
 
@@ -45,6 +46,7 @@ struct TpcExchange {
     long long max_elems;
     unsigned int* state;
     uint16_t* y_bf16;                        // the reduced, rounded result [M, N]
+    unsigned int wait_limit;
 };
 
 static inline TpcPeers tpc_peer_table(const scr_tp_comm* comm) {
@@ -62,16 +64,19 @@ static inline TpcPeers tpc_peer_table(const scr_tp_comm* comm) {
 __device__ __forceinline__ long long tpc_slot(unsigned int e, int world, int r, long long max_elems, long long i) {
     return ((long long)(e & 1u) * world + r) * max_elems + i;
 }
+// One 64-bit store and one 64-bit load per packet: a single aligned 8-byte access is single-copy atomic in the
+// memory model (a vector access is modelled as separate scalar accesses and promises nothing of the kind).
 __device__ __forceinline__ void tpc_ll_store(uint2* p, float v, unsigned int e) {
-    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(e) : "memory");
+    const unsigned long long w = ((unsigned long long)e << 32) | (unsigned long long)__float_as_uint(v);
+    asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
 }
-// Bounded wait for the packet of call e; gives up (recording the code) after TPC_WAIT_LIMIT polls or as soon as
-// another waiter has recorded a failure, and returns 0 then.
-__device__ __forceinline__ float tpc_ll_wait(const uint2* p, unsigned int e, int* status) {
-    for (unsigned int it = 0; it < TPC_WAIT_LIMIT; ++it) {
-        uint32_t v, f;
-        asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v), "=r"(f) : "l"(p) : "memory");
-        if (f == e) return __uint_as_float(v);
+// Bounded wait for the packet of call e: gives up (recording the code) after `limit` polls, or as soon as another
+// waiter has recorded a failure, and returns 0 then — the kernel runs to its end, nothing hangs.
+__device__ __forceinline__ float tpc_ll_wait(const uint2* p, unsigned int e, int* status, unsigned int limit) {
+    for (unsigned int it = 0; it < limit; ++it) {
+        unsigned long long w;
+        asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+        if ((unsigned int)(w >> 32) == e) return __uint_as_float((unsigned int)w);
         if ((it & 1023u) == 1023u && *reinterpret_cast<volatile int*>(status) != 0) return 0.f;
     }
     atomicCAS(status, 0, TPC_ERR_FLAG_WAIT);

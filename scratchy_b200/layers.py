@@ -188,6 +188,8 @@ class AffineQuantLinear:
         tokens (`scr_linear_affine_b4_silu_mul`), the linear into `scratch` plus `scr_silu_mul_pairs8_bf16` above."""
         if not getattr(self, "pairs8", False):
             raise ValueError("forward_silu_mul needs a gate/up matrix built by load_rows_interleave8")
+        if self.linear_bias is not None:
+            raise ValueError("the fused silu*up epilogue has no bias end: a `.bias` on gate/up is refused, not dropped")
         x2 = x.reshape(-1, self.in_features).contiguous()
         M, inter = int(x2.shape[0]), self.out_features // 2
         dev = x2.device
@@ -213,8 +215,9 @@ class AffineQuantLinear:
             raise ScratchyCudaError(-4, f"bits={bits}: the cuda target implements the 4-bit preset only")
         if weight.dtype not in (torch.int32, torch.uint32):
             raise ValueError(f"`.weight` must be U32, got {weight.dtype}")
-        if scales.dtype != torch.bfloat16 or biases.dtype != torch.bfloat16:
-            raise ValueError("scales/biases must be bf16 for this build")
+        if scales.dtype not in (torch.bfloat16, torch.float16) or biases.dtype != scales.dtype:
+            raise ValueError(f"scales/biases must both be F16 or both BF16, got {scales.dtype} / {biases.dtype}")
+        scale_dtype = _lib.DTYPE_F16 if scales.dtype == torch.float16 else _lib.DTYPE_BF16
         if not weight.is_cuda:
             raise ScratchyCudaError(-5, "weights must be on a CUDA device (there is no CPU path)")
         dev = weight.device
@@ -230,7 +233,7 @@ class AffineQuantLinear:
         ctx.check(L.scr_affine_b4_repack_size(N, K, group_size, ctypes.byref(size)))
         packed = torch.empty(size.value, dtype=torch.uint8, device=dev)
         weight, scales, biases = weight.contiguous(), scales.contiguous(), biases.contiguous()
-        ctx.check(L.scr_affine_b4_repack(ctx.handle, _ptr(weight), _ptr(scales), _ptr(biases), N, K, group_size,
+        ctx.check(L.scr_affine_b4_repack(ctx.handle, _ptr(weight), _ptr(scales), _ptr(biases), scale_dtype, N, K, group_size,
                                          _ptr(packed), _stream(dev)))
         src = {"weight": weight, "scales": scales, "biases": biases} if keep_source else None
         return cls(packed, K, N, group_size, bits, linear_bias, src)
@@ -273,6 +276,8 @@ class AffineQuantLinear:
         """`residual += x @ W^T` (in place, bf16) and `normed = rmsnorm(residual, gain)`: one launch up to 16 tokens
         (`scr_linear_affine_b4_residual_rmsnorm`; `scratch` = ENDS_SCRATCH_BYTES, zeroed once by the caller), the
         linear into `delta` followed by `scr_fused_add_rmsnorm_bf16` above."""
+        if self.linear_bias is not None:
+            raise ValueError("the fused residual + norm epilogue has no bias end: a `.bias` is refused, not dropped")
         x2 = x.reshape(-1, self.in_features).contiguous()
         M = int(x2.shape[0])
         dev = x2.device

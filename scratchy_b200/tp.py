@@ -111,7 +111,10 @@ class OneShotAllReduce:
     Creating it allocates the rank's receive buffer and exchanges the IPC handles through the process
     group; every rank must then issue the same sequence of calls."""
 
-    def __init__(self, tp: TpWorld, device, max_elems: int, group: Optional[dist.ProcessGroup] = None):
+    def __init__(self, tp: TpWorld, device, max_elems: int, group: Optional[dist.ProcessGroup] = None,
+                 connect: bool = True):
+        """`connect=False` leaves the peers unconnected: ranks that are threads of one process then call
+        `connect_local` on each other (an IPC handle opens only in another process)."""
         import ctypes
         from . import _lib
         self.tp, self.max_elems = tp, int(max_elems)
@@ -123,7 +126,7 @@ class OneShotAllReduce:
         with torch.cuda.device(self.device):
             self._ctx.check(_lib.lib().scr_tp_comm_create(self._ctx.handle, tp.world, tp.rank, self.max_elems,
                                                           ctypes.byref(self._h), handle))
-            if tp.world > 1:
+            if tp.world > 1 and connect:
                 if not dist.is_initialized():
                     raise RuntimeError("torch.distributed is not initialised")
                 gathered = [None] * tp.world
@@ -132,6 +135,35 @@ class OneShotAllReduce:
                 self._ctx.check(_lib.lib().scr_tp_comm_connect(self._h, blob))
                 dist.barrier(group=group)
         self._group = group
+
+    @property
+    def base(self) -> int:
+        """Device address of this rank's receive buffer (`scr_tp_comm_base`), what in-process peers connect to."""
+        import ctypes
+        b = ctypes.c_void_p()
+        self._ctx.check(self._lib.lib().scr_tp_comm_base(self._h, ctypes.byref(b)))
+        return int(b.value)
+
+    def connect_local(self, bases, devices) -> None:
+        """`scr_tp_comm_connect_local`: ranks as threads of one process (the reference's `ThreadPoolExecutor`,
+        crates/serving/worker/src/threadpool.rs:1-16) connect through raw device pointers; `bases[r]`,
+        `devices[r]` = rank r's `base` and device index.  Call with this rank's device current."""
+        import ctypes
+        arr = (ctypes.c_void_p * self.tp.world)(*[ctypes.c_void_p(int(b)) for b in bases])
+        dev = (ctypes.c_int32 * self.tp.world)(*[int(d) for d in devices])
+        with torch.cuda.device(self.device):
+            self._ctx.check(self._lib.lib().scr_tp_comm_connect_local(self._h, arr, dev))
+
+    def set_wait_limit(self, polls: int) -> None:
+        """`scr_tp_comm_set_wait_limit`: polls before a kernel of this communicator gives up on a peer."""
+        self._ctx.check(self._lib.lib().scr_tp_comm_set_wait_limit(self._h, int(polls)))
+
+    def check_health(self) -> None:
+        """Synchronise and raise `ScratchyCudaError(SCR_E_TIMEOUT)` if a bounded wait ran out since the last
+        check (`scr_device_status`; the reference's `Executor::check_health`).  Call it once per step, after the
+        host has synchronised on the step's result anyway: while the status word is set every bounded wait on
+        this context gives up early."""
+        self._ctx.device_status(None)
 
     def all_reduce(self, part: torch.Tensor, out_bf16: Optional[torch.Tensor] = None,
                    out_f32: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -192,10 +192,12 @@ def test_prefill_gemm_llama_shapes_full_oracle(name, M):
     assert r <= REL_L2_TOL
 
 
-@pytest.mark.parametrize("name,M", [("gate", 2048), ("down", 2048), ("q", 512)])
+@pytest.mark.parametrize("M", [64, 512, 2048])
+@pytest.mark.parametrize("name", ["q", "k", "gate", "down"])
 def test_prefill_gemm_full_size_sampled_rows(name, M):
-    """Full benchmark sizes: the oracle evaluates a seeded subset of 24 token rows (each output row
-    depends only on its own activation row), and the whole output must be finite."""
+    """Every prefill cell of the Llama-3.2-3B sweep (o has q's shape, v has k's, up has gate's; each (M, N, K) picks
+    its own tile and split-K plan): the oracle evaluates a seeded subset of 24 token rows (each output row depends
+    only on its own activation row), and the whole output must be finite."""
     import torch
     K, N = synth.LLAMA_3_2_3B[name]
     w, s, b = synth.affine_int4_weights(N, K, 64, synth.seed_for("g4s", N, K))
@@ -372,3 +374,60 @@ def test_bias_is_refused_where_no_epilogue_has_it():
     layer.pairs8 = True
     with pytest.raises((ScratchyCudaError, ValueError)):
         layer.forward_silu_mul(torch.zeros((1, 128), dtype=torch.bfloat16, device="cuda"))
+
+
+def _f16_bits(a):
+    return np.asarray(a, np.float32).astype(np.float16).view(np.uint16)
+
+
+def test_f16_scales_kat_values_through_the_dump_hook():
+    """F16 scale/bias storage with bf16 activations — what every mlx-community 4-bit checkpoint ships
+    (crates/targets/metal/src/cpu_reference.rs:63-68).  The scale/bias/code triples of the reference's known-answer
+    test `dequant_b4_bf16_scale_bias_apply_per_group` (crates/targets/metal/tests/cpu_reference_test.rs:33-54: scale 2,
+    bias 1, codes 3,4,5,6 -> 7,9,11,13; scale 0.5, bias -1, codes 1,2,3,4 -> -0.5,0,0.5,1), laid out at this preset's
+    group size, must come back from the repacked buffer bit for bit."""
+    import torch
+    from scratchy_b200 import AffineQuantLinear
+    N, K = 16, 128
+    codes = np.zeros((N, K), np.uint32)
+    codes[0, 0:4] = [3, 4, 5, 6]
+    codes[0, 64:68] = [1, 2, 3, 4]
+    shifts = (np.arange(8, dtype=np.uint32) * 4)[None, None, :]
+    w = (codes.reshape(N, K // 8, 8) << shifts).sum(axis=2, dtype=np.uint32)
+    sc = np.ones((N, 2), np.float32)
+    bi = np.zeros((N, 2), np.float32)
+    sc[0] = [2.0, 0.5]
+    bi[0] = [1.0, -1.0]
+    layer = AffineQuantLinear.from_tensors(u32_dev(w), torch.from_numpy(_f16_bits(sc).view(np.float16)).cuda(),
+                                           torch.from_numpy(_f16_bits(bi).view(np.float16)).cuda(), 64, 4)
+    got = bits_of(layer.dequantize()).reshape(N, K)
+    from util import bf16_to_f32
+    assert bf16_to_f32(got[0, 0:4]).tolist() == [7.0, 9.0, 11.0, 13.0]
+    assert bf16_to_f32(got[0, 64:68]).tolist() == [-0.5, 0.0, 0.5, 1.0]
+    want = oracle.affine_dequant_b4(w.view(np.uint8).reshape(-1), _f16_bits(sc), _f16_bits(bi), N, K, 64, oracle.F16, oracle.BF16,
+                                    True)      # scale narrowed to the activation type first: cpu_reference.rs:90-92
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("N,K,M", [(3072, 3072, 1), (1024, 3072, 16), (256, 512, 100)])
+def test_f16_scales_match_the_oracle(N, K, M):
+    """F16 scales that are NOT bf16-representable (11 significant bits): the narrowing to the activation type at load
+    time must be the reference's (`TAct::from_f32(scale.to_f32())`, cpu_reference.rs:90-92) — dequantised weights bit
+    for bit, outputs within the bar."""
+    import torch
+    from scratchy_b200 import AffineQuantLinear
+    rng = np.random.default_rng(synth.seed_for("f16s", N, K, M))
+    w, _, _ = synth.affine_int4_weights(N, K, 64, synth.seed_for("f16w", N, K))
+    sc = (np.abs(rng.normal(0.0, 0.02, (N, K // 64))) + 1e-3).astype(np.float16)
+    bi = (-8.0 * sc.astype(np.float32) + rng.normal(0.0, 1e-3, (N, K // 64))).astype(np.float16)
+    x = synth.activations_bf16(M, K, synth.seed_for("f16x", N, K, M))
+    layer = AffineQuantLinear.from_tensors(u32_dev(w), torch.from_numpy(sc).cuda(), torch.from_numpy(bi).cuda(), 64, 4)
+    wd = bits_of(layer.dequantize()).reshape(N, K)
+    want_w = oracle.affine_dequant_b4(w.view(np.uint8).reshape(-1), sc.view(np.uint16), bi.view(np.uint16), N, K, 64, oracle.F16,
+                                      oracle.BF16, True)
+    assert np.array_equal(wd, want_w)
+    y = bits_of(layer.forward(bf16_dev(x).reshape(M, K))).reshape(M, N)
+    torch.cuda.synchronize()
+    want = oracle.affine_qmm_t_b4(w.view(np.uint8).reshape(-1), sc.view(np.uint16), bi.view(np.uint16), x, M, N, K, 64,
+                                  scale_dt=oracle.F16)
+    assert rel_l2(y, want) <= REL_L2_TOL

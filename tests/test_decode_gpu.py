@@ -403,6 +403,105 @@ def test_decode_step_matches_oracle_chain(batch, fuse_residual_norm, head_dim, b
     _lib.context(0).device_status(None)
 
 
+@pytest.mark.parametrize("batch", [1, 8])
+def test_llama_3b_layer_at_real_geometry_operator_by_operator(batch):
+    """One decoder layer at the Llama-3.2-3B geometry of the decode benchmark (hidden 3072, 24 query / 8 kv heads of
+    128, intermediate 8192, RoPE theta 500000, context 2048 in 16-token blocks): every operator of the step is given
+    the ORACLE's input for it (as the bf16 bits the device would hold) and must meet the per-operator bar — index and
+    byte work bit for bit, floating point within 1e-3 — so no operator hides behind the chain's accumulated error; then
+    the whole step through `LlamaDecoder.step` against the oracle chain."""
+    import torch
+    from scratchy_b200 import _lib, decode
+    f, r = bf16_to_f32, rbits
+    cfg = decode.LlamaConfig(hidden=3072, n_layers=1, n_q_heads=24, n_kv_heads=8, head_dim=128, intermediate=8192,
+                             vocab=4096, rope_theta=500000.0)
+    ck = decode.synthetic_checkpoint(cfg, seed=40 + batch)
+    dec = decode.LlamaDecoder(cfg, ck, "cuda:0", max_pos=2048)
+    layer = dec.layers[0]
+    bs, ctx = 16, 2048
+    max_blocks = ctx // bs
+    nblk = batch * max_blocks
+    rng = np.random.default_rng(batch)
+    table = rng.permutation(nblk).reshape(batch, max_blocks).astype(np.uint32)
+    hist_k = rbits(rng.standard_normal((nblk, cfg.n_kv_heads, bs, cfg.head_dim)))
+    hist_v = rbits(rng.standard_normal((nblk, cfg.n_kv_heads, bs, cfg.head_dim)))
+    cos, sin = decode.rope_tables(2048, cfg.head_dim, cfg.rope_theta)
+    ids = rng.integers(0, cfg.vocab, size=batch).astype(np.uint32)
+    pos = np.full(batch, ctx - 1, np.uint32)
+    if batch > 1:
+        pos[1:] = rng.integers(1, ctx - 1, size=batch - 1)                 # ragged histories, one of them full
+    used = (pos + 1).astype(np.uint32)
+    slots = np.array([table[b, pos[b] // bs] * bs + pos[b] % bs for b in range(batch)], np.uint32)
+    qd, kd = cfg.q_dim, cfg.kv_dim
+    root = "model.layers.0"
+
+    def check(name, got_bits, want_bits, exact=False):
+        if exact:
+            assert np.array_equal(got_bits, want_bits), f"{name}: must be bit-exact"
+        else:
+            e = rel_l2(got_bits, want_bits)
+            assert e <= REL_L2_TOL, f"{name}: rel-L2 {e:.3e}"
+
+    # embed, norm
+    residual = ck["model.embed_tokens.weight"][ids]
+    check("embed", bits_of(decode.embed(i32_dev(ids), dec.embed_table)), residual, exact=True)
+    normed = r(oracle.rmsnorm(f(residual), f(ck[f"{root}.input_layernorm.weight"]), cfg.rms_eps))
+    check("rmsnorm", bits_of(decode.rmsnorm(bf16_dev(residual), layer.input_norm, cfg.rms_eps)), normed)
+    # fused q|k|v projection
+    qkv = _oracle_linear(ck, [f"{root}.self_attn.{p}_proj" for p in "qkv"], normed, cfg.hidden)
+    check("qkv", bits_of(layer.qkv.forward(bf16_dev(normed))), qkv)
+    # RoPE + append + attention in one launch
+    ok, ov = f(hist_k).copy(), f(hist_v).copy()
+    fq = f(qkv)
+    q_rot = oracle.rope_append(fq[:, :qd], fq[:, qd:qd + kd], fq[:, qd + kd:], pos, slots, cos, sin, ok, ov, cfg.n_q_heads,
+                               cfg.n_kv_heads, cfg.head_dim, bs)
+    attn = r(oracle.attention_via_cache(f(r(q_rot)), f(r(ok)), ov, table, used, cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, bs,
+                                        np.float32(1.0 / math.sqrt(cfg.head_dim))))
+    t = bf16_dev(qkv)
+    ckd, cvd = bf16_dev(hist_k), bf16_dev(hist_v)
+    got_attn = decode.rope_attention_via_cache(t[:, :qd], t[:, qd:qd + kd], t[:, qd + kd:], i32_dev(pos), dec.cos, dec.sin, ckd, cvd,
+                                               i32_dev(table), i32_dev(used), cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, bs,
+                                               dec.attn_scale)
+    check("cache k", bits_of(ckd), r(ok), exact=True)
+    check("cache v", bits_of(cvd), r(ov), exact=True)
+    check("attention", bits_of(got_attn), attn)
+    # o projection, residual add + norm
+    delta = _oracle_linear(ck, [f"{root}.self_attn.o_proj"], attn, qd)
+    check("o", bits_of(layer.o.forward(bf16_dev(attn))), delta)
+    res, nrm = oracle.fused_add_rmsnorm(f(residual), f(delta), f(ck[f"{root}.post_attention_layernorm.weight"]), cfg.rms_eps,
+                                        round_residual_bf16=True)
+    res_d = bf16_dev(residual)
+    got_n = decode.fused_add_rmsnorm(res_d, bf16_dev(delta), layer.post_norm, cfg.rms_eps)
+    check("residual after o", bits_of(res_d), r(res), exact=True)
+    check("post-attention norm", bits_of(got_n), r(nrm))
+    # gate|up with silu*up in the epilogue, down projection
+    gu = f(_oracle_linear(ck, [f"{root}.mlp.gate_proj", f"{root}.mlp.up_proj"], r(nrm), cfg.hidden))
+    act = r(oracle.silu_mul(gu[:, :cfg.intermediate], gu[:, cfg.intermediate:]))
+    check("silu(gate)*up", bits_of(layer.gate_up.forward_silu_mul(bf16_dev(r(nrm)))), act)
+    delta2 = _oracle_linear(ck, [f"{root}.mlp.down_proj"], act, cfg.intermediate)
+    check("down", bits_of(layer.down.forward(bf16_dev(act))), delta2)
+    torch.cuda.synchronize()
+    _lib.context(0).device_status(None)
+
+    # the whole step through the decoder, from the same history
+    cache = decode.PagedKvCache(cfg, nblk, bs, "cuda:0")
+    cache.k[0].copy_(bf16_dev(hist_k))
+    cache.v[0].copy_(bf16_dev(hist_v))
+    buf = dec.buffers(batch, max_blocks)
+    buf.block_table.copy_(i32_dev(table))
+    buf.ids.copy_(i32_dev(ids))
+    buf.positions.copy_(i32_dev(pos))
+    buf.slot_mapping.copy_(i32_dev(slots))
+    buf.seq_used_k.copy_(i32_dev(used))
+    dec.step(buf, cache)
+    torch.cuda.synchronize()
+    want = _oracle_step(cfg, ck, ids, pos, slots, table, used, [f(hist_k).copy()], [f(hist_v).copy()], cos, sin, bs)
+    e = rel_l2(bits_of(buf.logits), want)
+    print(f"3B layer batch={batch}: logits rel-L2 {e:.3e}")
+    assert e <= STEP_REL_L2_TOL
+    _lib.context(0).device_status(None)
+
+
 def test_decode_ops_against_the_committed_fixture():
     """tests/golden/decode_ops_small.npz (written by tests/golden/make_golden.py from the oracle)."""
     import os

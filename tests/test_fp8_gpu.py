@@ -168,10 +168,12 @@ def test_prefill_gemm_qwen_shapes_full_oracle(name, M):
     assert r <= REL_L2_TOL
 
 
-@pytest.mark.parametrize("name,M", [("gate", 2048), ("down", 2048), ("gate", 8192)])
+@pytest.mark.parametrize("M", [256, 2048, 8192])
+@pytest.mark.parametrize("name", ["q", "k", "gate", "down"])
 def test_prefill_gemm_full_size_sampled_rows(name, M):
-    """Full benchmark sizes: oracle on a seeded subset of 16 token rows; x_q and a_scale of those rows
-    must be bit-exact and the outputs within tolerance; the whole output must be finite."""
+    """Every prefill cell of the Qwen2.5-7B sweep (v has k's shape, up has gate's; down at 8192 tokens takes the
+    tail-split plan): oracle on a seeded subset of 16 token rows; x_q and a_scale of those rows must be bit-exact
+    and the outputs within tolerance; the whole output must be finite."""
     import torch
     from scratchy_b200 import Fp8Linear
     K, N = synth.QWEN_2_5_7B[name]

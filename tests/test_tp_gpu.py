@@ -55,6 +55,42 @@ def test_fp8_row_parallel_partials_one_gpu(W, M):
     assert rel_l2(got, want) <= REL_L2_TOL
 
 
+@pytest.mark.parametrize("name,M", [("o", 1), ("o", 4), ("o", 32), ("down", 1), ("down", 4)])
+def test_llama_70b_row_parallel_shards_at_tp8(name, M):
+    """The Llama-3-70B row-parallel shapes of the tensor-parallel benchmark configuration at world size 8 (o: 1024 of
+    8192 input features per rank, down: 3584 of 28672; 8192 outputs), every rank's shard run on this one GPU:
+    (i) the f32 partials summed in rank order and rounded once against the lockstep oracle, (ii) every rank's partial
+    against the oracle's, (iii) for the self-quantising matvec sizes, the matvec with the exchange in its epilogue on
+    a one-rank communicator against the ORACLE's rounded partial of that rank (not against the partial path)."""
+    import torch
+    from scratchy_b200 import Fp8Linear, tp as tpmod
+    W = 8
+    K, N = synth.LLAMA_3_70B[name]
+    wq, ws = oracle.fp8_quantize_weight_per_channel(synth.fp8_weights_f32(N, K, synth.seed_for("tp70", N, K)))
+    x = synth.activations_bf16(M, K, synth.seed_for("tp70x", N, K, M))
+    want, want_parts = lockstep_fp8_row_parallel(wq, ws, x, W)
+    dev = torch.device("cuda", 0)
+    one = tpmod.OneShotAllReduce(tpmod.TpWorld(1, 0), dev, max_elems=M * N)
+    parts = []
+    for r in range(W):
+        lin = Fp8Linear.from_tensors(to_dev(oracle.slice_cols(wq, W, r)), to_dev(ws))
+        xr = bf16_dev(oracle.slice_cols(x, W, r)).reshape(M, K // W)
+        part = lin.forward_partial(xr)
+        parts.append(part.cpu().numpy())
+        assert rel_l2(oracle.f32_to_bf16_bits(parts[-1]), oracle.f32_to_bf16_bits(want_parts[r])) <= REL_L2_TOL, f"rank {r} partial"
+        if one.fp8_linear_all_reduce_supported(lin, M):
+            fused = one.fp8_linear_all_reduce(lin, xr)
+            torch.cuda.synchronize()
+            assert rel_l2(bits_of(fused), oracle.f32_to_bf16_bits(want_parts[r])) <= REL_L2_TOL, f"rank {r} fused"
+    torch.cuda.synchronize()
+    got = oracle.f32_to_bf16_bits(oracle.allreduce_rank_order(parts))
+    r = rel_l2(got, want)
+    print(f"70B {name} TP=8 M={M} rel_l2={r:.3e}")
+    assert r <= REL_L2_TOL
+    __import__("scratchy_b200")._lib.context(0).device_status(None)
+    one.close()
+
+
 def _nccl_worker(rank, world, port, q):
     import torch
     import torch.distributed as dist
@@ -156,23 +192,117 @@ def _nccl_worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
-def test_two_ranks_nccl_row_parallel():
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_ranks_nccl_row_parallel(world):
+    """One process per GPU at world sizes 2, 4 and 8 (each needs that many devices): both exchange paths and the
+    matvec with the exchange in its epilogue against the lockstep oracle at the same world size."""
     import torch
     import torch.multiprocessing as mp
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     with socket.socket() as sk:
         sk.bind(("127.0.0.1", 0))
         port = sk.getsockname()[1]
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_nccl_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_nccl_worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
-    res = [q.get(timeout=300) for _ in procs]
+    res = [q.get(timeout=600) for _ in procs]
     for p in procs:
         p.join(timeout=60)
-    assert sorted(res) == [(0, True), (1, True)]
+    assert sorted(res) == [(r, True) for r in range(world)]
+
+
+def test_ranks_as_threads_of_one_process_connect_locally():
+    """The reference's executor drives its ranks as threads of ONE process (crates/serving/worker/src/threadpool.rs:1-16):
+    such ranks cannot open each other's IPC handles and connect through raw device pointers instead
+    (`scr_tp_comm_connect_local`).  World 1 on one GPU always; two host threads on two GPUs when they exist."""
+    import threading
+    import torch
+    from scratchy_b200 import _lib, tp as tpmod
+    dev0 = torch.device("cuda", 0)
+    one = tpmod.OneShotAllReduce(tpmod.TpWorld(1, 0), dev0, max_elems=8192, connect=False)
+    one.connect_local([one.base], [0])
+    part = torch.from_numpy(np.random.default_rng(1).standard_normal((2, 1024)).astype(np.float32)).to(dev0)
+    got = one.all_reduce(part)
+    torch.cuda.synchronize()
+    assert np.array_equal(bits_of(got), oracle.f32_to_bf16_bits(part.cpu().numpy()))
+    one.close()
+    if torch.cuda.device_count() < 2:
+        return
+    world = 2
+    rng = np.random.default_rng(11)
+    small = [rng.standard_normal((3, 1024)).astype(np.float32) * (1.0 + r) for r in range(world)]
+    large = [rng.standard_normal((40, 1024)).astype(np.float32) * (1.0 + r) for r in range(world)]
+    comms, results, errors = [None] * world, [None] * world, []
+    gate = threading.Barrier(world)
+
+    def rank_thread(r):
+        try:
+            dev = torch.device("cuda", r)
+            torch.cuda.set_device(dev)
+            comms[r] = tpmod.OneShotAllReduce(tpmod.TpWorld(world, r), dev, max_elems=64 * 1024, connect=False)
+            gate.wait()
+            comms[r].connect_local([c.base for c in comms], list(range(world)))
+            gate.wait()
+            out = []
+            for parts in (small, large, small):                 # packets, dense stores + flags, packets again
+                got = comms[r].all_reduce(torch.from_numpy(parts[r]).to(dev))
+                torch.cuda.synchronize(dev)
+                out.append(bits_of(got))
+            results[r] = out
+            _lib.context(r).device_status(None)
+            gate.wait()                                          # nobody frees a buffer a peer may still write
+            comms[r].close()
+        except Exception as exc:                                 # a failing rank must not leave the other at the barrier
+            errors.append(exc)
+            gate.abort()
+
+    threads = [threading.Thread(target=rank_thread, args=(r,)) for r in range(world)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout=120)
+    assert not errors, errors
+    for r in range(world):
+        for got, parts in zip(results[r], (small, large, small)):
+            assert np.array_equal(got, oracle.f32_to_bf16_bits(oracle.allreduce_rank_order(parts)))
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_and_the_next_call_works():
+    """Failure detection without a fault: a world-2 communicator on ONE GPU whose second "peer" is the rank's own
+    buffer, so nothing ever writes rank 1's slots.  With a short poll limit the exchange kernels give up, return,
+    and `scr_device_status` reports SCR_E_TIMEOUT; the context stays usable and the next call on an ordinary
+    communicator gives the right bits."""
+    import torch
+    from scratchy_b200 import Fp8Linear, _lib, tp as tpmod
+    dev = torch.device("cuda", 0)
+    ctx = _lib.context(0)
+    ctx.device_status(None)
+    lame = tpmod.OneShotAllReduce(tpmod.TpWorld(2, 0), dev, max_elems=64 * 1024, connect=False)
+    lame.connect_local([lame.base, lame.base], [0, 0])
+    lame.set_wait_limit(1 << 12)
+    wq, ws = oracle.fp8_quantize_weight_per_channel(synth.fp8_weights_f32(512, 1024, 9))
+    lin = Fp8Linear.from_tensors(to_dev(wq), to_dev(ws))
+    x = bf16_dev(synth.activations_bf16(1, 1024, 10)).reshape(1, 1024)
+    calls = [lambda: lame.all_reduce(torch.ones((2, 1024), device=dev)),           # packets
+             lambda: lame.all_reduce(torch.ones((40, 1024), device=dev)),          # dense stores + flags
+             lambda: lame.fp8_linear_all_reduce(lin, x)]                           # the matvec that exchanges in its epilogue
+    for i, call in enumerate(calls):
+        call()
+        with pytest.raises(_lib.ScratchyCudaError) as e:
+            lame.check_health()
+        assert e.value.status == -8, f"call {i}: expected SCR_E_TIMEOUT, got {e.value.name}"
+        ctx.device_status(None)                                                    # read and cleared: healthy again
+    lame.close()
+    good = tpmod.OneShotAllReduce(tpmod.TpWorld(1, 0), dev, max_elems=8192)
+    part = torch.from_numpy(np.random.default_rng(2).standard_normal((4, 1024)).astype(np.float32)).to(dev)
+    got = good.all_reduce(part)
+    torch.cuda.synchronize()
+    assert np.array_equal(bits_of(got), oracle.f32_to_bf16_bits(part.cpu().numpy()))
+    ctx.device_status(None)
+    good.close()
 
 
 def test_one_shot_all_reduce_single_rank():
