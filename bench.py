@@ -51,6 +51,11 @@ def fp8_alg_bytes(M, N, K):
     return N * K + 4 * N + 2 * M * K + 2 * M * N
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of affine_b4_gemv_kernel at M = 1, by shape, from the ncu
+# captures summarised in profiles/affine_b4_gemv_llama3b_m1_full.md (weights cross HBM once; activations come from L2)
+GEMV_DRAM_TRAFFIC = {"q": 5335808, "o": 5335808, "k": 1797120, "v": 1797120, "gate": 14181120, "up": 14181120, "down": 14191360}
+
+
 def measured_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -128,6 +133,7 @@ def time_cpu_layer(reps: int, n_lin: int = 7):
     """One 'sample' = the first `n_lin` of the 7 int4 linears of one Llama-3.2-3B layer at M = 1 through the
     oracle; returns (algorithmic GB/s, seconds per sample, threads)."""
     oracle, data = cpu_linears()
+    oracle.set_num_threads(os.cpu_count() or 1)       # launchers export OMP_NUM_THREADS=1: use the host's cores all the same
     data = data[:n_lin]
     byts = sum(affine_alg_bytes(1, N, K) for *_, N, K in data)
     oracle.affine_qmm_t_b4(*data[0][:4], 1, data[0][4], data[0][5], 64)    # warm the thread pool
@@ -428,6 +434,9 @@ def run_gpu(args):
         extra["fused_projections"] = fused_info
     if tape_info:
         extra["tape"] = tape_info
+    if world == 1:
+        extra["config0"] = run_config0(device, peaks)
+        extra["prefill"] = run_prefill_extra(device, peaks)
     if world == 1 and not args.no_decode:
         del layers, graph, graph_e2e
         layers = graph = graph_e2e = None
@@ -451,13 +460,16 @@ def run_gpu(args):
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "llama-3.2-3b int4 g64 linears (q,k,v,o,gate,up,down) x 28 layers, M=1",
                        "bytes_per_step": step_bytes, "l2": "inputs larger than L2 (1.585 GB of distinct weights per step)",
+                       "dependencies": "stream order only: the linears of one shape share one input and one output buffer, so a linear "
+                                       "waits for its predecessors without consuming their values (a weight-stream measurement)",
                        "replicas": world, "launch": "one CUDA graph of 196 matvec launches per step; q/k/v and gate/up on parallel branches"
                        if not args.serial else "one CUDA graph of 196 matvec launches per step, one branch"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"],
-                         # dram__bytes_read+write per launch from the ncu capture summarised under profiles/
-                         # (launch-weighted mean over the 7 shapes; 1.0016 x the algorithmic bytes)
-                         "traffic": 8117138, "peak_source": peaks["src"],
+                         # launch-weighted mean over the 7 shapes of the per-shape ncu figures (GEMV_DRAM_TRAFFIC)
+                         "traffic": sum(GEMV_DRAM_TRAFFIC[n] for n in LAYER_ORDER) / len(LAYER_ORDER),
+                         "traffic_source": "ncu dram__bytes_read+write per launch, by shape: profiles/affine_b4_gemv_llama3b_m1_full.md",
+                         "peak_source": peaks["src"],
                          "kernel": "affine_b4_gemv_kernel", "avg_launch_us": per_launch_us,
                          "alg_bytes_per_launch": step_bytes / (N_LAYERS * len(LAYER_ORDER))},
             "cpu_baseline": {"value": cpu_v, "unit": UNIT, "cores": cores, "kind": "port",
@@ -470,6 +482,107 @@ def run_gpu(args):
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def _time_calls(device, calls, replays):
+    """One CUDA graph over `calls` (each on its own weight copy), replayed; seconds per call."""
+    import torch
+    for c in calls[:2]:
+        c()
+    torch.cuda.synchronize(device)
+    side = torch.cuda.Stream(device)
+    gr = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(gr, stream=side):
+        for c in calls:
+            c()
+    for _ in range(3):
+        gr.replay()
+    torch.cuda.synchronize(device)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(replays):
+        gr.replay()
+    b.record()
+    torch.cuda.synchronize(device)
+    return a.elapsed_time(b) * 1e-3 / (replays * len(calls))
+
+
+def _int4_copies(device, N, K, copies):
+    import torch
+    from scratchy_b200 import AffineQuantLinear
+    lins = []
+    for c in range(copies):
+        g = torch.Generator(device=device)
+        g.manual_seed(7000 + c)
+        w = torch.randint(-2 ** 31, 2 ** 31 - 1, (N, K // 8), dtype=torch.int32, device=device, generator=g)
+        s = (torch.randn((N, K // 64), device=device, generator=g) * 0.02).abs().add(1e-3).to(torch.bfloat16)
+        b = (-8.0 * s.float() + torch.randn((N, K // 64), device=device, generator=g) * 1e-3).to(torch.bfloat16)
+        lins.append(AffineQuantLinear.from_tensors(w, s, b, 64, 4))
+    return lins
+
+
+def run_config0(device, peaks):
+    """Benchmark configuration 0 on its own: the single MLX int4 linear M = 1, K = 3072, N = 8192, timed over 29 distinct
+    weight copies (411 MB, larger than L2) inside one CUDA graph — no neighbour prefetches for it."""
+    import torch
+    N, K, M = 8192, 3072, 1
+    lins = _int4_copies(device, N, K, 29)
+    x = torch.randn((M, K), device=device).to(torch.bfloat16)
+    y = torch.empty((M, N), dtype=torch.bfloat16, device=device)
+    dt = _time_calls(device, [(lambda l=l: l.forward(x, out=y)) for l in lins], 20)
+    byts = affine_alg_bytes(M, N, K)
+    return {"workload": "one int4 g64 linear, M=1, K=3072, N=8192, 29 rotating weight copies (larger than L2)", "us": dt * 1e6,
+            "alg_bytes": byts, "GBps": byts / dt / 1e9, "frac_hbm_measured": byts / dt / 1e9 / peaks["hbm_gbs"],
+            "frac_hbm_nominal_8000": byts / dt / 1e9 / 8000.0}
+
+
+def run_prefill_extra(device, peaks):
+    """A bounded sample of the prefill and fp8 sweeps for the default line: int4 gate at 2048 tokens, fp8 gate at 2048 and
+    8192 tokens (quantise + GEMM), fp8 gate at one token.  The fp8 tensor peak is not in the measured-peaks file: fractions are
+    quoted against 2 x the measured bf16 burst figure (named as such), against a library fp8 GEMM measured here the same way
+    (`torch._scaled_mm`, 8192^3), and against the nominal 4500 TFLOP/s."""
+    import torch
+    from scratchy_b200 import Fp8Linear
+    out = []
+    fp8_lib = measure_fp8_peak(device)
+    K, N = synth.LLAMA_3_2_3B["gate"]
+    lins = _int4_copies(device, N, K, 4)
+    M = 2048
+    x = torch.randn((M, K), device=device).to(torch.bfloat16)
+    y = torch.empty((M, N), dtype=torch.bfloat16, device=device)
+    ws = torch.empty(max(16, lins[0].workspace_bytes(M)), dtype=torch.uint8, device=device)
+    dt = _time_calls(device, [(lambda l=l: l.forward(x, out=y, workspace=ws)) for l in lins], 5)
+    tf = 2.0 * M * N * K / dt / 1e12
+    out.append({"kind": "int4", "shape": "gate", "M": M, "N": N, "K": K, "us": dt * 1e6, "TFLOPs": tf,
+                "frac_bf16_measured": tf / peaks["bf16_tflops"], "frac_bf16_nominal_2250": tf / 2250.0})
+    del lins, x, y, ws
+    K, N = synth.QWEN_2_5_7B["gate"]
+    copies = 4
+    flins = []
+    for c in range(copies):
+        g = torch.Generator(device=device)
+        g.manual_seed(7100 + c)
+        w = torch.randint(0, 0x7E, (N, K), dtype=torch.uint8, device=device, generator=g)
+        flins.append(Fp8Linear.from_tensors(w, torch.rand(N, device=device, generator=g) * 1e-3 + 1e-4))
+    for M in (1, 2048, 8192):
+        x = torch.randn((M, K), device=device).to(torch.bfloat16)
+        y = torch.empty((M, N), dtype=torch.bfloat16, device=device)
+        ws = torch.empty(max(16, flins[0].workspace_bytes(M)), dtype=torch.uint8, device=device)
+        dt = _time_calls(device, [(lambda l=l: l.forward(x, out=y, workspace=ws)) for l in flins], 20 if M == 1 else 3)
+        tf = 2.0 * M * N * K / dt / 1e12
+        row = {"kind": "fp8", "shape": "gate", "M": M, "N": N, "K": K, "us": dt * 1e6}
+        if M == 1:
+            row.update({"GBps": fp8_alg_bytes(M, N, K) / dt / 1e9, "frac_hbm_measured": fp8_alg_bytes(M, N, K) / dt / 1e9 / peaks["hbm_gbs"],
+                        "note": "one launch: the matvec quantises the activation itself; 4 copies x 68 MB rotate (larger than L2)"})
+        else:
+            row.update({"TFLOPs": tf, "frac_of_2x_bf16_measured": tf / (2.0 * peaks["bf16_tflops"]),
+                        "frac_of_scaled_mm_8192": (tf / fp8_lib) if fp8_lib else None, "frac_fp8_nominal_4500": tf / 4500.0,
+                        "note": "per-token quantise + GEMM (two launches)"})
+        out.append(row)
+        del x, y, ws
+    out.append({"kind": "peaks", "bf16_tflops_measured": peaks["bf16_tflops"], "fp8_tflops_scaled_mm_8192": fp8_lib,
+                "fp8_tflops_nominal": 4500.0, "hbm_gbs_measured": peaks["hbm_gbs"]})
+    return out
 
 
 def measure_fp8_peak(device):
@@ -625,35 +738,75 @@ def run_decode(device, steps=20, batches=(1, 8, 32), context=2048, block_size=16
     return out
 
 
+TP_H, TP_QKV, TP_FF = 8192, 10240, 28672          # Llama-3-70B: hidden, q|k|v rows (64 q + 2 x 8 kv heads of 128), intermediate
+TP_CHUNK_ROWS = 1024                              # prefill rows per pipeline chunk (chunk i's exchange overlaps chunk i+1's GEMMs)
+
+
+def tp_parity_check(device, world, rank, tpw, one, fuse_exchange):
+    """In-run value check of the tensor-parallel row-parallel path on the real ranks: a seeded o-projection
+    (8192 -> 8192, every rank its K-slice) at M = 1, 32 and 256 through the very calls the timed step makes, rank 0
+    against the lockstep oracle (every rank's f32 partial, summed in rank order, rounded once) on a seeded sample of
+    output channels.  Returns "ok" or a description of the first failure; every rank takes part."""
+    import torch
+    import oracle
+    from scratchy_b200 import Fp8Linear, tp as tpmod
+    H = TP_H
+    rng = np.random.default_rng(1234)
+    wq = rng.integers(0, 0x7E, size=(H, H), dtype=np.uint8)                 # finite e4m3 patterns
+    wsc = (rng.random(H) * 1e-3 + 1e-4).astype(np.float32)
+    cols = np.sort(rng.choice(H, 256, replace=False))
+    lo, hi = rank * (H // world), (rank + 1) * (H // world)
+    lin = Fp8Linear.from_tensors(torch.from_numpy(np.ascontiguousarray(wq[:, lo:hi])).to(device), torch.from_numpy(wsc).to(device))
+    comm = tpmod.TpCommunicator(tpw)
+    verdict = "ok"
+    for M in (1, 32, 256):
+        x = synth.activations_bf16(M, H, 77 + M)
+        xl = torch.from_numpy(np.ascontiguousarray(x[:, lo:hi]).view(np.int16)).view(torch.bfloat16).to(device)
+        if world == 1:
+            y = tpmod.partial_to_bf16(lin.forward_partial(xl))
+        elif one is not None and fuse_exchange and one.fp8_linear_all_reduce_supported(lin, M):
+            y = one.fp8_linear_all_reduce(lin, xl)
+        elif one is not None and M * H <= one.max_elems:
+            y = one.all_reduce(lin.forward_partial(xl))
+        else:
+            part = lin.forward_partial(xl)
+            comm.all_reduce(part)
+            y = tpmod.partial_to_bf16(part)
+        torch.cuda.synchronize(device)
+        if rank == 0 and verdict == "ok":
+            rows = np.arange(M) if M <= 32 else np.sort(rng.choice(M, 16, replace=False))
+            parts = []
+            for r in range(world):
+                sl = slice(r * (H // world), (r + 1) * (H // world))
+                _, pf = oracle.fp8_dynamic_linear(np.ascontiguousarray(x[rows][:, sl]), np.ascontiguousarray(wq[cols][:, sl]),
+                                                  wsc[cols], len(rows), len(cols), H // world, want_f32=True)
+                parts.append(pf)
+            want = synth.bf16_bits_to_f32(oracle.f32_to_bf16_bits(oracle.allreduce_rank_order(parts))).astype(np.float64)
+            got = y.float().cpu().numpy()[rows][:, cols].astype(np.float64)
+            err = float(np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30))
+            if not err <= 1e-3:
+                verdict = f"M={M}: rel-L2 {err:.3e} against the lockstep oracle"
+    return verdict
+
+
 def run_tp(device, world, rank, fuse_exchange=True):
     """Benchmark configuration 4: Llama-3-70B-shaped fp8 per-channel linears, tensor parallel over `world`
-    GPUs: column-parallel qkv and gate/up, row-parallel o and down, each followed by the all-reduce
-    of the f32 partials [M, 8192] and one rounding to bf16 — the one-shot peer-memory kernel
-    (`scr_tp_allreduce_partial`) up to M = 64, the process group's NCCL all-reduce above.  One
-    "layer" = qkv, o, gate_up, down (attention and the activation function are outside the path:
-    the row-parallel inputs are fixed buffers of their shapes).  Weights are random e4m3 bytes of
-    the per-rank shard shapes; three layer copies rotate so that small-M steps read HBM, not L2."""
+    GPUs: column-parallel qkv and gate/up, row-parallel o and down, each followed by the all-reduce of the f32
+    partials [M, 8192] in rank order and one rounding to bf16 — inside the row-parallel matvec's epilogue up to 4
+    tokens, the stand-alone peer-memory kernel above (packets, dense one-shot, or — from 16 tokens on — the two-phase
+    reduce-scatter + all-gather form, `scr_tp_allreduce_partial`).  Prefill batches run as chunks of 1024 rows on two
+    streams, so that one chunk's exchange overlaps the next chunk's GEMMs.  One "layer" = qkv, o, gate_up, down
+    (attention and the activation function are outside the path: the row-parallel inputs are fixed buffers of their
+    shapes).  Weights are random e4m3 bytes; three layer copies rotate so that small-M steps read HBM, not L2.
+    Every rank first times the unsharded (TP = 1) stack on its own GPU: `efficiency` = t(TP=1) / (W * t(TP=W))."""
     import torch
     import torch.distributed as dist
-    from scratchy_b200 import Fp8Linear, tp as tpmod
+    from scratchy_b200 import Fp8Linear, _lib, tp as tpmod
     tpw = tpmod.TpWorld(world, rank)
-    comm = tpmod.TpCommunicator(tpw)
-    H, QKV, FF = 8192, 10240, 28672
+    H, QKV, FF = TP_H, TP_QKV, TP_FF
     copies = 3
-    one_shot_max_m = 64
-    one, one_note = None, None
-    if world > 1:
-        # every rank must take the same path: agree on whether the peer-memory exchange came up everywhere
-        try:
-            one = tpmod.OneShotAllReduce(tpw, device, max_elems=one_shot_max_m * H)
-            ok = torch.ones(1, device=device)
-        except Exception as exc:                                  # e.g. peer access unavailable between two GPUs
-            one_note = f"one-shot exchange unavailable ({type(exc).__name__}); NCCL used"
-            ok = torch.zeros(1, device=device)
-        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-        if float(ok[0]) == 0.0:
-            one = None
-            one_note = one_note or "one-shot exchange unavailable on another rank; NCCL used"
+    Ms = [1, 32, 256, 8192]
+    side = [torch.cuda.Stream(device) for _ in range(2)]
 
     def lin(n, k, seed):
         g = torch.Generator(device=device)
@@ -661,71 +814,10 @@ def run_tp(device, world, rank, fuse_exchange=True):
         w = torch.randint(0, 0x7E, (n, k), dtype=torch.uint8, device=device, generator=g)
         return Fp8Linear.from_tensors(w, torch.rand(n, device=device, generator=g) * 1e-3 + 1e-4)
 
-    layers = []
-    for c in range(copies):
-        layers.append({"qkv": lin(QKV // world, H, 10 * c + 1), "o": lin(H, H // world, 10 * c + 2),
-                       "gate_up": lin(2 * FF // world, H, 10 * c + 3), "down": lin(H, FF // world, 10 * c + 4)})
-    out = []
-    side = torch.cuda.Stream(device)
-    for M in [1, 32, 256, 8192]:
-        x = torch.randn((M, H), device=device).to(torch.bfloat16)
-        ws = torch.empty(max(l.workspace_bytes(M) for l in layers[0].values()), dtype=torch.uint8, device=device)
-        bufs = {"qkv": torch.empty((M, QKV // world), dtype=torch.bfloat16, device=device),
-                "gu": torch.empty((M, 2 * FF // world), dtype=torch.bfloat16, device=device),
-                "po": torch.empty((M, H), dtype=torch.float32, device=device),
-                "pd": torch.empty((M, H), dtype=torch.float32, device=device),
-                "h": torch.empty((M, H), dtype=torch.bfloat16, device=device),
-                "y": torch.empty((M, H), dtype=torch.bfloat16, device=device),
-                "attn": torch.randn((M, H // world), device=device).to(torch.bfloat16),
-                "act": torch.randn((M, FF // world), device=device).to(torch.bfloat16)}
-        use_one_shot = one is not None and M <= one_shot_max_m
-
-        def reduce_round(part, dst):
-            if world == 1:                       # nothing to exchange: the partial is the sum
-                dst.copy_(tpmod.partial_to_bf16(part))
-            elif use_one_shot:
-                one.all_reduce(part, out_bf16=dst)
-            else:
-                comm.all_reduce(part)
-                dst.copy_(tpmod.partial_to_bf16(part))
-            return dst
-
-        # a few tokens: the row-parallel matvec pushes its partials to the peers and sums in its own epilogue
-        fused = (use_one_shot and fuse_exchange and one.fp8_linear_all_reduce_supported(layers[0]["o"], M)
-                 and one.fp8_linear_all_reduce_supported(layers[0]["down"], M))
-
-        def layer_step(L):
-            L["qkv"].forward(x, out=bufs["qkv"], workspace=ws)
-            if fused:
-                h = one.fp8_linear_all_reduce(L["o"], bufs["attn"], out=bufs["h"])
-            else:
-                L["o"].forward_partial(bufs["attn"], out=bufs["po"], workspace=ws)
-                h = reduce_round(bufs["po"], bufs["h"])
-            L["gate_up"].forward(h, out=bufs["gu"], workspace=ws)
-            if fused:
-                return one.fp8_linear_all_reduce(L["down"], bufs["act"], out=bufs["y"])
-            L["down"].forward_partial(bufs["act"], out=bufs["pd"], workspace=ws)
-            return reduce_round(bufs["pd"], bufs["y"])
-
-        def step():
-            for L in layers:
-                layer_step(L)
-
-        step()
-        torch.cuda.synchronize(device)
-        mode = "graph"
-        try:
-            gr = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(gr, stream=side):
-                step()
-            run = gr.replay
-        except Exception:
-            mode = "eager"
-            run = step
-        reps = 20 if M <= 256 else 3
+    def time_run(run, reps, sync_ranks):
         for _ in range(3):
             run()
-        if world > 1:
+        if sync_ranks:
             dist.barrier()
         torch.cuda.synchronize(device)
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -735,26 +827,159 @@ def run_tp(device, world, rank, fuse_exchange=True):
         b.record()
         torch.cuda.synchronize(device)
         t = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=device)
-        if world > 1:
+        if sync_ranks:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        us_layer = float(t[0]) * 1e3 / (reps * copies)
+        return float(t[0]) * 1e3 / (reps * copies)                  # us per layer
+
+    def graph_of(step):
+        step()
+        torch.cuda.synchronize(device)
+        try:
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=side[0]):
+                step()
+            return gr.replay, "graph", gr
+        except Exception:
+            return step, "eager", None
+
+    # ---- the unsharded stack on this GPU (no exchange: the partial is the sum)
+    t1 = {}
+    if world > 1:
+        layers1 = [{"qkv": lin(QKV, H, 10 * c + 1), "o": lin(H, H, 10 * c + 2), "gate_up": lin(2 * FF, H, 10 * c + 3),
+                    "down": lin(H, FF, 10 * c + 4)} for c in range(copies)]
+        for M in Ms:
+            x = torch.randn((M, H), device=device).to(torch.bfloat16)
+            act = torch.randn((M, FF), device=device).to(torch.bfloat16)
+            ws = torch.empty(max(l.workspace_bytes(M) for l in layers1[0].values()), dtype=torch.uint8, device=device)
+            o_qkv = torch.empty((M, QKV), dtype=torch.bfloat16, device=device)
+            o_gu = torch.empty((M, 2 * FF), dtype=torch.bfloat16, device=device)
+            h = torch.empty((M, H), dtype=torch.bfloat16, device=device)
+            y = torch.empty((M, H), dtype=torch.bfloat16, device=device)
+
+            def step1():
+                for L in layers1:
+                    L["qkv"].forward(x, out=o_qkv, workspace=ws)
+                    L["o"].forward(x, out=h, workspace=ws)
+                    L["gate_up"].forward(h, out=o_gu, workspace=ws)
+                    L["down"].forward(act, out=y, workspace=ws)
+            run, _, gr = graph_of(step1)
+            t1[M] = time_run(run, 20 if M <= 256 else 3, sync_ranks=False)
+            del gr, x, act, ws, o_qkv, o_gu
+        del layers1
+        torch.cuda.empty_cache()
+
+    # ---- the peer-memory exchange (every rank must take the same path: agree on whether it came up everywhere)
+    ones, one_note = [None, None], None
+    if world > 1:
+        try:
+            ones = [tpmod.OneShotAllReduce(tpw, device, max_elems=TP_CHUNK_ROWS * H) for _ in range(2)]    # one per stream
+            ok = torch.ones(1, device=device)
+        except Exception as exc:                                  # e.g. peer access unavailable between two GPUs
+            one_note = f"peer-memory exchange unavailable ({type(exc).__name__}); NCCL used"
+            ok = torch.zeros(1, device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if float(ok[0]) == 0.0:
+            ones = [None, None]
+            one_note = one_note or "peer-memory exchange unavailable on another rank; NCCL used"
+    one = ones[0]
+    comm = tpmod.TpCommunicator(tpw)
+    parity = tp_parity_check(device, world, rank, tpw, one, fuse_exchange)
+
+    layers = []
+    for c in range(copies):
+        layers.append({"qkv": lin(QKV // world, H, 10 * c + 1), "o": lin(H, H // world, 10 * c + 2),
+                       "gate_up": lin(2 * FF // world, H, 10 * c + 3), "down": lin(H, FF // world, 10 * c + 4)})
+    out = []
+    for M in Ms:
+        rows = min(M, TP_CHUNK_ROWS)
+        n_chunks = M // rows
+        lanes = 2 if n_chunks > 1 and one is not None else 1      # pipeline lanes (streams), each with its own buffers
+        x = torch.randn((M, H), device=device).to(torch.bfloat16)
+        attn = torch.randn((M, H // world), device=device).to(torch.bfloat16)
+        act = torch.randn((M, FF // world), device=device).to(torch.bfloat16)
+        ws_bytes = max(l.workspace_bytes(rows) for l in layers[0].values())
+        lane_bufs = [{"ws": torch.empty(ws_bytes, dtype=torch.uint8, device=device),
+                      "qkv": torch.empty((rows, QKV // world), dtype=torch.bfloat16, device=device),
+                      "gu": torch.empty((rows, 2 * FF // world), dtype=torch.bfloat16, device=device),
+                      "po": torch.empty((rows, H), dtype=torch.float32, device=device),
+                      "pd": torch.empty((rows, H), dtype=torch.float32, device=device),
+                      "h": torch.empty((rows, H), dtype=torch.bfloat16, device=device),
+                      "y": torch.empty((rows, H), dtype=torch.bfloat16, device=device)} for _ in range(lanes)]
+        use_peer = one is not None and rows * H <= one.max_elems
+        # a few tokens: the row-parallel matvec pushes its partials to the peers and sums in its own epilogue
+        fused = (use_peer and fuse_exchange and one.fp8_linear_all_reduce_supported(layers[0]["o"], M)
+                 and one.fp8_linear_all_reduce_supported(layers[0]["down"], M))
+
+        def reduce_round(part, dst, lane):
+            if world == 1:                       # nothing to exchange: the partial is the sum
+                dst.copy_(tpmod.partial_to_bf16(part))
+            elif use_peer:
+                ones[lane].all_reduce(part, out_bf16=dst)
+            else:
+                comm.all_reduce(part)
+                dst.copy_(tpmod.partial_to_bf16(part))
+            return dst
+
+        def chunk_step(L, m0, lane):
+            B = lane_bufs[lane]
+            L["qkv"].forward(x[m0:m0 + rows], out=B["qkv"], workspace=B["ws"])
+            if fused:
+                h = ones[lane].fp8_linear_all_reduce(L["o"], attn[m0:m0 + rows], out=B["h"])
+            else:
+                L["o"].forward_partial(attn[m0:m0 + rows], out=B["po"], workspace=B["ws"])
+                h = reduce_round(B["po"], B["h"], lane)
+            L["gate_up"].forward(h, out=B["gu"], workspace=B["ws"])
+            if fused:
+                return ones[lane].fp8_linear_all_reduce(L["down"], act[m0:m0 + rows], out=B["y"])
+            L["down"].forward_partial(act[m0:m0 + rows], out=B["pd"], workspace=B["ws"])
+            return reduce_round(B["pd"], B["y"], lane)
+
+        def step():
+            cur = torch.cuda.current_stream(device)
+            for L in layers:
+                if lanes == 1:
+                    for ci in range(n_chunks):
+                        chunk_step(L, ci * rows, 0)
+                    continue
+                # two lanes: even chunks on the current stream, odd chunks on the second one; every rank issues the
+                # calls of a lane's communicator in the same order
+                side[1].wait_stream(cur)
+                for ci in range(n_chunks):
+                    if ci % 2 == 0:
+                        chunk_step(L, ci * rows, 0)
+                    else:
+                        with torch.cuda.stream(side[1]):
+                            chunk_step(L, ci * rows, 1)
+                cur.wait_stream(side[1])
+
+        run, mode, gr = graph_of(step)
+        us_layer = time_run(run, 20 if M <= 256 else 3, sync_ranks=world > 1)
         flops = 2.0 * M * H * (QKV + H + 2 * FF + FF)
-        out.append({"M": M, "tp": world, "us_per_layer": us_layer, "layers_per_s": 1e6 / us_layer,
-                    "tok_per_s_per_layer": M * 1e6 / us_layer, "TFLOPs_all_gpus": flops / us_layer / 1e6,
-                    "weight_GBps_per_gpu": (H * (QKV + H + 3 * FF) / world) / us_layer / 1e3, "launch": mode,
-                    "allreduce": ("none (one rank)" if world == 1 else
-                                  "f32 [M,8192] x2 per layer, pushed and summed in the row-parallel matvec's epilogue over peer "
-                                  "memory (rank-ordered sum, one launch with the matvec)" if fused else
-                                  "f32 [M,8192] x2 per layer, one-shot peer-memory kernel (rank-ordered sum)" if use_one_shot
-                                  else "f32 [M,8192] x2 per layer (NCCL)")})
-        del gr
-    from scratchy_b200 import _lib
+        count = rows * H
+        form = ("none (one rank)" if world == 1 else
+                "pushed and summed in the row-parallel matvec's epilogue over peer memory (one launch with the matvec)" if fused else
+                "NCCL all-reduce of the f32 partials, then one rounding kernel" if not use_peer else
+                "peer-memory kernel, packets" if count * world <= 32768 else
+                "peer-memory kernel, two phases (reduce-scatter + all-gather of bf16)" if count >= 131072 else
+                "peer-memory kernel, dense one-shot")
+        row = {"M": M, "tp": world, "us_per_layer": us_layer, "layers_per_s": 1e6 / us_layer,
+               "tok_per_s_per_layer": M * 1e6 / us_layer, "TFLOPs_all_gpus": flops / us_layer / 1e6,
+               "weight_GBps_per_gpu": (H * (QKV + H + 3 * FF) / world) / us_layer / 1e3, "launch": mode,
+               "chunks": n_chunks, "lanes": lanes, "allreduce": f"f32 [M,8192] x2 per layer, rank-ordered sum: {form}"}
+        if world > 1:
+            row["us_per_layer_tp1"] = t1[M]
+            row["efficiency"] = t1[M] / (world * us_layer)
+        out.append(row)
+        del gr, lane_bufs
     try:
         _lib.context(device.index).device_status(None)
     except _lib.ScratchyCudaError as exc:                         # a bounded wait ran out somewhere: the numbers are void
         out.append({"error": str(exc)})
-    if one is not None:
-        one.close()
+    out.append({"tp_parity": parity, "what": "o-projection 8192 -> 8192 at M = 1, 32, 256 on the real ranks against the lockstep oracle "
+                                            "(rank-ordered f32 sum, one rounding) on 256 sampled channels, rel-L2 <= 1e-3"})
+    for o in ones:
+        if o is not None:
+            o.close()
     if one_note:
         out.append({"note": one_note})
     return out

@@ -60,6 +60,12 @@ def _c(a, dtype) -> np.ndarray:
     return np.ascontiguousarray(a, dtype=dtype)
 
 
+def set_num_threads(n: int) -> None:
+    """OpenMP threads of the following oracle calls (the bench's CPU arm: every host core, whatever OMP_NUM_THREADS
+    the launcher exported)."""
+    lib().orc_set_num_threads(ctypes.c_int(int(n)))
+
+
 def num_threads() -> int:
     return int(lib().orc_num_threads())
 

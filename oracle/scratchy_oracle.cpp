@@ -62,6 +62,12 @@ inline uint16_t f32_to_half(float f, int dt) { return dt == DT_BF16 ? f32_to_bf1
 
 extern "C" {
 
+// The bench's CPU arm runs under launchers that export OMP_NUM_THREADS=1 (torchrun does): it sets the
+// thread count explicitly so that the baseline uses the host's cores whatever the environment says.
+void orc_set_num_threads(int n) {
+    if (n > 0) omp_set_num_threads(n);
+}
+
 int orc_num_threads() {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -886,9 +886,9 @@ extern "C" int32_t scr_linear_fp8_dynamic_allreduce(scr_tp_comm* comm, const voi
     int32_t st = fp8_check_shape(ctx, N, K);
     if (st) return st;
     if (M <= 0) return scr_fail(ctx, SCR_E_SHAPE, "M=%d must be positive", M);
-    if ((long long)M * N > comm->max_elems)
+    if ((long long)M * N > comm->one_elems)
         return scr_fail(ctx, SCR_E_SHAPE, "fp8 matvec + exchange: %lld outputs exceed the communicator's %lld", (long long)M * N,
-                        comm->max_elems);
+                        comm->one_elems);
     if (!fp8_gemv_fuses_quant(M, K))
         return scr_fail(ctx, SCR_E_UNSUPPORTED,
                         "fp8 matvec + exchange: M=%d K=%d is beyond the self-quantising matvec (use scr_linear_fp8_dynamic_partial "
@@ -898,7 +898,7 @@ extern "C" int32_t scr_linear_fp8_dynamic_allreduce(scr_tp_comm* comm, const voi
     ex.peers = tpc_peer_table(comm);
     ex.world = comm->world;
     ex.rank = comm->rank;
-    ex.max_elems = comm->max_elems;
+    ex.max_elems = comm->one_elems;
     ex.state = comm->state;
     ex.y_bf16 = y;
     ex.wait_limit = comm->wait_limit;

@@ -150,6 +150,89 @@ __global__ void __launch_bounds__(TPC_THREADS) tp_allreduce_flags_kernel(TpcPeer
     tpc_finish_call(state, e, gridDim.x);
 }
 
+// ---- two phases in one kernel, for prefill-size payloads (count a multiple of 8 * world) --------------------
+// CTA c of every rank owns the same sub-range of every slice, so the flags CTA c exchanges with the peers' CTA c
+// cover exactly the data it reads.
+__device__ __forceinline__ void tpc_flag_round(unsigned int* const* flags2, int phase, long long half, int world, int rank, int c,
+                                               unsigned int e, int* status, unsigned int wait_limit) {
+    __syncthreads();                                    // this CTA's stores are ordered before the release below
+    const int tid = threadIdx.x;
+    if (tid < world) {
+        const long long row = ((long long)phase * 2 + half) * world;
+        tpc_st_release_sys(flags2[tid] + (row + rank) * TPC_MAX_CTAS + c, e);
+        const unsigned int* mine = flags2[rank] + (row + tid) * TPC_MAX_CTAS + c;
+        bool seen = false;
+        for (unsigned int it = 0; it < wait_limit; ++it) {
+            if ((int)(tpc_ld_acquire_sys(mine) - e) >= 0) {
+                seen = true;
+                break;
+            }
+            if ((it & 1023u) == 1023u && *reinterpret_cast<volatile int*>(status) != 0) break;
+        }
+        if (!seen) atomicCAS(status, 0, TPC_ERR_FLAG_WAIT);
+    }
+    __syncthreads();
+}
+__device__ __forceinline__ uint4 ld_cg_u4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+__global__ void __launch_bounds__(TPC_THREADS) tp_allreduce_two_phase_kernel(TpcPeers peers, int world, int rank, long long ag_stride,
+                                                                             long long slice_max, const float* __restrict__ partial,
+                                                                             long long count, uint16_t* __restrict__ y_bf16,
+                                                                             unsigned int* state, int* status, unsigned int wait_limit) {
+    __shared__ unsigned int s_epoch;
+    const int c = blockIdx.x, tid = threadIdx.x, G = gridDim.x;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (tid == 0) s_epoch = *reinterpret_cast<volatile unsigned int*>(&state[0]) + 1u;
+    __syncthreads();
+    const unsigned int e = s_epoch;
+    const long long half = (long long)(e & 1u);
+    const long long S = count / world;                   // elements per slice (a multiple of 8)
+    const long long per = ((S / 8 + G - 1) / G) * 8;     // this CTA's sub-range of a slice
+    const long long lo = (long long)c * per, hi = min(S, lo + per);
+
+    // 1. reduce-scatter, pushed: slice q of my partials -> my row of rank q's receive area (starting with my right
+    //    neighbour, so that at any moment the ranks write to different peers)
+    for (int dq = 0; dq < world; ++dq) {
+        const int q = (rank + 1 + dq) % world;
+        const float* src = partial + q * S;
+        float* dst = peers.rs[q] + (half * world + rank) * slice_max;
+        for (long long i = lo + tid * 4; i < hi; i += TPC_THREADS * 4) *reinterpret_cast<float4*>(dst + i) = *reinterpret_cast<const float4*>(src + i);
+    }
+    tpc_flag_round(peers.flags2, 0, half, world, rank, c, e, status, wait_limit);
+
+    // 2. my slice: the W copies summed in rank order, one rounding, the bf16 values pushed to every rank (all-gather)
+    const float* mine = peers.rs[rank] + half * world * slice_max;
+    for (long long i = lo + tid * 8; i < hi; i += TPC_THREADS * 8) {
+        float4 a = ld_cg_f4(mine + i), b = ld_cg_f4(mine + i + 4);
+        for (int p = 1; p < world; ++p) {
+            const float4 u = ld_cg_f4(mine + p * slice_max + i), v = ld_cg_f4(mine + p * slice_max + i + 4);
+            a.x = __fadd_rn(a.x, u.x); a.y = __fadd_rn(a.y, u.y); a.z = __fadd_rn(a.z, u.z); a.w = __fadd_rn(a.w, u.w);
+            b.x = __fadd_rn(b.x, v.x); b.y = __fadd_rn(b.y, v.y); b.z = __fadd_rn(b.z, v.z); b.w = __fadd_rn(b.w, v.w);
+        }
+        const __nv_bfloat162 r0 = __floats2bfloat162_rn(a.x, a.y), r1 = __floats2bfloat162_rn(a.z, a.w);
+        const __nv_bfloat162 r2 = __floats2bfloat162_rn(b.x, b.y), r3 = __floats2bfloat162_rn(b.z, b.w);
+        const uint4 o = make_uint4(*reinterpret_cast<const uint32_t*>(&r0), *reinterpret_cast<const uint32_t*>(&r1),
+                                   *reinterpret_cast<const uint32_t*>(&r2), *reinterpret_cast<const uint32_t*>(&r3));
+        for (int dq = 0; dq < world; ++dq) {
+            const int q = (rank + 1 + dq) % world;
+            *reinterpret_cast<uint4*>(peers.ag[q] + half * ag_stride + rank * S + i) = o;
+        }
+    }
+    tpc_flag_round(peers.flags2, 1, half, world, rank, c, e, status, wait_limit);
+
+    // 3. everybody's slices have arrived here: into the caller's output
+    const uint16_t* got = peers.ag[rank] + half * ag_stride;
+    for (int q = 0; q < world; ++q)
+        for (long long i = lo + tid * 8; i < hi; i += TPC_THREADS * 8)
+            *reinterpret_cast<uint4*>(y_bf16 + q * S + i) = ld_cg_u4(got + q * S + i);
+    tpc_finish_call(state, e, gridDim.x);
+}
+
 }  // namespace
 
 extern "C" int32_t scr_tp_comm_create(scr_ctx* ctx, int32_t world, int32_t rank, int64_t max_elems, scr_tp_comm** out,
@@ -167,10 +250,19 @@ extern "C" int32_t scr_tp_comm_create(scr_ctx* ctx, int32_t world, int32_t rank,
     c->world = world;
     c->rank = rank;
     c->max_elems = max_elems;
-    // packets | dense f32 | flags; zeroed: call numbers start at 1
-    c->recv_off = ((size_t)2 * world * max_elems * sizeof(uint2) + 255) & ~(size_t)255;
-    c->flags_off = (c->recv_off + (size_t)2 * world * max_elems * sizeof(float) + 255) & ~(size_t)255;
-    c->bytes = c->flags_off + (size_t)2 * world * TPC_MAX_CTAS * sizeof(unsigned int);
+    c->one_elems = std::min<long long>(max_elems, TPC_ONE_SHOT_MAX);
+    c->slice_max = ((max_elems + world - 1) / world + 7) / 8 * 8;
+    // one-shot: packets | dense f32 | flags; two-phase: received slices | gathered result | flags.  Zeroed: call numbers start at 1
+    auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
+    c->recv_off = up((size_t)2 * world * c->one_elems * sizeof(uint2));
+    c->flags_off = up(c->recv_off + (size_t)2 * world * c->one_elems * sizeof(float));
+    c->rs_off = up(c->flags_off + (size_t)2 * world * TPC_MAX_CTAS * sizeof(unsigned int));
+    c->bytes = c->rs_off;
+    if (max_elems >= TPC_TWO_PHASE_MIN) {
+        c->ag_off = up(c->rs_off + (size_t)2 * world * c->slice_max * sizeof(float));
+        c->flags2_off = up(c->ag_off + (size_t)2 * ((max_elems + 7) / 8 * 8) * sizeof(uint16_t));
+        c->bytes = c->flags2_off + (size_t)2 * 2 * world * TPC_MAX_CTAS * sizeof(unsigned int);
+    }
     cudaError_t e = cudaMalloc((void**)&c->local, c->bytes);
     if (e == cudaSuccess) e = cudaMemset(c->local, 0, c->bytes);
     if (e == cudaSuccess) e = cudaMalloc((void**)&c->state, 2 * sizeof(unsigned int));
@@ -269,7 +361,13 @@ extern "C" int32_t scr_tp_allreduce_partial(scr_tp_comm* comm, const float* part
     if (!scr_aligned16(partial) || (y_f32 && !scr_aligned16(y_f32)) || (y_bf16 && ((uintptr_t)y_bf16 & 7u)))
         return scr_fail(ctx, SCR_E_ALIGN, "tp all-reduce: buffers must be 16-byte aligned");
     const TpcPeers peers = tpc_peer_table(comm);
-    const int grid = (int)std::min<long long>((count + TPC_SLICE - 1) / TPC_SLICE, TPC_MAX_GRID);
+    const bool two_phase = count >= TPC_TWO_PHASE_MIN && count % (8 * comm->world) == 0 && y_bf16 && !y_f32 &&
+                           comm->max_elems >= TPC_TWO_PHASE_MIN && scr_aligned16(y_bf16);
+    if (!two_phase && count > comm->one_elems)
+        return scr_fail(ctx, SCR_E_SHAPE, "tp all-reduce: %lld values need the two-phase form (bf16 output only, count a multiple of %d)",
+                        (long long)count, 8 * comm->world);
+    const int grid = two_phase ? std::min(ctx->sm_count, TPC_MAX_CTAS)
+                               : (int)std::min<long long>((count + TPC_SLICE - 1) / TPC_SLICE, TPC_MAX_GRID);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(TPC_THREADS);
@@ -279,10 +377,17 @@ extern "C" int32_t scr_tp_allreduce_partial(scr_tp_comm* comm, const float* part
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    // every rank takes the same branch: count and world are the same everywhere
-    auto kernel = (long long)count * comm->world <= TPC_PACKET_MAX ? tp_allreduce_kernel : tp_allreduce_flags_kernel;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, peers, comm->world, comm->rank, (long long)comm->max_elems, partial,
-                                       (long long)count, y_bf16, y_f32, comm->state, ctx->dev_status, comm->wait_limit);
+    // every rank takes the same branch: count, world and the output kinds are the same everywhere
+    cudaError_t e;
+    if (two_phase) {
+        e = cudaLaunchKernelEx(&cfg, tp_allreduce_two_phase_kernel, peers, comm->world, comm->rank, (long long)((comm->max_elems + 7) / 8 * 8),
+                               (long long)comm->slice_max, partial, (long long)count, y_bf16, comm->state, ctx->dev_status,
+                               comm->wait_limit);
+    } else {
+        auto kernel = (long long)count * comm->world <= TPC_PACKET_MAX ? tp_allreduce_kernel : tp_allreduce_flags_kernel;
+        e = cudaLaunchKernelEx(&cfg, kernel, peers, comm->world, comm->rank, (long long)comm->one_elems, partial, (long long)count,
+                               y_bf16, y_f32, comm->state, ctx->dev_status, comm->wait_limit);
+    }
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "tp all-reduce launch: %s", cudaGetErrorString(e));
     return scr_check_launch(ctx, "tp_allreduce");
 }

@@ -20,17 +20,28 @@
 // against 332 us with packets).
 #define TPC_PACKET_MAX 32768
 #define TPC_MAX_CTAS 256                     // flag slots per (half, rank)
+// Payloads of TPC_TWO_PHASE_MIN values and more (prefill chunks) are bandwidth, not latency: pushing every rank's whole
+// partial to every rank moves (W-1) * 4 bytes per element and rank.  The two-phase kernel moves (W-1)/W * (4 + 2):
+// each rank receives only its 1/W slice of the others' f32 partials, sums the W copies in rank order, rounds once and
+// pushes the bf16 slice to everybody (a reduce-scatter and an all-gather inside one kernel, plain peer stores).
+#define TPC_TWO_PHASE_MIN 131072
+#define TPC_ONE_SHOT_MAX 524288              // capacity of the one-shot areas (64 tokens x 8192)
 struct TpcPeers {
-    uint2* ll[TPC_MAX_WORLD];                // base of each rank's packet area   [2][W][max_elems] packets
-    float* recv[TPC_MAX_WORLD];              // base of each rank's dense area    [2][W][max_elems] f32
+    uint2* ll[TPC_MAX_WORLD];                // base of each rank's packet area   [2][W][one_elems] packets
+    float* recv[TPC_MAX_WORLD];              // base of each rank's dense area    [2][W][one_elems] f32
     unsigned int* flags[TPC_MAX_WORLD];      // base of each rank's flag area     [2][W][TPC_MAX_CTAS]
+    float* rs[TPC_MAX_WORLD];                // two-phase: slices received        [2][W][slice_max] f32
+    uint16_t* ag[TPC_MAX_WORLD];             // two-phase: the gathered result    [2][max_elems] bf16
+    unsigned int* flags2[TPC_MAX_WORLD];     // two-phase: flags                  [2 phases][2][W][TPC_MAX_CTAS]
 };
 
 struct scr_tp_comm {
     scr_ctx* ctx = nullptr;
     int world = 1, rank = 0;
-    long long max_elems = 0;
-    size_t bytes = 0, recv_off = 0, flags_off = 0;
+    long long max_elems = 0;                 // largest count of a call
+    long long one_elems = 0;                 // capacity (and stride) of the one-shot areas: min(max_elems, TPC_ONE_SHOT_MAX)
+    long long slice_max = 0;                 // two-phase: ceil(max_elems / world), a multiple of 8
+    size_t bytes = 0, recv_off = 0, flags_off = 0, rs_off = 0, ag_off = 0, flags2_off = 0;
     unsigned char* local = nullptr;
     unsigned char* peer[TPC_MAX_WORLD] = {nullptr};
     bool opened[TPC_MAX_WORLD] = {false};
@@ -56,6 +67,9 @@ static inline TpcPeers tpc_peer_table(const scr_tp_comm* comm) {
         peers.ll[p] = reinterpret_cast<uint2*>(base);
         peers.recv[p] = reinterpret_cast<float*>(base + comm->recv_off);
         peers.flags[p] = reinterpret_cast<unsigned int*>(base + comm->flags_off);
+        peers.rs[p] = reinterpret_cast<float*>(base + comm->rs_off);
+        peers.ag[p] = reinterpret_cast<uint16_t*>(base + comm->ag_off);
+        peers.flags2[p] = reinterpret_cast<unsigned int*>(base + comm->flags2_off);
     }
     return peers;
 }

@@ -197,7 +197,8 @@ class OneShotAllReduce:
 
     def fp8_linear_all_reduce_supported(self, linear, M: int) -> bool:
         k16 = (linear.in_features + 15) // 16 * 16
-        return M <= 4 and linear.in_features % 8 == 0 and M * k16 <= 14 * 1024 and M * linear.out_features <= self.max_elems
+        one_shot = min(self.max_elems, 524288)        # TPC_ONE_SHOT_MAX: capacity of the packet area
+        return M <= 4 and linear.in_features % 8 == 0 and M * k16 <= 14 * 1024 and M * linear.out_features <= one_shot
 
     def close(self) -> None:
         if self._h:
@@ -234,8 +235,10 @@ class RowParallel:
     def forward(self, x_local: torch.Tensor, workspace=None) -> torch.Tensor:
         """f32 partials over the rank's K-slice, summed over ranks, rounded to bf16 once."""
         part = self.linear.forward_partial(x_local, workspace=workspace)
-        if self.one_shot is not None and part.numel() <= self.one_shot.max_elems and part.numel() % 4 == 0:
-            return self.one_shot.all_reduce(part)
+        n = part.numel()
+        if self.one_shot is not None and n <= self.one_shot.max_elems and (
+                (n <= 524288 and n % 4 == 0) or (n >= 131072 and n % (8 * self.comm.tp.world) == 0)):
+            return self.one_shot.all_reduce(part)      # packets / dense one-shot, or the two-phase form for prefill sizes
         self.comm.all_reduce(part)
         return partial_to_bf16(part)
 
