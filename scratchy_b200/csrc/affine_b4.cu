@@ -230,7 +230,27 @@ __device__ __forceinline__ uint4 tape_ld_v4(const void* p) {
     return v;
 }
 
-template <int MT, int SPLIT_CLUSTER, bool CHECK>
+// A ring stage holds U blocks per consumer warp (8 * U blocks, one bulk copy): one full/empty handshake, one wait and one
+// set of loop bookkeeping per U blocks instead of per block, and U independent dequantise + MMA streams for the
+// scheduler to interleave.  Warp w takes blocks w, w + 8, .. of a stage, so a short last stage still spreads over the warps.
+template <int U> struct GemvRing {
+    static constexpr int kStageBlocks = GEMV_CWARPS * U;
+    static constexpr int kStageBytes = kStageBlocks * AFF_BLOCK_BYTES;
+    static constexpr int kStages = (U == 1) ? 4 : 3;
+    static constexpr int kBytes = kStages * kStageBytes;
+    static constexpr int kCtasPerSm = (U <= 2) ? 3 : 2;
+};
+// The common case is one try_wait (the stage has landed long ago); the bounded slow path is out of line.
+static __device__ __noinline__ void gemv_wait_slow(uint32_t bar, uint32_t parity, int* status) { gemv_wait(bar, parity, status); }
+__device__ __forceinline__ void gemv_wait_fast(uint32_t bar, uint32_t parity, int* status) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    if (!ok) gemv_wait_slow(bar, parity, status);
+}
+
+template <int MT, int SPLIT_CLUSTER, bool CHECK, int U>
 __device__ __forceinline__ void gemv_consumer(const uint16_t* __restrict__ x, uint16_t* __restrict__ y, int M, int N,
                                               int K, int kc_lo, int kc_hi, int nstage, int rb_real, int split, int sp,
                                               int out_f32, const uint16_t* __restrict__ bias, int* __restrict__ status, uint32_t ring_base, uint32_t full_base,
@@ -245,7 +265,8 @@ __device__ __forceinline__ void gemv_consumer(const uint16_t* __restrict__ x, ui
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) xrow[mt] = x + (size_t)min(mt * 8 + g, M - 1) * K;
 
-    uint32_t n_it = 0;                         // stages consumed so far (ring position and phase)
+    using R = GemvRing<U>;
+    uint32_t slot = 0, phase = 0;              // ring position and phase of the next stage
     int it = 0;
     for (int rb = blockIdx.x; rb < rb_real; rb += gridDim.x, ++it) {
         float acc[2][MT][4];
@@ -257,22 +278,31 @@ __device__ __forceinline__ void gemv_consumer(const uint16_t* __restrict__ x, ui
                 for (int i = 0; i < 4; ++i) acc[a][mt][i] = 0.f;
 
 #pragma unroll 1
-        for (int j = 0; j < nstage; ++j, ++n_it) {
-            const int kc = kc_lo + j * GEMV_CWARPS + warp;
-            const bool active = kc < kc_hi;                       // warp-uniform
-            const uint32_t slot = n_it & (GEMV_STAGES - 1);
-            // the activations do not depend on the ring: fetch them while the weights are in flight
-            uint4 xv[MT][4];
-            int k0 = kc * 128 + t * 32;
-            if (k0 >= K) k0 = 0;                                  // padded k (zero weights) or idle warp
+        for (int j = 0; j < nstage; ++j) {
+            const int kc0 = kc_lo + j * R::kStageBlocks + warp;
+            // the activations do not depend on the ring: the first block's are fetched while the weights are in flight,
+            // the next block's while the current one is computed (L1 hits after the CTA's first row-block)
+            uint4 xv[2][MT][4];
+            auto load_x = [&](int u, uint4 (&dst)[MT][4]) {
+                int k0 = (kc0 + u * GEMV_CWARPS) * 128 + t * 32;
+                if (k0 >= K) k0 = 0;                              // padded k (zero weights) or idle warp
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt)
+                for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) xv[mt][i] = tape_ld_v4(xrow[mt] + k0 + 8 * i);      // coherent: the preceding kernel wrote x
-            gemv_wait(full_base + 8u * slot, (n_it / GEMV_STAGES) & 1u, status);
-            if (active) gemv_block_compute<MT, CHECK>(ring_base + slot * GEMV_STAGE_BYTES + warp * AFF_BLOCK_BYTES, acc, xv, lane);
+                    for (int i = 0; i < 4; ++i) dst[mt][i] = tape_ld_v4(xrow[mt] + k0 + 8 * i);      // coherent: the preceding kernel wrote x
+            };
+            load_x(0, xv[0]);
+            gemv_wait_fast(full_base + 8u * slot, phase, status);
+            const uint32_t stage = ring_base + slot * R::kStageBytes + warp * AFF_BLOCK_BYTES;
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (u + 1 < U) load_x(u + 1, xv[(u + 1) & 1]);
+                if (kc0 + u * GEMV_CWARPS < kc_hi)                // warp-uniform
+                    gemv_block_compute<MT, CHECK>(stage + u * GEMV_CWARPS * AFF_BLOCK_BYTES, acc, xv[u & 1], lane);
+            }
             __syncwarp();                                         // every lane has consumed the stage
             if (lane == 0) gemv_mbar_arrive(empty_base + 8u * slot);
+            if (++slot == R::kStages) { slot = 0; phase ^= 1u; }
         }
 
         // cross-warp reduction of this row-block, fixed warp order, double-buffered
@@ -323,22 +353,23 @@ __device__ __forceinline__ void gemv_consumer(const uint16_t* __restrict__ x, ui
         gemv_norm_tail(cta_sq, M, N, gridDim.x, blockIdx.x, ends, 1, GEMV_CWARPS * 32);
 }
 
-template <int MT, int SPLIT_CLUSTER>
-__global__ void __launch_bounds__(GEMV_THREADS, (MT == 1 ? 3 : 2))
+template <int MT, int SPLIT_CLUSTER, int U>
+__global__ void __launch_bounds__(GEMV_THREADS, (MT == 1 ? GemvRing<U>::kCtasPerSm : 2))
 affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __restrict__ x, uint16_t* __restrict__ y,
                       int M, int N, int K, int RB, int KC, int rb_real, int split, int out_f32,
                       const uint16_t* __restrict__ bias, int* __restrict__ status, GemvEnds ends) {
-    extern __shared__ __align__(128) uint8_t gemv_ring[];          // [GEMV_STAGES][8 blocks]
+    extern __shared__ __align__(128) uint8_t gemv_ring[];          // [stages][8 * U blocks]
     __shared__ float sq_s[2][16][16];                              // RESIDUAL_NORM: squares of the stored residuals [token][row]
-    __shared__ __align__(8) uint64_t full_bar[GEMV_STAGES];
-    __shared__ __align__(8) uint64_t empty_bar[GEMV_STAGES];
+    using R = GemvRing<U>;
+    __shared__ __align__(8) uint64_t full_bar[R::kStages];
+    __shared__ __align__(8) uint64_t empty_bar[R::kStages];
     __shared__ float red[2][GEMV_CWARPS][32][MT * 4];
     __shared__ float cl_part[SPLIT_CLUSTER ? GEMV_MAX_SPLIT : 1][16][MT * 8];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
 #pragma unroll
-        for (int d = 0; d < GEMV_STAGES; ++d) {
+        for (int d = 0; d < R::kStages; ++d) {
             gemv_mbar_init(gemv_smem_u32(&full_bar[d]), 1);
             gemv_mbar_init(gemv_smem_u32(&empty_bar[d]), GEMV_CWARPS);
         }
@@ -355,7 +386,7 @@ affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __rest
     const int per = (KC + split - 1) / split;
     const int kc_lo = sp * per;
     const int kc_hi = min(KC, kc_lo + per);
-    const int nstage = (max(kc_hi - kc_lo, 0) + GEMV_CWARPS - 1) / GEMV_CWARPS;
+    const int nstage = (max(kc_hi - kc_lo, 0) + R::kStageBlocks - 1) / R::kStageBlocks;
     const uint32_t ring_base = gemv_smem_u32(gemv_ring);
     const uint32_t full_base = gemv_smem_u32(&full_bar[0]);
     const uint32_t empty_base = gemv_smem_u32(&empty_bar[0]);
@@ -363,16 +394,15 @@ affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __rest
     if (warp == GEMV_CWARPS) {
         // ---- producer warp: one lane streams the row-blocks' k extents into the ring
         if (lane == 0) {
-            uint32_t n_it = 0;
+            uint32_t slot = 0, phase = 0;
             for (int rb = blockIdx.x; rb < rb_real; rb += gridDim.x) {
                 const uint8_t* src = packed + ((size_t)rb * KC + kc_lo) * AFF_BLOCK_BYTES;
-                for (int j = 0; j < nstage; ++j, ++n_it) {
-                    const uint32_t slot = n_it & (GEMV_STAGES - 1);
-                    gemv_wait(empty_base + 8u * slot, ((n_it / GEMV_STAGES) & 1u) ^ 1u, status);
-                    const uint32_t bytes = (uint32_t)min(GEMV_CWARPS, kc_hi - kc_lo - j * GEMV_CWARPS) * AFF_BLOCK_BYTES;
+                for (int j = 0; j < nstage; ++j) {
+                    gemv_wait(empty_base + 8u * slot, phase ^ 1u, status);
+                    const uint32_t bytes = (uint32_t)min(R::kStageBlocks, kc_hi - kc_lo - j * R::kStageBlocks) * AFF_BLOCK_BYTES;
                     gemv_arrive_expect_tx(full_base + 8u * slot, bytes);
-                    gemv_bulk_g2s(ring_base + slot * GEMV_STAGE_BYTES, src + (size_t)j * GEMV_STAGE_BYTES, bytes,
-                                  full_base + 8u * slot);
+                    gemv_bulk_g2s(ring_base + slot * R::kStageBytes, src + (size_t)j * R::kStageBytes, bytes, full_base + 8u * slot);
+                    if (++slot == R::kStages) { slot = 0; phase ^= 1u; }
                 }
             }
         }
@@ -384,10 +414,10 @@ affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __rest
         asm volatile("griddepcontrol.wait;" ::: "memory");        // x (and y's previous readers) are settled
         const bool check = trailer_flag != 0;
         if (check)
-            gemv_consumer<MT, SPLIT_CLUSTER, true>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, out_f32, bias, status, ring_base,
+            gemv_consumer<MT, SPLIT_CLUSTER, true, U>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, out_f32, bias, status, ring_base,
                                                    full_base, empty_base, red, cl_part, ends, sq_s);
         else
-            gemv_consumer<MT, SPLIT_CLUSTER, false>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, out_f32, bias, status, ring_base,
+            gemv_consumer<MT, SPLIT_CLUSTER, false, U>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, out_f32, bias, status, ring_base,
                                                     full_base, empty_base, red, cl_part, ends, sq_s);
     }
 
@@ -496,9 +526,9 @@ extern "C" int32_t scr_affine_b4_dequant_dump(scr_ctx* ctx, const void* packed, 
 // Launch shape.  With enough row-blocks the grid is persistent (two CTAs per SM) and nothing
 // is split; with few row-blocks each CTA takes one row-block and a cluster of `split` CTAs
 // shares its k-chunks so that about one CTA per SM is busy.
-static void affine_gemv_shape(int rb_real, int KC, int sms, int* grid_x, int* split) {
-    // Enough row-blocks: persistent CTAs (3 per SM) walk them, nothing is split.
-    const int slots = 3 * sms;
+static void affine_gemv_shape(int rb_real, int KC, int sms, int ctas_per_sm, int* grid_x, int* split) {
+    // Enough row-blocks: persistent CTAs walk them, nothing is split.
+    const int slots = ctas_per_sm * sms;
     if (rb_real >= slots) {
         *grid_x = slots;
         *split = 1;
@@ -524,21 +554,26 @@ struct AffineFwd {
     const GemvEnds* ends = nullptr;          // GEMV_OUT_RESIDUAL_NORM only
 };
 
-template <int MT>
-static int32_t affine_gemv_launch(scr_ctx* ctx, const uint8_t* packed, const uint16_t* x, uint16_t* y, int M, int N,
-                                  int K, const AffineFwd& f, cudaStream_t stream) {
+// Blocks per warp and ring stage.  Up to 8 tokens: 3 (measured on the Llama-3.2-3B shapes: 162 executed warp instructions per
+// 1152-byte block against 197 with 1, two CTAs of 96 registers per SM instead of three of 72, the dependent chain of a
+// decode layer 6 % faster); the two-tile (9..16 tokens) kernel keeps 1: its activation registers leave no room for more.
+static int affine_gemv_u(int MT) { return MT == 1 ? 3 : 1; }
+
+template <int MT, int U>
+static int32_t affine_gemv_launch_u(scr_ctx* ctx, const uint8_t* packed, const uint16_t* x, uint16_t* y, int M, int N,
+                                    int K, const AffineFwd& f, cudaStream_t stream) {
+    using R = GemvRing<U>;
     const AffineGeom g = affine_geom(N, K);
     const int rb_real = scr_ceil_div(N, 16);
     int grid_x = 1, split = 1;
-    affine_gemv_shape(rb_real, g.KC, ctx->sm_count, &grid_x, &split);
-    constexpr int kRingBytes = GEMV_STAGES * GEMV_STAGE_BYTES;
-    auto kernel = (split == 1) ? affine_b4_gemv_kernel<MT, 0> : affine_b4_gemv_kernel<MT, 1>;
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes);
+    affine_gemv_shape(rb_real, g.KC, ctx->sm_count, MT == 1 ? R::kCtasPerSm : 2, &grid_x, &split);
+    auto kernel = (split == 1) ? affine_b4_gemv_kernel<MT, 0, U> : affine_b4_gemv_kernel<MT, 1, U>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, R::kBytes);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine_b4_gemv smem attribute: %s", cudaGetErrorString(e));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid_x, split, 1);
     cfg.blockDim = dim3(GEMV_THREADS, 1, 1);
-    cfg.dynamicSmemBytes = kRingBytes;
+    cfg.dynamicSmemBytes = R::kBytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     int na = 0;
@@ -564,6 +599,15 @@ static int32_t affine_gemv_launch(scr_ctx* ctx, const uint8_t* packed, const uin
     e = cudaLaunchKernelEx(&cfg, kernel, packed, x, y, M, N, K, g.RB, g.KC, rb_real, split, f.out_mode, f.bias, ctx->dev_status, ends);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine_b4_gemv launch: %s", cudaGetErrorString(e));
     return scr_check_launch(ctx, "affine_b4_gemv");
+}
+
+template <int MT>
+static int32_t affine_gemv_launch(scr_ctx* ctx, const uint8_t* packed, const uint16_t* x, uint16_t* y, int M, int N,
+                                  int K, const AffineFwd& f, cudaStream_t stream) {
+    if (MT == 1) {
+        if (affine_gemv_u(MT) == 3) return affine_gemv_launch_u<1, 3>(ctx, packed, x, y, M, N, K, f, stream);
+    }
+    return affine_gemv_launch_u<MT, 1>(ctx, packed, x, y, M, N, K, f, stream);
 }
 
 // Defined in affine_b4_gemm.cu
