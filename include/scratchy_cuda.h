@@ -117,6 +117,31 @@ int32_t scr_linear_affine_b4_silu_mul(scr_ctx* ctx, const void* packed, const ui
                                       int32_t M, int32_t N2, int32_t K, int32_t group,
                                       uint16_t* out_bf16, void* stream);
 
+/* The one-row matvec with the ends the reference folds around it — `QmvEnds {norm, bias, scale, residual}`
+ * (crates/targets/metal/src/tape/step.rs:472-498; shader crates/targets/metal/shaders/quantized_qmv.metal:60-112) — and,
+ * on the output side, the gate/up pairing of `scr_linear_affine_b4_silu_mul`.  Up to 16 tokens (SCR_E_UNSUPPORTED above).
+ *   norm_gain != NULL   x is the INPUT of an RMSNorm whose gain this is: every CTA normalises the rows into shared
+ *                       memory as it loads them, with the arithmetic and summation order of `scr_rmsnorm_bf16`
+ *                       (cpu_golden.rs:25-37), so the result is the bits of that operator followed by the plain linear
+ *                       (the reference's fused kernel keeps x * gain in f32 instead, one rounding away from its own
+ *                       unfused path).  Up to 8 tokens and M * K * 2 <= 20 KiB.
+ *   bias, scale         sum + bias[n], then * scale, in f32 before the one rounding (scale 0 is read as 1)
+ *   residual            y is the residual stream: y <- bf16(y + bf16(sum)), the bits of the separate add
+ *                       (`fused_add_rmsnorm`'s residual, cpu_golden.rs:171-200)
+ *   silu_pairs          the gate/up pairing (N = fused rows, y is [M, N/2]); excludes bias, scale and residual */
+typedef struct scr_qmv_ends {
+    const uint16_t* norm_gain;     /* [K] bf16 or NULL */
+    float norm_eps;
+    float norm_gain_offset;        /* rmsnorm(x, gain + offset) (`RowNorm.offset`) */
+    const uint16_t* bias;          /* [N] bf16 or NULL */
+    float scale;
+    int32_t residual;
+    int32_t silu_pairs;
+} scr_qmv_ends;
+int32_t scr_linear_affine_b4_ends(scr_ctx* ctx, const void* packed, const uint16_t* x_bf16, int32_t M,
+                                  int32_t N, int32_t K, int32_t group, const scr_qmv_ends* ends,
+                                  uint16_t* y_bf16, void* stream);
+
 /* The o / down projection with the residual add and the following RMSNorm folded in (the reference's
  * `QmvEnds` residual end, step.rs:472-482, and `fused_add_rmsnorm`, cpu_golden.rs:171-200), one launch:
  *   residual[M,N] <- bf16(residual + bf16(x @ W^T));  normed[M,N] <- rmsnorm(residual, gain, eps)

@@ -43,6 +43,7 @@ SIGNATURES = {
     "scr_affine_b4_dequant_dump": (_i32, [_vp, _vp, _i32, _i32, _i32, _vp, _vp]),
     "scr_linear_workspace_size": (_i32, [_i32, _i32, _i32, _i32, _psz]),
     "scr_linear_affine_b4": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _sz, _vp]),
+    "scr_linear_affine_b4_ends": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),
     "scr_linear_affine_b4_silu_mul": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp]),
     "scr_linear_affine_b4_residual_rmsnorm": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, ctypes.c_float, _vp,
                                                      _vp, _sz, _vp]),
@@ -86,6 +87,12 @@ SIGNATURES = {
     "scr_argmax_bf16": (_i32, [_vp, _vp, _i64, _i32, _i32, _vp, _vp]),
 }
 
+
+
+class QmvEnds(ctypes.Structure):
+    """`scr_qmv_ends` of include/scratchy_cuda.h."""
+    _fields_ = [("norm_gain", _vp), ("norm_eps", ctypes.c_float), ("norm_gain_offset", ctypes.c_float), ("bias", _vp),
+                ("scale", ctypes.c_float), ("residual", _i32), ("silu_pairs", _i32)]
 
 
 class TapeLinear(ctypes.Structure):

@@ -153,6 +153,7 @@ __global__ void affine_b4_dump_kernel(const uint8_t* __restrict__ packed, int N,
 // and normalises the rows.  `scratch` = the ticket counter (16 floats reserved), then [gridDim.x][16] f32; the
 // counter must be zero before the first call and is left zero.
 #define GEMV_OUT_RESIDUAL_NORM 3
+#define GEMV_OUT_RESIDUAL_ADD 4
 struct GemvEnds {
     uint16_t* residual;
     const uint16_t* gain;
@@ -230,6 +231,82 @@ __device__ __forceinline__ uint4 tape_ld_v4(const void* p) {
     return v;
 }
 
+// The ends of the reference's one-row matvec (`QmvEnds`, crates/targets/metal/src/tape/step.rs:472-498) that are not an
+// output mode of their own: RMSNorm applied to the input as it is loaded, the projection's bias, a scale.
+struct GemvExtra {
+    const uint16_t* bias;        // [N] bf16 or null: added to the f32 sum
+    const uint16_t* norm_gain;   // [K] bf16 or null: x is an RMSNorm's INPUT, this its gain
+    float norm_eps, norm_offset; // rmsnorm(x, gain + offset)
+    float scale;                 // multiplies the sum after the bias (1 = none)
+};
+__device__ __forceinline__ void gemv_unpack8(const uint4& v, float* f) {
+    f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xFFFF0000u);
+    f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xFFFF0000u);
+    f[4] = __uint_as_float(v.z << 16); f[5] = __uint_as_float(v.z & 0xFFFF0000u);
+    f[6] = __uint_as_float(v.w << 16); f[7] = __uint_as_float(v.w & 0xFFFF0000u);
+}
+__device__ __forceinline__ uint32_t gemv_pack2(float lo, float hi) {
+    const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&p);
+}
+// The norm-in end: the 256 consumer threads normalise the M activation rows into shared memory with the arithmetic AND
+// the summation order of the stand-alone RMSNorm kernel (thread t sums the squares of vectors t, t + 256, .. in order,
+// a shuffle tree per warp, the eight warp sums in warp order; out = bf16((x * inv_rms) * (gain + offset))), so the
+// matvec sees the very bits that kernel would have stored (golden: crates/targets/metal/src/cpu_golden.rs:25-37).
+__device__ __forceinline__ void gemv_norm_rows(const uint16_t* __restrict__ x, const GemvExtra& ex, int M, int K, uint8_t* xs,
+                                               float* red8) {
+    const int tid = threadIdx.x, nv = K >> 3;
+    for (int m = 0; m < M; ++m) {
+        const uint16_t* xr = x + (size_t)m * K;
+        float ss = 0.f;
+        for (int v = tid; v < nv; v += GEMV_CWARPS * 32) {
+            float f[8];
+            gemv_unpack8(tape_ld_v4(xr + v * 8), f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ss = __fadd_rn(ss, __fmul_rn(f[j], f[j]));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        gemv_consumer_sync();                                    // red8 of the previous row has been read
+        if ((tid & 31) == 0) red8[tid >> 5] = ss;
+        gemv_consumer_sync();
+        float total = 0.f;
+#pragma unroll
+        for (int w = 0; w < GEMV_CWARPS; ++w) total += red8[w];
+        const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, float(K)), ex.norm_eps)));
+        uint4* dst = reinterpret_cast<uint4*>(xs + (size_t)m * K * 2);
+        for (int v = tid; v < nv; v += GEMV_CWARPS * 32) {
+            float f[8], w8[8];
+            gemv_unpack8(tape_ld_v4(xr + v * 8), f);
+            gemv_unpack8(*reinterpret_cast<const uint4*>(ex.norm_gain + v * 8), w8);
+            uint32_t o[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float g0 = ex.norm_offset != 0.f ? __fadd_rn(w8[2 * j], ex.norm_offset) : w8[2 * j];
+                const float g1 = ex.norm_offset != 0.f ? __fadd_rn(w8[2 * j + 1], ex.norm_offset) : w8[2 * j + 1];
+                o[j] = gemv_pack2(__fmul_rn(__fmul_rn(f[2 * j], inv), g0), __fmul_rn(__fmul_rn(f[2 * j + 1], inv), g1));
+            }
+            dst[v] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    }
+    gemv_consumer_sync();                                        // every row is in shared memory
+}
+
+// The plain ends of one finished (row, token) sum: bias, scale, then bf16 / f32 / add into the residual stream.
+// GEMV_OUT_RESIDUAL_ADD: y IS the residual stream and receives bf16(y + bf16(sum)) — the bits the separate add produces from the
+// matvec's bf16 output (the residual end of `QmvEnds` with the roundings of `fused_add_rmsnorm`, cpu_golden.rs:171-200).
+__device__ __forceinline__ void gemv_store_plain(float total, int mode, const GemvExtra& ex, uint16_t* __restrict__ y, size_t at, int n) {
+    if (ex.bias) total += __uint_as_float(uint32_t(ex.bias[n]) << 16);
+    if (ex.scale != 1.0f) total *= ex.scale;
+    if (mode == GEMV_OUT_F32) {
+        reinterpret_cast<float*>(y)[at] = total;
+        return;
+    }
+    __nv_bfloat16 v = __float2bfloat16_rn(total);
+    if (mode == GEMV_OUT_RESIDUAL_ADD) v = __float2bfloat16_rn(__fadd_rn(__uint_as_float(uint32_t(y[at]) << 16), __bfloat162float(v)));
+    y[at] = *reinterpret_cast<const uint16_t*>(&v);
+}
+
 // A ring stage holds U blocks per consumer warp (8 * U blocks, one bulk copy): one full/empty handshake, one wait and one
 // set of loop bookkeeping per U blocks instead of per block, and U independent dequantise + MMA streams for the
 // scheduler to interleave.  Warp w takes blocks w, w + 8, .. of a stage, so a short last stage still spreads over the warps.
@@ -250,10 +327,10 @@ __device__ __forceinline__ void gemv_wait_fast(uint32_t bar, uint32_t parity, in
     if (!ok) gemv_wait_slow(bar, parity, status);
 }
 
-template <int MT, int SPLIT_CLUSTER, bool CHECK, int U>
+template <int MT, int SPLIT_CLUSTER, bool CHECK, int U, bool NORM>
 __device__ __forceinline__ void gemv_consumer(const uint16_t* __restrict__ x, uint16_t* __restrict__ y, int M, int N,
                                               int K, int kc_lo, int kc_hi, int nstage, int rb_real, int split, int sp,
-                                              int out_f32, const uint16_t* __restrict__ bias, int* __restrict__ status, uint32_t ring_base, uint32_t full_base,
+                                              int out_f32, const GemvExtra& ex, uint32_t xs_base, int* __restrict__ status, uint32_t ring_base, uint32_t full_base,
                                               uint32_t empty_base, float (*red)[GEMV_CWARPS][32][MT * 4],
                                               float (*cl_part)[16][MT * 8], const GemvEnds& ends, float (*sq_s)[16][16]) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -289,7 +366,9 @@ __device__ __forceinline__ void gemv_consumer(const uint16_t* __restrict__ x, ui
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) dst[mt][i] = tape_ld_v4(xrow[mt] + k0 + 8 * i);      // coherent: the preceding kernel wrote x
+                    for (int i = 0; i < 4; ++i)
+                        dst[mt][i] = NORM ? gemv_lds_v4(xs_base + (uint32_t)(min(mt * 8 + g, M - 1) * K + k0 + 8 * i) * 2u)   // the normalised rows
+                                          : tape_ld_v4(xrow[mt] + k0 + 8 * i);      // coherent: the preceding kernel wrote x
             };
             load_x(0, xv[0]);
             gemv_wait_fast(full_base + 8u * slot, phase, status);
@@ -332,13 +411,7 @@ __device__ __forceinline__ void gemv_consumer(const uint16_t* __restrict__ x, ui
             } else if (out_f32 == GEMV_OUT_RESIDUAL_NORM) {
                 sq_s[buf][tok][row] = gemv_residual_update(total, tok, M, n, N, ends);
             } else if (tok < M && n < N) {
-                if (bias) total += __uint_as_float(uint32_t(bias[n]) << 16);
-                if (out_f32) {
-                    reinterpret_cast<float*>(y)[(size_t)tok * N + n] = total;
-                } else {
-                    const __nv_bfloat16 v = __float2bfloat16_rn(total);
-                    y[(size_t)tok * N + n] = *reinterpret_cast<const uint16_t*>(&v);
-                }
+                gemv_store_plain(total, out_f32, ex, y, (size_t)tok * N + n, n);
             }
         }
         if (!SPLIT_CLUSTER && out_f32 == GEMV_OUT_RESIDUAL_NORM) {
@@ -353,12 +426,13 @@ __device__ __forceinline__ void gemv_consumer(const uint16_t* __restrict__ x, ui
         gemv_norm_tail(cta_sq, M, N, gridDim.x, blockIdx.x, ends, 1, GEMV_CWARPS * 32);
 }
 
-template <int MT, int SPLIT_CLUSTER, int U>
+template <int MT, int SPLIT_CLUSTER, int U, bool NORM>
 __global__ void __launch_bounds__(GEMV_THREADS, (MT == 1 ? GemvRing<U>::kCtasPerSm : 2))
 affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __restrict__ x, uint16_t* __restrict__ y,
                       int M, int N, int K, int RB, int KC, int rb_real, int split, int out_f32,
-                      const uint16_t* __restrict__ bias, int* __restrict__ status, GemvEnds ends) {
-    extern __shared__ __align__(128) uint8_t gemv_ring[];          // [stages][8 * U blocks]
+                      GemvExtra ex, int* __restrict__ status, GemvEnds ends) {
+    extern __shared__ __align__(128) uint8_t gemv_ring[];          // [stages][8 * U blocks], then (NORM) the normalised rows [M][K] bf16
+    __shared__ float norm_red[GEMV_CWARPS];
     __shared__ float sq_s[2][16][16];                              // RESIDUAL_NORM: squares of the stored residuals [token][row]
     using R = GemvRing<U>;
     __shared__ __align__(8) uint64_t full_bar[R::kStages];
@@ -412,13 +486,15 @@ affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __rest
         // load-time constant, so its (cold, HBM) fetch is issued before the wait and hides under it
         const unsigned int trailer_flag = *reinterpret_cast<const volatile unsigned int*>(packed + (size_t)RB * KC * AFF_BLOCK_BYTES);
         asm volatile("griddepcontrol.wait;" ::: "memory");        // x (and y's previous readers) are settled
+        const uint32_t xs_base = ring_base + R::kBytes;
+        if (NORM) gemv_norm_rows(x, ex, M, K, gemv_ring + R::kBytes, norm_red);
         const bool check = trailer_flag != 0;
         if (check)
-            gemv_consumer<MT, SPLIT_CLUSTER, true, U>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, out_f32, bias, status, ring_base,
-                                                   full_base, empty_base, red, cl_part, ends, sq_s);
+            gemv_consumer<MT, SPLIT_CLUSTER, true, U, NORM>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, out_f32, ex, xs_base, status,
+                                                            ring_base, full_base, empty_base, red, cl_part, ends, sq_s);
         else
-            gemv_consumer<MT, SPLIT_CLUSTER, false, U>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, out_f32, bias, status, ring_base,
-                                                    full_base, empty_base, red, cl_part, ends, sq_s);
+            gemv_consumer<MT, SPLIT_CLUSTER, false, U, NORM>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, out_f32, ex, xs_base, status,
+                                                             ring_base, full_base, empty_base, red, cl_part, ends, sq_s);
     }
 
     if (SPLIT_CLUSTER) {
@@ -453,13 +529,7 @@ affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __rest
         } else if (sp == 0 && e < SLOTS && tok < M && n < N) {
             float s = 0.f;
             for (int r = 0; r < split; ++r) s += cl_part[r][row][tok];
-            if (bias) s += __uint_as_float(uint32_t(bias[n]) << 16);
-            if (out_f32) {
-                reinterpret_cast<float*>(y)[(size_t)tok * N + n] = s;
-            } else {
-                const __nv_bfloat16 v = __float2bfloat16_rn(s);
-                y[(size_t)tok * N + n] = *reinterpret_cast<const uint16_t*>(&v);
-            }
+            gemv_store_plain(s, out_f32, ex, y, (size_t)tok * N + n, n);
         }
     }
 }
@@ -551,15 +621,22 @@ static void affine_gemv_shape(int rb_real, int KC, int sms, int ctas_per_sm, int
 struct AffineFwd {
     int out_mode = GEMV_OUT_BF16;            // GEMV_OUT_*
     const uint16_t* bias = nullptr;          // the linear's own bias [N] (bf16), added in f32 before the one rounding
+    const uint16_t* norm_gain = nullptr;     // norm-in: x is an RMSNorm's input, this its gain [K]
+    float norm_eps = 0.f, norm_offset = 0.f;
+    float scale = 1.0f;                      // multiplies the sum after the bias
     const GemvEnds* ends = nullptr;          // GEMV_OUT_RESIDUAL_NORM only
 };
+// Shared memory the norm-in end may take for the normalised rows beside the ring (two CTAs per SM).
+#define GEMV_NORM_MAX_BYTES (20 * 1024)
 
-// Blocks per warp and ring stage.  Up to 8 tokens: 3 (measured on the Llama-3.2-3B shapes: 162 executed warp instructions per
-// 1152-byte block against 197 with 1, two CTAs of 96 registers per SM instead of three of 72, the dependent chain of a
-// decode layer 6 % faster); the two-tile (9..16 tokens) kernel keeps 1: its activation registers leave no room for more.
-static int affine_gemv_u(int MT) { return MT == 1 ? 3 : 1; }
+// Blocks per warp and ring stage.  3 costs 162 executed warp instructions per 1152-byte block against 197 with 1, but runs two
+// CTAs of 96 registers per SM instead of three of 72.  Measured on Llama-3.2-3B: with 3, the dependent chain of a layer's
+// linears at one token is 6 % faster (828 against 894 us per 28 layers; as fused projections 637 against 680) and the batch-1
+// decode step 4 % (1.086 against 1.133 ms); at 8 tokens, where every lane reads its own activation row, 1 is 3 % faster
+// (1.682 against 1.733 ms).  So: 3 up to 4 tokens, 1 above (the two-tile kernel for 9..16 tokens has no registers to spare).
+static int affine_gemv_u(int M) { return M <= 4 ? 3 : 1; }
 
-template <int MT, int U>
+template <int MT, int U, bool NORM>
 static int32_t affine_gemv_launch_u(scr_ctx* ctx, const uint8_t* packed, const uint16_t* x, uint16_t* y, int M, int N,
                                     int K, const AffineFwd& f, cudaStream_t stream) {
     using R = GemvRing<U>;
@@ -567,13 +644,14 @@ static int32_t affine_gemv_launch_u(scr_ctx* ctx, const uint8_t* packed, const u
     const int rb_real = scr_ceil_div(N, 16);
     int grid_x = 1, split = 1;
     affine_gemv_shape(rb_real, g.KC, ctx->sm_count, MT == 1 ? R::kCtasPerSm : 2, &grid_x, &split);
-    auto kernel = (split == 1) ? affine_b4_gemv_kernel<MT, 0, U> : affine_b4_gemv_kernel<MT, 1, U>;
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, R::kBytes);
+    auto kernel = (split == 1) ? affine_b4_gemv_kernel<MT, 0, U, NORM> : affine_b4_gemv_kernel<MT, 1, U, NORM>;
+    const int smem = R::kBytes + (NORM ? M * K * 2 : 0);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, R::kBytes + (NORM ? GEMV_NORM_MAX_BYTES : 0));
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine_b4_gemv smem attribute: %s", cudaGetErrorString(e));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid_x, split, 1);
     cfg.blockDim = dim3(GEMV_THREADS, 1, 1);
-    cfg.dynamicSmemBytes = R::kBytes;
+    cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     int na = 0;
@@ -596,7 +674,8 @@ static int32_t affine_gemv_launch_u(scr_ctx* ctx, const uint8_t* packed, const u
         if ((size_t)(16 + grid_x * 16) * sizeof(float) > SCR_ENDS_SCRATCH_BYTES)
             return scr_fail(ctx, SCR_E_WORKSPACE, "residual + norm epilogue: %d CTAs exceed the scratch", grid_x);
     }
-    e = cudaLaunchKernelEx(&cfg, kernel, packed, x, y, M, N, K, g.RB, g.KC, rb_real, split, f.out_mode, f.bias, ctx->dev_status, ends);
+    const GemvExtra ex = {f.bias, f.norm_gain, f.norm_eps, f.norm_offset, f.scale};
+    e = cudaLaunchKernelEx(&cfg, kernel, packed, x, y, M, N, K, g.RB, g.KC, rb_real, split, f.out_mode, ex, ctx->dev_status, ends);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine_b4_gemv launch: %s", cudaGetErrorString(e));
     return scr_check_launch(ctx, "affine_b4_gemv");
 }
@@ -604,10 +683,17 @@ static int32_t affine_gemv_launch_u(scr_ctx* ctx, const uint8_t* packed, const u
 template <int MT>
 static int32_t affine_gemv_launch(scr_ctx* ctx, const uint8_t* packed, const uint16_t* x, uint16_t* y, int M, int N,
                                   int K, const AffineFwd& f, cudaStream_t stream) {
-    if (MT == 1) {
-        if (affine_gemv_u(MT) == 3) return affine_gemv_launch_u<1, 3>(ctx, packed, x, y, M, N, K, f, stream);
+    const int u = affine_gemv_u(M);
+    if (f.norm_gain) {
+        // the normalised rows sit in shared memory beside the ring: a few tokens only
+        if (MT != 1 || (size_t)M * K * 2 > GEMV_NORM_MAX_BYTES)
+            return scr_fail(ctx, SCR_E_UNSUPPORTED, "norm-in end: M=%d rows of K=%d exceed %d bytes of shared memory (run the norm on its own)",
+                            M, K, GEMV_NORM_MAX_BYTES);
+        if (u == 3) return affine_gemv_launch_u<1, 3, true>(ctx, packed, x, y, M, N, K, f, stream);
+        return affine_gemv_launch_u<1, 1, true>(ctx, packed, x, y, M, N, K, f, stream);
     }
-    return affine_gemv_launch_u<MT, 1>(ctx, packed, x, y, M, N, K, f, stream);
+    if (u == 3) return affine_gemv_launch_u<1, 3, false>(ctx, packed, x, y, M, N, K, f, stream);
+    return affine_gemv_launch_u<MT, 1, false>(ctx, packed, x, y, M, N, K, f, stream);
 }
 
 // Defined in affine_b4_gemm.cu
@@ -631,8 +717,11 @@ static int32_t affine_forward(scr_ctx* ctx, const void* packed, const uint16_t* 
     if (st) return st;
     if (M <= 0) return scr_fail(ctx, SCR_E_SHAPE, "M=%d must be positive", M);
     if (!scr_aligned16(packed) || !scr_aligned16(x)) return scr_fail(ctx, SCR_E_ALIGN, "packed/x must be 16-byte aligned");
-    if (f.bias && (f.out_mode == GEMV_OUT_SILU_PAIRS || f.out_mode == GEMV_OUT_RESIDUAL_NORM))
-        return scr_fail(ctx, SCR_E_UNSUPPORTED, "a linear bias cannot be combined with this fused epilogue");
+    if ((f.bias || f.scale != 1.0f) && (f.out_mode == GEMV_OUT_SILU_PAIRS || f.out_mode == GEMV_OUT_RESIDUAL_NORM))
+        return scr_fail(ctx, SCR_E_UNSUPPORTED, "a bias or a scale cannot be combined with this fused epilogue");
+    if (M > 16 && (f.norm_gain || f.scale != 1.0f || f.out_mode == GEMV_OUT_RESIDUAL_ADD))
+        return scr_fail(ctx, SCR_E_UNSUPPORTED, "the norm-in, scale and residual ends exist on the matvec path only (M <= 16)");
+    if (f.norm_gain && !scr_aligned16(f.norm_gain)) return scr_fail(ctx, SCR_E_ALIGN, "the norm gain must be 16-byte aligned");
     const uint8_t* pk = (const uint8_t*)packed;
     uint16_t* y = static_cast<uint16_t*>(y_);
     if (M <= 8) return affine_gemv_launch<1>(ctx, pk, x, y, M, N, K, f, stream);
@@ -677,6 +766,24 @@ extern "C" int32_t scr_linear_affine_b4_partial(scr_ctx* ctx, const void* packed
     AffineFwd f;
     f.out_mode = GEMV_OUT_F32;
     return affine_forward(ctx, packed, x, M, N, K, group, y_f32, f, workspace, workspace_bytes, (cudaStream_t)stream_);
+}
+
+// The one-row matvec with the reference's ends around it (`QmvEnds`, crates/targets/metal/src/tape/step.rs:472-498).
+extern "C" int32_t scr_linear_affine_b4_ends(scr_ctx* ctx, const void* packed, const uint16_t* x, int32_t M, int32_t N, int32_t K,
+                                             int32_t group, const scr_qmv_ends* ends, uint16_t* y, void* stream_) {
+    SCR_REQUIRE_CTX(ctx);
+    if (!ends) return scr_fail(ctx, SCR_E_ARG, "null ends");
+    AffineFwd f;
+    f.bias = ends->bias;
+    f.norm_gain = ends->norm_gain;
+    f.norm_eps = ends->norm_eps;
+    f.norm_offset = ends->norm_gain_offset;
+    f.scale = ends->scale == 0.f ? 1.0f : ends->scale;
+    if (ends->silu_pairs && ends->residual) return scr_fail(ctx, SCR_E_ARG, "the gate/up pairing and the residual end exclude each other");
+    f.out_mode = ends->residual ? GEMV_OUT_RESIDUAL_ADD : (ends->silu_pairs ? GEMV_OUT_SILU_PAIRS : GEMV_OUT_BF16);
+    if (ends->silu_pairs && (N <= 0 || N % 16 != 0)) return scr_fail(ctx, SCR_E_SHAPE, "gate/up pairing: %d fused rows (8 gate + 8 up per block)", N);
+    if (M > 16) return scr_fail(ctx, SCR_E_UNSUPPORTED, "the matvec ends exist up to 16 tokens (M=%d): run the operators separately", M);
+    return affine_forward(ctx, packed, x, M, N, K, group, y, f, nullptr, 0, (cudaStream_t)stream_);
 }
 
 extern "C" int32_t scr_linear_affine_b4_residual_rmsnorm(scr_ctx* ctx, const void* packed, const uint16_t* x, int32_t M,

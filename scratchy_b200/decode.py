@@ -332,16 +332,20 @@ class LlamaDecoder:
     """Random-init or checkpoint-loaded Llama decoder whose every linear is MLX affine int4 g64."""
 
     def __init__(self, cfg: LlamaConfig, checkpoint, device, max_pos: int = 4096, fuse_residual_norm: bool = False,
-                 fuse_rope: bool = True):
+                 fuse_rope: bool = True, fuse_ends: bool = False):
         """`checkpoint`: a `GpuWeights` (e.g. `CheckpointWeights.from_dir(...)`) or a dict of host / device
         tensors with the HF Llama names.  `fuse_rope`: run RoPE + cache append inside the attention launch where
         the cache geometry allows it (the new token's slot is then taken from block_table / seq_used_k, which a
-        decode step keeps consistent with slot_mapping)."""
+        decode step keeps consistent with slot_mapping).  `fuse_ends`: for the few tokens whose normalised rows fit the
+        matvec's shared memory, run every RMSNorm inside the matvec that consumes it and every residual add inside the
+        matvec that produces its summand (the reference's `QmvEnds`): five launches per layer instead of seven, the
+        same bits."""
         if not torch.cuda.is_available():
             raise _lib.ScratchyCudaError(-5, "LlamaDecoder needs a CUDA device (there is no CPU path)")
         self.cfg, self.device = cfg, torch.device(device)
         self.fuse_residual_norm = fuse_residual_norm
         self.fuse_rope = fuse_rope
+        self.fuse_ends = fuse_ends
         dev = self.device
         gw = checkpoint if isinstance(checkpoint, GpuWeights) else GpuWeights({k: _to_device(v, dev)
                                                                               for k, v in checkpoint.items()})
@@ -389,9 +393,15 @@ class LlamaDecoder:
         cfg = self.cfg
         qd, kd = cfg.q_dim, cfg.kv_dim
         embed(buf.ids, self.embed_table, out=buf.residual)
-        rmsnorm(buf.residual, self.layers[0].input_norm, cfg.rms_eps, out=buf.normed)
+        ends = (self.fuse_ends and not self.fuse_residual_norm and
+                AffineQuantLinear.norm_in_supported(buf.batch, cfg.hidden))
+        if not ends:
+            rmsnorm(buf.residual, self.layers[0].input_norm, cfg.rms_eps, out=buf.normed)
         for i, layer in enumerate(self.layers):
-            layer.qkv.forward(buf.normed, out=buf.qkv, workspace=buf.workspace)
+            if ends:
+                layer.qkv.forward_ends(buf.residual, buf.qkv, norm_gain=layer.input_norm, norm_eps=cfg.rms_eps)
+            else:
+                layer.qkv.forward(buf.normed, out=buf.qkv, workspace=buf.workspace)
             q, k, v = buf.qkv[:, :qd], buf.qkv[:, qd:qd + kd], buf.qkv[:, qd + kd:]
             if self.fuse_rope and rope_attention_supported(cache.block_size):
                 rope_attention_via_cache(q, k, v, buf.positions, self.cos, self.sin, cache.k[i], cache.v[i], buf.block_table,
@@ -403,7 +413,12 @@ class LlamaDecoder:
                 attention_via_cache(q, cache.k[i], cache.v[i], buf.block_table, buf.seq_used_k, cfg.n_q_heads,
                                     cfg.n_kv_heads, cfg.head_dim, cache.block_size, self.attn_scale, out=buf.attn)
             nxt = self.layers[i + 1].input_norm if i + 1 < len(self.layers) else self.final_norm
-            if self.fuse_residual_norm:
+            if ends:
+                # residual += o(attn); act = silu(gate) * up of rmsnorm(residual); residual += down(act)
+                layer.o.forward_ends(buf.attn, buf.residual, residual=True)
+                layer.gate_up.forward_ends(buf.residual, buf.act, norm_gain=layer.post_norm, norm_eps=cfg.rms_eps, silu_pairs=True)
+                layer.down.forward_ends(buf.act, buf.residual, residual=True)
+            elif self.fuse_residual_norm:
                 layer.o.forward_residual_rmsnorm(buf.attn, buf.residual, layer.post_norm, cfg.rms_eps, buf.normed,
                                                  buf.ends_scratch, delta=buf.delta, workspace=buf.workspace)
                 layer.gate_up.forward_silu_mul(buf.normed, out=buf.act, scratch=buf.gate_up, workspace=buf.workspace)
@@ -415,7 +430,10 @@ class LlamaDecoder:
                 layer.gate_up.forward_silu_mul(buf.normed, out=buf.act, scratch=buf.gate_up, workspace=buf.workspace)
                 layer.down.forward(buf.act, out=buf.delta, workspace=buf.workspace)
                 fused_add_rmsnorm(buf.residual, buf.delta, nxt, cfg.rms_eps, out=buf.normed)
-        self.lm_head.forward(buf.normed, out=buf.logits, workspace=buf.workspace)
+        if ends:
+            self.lm_head.forward_ends(buf.residual, buf.logits, norm_gain=self.final_norm, norm_eps=cfg.rms_eps)
+        else:
+            self.lm_head.forward(buf.normed, out=buf.logits, workspace=buf.workspace)
         argmax(buf.logits, out=buf.next_ids)
         return buf.logits
 

@@ -502,6 +502,92 @@ def test_llama_3b_layer_at_real_geometry_operator_by_operator(batch):
     _lib.context(0).device_status(None)
 
 
+@pytest.mark.parametrize("batch", [1, 2, 3])
+def test_matvec_ends_give_the_bits_of_the_separate_operators(batch):
+    """The reference's `QmvEnds` on the decode path: RMSNorm inside the matvec that consumes it, the residual add inside the
+    matvec that produces its summand.  A decoder that uses them (five launches per layer) and one that runs the norms and
+    adds as kernels of their own (seven) must produce the same logits, residual stream and next token, bit for bit, over
+    two steps at the Llama-3.2-3B hidden size; the ends are also checked one by one against the operators they replace."""
+    import torch
+    from scratchy_b200 import _lib, decode
+    cfg = decode.LlamaConfig(hidden=3072, n_layers=2, n_q_heads=24, n_kv_heads=8, head_dim=128, intermediate=8192,
+                             vocab=2048, rope_theta=500000.0)
+    ck = decode.synthetic_checkpoint(cfg, seed=70 + batch)
+    a = decode.LlamaDecoder(cfg, ck, "cuda:0", max_pos=256, fuse_ends=True)
+    b = decode.LlamaDecoder(cfg, ck, "cuda:0", max_pos=256, fuse_ends=False)
+    bs, max_blocks = 16, 8
+    nblk = batch * max_blocks
+    rng = np.random.default_rng(batch)
+    table = rng.permutation(nblk).reshape(batch, max_blocks).astype(np.uint32)
+    hist = [rbits(rng.standard_normal((nblk, cfg.n_kv_heads, bs, cfg.head_dim))) for _ in range(2 * cfg.n_layers)]
+    ids = rng.integers(0, cfg.vocab, size=batch).astype(np.uint32)
+    ctx_len = rng.integers(20, 100, size=batch)
+    outs = []
+    for dec in (a, b):
+        cache = decode.PagedKvCache(cfg, nblk, bs, "cuda:0")
+        for i in range(cfg.n_layers):
+            cache.k[i].copy_(bf16_dev(hist[2 * i]))
+            cache.v[i].copy_(bf16_dev(hist[2 * i + 1]))
+        buf = dec.buffers(batch, max_blocks)
+        buf.block_table.copy_(i32_dev(table))
+        cur, res = ids.copy(), []
+        n0 = _lib.context(0).launch_count()
+        for step in range(2):
+            pos = (ctx_len + step).astype(np.uint32)
+            buf.ids.copy_(i32_dev(cur))
+            buf.positions.copy_(i32_dev(pos))
+            buf.slot_mapping.copy_(i32_dev(np.array([table[q, pos[q] // bs] * bs + pos[q] % bs for q in range(batch)], np.uint32)))
+            buf.seq_used_k.copy_(i32_dev(pos + 1))
+            dec.step(buf, cache)
+            torch.cuda.synchronize()
+            res.append((bits_of(buf.logits).copy(), bits_of(buf.residual).copy(), buf.next_ids.cpu().numpy().copy()))
+            cur = res[-1][2].view(np.uint32).copy()
+        outs.append((res, _lib.context(0).launch_count() - n0))
+    (ra, la), (rb, lb) = outs
+    assert la < lb, f"the ends must save launches ({la} against {lb})"
+    for step in range(2):
+        assert np.array_equal(ra[step][1], rb[step][1]), f"step {step}: residual stream"
+        assert np.array_equal(ra[step][0], rb[step][0]), f"step {step}: logits"
+        assert np.array_equal(ra[step][2], rb[step][2]), f"step {step}: next token"
+    _lib.context(0).device_status(None)
+
+
+@pytest.mark.parametrize("N,K,M", [(1024, 3072, 1), (3072, 3072, 3), (8192, 3072, 2), (3072, 8192, 1), (136, 320, 5)])
+def test_each_matvec_end_against_the_operator_it_replaces(N, K, M):
+    import torch
+    from scratchy_b200 import AffineQuantLinear, decode
+    from util import u32_dev
+    rng = np.random.default_rng(synth.seed_for("ends1", N, K, M))
+    w, s, b = synth.affine_int4_weights(N, K, 64, synth.seed_for("endsw", N, K))
+    bias = rbits(rng.normal(0, 1, N))
+    lin = AffineQuantLinear.from_tensors(u32_dev(w), bf16_dev(s), bf16_dev(b), 64, 4)
+    linb = AffineQuantLinear.from_tensors(u32_dev(w), bf16_dev(s), bf16_dev(b), 64, 4, linear_bias=bf16_dev(bias))
+    x = bf16_dev(rbits(rng.standard_normal((M, K)) * 3.0))
+    gain = bf16_dev(rbits(1.0 + 0.1 * rng.standard_normal(K)))
+    res0 = rbits(rng.standard_normal((M, N)))
+    # norm-in == rmsnorm, then the plain linear
+    want = lin.forward(decode.rmsnorm(x, gain, 1e-5))
+    got = lin.forward_ends(x, torch.empty((M, N), dtype=torch.bfloat16, device="cuda"), norm_gain=gain, norm_eps=1e-5)
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16)), "norm-in"
+    # residual end == the linear, then residual <- bf16(residual + y)
+    y = lin.forward(x)
+    want_res = (bf16_dev(res0).float() + y.float()).to(torch.bfloat16)
+    got_res = lin.forward_ends(x, bf16_dev(res0), residual=True)
+    assert torch.equal(got_res.view(torch.int16), want_res.view(torch.int16)), "residual"
+    # bias and scale against the oracle's f32 sums
+    _, acc = oracle.affine_qmm_t_b4(w.view(np.uint8).reshape(-1), s, b, bits_of(x), M, N, K, 64, want_f32=True)
+    want_bs = rbits((acc + bf16_to_f32(bias)[None, :]) * np.float32(0.125))
+    got_bs = linb.forward_ends(x, torch.empty((M, N), dtype=torch.bfloat16, device="cuda"), scale=0.125)
+    torch.cuda.synchronize()
+    assert rel_l2(bits_of(got_bs), want_bs) <= REL_L2_TOL, "bias + scale"
+    # everything at once: norm-in, bias, scale, residual
+    yn = linb.forward_ends(x, torch.empty((M, N), dtype=torch.bfloat16, device="cuda"), norm_gain=gain, norm_eps=1e-5, scale=0.5)
+    want_all = (bf16_dev(res0).float() + yn.float()).to(torch.bfloat16)
+    got_all = linb.forward_ends(x, bf16_dev(res0), norm_gain=gain, norm_eps=1e-5, scale=0.5, residual=True)
+    torch.cuda.synchronize()
+    assert torch.equal(got_all.view(torch.int16), want_all.view(torch.int16)), "all ends"
+
+
 def test_decode_ops_against_the_committed_fixture():
     """tests/golden/decode_ops_small.npz (written by tests/golden/make_golden.py from the oracle)."""
     import os
