@@ -304,7 +304,7 @@ def run_gpu(args):
         def step_fused():
             for row in fused_layers:
                 for i in range(4):
-                    row[i].forward(fx[i], out=fy[i])
+                    row[i].forward_ends(fx[i], fy[i])
         step_fused()
         torch.cuda.synchronize(device)
         graph_f = torch.cuda.CUDAGraph()
@@ -323,7 +323,8 @@ def run_gpu(args):
         fused_info = {"value": step_bytes * args.steps / (ms_f * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": ms_f / args.steps,
                       "launches_per_step": 4 * N_LAYERS,
                       "workload": "the same 7 linears per layer as q|k|v and gate|up rows-concat fused projections "
-                                  "(the reference's load_rows_concat): 4 dependent launches per layer"}
+                                  "(the reference's load_rows_concat): 4 launches per layer in stream order, issued as a decode step "
+                                  "issues them (scr_linear_affine_b4_ends with no end set, which sizes the ring for a chain)"}
         del graph_f
     fused_layers = None
 

@@ -625,16 +625,24 @@ struct AffineFwd {
     float norm_eps = 0.f, norm_offset = 0.f;
     float scale = 1.0f;                      // multiplies the sum after the bias
     const GemvEnds* ends = nullptr;          // GEMV_OUT_RESIDUAL_NORM only
+    bool chain = false;                      // an operator of a decode chain: its input is the previous launch's output
 };
 // Shared memory the norm-in end may take for the normalised rows beside the ring (two CTAs per SM).
 #define GEMV_NORM_MAX_BYTES (20 * 1024)
 
 // Blocks per warp and ring stage.  3 costs 162 executed warp instructions per 1152-byte block against 197 with 1, but runs two
-// CTAs of 96 registers per SM instead of three of 72.  Measured on Llama-3.2-3B: with 3, the dependent chain of a layer's
-// linears at one token is 6 % faster (828 against 894 us per 28 layers; as fused projections 637 against 680) and the batch-1
-// decode step 4 % (1.086 against 1.133 ms); at 8 tokens, where every lane reads its own activation row, 1 is 3 % faster
-// (1.682 against 1.733 ms).  So: 3 up to 4 tokens, 1 above (the two-tile kernel for 9..16 tokens has no registers to spare).
-static int affine_gemv_u(int M) { return M <= 4 ? 3 : 1; }
+// CTAs of 96 registers per SM instead of three of 72.  Measured on Llama-3.2-3B at one token: where each matvec consumes
+// the previous one's output (a decode step) 3 is faster throughout (the chain of 28 layers' linears 829 against 894 us, as
+// fused projections 641 against 678 us, the batch-1 decode step 1.100 against 1.150 ms); where independent matvecs follow one
+// another in stream order and overlap their neighbours' tails, 1 is (790 against 856 us for the 196 linears), except for
+// matrices of 28 MB and more, which fill the GPU on their own.  At 8 tokens, where every lane reads its own activation row,
+// 1 is 2 % faster in both settings.  So: 3 up to 4 tokens for the operators that only a decode chain uses (the ends below) and
+// for matrices of at least GEMV_U3_MIN_BLOCKS blocks; 1 otherwise (the two-tile kernel for 9..16 tokens has no registers to spare).
+#define GEMV_U3_MIN_BLOCKS 20000
+static int affine_gemv_u(int M, int N, int K, bool chain) {
+    if (M > 4) return 1;
+    return (chain || (long long)scr_ceil_div(N, 16) * scr_ceil_div(K, AFF_BLOCK_K) >= GEMV_U3_MIN_BLOCKS) ? 3 : 1;
+}
 
 template <int MT, int U, bool NORM>
 static int32_t affine_gemv_launch_u(scr_ctx* ctx, const uint8_t* packed, const uint16_t* x, uint16_t* y, int M, int N,
@@ -683,7 +691,7 @@ static int32_t affine_gemv_launch_u(scr_ctx* ctx, const uint8_t* packed, const u
 template <int MT>
 static int32_t affine_gemv_launch(scr_ctx* ctx, const uint8_t* packed, const uint16_t* x, uint16_t* y, int M, int N,
                                   int K, const AffineFwd& f, cudaStream_t stream) {
-    const int u = affine_gemv_u(M);
+    const int u = affine_gemv_u(M, N, K, f.chain);
     if (f.norm_gain) {
         // the normalised rows sit in shared memory beside the ring: a few tokens only
         if (MT != 1 || (size_t)M * K * 2 > GEMV_NORM_MAX_BYTES)
@@ -783,6 +791,7 @@ extern "C" int32_t scr_linear_affine_b4_ends(scr_ctx* ctx, const void* packed, c
     f.out_mode = ends->residual ? GEMV_OUT_RESIDUAL_ADD : (ends->silu_pairs ? GEMV_OUT_SILU_PAIRS : GEMV_OUT_BF16);
     if (ends->silu_pairs && (N <= 0 || N % 16 != 0)) return scr_fail(ctx, SCR_E_SHAPE, "gate/up pairing: %d fused rows (8 gate + 8 up per block)", N);
     if (M > 16) return scr_fail(ctx, SCR_E_UNSUPPORTED, "the matvec ends exist up to 16 tokens (M=%d): run the operators separately", M);
+    f.chain = true;
     return affine_forward(ctx, packed, x, M, N, K, group, y, f, nullptr, 0, (cudaStream_t)stream_);
 }
 
@@ -802,6 +811,7 @@ extern "C" int32_t scr_linear_affine_b4_residual_rmsnorm(scr_ctx* ctx, const voi
     AffineFwd f;
     f.out_mode = GEMV_OUT_RESIDUAL_NORM;
     f.ends = &ends;
+    f.chain = true;
     // y is not written in this mode; the residual buffer stands in for the (unused) output pointer
     return affine_forward(ctx, packed, x, M, N, K, group, residual, f, nullptr, 0, (cudaStream_t)stream_);
 }
@@ -813,6 +823,7 @@ extern "C" int32_t scr_linear_affine_b4_silu_mul(scr_ctx* ctx, const void* packe
     if (N2 <= 0 || N2 % 16 != 0) return scr_fail(ctx, SCR_E_SHAPE, "fused silu*up epilogue: %d fused rows (8 gate + 8 up per block)", N2);
     AffineFwd f;
     f.out_mode = GEMV_OUT_SILU_PAIRS;
+    f.chain = true;
     return affine_forward(ctx, packed, x, M, N2, K, group, out, f, nullptr, 0, (cudaStream_t)stream_);
 }
 

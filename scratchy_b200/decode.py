@@ -389,6 +389,14 @@ class LlamaDecoder:
         return DecodeBuffers(self.cfg, batch, max_blocks_per_seq, self.device, self.workspace_bytes(batch))
 
     # ---- one step: reads buf.ids/positions/slot_mapping/block_table/seq_used_k, writes buf.logits/next_ids
+    @staticmethod
+    def _linear(lin, x: torch.Tensor, out: torch.Tensor, buf: DecodeBuffers) -> torch.Tensor:
+        """A linear of the step.  Up to 16 tokens it goes through the ends entry point with no end set, which marks the matvec
+        as one of a decode chain (every launch consumes the one before it; the kernel sizes its ring for that)."""
+        if buf.batch <= 16 and isinstance(lin, AffineQuantLinear):
+            return lin.forward_ends(x, out)
+        return lin.forward(x, out=out, workspace=buf.workspace)
+
     def step(self, buf: DecodeBuffers, cache: PagedKvCache) -> torch.Tensor:
         cfg = self.cfg
         qd, kd = cfg.q_dim, cfg.kv_dim
@@ -401,7 +409,7 @@ class LlamaDecoder:
             if ends:
                 layer.qkv.forward_ends(buf.residual, buf.qkv, norm_gain=layer.input_norm, norm_eps=cfg.rms_eps)
             else:
-                layer.qkv.forward(buf.normed, out=buf.qkv, workspace=buf.workspace)
+                self._linear(layer.qkv, buf.normed, buf.qkv, buf)
             q, k, v = buf.qkv[:, :qd], buf.qkv[:, qd:qd + kd], buf.qkv[:, qd + kd:]
             if self.fuse_rope and rope_attention_supported(cache.block_size):
                 rope_attention_via_cache(q, k, v, buf.positions, self.cos, self.sin, cache.k[i], cache.v[i], buf.block_table,
@@ -425,15 +433,15 @@ class LlamaDecoder:
                 layer.down.forward_residual_rmsnorm(buf.act, buf.residual, nxt, cfg.rms_eps, buf.normed, buf.ends_scratch,
                                                     delta=buf.delta, workspace=buf.workspace)
             else:
-                layer.o.forward(buf.attn, out=buf.delta, workspace=buf.workspace)
+                self._linear(layer.o, buf.attn, buf.delta, buf)
                 fused_add_rmsnorm(buf.residual, buf.delta, layer.post_norm, cfg.rms_eps, out=buf.normed)
                 layer.gate_up.forward_silu_mul(buf.normed, out=buf.act, scratch=buf.gate_up, workspace=buf.workspace)
-                layer.down.forward(buf.act, out=buf.delta, workspace=buf.workspace)
+                self._linear(layer.down, buf.act, buf.delta, buf)
                 fused_add_rmsnorm(buf.residual, buf.delta, nxt, cfg.rms_eps, out=buf.normed)
         if ends:
             self.lm_head.forward_ends(buf.residual, buf.logits, norm_gain=self.final_norm, norm_eps=cfg.rms_eps)
         else:
-            self.lm_head.forward(buf.normed, out=buf.logits, workspace=buf.workspace)
+            self._linear(self.lm_head, buf.normed, buf.logits, buf)
         argmax(buf.logits, out=buf.next_ids)
         return buf.logits
 
