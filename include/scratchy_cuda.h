@@ -364,6 +364,14 @@ int32_t scr_tp_comm_set_wait_limit(scr_tp_comm* comm, uint32_t polls);
 /* y_bf16 and/or y_f32 receive the reduced [count] values (either may be NULL, not both). */
 int32_t scr_tp_allreduce_partial(scr_tp_comm* comm, const float* partial, int64_t count,
                                  uint16_t* y_bf16, float* y_f32, void* stream);
+/* The other collective of the reference's placement lattice, `SubOp::AllGather{cols}`
+ * (crates/compiler/subtile/src/tensor_parallel.rs:1363-1386): an N-split projection (the vocabulary head) restores
+ * its full width.  Every rank passes its [rows, lc] bf16 column block; every rank receives
+ *   y[rows, cols] = the ranks' blocks side by side in absolute rank order, cropped to `cols`
+ * (world * lc >= cols: a padded last block's tail is cut off).  One launch over peer memory; a block holds at most
+ * 2 * min(max_elems, 524288) values.  Counts as one call in the communicator's call sequence. */
+int32_t scr_tp_allgather_cols(scr_tp_comm* comm, const uint16_t* local_bf16, int64_t rows, int64_t lc,
+                              int64_t cols, uint16_t* y_bf16, void* stream);
 int32_t scr_tp_comm_destroy(scr_tp_comm* comm);
 /* A row-parallel fp8-dynamic linear and its all-reduce as ONE launch, for decode sizes: the matvec's
  * epilogue stores its f32 partial sums straight into every rank's receive buffer over NVLink, and

@@ -219,6 +219,23 @@ def allreduce_rank_order(parts) -> np.ndarray:
     return out
 
 
+def allgather_cols_rank_order(parts, cols: int) -> np.ndarray:
+    """tensor_parallel.rs:1363-1386 (`SubOp::AllGather{cols}`): every rank's [rows, lc] column block side by side in
+    absolute rank order, row by row, cropped to `cols` (a padded last block's tail is cut off).  Any dtype; values
+    are moved, never changed."""
+    parts = [np.asarray(p) for p in parts]
+    rows, lc = parts[0].shape
+    if lc * len(parts) < cols:
+        raise ValueError(f"{len(parts)} blocks of {lc} columns cannot restore {cols}")
+    out = np.empty((rows, cols), parts[0].dtype)
+    for i in range(rows):
+        row = []
+        for p in parts:
+            row.extend(p[i, :lc].tolist())
+        out[i, :] = np.asarray(row[:cols], dtype=parts[0].dtype)
+    return out
+
+
 # --------------------------------------------------------------------------- decode-step operators
 # f32 in, f32 out, exactly as the reference's host golden (decode_oracle.cpp cites the lines).
 def rmsnorm(x, weight, eps=1e-5) -> np.ndarray:

@@ -69,6 +69,7 @@ SIGNATURES = {
     "scr_tp_comm_connect_local": (_i32, [_vp, ctypes.POINTER(_vp), ctypes.POINTER(_i32)]),
     "scr_tp_comm_set_wait_limit": (_i32, [_vp, ctypes.c_uint32]),
     "scr_tp_allreduce_partial": (_i32, [_vp, _vp, _i64, _vp, _vp, _vp]),
+    "scr_tp_allgather_cols": (_i32, [_vp, _vp, _i64, _i64, _i64, _vp, _vp]),
     "scr_tp_comm_destroy": (_i32, [_vp]),
     "scr_linear_fp8_dynamic_allreduce": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp]),
     "scr_linear_fp8_dynamic_static": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp]),

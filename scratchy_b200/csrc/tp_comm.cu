@@ -233,6 +233,89 @@ __global__ void __launch_bounds__(TPC_THREADS) tp_allreduce_two_phase_kernel(Tpc
     tpc_finish_call(state, e, gridDim.x);
 }
 
+// ---- all-gather of column blocks (the reference's `SubOp::AllGather{cols}`: an N-split projection, e.g. the
+// vocabulary head, restores its full width; crates/compiler/subtile/src/tensor_parallel.rs:1363-1386) -----------
+// Every rank holds `rows` x `lc` bf16 values; the result on every rank is, row by row, the ranks' blocks in
+// absolute rank order, cropped to `cols` (a padded last block's tail is cut off).  Each CTA pushes its sub-range of
+// the local block into this rank's row of every rank's dense receive area (16-byte peer stores), publishes one flag
+// per rank, waits (bounded) for the peers' CTA of the same index, and copies that sub-range of every rank's block
+// into place.  VEC: lc is a multiple of 8, so a 16-byte chunk never straddles a row.
+template <bool VEC>
+__global__ void __launch_bounds__(TPC_THREADS) tp_allgather_cols_kernel(TpcPeers peers, int world, int rank, long long one_elems,
+                                                                        const uint16_t* __restrict__ local, long long rows, long long lc,
+                                                                        long long cols, uint16_t* __restrict__ y, unsigned int* state,
+                                                                        int* status, unsigned int wait_limit) {
+    __shared__ unsigned int s_epoch;
+    const int c = blockIdx.x, tid = threadIdx.x, G = gridDim.x;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (tid == 0) s_epoch = *reinterpret_cast<volatile unsigned int*>(&state[0]) + 1u;
+    __syncthreads();
+    const unsigned int e = s_epoch;
+    const long long half = (long long)(e & 1u) * world;
+    const long long n = rows * lc;                           // bf16 values of one block
+    const long long slot = 2 * one_elems;                    // bf16 values one (half, rank) row of the dense area holds
+    const long long per = (((n + 7) / 8 + G - 1) / G) * 8;   // this CTA's sub-range, in whole 16-byte chunks
+    const long long lo = (long long)c * per, hi = min(n, lo + per);
+
+    // 1. my block -> my row of every rank's receive area
+    if (VEC) {
+        for (long long i = lo + tid * 8; i < hi; i += TPC_THREADS * 8) {
+            const uint4 v = *reinterpret_cast<const uint4*>(local + i);
+            for (int dq = 0; dq < world; ++dq) {
+                const int q = (rank + 1 + dq) % world;
+                *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(peers.recv[q]) + (half + rank) * slot + i) = v;
+            }
+        }
+    } else {
+        for (long long i = lo + tid; i < hi; i += TPC_THREADS) {
+            const uint16_t v = local[i];
+            for (int q = 0; q < world; ++q) (reinterpret_cast<uint16_t*>(peers.recv[q]) + (half + rank) * slot)[i] = v;
+        }
+    }
+    __syncthreads();
+    // 2. publish, 3. wait for every rank's CTA c (bounded)
+    if (tid < world) {
+        tpc_st_release_sys(peers.flags[tid] + (half + rank) * TPC_MAX_CTAS + c, e);
+        const unsigned int* mine = peers.flags[rank] + (half + tid) * TPC_MAX_CTAS + c;
+        bool seen = false;
+        for (unsigned int it = 0; it < wait_limit; ++it) {
+            if ((int)(tpc_ld_acquire_sys(mine) - e) >= 0) {
+                seen = true;
+                break;
+            }
+            if ((it & 1023u) == 1023u && *reinterpret_cast<volatile int*>(status) != 0) break;
+        }
+        if (!seen) atomicCAS(status, 0, TPC_ERR_FLAG_WAIT);
+    }
+    __syncthreads();
+    // 4. the blocks into place, rank order along the columns, cropped to `cols`
+    const uint16_t* got = reinterpret_cast<const uint16_t*>(peers.recv[rank]) + half * slot;
+    for (int q = 0; q < world; ++q) {
+        const uint16_t* blk = got + q * slot;
+        if (VEC) {
+            for (long long i = lo + tid * 8; i < hi; i += TPC_THREADS * 8) {
+                const long long row = i / lc, col = q * lc + (i - row * lc);
+                if (col >= cols) continue;
+                const uint4 v = ld_cg_u4(blk + i);
+                uint16_t* dst = y + row * cols + col;
+                if (col + 8 <= cols && ((row * cols + col) & 7) == 0) {
+                    *reinterpret_cast<uint4*>(dst) = v;
+                } else {
+                    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+                    for (int j = 0; j < 8 && col + j < cols; ++j) dst[j] = (uint16_t)(w[j >> 1] >> ((j & 1) * 16));
+                }
+            }
+        } else {
+            for (long long i = lo + tid; i < hi; i += TPC_THREADS) {
+                const long long row = i / lc, col = q * lc + (i - row * lc);
+                if (col < cols) y[row * cols + col] = *reinterpret_cast<const volatile uint16_t*>(blk + i);
+            }
+        }
+    }
+    tpc_finish_call(state, e, gridDim.x);
+}
+
 }  // namespace
 
 extern "C" int32_t scr_tp_comm_create(scr_ctx* ctx, int32_t world, int32_t rank, int64_t max_elems, scr_tp_comm** out,
@@ -390,6 +473,44 @@ extern "C" int32_t scr_tp_allreduce_partial(scr_tp_comm* comm, const float* part
     }
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "tp all-reduce launch: %s", cudaGetErrorString(e));
     return scr_check_launch(ctx, "tp_allreduce");
+}
+
+// `SubOp::AllGather{cols}` over peer memory: y[rows, cols] = the ranks' [rows, lc] bf16 column blocks side by side in
+// absolute rank order, cropped to `cols` (world * lc >= cols).  One launch; the same bytes on every rank.
+extern "C" int32_t scr_tp_allgather_cols(scr_tp_comm* comm, const uint16_t* local_bf16, int64_t rows, int64_t lc, int64_t cols,
+                                         uint16_t* y_bf16, void* stream) {
+    if (!comm) return SCR_E_ARG;
+    scr_ctx* ctx = comm->ctx;
+    SCR_REQUIRE_CTX(ctx);
+    if (!local_bf16 || !y_bf16) return scr_fail(ctx, SCR_E_ARG, "tp all-gather: null pointer");
+    if (!comm->connected) return scr_fail(ctx, SCR_E_COMM, "tp all-gather: peers are not connected");
+    if (rows <= 0 || lc <= 0 || cols <= 0) return scr_fail(ctx, SCR_E_SHAPE, "tp all-gather: rows=%lld lc=%lld cols=%lld must be positive",
+                                                           (long long)rows, (long long)lc, (long long)cols);
+    if (lc * comm->world < cols)
+        return scr_fail(ctx, SCR_E_SHAPE, "tp all-gather: %d blocks of %lld columns cannot restore %lld", comm->world, (long long)lc,
+                        (long long)cols);
+    const long long n = (long long)rows * lc;
+    if ((n + 7) / 8 * 8 > 2 * comm->one_elems)
+        return scr_fail(ctx, SCR_E_SHAPE, "tp all-gather: a block of %lld values exceeds the receive area (%lld)", n, 2 * comm->one_elems);
+    const bool vec = lc % 8 == 0 && scr_aligned16(local_bf16);
+    const TpcPeers peers = tpc_peer_table(comm);
+    // the same grid on every rank: it depends on the block's size only
+    const int grid = (int)std::min<long long>((n + TPC_THREADS * 8 - 1) / (TPC_THREADS * 8), TPC_MAX_GRID);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(TPC_THREADS);
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    auto kernel = vec ? tp_allgather_cols_kernel<true> : tp_allgather_cols_kernel<false>;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, peers, comm->world, comm->rank, (long long)comm->one_elems, local_bf16,
+                                             (long long)rows, (long long)lc, (long long)cols, y_bf16, comm->state, ctx->dev_status,
+                                             comm->wait_limit);
+    if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "tp all-gather launch: %s", cudaGetErrorString(e));
+    return scr_check_launch(ctx, "tp_allgather_cols");
 }
 
 extern "C" int32_t scr_tp_comm_destroy(scr_tp_comm* comm) {

@@ -104,6 +104,18 @@ class TpCommunicator:
             dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
         return t
 
+    def all_gather_cols(self, local: torch.Tensor, cols: int) -> torch.Tensor:
+        """The `SubOp::AllGather{cols}` of an N-split layer (crates/compiler/subtile/src/tensor_parallel.rs:1363-1386):
+        the ranks' [rows, lc] column blocks side by side in rank order, cropped to `cols`."""
+        rows, lc = local.shape
+        if lc * self.tp.world < cols:
+            raise ValueError(f"{self.tp.world} blocks of {lc} columns cannot restore {cols}")
+        if self.tp.world == 1:
+            return local[:, :cols].contiguous()
+        blocks = [torch.empty_like(local) for _ in range(self.tp.world)]
+        dist.all_gather(blocks, local.contiguous(), group=self.group)
+        return torch.cat(blocks, dim=1)[:, :cols].contiguous()
+
 
 class OneShotAllReduce:
     """The decode-size exchange: `scr_tp_allreduce_partial`, one kernel per rank over NVLink peer memory,
@@ -180,6 +192,20 @@ class OneShotAllReduce:
             ctypes.c_void_p(torch.cuda.current_stream(part.device).cuda_stream)))
         return out_bf16 if out_bf16 is not None else out_f32
 
+    def all_gather_cols(self, local: torch.Tensor, cols: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """`scr_tp_allgather_cols`: the ranks' [rows, lc] bf16 column blocks side by side in rank order, cropped to
+        `cols`, on every rank, as one launch over peer memory."""
+        import ctypes
+        if local.dtype != torch.bfloat16 or not local.is_cuda or not local.is_contiguous() or local.dim() != 2:
+            raise ValueError("the column block must be a contiguous 2-D bf16 CUDA tensor")
+        rows, lc = (int(v) for v in local.shape)
+        if out is None:
+            out = torch.empty((rows, cols), dtype=torch.bfloat16, device=local.device)
+        self._ctx.check(self._lib.lib().scr_tp_allgather_cols(
+            self._h, ctypes.c_void_p(local.data_ptr()), rows, lc, int(cols), ctypes.c_void_p(out.data_ptr()),
+            ctypes.c_void_p(torch.cuda.current_stream(local.device).cuda_stream)))
+        return out
+
     def fp8_linear_all_reduce(self, linear, x_local: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """A row-parallel `Fp8Linear` and its all-reduce as one launch (`scr_linear_fp8_dynamic_allreduce`):
         the same bits as `linear.forward_partial` followed by `all_reduce`.  Raises SCR_E_UNSUPPORTED beyond
@@ -244,10 +270,28 @@ class RowParallel:
 
 
 class ColumnParallel:
-    """A column-parallel linear (q/k/v, gate/up): whole activation in, the rank's channels out."""
+    """A column-parallel linear (q/k/v, gate/up): whole activation in, the rank's channels out.  With `gather_cols`
+    (an N-split vocabulary head) the ranks' channel blocks are gathered back to the full width on every rank:
+    through `one_shot` as one launch over peer memory, else through the process group of `comm`."""
 
-    def __init__(self, linear):
+    def __init__(self, linear, comm: Optional[TpCommunicator] = None, one_shot: Optional[OneShotAllReduce] = None,
+                 gather_cols: Optional[int] = None):
+        if gather_cols is not None and comm is None and one_shot is None:
+            raise ValueError("gather_cols needs a communicator")
         self.linear = linear
+        self.comm = comm
+        self.one_shot = one_shot
+        self.gather_cols = gather_cols
 
     def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, workspace=None) -> torch.Tensor:
-        return self.linear.forward(x, out=out, workspace=workspace)
+        if self.gather_cols is None:
+            return self.linear.forward(x, out=out, workspace=workspace)
+        local = self.linear.forward(x, workspace=workspace)
+        local = local.reshape(-1, local.shape[-1])
+        if self.one_shot is not None and local.numel() <= 2 * min(self.one_shot.max_elems, 524288):
+            return self.one_shot.all_gather_cols(local, self.gather_cols, out=out)
+        full = self.comm.all_gather_cols(local, self.gather_cols)
+        if out is not None:
+            out.copy_(full)
+            return out
+        return full

@@ -128,9 +128,27 @@ def _gloo_worker(rank, world, port, q):
         else:                               # the collective's order is not rank order: the 1e-3 bar applies
             gf, wf = oracle.bf16_bits_to_f32(got).astype(np.float64), oracle.bf16_bits_to_f32(want).astype(np.float64)
             ok = bool(np.linalg.norm(gf - wf) / np.linalg.norm(wf) <= 1e-3)
+        # AllGather{cols}: the ranks' column blocks in rank order, the padded tail cropped
+        rng = np.random.default_rng(5)
+        blocks = [rng.integers(0, 65536, size=(3, 10)).astype(np.int32) for _ in range(world)]
+        cols = 10 * world - 3
+        got = comm.all_gather_cols(torch.from_numpy(blocks[rank]), cols).numpy()
+        ok = ok and bool(np.array_equal(got, oracle.allgather_cols_rank_order(blocks, cols)))
         q.put((rank, ok))
     finally:
         dist.destroy_process_group()
+
+
+def test_all_gather_law_small_case():
+    """tensor_parallel.rs:1363-1386 restated on a case small enough to write out: two ranks, blocks of 3 columns,
+    5 real columns: the last block's padded column is cut off, row by row."""
+    a = np.array([[1, 2, 3], [7, 8, 9]], np.uint16)
+    b = np.array([[4, 5, 99], [10, 11, 99]], np.uint16)
+    assert np.array_equal(oracle.allgather_cols_rank_order([a, b], 5), np.array([[1, 2, 3, 4, 5], [7, 8, 9, 10, 11]], np.uint16))
+    with pytest.raises(ValueError):
+        oracle.allgather_cols_rank_order([a, b], 7)
+    comm = tpmod.TpCommunicator(TpWorld(1, 0))
+    assert torch.equal(comm.all_gather_cols(torch.from_numpy(a.astype(np.int32)), 2), torch.tensor([[1, 2], [7, 8]], dtype=torch.int32))
 
 
 @pytest.mark.parametrize("world", [2, 4])

@@ -97,6 +97,7 @@ def _nccl_worker(rank, world, port, q):
     from scratchy_b200 import AffineQuantLinear, Fp8Linear, tp as tpmod
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")           # a rank that fails must not die bound to a multicast object
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
@@ -139,6 +140,27 @@ def _nccl_worker(rank, world, port, q):
             ok &= bool(np.array_equal(got.view(torch.int16).cpu().numpy().view(np.uint16), big_bits))
             got = one.all_reduce(mine)
             ok &= bool(np.array_equal(got.view(torch.int16).cpu().numpy().view(np.uint16), want_bits))
+        # the other collective, AllGather{cols}: column blocks side by side in rank order, the padded tail cropped;
+        # 16-byte rows, odd rows (the scalar form), and an N-split vocabulary head through ColumnParallel
+        for rows_g, lc_g, cols_g in [(3, 1024, world * 1024), (5, 64, world * 64 - 24), (2, 37, world * 37 - 5)]:
+            blocks = [synth.f32_to_bf16_bits(rng.standard_normal((rows_g, lc_g)).astype(np.float32) + r) for r in range(world)]
+            want_g = oracle.allgather_cols_rank_order(blocks, cols_g)
+            mine_g = torch.from_numpy(blocks[rank].view(np.int16)).view(torch.bfloat16).to(dev)
+            for _ in range(2):
+                got = one.all_gather_cols(mine_g, cols_g)
+                ok &= bool(np.array_equal(got.view(torch.int16).cpu().numpy().view(np.uint16), want_g))
+                got = one.all_reduce(mine)                   # interleaved with the all-reduce on the same communicator
+                ok &= bool(np.array_equal(got.view(torch.int16).cpu().numpy().view(np.uint16), want_bits))
+            got = comm.all_gather_cols(mine_g, cols_g)       # the process group's form gives the same bytes
+            ok &= bool(np.array_equal(got.view(torch.int16).cpu().numpy().view(np.uint16), want_g))
+        vocab = 64 * world
+        wv, sv, bv = synth.affine_int4_weights(vocab, K, 64, 47)
+        head = AffineQuantLinear.from_tensors(*tpmod.shard_affine_column_parallel(
+            torch.from_numpy(wv.view(np.int32)).to(dev), torch.from_numpy(sv.view(np.int16)).view(torch.bfloat16).to(dev),
+            torch.from_numpy(bv.view(np.int16)).view(torch.bfloat16).to(dev), tp))
+        logits = tpmod.ColumnParallel(head, comm, one_shot=one, gather_cols=vocab).forward(xt)
+        want_logits = oracle.affine_qmm_t_b4(wv.view(np.uint8).reshape(-1), sv, bv, x, M, vocab, K, 64)
+        ok &= rel_l2(logits.view(torch.int16).cpu().numpy().view(np.uint16), want_logits) <= REL_L2_TOL
         got16 = torch.empty((5, 1024), dtype=torch.bfloat16, device=dev)
         got32 = torch.empty((5, 1024), dtype=torch.float32, device=dev)
         torch.cuda.synchronize()
@@ -188,6 +210,13 @@ def _nccl_worker(rank, world, port, q):
         _lib_ctx.device_status(None)                         # no bounded flag wait ran out
         one.close()
         q.put((rank, bool(ok)))
+    except BaseException as exc:                             # a rank that raises reports it at once: the parent must not wait
+        import traceback
+        q.put((rank, f"{type(exc).__name__}: {exc}\n{traceback.format_exc()}"))
+        q.close()
+        q.join_thread()
+        torch.cuda.synchronize()                             # leave with none of this rank's kernels in flight
+        os._exit(1)                                          # no collective teardown with a peer that may be mid-call
     finally:
         dist.destroy_process_group()
 
@@ -208,10 +237,16 @@ def test_ranks_nccl_row_parallel(world):
     procs = [ctx.Process(target=_nccl_worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
-    res = [q.get(timeout=600) for _ in procs]
+    res = []
+    for _ in procs:
+        res.append(q.get(timeout=240))
+        if res[-1][1] is not True:                           # one rank failed: the others may be waiting for it
+            break
     for p in procs:
-        p.join(timeout=60)
-    assert sorted(res) == [(r, True) for r in range(world)]
+        p.join(timeout=20 if len(res) == len(procs) and all(r[1] is True for r in res) else 1)
+        if p.is_alive():
+            p.kill()                                         # exactly the processes this test started
+    assert sorted(res) == [(r, True) for r in range(world)], res
 
 
 def test_ranks_as_threads_of_one_process_connect_locally():
@@ -235,7 +270,8 @@ def test_ranks_as_threads_of_one_process_connect_locally():
     rng = np.random.default_rng(11)
     small = [rng.standard_normal((3, 1024)).astype(np.float32) * (1.0 + r) for r in range(world)]
     large = [rng.standard_normal((40, 1024)).astype(np.float32) * (1.0 + r) for r in range(world)]
-    comms, results, errors = [None] * world, [None] * world, []
+    blocks = [synth.f32_to_bf16_bits(rng.standard_normal((4, 264)).astype(np.float32)) for _ in range(world)]
+    comms, results, gathered, errors = [None] * world, [None] * world, [None] * world, []
     gate = threading.Barrier(world)
 
     def rank_thread(r):
@@ -251,6 +287,8 @@ def test_ranks_as_threads_of_one_process_connect_locally():
                 got = comms[r].all_reduce(torch.from_numpy(parts[r]).to(dev))
                 torch.cuda.synchronize(dev)
                 out.append(bits_of(got))
+            gathered[r] = bits_of(comms[r].all_gather_cols(bf16_dev(blocks[r]).to(dev), 2 * 264 - 8))
+            torch.cuda.synchronize(dev)
             results[r] = out
             _lib.context(r).device_status(None)
             gate.wait()                                          # nobody frees a buffer a peer may still write
@@ -268,6 +306,7 @@ def test_ranks_as_threads_of_one_process_connect_locally():
     for r in range(world):
         for got, parts in zip(results[r], (small, large, small)):
             assert np.array_equal(got, oracle.f32_to_bf16_bits(oracle.allreduce_rank_order(parts)))
+        assert np.array_equal(gathered[r], oracle.allgather_cols_rank_order(blocks, 2 * 264 - 8))
 
 
 def test_a_bounded_wait_that_runs_out_is_reported_and_the_next_call_works():
@@ -303,6 +342,24 @@ def test_a_bounded_wait_that_runs_out_is_reported_and_the_next_call_works():
     assert np.array_equal(bits_of(got), oracle.f32_to_bf16_bits(part.cpu().numpy()))
     ctx.device_status(None)
     good.close()
+
+
+@pytest.mark.parametrize("rows,lc,cols", [(1, 128256, 128256), (4, 4096, 4000), (3, 37, 30), (16, 8, 8)])
+def test_all_gather_cols_single_rank(rows, lc, cols):
+    """`SubOp::AllGather{cols}` at world 1 is the crop of the padded block; the oracle's law gives the bytes."""
+    import torch
+    from scratchy_b200 import _lib, tp as tpmod
+    dev = torch.device("cuda", 0)
+    one = tpmod.OneShotAllReduce(tpmod.TpWorld(1, 0), dev, max_elems=256 * 1024)
+    blk = synth.f32_to_bf16_bits(np.random.default_rng(rows * lc).standard_normal((rows, lc)).astype(np.float32))
+    for _ in range(2):
+        got = one.all_gather_cols(bf16_dev(blk), cols)
+        torch.cuda.synchronize()
+        assert np.array_equal(bits_of(got), oracle.allgather_cols_rank_order([blk], cols))
+    with pytest.raises(_lib.ScratchyCudaError) as e:
+        one.all_gather_cols(bf16_dev(blk), lc + 1)               # one block of lc columns cannot restore lc + 1
+    assert e.value.name == "SCR_E_SHAPE"
+    one.close()
 
 
 def test_one_shot_all_reduce_single_rank():
