@@ -60,20 +60,22 @@ int64_t scr_launch_count(const scr_ctx* ctx);
  * range).  Not for the step path. */
 int32_t scr_device_status(scr_ctx* ctx, void* stream, int32_t* code);
 
-/* ---- MLX affine int4, group 64: load-time repack --------------------------
+/* ---- MLX affine int4 (groups of 32, 64 or 128): load-time repack ------------
  * Replaces `MetalAffineQuantOps::load` (crates/targets/metal/src/layers_quant.rs:289-345)
  * + `load_layered_linear_affine_quant` (crates/targets/metal/src/loaders.rs:96-116): the
  * checkpoint tensors of `AffineQuantLinear` (crates/models/quantization/src/layers_quant.rs:33-52)
  *   w       U32  [N, K/8]   element i of a word at bits [4i, 4i+4)
- *   scales  F16 or BF16 [N, K/64]   (`scale_dtype`: the model's SCALE_DTYPE the loader pins,
- *   biases  F16 or BF16 [N, K/64]    crates/targets/metal/src/layers_quant.rs:238-285)
+ *   scales  F16 or BF16 [N, K/group]   (`scale_dtype`: the model's SCALE_DTYPE the loader pins,
+ *   biases  F16 or BF16 [N, K/group]    crates/targets/metal/src/layers_quant.rs:238-285)
  * already resident on the device, are rewritten once into the kernels' streaming
  * layout (`dst`, `scr_affine_b4_repack_size` bytes, 128-byte aligned).  F16 scales and biases —
  * what every mlx-community 4-bit checkpoint ships — are narrowed to the bf16 activation type here,
  * exactly as the reference narrows them before it multiplies (`TAct::from_f32(scale.to_f32())`,
  * crates/targets/metal/src/cpu_reference.rs:63-68,90-92), so the kernels see one layout.
- * Validation follows layers_quant.rs:310-338: bits == 4, K % group == 0; this build
- * implements group == 64 only (SCR_E_DTYPE otherwise). */
+ * Validation follows layers_quant.rs:310-338: bits == 4, K % group == 0; group is 32, 64 or 128, the
+ * sizes the reference's lowering admits (crates/compiler/subtile/src/lower.rs:112-127; SCR_E_DTYPE otherwise).
+ * Every forward entry point takes the three; two things are built for groups of 64 and 128 only and answer
+ * SCR_E_UNSUPPORTED at 32: the norm-in end of `scr_linear_affine_b4_ends` and the matvec tape. */
 int32_t scr_affine_b4_repack_size(int32_t N, int32_t K, int32_t group, size_t* bytes);
 /* The reference's `DType` discriminants (crates/tensors/src/dtype.rs:7-16). */
 #define SCR_DTYPE_F16  0

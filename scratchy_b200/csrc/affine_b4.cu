@@ -1,4 +1,4 @@
-// MLX affine int4 (group 64): load-time repack, dequant dump hook and the decode matvec.
+// MLX affine int4 (groups of 32, 64, 128): load-time repack, dequant dump hook and the decode matvec.
 #include "affine_b4.cuh"
 #include "gemv_common.cuh"
 
@@ -35,16 +35,19 @@ __device__ __forceinline__ uint32_t affine_scale_bits(uint16_t raw, int f16) {
 }
 
 __global__ void affine_b4_repack_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict__ scales,
-                                        const uint16_t* __restrict__ biases, int f16, int N, int K, int RB, int KC,
+                                        const uint16_t* __restrict__ biases, int f16, int N, int K, int group, int gs, int RB, int KC,
                                         uint8_t* __restrict__ dst, unsigned int* __restrict__ slow_flag) {
     const long long nblocks = (long long)RB * KC;
-    const long long items = nblocks * 80;               // 64 pieces + 16 scale entries per block
+    const int epr = 1 << gs;                            // entries per row and block
+    const int per_block = 64 + 8 * epr;                 // 64 pieces + one 8-byte entry per row pair and k extent
+    const int block_bytes = aff_block_bytes(gs);
+    const long long items = nblocks * per_block;
     for (long long it = blockIdx.x * (long long)blockDim.x + threadIdx.x; it < items;
          it += (long long)gridDim.x * blockDim.x) {
-        const long long blk = it / 80;
-        const int sub = int(it % 80);
+        const long long blk = it / per_block;
+        const int sub = int(it % per_block);
         const int rb = int(blk / KC), kc = int(blk % KC);
-        uint8_t* out = dst + blk * AFF_BLOCK_BYTES;
+        uint8_t* out = dst + blk * block_bytes;
         if (sub < 64) {
             const int half = sub >> 5, lane = sub & 31, g = lane >> 2, t = lane & 3;
             const int row = rb * 16 + half * 8 + g;
@@ -59,11 +62,13 @@ __global__ void affine_b4_repack_kernel(const uint32_t* __restrict__ w, const ui
             }
             *reinterpret_cast<uint4*>(out + half * 512 + lane * 16) = v;
         } else {
-            const int e = sub - 64, g = e >> 1, h = e & 1;
-            const int grp = kc * 2 + h;
+            // entry e = g * epr + h covers k [kc * 128 + h * (128 / epr), +128 / epr) of rows g and g + 8; with groups of
+            // 128 both entries of a row are the same group's
+            const int e = sub - 64, g = e >> gs, h = e & (epr - 1);
+            const int k0 = kc * 128 + h * (128 >> gs);
             uint2 v = make_uint2(0, 0);
-            if (grp * 64 < K) {
-                const int G = K / 64;
+            if (k0 < K) {
+                const int G = K / group, grp = k0 / group;
                 const int r0 = rb * 16 + g, r1 = r0 + 8;
                 if (r0 < N) v.x = affine_scale_bits(scales[(size_t)r0 * G + grp], f16) | (affine_scale_bits(biases[(size_t)r0 * G + grp], f16) << 16);
                 if (r1 < N) v.y = affine_scale_bits(scales[(size_t)r1 * G + grp], f16) | (affine_scale_bits(biases[(size_t)r1 * G + grp], f16) << 16);
@@ -83,10 +88,11 @@ __global__ void affine_b4_repack_fence_kernel() {}
 // ------------------------------------------------------------------------------------
 // Dump hook: streaming blocks -> dense bf16 [N, K], through affine_dequant_piece.
 // ------------------------------------------------------------------------------------
-__global__ void affine_b4_dump_kernel(const uint8_t* __restrict__ packed, int N, int K, int RB, int KC,
+__global__ void affine_b4_dump_kernel(const uint8_t* __restrict__ packed, int N, int K, int gs, int RB, int KC,
                                       uint16_t* __restrict__ out) {
     const long long items = (long long)RB * KC * 64;
-    const bool check = *reinterpret_cast<const unsigned int*>(packed + (size_t)RB * KC * AFF_BLOCK_BYTES) != 0;
+    const int block_bytes = aff_block_bytes(gs);
+    const bool check = *reinterpret_cast<const unsigned int*>(packed + (size_t)RB * KC * block_bytes) != 0;
     for (long long it = blockIdx.x * (long long)blockDim.x + threadIdx.x; it < items;
          it += (long long)gridDim.x * blockDim.x) {
         const long long blk = it / 64;
@@ -96,9 +102,9 @@ __global__ void affine_b4_dump_kernel(const uint8_t* __restrict__ packed, int N,
         const int row = rb * 16 + half * 8 + g;
         const int k0 = kc * 128 + t * 32;
         if (row >= N || k0 >= K) continue;
-        const uint8_t* b = packed + blk * AFF_BLOCK_BYTES;
+        const uint8_t* b = packed + blk * block_bytes;
         const uint4 piece = *reinterpret_cast<const uint4*>(b + half * 512 + lane * 16);
-        const uint2 sb2 = *reinterpret_cast<const uint2*>(b + 1024 + (g * 2 + (t >> 1)) * 8);
+        const uint2 sb2 = *reinterpret_cast<const uint2*>(b + 1024 + ((g << gs) + (t >> (2 - gs))) * 8);
         uint32_t regs[16];
         const uint32_t sb = half ? sb2.y : sb2.x;
         if (check) {
@@ -310,9 +316,10 @@ __device__ __forceinline__ void gemv_store_plain(float total, int mode, const Ge
 // A ring stage holds U blocks per consumer warp (8 * U blocks, one bulk copy): one full/empty handshake, one wait and one
 // set of loop bookkeeping per U blocks instead of per block, and U independent dequantise + MMA streams for the
 // scheduler to interleave.  Warp w takes blocks w, w + 8, .. of a stage, so a short last stage still spreads over the warps.
-template <int U> struct GemvRing {
+template <int U, int GS = 1> struct GemvRing {
+    static constexpr int kBlockBytes = aff_block_bytes(GS);
     static constexpr int kStageBlocks = GEMV_CWARPS * U;
-    static constexpr int kStageBytes = kStageBlocks * AFF_BLOCK_BYTES;
+    static constexpr int kStageBytes = kStageBlocks * kBlockBytes;
     static constexpr int kStages = (U == 1) ? 4 : 3;
     static constexpr int kBytes = kStages * kStageBytes;
     static constexpr int kCtasPerSm = (U <= 2) ? 3 : 2;
@@ -327,7 +334,7 @@ __device__ __forceinline__ void gemv_wait_fast(uint32_t bar, uint32_t parity, in
     if (!ok) gemv_wait_slow(bar, parity, status);
 }
 
-template <int MT, int SPLIT_CLUSTER, bool CHECK, int U, bool NORM>
+template <int MT, int SPLIT_CLUSTER, bool CHECK, int U, bool NORM, int GS>
 __device__ __forceinline__ void gemv_consumer(const uint16_t* __restrict__ x, uint16_t* __restrict__ y, int M, int N,
                                               int K, int kc_lo, int kc_hi, int nstage, int rb_real, int split, int sp,
                                               int out_f32, const GemvExtra& ex, uint32_t xs_base, int* __restrict__ status, uint32_t ring_base, uint32_t full_base,
@@ -342,7 +349,7 @@ __device__ __forceinline__ void gemv_consumer(const uint16_t* __restrict__ x, ui
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) xrow[mt] = x + (size_t)min(mt * 8 + g, M - 1) * K;
 
-    using R = GemvRing<U>;
+    using R = GemvRing<U, GS>;
     uint32_t slot = 0, phase = 0;              // ring position and phase of the next stage
     int it = 0;
     for (int rb = blockIdx.x; rb < rb_real; rb += gridDim.x, ++it) {
@@ -372,12 +379,12 @@ __device__ __forceinline__ void gemv_consumer(const uint16_t* __restrict__ x, ui
             };
             load_x(0, xv[0]);
             gemv_wait_fast(full_base + 8u * slot, phase, status);
-            const uint32_t stage = ring_base + slot * R::kStageBytes + warp * AFF_BLOCK_BYTES;
+            const uint32_t stage = ring_base + slot * R::kStageBytes + warp * R::kBlockBytes;
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 if (u + 1 < U) load_x(u + 1, xv[(u + 1) & 1]);
                 if (kc0 + u * GEMV_CWARPS < kc_hi)                // warp-uniform
-                    gemv_block_compute<MT, CHECK>(stage + u * GEMV_CWARPS * AFF_BLOCK_BYTES, acc, xv[u & 1], lane);
+                    gemv_block_compute<MT, CHECK, GS>(stage + u * GEMV_CWARPS * R::kBlockBytes, acc, xv[u & 1], lane);
             }
             __syncwarp();                                         // every lane has consumed the stage
             if (lane == 0) gemv_mbar_arrive(empty_base + 8u * slot);
@@ -426,15 +433,15 @@ __device__ __forceinline__ void gemv_consumer(const uint16_t* __restrict__ x, ui
         gemv_norm_tail(cta_sq, M, N, gridDim.x, blockIdx.x, ends, 1, GEMV_CWARPS * 32);
 }
 
-template <int MT, int SPLIT_CLUSTER, int U, bool NORM>
-__global__ void __launch_bounds__(GEMV_THREADS, (MT == 1 ? GemvRing<U>::kCtasPerSm : 2))
+template <int MT, int SPLIT_CLUSTER, int U, bool NORM, int GS>
+__global__ void __launch_bounds__(GEMV_THREADS, (MT == 1 ? GemvRing<U, GS>::kCtasPerSm : 2))
 affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __restrict__ x, uint16_t* __restrict__ y,
                       int M, int N, int K, int RB, int KC, int rb_real, int split, int out_f32,
                       GemvExtra ex, int* __restrict__ status, GemvEnds ends) {
     extern __shared__ __align__(128) uint8_t gemv_ring[];          // [stages][8 * U blocks], then (NORM) the normalised rows [M][K] bf16
     __shared__ float norm_red[GEMV_CWARPS];
     __shared__ float sq_s[2][16][16];                              // RESIDUAL_NORM: squares of the stored residuals [token][row]
-    using R = GemvRing<U>;
+    using R = GemvRing<U, GS>;
     __shared__ __align__(8) uint64_t full_bar[R::kStages];
     __shared__ __align__(8) uint64_t empty_bar[R::kStages];
     __shared__ float red[2][GEMV_CWARPS][32][MT * 4];
@@ -470,10 +477,10 @@ affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __rest
         if (lane == 0) {
             uint32_t slot = 0, phase = 0;
             for (int rb = blockIdx.x; rb < rb_real; rb += gridDim.x) {
-                const uint8_t* src = packed + ((size_t)rb * KC + kc_lo) * AFF_BLOCK_BYTES;
+                const uint8_t* src = packed + ((size_t)rb * KC + kc_lo) * R::kBlockBytes;
                 for (int j = 0; j < nstage; ++j) {
                     gemv_wait(empty_base + 8u * slot, phase ^ 1u, status);
-                    const uint32_t bytes = (uint32_t)min(R::kStageBlocks, kc_hi - kc_lo - j * R::kStageBlocks) * AFF_BLOCK_BYTES;
+                    const uint32_t bytes = (uint32_t)min(R::kStageBlocks, kc_hi - kc_lo - j * R::kStageBlocks) * R::kBlockBytes;
                     gemv_arrive_expect_tx(full_base + 8u * slot, bytes);
                     gemv_bulk_g2s(ring_base + slot * R::kStageBytes, src + (size_t)j * R::kStageBytes, bytes, full_base + 8u * slot);
                     if (++slot == R::kStages) { slot = 0; phase ^= 1u; }
@@ -484,16 +491,16 @@ affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __rest
     } else {
         // one word per matrix says whether any group needs the exact (two-step rounding) path; it is a
         // load-time constant, so its (cold, HBM) fetch is issued before the wait and hides under it
-        const unsigned int trailer_flag = *reinterpret_cast<const volatile unsigned int*>(packed + (size_t)RB * KC * AFF_BLOCK_BYTES);
+        const unsigned int trailer_flag = *reinterpret_cast<const volatile unsigned int*>(packed + (size_t)RB * KC * R::kBlockBytes);
         asm volatile("griddepcontrol.wait;" ::: "memory");        // x (and y's previous readers) are settled
         const uint32_t xs_base = ring_base + R::kBytes;
         if (NORM) gemv_norm_rows(x, ex, M, K, gemv_ring + R::kBytes, norm_red);
         const bool check = trailer_flag != 0;
         if (check)
-            gemv_consumer<MT, SPLIT_CLUSTER, true, U, NORM>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, out_f32, ex, xs_base, status,
+            gemv_consumer<MT, SPLIT_CLUSTER, true, U, NORM, GS>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, out_f32, ex, xs_base, status,
                                                             ring_base, full_base, empty_base, red, cl_part, ends, sq_s);
         else
-            gemv_consumer<MT, SPLIT_CLUSTER, false, U, NORM>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, out_f32, ex, xs_base, status,
+            gemv_consumer<MT, SPLIT_CLUSTER, false, U, NORM, GS>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, out_f32, ex, xs_base, status,
                                                              ring_base, full_base, empty_base, red, cl_part, ends, sq_s);
     }
 
@@ -539,7 +546,8 @@ affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __rest
 // ------------------------------------------------------------------------------------
 static int32_t affine_check_shape(scr_ctx* ctx, int N, int K, int group) {
     if (N <= 0 || K <= 0) return scr_fail(ctx, SCR_E_SHAPE, "N=%d K=%d must be positive", N, K);
-    if (group != 64) return scr_fail(ctx, SCR_E_DTYPE, "group_size=%d: this build implements group 64 only", group);
+    if (group != 32 && group != 64 && group != 128)
+        return scr_fail(ctx, SCR_E_DTYPE, "group_size=%d: the affine presets have groups of 32, 64 or 128", group);
     if (K % group != 0) return scr_fail(ctx, SCR_E_SHAPE, "K=%d not divisible by group_size=%d", K, group);
     return SCR_OK;
 }
@@ -547,9 +555,9 @@ static int32_t affine_check_shape(scr_ctx* ctx, int N, int K, int group) {
 extern "C" int32_t scr_affine_b4_repack_size(int32_t N, int32_t K, int32_t group, size_t* bytes) {
     if (!bytes) return SCR_E_ARG;
     if (N <= 0 || K <= 0) return SCR_E_SHAPE;
-    if (group != 64) return SCR_E_DTYPE;
+    if (group != 32 && group != 64 && group != 128) return SCR_E_DTYPE;
     if (K % group != 0) return SCR_E_SHAPE;
-    const AffineGeom g = affine_geom(N, K);
+    const AffineGeom g = affine_geom(N, K, group);
     *bytes = affine_packed_bytes(g);
     return SCR_OK;
 }
@@ -563,15 +571,15 @@ extern "C" int32_t scr_affine_b4_repack(scr_ctx* ctx, const uint32_t* w, const u
     int32_t st = affine_check_shape(ctx, N, K, group);
     if (st) return st;
     if (!scr_aligned16(w) || !scr_aligned16(dst)) return scr_fail(ctx, SCR_E_ALIGN, "w/dst must be 16-byte aligned");
-    const AffineGeom g = affine_geom(N, K);
-    const long long items = (long long)g.RB * g.KC * 80;
+    const AffineGeom g = affine_geom(N, K, group);
+    const long long items = (long long)g.RB * g.KC * (64 + (8 << g.gs));
     const int threads = 256;
     const int blocks = (int)std::min<long long>((items + threads - 1) / threads, (long long)ctx->sm_count * 32);
     unsigned int* flag = reinterpret_cast<unsigned int*>((uint8_t*)dst + affine_blocks_bytes(g));
     cudaError_t e = cudaMemsetAsync(flag, 0, AFF_TRAILER_BYTES, (cudaStream_t)stream);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine_b4_repack memset: %s", cudaGetErrorString(e));
-    affine_b4_repack_kernel<<<blocks, threads, 0, (cudaStream_t)stream>>>(w, scales, biases, scale_dtype == SCR_DTYPE_F16, N, K, g.RB, g.KC,
-                                                                         (uint8_t*)dst, flag);
+    affine_b4_repack_kernel<<<blocks, threads, 0, (cudaStream_t)stream>>>(w, scales, biases, scale_dtype == SCR_DTYPE_F16, N, K, group, g.gs,
+                                                                         g.RB, g.KC, (uint8_t*)dst, flag);
     int32_t st2 = scr_check_launch(ctx, "affine_b4_repack");
     if (st2) return st2;
     affine_b4_repack_fence_kernel<<<1, 32, 0, (cudaStream_t)stream>>>();
@@ -585,11 +593,11 @@ extern "C" int32_t scr_affine_b4_dequant_dump(scr_ctx* ctx, const void* packed, 
     int32_t st = affine_check_shape(ctx, N, K, group);
     if (st) return st;
     if (!scr_aligned16(packed) || !scr_aligned16(w_bf16)) return scr_fail(ctx, SCR_E_ALIGN, "pointers must be 16-byte aligned");
-    const AffineGeom g = affine_geom(N, K);
+    const AffineGeom g = affine_geom(N, K, group);
     const long long items = (long long)g.RB * g.KC * 64;
     const int threads = 256;
     const int blocks = (int)std::min<long long>((items + threads - 1) / threads, (long long)ctx->sm_count * 32);
-    affine_b4_dump_kernel<<<blocks, threads, 0, (cudaStream_t)stream>>>((const uint8_t*)packed, N, K, g.RB, g.KC, w_bf16);
+    affine_b4_dump_kernel<<<blocks, threads, 0, (cudaStream_t)stream>>>((const uint8_t*)packed, N, K, g.gs, g.RB, g.KC, w_bf16);
     return scr_check_launch(ctx, "affine_b4_dequant_dump");
 }
 
@@ -626,6 +634,7 @@ struct AffineFwd {
     float scale = 1.0f;                      // multiplies the sum after the bias
     const GemvEnds* ends = nullptr;          // GEMV_OUT_RESIDUAL_NORM only
     bool chain = false;                      // an operator of a decode chain: its input is the previous launch's output
+    int gs = 1;                              // (scale, bias) entries per row and block, log2: set from the group size by affine_forward
 };
 // Shared memory the norm-in end may take for the normalised rows beside the ring (two CTAs per SM).
 #define GEMV_NORM_MAX_BYTES (20 * 1024)
@@ -644,15 +653,15 @@ static int affine_gemv_u(int M, int N, int K, bool chain) {
     return (chain || (long long)scr_ceil_div(N, 16) * scr_ceil_div(K, AFF_BLOCK_K) >= GEMV_U3_MIN_BLOCKS) ? 3 : 1;
 }
 
-template <int MT, int U, bool NORM>
+template <int MT, int U, bool NORM, int GS = 1>
 static int32_t affine_gemv_launch_u(scr_ctx* ctx, const uint8_t* packed, const uint16_t* x, uint16_t* y, int M, int N,
                                     int K, const AffineFwd& f, cudaStream_t stream) {
-    using R = GemvRing<U>;
-    const AffineGeom g = affine_geom(N, K);
+    using R = GemvRing<U, GS>;
+    const AffineGeom g = affine_geom(N, K, GS == 2 ? 32 : 64);
     const int rb_real = scr_ceil_div(N, 16);
     int grid_x = 1, split = 1;
     affine_gemv_shape(rb_real, g.KC, ctx->sm_count, MT == 1 ? R::kCtasPerSm : 2, &grid_x, &split);
-    auto kernel = (split == 1) ? affine_b4_gemv_kernel<MT, 0, U, NORM> : affine_b4_gemv_kernel<MT, 1, U, NORM>;
+    auto kernel = (split == 1) ? affine_b4_gemv_kernel<MT, 0, U, NORM, GS> : affine_b4_gemv_kernel<MT, 1, U, NORM, GS>;
     const int smem = R::kBytes + (NORM ? M * K * 2 : 0);
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, R::kBytes + (NORM ? GEMV_NORM_MAX_BYTES : 0));
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine_b4_gemv smem attribute: %s", cudaGetErrorString(e));
@@ -691,6 +700,11 @@ static int32_t affine_gemv_launch_u(scr_ctx* ctx, const uint8_t* packed, const u
 template <int MT>
 static int32_t affine_gemv_launch(scr_ctx* ctx, const uint8_t* packed, const uint16_t* x, uint16_t* y, int M, int N,
                                   int K, const AffineFwd& f, cudaStream_t stream) {
+    if (f.gs == 2) {
+        // groups of 32: the 1280-byte block, one block per warp and ring stage
+        if (f.norm_gain) return scr_fail(ctx, SCR_E_UNSUPPORTED, "norm-in end: not built for groups of 32 (run the norm on its own)");
+        return affine_gemv_launch_u<MT, 1, false, 2>(ctx, packed, x, y, M, N, K, f, stream);
+    }
     const int u = affine_gemv_u(M, N, K, f.chain);
     if (f.norm_gain) {
         // the normalised rows sit in shared memory beside the ring: a few tokens only
@@ -706,7 +720,7 @@ static int32_t affine_gemv_launch(scr_ctx* ctx, const uint8_t* packed, const uin
 
 // Defined in affine_b4_gemm.cu
 int32_t affine_b4_gemm_tc_launch(scr_ctx* ctx, const uint8_t* packed, const uint16_t* x, uint16_t* y, int M, int N,
-                                 int K, int out_f32, const uint16_t* bias, void* workspace, size_t workspace_bytes,
+                                 int K, int gs, int out_f32, const uint16_t* bias, void* workspace, size_t workspace_bytes,
                                  cudaStream_t stream);
 size_t affine_b4_gemm_tc_workspace(int M, int N, int K);
 bool affine_b4_gemm_tc_enabled();
@@ -719,10 +733,12 @@ size_t affine_workspace_bytes(int M, int N, int K) {
 // The forward dispatch every int4 entry point goes through: the balanced matvec up to 8 tokens, the
 // two-tile matvec up to 16, the tensor-core GEMM above.
 static int32_t affine_forward(scr_ctx* ctx, const void* packed, const uint16_t* x, int M, int N, int K, int group, void* y_,
-                              const AffineFwd& f, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+                              const AffineFwd& f_in, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
     if (!packed || !x || !y_) return scr_fail(ctx, SCR_E_ARG, "null pointer");
     int32_t st = affine_check_shape(ctx, N, K, group);
     if (st) return st;
+    AffineFwd f = f_in;
+    f.gs = affine_gs(group);
     if (M <= 0) return scr_fail(ctx, SCR_E_SHAPE, "M=%d must be positive", M);
     if (!scr_aligned16(packed) || !scr_aligned16(x)) return scr_fail(ctx, SCR_E_ALIGN, "packed/x must be 16-byte aligned");
     if ((f.bias || f.scale != 1.0f) && (f.out_mode == GEMV_OUT_SILU_PAIRS || f.out_mode == GEMV_OUT_RESIDUAL_NORM))
@@ -740,7 +756,7 @@ static int32_t affine_forward(scr_ctx* ctx, const void* packed, const uint16_t* 
         const size_t need = affine_b4_gemm_tc_workspace(M, N, K);
         if (need > 0 && (!workspace || workspace_bytes < need))
             return scr_fail(ctx, SCR_E_WORKSPACE, "workspace %zu bytes < required %zu", workspace_bytes, need);
-        return affine_b4_gemm_tc_launch(ctx, pk, x, y, M, N, K, f.out_mode == GEMV_OUT_F32, f.bias, workspace, workspace_bytes, stream);
+        return affine_b4_gemm_tc_launch(ctx, pk, x, y, M, N, K, f.gs, f.out_mode == GEMV_OUT_F32, f.bias, workspace, workspace_bytes, stream);
     }
     // Token tiles of 16 through the matvec kernel (weights re-streamed per tile).
     const size_t ystride = f.out_mode == GEMV_OUT_F32 ? 2 : 1;
@@ -1077,7 +1093,8 @@ extern "C" int32_t scr_affine_b4_tape_create(scr_ctx* ctx, const scr_tape_linear
         int32_t st = affine_check_shape(ctx, s.N, s.K, s.group);
         if (st) return st;
         if (!scr_aligned16(s.packed) || !scr_aligned16(s.x)) return scr_fail(ctx, SCR_E_ALIGN, "tape job %d: packed/x must be 16-byte aligned", j);
-        const AffineGeom g = affine_geom(s.N, s.K);
+        if (s.group == 32) return scr_fail(ctx, SCR_E_UNSUPPORTED, "tape job %d: the tape kernel is built for groups of 64 and 128", j);
+        const AffineGeom g = affine_geom(s.N, s.K, s.group);
         TapeJob& t = host[(size_t)j];
         t.packed = static_cast<const uint8_t*>(s.packed);
         t.x = s.x;

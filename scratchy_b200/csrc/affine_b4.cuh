@@ -1,4 +1,4 @@
-// MLX affine int4 (group 64): the streaming layout and the one dequantisation routine
+// MLX affine int4 (groups of 64; 32 and 128 below): the streaming layout and the one dequantisation routine
 // every kernel shares (matvec, tensor-core GEMM, the dump hook), so a weight has the
 // same bf16 value wherever it is expanded.
 //
@@ -43,6 +43,13 @@
 #include "common.cuh"
 
 #define AFF_BLOCK_BYTES 1152
+// Group sizes 32 and 128 (the reference's sibling presets, crates/compiler/subtile/src/lower.rs:112-127) use the same block
+// of 16 rows x 128 k.  A lane's 16-byte piece (32 codes) never crosses a group, whichever of the three sizes, so only the
+// number of (scale, bias) entries per row and block differs: 2^gs.  Group 128 keeps gs = 1 (its one entry per row is
+// stored twice, so every kernel written for group 64 runs it unchanged); group 32 has gs = 2: 4 entries per row, a
+// 1280-byte block, entry of (row g, piece t) at 1024 + (g * 4 + t) * 8.
+__host__ __device__ constexpr int aff_block_bytes(int gs) { return 1024 + (64 << gs); }
+static inline int affine_gs(int group) { return group == 32 ? 2 : 1; }
 #define AFF_BLOCK_ROWS 16
 #define AFF_BLOCK_K 128
 #define AFF_ROW_PAD 128
@@ -52,16 +59,18 @@ struct AffineGeom {
     int N, K;        // logical
     int RB;          // row blocks (N_pad / 16)
     int KC;          // k chunks (ceil(K / 128))
+    int gs;          // log2 of the (scale, bias) entries per row and block: 1 (groups of 64 and 128) or 2 (groups of 32)
 };
 
-static inline AffineGeom affine_geom(int N, int K) {
+static inline AffineGeom affine_geom(int N, int K, int group) {
     AffineGeom g;
     g.N = N; g.K = K;
+    g.gs = affine_gs(group);
     g.RB = scr_ceil_div(N, AFF_ROW_PAD) * (AFF_ROW_PAD / AFF_BLOCK_ROWS);
     g.KC = scr_ceil_div(K, AFF_BLOCK_K);
     return g;
 }
-static inline size_t affine_blocks_bytes(const AffineGeom& g) { return (size_t)g.RB * g.KC * AFF_BLOCK_BYTES; }
+static inline size_t affine_blocks_bytes(const AffineGeom& g) { return (size_t)g.RB * g.KC * aff_block_bytes(g.gs); }
 static inline size_t affine_packed_bytes(const AffineGeom& g) { return affine_blocks_bytes(g) + AFF_TRAILER_BYTES; }
 
 // True when the packed-bf16 fast path could differ from the reference's two-step rounding

@@ -35,7 +35,7 @@ struct A4GSmem {
     static constexpr int kSX = (TM == 1) ? 3 : 2;                       // activation stages
     static constexpr uint32_t kXStage = 32768u * TM;                    // TM x 2 atoms of 128 rows x 128 B
     static constexpr uint32_t kDStage = 2u * A4G_BN * 128u;             // 2 atoms of 128 rows x 128 B
-    static constexpr uint32_t kPStage = (uint32_t)(A4G_BN / 16) * AFF_BLOCK_BYTES;
+    static constexpr uint32_t kPStage = (uint32_t)(A4G_BN / 16) * aff_block_bytes(2);   // sized for the largest block (groups of 32)
     static constexpr uint32_t kXOff = 0;
     static constexpr uint32_t kDOff = kXOff + kSX * kXStage;
     static constexpr uint32_t kPOff = kDOff + A4G_SD * kDStage;
@@ -97,10 +97,11 @@ __global__ void __launch_bounds__(256) affine_b4_gemm_tail_finish_kernel(const f
 template <int TM>
 __global__ void __launch_bounds__(A4G_THREADS, 1)
 affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_t* __restrict__ packed,
-                         uint16_t* __restrict__ y, int M, int N, int RB, int KC, int MT, int out_f32,
+                         uint16_t* __restrict__ y, int M, int N, int RB, int KC, int gs, int MT, int out_f32,
                          const uint16_t* __restrict__ bias, int full, int ks_tail, float* __restrict__ slabs,
                          int* __restrict__ status) {
     using S = A4GSmem<TM>;
+    const uint32_t block_bytes = (uint32_t)aff_block_bytes(gs);       // 1152 (groups of 64, 128) or 1280 (groups of 32)
     constexpr int SX = S::kSX;
     constexpr int BN = A4G_BN;
     extern __shared__ uint8_t smem_raw[];
@@ -155,10 +156,10 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
                 const int rb0 = nb * (BN / 16);
                 for (int kc = kc_lo; kc < kc_hi; ++kc) {
                     mbar_wait(pempty(sp), php ^ 1u, status, TC_ERR_EMPTY_WAIT);
-                    mbar_arrive_expect_tx(pfull(sp), S::kPStage);
+                    mbar_arrive_expect_tx(pfull(sp), (BN / 16) * block_bytes);
                     for (int j = 0; j < BN / 16; ++j)   // row-block-major packing: one block per row-block
-                        bulk_g2s(smem_base + S::kPOff + sp * S::kPStage + j * AFF_BLOCK_BYTES,
-                                 packed + ((size_t)(rb0 + j) * KC + kc) * AFF_BLOCK_BYTES, AFF_BLOCK_BYTES, pfull(sp));
+                        bulk_g2s(smem_base + S::kPOff + sp * S::kPStage + j * block_bytes,
+                                 packed + ((size_t)(rb0 + j) * KC + kc) * block_bytes, block_bytes, pfull(sp));
                     if (++sp == A4G_SP) { sp = 0; php ^= 1u; }
 
                     mbar_wait(xempty(sx), phx ^ 1u, status, TC_ERR_EMPTY_WAIT);
@@ -221,7 +222,8 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
         // hold four rows and one k-quarter pair: their 16-byte stores then hit eight distinct bank groups.
         const int g = ((lane >> 3) & 1) * 4 + ((lane & 7) >> 1);
         const int t = (lane >> 4) * 2 + (lane & 1);
-        const bool check = *reinterpret_cast<const unsigned int*>(packed + (size_t)RB * KC * AFF_BLOCK_BYTES) != 0;
+        const bool check = *reinterpret_cast<const unsigned int*>(packed + (size_t)RB * KC * block_bytes) != 0;
+        const uint32_t entry = (uint32_t)(((g << gs) + (t >> (2 - gs))) * 8);     // this lane's (scale, bias) entry in a block
         int sp = 0, sd = 0;
         uint32_t php = 0, phd = 0;
         for (int unit = blockIdx.x; unit < tiles; unit += gridDim.x) {
@@ -237,9 +239,9 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
                 for (int u = 0; u < 2 * (BN / 16) / A4G_DQ_WARPS; ++u) {
                     const int pr = dw + u * A4G_DQ_WARPS;
                     const int rbl = pr >> 1, half = pr & 1;
-                    const uint32_t blk = ps + (uint32_t)rbl * AFF_BLOCK_BYTES;
+                    const uint32_t blk = ps + (uint32_t)rbl * block_bytes;
                     const uint4 piece = ld_shared_v4(blk + half * 512 + (4 * g + t) * 16);
-                    const uint32_t sb = ld_shared_u32(blk + 1024 + (g * 2 + (t >> 1)) * 8 + half * 4);
+                    const uint32_t sb = ld_shared_u32(blk + 1024 + entry + half * 4);
                     uint32_t w[16];
                     if (check) {
                         affine_dequant_piece<true>(piece, sb, w);
@@ -273,7 +275,7 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
         const int q = warp & 3;                        // TMEM lane quadrant this warp may read
         const bool vec_ok = (N % 8) == 0;
         const float out_scale =
-            (*reinterpret_cast<const unsigned int*>(packed + (size_t)RB * KC * AFF_BLOCK_BYTES) != 0) ? 1.0f : AFF_SCALED_FACTOR;
+            (*reinterpret_cast<const unsigned int*>(packed + (size_t)RB * KC * block_bytes) != 0) ? 1.0f : AFF_SCALED_FACTOR;
         int it = 0;
         for (int unit = blockIdx.x; unit < tiles; unit += gridDim.x, ++it) {
             int t2, ks, kc_lo, kc_hi;
@@ -363,7 +365,7 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
 static int affine_gemm_tm(int M, int N, int K, int sms) {
     // 256-token tiles reuse every dequantised weight tile twice; below 129 tokens they would be half
     // empty, and they need enough tiles to fill the machine.
-    const AffineGeom g = affine_geom(N, K);
+    const AffineGeom g = affine_geom(N, K, 64);
     const int tiles2 = scr_ceil_div(M, 256) * (g.RB * 16 / A4G_BN);
     return (M > 128 && tiles2 >= sms / 2) ? 2 : 1;
 }
@@ -376,7 +378,7 @@ struct AffineGemmPlan {
     size_t slab_floats() const { return ks_tail > 1 ? (size_t)ks_tail * n_tail() * (size_t)(tm * 128 * A4G_BN) : 0; }
 };
 static AffineGemmPlan affine_gemm_plan(int M, int N, int K, int sms) {
-    const AffineGeom g = affine_geom(N, K);
+    const AffineGeom g = affine_geom(N, K, 64);
     AffineGemmPlan p;
     p.tm = affine_gemm_tm(M, N, K, sms);
     p.mt = scr_ceil_div(M, 128 * p.tm);
@@ -388,15 +390,15 @@ size_t affine_b4_gemm_tc_workspace_plan(int M, int N, int K) { return affine_gem
 
 template <int TM>
 static int32_t affine_gemm_launch_tm(scr_ctx* ctx, const CUtensorMap& map, const uint8_t* packed, uint16_t* y, int M, int N,
-                                     int K, int out_f32, const uint16_t* bias, const AffineGemmPlan& p, float* slabs,
+                                     int K, int gs, int out_f32, const uint16_t* bias, const AffineGemmPlan& p, float* slabs,
                                      cudaStream_t stream) {
-    const AffineGeom g = affine_geom(N, K);
+    const AffineGeom g = affine_geom(N, K, 64);
     const int units = p.full + p.n_tail() * p.ks_tail;
     const int grid = std::min(units, ctx->sm_count);
     cudaError_t e = cudaFuncSetAttribute(affine_b4_gemm_tc_kernel<TM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)A4GSmem<TM>::kTotal);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine gemm smem attribute: %s", cudaGetErrorString(e));
-    affine_b4_gemm_tc_kernel<TM><<<grid, A4G_THREADS, A4GSmem<TM>::kTotal, stream>>>(map, packed, y, M, N, g.RB, g.KC, p.mt,
+    affine_b4_gemm_tc_kernel<TM><<<grid, A4G_THREADS, A4GSmem<TM>::kTotal, stream>>>(map, packed, y, M, N, g.RB, g.KC, gs, p.mt,
                                                                                     out_f32, bias, p.full, p.ks_tail, slabs,
                                                                                     ctx->dev_status);
     int32_t st = scr_check_launch(ctx, "affine_b4_gemm_tc");
@@ -407,7 +409,7 @@ static int32_t affine_gemm_launch_tm(scr_ctx* ctx, const CUtensorMap& map, const
 }
 
 int32_t affine_b4_gemm_tc_launch(scr_ctx* ctx, const uint8_t* packed, const uint16_t* x, uint16_t* y, int M, int N, int K,
-                                 int out_f32, const uint16_t* bias, void* workspace, size_t, cudaStream_t stream) {
+                                 int gs, int out_f32, const uint16_t* bias, void* workspace, size_t, cudaStream_t stream) {
     if (((uintptr_t)packed & 127u) != 0) return scr_fail(ctx, SCR_E_ALIGN, "packed weights must be 128-byte aligned for the GEMM path");
     if (!scr_aligned16(y)) return scr_fail(ctx, SCR_E_ALIGN, "y must be 16-byte aligned");
     tc_encode_tiled_fn enc = tc_tensor_map_encoder();
@@ -423,6 +425,6 @@ int32_t affine_b4_gemm_tc_launch(scr_ctx* ctx, const uint8_t* packed, const uint
     const AffineGemmPlan plan = affine_gemm_plan(M, N, K, ctx->sm_count);
     float* slabs = reinterpret_cast<float*>(workspace);
     if (plan.ks_tail > 1 && (!slabs || !scr_aligned16(slabs))) return scr_fail(ctx, SCR_E_WORKSPACE, "split-K needs an aligned workspace");
-    if (plan.tm == 2) return affine_gemm_launch_tm<2>(ctx, map, packed, y, M, N, K, out_f32, bias, plan, slabs, stream);
-    return affine_gemm_launch_tm<1>(ctx, map, packed, y, M, N, K, out_f32, bias, plan, slabs, stream);
+    if (plan.tm == 2) return affine_gemm_launch_tm<2>(ctx, map, packed, y, M, N, K, gs, out_f32, bias, plan, slabs, stream);
+    return affine_gemm_launch_tm<1>(ctx, map, packed, y, M, N, K, gs, out_f32, bias, plan, slabs, stream);
 }

@@ -79,11 +79,12 @@ __device__ __forceinline__ void gemv_consumer_sync() {          // the 8 consume
 
 // One 1152-byte block from shared memory against pre-loaded activations (xv: this lane's 32
 // activations per token tile, in k order).
-template <int MT, bool CHECK>
+// GS: log2 of the (scale, bias) entries per row and block (1: groups of 64 or 128, 2: groups of 32).
+template <int MT, bool CHECK, int GS = 1>
 __device__ __forceinline__ void gemv_block_compute(uint32_t blk, float acc[2][MT][4], const uint4 xv[MT][4], int lane) {
     const uint4 p0 = gemv_lds_v4(blk + lane * 16);
     const uint4 p1 = gemv_lds_v4(blk + 512 + lane * 16);
-    const uint2 sb = gemv_lds_v2(blk + 1024 + ((lane >> 2) * 2 + ((lane & 3) >> 1)) * 8);
+    const uint2 sb = gemv_lds_v2(blk + 1024 + (((lane >> 2) << GS) + ((lane & 3) >> (2 - GS))) * 8);
     const uint32_t wa[4] = {p0.x, p0.y, p0.z, p0.w};
     const uint32_t wb[4] = {p1.x, p1.y, p1.z, p1.w};
     if (CHECK) {

@@ -45,9 +45,15 @@ def test_affine_repack_size_law():
     # rows pad to 128, k to 128
     assert L.scr_affine_b4_repack_size(8, 64, 64, ctypes.byref(s)) == 0
     assert s.value == (128 // 16) * 1 * 1152 + 128
-    # the preset's law: K % group == 0 (crates/compiler/subtile/src/lower.rs:112-127), group 64 only here
+    # the sibling presets: groups of 32 carry four (scale, bias) entries per row and 128 k, groups of 128 store theirs twice
+    assert L.scr_affine_b4_repack_size(256, 256, 32, ctypes.byref(s)) == 0
+    assert s.value == (256 // 16) * 2 * 1280 + 128
+    assert L.scr_affine_b4_repack_size(256, 256, 128, ctypes.byref(s)) == 0
+    assert s.value == (256 // 16) * 2 * 1152 + 128
+    # the preset's law: K % group == 0, groups of 32, 64 or 128 (crates/compiler/subtile/src/lower.rs:112-127)
     assert L.scr_affine_b4_repack_size(16, 96, 64, ctypes.byref(s)) == -2
-    assert L.scr_affine_b4_repack_size(16, 128, 32, ctypes.byref(s)) == -4
+    assert L.scr_affine_b4_repack_size(16, 192, 128, ctypes.byref(s)) == -2
+    assert L.scr_affine_b4_repack_size(16, 96, 48, ctypes.byref(s)) == -4
     assert L.scr_affine_b4_repack_size(0, 128, 64, ctypes.byref(s)) == -2
     assert L.scr_affine_b4_repack_size(16, 128, 64, None) == -1
 

@@ -159,7 +159,7 @@ def test_error_codes_through_the_abi():
     buf = torch.zeros(4096, dtype=torch.uint8, device="cuda")
     p = ctypes.c_void_p(buf.data_ptr())
     assert L.scr_linear_affine_b4(ctx.handle, p, p, 1, 16, 96, 64, None, p, None, 0, None) == -2     # K % group
-    assert L.scr_linear_affine_b4(ctx.handle, p, p, 1, 16, 128, 32, None, p, None, 0, None) == -4    # group 32
+    assert L.scr_linear_affine_b4(ctx.handle, p, p, 1, 16, 96, 48, None, p, None, 0, None) == -4     # groups are 32, 64 or 128
     assert L.scr_linear_affine_b4(ctx.handle, p, p, 0, 16, 128, 64, None, p, None, 0, None) == -2    # M
     assert L.scr_linear_affine_b4(ctx.handle, None, p, 1, 16, 128, 64, None, p, None, 0, None) == -1
     mis = ctypes.c_void_p(buf.data_ptr() + 4)
@@ -431,3 +431,59 @@ def test_f16_scales_match_the_oracle(N, K, M):
     want = oracle.affine_qmm_t_b4(w.view(np.uint8).reshape(-1), sc.view(np.uint16), bi.view(np.uint16), x, M, N, K, 64,
                                   scale_dt=oracle.F16)
     assert rel_l2(y, want) <= REL_L2_TOL
+
+
+# ---- the sibling presets: groups of 32 and 128 (crates/compiler/subtile/src/lower.rs:112-127) ------------------------
+def _group_layer(N, K, group, seed, f16=False):
+    from scratchy_b200 import AffineQuantLinear
+    w, s, b = synth.affine_int4_weights(N, K, group, seed)
+    return w, s, b, AffineQuantLinear.from_tensors(u32_dev(w), bf16_dev(s), bf16_dev(b), group, 4)
+
+
+@pytest.mark.parametrize("group", [32, 128])
+@pytest.mark.parametrize("N,K", [(8192, 3072), (1024, 3072), (3072, 8192), (8, 128), (24, 384), (130, 640)])
+def test_group_sizes_dequant_bit_exact(N, K, group):
+    w, s, b, layer = _group_layer(N, K, group, synth.seed_for("deqg", N, K, group))
+    got = bits_of(layer.dequantize()).reshape(N, K)
+    want = oracle.affine_dequant_b4(w.view(np.uint8).reshape(-1), s, b, N, K, group)
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("group", [32, 128])
+@pytest.mark.parametrize("N,K,M", [(8192, 3072, 1), (3072, 8192, 1), (1024, 3072, 4), (3072, 3072, 8), (3072, 3072, 16), (24, 384, 5),
+                                   (130, 640, 9), (256, 512, 130), (1024, 3072, 64), (3072, 8192, 512)])
+def test_group_sizes_match_the_oracle(N, K, M, group):
+    """Matvec (one and two token tiles, persistent and cluster-split grids) and the tensor-core GEMM at groups of 32 and 128."""
+    import torch
+    w, s, b, layer = _group_layer(N, K, group, synth.seed_for("lg", N, K, group))
+    x = synth.activations_bf16(M, K, synth.seed_for("lgx", N, K, M))
+    y = layer.forward(bf16_dev(x).reshape(M, K))
+    torch.cuda.synchronize()
+    rows = np.arange(M) if M * N * K <= 2 ** 31 else np.unique(np.random.default_rng(1).integers(0, M, 24))
+    want = oracle.affine_qmm_t_b4(w.view(np.uint8).reshape(-1), s, b, x[rows], len(rows), N, K, group)
+    assert rel_l2(bits_of(y).reshape(M, N)[rows], want) <= REL_L2_TOL
+
+
+@pytest.mark.parametrize("group", [32, 128])
+def test_group_sizes_fused_ends_and_refusals(group):
+    """The ends that ride on the matvec keep their bits at the other group sizes; what is not built is refused by name."""
+    import torch
+    from scratchy_b200 import _lib, decode
+    N, K, M = 3072, 1024, 2
+    w, s, b, lin = _group_layer(N, K, group, 77)
+    x = bf16_dev(synth.activations_bf16(M, K, 78)).reshape(M, K)
+    res0 = synth.activations_bf16(M, N, 79)
+    y = lin.forward_ends(x, torch.empty((M, N), dtype=torch.bfloat16, device="cuda"))
+    want_res = (bf16_dev(res0).reshape(M, N).float() + y.float()).to(torch.bfloat16)
+    got_res = lin.forward_ends(x, bf16_dev(res0).reshape(M, N), residual=True)
+    assert torch.equal(got_res.view(torch.int16), want_res.view(torch.int16))
+    want = oracle.affine_qmm_t_b4(w.view(np.uint8).reshape(-1), s, b, bits_of(x), M, N, K, group)
+    assert rel_l2(bits_of(y), want) <= REL_L2_TOL
+    gain = bf16_dev(synth.f32_to_bf16_bits(np.ones(K, np.float32)))
+    if group == 32:
+        with pytest.raises(_lib.ScratchyCudaError) as e:
+            lin.forward_ends(x, torch.empty((M, N), dtype=torch.bfloat16, device="cuda"), norm_gain=gain, norm_eps=1e-5)
+        assert e.value.name == "SCR_E_UNSUPPORTED"
+    else:
+        got = lin.forward_ends(x, torch.empty((M, N), dtype=torch.bfloat16, device="cuda"), norm_gain=gain, norm_eps=1e-5)
+        assert torch.equal(got.view(torch.int16), lin.forward_ends(decode.rmsnorm(x, gain, 1e-5), torch.empty_like(got)).view(torch.int16))
