@@ -89,6 +89,15 @@ int32_t scr_affine_b4_repack(scr_ctx* ctx, const uint32_t* w, const uint16_t* sc
  * `affine_dequant_b4_to_dtype` (crates/models/quantization/src/affine.rs:35-196). */
 int32_t scr_affine_b4_dequant_dump(scr_ctx* ctx, const void* packed, int32_t N, int32_t K,
                                    int32_t group, uint16_t* w_bf16, void* stream);
+/* The quantized token embedding, `AffineQuantEmbedding` (crates/models/quantization/src/layers_quant.rs:105-150;
+ * `Instruction::AffineEmbed`, kernel `affine_embed_b4`, crates/targets/metal/shaders/quantized_dequantize.metal:82-157):
+ *   out[i, :] (bf16) = dequant(table[ids[i], :])        gather and dequantisation in one pass
+ * with the dequantisation of the matrix path, bit for bit.  `packed` is a table [vocab, hidden] repacked by
+ * `scr_affine_b4_repack` — the buffer a tied lm_head multiplies with (`scr_linear_affine_b4` with N = vocab,
+ * K = hidden), as the reference shares one buffer triple between the two layers.  An id >= vocab records a code
+ * (`scr_device_status` reports SCR_E_ARG) and yields a row of zeros. */
+int32_t scr_affine_b4_embed(scr_ctx* ctx, const void* packed, const uint32_t* ids, int32_t n_ids,
+                            int32_t vocab, int32_t hidden, int32_t group, uint16_t* out_bf16, void* stream);
 
 /* ---- MLX affine int4: forward ---------------------------------------------
  * Replaces the `MetalStep::AffineQmm(AffineMatmul{input, output, layer, n, k, group_size,

@@ -219,6 +219,21 @@ def allreduce_rank_order(parts) -> np.ndarray:
     return out
 
 
+def affine_embed_b4(packed_bytes, scales, biases, ids, vocab, hidden, group_size, scale_dt=BF16) -> np.ndarray:
+    """The quantized embedding's host reference (crates/targets/metal/tests/quantized_affine_embed_test.rs:27-90, after MLX
+    `nn.QuantizedEmbedding.__call__`): gather the packed row, its scales and its offsets by token id, then dequantise
+    the row — scale and offset narrowed to the activation type first, `bf16(f32(scale) * f32(code) + f32(bias))`.
+    Returns [len(ids), hidden] bf16 bit patterns."""
+    packed = _c(packed_bytes, np.uint8).reshape(vocab, hidden // 2)
+    sc = _c(scales, np.uint16).reshape(vocab, hidden // group_size)
+    bi = _c(biases, np.uint16).reshape(vocab, hidden // group_size)
+    ids = np.asarray(ids).astype(np.int64).reshape(-1)
+    if ids.size and (ids.min() < 0 or ids.max() >= vocab):
+        raise ValueError("token id beyond the vocabulary")
+    return affine_dequant_b4(packed[ids], sc[ids], bi[ids], ids.size, hidden, group_size, scale_dt=scale_dt,
+                             cast_scale_to_act=True)
+
+
 def allgather_cols_rank_order(parts, cols: int) -> np.ndarray:
     """tensor_parallel.rs:1363-1386 (`SubOp::AllGather{cols}`): every rank's [rows, lc] column block side by side in
     absolute rank order, row by row, cropped to `cols` (a padded last block's tail is cut off).  Any dtype; values

@@ -8,6 +8,6 @@ There is no CPU fallback: every call fails loudly if the CUDA library is missing
 """
 from ._lib import ScratchyCudaError, lib, lib_path, Context  # noqa: F401
 from .layers import (  # noqa: F401
-    AffineQuantLinear, AffineTape, Fp8Linear, Fp8ActPack, GpuWeights, LinearLayer,
+    AffineQuantEmbedding, AffineQuantLinear, AffineTape, Fp8Linear, Fp8ActPack, GpuWeights, LinearLayer,
     load_layered_linear_affine_quant, load_layered_linear_fp8_dynamic,
 )

@@ -41,6 +41,7 @@ SIGNATURES = {
     "scr_affine_b4_repack_size": (_i32, [_i32, _i32, _i32, _psz]),
     "scr_affine_b4_repack": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp]),
     "scr_affine_b4_dequant_dump": (_i32, [_vp, _vp, _i32, _i32, _i32, _vp, _vp]),
+    "scr_affine_b4_embed": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp]),
     "scr_linear_workspace_size": (_i32, [_i32, _i32, _i32, _i32, _psz]),
     "scr_linear_affine_b4": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _sz, _vp]),
     "scr_linear_affine_b4_ends": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),

@@ -88,6 +88,30 @@ __global__ void affine_b4_repack_fence_kernel() {}
 // ------------------------------------------------------------------------------------
 // Dump hook: streaming blocks -> dense bf16 [N, K], through affine_dequant_piece.
 // ------------------------------------------------------------------------------------
+// One piece (32 weights of one row) of a block, dequantised the way the kernels do it: 16 words of two bf16 each.
+__device__ __forceinline__ void affine_block_piece(const uint8_t* b, int half, int g, int t, int gs, bool check, uint32_t regs[16]) {
+    const uint4 piece = *reinterpret_cast<const uint4*>(b + half * 512 + (4 * g + t) * 16);
+    const uint2 sb2 = *reinterpret_cast<const uint2*>(b + 1024 + ((g << gs) + (t >> (2 - gs))) * 8);
+    const uint32_t sb = half ? sb2.y : sb2.x;
+    if (check) {
+        affine_dequant_piece<true>(piece, sb, regs);
+    } else {
+        // the scaled variant the kernels use, brought back by the exact factor 2^7
+        const AffineScaled c = affine_scaled_consts(sb);
+        affine_dequant_word_scaled(piece.x, c, regs + 0);
+        affine_dequant_word_scaled(piece.y, c, regs + 4);
+        affine_dequant_word_scaled(piece.z, c, regs + 8);
+        affine_dequant_word_scaled(piece.w, c, regs + 12);
+        const uint32_t k128 = 0x43004300u;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const __nv_bfloat162 v = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&regs[i]),
+                                             *reinterpret_cast<const __nv_bfloat162*>(&k128));
+            regs[i] = *reinterpret_cast<const uint32_t*>(&v);
+        }
+    }
+}
+
 __global__ void affine_b4_dump_kernel(const uint8_t* __restrict__ packed, int N, int K, int gs, int RB, int KC,
                                       uint16_t* __restrict__ out) {
     const long long items = (long long)RB * KC * 64;
@@ -102,31 +126,46 @@ __global__ void affine_b4_dump_kernel(const uint8_t* __restrict__ packed, int N,
         const int row = rb * 16 + half * 8 + g;
         const int k0 = kc * 128 + t * 32;
         if (row >= N || k0 >= K) continue;
-        const uint8_t* b = packed + blk * block_bytes;
-        const uint4 piece = *reinterpret_cast<const uint4*>(b + half * 512 + lane * 16);
-        const uint2 sb2 = *reinterpret_cast<const uint2*>(b + 1024 + ((g << gs) + (t >> (2 - gs))) * 8);
         uint32_t regs[16];
-        const uint32_t sb = half ? sb2.y : sb2.x;
-        if (check) {
-            affine_dequant_piece<true>(piece, sb, regs);
-        } else {
-            // the scaled variant the kernels use, brought back by the exact factor 2^7
-            const AffineScaled c = affine_scaled_consts(sb);
-            affine_dequant_word_scaled(piece.x, c, regs + 0);
-            affine_dequant_word_scaled(piece.y, c, regs + 4);
-            affine_dequant_word_scaled(piece.z, c, regs + 8);
-            affine_dequant_word_scaled(piece.w, c, regs + 12);
-            const uint32_t k128 = 0x43004300u;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const __nv_bfloat162 v = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&regs[i]),
-                                                 *reinterpret_cast<const __nv_bfloat162*>(&k128));
-                regs[i] = *reinterpret_cast<const uint32_t*>(&v);
-            }
-        }
+        affine_block_piece(packed + blk * block_bytes, half, g, t, gs, check, regs);
         uint4* o = reinterpret_cast<uint4*>(out + (size_t)row * K + k0);
 #pragma unroll
         for (int i = 0; i < 4; ++i) o[i] = make_uint4(regs[4 * i], regs[4 * i + 1], regs[4 * i + 2], regs[4 * i + 3]);
+    }
+}
+
+// ------------------------------------------------------------------------------------
+// Quantized token embedding (`AffineQuantEmbedding`, crates/models/quantization/src/layers_quant.rs:105-150; kernel
+// `affine_embed_b4`, crates/targets/metal/shaders/quantized_dequantize.metal:82-157): out[i, :] = dequant(table[ids[i], :]),
+// the gather and the dequantisation in one pass.  The table is a repacked matrix [vocab, hidden] — the same buffer a
+// tied lm_head multiplies with, as in the reference, where both layers share one buffer triple.  One thread per
+// 32-weight piece; an id beyond the vocabulary records a code and leaves a row of zeros.
+// ------------------------------------------------------------------------------------
+#define AFF_BAD_TOKEN_ID 0x0E000001
+__global__ void affine_b4_embed_kernel(const uint8_t* __restrict__ packed, const uint32_t* __restrict__ ids, int n_ids, int vocab,
+                                       int K, int gs, int RB, int KC, uint16_t* __restrict__ out, int* status) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");                 // the ids may be the preceding kernel's output
+    const int block_bytes = aff_block_bytes(gs);
+    const bool check = *reinterpret_cast<const unsigned int*>(packed + (size_t)RB * KC * block_bytes) != 0;
+    const int pieces = K / 32;                                         // per row
+    const long long items = (long long)n_ids * pieces;
+    for (long long it = blockIdx.x * (long long)blockDim.x + threadIdx.x; it < items; it += (long long)gridDim.x * blockDim.x) {
+        const int i = int(it / pieces), p = int(it % pieces);
+        const uint32_t id = ids[i];
+        uint4* o = reinterpret_cast<uint4*>(out + (size_t)i * K + (size_t)p * 32);
+        if (id >= (uint32_t)vocab) {
+            if (p == 0) atomicCAS(status, 0, AFF_BAD_TOKEN_ID);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) o[j] = make_uint4(0, 0, 0, 0);
+            continue;
+        }
+        const int rb = int(id >> 4), half = int(id >> 3) & 1, g = int(id) & 7;
+        const int kc = p >> 2, t = p & 3;
+        uint32_t regs[16];
+        affine_block_piece(packed + ((size_t)rb * KC + kc) * block_bytes, half, g, t, gs, check, regs);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[j] = make_uint4(regs[4 * j], regs[4 * j + 1], regs[4 * j + 2], regs[4 * j + 3]);
     }
 }
 
@@ -599,6 +638,33 @@ extern "C" int32_t scr_affine_b4_dequant_dump(scr_ctx* ctx, const void* packed, 
     const int blocks = (int)std::min<long long>((items + threads - 1) / threads, (long long)ctx->sm_count * 32);
     affine_b4_dump_kernel<<<blocks, threads, 0, (cudaStream_t)stream>>>((const uint8_t*)packed, N, K, g.gs, g.RB, g.KC, w_bf16);
     return scr_check_launch(ctx, "affine_b4_dequant_dump");
+}
+
+extern "C" int32_t scr_affine_b4_embed(scr_ctx* ctx, const void* packed, const uint32_t* ids, int32_t n_ids, int32_t vocab,
+                                       int32_t hidden, int32_t group, uint16_t* out_bf16, void* stream) {
+    SCR_REQUIRE_CTX(ctx);
+    if (!packed || !ids || !out_bf16) return scr_fail(ctx, SCR_E_ARG, "null pointer");
+    int32_t st = affine_check_shape(ctx, vocab, hidden, group);
+    if (st) return st;
+    if (n_ids < 0) return scr_fail(ctx, SCR_E_SHAPE, "n_ids=%d", n_ids);
+    if (n_ids == 0) return SCR_OK;
+    if (!scr_aligned16(packed) || !scr_aligned16(out_bf16)) return scr_fail(ctx, SCR_E_ALIGN, "pointers must be 16-byte aligned");
+    const AffineGeom g = affine_geom(vocab, hidden, group);
+    const long long items = (long long)n_ids * (hidden / 32);
+    const int threads = 128;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)std::min<long long>((items + threads - 1) / threads, (long long)ctx->sm_count * 16));
+    cfg.blockDim = dim3(threads);
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, affine_b4_embed_kernel, (const uint8_t*)packed, ids, (int)n_ids, (int)vocab, (int)hidden,
+                                             g.gs, g.RB, g.KC, out_bf16, ctx->dev_status);
+    if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine_b4_embed launch: %s", cudaGetErrorString(e));
+    return scr_check_launch(ctx, "affine_b4_embed");
 }
 
 // Launch shape.  With enough row-blocks the grid is persistent (two CTAs per SM) and nothing

@@ -24,7 +24,7 @@ import numpy as np
 import torch
 
 from . import _lib, synth
-from .layers import AffineQuantLinear, GpuWeights, _dev_index, _ptr, _stream
+from .layers import AffineQuantEmbedding, AffineQuantLinear, GpuWeights, _dev_index, _ptr, _stream
 
 
 def _ctx(dev):
@@ -364,9 +364,23 @@ class LlamaDecoder:
             self.layers.append(DecoderLayer(qkv, o, gate_up, down, gw.take(f"{root}.input_layernorm.weight"),
                                             gw.take(f"{root}.post_attention_layernorm.weight")))
         self.final_norm = gw.take("model.norm.weight")
-        self.embed_table = gw.take("model.embed_tokens.weight")
-        self.lm_head = AffineQuantLinear.load(gw, "lm_head", g, 4, h)
-        for t in [self.final_norm, self.embed_table] + [x for l in self.layers for x in (l.input_norm, l.post_norm)]:
+        # `model.embed_tokens` with (weight = U32, scales, biases) is an `AffineQuantEmbedding`; without an `lm_head` of
+        # its own the vocabulary head is tied to it and multiplies with the same buffer (the macro's rule,
+        # crates/models/quantization/src/layers_quant.rs:105-126)
+        self.quant_embed = None
+        if gw.contains("model.embed_tokens.scales"):
+            self.quant_embed = AffineQuantEmbedding.load(gw, "model.embed_tokens", g, 4)
+            self.embed_table = None
+        else:
+            self.embed_table = gw.take("model.embed_tokens.weight")
+        if gw.contains("lm_head.weight"):
+            self.lm_head = AffineQuantLinear.load(gw, "lm_head", g, 4, h)
+        elif self.quant_embed is not None:
+            self.lm_head = self.quant_embed.as_linear()
+        else:
+            raise KeyError("tensor `lm_head.weight` not found in checkpoint (and no quantized embedding to tie it to)")
+        for t in [self.final_norm] + ([self.embed_table] if self.embed_table is not None else []) + \
+                [x for l in self.layers for x in (l.input_norm, l.post_norm)]:
             if t.dtype != torch.bfloat16:
                 raise ValueError("norm gains and the embedding table must be bf16 for this build")
         cos, sin = rope_tables(max_pos, cfg.head_dim, cfg.rope_theta)
@@ -400,7 +414,10 @@ class LlamaDecoder:
     def step(self, buf: DecodeBuffers, cache: PagedKvCache) -> torch.Tensor:
         cfg = self.cfg
         qd, kd = cfg.q_dim, cfg.kv_dim
-        embed(buf.ids, self.embed_table, out=buf.residual)
+        if self.quant_embed is not None:
+            self.quant_embed.forward(buf.ids, out=buf.residual)
+        else:
+            embed(buf.ids, self.embed_table, out=buf.residual)
         ends = (self.fuse_ends and not self.fuse_residual_norm and
                 AffineQuantLinear.norm_in_supported(buf.batch, cfg.hidden))
         if not ends:

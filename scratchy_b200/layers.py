@@ -343,6 +343,54 @@ class AffineQuantLinear:
         return w
 
 
+@dataclass
+class AffineQuantEmbedding:
+    """MLX affine int4 token embedding (`AffineQuantEmbedding`, crates/models/quantization/src/layers_quant.rs:105-150):
+    a `[vocab, hidden]` table of 4-bit codes with a scale and an offset per group, gathered and dequantised in one
+    pass (`scr_affine_b4_embed`).  The table is held as an `AffineQuantLinear` of N = vocab, K = hidden, so a tied
+    lm_head is the same object and the same device buffer (the reference shares one buffer triple the same way)."""
+    table: AffineQuantLinear
+
+    # ---- MetalAffineEmbedOps::load (crates/targets/metal/src/layers_quant.rs:672-700)
+    @classmethod
+    def load(cls, weights: GpuWeights, prefix: str, group_size: int, bits: int) -> "AffineQuantEmbedding":
+        if bits != 4:
+            raise ScratchyCudaError(-4, f"bits={bits}: the quantized embedding exists at 4 bits only")
+        # vocab and hidden come from the packed tensor's shape (hidden through the ceil(K * bits / 32) law), as in the reference
+        hidden = int(weights.peek(f"{prefix}.weight").shape[1]) * 32 // bits
+        return cls(AffineQuantLinear.load(weights, prefix, group_size, bits, hidden))
+
+    @classmethod
+    def from_tensors(cls, weight: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor, group_size: int = 64,
+                     bits: int = 4) -> "AffineQuantEmbedding":
+        return cls(AffineQuantLinear.from_tensors(weight, scales, biases, group_size, bits))
+
+    @property
+    def vocab_size(self) -> int:
+        return self.table.out_features
+
+    @property
+    def hidden_size(self) -> int:
+        return self.table.in_features
+
+    def as_linear(self) -> AffineQuantLinear:
+        """The tied lm_head: logits = x @ dequant(table)^T over the same buffer."""
+        return self.table
+
+    def forward(self, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        ids = ids.reshape(-1).contiguous()
+        if ids.dtype not in (torch.int32, torch.uint32):
+            raise ValueError(f"token ids must be 32-bit integers, got {ids.dtype}")
+        n = int(ids.numel())
+        dev = ids.device
+        if out is None:
+            out = torch.empty((n, self.hidden_size), dtype=torch.bfloat16, device=dev)
+        ctx = _lib.context(_dev_index(dev))
+        ctx.check(_lib.lib().scr_affine_b4_embed(ctx.handle, _ptr(self.table.packed), _ptr(ids), n, self.vocab_size,
+                                                 self.hidden_size, self.table.group_size, _ptr(out), _stream(dev)))
+        return out
+
+
 class AffineTape:
     """A static tape of int4 matvecs that runs as ONE launch (`scr_linear_affine_b4_tape`), the way the
     reference's decode step is a tape of dispatches fixed at build time

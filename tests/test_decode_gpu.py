@@ -11,7 +11,7 @@ import pytest
 
 import oracle
 from scratchy_b200 import synth
-from util import bf16_dev, bf16_to_f32, bits_of, rel_l2, to_dev
+from util import bf16_dev, bf16_to_f32, bits_of, rel_l2, to_dev, u32_dev
 
 pytestmark = pytest.mark.gpu
 REL_L2_TOL = 1e-3
@@ -314,7 +314,12 @@ def _oracle_step(cfg, ck, ids, pos, slots, table, used, cache_k, cache_v, cos, s
     """The step as a chain of oracle operators, rounding to bf16 wherever the device stores bf16."""
     f, r = bf16_to_f32, rbits
     qd, kd = cfg.q_dim, cfg.kv_dim
-    residual = ck["model.embed_tokens.weight"][ids]                       # bf16 bits
+    if "model.embed_tokens.scales" in ck:                                  # an AffineQuantEmbedding: gather + dequantise
+        e = "model.embed_tokens"
+        residual = oracle.affine_embed_b4(ck[f"{e}.weight"].view(np.uint8).reshape(-1), ck[f"{e}.scales"], ck[f"{e}.biases"], ids,
+                                          cfg.vocab, cfg.hidden, 64)
+    else:
+        residual = ck["model.embed_tokens.weight"][ids]                   # bf16 bits
     normed = r(oracle.rmsnorm(f(residual), f(ck["model.layers.0.input_layernorm.weight"]), cfg.rms_eps))
     for i in range(cfg.n_layers):
         root = f"model.layers.{i}"
@@ -335,7 +340,85 @@ def _oracle_step(cfg, ck, ids, pos, slots, table, used, cache_k, cache_v, cos, s
         nxt = ck[f"model.layers.{i + 1}.input_layernorm.weight"] if i + 1 < cfg.n_layers else ck["model.norm.weight"]
         res, nrm = oracle.fused_add_rmsnorm(f(residual), f(delta), f(nxt), cfg.rms_eps, round_residual_bf16=True)
         residual, normed = r(res), r(nrm)
-    return _oracle_linear(ck, ["lm_head"], normed, cfg.hidden)
+    return _oracle_linear(ck, ["lm_head" if "lm_head.weight" in ck else "model.embed_tokens"], normed, cfg.hidden)
+
+
+@pytest.mark.parametrize("group,f16", [(64, False), (32, False), (128, True)])
+@pytest.mark.parametrize("vocab,hidden,n", [(1000, 256, 7), (128256, 3072, 5), (40, 128, 40)])
+def test_quantized_embedding_gathers_and_dequantises_bit_exact(vocab, hidden, n, group, f16):
+    """`AffineQuantEmbedding` (quantized_dequantize.metal:82-157; host reference quantized_affine_embed_test.rs:27-90):
+    every gathered row has the bits of the oracle's dequantisation; the tied head multiplies with the same buffer; an
+    id beyond the vocabulary is reported and yields zeros."""
+    import torch
+    from scratchy_b200 import AffineQuantEmbedding, _lib
+    w, s, b = synth.affine_int4_weights(vocab, hidden, group, synth.seed_for("qembed", vocab, hidden, group))
+    sdt = oracle.BF16
+    st, bt = bf16_dev(s), bf16_dev(b)
+    if f16:
+        s = bf16_to_f32(s).astype(np.float16).view(np.uint16)
+        b = bf16_to_f32(b).astype(np.float16).view(np.uint16)
+        st, bt = (torch.from_numpy(v.view(np.float16)).cuda() for v in (s, b))
+        sdt = oracle.F16
+    emb = AffineQuantEmbedding.from_tensors(u32_dev(w), st, bt, group, 4)
+    rng = np.random.default_rng(n)
+    ids = rng.integers(0, vocab, size=n).astype(np.uint32)
+    ids[0], ids[-1] = 0, vocab - 1
+    got = emb.forward(i32_dev(ids))
+    torch.cuda.synchronize()
+    want = oracle.affine_embed_b4(w.view(np.uint8).reshape(-1), s, b, ids, vocab, hidden, group, scale_dt=sdt)
+    assert np.array_equal(bits_of(got), want)
+    assert emb.as_linear().packed.data_ptr() == emb.table.packed.data_ptr() and emb.as_linear().out_features == vocab
+    ctx = _lib.context(0)
+    ctx.device_status(None)
+    bad = ids.copy()
+    bad[1 % n] = vocab
+    got = emb.forward(i32_dev(bad))
+    with pytest.raises(_lib.ScratchyCudaError) as e:
+        ctx.device_status(None)
+    assert e.value.name == "SCR_E_ARG"
+    assert not bits_of(got)[1 % n].any()
+    ctx.device_status(None)
+
+
+def test_decode_step_with_a_tied_quantized_embedding():
+    """A checkpoint whose `model.embed_tokens` is quantized and that has no `lm_head`: the embedding gathers from, and the
+    vocabulary head multiplies with, one buffer."""
+    import torch
+    from scratchy_b200 import decode
+    cfg = decode.LlamaConfig(hidden=256, n_layers=2, n_q_heads=4, n_kv_heads=2, head_dim=64, intermediate=512,
+                             vocab=1024, rope_theta=10000.0)
+    ck = decode.synthetic_checkpoint(cfg, seed=5)
+    for suffix in ("weight", "scales", "biases"):
+        ck[f"model.embed_tokens.{suffix}"] = ck.pop(f"lm_head.{suffix}")
+    dec = decode.LlamaDecoder(cfg, dict(ck), "cuda:0", max_pos=128)
+    assert dec.embed_table is None and dec.lm_head is dec.quant_embed.as_linear()
+    batch, bs, max_blocks = 3, 4, 8
+    nblk = batch * max_blocks
+    cache = decode.PagedKvCache(cfg, nblk, bs, "cuda:0")
+    rng = np.random.default_rng(3)
+    ctx_len = rng.integers(3, 20, size=batch)
+    table = rng.permutation(nblk).reshape(batch, max_blocks).astype(np.uint32)
+    hist = [rbits(rng.standard_normal((nblk, cfg.n_kv_heads, bs, cfg.head_dim))) for _ in range(2 * cfg.n_layers)]
+    for i in range(cfg.n_layers):
+        cache.k[i].copy_(bf16_dev(hist[2 * i]))
+        cache.v[i].copy_(bf16_dev(hist[2 * i + 1]))
+    ok = [bf16_to_f32(hist[2 * i]).copy() for i in range(cfg.n_layers)]
+    ov = [bf16_to_f32(hist[2 * i + 1]).copy() for i in range(cfg.n_layers)]
+    cos, sin = decode.rope_tables(128, cfg.head_dim, cfg.rope_theta)
+    buf = dec.buffers(batch, max_blocks)
+    buf.block_table.copy_(i32_dev(table))
+    ids = rng.integers(0, cfg.vocab, size=batch).astype(np.uint32)
+    pos = ctx_len.astype(np.uint32)
+    slots = np.array([table[q, pos[q] // bs] * bs + pos[q] % bs for q in range(batch)], np.uint32)
+    used = (pos + 1).astype(np.uint32)
+    buf.ids.copy_(i32_dev(ids))
+    buf.positions.copy_(i32_dev(pos))
+    buf.slot_mapping.copy_(i32_dev(slots))
+    buf.seq_used_k.copy_(i32_dev(used))
+    dec.step(buf, cache)
+    torch.cuda.synchronize()
+    want = _oracle_step(cfg, ck, ids, pos, slots, table, used, ok, ov, cos, sin, bs)
+    assert rel_l2(bits_of(buf.logits), want) <= STEP_REL_L2_TOL
 
 
 @pytest.mark.parametrize("batch,fuse_residual_norm,head_dim,bs,max_ctx,fuse_rope", [
