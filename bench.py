@@ -998,11 +998,12 @@ def run_case(args):
         return run_case_attention(device, batch=int(name), context=M, reps=args.steps)
     # kind "fp8x": the fp8 matvec with the tensor-parallel exchange in its epilogue, on a one-rank communicator
     # (pushes to itself: the whole kernel runs on one GPU)
-    K, N = (synth.LLAMA_3_2_3B if kind == "int4" else synth.QWEN_2_5_7B)[name]
+    # kind "int4c": the int4 matvec issued as a decode chain issues it (scr_linear_affine_b4_ends with no end set)
+    K, N = (synth.LLAMA_3_2_3B if kind in ("int4", "int4c") else synth.QWEN_2_5_7B)[name]
     copies = max(2, int((256 << 20) // (N * K)) + 1)
     lins = []
     for c in range(copies):
-        if kind == "int4":
+        if kind in ("int4", "int4c"):
             w = torch.randint(-2 ** 31, 2 ** 31 - 1, (N, K // 8), dtype=torch.int32, device=device)
             s_ = (torch.randn((N, K // 64), device=device) * 0.02).abs().add(1e-3).to(torch.bfloat16)
             lins.append(AffineQuantLinear.from_tensors(w, s_, (-8.0 * s_.float()).to(torch.bfloat16)))
@@ -1018,6 +1019,9 @@ def run_case(args):
 
         def call(l):
             one.fp8_linear_all_reduce(l, x, out=y)
+    elif kind == "int4c":
+        def call(l):
+            l.forward_ends(x, y)
     else:
         def call(l):
             l.forward(x, out=y, workspace=ws)
