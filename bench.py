@@ -52,8 +52,9 @@ def fp8_alg_bytes(M, N, K):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of affine_b4_gemv_kernel at M = 1, by shape, from the ncu
-# captures summarised in profiles/affine_b4_gemv_llama3b_m1_full.md (weights cross HBM once; activations come from L2)
-GEMV_DRAM_TRAFFIC = {"q": 5335808, "o": 5335808, "k": 1797120, "v": 1797120, "gate": 14181120, "up": 14181120, "down": 14191360}
+# captures summarised in profiles/affine_b4_gemv_llama3b_m1_full.md (q/o, k/v, down) and
+# profiles/affine_b4_gemv_llama3b_gate_m1_full.md (gate/up) (weights cross HBM once; activations come from L2)
+GEMV_DRAM_TRAFFIC = {"q": 5335808, "o": 5335808, "k": 1797120, "v": 1797120, "gate": 14208512, "up": 14208512, "down": 14191360}
 
 
 def measured_peaks():
@@ -469,7 +470,8 @@ def run_gpu(args):
                          "frac": achieved / peaks["hbm_gbs"],
                          # launch-weighted mean over the 7 shapes of the per-shape ncu figures (GEMV_DRAM_TRAFFIC)
                          "traffic": sum(GEMV_DRAM_TRAFFIC[n] for n in LAYER_ORDER) / len(LAYER_ORDER),
-                         "traffic_source": "ncu dram__bytes_read+write per launch, by shape: profiles/affine_b4_gemv_llama3b_m1_full.md",
+                         "traffic_source": "ncu dram__bytes_read+write per launch, by shape: profiles/affine_b4_gemv_llama3b_m1_full.md, "
+                                           "profiles/affine_b4_gemv_llama3b_gate_m1_full.md",
                          "peak_source": peaks["src"],
                          "kernel": "affine_b4_gemv_kernel", "avg_launch_us": per_launch_us,
                          "alg_bytes_per_launch": step_bytes / (N_LAYERS * len(LAYER_ORDER))},
