@@ -4,8 +4,10 @@ Some callers of this library have no device allocator on the step path (a runtim
 already owns all device memory, code inside a no-allocation region, a thin FFI shim that owns
 only the input and output tensors).  The entry point keeps the activation pack in an 8 MiB array
 built into the library instead of a caller workspace.  It must produce exactly what
-`scr_linear_fp8_dynamic` produces (same kernels, same bytes), also on a second call that finds
-the previous call's contents in the array, and refuse requests that do not fit.
+`scr_linear_fp8_dynamic` produces — bit for bit: up to 4 tokens that entry point takes the one-launch
+self-quantising matvec while this one always quantises into the array first, and the two do the same
+arithmetic statement for statement — also on a second call that finds the previous call's contents in
+the array; it must not change the device's free memory; and it must refuse requests that do not fit.
 
 This file sorts last on purpose, so a run that stops at the first failure has already run
 every other test.
@@ -34,6 +36,13 @@ def _both(layer, x, M, N, K):
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     ctx.check(L.scr_linear_fp8_dynamic_static(ctx.handle, _ptr(layer.packed), _ptr(x), M, N, K, _ptr(y), stream))
     torch.cuda.synchronize()
+    # the first call above resolved the array's address; from here on a call must leave the device's memory alone
+    free0, _ = torch.cuda.mem_get_info()
+    for _ in range(2):
+        ctx.check(L.scr_linear_fp8_dynamic_static(ctx.handle, _ptr(layer.packed), _ptr(x), M, N, K, _ptr(y), stream))
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0, f"the call changed the device's free memory by {free0 - free1} bytes"
     return y, y_ref
 
 
@@ -48,7 +57,7 @@ def test_static_scratch_matches_workspace_entry_point_twice(N, K, M1, M2):
     for M, seed in ((M1, 5), (M2, 6)):      # two calls in a row share the built-in array
         x = torch.from_numpy(synth.activations_bf16(M, K, seed).view(np.int16)).view(torch.bfloat16).cuda().reshape(M, K)
         y, y_ref = _both(layer, x, M, N, K)
-        assert torch.equal(y, y_ref)        # same kernels on the same bytes: bit-identical
+        assert torch.equal(y, y_ref)        # the same arithmetic on the same bytes: bit-identical
 
 
 def test_requests_beyond_the_array_are_refused():
