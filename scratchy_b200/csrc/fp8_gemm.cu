@@ -17,6 +17,10 @@
 #include "tc_common.cuh"
 
 bool fp8_gemm_tc_enabled() { return true; }
+// Defined in fp8_gemm_pair.cu
+bool fp8_gemm_pair_applies(int M, int N, int K, int sms);
+int32_t fp8_gemm_pair_launch(scr_ctx* ctx, const uint8_t* wpack, const uint8_t* act, uint16_t* y, int M, int N, int K,
+                             const LinearEnds& ends, cudaStream_t stream, bool* launched);
 // Channel-tile width and work units.  Wide (256-channel) tiles reuse every activation tile twice and are preferred;
 // a 128-channel tile does half the work in about three quarters of the time (measured), which can still win
 // when it quantises better over the SMs.  Units as in `tc_plan_units`.
@@ -311,6 +315,11 @@ int32_t fp8_gemm_tc_launch(scr_ctx* ctx, const uint8_t* wpack, const uint8_t* ac
     if (((uintptr_t)(act + fp8_act_scale_bytes(M)) & 127u) != 0 || ((uintptr_t)wpack & 127u) != 0)
         return scr_fail(ctx, SCR_E_ALIGN, "weight pack and activation pack must be 128-byte aligned for the GEMM path");
     if (!scr_aligned16(y)) return scr_fail(ctx, SCR_E_ALIGN, "y must be 16-byte aligned");
+    if (fp8_gemm_pair_applies(M, N, K, ctx->sm_count)) {        // large, evenly tiled GEMMs: the two-CTA kernel (fp8_gemm_pair.cu)
+        bool launched = false;
+        const int32_t st = fp8_gemm_pair_launch(ctx, wpack, act, y, M, N, K, ends, stream, &launched);
+        if (st || launched) return st;
+    }
     const Fp8GemmPlan plan = fp8_gemm_plan(M, N, K, ctx->sm_count);
     float* slabs = reinterpret_cast<float*>(workspace);
     if (plan.ks_tail > 1 && (!slabs || !scr_aligned16(slabs))) return scr_fail(ctx, SCR_E_WORKSPACE, "split-K needs an aligned workspace");

@@ -274,6 +274,35 @@ def test_linear_bias_in_the_epilogue(N, K, M):
     assert rel_l2(y[rows], plain) > 0.1, "the bias must have been applied"
 
 
+@pytest.mark.parametrize("N,K,M", [(18944, 384, 512), (18944, 256, 768), (4864, 3584, 2048)])
+def test_two_cta_gemm_against_the_oracle(N, K, M):
+    """Shapes the CTA-pair kernel takes (whole 256 x 256 tiles, full rounds of 74 pairs; K = 384 is an odd number of
+    k-tiles, so the last ring stage is half full): bf16 with a bias, the unrounded f32 partials of a row-parallel layer,
+    and run-to-run identical bits.  Rows are sampled over both CTAs of a pair."""
+    import torch
+    from scratchy_b200 import Fp8Linear
+    wq, ws = oracle.fp8_quantize_weight_per_channel(synth.fp8_weights_f32(N, K, synth.seed_for("pair", N, K, M)))
+    x = synth.activations_bf16(M, K, synth.seed_for("pairx", N, K, M))
+    bias = synth.f32_to_bf16_bits(np.random.default_rng(7).normal(0.0, 2.0, N).astype(np.float32))
+    xd = bf16_dev(x).reshape(M, K)
+    layer = Fp8Linear.from_tensors(to_dev(wq), to_dev(ws), linear_bias=bf16_dev(bias))
+    y = layer.forward(xd)
+    y2 = layer.forward(xd)
+    plain = Fp8Linear.from_tensors(to_dev(wq), to_dev(ws))
+    part = plain.forward_partial(xd)
+    torch.cuda.synchronize()
+    assert torch.equal(y.view(torch.int16), y2.view(torch.int16))
+    rows = np.unique(np.concatenate([np.arange(0, M, 37), [0, 127, 128, 255, 256, M - 129, M - 128, M - 1]]))
+    xs = x.reshape(M, K)[rows]
+    want = oracle.fp8_dynamic_linear_bias(xs, wq, ws, bias, len(rows), N, K)
+    assert rel_l2(bits_of(y).reshape(M, N)[rows], want) <= REL_L2_TOL
+    _, acc = oracle.fp8_dynamic_linear(xs, wq, ws, len(rows), N, K, want_f32=True)
+    got = part.cpu().numpy().reshape(M, N)[rows].astype(np.float64)
+    assert np.linalg.norm(got - acc) / np.linalg.norm(acc) <= 1e-5
+    from scratchy_b200 import _lib
+    _lib.context(0).device_status(None)
+
+
 def test_misaligned_pointers_are_refused_on_the_host():
     """Every fp8 forward entry point refuses a pointer that is not 16-byte aligned with SCR_E_ALIGN before anything
     is launched: the matvec's bulk copies would otherwise fault on the device."""
