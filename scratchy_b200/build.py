@@ -15,7 +15,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(CSRC, "build")
 LIB = os.path.join(HERE, "libscratchy_cuda.so")
 
-SOURCES = ["abi.cu", "affine_b4.cu", "affine_b4_gemm.cu", "fp8.cu", "fp8_gemm.cu", "fp8_gemm_pair.cu", "decode_ops.cu", "tp_comm.cu"]
+SOURCES = ["abi.cu", "affine_b4.cu", "affine_b4_gemm.cu", "affine_b4_gemm_pair.cu", "fp8.cu", "fp8_gemm.cu", "fp8_gemm_pair.cu", "decode_ops.cu", "tp_comm.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

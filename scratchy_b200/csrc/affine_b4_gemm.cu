@@ -21,6 +21,10 @@
 #include "tc_common.cuh"
 
 bool affine_b4_gemm_tc_enabled() { return true; }
+// Defined in affine_b4_gemm_pair.cu
+bool affine_b4_gemm_pair_applies(int M, int N, int K, int sms);
+int32_t affine_b4_gemm_pair_launch(scr_ctx* ctx, const CUtensorMap& x_map, const uint8_t* packed, uint16_t* y, int M, int N, int K,
+                                   int gs, int out_f32, const uint16_t* bias, cudaStream_t stream, bool* launched);
 size_t affine_b4_gemm_tc_workspace_plan(int M, int N, int K);
 size_t affine_b4_gemm_tc_workspace(int M, int N, int K) { return affine_b4_gemm_tc_workspace_plan(M, N, K); }
 
@@ -130,8 +134,10 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < SX; ++s) { mbar_init(xfull(s), 1); mbar_init(xempty(s), 1); }
-        for (int s = 0; s < A4G_SP; ++s) { mbar_init(pfull(s), 1); mbar_init(pempty(s), A4G_DQ_WARPS * 32); }
-        for (int s = 0; s < A4G_SD; ++s) { mbar_init(dfull(s), A4G_DQ_WARPS * 32); mbar_init(dempty(s), 1); }
+        // one arrival per dequantise WARP (its lane 0, after the warp has synchronised): 512 thread arrivals per stage on
+        // one barrier serialise in the barrier unit and cost more than the dequantisation itself (measured)
+        for (int s = 0; s < A4G_SP; ++s) { mbar_init(pfull(s), 1); mbar_init(pempty(s), A4G_DQ_WARPS); }
+        for (int s = 0; s < A4G_SD; ++s) { mbar_init(dfull(s), A4G_DQ_WARPS); mbar_init(dempty(s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(accf(b), 1); mbar_init(acce(b), 128); }
         fence_mbar_init();
     }
@@ -264,8 +270,11 @@ affine_b4_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const uint8_
                     }
                 }
                 fence_proxy_async_smem();              // generic-proxy stores -> visible to the tensor core
-                mbar_arrive(dfull(sd));
-                mbar_arrive(pempty(sp));
+                __syncwarp();                          // every lane has stored (and fenced) and is done with the packed stage
+                if (lane == 0) {
+                    mbar_arrive(dfull(sd));
+                    mbar_arrive(pempty(sp));
+                }
                 if (++sp == A4G_SP) { sp = 0; php ^= 1u; }
                 if (++sd == A4G_SD) { sd = 0; phd ^= 1u; }
             }
@@ -422,6 +431,11 @@ int32_t affine_b4_gemm_tc_launch(scr_ctx* ctx, const uint8_t* packed, const uint
     CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)x, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return scr_fail(ctx, SCR_E_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+    if (affine_b4_gemm_pair_applies(M, N, K, ctx->sm_count)) {     // large, evenly tiled GEMMs: the two-CTA kernel (affine_b4_gemm_pair.cu)
+        bool launched = false;
+        const int32_t st = affine_b4_gemm_pair_launch(ctx, map, packed, y, M, N, K, gs, out_f32, bias, stream, &launched);
+        if (st || launched) return st;
+    }
     const AffineGemmPlan plan = affine_gemm_plan(M, N, K, ctx->sm_count);
     float* slabs = reinterpret_cast<float*>(workspace);
     if (plan.ks_tail > 1 && (!slabs || !scr_aligned16(slabs))) return scr_fail(ctx, SCR_E_WORKSPACE, "split-K needs an aligned workspace");

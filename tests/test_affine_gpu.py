@@ -487,3 +487,39 @@ def test_group_sizes_fused_ends_and_refusals(group):
     else:
         got = lin.forward_ends(x, torch.empty((M, N), dtype=torch.bfloat16, device="cuda"), norm_gain=gain, norm_eps=1e-5)
         assert torch.equal(got.view(torch.int16), lin.forward_ends(decode.rmsnorm(x, gain, 1e-5), torch.empty_like(got)).view(torch.int16))
+
+
+def test_two_cta_gemm_gives_the_bits_of_the_one_cta_kernel(tmp_path):
+    """The CTA-pair int4 GEMM (`tcgen05.mma.cta_group::2`, each CTA dequantising half of the pair's channels) is opt-in
+    through the environment, read once per process: a child process runs it on a shape it takes (whole 256 x 256 tiles,
+    two full rounds of 74 pairs), this process runs the one-CTA kernel; same bits, and the oracle's bound on sampled rows."""
+    import subprocess
+    import sys
+    import torch
+    N, K, M, group = 18944, 256, 512, 64
+    w, s, b = synth.affine_int4_weights(N, K, group, 3)
+    x = synth.activations_bf16(M, K, 4)
+    bias = synth.f32_to_bf16_bits(np.random.default_rng(5).normal(0.0, 1.0, N).astype(np.float32))
+    np.savez(tmp_path / "in.npz", w=w, s=s, b=b, x=x, bias=bias)
+    child = (
+        "import sys, numpy as np, torch\n"
+        f"sys.path.insert(0, {os.path.dirname(os.path.dirname(os.path.abspath(__file__)))!r})\n"
+        f"sys.path.insert(0, {os.path.dirname(os.path.abspath(__file__))!r})\n"
+        "from scratchy_b200 import AffineQuantLinear, _lib\n"
+        "from util import bf16_dev, bits_of, u32_dev\n"
+        f"g = np.load({str(tmp_path / 'in.npz')!r})\n"
+        f"lin = AffineQuantLinear.from_tensors(u32_dev(g['w']), bf16_dev(g['s']), bf16_dev(g['b']), {group}, 4, linear_bias=bf16_dev(g['bias']))\n"
+        f"y = lin.forward(bf16_dev(g['x']).reshape({M}, {K}))\n"
+        "torch.cuda.synchronize(); _lib.context(0).device_status(None)\n"
+        f"np.save({str(tmp_path / 'y.npy')!r}, bits_of(y))\n")
+    env = dict(os.environ, SCR_AFFINE_GEMM_PAIR="1")
+    subprocess.run([sys.executable, "-c", child], check=True, env=env, timeout=300)
+    from scratchy_b200 import AffineQuantLinear
+    lin = AffineQuantLinear.from_tensors(u32_dev(w), bf16_dev(s), bf16_dev(b), group, 4, linear_bias=bf16_dev(bias))
+    here = bits_of(lin.forward(bf16_dev(x).reshape(M, K)))
+    torch.cuda.synchronize()
+    pair = np.load(tmp_path / "y.npy")
+    assert np.array_equal(pair, here)
+    rows = np.array([0, 127, 128, 255, 256, 383, 384, 511])
+    want = oracle.affine_qmm_t_b4_bias(w.view(np.uint8).reshape(-1), s, b, x[rows], bias, len(rows), N, K, group)
+    assert rel_l2(pair.reshape(M, N)[rows], want) <= REL_L2_TOL
