@@ -367,7 +367,10 @@ def run_gpu(args):
     # Every linear's input is copied from pinned host memory and its output copied back inside
     # the timed region; the copies are captured in the same graph as the launches.
     # One pinned staging buffer holds the step's activations (one row-set per linear of every
-    # layer) and one receives all outputs: one H2D and one D2H copy per step.
+    # layer) and one receives all outputs.  Two H2D and two D2H copies per step on copy streams of their own (graph
+    # branches): the first layer's inputs, then everything else while the first layer computes; the outputs of all but
+    # the last layer while the last layer computes, then the last layer's.  (A copy per layer was measured slower: 56
+    # copy nodes and 56 cross-stream dependencies cost more than the 3 MB they hide.)
     in_elems = [M * K for K, _ in shapes]
     out_elems = [M * N for _, N in shapes]
     h_in = torch.randn(N_LAYERS * sum(in_elems)).to(torch.bfloat16).pin_memory()
@@ -386,9 +389,32 @@ def run_gpu(args):
             oo += ne_o
         views.append(row)
 
+    in_per_layer, out_per_layer = sum(in_elems), sum(out_elems)
+    copy_in, copy_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+
     def step_e2e():
-        d_in.copy_(h_in, non_blocking=True)
-        for row, vrow in zip(layers, views):
+        main = torch.cuda.current_stream(device)
+        copy_in.wait_stream(main)
+        copy_out.wait_stream(main)
+        last = N_LAYERS - 1
+        with torch.cuda.stream(copy_in):
+            d_in[:in_per_layer].copy_(h_in[:in_per_layer], non_blocking=True)
+            first_in = torch.cuda.Event()
+            first_in.record(copy_in)
+            d_in[in_per_layer:].copy_(h_in[in_per_layer:], non_blocking=True)
+            rest_in = torch.cuda.Event()
+            rest_in.record(copy_in)
+        for li, (row, vrow) in enumerate(zip(layers, views)):
+            if li == 0:
+                main.wait_event(first_in)
+            elif li == 1:
+                main.wait_event(rest_in)
+            if li == last:                                   # everything before the last layer goes home while it computes
+                done = torch.cuda.Event()
+                done.record(main)
+                copy_out.wait_event(done)
+                with torch.cuda.stream(copy_out):
+                    h_out[:last * out_per_layer].copy_(d_out[:last * out_per_layer], non_blocking=True)
             for idxs in ([0, 1, 2], [3], [4, 5], [6]):
                 cur = torch.cuda.current_stream(device)
                 if len(idxs) == 1 or args.serial:
@@ -402,7 +428,11 @@ def run_gpu(args):
                 row[idxs[0]].forward(vrow[idxs[0]][0], out=vrow[idxs[0]][1])
                 for b in range(len(idxs) - 1):
                     cur.wait_stream(branch[b])
-        h_out.copy_(d_out, non_blocking=True)
+        main.wait_stream(copy_in)
+        copy_out.wait_stream(main)
+        with torch.cuda.stream(copy_out):
+            h_out[last * out_per_layer:].copy_(d_out[last * out_per_layer:], non_blocking=True)
+        main.wait_stream(copy_out)
 
     step_e2e()
     barrier()
