@@ -383,12 +383,18 @@ int32_t affine_b4_gemm_pair_launch(scr_ctx* ctx, const CUtensorMap& x_map, const
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     cfg.gridDim = dim3(2 * (ctx->sm_count / 2));
-    int max_pairs = 0;                                    // the pairing may leave an SM of a GPC unused: the grid is persistent
-    e = cudaOccupancyMaxActiveClusters(&max_pairs, affine_b4_gemm_pair_kernel, &cfg);
-    if (e != cudaSuccess || max_pairs < 1) {
-        (void)cudaGetLastError();
-        return SCR_OK;                                    // not launched: the caller runs the one-CTA kernel
+    // how many pairs fit at once (the pairing may leave an SM of a GPC unused; the grid is persistent): asked once per device
+    static int pairs_of_device[64] = {0};
+    int max_pairs = (ctx->device >= 0 && ctx->device < 64) ? pairs_of_device[ctx->device] : 0;
+    if (max_pairs == 0) {
+        e = cudaOccupancyMaxActiveClusters(&max_pairs, affine_b4_gemm_pair_kernel, &cfg);
+        if (e != cudaSuccess || max_pairs < 1) {
+            (void)cudaGetLastError();
+            max_pairs = -1;
+        }
+        if (ctx->device >= 0 && ctx->device < 64) pairs_of_device[ctx->device] = max_pairs;
     }
+    if (max_pairs < 1) return SCR_OK;                     // not launched: the caller runs the one-CTA kernel
     const int MTP = scr_ceil_div(M, 256);
     const int tiles = MTP * (g.RB / 16);
     cfg.gridDim = dim3(2 * std::min(tiles, max_pairs));

@@ -303,14 +303,19 @@ int32_t fp8_gemm_pair_launch(scr_ctx* ctx, const uint8_t* wpack, const uint8_t* 
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    // how many pairs fit at once (the pairing may leave an SM of a GPC unused): the grid is persistent
     cfg.gridDim = dim3(2 * (ctx->sm_count / 2));
-    int max_pairs = 0;
-    e = cudaOccupancyMaxActiveClusters(&max_pairs, fp8_gemm_pair_kernel, &cfg);
-    if (e != cudaSuccess || max_pairs < 1) {
-        (void)cudaGetLastError();
-        return SCR_OK;                                    // not launched: the caller runs the one-CTA kernel
+    // how many pairs fit at once (the pairing may leave an SM of a GPC unused; the grid is persistent): asked once per device
+    static int pairs_of_device[64] = {0};
+    int max_pairs = (ctx->device >= 0 && ctx->device < 64) ? pairs_of_device[ctx->device] : 0;
+    if (max_pairs == 0) {
+        e = cudaOccupancyMaxActiveClusters(&max_pairs, fp8_gemm_pair_kernel, &cfg);
+        if (e != cudaSuccess || max_pairs < 1) {
+            (void)cudaGetLastError();
+            max_pairs = -1;
+        }
+        if (ctx->device >= 0 && ctx->device < 64) pairs_of_device[ctx->device] = max_pairs;
     }
+    if (max_pairs < 1) return SCR_OK;                     // not launched: the caller runs the one-CTA kernel
     const int tiles = (MT / 2) * (g.NT / 2);
     cfg.gridDim = dim3(2 * std::min(tiles, max_pairs));
     // the pre-swizzled 16 KB tiles of both operands as byte tensors [bytes / 256][256]: a tile is a box of 64 rows
