@@ -242,11 +242,17 @@ def run_gpu(args):
     # parallel branches of the graph (forked streams at capture), dependent ones join first.
     branch = [torch.cuda.Stream(device) for _ in range(2)]
 
+    from scratchy_b200 import AffineQuantLinear
+
     def run_group(row, idxs):
         cur = torch.cuda.current_stream(device)
         if len(idxs) == 1 or args.serial:
             for i in idxs:
                 row[i].forward(xs[i], out=ys[i])
+            return
+        if not args.branches:
+            # independent linears over the same activation (q, k, v; gate, up): one group launch
+            AffineQuantLinear.forward_group([row[i] for i in idxs], xs[idxs[0]], [ys[i] for i in idxs])
             return
         for b, i in enumerate(idxs[1:]):
             branch[b].wait_stream(cur)
@@ -324,8 +330,8 @@ def run_gpu(args):
         fused_info = {"value": step_bytes * args.steps / (ms_f * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": ms_f / args.steps,
                       "launches_per_step": 4 * N_LAYERS,
                       "workload": "the same 7 linears per layer as q|k|v and gate|up rows-concat fused projections "
-                                  "(the reference's load_rows_concat): 4 launches per layer in stream order, issued as a decode step "
-                                  "issues them (scr_linear_affine_b4_ends with no end set, which sizes the ring for a chain)"}
+                                  "(the reference's load_rows_concat): 4 launches per layer in stream order over concatenated "
+                                  "matrices (the headline runs the same 4 launches over the separate matrices)"}
         del graph_f
     fused_layers = None
 
@@ -371,7 +377,11 @@ def run_gpu(args):
     # branches): the first layer's inputs, then everything else while the first layer computes; the outputs of all but
     # the last layer while the last layer computes, then the last layer's.  (A copy per layer was measured slower: 56
     # copy nodes and 56 cross-stream dependencies cost more than the 3 MB they hide.)
-    in_elems = [M * K for K, _ in shapes]
+    # q, k and v read one activation, gate and up another: a layer has four distinct inputs (`--branches` / `--serial`,
+    # where every linear is its own launch, keep one input per linear)
+    shared_in = not (args.branches or args.serial)
+    in_of = [0, 0, 0, 3, 4, 4, 6] if shared_in else list(range(7))       # linear -> the input it reads
+    in_elems = [M * shapes[i][0] if in_of[i] == i else 0 for i in range(7)]
     out_elems = [M * N for _, N in shapes]
     h_in = torch.randn(N_LAYERS * sum(in_elems)).to(torch.bfloat16).pin_memory()
     h_out = torch.empty(N_LAYERS * sum(out_elems), dtype=torch.bfloat16).pin_memory()
@@ -382,10 +392,12 @@ def run_gpu(args):
     views = []
     oi = oo = 0
     for li in range(N_LAYERS):
-        row = []
-        for (K, N), ne_i, ne_o in zip(shapes, in_elems, out_elems):
-            row.append((d_in[oi:oi + ne_i].view(M, K), d_out[oo:oo + ne_o].view(M, N)))
-            oi += ne_i
+        row, in_views = [], {}
+        for i, ((K, N), ne_i, ne_o) in enumerate(zip(shapes, in_elems, out_elems)):
+            if in_of[i] == i:
+                in_views[i] = d_in[oi:oi + ne_i].view(M, K)
+                oi += ne_i
+            row.append((in_views[in_of[i]], d_out[oo:oo + ne_o].view(M, N)))
             oo += ne_o
         views.append(row)
 
@@ -420,6 +432,9 @@ def run_gpu(args):
                 if len(idxs) == 1 or args.serial:
                     for i in idxs:
                         row[i].forward(vrow[i][0], out=vrow[i][1])
+                    continue
+                if not args.branches:
+                    AffineQuantLinear.forward_group([row[i] for i in idxs], vrow[idxs[0]][0], [vrow[i][1] for i in idxs])
                     continue
                 for b, i in enumerate(idxs[1:]):
                     branch[b].wait_stream(cur)
@@ -494,17 +509,23 @@ def run_gpu(args):
                        "bytes_per_step": step_bytes, "l2": "inputs larger than L2 (1.585 GB of distinct weights per step)",
                        "dependencies": "stream order only: the linears of one shape share one input and one output buffer, so a linear "
                                        "waits for its predecessors without consuming their values (a weight-stream measurement)",
-                       "replicas": world, "launch": "one CUDA graph of 196 matvec launches per step; q/k/v and gate/up on parallel branches"
-                       if not args.serial else "one CUDA graph of 196 matvec launches per step, one branch"},
+                       "replicas": world,
+                       "launch": ("one CUDA graph per step; the 7 linears of a layer in 4 launches: q, k, v (one activation) and gate, up "
+                                  "(one activation) each as one group launch over the members' own packed buffers "
+                                  "(scr_linear_affine_b4_group), o and down on their own") if not (args.serial or args.branches)
+                       else ("one CUDA graph of 196 matvec launches per step; q/k/v and gate/up on parallel branches" if args.branches
+                             else "one CUDA graph of 196 matvec launches per step, one branch")},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"],
-                         # launch-weighted mean over the 7 shapes of the per-shape ncu figures (GEMV_DRAM_TRAFFIC)
-                         "traffic": sum(GEMV_DRAM_TRAFFIC[n] for n in LAYER_ORDER) / len(LAYER_ORDER),
+                         # per launch: the per-shape ncu figures (GEMV_DRAM_TRAFFIC) of a layer's 7 matrices over the
+                         # launches that stream them (a group launch streams its members' matrices, each once)
+                         "traffic": N_LAYERS * sum(GEMV_DRAM_TRAFFIC[n] for n in LAYER_ORDER) / launches_per_step,
                          "traffic_source": "ncu dram__bytes_read+write per launch, by shape: profiles/affine_b4_gemv_llama3b_m1_full.md, "
                                            "profiles/affine_b4_gemv_llama3b_gate_m1_full.md",
                          "peak_source": peaks["src"],
                          "kernel": "affine_b4_gemv_kernel", "avg_launch_us": per_launch_us,
-                         "alg_bytes_per_launch": step_bytes / (N_LAYERS * len(LAYER_ORDER))},
+                         "launches_per_step": launches_per_step,
+                         "alg_bytes_per_launch": step_bytes / launches_per_step},
             "cpu_baseline": {"value": cpu_v, "unit": UNIT, "cores": cores, "kind": "port",
                              "sample": f"7 linears of one layer, {cpu_dt * 1e3:.1f} ms per pass, oracle C++/OpenMP"},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -1030,7 +1051,7 @@ def run_case(args):
         return run_case_attention(device, batch=int(name), context=M, reps=args.steps)
     # kind "fp8x": the fp8 matvec with the tensor-parallel exchange in its epilogue, on a one-rank communicator
     # (pushes to itself: the whole kernel runs on one GPU)
-    # kind "int4c": the int4 matvec issued as a decode chain issues it (scr_linear_affine_b4_ends with no end set)
+    # kind "int4c": the int4 matvec through the matvec-ends entry point with no end set (scr_linear_affine_b4_ends)
     K, N = (synth.LLAMA_3_2_3B if kind in ("int4", "int4c") else synth.QWEN_2_5_7B)[name]
     copies = max(2, int((256 << 20) // (N * K)) + 1)
     lins = []
@@ -1119,6 +1140,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--sweep", action="store_true")
     ap.add_argument("--serial", action="store_true", help="one branch: every linear waits for the previous one")
+    ap.add_argument("--branches", action="store_true",
+                    help="every linear its own launch, q/k/v and gate/up on parallel graph branches (instead of group launches)")
     ap.add_argument("--no-decode", action="store_true", help="skip the whole-decode-step section (config 3)")
     ap.add_argument("--decode-only", action="store_true", help="run only the whole-decode-step section and print it")
     ap.add_argument("--decode-batches", default="1,8,32")

@@ -118,6 +118,15 @@ int32_t scr_linear_affine_b4(scr_ctx* ctx, const void* packed, const uint16_t* x
                              int32_t M, int32_t N, int32_t K, int32_t group,
                              const uint16_t* bias_bf16, uint16_t* y_bf16,
                              void* workspace, size_t workspace_bytes, void* stream);
+/* Up to 4 independent linears over the SAME activations — q, k, v of a layer; gate and up — as ONE launch: what the
+ * reference gets by fusing the projections at load time (`load_rows_concat`, crates/targets/metal/src/layers_quant.rs:363-450)
+ * without re-laying the weights.  Every member keeps its own packed buffer (`packed[i]`, [N[i], K]) and its own output
+ * (`y[i]`, [M, N[i]] bf16); all share K, the group size and x.  Same bits per member as `scr_linear_affine_b4`.  Up to
+ * 16 tokens one matvec launch runs over all members' rows; above, the members run one after the other (`workspace` as
+ * for `scr_linear_affine_b4` at the largest member). */
+int32_t scr_linear_affine_b4_group(scr_ctx* ctx, int32_t count, const void* const* packed, const uint16_t* x_bf16,
+                                   int32_t M, const int32_t* N, int32_t K, int32_t group, uint16_t* const* y_bf16,
+                                   void* workspace, size_t workspace_bytes, void* stream);
 /* The fused gate/up projection with its activation, the `FusedGateUpSiluMul` end of the reference's
  * matvec (`QmvEnds`, crates/targets/metal/src/tape/step.rs:472-482; golden cpu_golden.rs:211-219):
  *   out[M, N2/2] (bf16) = silu(bf16(x @ gate^T)) * bf16(x @ up^T)

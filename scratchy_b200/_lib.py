@@ -45,6 +45,7 @@ SIGNATURES = {
     "scr_linear_workspace_size": (_i32, [_i32, _i32, _i32, _i32, _psz]),
     "scr_linear_affine_b4": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _sz, _vp]),
     "scr_linear_affine_b4_ends": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),
+    "scr_linear_affine_b4_group": (_i32, [_vp, _i32, ctypes.POINTER(_vp), _vp, _i32, ctypes.POINTER(_i32), _i32, _i32, ctypes.POINTER(_vp), _vp, ctypes.c_size_t, _vp]),
     "scr_linear_affine_b4_silu_mul": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp]),
     "scr_linear_affine_b4_residual_rmsnorm": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, ctypes.c_float, _vp,
                                                      _vp, _sz, _vp]),

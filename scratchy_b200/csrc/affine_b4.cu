@@ -284,6 +284,28 @@ struct GemvExtra {
     float norm_eps, norm_offset; // rmsnorm(x, gain + offset)
     float scale;                 // multiplies the sum after the bias (1 = none)
 };
+// Several independent linears that read the SAME activations (q, k, v; gate, up), run by ONE launch: the launch's row-block
+// space is the matrices' row-blocks one after the other, and a row-block finds its matrix, its packed rows and its output
+// through this table (passed by value; count 0 = a single matrix, the plain arguments apply).  What the reference gets by
+// fusing the projections at load time (`load_rows_concat`) without re-laying the weights.
+#define GEMV_GROUP_MAX 4
+struct GemvGroup {
+    const uint8_t* packed[GEMV_GROUP_MAX];
+    uint16_t* y[GEMV_GROUP_MAX];
+    int rb_start[GEMV_GROUP_MAX + 1];    // first row-block of each matrix in the launch's row-block space
+    int n[GEMV_GROUP_MAX];               // output channels of each matrix
+    int rb_pad[GEMV_GROUP_MAX];          // padded row-blocks of each matrix (where its trailer sits)
+    int count;
+};
+// Matrix of row-block `rb` and everything of it (no dynamic indexing of the by-value table: selects only).
+struct GemvGroupPick { const uint8_t* packed; uint16_t* y; int rb_local, n; };
+__device__ __forceinline__ GemvGroupPick gemv_group_pick(const GemvGroup& g, int rb) {
+    GemvGroupPick p = {g.packed[0], g.y[0], rb, g.n[0]};
+#pragma unroll
+    for (int i = 1; i < GEMV_GROUP_MAX; ++i)
+        if (i < g.count && rb >= g.rb_start[i]) { p.packed = g.packed[i]; p.y = g.y[i]; p.rb_local = rb - g.rb_start[i]; p.n = g.n[i]; }
+    return p;
+}
 __device__ __forceinline__ void gemv_unpack8(const uint4& v, float* f) {
     f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xFFFF0000u);
     f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xFFFF0000u);
@@ -373,12 +395,13 @@ __device__ __forceinline__ void gemv_wait_fast(uint32_t bar, uint32_t parity, in
     if (!ok) gemv_wait_slow(bar, parity, status);
 }
 
-template <int MT, int SPLIT_CLUSTER, bool CHECK, int U, bool NORM, int GS>
+template <int MT, int SPLIT_CLUSTER, bool CHECK, int U, bool NORM, int GS, bool GROUP>
 __device__ __forceinline__ void gemv_consumer(const uint16_t* __restrict__ x, uint16_t* __restrict__ y, int M, int N,
                                               int K, int kc_lo, int kc_hi, int nstage, int rb_real, int split, int sp,
                                               int out_f32, const GemvExtra& ex, uint32_t xs_base, int* __restrict__ status, uint32_t ring_base, uint32_t full_base,
                                               uint32_t empty_base, float (*red)[GEMV_CWARPS][32][MT * 4],
-                                              float (*cl_part)[16][MT * 8], const GemvEnds& ends, float (*sq_s)[16][16]) {
+                                              float (*cl_part)[16][MT * 8], const GemvEnds& ends, float (*sq_s)[16][16],
+                                              const GemvGroup& grp) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     float cta_sq = 0.f;                        // RESIDUAL_NORM: thread tok's sum of squares over this CTA's row-blocks
@@ -456,6 +479,10 @@ __device__ __forceinline__ void gemv_consumer(const uint16_t* __restrict__ x, ui
                 gemv_store_silu_pair(total, idx, tok, M, rb * 8 + (ln >> 2), N >> 1, y);
             } else if (out_f32 == GEMV_OUT_RESIDUAL_NORM) {
                 sq_s[buf][tok][row] = gemv_residual_update(total, tok, M, n, N, ends);
+            } else if (GROUP) {
+                const GemvGroupPick gp = gemv_group_pick(grp, rb);
+                const int nl = gp.rb_local * 16 + row;
+                if (tok < M && nl < gp.n) gemv_store_plain(total, out_f32, ex, gp.y, (size_t)tok * gp.n + nl, nl);
             } else if (tok < M && n < N) {
                 gemv_store_plain(total, out_f32, ex, y, (size_t)tok * N + n, n);
             }
@@ -472,11 +499,11 @@ __device__ __forceinline__ void gemv_consumer(const uint16_t* __restrict__ x, ui
         gemv_norm_tail(cta_sq, M, N, gridDim.x, blockIdx.x, ends, 1, GEMV_CWARPS * 32);
 }
 
-template <int MT, int SPLIT_CLUSTER, int U, bool NORM, int GS>
+template <int MT, int SPLIT_CLUSTER, int U, bool NORM, int GS, bool GROUP>
 __global__ void __launch_bounds__(GEMV_THREADS, (MT == 1 ? GemvRing<U, GS>::kCtasPerSm : 2))
 affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __restrict__ x, uint16_t* __restrict__ y,
                       int M, int N, int K, int RB, int KC, int rb_real, int split, int out_f32,
-                      GemvExtra ex, int* __restrict__ status, GemvEnds ends) {
+                      GemvExtra ex, int* __restrict__ status, GemvEnds ends, GemvGroup grp) {
     extern __shared__ __align__(128) uint8_t gemv_ring[];          // [stages][8 * U blocks], then (NORM) the normalised rows [M][K] bf16
     __shared__ float norm_red[GEMV_CWARPS];
     __shared__ float sq_s[2][16][16];                              // RESIDUAL_NORM: squares of the stored residuals [token][row]
@@ -516,7 +543,9 @@ affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __rest
         if (lane == 0) {
             uint32_t slot = 0, phase = 0;
             for (int rb = blockIdx.x; rb < rb_real; rb += gridDim.x) {
-                const uint8_t* src = packed + ((size_t)rb * KC + kc_lo) * R::kBlockBytes;
+                const uint8_t* src = GROUP ? [&] { const GemvGroupPick gp = gemv_group_pick(grp, rb);
+                                                       return gp.packed + ((size_t)gp.rb_local * KC + kc_lo) * R::kBlockBytes; }()
+                                               : packed + ((size_t)rb * KC + kc_lo) * R::kBlockBytes;
                 for (int j = 0; j < nstage; ++j) {
                     gemv_wait(empty_base + 8u * slot, phase ^ 1u, status);
                     const uint32_t bytes = (uint32_t)min(R::kStageBlocks, kc_hi - kc_lo - j * R::kStageBlocks) * R::kBlockBytes;
@@ -530,17 +559,26 @@ affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __rest
     } else {
         // one word per matrix says whether any group needs the exact (two-step rounding) path; it is a
         // load-time constant, so its (cold, HBM) fetch is issued before the wait and hides under it
-        const unsigned int trailer_flag = *reinterpret_cast<const volatile unsigned int*>(packed + (size_t)RB * KC * R::kBlockBytes);
+        unsigned int trailer_flag;
+        if (GROUP) {                                               // any matrix of the group that needs the exact path
+            trailer_flag = 0;
+#pragma unroll
+            for (int i = 0; i < GEMV_GROUP_MAX; ++i)
+                if (i < grp.count)
+                    trailer_flag |= *reinterpret_cast<const volatile unsigned int*>(grp.packed[i] + (size_t)grp.rb_pad[i] * KC * R::kBlockBytes);
+        } else {
+            trailer_flag = *reinterpret_cast<const volatile unsigned int*>(packed + (size_t)RB * KC * R::kBlockBytes);
+        }
         asm volatile("griddepcontrol.wait;" ::: "memory");        // x (and y's previous readers) are settled
         const uint32_t xs_base = ring_base + R::kBytes;
         if (NORM) gemv_norm_rows(x, ex, M, K, gemv_ring + R::kBytes, norm_red);
         const bool check = trailer_flag != 0;
         if (check)
-            gemv_consumer<MT, SPLIT_CLUSTER, true, U, NORM, GS>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, out_f32, ex, xs_base, status,
-                                                            ring_base, full_base, empty_base, red, cl_part, ends, sq_s);
+            gemv_consumer<MT, SPLIT_CLUSTER, true, U, NORM, GS, GROUP>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, out_f32, ex, xs_base, status,
+                                                            ring_base, full_base, empty_base, red, cl_part, ends, sq_s, grp);
         else
-            gemv_consumer<MT, SPLIT_CLUSTER, false, U, NORM, GS>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, out_f32, ex, xs_base, status,
-                                                             ring_base, full_base, empty_base, red, cl_part, ends, sq_s);
+            gemv_consumer<MT, SPLIT_CLUSTER, false, U, NORM, GS, GROUP>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, out_f32, ex, xs_base, status,
+                                                             ring_base, full_base, empty_base, red, cl_part, ends, sq_s, grp);
     }
 
     if (SPLIT_CLUSTER) {
@@ -572,6 +610,14 @@ affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __rest
             float s = 0.f;
             for (int r = 0; r < split; ++r) s += cl_part[r][row][min(tok, MT * 8 - 1)];
             gemv_store_silu_pair(s, idx, tok, M, blockIdx.x * 8 + (ln >> 2), N >> 1, y);
+        } else if (GROUP && sp == 0 && e < SLOTS) {
+            const GemvGroupPick gp = gemv_group_pick(grp, blockIdx.x);
+            const int nl = gp.rb_local * 16 + row;
+            if (tok < M && nl < gp.n) {
+                float s = 0.f;
+                for (int r = 0; r < split; ++r) s += cl_part[r][row][tok];
+                gemv_store_plain(s, out_f32, ex, gp.y, (size_t)tok * gp.n + nl, nl);
+            }
         } else if (sp == 0 && e < SLOTS && tok < M && n < N) {
             float s = 0.f;
             for (int r = 0; r < split; ++r) s += cl_part[r][row][tok];
@@ -699,35 +745,32 @@ struct AffineFwd {
     float norm_eps = 0.f, norm_offset = 0.f;
     float scale = 1.0f;                      // multiplies the sum after the bias
     const GemvEnds* ends = nullptr;          // GEMV_OUT_RESIDUAL_NORM only
-    bool chain = false;                      // an operator of a decode chain: its input is the previous launch's output
     int gs = 1;                              // (scale, bias) entries per row and block, log2: set from the group size by affine_forward
+    const GemvGroup* grp = nullptr;          // several matrices in one launch (scr_linear_affine_b4_group); N is then unused
+    int grp_rb = 0;                          // ... the launch's total row-blocks
 };
 // Shared memory the norm-in end may take for the normalised rows beside the ring (two CTAs per SM).
 #define GEMV_NORM_MAX_BYTES (20 * 1024)
 
-// Blocks per warp and ring stage.  3 costs 162 executed warp instructions per 1152-byte block against 197 with 1, but runs two
-// CTAs of 96 registers per SM instead of three of 72.  Measured on Llama-3.2-3B at one token: where each matvec consumes
-// the previous one's output (a decode step) 3 is faster throughout (the chain of 28 layers' linears 829 against 894 us, as
-// fused projections 641 against 678 us, the batch-1 decode step 1.100 against 1.150 ms); where independent matvecs follow one
-// another in stream order and overlap their neighbours' tails, 1 is (790 against 856 us for the 196 linears), except for
-// matrices of 28 MB and more, which fill the GPU on their own.  At 8 tokens, where every lane reads its own activation row,
-// 1 is 2 % faster in both settings.  So: 3 up to 4 tokens for the operators that only a decode chain uses (the ends below) and
-// for matrices of at least GEMV_U3_MIN_BLOCKS blocks; 1 otherwise (the two-tile kernel for 9..16 tokens has no registers to spare).
-#define GEMV_U3_MIN_BLOCKS 20000
-static int affine_gemv_u(int M, int N, int K, bool chain) {
-    if (M > 4) return 1;
-    return (chain || (long long)scr_ceil_div(N, 16) * scr_ceil_div(K, AFF_BLOCK_K) >= GEMV_U3_MIN_BLOCKS) ? 3 : 1;
-}
+// Blocks per warp and ring stage.  3 costs 173 executed warp instructions per 1152-byte block against 217 with 1, but runs two
+// CTAs of 96 registers per SM instead of three of 72.  Measured on Llama-3.2-3B at one token: for launches that follow one
+// another in one stream (a decode step; a layer's linears as 4 launches) 3 is faster throughout (the 28 layers' linears one
+// after the other 829 against 894 us, as fused projections 641 against 678 us, the batch-1 decode step 1.085-1.100 against
+// 1.150 ms, the largest shape alone 5.66 against 5.81 us); only where independent matvecs run on parallel streams and
+// overlap their neighbours' tails is 1 ahead (790 against 856 us for the 196 linears on two graph branches); 2 loses in both
+// settings.  At 8 tokens, where every lane reads its own activation row, 1 is 2 % faster.  So: 3 up to 4 tokens, 1 above
+// (the two-tile kernel for 9..16 tokens has no registers to spare).
+static int affine_gemv_u(int M) { return M <= 4 ? 3 : 1; }
 
-template <int MT, int U, bool NORM, int GS = 1>
+template <int MT, int U, bool NORM, int GS = 1, bool GROUP = false>
 static int32_t affine_gemv_launch_u(scr_ctx* ctx, const uint8_t* packed, const uint16_t* x, uint16_t* y, int M, int N,
                                     int K, const AffineFwd& f, cudaStream_t stream) {
     using R = GemvRing<U, GS>;
-    const AffineGeom g = affine_geom(N, K, GS == 2 ? 32 : 64);
-    const int rb_real = scr_ceil_div(N, 16);
+    const AffineGeom g = affine_geom(f.grp ? 16 : N, K, GS == 2 ? 32 : 64);   // KC only matters for a group
+    const int rb_real = f.grp ? f.grp_rb : scr_ceil_div(N, 16);
     int grid_x = 1, split = 1;
     affine_gemv_shape(rb_real, g.KC, ctx->sm_count, MT == 1 ? R::kCtasPerSm : 2, &grid_x, &split);
-    auto kernel = (split == 1) ? affine_b4_gemv_kernel<MT, 0, U, NORM, GS> : affine_b4_gemv_kernel<MT, 1, U, NORM, GS>;
+    auto kernel = (split == 1) ? affine_b4_gemv_kernel<MT, 0, U, NORM, GS, GROUP> : affine_b4_gemv_kernel<MT, 1, U, NORM, GS, GROUP>;
     const int smem = R::kBytes + (NORM ? M * K * 2 : 0);
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, R::kBytes + (NORM ? GEMV_NORM_MAX_BYTES : 0));
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine_b4_gemv smem attribute: %s", cudaGetErrorString(e));
@@ -758,7 +801,8 @@ static int32_t affine_gemv_launch_u(scr_ctx* ctx, const uint8_t* packed, const u
             return scr_fail(ctx, SCR_E_WORKSPACE, "residual + norm epilogue: %d CTAs exceed the scratch", grid_x);
     }
     const GemvExtra ex = {f.bias, f.norm_gain, f.norm_eps, f.norm_offset, f.scale};
-    e = cudaLaunchKernelEx(&cfg, kernel, packed, x, y, M, N, K, g.RB, g.KC, rb_real, split, f.out_mode, ex, ctx->dev_status, ends);
+    const GemvGroup grp = f.grp ? *f.grp : GemvGroup{};
+    e = cudaLaunchKernelEx(&cfg, kernel, packed, x, y, M, N, K, g.RB, g.KC, rb_real, split, f.out_mode, ex, ctx->dev_status, ends, grp);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine_b4_gemv launch: %s", cudaGetErrorString(e));
     return scr_check_launch(ctx, "affine_b4_gemv");
 }
@@ -771,7 +815,12 @@ static int32_t affine_gemv_launch(scr_ctx* ctx, const uint8_t* packed, const uin
         if (f.norm_gain) return scr_fail(ctx, SCR_E_UNSUPPORTED, "norm-in end: not built for groups of 32 (run the norm on its own)");
         return affine_gemv_launch_u<MT, 1, false, 2>(ctx, packed, x, y, M, N, K, f, stream);
     }
-    const int u = affine_gemv_u(M, N, K, f.chain);
+    const int u = affine_gemv_u(M);
+    if (f.grp) {
+        if (f.gs == 2 || f.norm_gain) return scr_fail(ctx, SCR_E_UNSUPPORTED, "a group launch is built for groups of 64 and 128 without the norm-in end");
+        if (u == 3) return affine_gemv_launch_u<1, 3, false, 1, true>(ctx, packed, x, y, M, N, K, f, stream);
+        return affine_gemv_launch_u<MT, 1, false, 1, true>(ctx, packed, x, y, M, N, K, f, stream);
+    }
     if (f.norm_gain) {
         // the normalised rows sit in shared memory beside the ring: a few tokens only
         if (MT != 1 || (size_t)M * K * 2 > GEMV_NORM_MAX_BYTES)
@@ -858,6 +907,49 @@ extern "C" int32_t scr_linear_affine_b4_partial(scr_ctx* ctx, const void* packed
     return affine_forward(ctx, packed, x, M, N, K, group, y_f32, f, workspace, workspace_bytes, (cudaStream_t)stream_);
 }
 
+// Up to GEMV_GROUP_MAX independent linears over the SAME activations in one launch (q, k, v; gate, up): matrices of one K and
+// one group size, each with its own packed buffer and its own output.  Up to 16 tokens it is one matvec launch whose
+// row-block space runs over the matrices; above, the linears run one after the other (the GEMM fills the GPU by itself).
+extern "C" int32_t scr_linear_affine_b4_group(scr_ctx* ctx, int32_t count, const void* const* packed, const uint16_t* x, int32_t M,
+                                              const int32_t* N, int32_t K, int32_t group, uint16_t* const* y, void* workspace,
+                                              size_t workspace_bytes, void* stream_) {
+    SCR_REQUIRE_CTX(ctx);
+    if (!packed || !N || !y || !x) return scr_fail(ctx, SCR_E_ARG, "null pointer");
+    if (count < 1 || count > GEMV_GROUP_MAX) return scr_fail(ctx, SCR_E_SHAPE, "a group holds 1 to %d linears (%d)", GEMV_GROUP_MAX, count);
+    if (M <= 0) return scr_fail(ctx, SCR_E_SHAPE, "M=%d must be positive", M);
+    GemvGroup grp = {};
+    grp.count = count;
+    int rb = 0;
+    for (int i = 0; i < count; ++i) {
+        if (!packed[i] || !y[i]) return scr_fail(ctx, SCR_E_ARG, "group member %d: null pointer", i);
+        const int32_t st = affine_check_shape(ctx, N[i], K, group);
+        if (st) return st;
+        if (!scr_aligned16(packed[i])) return scr_fail(ctx, SCR_E_ALIGN, "group member %d: packed must be 16-byte aligned", i);
+        grp.packed[i] = static_cast<const uint8_t*>(packed[i]);
+        grp.y[i] = y[i];
+        grp.n[i] = N[i];
+        grp.rb_start[i] = rb;
+        grp.rb_pad[i] = affine_geom(N[i], K, group).RB;
+        rb += scr_ceil_div(N[i], 16);
+    }
+    for (int i = count; i <= GEMV_GROUP_MAX; ++i) grp.rb_start[i] = rb;
+    if (!scr_aligned16(x)) return scr_fail(ctx, SCR_E_ALIGN, "x must be 16-byte aligned");
+    if (M > 16 || count == 1 || group == 32) {            // (groups of 32 have no group launch: member by member)
+        for (int i = 0; i < count; ++i) {
+            AffineFwd f;
+            const int32_t st = affine_forward(ctx, packed[i], x, M, N[i], K, group, y[i], f, workspace, workspace_bytes, (cudaStream_t)stream_);
+            if (st) return st;
+        }
+        return SCR_OK;
+    }
+    AffineFwd f;
+    f.gs = affine_gs(group);
+    f.grp = &grp;
+    f.grp_rb = rb;
+    if (M <= 8) return affine_gemv_launch<1>(ctx, grp.packed[0], x, grp.y[0], M, N[0], K, f, (cudaStream_t)stream_);
+    return affine_gemv_launch<2>(ctx, grp.packed[0], x, grp.y[0], M, N[0], K, f, (cudaStream_t)stream_);
+}
+
 // The one-row matvec with the reference's ends around it (`QmvEnds`, crates/targets/metal/src/tape/step.rs:472-498).
 extern "C" int32_t scr_linear_affine_b4_ends(scr_ctx* ctx, const void* packed, const uint16_t* x, int32_t M, int32_t N, int32_t K,
                                              int32_t group, const scr_qmv_ends* ends, uint16_t* y, void* stream_) {
@@ -873,7 +965,6 @@ extern "C" int32_t scr_linear_affine_b4_ends(scr_ctx* ctx, const void* packed, c
     f.out_mode = ends->residual ? GEMV_OUT_RESIDUAL_ADD : (ends->silu_pairs ? GEMV_OUT_SILU_PAIRS : GEMV_OUT_BF16);
     if (ends->silu_pairs && (N <= 0 || N % 16 != 0)) return scr_fail(ctx, SCR_E_SHAPE, "gate/up pairing: %d fused rows (8 gate + 8 up per block)", N);
     if (M > 16) return scr_fail(ctx, SCR_E_UNSUPPORTED, "the matvec ends exist up to 16 tokens (M=%d): run the operators separately", M);
-    f.chain = true;
     return affine_forward(ctx, packed, x, M, N, K, group, y, f, nullptr, 0, (cudaStream_t)stream_);
 }
 
@@ -893,7 +984,6 @@ extern "C" int32_t scr_linear_affine_b4_residual_rmsnorm(scr_ctx* ctx, const voi
     AffineFwd f;
     f.out_mode = GEMV_OUT_RESIDUAL_NORM;
     f.ends = &ends;
-    f.chain = true;
     // y is not written in this mode; the residual buffer stands in for the (unused) output pointer
     return affine_forward(ctx, packed, x, M, N, K, group, residual, f, nullptr, 0, (cudaStream_t)stream_);
 }
@@ -905,7 +995,6 @@ extern "C" int32_t scr_linear_affine_b4_silu_mul(scr_ctx* ctx, const void* packe
     if (N2 <= 0 || N2 % 16 != 0) return scr_fail(ctx, SCR_E_SHAPE, "fused silu*up epilogue: %d fused rows (8 gate + 8 up per block)", N2);
     AffineFwd f;
     f.out_mode = GEMV_OUT_SILU_PAIRS;
-    f.chain = true;
     return affine_forward(ctx, packed, x, M, N2, K, group, out, f, nullptr, 0, (cudaStream_t)stream_);
 }
 

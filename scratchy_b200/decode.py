@@ -405,8 +405,8 @@ class LlamaDecoder:
     # ---- one step: reads buf.ids/positions/slot_mapping/block_table/seq_used_k, writes buf.logits/next_ids
     @staticmethod
     def _linear(lin, x: torch.Tensor, out: torch.Tensor, buf: DecodeBuffers) -> torch.Tensor:
-        """A linear of the step.  Up to 16 tokens it goes through the ends entry point with no end set, which marks the matvec
-        as one of a decode chain (every launch consumes the one before it; the kernel sizes its ring for that)."""
+        """A linear of the step: up to 16 tokens through the matvec-ends entry point (no end set here; the same kernel as
+        `forward`), above through `forward` with the step's workspace."""
         if buf.batch <= 16 and isinstance(lin, AffineQuantLinear):
             return lin.forward_ends(x, out)
         return lin.forward(x, out=out, workspace=buf.workspace)

@@ -268,6 +268,38 @@ class AffineQuantLinear:
             _stream(dev)))
         return out.reshape(*x.shape[:-1], self.out_features)
 
+    @staticmethod
+    def forward_group(layers, x: torch.Tensor, outs=None, workspace: Optional[torch.Tensor] = None):
+        """Up to 4 linears over the SAME activations (q, k, v; gate, up) as one launch (`scr_linear_affine_b4_group`): each
+        keeps its own packed buffer and gets its own output, the bits of `forward` per member.  Returns the outputs."""
+        layers = list(layers)
+        if not 1 <= len(layers) <= 4:
+            raise ValueError(f"a group holds 1 to 4 linears, got {len(layers)}")
+        K, g = layers[0].in_features, layers[0].group_size
+        if any(l.in_features != K or l.group_size != g for l in layers):
+            raise ValueError("the linears of a group share in_features and the group size")
+        if any(l.linear_bias is not None for l in layers):
+            raise ValueError("a group launch has no bias end: a `.bias` is refused, not dropped")
+        x2 = x.reshape(-1, K).contiguous()
+        M = int(x2.shape[0])
+        dev = x2.device
+        if outs is None:
+            outs = [torch.empty((M, l.out_features), dtype=torch.bfloat16, device=dev) for l in layers]
+        n = len(layers)
+        packed = (ctypes.c_void_p * n)(*[l.packed.data_ptr() for l in layers])
+        ys = (ctypes.c_void_p * n)(*[o.data_ptr() for o in outs])
+        ns = (ctypes.c_int32 * n)(*[l.out_features for l in layers])
+        ws_ptr, ws_bytes = (_ptr(workspace), workspace.numel() * workspace.element_size()) if workspace is not None else (None, 0)
+        if M > 16 and workspace is None:
+            need = max(l.workspace_bytes(M) for l in layers)
+            if need:
+                workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+                ws_ptr, ws_bytes = _ptr(workspace), need
+        ctx = _lib.context(_dev_index(dev))
+        ctx.check(_lib.lib().scr_linear_affine_b4_group(ctx.handle, n, packed, _ptr(x2), M, ns, K, g, ys, ws_ptr,
+                                                        ctypes.c_size_t(ws_bytes), _stream(dev)))
+        return outs
+
     def forward_ends(self, x: torch.Tensor, out: torch.Tensor, norm_gain: Optional[torch.Tensor] = None, norm_eps: float = 0.0,
                      norm_gain_offset: float = 0.0, scale: float = 1.0, residual: bool = False, silu_pairs: bool = False) -> torch.Tensor:
         """The matvec with the reference's `QmvEnds` around it (`scr_linear_affine_b4_ends`, up to 16 tokens): RMSNorm on the

@@ -523,3 +523,40 @@ def test_two_cta_gemm_gives_the_bits_of_the_one_cta_kernel(tmp_path):
     rows = np.array([0, 127, 128, 255, 256, 383, 384, 511])
     want = oracle.affine_qmm_t_b4_bias(w.view(np.uint8).reshape(-1), s, b, x[rows], bias, len(rows), N, K, group)
     assert rel_l2(pair.reshape(M, N)[rows], want) <= REL_L2_TOL
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 16, 40])
+@pytest.mark.parametrize("ns,K", [((3072, 1024, 1024), 3072), ((8192, 8192), 3072), ((24, 136, 8, 40), 320), ((3072,), 8192)])
+def test_group_launch_gives_each_member_the_bits_of_its_own_launch(ns, K, M):
+    """`scr_linear_affine_b4_group`: q, k, v (or gate, up) over the same activations in one launch.  A member's summation
+    order is that of its own row-block, so its bits are those of `forward` wherever the two launches split k alike, and
+    within rounding otherwise; both are held to the oracle's bound.  Outputs are prefilled with NaN to catch an unwritten row."""
+    import torch
+    from scratchy_b200 import AffineQuantLinear
+    trip = [synth.affine_int4_weights(n, K, 64, synth.seed_for("grp", n, K, i)) for i, n in enumerate(ns)]
+    lins = [make_layer(w, s, b) for w, s, b in trip]
+    x = synth.activations_bf16(M, K, synth.seed_for("grpx", K, M))
+    xd = bf16_dev(x).reshape(M, K)
+    outs = [torch.full((M, n), float("nan"), dtype=torch.bfloat16, device="cuda") for n in ns]
+    AffineQuantLinear.forward_group(lins, xd, outs)
+    torch.cuda.synchronize()
+    for (w, s, b), lin, out, n in zip(trip, lins, outs, ns):
+        want = oracle.affine_qmm_t_b4(w.view(np.uint8).reshape(-1), s, b, x, M, n, K, 64)
+        got = bits_of(out).reshape(M, n)
+        assert rel_l2(got, want) <= REL_L2_TOL
+        alone = bits_of(lin.forward(xd)).reshape(M, n)
+        assert rel_l2(got, alone) <= 1e-4 and np.mean(got == alone) > 0.98
+    from scratchy_b200 import _lib
+    _lib.context(0).device_status(None)
+
+
+def test_group_launch_refusals():
+    import torch
+    from scratchy_b200 import AffineQuantLinear
+    a = make_layer(*synth.affine_int4_weights(32, 128, 64, 1))
+    b = make_layer(*synth.affine_int4_weights(32, 256, 64, 2))
+    x = bf16_dev(synth.activations_bf16(1, 128, 3)).reshape(1, 128)
+    with pytest.raises(ValueError):
+        AffineQuantLinear.forward_group([a, b], x)                      # different in_features
+    with pytest.raises(ValueError):
+        AffineQuantLinear.forward_group([a] * 5, x)                     # more than four
