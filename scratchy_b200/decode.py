@@ -462,6 +462,14 @@ class LlamaDecoder:
         argmax(buf.logits, out=buf.next_ids)
         return buf.logits
 
+    def check_health(self) -> None:
+        """Synchronise and raise `ScratchyCudaError` if a device-side check fired since the last call: a token id,
+        position, slot or block id out of range (`SCR_E_ARG`; the access was skipped, the step's results are not to be
+        used) or a bounded wait that ran out (`SCR_E_TIMEOUT`).  The word is read and cleared (`scr_device_status`); a
+        serving loop calls this once per step, after it has synchronised on the step's tokens anyway — while the word is
+        set every bounded wait on the context gives up early."""
+        _ctx(self.device).device_status(None)
+
     def capture(self, buf: DecodeBuffers, cache: PagedKvCache) -> torch.cuda.CUDAGraph:
         """The whole step as one CUDA graph (warm once outside the capture first)."""
         stream = torch.cuda.Stream(self.device)

@@ -380,6 +380,30 @@ def test_quantized_embedding_gathers_and_dequantises_bit_exact(vocab, hidden, n,
     ctx.device_status(None)
 
 
+def test_decoder_health_check_reports_a_bad_token_id_and_clears():
+    """`LlamaDecoder.check_health` is the step-level reader of the device status word: a token id beyond the vocabulary
+    is skipped on the device, reported once as SCR_E_ARG, and the next check is clean."""
+    import torch
+    from scratchy_b200 import _lib, decode
+    cfg = decode.LlamaConfig(hidden=256, n_layers=1, n_q_heads=4, n_kv_heads=2, head_dim=64, intermediate=512,
+                             vocab=1024, rope_theta=10000.0)
+    dec = decode.LlamaDecoder(cfg, decode.synthetic_checkpoint(cfg, seed=2), "cuda:0", max_pos=64)
+    cache = decode.PagedKvCache(cfg, 8, 4, "cuda:0")
+    buf = dec.buffers(1, 8)
+    buf.block_table.copy_(i32_dev(np.arange(8, dtype=np.uint32).reshape(1, 8)))
+    for tok, bad in ((5, False), (cfg.vocab + 3, True), (7, False)):
+        buf.ids.copy_(i32_dev(np.array([tok], np.uint32)))
+        buf.positions.copy_(i32_dev(np.array([2], np.uint32)))
+        buf.slot_mapping.copy_(i32_dev(np.array([2], np.uint32)))
+        buf.seq_used_k.copy_(i32_dev(np.array([3], np.uint32)))
+        dec.step(buf, cache)
+        if bad:
+            with pytest.raises(_lib.ScratchyCudaError) as e:
+                dec.check_health()
+            assert e.value.name == "SCR_E_ARG"
+        dec.check_health()
+
+
 def test_decode_step_with_a_tied_quantized_embedding():
     """A checkpoint whose `model.embed_tokens` is quantized and that has no `lm_head`: the embedding gathers from, and the
     vocabulary head multiplies with, one buffer."""
