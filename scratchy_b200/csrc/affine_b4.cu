@@ -759,8 +759,13 @@ struct AffineFwd {
 // 1.150 ms, the largest shape alone 5.66 against 5.81 us); only where independent matvecs run on parallel streams and
 // overlap their neighbours' tails is 1 ahead (790 against 856 us for the 196 linears on two graph branches); 2 loses in both
 // settings.  At 8 tokens, where every lane reads its own activation row, 1 is 2 % faster.  So: 3 up to 4 tokens, 1 above
-// (the two-tile kernel for 9..16 tokens has no registers to spare).
-static int affine_gemv_u(int M) { return M <= 4 ? 3 : 1; }
+// (the two-tile kernel for 9..16 tokens has no registers to spare) — except for a matrix whose row-blocks fit the GPU in one
+// round at three CTAs per SM but not at two (the fused q|k|v of Llama-3.2-3B: 320 row-blocks for 296 or 444 slots): there
+// two dozen CTAs of the two-per-SM form would run a second row-block while the rest idle.
+static int affine_gemv_u(int M, int rb_real, int sms) {
+    if (M > 4) return 1;
+    return (rb_real > 2 * sms && rb_real <= 3 * sms) ? 1 : 3;
+}
 
 template <int MT, int U, bool NORM, int GS = 1, bool GROUP = false>
 static int32_t affine_gemv_launch_u(scr_ctx* ctx, const uint8_t* packed, const uint16_t* x, uint16_t* y, int M, int N,
@@ -815,7 +820,7 @@ static int32_t affine_gemv_launch(scr_ctx* ctx, const uint8_t* packed, const uin
         if (f.norm_gain) return scr_fail(ctx, SCR_E_UNSUPPORTED, "norm-in end: not built for groups of 32 (run the norm on its own)");
         return affine_gemv_launch_u<MT, 1, false, 2>(ctx, packed, x, y, M, N, K, f, stream);
     }
-    const int u = affine_gemv_u(M);
+    const int u = affine_gemv_u(M, f.grp ? f.grp_rb : scr_ceil_div(N, 16), ctx->sm_count);
     if (f.grp) {
         if (f.gs == 2 || f.norm_gain) return scr_fail(ctx, SCR_E_UNSUPPORTED, "a group launch is built for groups of 64 and 128 without the norm-in end");
         if (u == 3) return affine_gemv_launch_u<1, 3, false, 1, true>(ctx, packed, x, y, M, N, K, f, stream);
