@@ -316,21 +316,62 @@ __device__ __forceinline__ uint32_t gemv_pack2(float lo, float hi) {
     const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&p);
 }
+constexpr int GEMV_NORM_REG_VECS = 4;     // vectors of 8 a thread keeps in registers: rows up to 8192 wide are read once
+// The gain vectors this thread will use (load-time constants: fetched before the dependency wait, hidden under it).
+__device__ __forceinline__ void gemv_norm_gain_load(const GemvExtra& ex, int K, uint4 (&gv)[GEMV_NORM_REG_VECS]) {
+    const int nv = K >> 3;
+#pragma unroll
+    for (int i = 0; i < GEMV_NORM_REG_VECS; ++i) {
+        const int v = threadIdx.x + i * GEMV_CWARPS * 32;
+        gv[i] = v < nv ? *reinterpret_cast<const uint4*>(ex.norm_gain + v * 8) : make_uint4(0, 0, 0, 0);
+    }
+}
+__device__ __forceinline__ uint4 gemv_norm_scale8(const uint4& xv, const uint4& gvec, float inv, float offset) {
+    float f[8], w8[8];
+    gemv_unpack8(xv, f);
+    gemv_unpack8(gvec, w8);
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float g0 = offset != 0.f ? __fadd_rn(w8[2 * j], offset) : w8[2 * j];
+        const float g1 = offset != 0.f ? __fadd_rn(w8[2 * j + 1], offset) : w8[2 * j + 1];
+        o[j] = gemv_pack2(__fmul_rn(__fmul_rn(f[2 * j], inv), g0), __fmul_rn(__fmul_rn(f[2 * j + 1], inv), g1));
+    }
+    return make_uint4(o[0], o[1], o[2], o[3]);
+}
 // The norm-in end: the 256 consumer threads normalise the M activation rows into shared memory with the arithmetic AND
 // the summation order of the stand-alone RMSNorm kernel (thread t sums the squares of vectors t, t + 256, .. in order,
 // a shuffle tree per warp, the eight warp sums in warp order; out = bf16((x * inv_rms) * (gain + offset))), so the
 // matvec sees the very bits that kernel would have stored (golden: crates/targets/metal/src/cpu_golden.rs:25-37).
 __device__ __forceinline__ void gemv_norm_rows(const uint16_t* __restrict__ x, const GemvExtra& ex, int M, int K, uint8_t* xs,
-                                               float* red8) {
+                                               float* red8, const uint4 (&gv)[GEMV_NORM_REG_VECS]) {
+    constexpr int T = GEMV_CWARPS * 32;
     const int tid = threadIdx.x, nv = K >> 3;
+    const bool in_regs = nv <= GEMV_NORM_REG_VECS * T;           // block-uniform
     for (int m = 0; m < M; ++m) {
         const uint16_t* xr = x + (size_t)m * K;
         float ss = 0.f;
-        for (int v = tid; v < nv; v += GEMV_CWARPS * 32) {
-            float f[8];
-            gemv_unpack8(tape_ld_v4(xr + v * 8), f);
+        uint4 xv[GEMV_NORM_REG_VECS];
+        if (in_regs) {
+            // one trip to L2 per row: the vectors stay in registers between the sum and the scaling
 #pragma unroll
-            for (int j = 0; j < 8; ++j) ss = __fadd_rn(ss, __fmul_rn(f[j], f[j]));
+            for (int i = 0; i < GEMV_NORM_REG_VECS; ++i)
+                if (tid + i * T < nv) xv[i] = tape_ld_v4(xr + (tid + i * T) * 8);
+#pragma unroll
+            for (int i = 0; i < GEMV_NORM_REG_VECS; ++i)
+                if (tid + i * T < nv) {
+                    float f[8];
+                    gemv_unpack8(xv[i], f);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) ss = __fadd_rn(ss, __fmul_rn(f[j], f[j]));
+                }
+        } else {
+            for (int v = tid; v < nv; v += T) {
+                float f[8];
+                gemv_unpack8(tape_ld_v4(xr + v * 8), f);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) ss = __fadd_rn(ss, __fmul_rn(f[j], f[j]));
+            }
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
@@ -342,18 +383,13 @@ __device__ __forceinline__ void gemv_norm_rows(const uint16_t* __restrict__ x, c
         for (int w = 0; w < GEMV_CWARPS; ++w) total += red8[w];
         const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, float(K)), ex.norm_eps)));
         uint4* dst = reinterpret_cast<uint4*>(xs + (size_t)m * K * 2);
-        for (int v = tid; v < nv; v += GEMV_CWARPS * 32) {
-            float f[8], w8[8];
-            gemv_unpack8(tape_ld_v4(xr + v * 8), f);
-            gemv_unpack8(*reinterpret_cast<const uint4*>(ex.norm_gain + v * 8), w8);
-            uint32_t o[4];
+        if (in_regs) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float g0 = ex.norm_offset != 0.f ? __fadd_rn(w8[2 * j], ex.norm_offset) : w8[2 * j];
-                const float g1 = ex.norm_offset != 0.f ? __fadd_rn(w8[2 * j + 1], ex.norm_offset) : w8[2 * j + 1];
-                o[j] = gemv_pack2(__fmul_rn(__fmul_rn(f[2 * j], inv), g0), __fmul_rn(__fmul_rn(f[2 * j + 1], inv), g1));
-            }
-            dst[v] = make_uint4(o[0], o[1], o[2], o[3]);
+            for (int i = 0; i < GEMV_NORM_REG_VECS; ++i)
+                if (tid + i * T < nv) dst[tid + i * T] = gemv_norm_scale8(xv[i], gv[i], inv, ex.norm_offset);
+        } else {
+            for (int v = tid; v < nv; v += T)
+                dst[v] = gemv_norm_scale8(tape_ld_v4(xr + v * 8), *reinterpret_cast<const uint4*>(ex.norm_gain + v * 8), inv, ex.norm_offset);
         }
     }
     gemv_consumer_sync();                                        // every row is in shared memory
@@ -569,9 +605,11 @@ affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __rest
         } else {
             trailer_flag = *reinterpret_cast<const volatile unsigned int*>(packed + (size_t)RB * KC * R::kBlockBytes);
         }
+        uint4 norm_gv[GEMV_NORM_REG_VECS];
+        if (NORM) gemv_norm_gain_load(ex, K, norm_gv);
         asm volatile("griddepcontrol.wait;" ::: "memory");        // x (and y's previous readers) are settled
         const uint32_t xs_base = ring_base + R::kBytes;
-        if (NORM) gemv_norm_rows(x, ex, M, K, gemv_ring + R::kBytes, norm_red);
+        if (NORM) gemv_norm_rows(x, ex, M, K, gemv_ring + R::kBytes, norm_red, norm_gv);
         const bool check = trailer_flag != 0;
         if (check)
             gemv_consumer<MT, SPLIT_CLUSTER, true, U, NORM, GS, GROUP>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, out_f32, ex, xs_base, status,
