@@ -148,7 +148,15 @@ int32_t scr_linear_affine_b4_silu_mul(scr_ctx* ctx, const void* packed, const ui
  *   bias, scale         sum + bias[n], then * scale, in f32 before the one rounding (scale 0 is read as 1)
  *   residual            y is the residual stream: y <- bf16(y + bf16(sum)), the bits of the separate add
  *                       (`fused_add_rmsnorm`'s residual, cpu_golden.rs:171-200)
- *   silu_pairs          the gate/up pairing (N = fused rows, y is [M, N/2]); excludes bias, scale and residual */
+ *   silu_pairs          the gate/up pairing (N = fused rows, y is [M, N/2]); excludes bias, scale and residual
+ *   norm_row_scale      with `norm_gain`, which arithmetic the norm-in end uses.  0: the normalised row is formed and rounded
+ *                       to bf16 exactly as `scr_rmsnorm_bf16` stores it, then dotted — the bits of the two separate operators,
+ *                       at the price of every CTA finishing the row's sum of squares before its first product.  Non-zero: the
+ *                       reference matvec's own form (crates/targets/metal/tests/affine_qmv_ends_test.rs:6-9, "dots x (.) gain
+ *                       and scales the row by 1 / rms(x), so it skips the normed row's rounding"): the dot runs over
+ *                       bf16(x * (gain + offset)) and the finished f32 sum is multiplied by 1 / sqrt(mean(x^2) + eps) before
+ *                       the bias — as close to the exact W . rmsnorm(x) as the norm followed by the matvec is (the reference
+ *                       test's bound: one rounding of the output plus 2 ulp of the row's sum of |terms|), not its bits. */
 typedef struct scr_qmv_ends {
     const uint16_t* norm_gain;     /* [K] bf16 or NULL */
     float norm_eps;
@@ -157,6 +165,7 @@ typedef struct scr_qmv_ends {
     float scale;
     int32_t residual;
     int32_t silu_pairs;
+    int32_t norm_row_scale;
 } scr_qmv_ends;
 int32_t scr_linear_affine_b4_ends(scr_ctx* ctx, const void* packed, const uint16_t* x_bf16, int32_t M,
                                   int32_t N, int32_t K, int32_t group, const scr_qmv_ends* ends,

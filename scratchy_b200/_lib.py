@@ -95,7 +95,7 @@ SIGNATURES = {
 class QmvEnds(ctypes.Structure):
     """`scr_qmv_ends` of include/scratchy_cuda.h."""
     _fields_ = [("norm_gain", _vp), ("norm_eps", ctypes.c_float), ("norm_gain_offset", ctypes.c_float), ("bias", _vp),
-                ("scale", ctypes.c_float), ("residual", _i32), ("silu_pairs", _i32)]
+                ("scale", ctypes.c_float), ("residual", _i32), ("silu_pairs", _i32), ("norm_row_scale", _i32)]
 
 
 class TapeLinear(ctypes.Structure):

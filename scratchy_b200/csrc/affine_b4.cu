@@ -283,6 +283,9 @@ struct GemvExtra {
     const uint16_t* norm_gain;   // [K] bf16 or null: x is an RMSNorm's INPUT, this its gain
     float norm_eps, norm_offset; // rmsnorm(x, gain + offset)
     float scale;                 // multiplies the sum after the bias (1 = none)
+    int norm_row_scale;          // norm-in in the reference's own arithmetic: the dot runs over bf16(x * (gain + offset)) and the
+                                 //   finished row is scaled by 1 / rms(x) (0: the normalised row is rounded first, as the
+                                 //   stand-alone RMSNorm stores it)
 };
 // Several independent linears that read the SAME activations (q, k, v; gate, up), run by ONE launch: the launch's row-block
 // space is the matrices' row-blocks one after the other, and a row-block finds its matrix, its packed rows and its output
@@ -395,6 +398,69 @@ __device__ __forceinline__ void gemv_norm_rows(const uint16_t* __restrict__ x, c
     gemv_consumer_sync();                                        // every row is in shared memory
 }
 
+// Norm-in as the reference's matvec does it (crates/targets/metal/tests/affine_qmv_ends_test.rs:6-9: "dots x ⊙ gain and scales
+// the row by 1 / rms(x), so it skips the normed row's rounding"): the consumer threads stage bf16(x * (gain + offset)) in shared
+// memory and leave each row's sum of squares, per warp, in `sq`; nothing waits for the sum before the first MMA — the thread
+// that stores an output multiplies its finished sum by 1 / sqrt(mean(x^2) + eps) (`gemv_row_inv`).  One trip to L2 for up
+// to 1024 vectors of 8 (x and gain fetched together), one barrier.
+__device__ __forceinline__ void gemv_norm_rows_scaled(const uint16_t* __restrict__ x, const GemvExtra& ex, int M, int K, uint8_t* xs,
+                                                      float (*sq)[GEMV_CWARPS]) {
+    constexpr int T = GEMV_CWARPS * 32, S = 4;
+    const int tid = threadIdx.x, nv = K >> 3, total = M * nv;    // x is [M][K] without padding: vector f is row f / nv
+    uint4* dst = reinterpret_cast<uint4*>(xs);
+    for (int base = 0; base < total; base += S * T) {
+        uint4 xv[S], gv[S];
+        int row[S];
+#pragma unroll
+        for (int i = 0; i < S; ++i) {
+            const int f = base + tid + i * T;
+            row[i] = f < total ? f / nv : -1;
+            if (f < total) {
+                xv[i] = tape_ld_v4(x + (size_t)f * 8);
+                gv[i] = *reinterpret_cast<const uint4*>(ex.norm_gain + (f - row[i] * nv) * 8);
+            }
+        }
+        float sqv[S];
+#pragma unroll
+        for (int i = 0; i < S; ++i) {
+            sqv[i] = 0.f;
+            if (row[i] >= 0) {
+                float f8[8], w8[8];
+                gemv_unpack8(xv[i], f8);
+                gemv_unpack8(gv[i], w8);
+                uint32_t o[4];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) sqv[i] = __fadd_rn(sqv[i], __fmul_rn(f8[j], f8[j]));
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float g0 = ex.norm_offset != 0.f ? __fadd_rn(w8[2 * j], ex.norm_offset) : w8[2 * j];
+                    const float g1 = ex.norm_offset != 0.f ? __fadd_rn(w8[2 * j + 1], ex.norm_offset) : w8[2 * j + 1];
+                    o[j] = gemv_pack2(__fmul_rn(f8[2 * j], g0), __fmul_rn(f8[2 * j + 1], g1));
+                }
+                dst[base + tid + i * T] = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+        }
+        // a thread's vectors may lie in different rows: per row, its share in slot order, then a fixed shuffle tree
+        for (int m = 0; m < M; ++m) {
+            float a = 0.f;
+#pragma unroll
+            for (int i = 0; i < S; ++i) a = __fadd_rn(a, row[i] == m ? sqv[i] : 0.f);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, o));
+            if ((tid & 31) == 0) sq[m][tid >> 5] = base == 0 ? a : __fadd_rn(sq[m][tid >> 5], a);
+        }
+    }
+    gemv_consumer_sync();                                        // the staged rows and the sums are in shared memory
+}
+// 1 / rms of token `tok`'s row from the per-warp sums (warp order), for the thread that stores that token's outputs.
+__device__ __forceinline__ float gemv_row_inv(const float (*sq)[GEMV_CWARPS], int tok, int M, int K, float eps) {
+    const int m = min(tok, M - 1);
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < GEMV_CWARPS; ++w) t = __fadd_rn(t, sq[m][w]);
+    return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, float(K)), eps)));
+}
+
 // The plain ends of one finished (row, token) sum: bias, scale, then bf16 / f32 / add into the residual stream.
 // GEMV_OUT_RESIDUAL_ADD: y IS the residual stream and receives bf16(y + bf16(sum)) — the bits the separate add produces from the
 // matvec's bf16 output (the residual end of `QmvEnds` with the roundings of `fused_add_rmsnorm`, cpu_golden.rs:171-200).
@@ -437,7 +503,7 @@ __device__ __forceinline__ void gemv_consumer(const uint16_t* __restrict__ x, ui
                                               int out_f32, const GemvExtra& ex, uint32_t xs_base, int* __restrict__ status, uint32_t ring_base, uint32_t full_base,
                                               uint32_t empty_base, float (*red)[GEMV_CWARPS][32][MT * 4],
                                               float (*cl_part)[16][MT * 8], const GemvEnds& ends, float (*sq_s)[16][16],
-                                              const GemvGroup& grp) {
+                                              const GemvGroup& grp, const float (*norm_sq)[GEMV_CWARPS]) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     float cta_sq = 0.f;                        // RESIDUAL_NORM: thread tok's sum of squares over this CTA's row-blocks
@@ -448,6 +514,12 @@ __device__ __forceinline__ void gemv_consumer(const uint16_t* __restrict__ x, ui
     for (int mt = 0; mt < MT; ++mt) xrow[mt] = x + (size_t)min(mt * 8 + g, M - 1) * K;
 
     using R = GemvRing<U, GS>;
+    // norm-in, row-scale form: 1 / rms of the token whose outputs this thread stores (the same token for every row-block)
+    float row_inv = 1.0f;
+    if (NORM && !SPLIT_CLUSTER && ex.norm_row_scale && threadIdx.x < 32 * MT * 4) {
+        const int ln0 = threadIdx.x / (MT * 4), idx0 = threadIdx.x % (MT * 4);
+        row_inv = gemv_row_inv(norm_sq, (idx0 >> 2) * 8 + (ln0 & 3) * 2 + (idx0 & 1), M, K, ex.norm_eps);
+    }
     uint32_t slot = 0, phase = 0;              // ring position and phase of the next stage
     int it = 0;
     for (int rb = blockIdx.x; rb < rb_real; rb += gridDim.x, ++it) {
@@ -509,6 +581,7 @@ __device__ __forceinline__ void gemv_consumer(const uint16_t* __restrict__ x, ui
             float total = 0.f;
 #pragma unroll
             for (int wdx = 0; wdx < GEMV_CWARPS; ++wdx) total += red[buf][wdx][ln][idx];
+            if (NORM && !SPLIT_CLUSTER) total *= row_inv;
             if (SPLIT_CLUSTER) {
                 if (tok < M) gemv_st_cluster_rank0_f32(&cl_part[sp][row][tok], total);
             } else if (out_f32 == GEMV_OUT_SILU_PAIRS) {
@@ -542,6 +615,7 @@ affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __rest
                       GemvExtra ex, int* __restrict__ status, GemvEnds ends, GemvGroup grp) {
     extern __shared__ __align__(128) uint8_t gemv_ring[];          // [stages][8 * U blocks], then (NORM) the normalised rows [M][K] bf16
     __shared__ float norm_red[GEMV_CWARPS];
+    __shared__ float norm_sq[NORM ? 8 : 1][GEMV_CWARPS];          // norm-in, row-scale form: sums of squares [token][warp]
     __shared__ float sq_s[2][16][16];                              // RESIDUAL_NORM: squares of the stored residuals [token][row]
     using R = GemvRing<U, GS>;
     __shared__ __align__(8) uint64_t full_bar[R::kStages];
@@ -606,17 +680,20 @@ affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __rest
             trailer_flag = *reinterpret_cast<const volatile unsigned int*>(packed + (size_t)RB * KC * R::kBlockBytes);
         }
         uint4 norm_gv[GEMV_NORM_REG_VECS];
-        if (NORM) gemv_norm_gain_load(ex, K, norm_gv);
+        if (NORM && !ex.norm_row_scale) gemv_norm_gain_load(ex, K, norm_gv);
         asm volatile("griddepcontrol.wait;" ::: "memory");        // x (and y's previous readers) are settled
         const uint32_t xs_base = ring_base + R::kBytes;
-        if (NORM) gemv_norm_rows(x, ex, M, K, gemv_ring + R::kBytes, norm_red, norm_gv);
+        if (NORM) {
+            if (ex.norm_row_scale) gemv_norm_rows_scaled(x, ex, M, K, gemv_ring + R::kBytes, norm_sq);
+            else gemv_norm_rows(x, ex, M, K, gemv_ring + R::kBytes, norm_red, norm_gv);
+        }
         const bool check = trailer_flag != 0;
         if (check)
             gemv_consumer<MT, SPLIT_CLUSTER, true, U, NORM, GS, GROUP>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, out_f32, ex, xs_base, status,
-                                                            ring_base, full_base, empty_base, red, cl_part, ends, sq_s, grp);
+                                                            ring_base, full_base, empty_base, red, cl_part, ends, sq_s, grp, norm_sq);
         else
             gemv_consumer<MT, SPLIT_CLUSTER, false, U, NORM, GS, GROUP>(x, y, M, N, K, kc_lo, kc_hi, nstage, rb_real, split, sp, out_f32, ex, xs_base, status,
-                                                             ring_base, full_base, empty_base, red, cl_part, ends, sq_s, grp);
+                                                             ring_base, full_base, empty_base, red, cl_part, ends, sq_s, grp, norm_sq);
     }
 
     if (SPLIT_CLUSTER) {
@@ -628,6 +705,8 @@ affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __rest
         const int row = (ln >> 2) + (((idx & 3) >> 1) ? 8 : 0);
         const int tok = (idx >> 2) * 8 + (ln & 3) * 2 + (idx & 1);
         const int n = blockIdx.x * 16 + row;
+        // norm-in, row-scale form: every CTA of the cluster staged the whole rows, so rank 0 holds the sums of squares
+        const float row_inv = (NORM && ex.norm_row_scale && sp == 0 && e < SLOTS) ? gemv_row_inv(norm_sq, tok, M, K, ex.norm_eps) : 1.0f;
         if (out_f32 == GEMV_OUT_RESIDUAL_NORM) {
             if (sp != 0) return;                   // the cluster's CTA 0 owns the row-block's output (block-uniform exit)
             if (e < 256) sq_s[0][e >> 4][e & 15] = 0.f;
@@ -635,6 +714,7 @@ affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __rest
             if (e < SLOTS) {
                 float s = 0.f;
                 for (int r = 0; r < split; ++r) s += cl_part[r][row][tok];
+                if (NORM) s *= row_inv;
                 sq_s[0][tok][row] = gemv_residual_update(s, tok, M, n, N, ends);
             }
             __syncthreads();
@@ -647,6 +727,7 @@ affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __rest
         } else if (sp == 0 && e < SLOTS && out_f32 == GEMV_OUT_SILU_PAIRS) {
             float s = 0.f;
             for (int r = 0; r < split; ++r) s += cl_part[r][row][min(tok, MT * 8 - 1)];
+            if (NORM) s *= row_inv;
             gemv_store_silu_pair(s, idx, tok, M, blockIdx.x * 8 + (ln >> 2), N >> 1, y);
         } else if (GROUP && sp == 0 && e < SLOTS) {
             const GemvGroupPick gp = gemv_group_pick(grp, blockIdx.x);
@@ -659,6 +740,7 @@ affine_b4_gemv_kernel(const uint8_t* __restrict__ packed, const uint16_t* __rest
         } else if (sp == 0 && e < SLOTS && tok < M && n < N) {
             float s = 0.f;
             for (int r = 0; r < split; ++r) s += cl_part[r][row][tok];
+            if (NORM) s *= row_inv;
             gemv_store_plain(s, out_f32, ex, y, (size_t)tok * N + n, n);
         }
     }
@@ -781,6 +863,7 @@ struct AffineFwd {
     const uint16_t* bias = nullptr;          // the linear's own bias [N] (bf16), added in f32 before the one rounding
     const uint16_t* norm_gain = nullptr;     // norm-in: x is an RMSNorm's input, this its gain [K]
     float norm_eps = 0.f, norm_offset = 0.f;
+    int norm_row_scale = 0;                  // norm-in in the reference's arithmetic (see GemvExtra)
     float scale = 1.0f;                      // multiplies the sum after the bias
     const GemvEnds* ends = nullptr;          // GEMV_OUT_RESIDUAL_NORM only
     int gs = 1;                              // (scale, bias) entries per row and block, log2: set from the group size by affine_forward
@@ -843,7 +926,7 @@ static int32_t affine_gemv_launch_u(scr_ctx* ctx, const uint8_t* packed, const u
         if ((size_t)(16 + grid_x * 16) * sizeof(float) > SCR_ENDS_SCRATCH_BYTES)
             return scr_fail(ctx, SCR_E_WORKSPACE, "residual + norm epilogue: %d CTAs exceed the scratch", grid_x);
     }
-    const GemvExtra ex = {f.bias, f.norm_gain, f.norm_eps, f.norm_offset, f.scale};
+    const GemvExtra ex = {f.bias, f.norm_gain, f.norm_eps, f.norm_offset, f.scale, f.norm_gain ? f.norm_row_scale : 0};
     const GemvGroup grp = f.grp ? *f.grp : GemvGroup{};
     e = cudaLaunchKernelEx(&cfg, kernel, packed, x, y, M, N, K, g.RB, g.KC, rb_real, split, f.out_mode, ex, ctx->dev_status, ends, grp);
     if (e != cudaSuccess) return scr_fail(ctx, SCR_E_CUDA, "affine_b4_gemv launch: %s", cudaGetErrorString(e));
@@ -1003,6 +1086,7 @@ extern "C" int32_t scr_linear_affine_b4_ends(scr_ctx* ctx, const void* packed, c
     f.norm_gain = ends->norm_gain;
     f.norm_eps = ends->norm_eps;
     f.norm_offset = ends->norm_gain_offset;
+    f.norm_row_scale = ends->norm_row_scale != 0;
     f.scale = ends->scale == 0.f ? 1.0f : ends->scale;
     if (ends->silu_pairs && ends->residual) return scr_fail(ctx, SCR_E_ARG, "the gate/up pairing and the residual end exclude each other");
     f.out_mode = ends->residual ? GEMV_OUT_RESIDUAL_ADD : (ends->silu_pairs ? GEMV_OUT_SILU_PAIRS : GEMV_OUT_BF16);

@@ -332,20 +332,28 @@ class LlamaDecoder:
     """Random-init or checkpoint-loaded Llama decoder whose every linear is MLX affine int4 g64."""
 
     def __init__(self, cfg: LlamaConfig, checkpoint, device, max_pos: int = 4096, fuse_residual_norm: bool = False,
-                 fuse_rope: bool = True, fuse_ends: bool = False):
+                 fuse_rope: bool = True, fuse_ends: bool = False, exact_norm_in: bool = False, fuse_residual: bool = True):
         """`checkpoint`: a `GpuWeights` (e.g. `CheckpointWeights.from_dir(...)`) or a dict of host / device
         tensors with the HF Llama names.  `fuse_rope`: run RoPE + cache append inside the attention launch where
         the cache geometry allows it (the new token's slot is then taken from block_table / seq_used_k, which a
         decode step keeps consistent with slot_mapping).  `fuse_ends`: for the few tokens whose normalised rows fit the
         matvec's shared memory, run every RMSNorm inside the matvec that consumes it and every residual add inside the
-        matvec that produces its summand (the reference's `QmvEnds`): five launches per layer instead of seven, the
-        same bits."""
+        matvec that produces its summand (the reference's `QmvEnds`): five launches per layer instead of seven.  The
+        residual adds keep the bits of the separate operator; the norm-in end runs the reference matvec's own arithmetic
+        (the dot over `x * gain`, the row scaled by `1 / rms(x)`: as close to the exact product as norm-then-matvec, not
+        its bits) unless `exact_norm_in` asks for the rounded normalised row of the separate RMSNorm (slower: every
+        CTA then finishes the row's sum of squares before its first product).  `fuse_residual` (up to 16 tokens, when
+        `fuse_ends` is off): the o and down projections add into the residual stream themselves (the residual end alone,
+        the bits of the separate add) and the norms run as plain RMSNorm launches — the same number of launches as with
+        `fused_add_rmsnorm`, each norm reading one row instead of two and no intermediate projection output."""
         if not torch.cuda.is_available():
             raise _lib.ScratchyCudaError(-5, "LlamaDecoder needs a CUDA device (there is no CPU path)")
         self.cfg, self.device = cfg, torch.device(device)
         self.fuse_residual_norm = fuse_residual_norm
         self.fuse_rope = fuse_rope
         self.fuse_ends = fuse_ends
+        self.exact_norm_in = exact_norm_in
+        self.fuse_residual = fuse_residual
         dev = self.device
         gw = checkpoint if isinstance(checkpoint, GpuWeights) else GpuWeights({k: _to_device(v, dev)
                                                                               for k, v in checkpoint.items()})
@@ -420,11 +428,14 @@ class LlamaDecoder:
             embed(buf.ids, self.embed_table, out=buf.residual)
         ends = (self.fuse_ends and not self.fuse_residual_norm and
                 AffineQuantLinear.norm_in_supported(buf.batch, cfg.hidden))
+        row_scale = not self.exact_norm_in
+        resid_end = self.fuse_residual and not ends and not self.fuse_residual_norm and buf.batch <= 16
         if not ends:
             rmsnorm(buf.residual, self.layers[0].input_norm, cfg.rms_eps, out=buf.normed)
         for i, layer in enumerate(self.layers):
             if ends:
-                layer.qkv.forward_ends(buf.residual, buf.qkv, norm_gain=layer.input_norm, norm_eps=cfg.rms_eps)
+                layer.qkv.forward_ends(buf.residual, buf.qkv, norm_gain=layer.input_norm, norm_eps=cfg.rms_eps,
+                                       norm_row_scale=row_scale)
             else:
                 self._linear(layer.qkv, buf.normed, buf.qkv, buf)
             q, k, v = buf.qkv[:, :qd], buf.qkv[:, qd:qd + kd], buf.qkv[:, qd + kd:]
@@ -441,8 +452,15 @@ class LlamaDecoder:
             if ends:
                 # residual += o(attn); act = silu(gate) * up of rmsnorm(residual); residual += down(act)
                 layer.o.forward_ends(buf.attn, buf.residual, residual=True)
-                layer.gate_up.forward_ends(buf.residual, buf.act, norm_gain=layer.post_norm, norm_eps=cfg.rms_eps, silu_pairs=True)
+                layer.gate_up.forward_ends(buf.residual, buf.act, norm_gain=layer.post_norm, norm_eps=cfg.rms_eps, silu_pairs=True,
+                                           norm_row_scale=row_scale)
                 layer.down.forward_ends(buf.act, buf.residual, residual=True)
+            elif resid_end:
+                layer.o.forward_ends(buf.attn, buf.residual, residual=True)
+                rmsnorm(buf.residual, layer.post_norm, cfg.rms_eps, out=buf.normed)
+                layer.gate_up.forward_silu_mul(buf.normed, out=buf.act, scratch=buf.gate_up, workspace=buf.workspace)
+                layer.down.forward_ends(buf.act, buf.residual, residual=True)
+                rmsnorm(buf.residual, nxt, cfg.rms_eps, out=buf.normed)
             elif self.fuse_residual_norm:
                 layer.o.forward_residual_rmsnorm(buf.attn, buf.residual, layer.post_norm, cfg.rms_eps, buf.normed,
                                                  buf.ends_scratch, delta=buf.delta, workspace=buf.workspace)
@@ -456,7 +474,8 @@ class LlamaDecoder:
                 self._linear(layer.down, buf.act, buf.delta, buf)
                 fused_add_rmsnorm(buf.residual, buf.delta, nxt, cfg.rms_eps, out=buf.normed)
         if ends:
-            self.lm_head.forward_ends(buf.residual, buf.logits, norm_gain=self.final_norm, norm_eps=cfg.rms_eps)
+            self.lm_head.forward_ends(buf.residual, buf.logits, norm_gain=self.final_norm, norm_eps=cfg.rms_eps,
+                                      norm_row_scale=row_scale)
         else:
             self._linear(self.lm_head, buf.normed, buf.logits, buf)
         argmax(buf.logits, out=buf.next_ids)

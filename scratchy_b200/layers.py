@@ -301,17 +301,20 @@ class AffineQuantLinear:
         return outs
 
     def forward_ends(self, x: torch.Tensor, out: torch.Tensor, norm_gain: Optional[torch.Tensor] = None, norm_eps: float = 0.0,
-                     norm_gain_offset: float = 0.0, scale: float = 1.0, residual: bool = False, silu_pairs: bool = False) -> torch.Tensor:
+                     norm_gain_offset: float = 0.0, scale: float = 1.0, residual: bool = False, silu_pairs: bool = False,
+                     norm_row_scale: bool = False) -> torch.Tensor:
         """The matvec with the reference's `QmvEnds` around it (`scr_linear_affine_b4_ends`, up to 16 tokens): RMSNorm on the
         input as it is loaded (`norm_gain`: x is the norm's INPUT), the layer's bias, a scale, and either the add into the
-        residual stream `out` (`residual`) or the gate/up pairing (`silu_pairs`, a matrix built by `load_rows_interleave8`)."""
+        residual stream `out` (`residual`) or the gate/up pairing (`silu_pairs`, a matrix built by `load_rows_interleave8`).
+        `norm_row_scale`: the reference matvec's own norm-in arithmetic (dot over `x * gain`, the row scaled by `1 / rms(x)`;
+        crates/targets/metal/tests/affine_qmv_ends_test.rs:6-9) instead of the bits of the separate RMSNorm."""
         x2 = x.reshape(-1, self.in_features).contiguous()
         M = int(x2.shape[0])
         dev = x2.device
         if silu_pairs and not getattr(self, "pairs8", False):
             raise ValueError("silu_pairs needs a gate/up matrix built by load_rows_interleave8")
         ends = _lib.QmvEnds(_ptr(norm_gain), float(norm_eps), float(norm_gain_offset), _ptr(self.linear_bias), float(scale),
-                            int(residual), int(silu_pairs))
+                            int(residual), int(silu_pairs), int(norm_row_scale))
         ctx = _lib.context(_dev_index(dev))
         ctx.check(_lib.lib().scr_linear_affine_b4_ends(ctx.handle, _ptr(self.packed), _ptr(x2), M, self.out_features, self.in_features,
                                                        self.group_size, ctypes.byref(ends), _ptr(out), _stream(dev)))

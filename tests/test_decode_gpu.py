@@ -612,16 +612,21 @@ def test_llama_3b_layer_at_real_geometry_operator_by_operator(batch):
 @pytest.mark.parametrize("batch", [1, 2, 3])
 def test_matvec_ends_give_the_bits_of_the_separate_operators(batch):
     """The reference's `QmvEnds` on the decode path: RMSNorm inside the matvec that consumes it, the residual add inside the
-    matvec that produces its summand.  A decoder that uses them (five launches per layer) and one that runs the norms and
-    adds as kernels of their own (seven) must produce the same logits, residual stream and next token, bit for bit, over
-    two steps at the Llama-3.2-3B hidden size; the ends are also checked one by one against the operators they replace."""
+    matvec that produces its summand.  A decoder that uses them (five launches per layer) with the norm-in end in its
+    rounded-row form and one that runs the norms and adds as kernels of their own (seven) must produce the same logits,
+    residual stream and next token, bit for bit, over two steps at the Llama-3.2-3B hidden size, and so must the default
+    decoder (the residual end alone, the norms as plain RMSNorm launches); with the norm-in end in the
+    reference matvec's own arithmetic (the row scaled by 1 / rms(x) after the dot: no rounded normalised row) the step agrees
+    within the step tolerance.  The ends are also checked one by one against the operators they replace."""
     import torch
     from scratchy_b200 import _lib, decode
     cfg = decode.LlamaConfig(hidden=3072, n_layers=2, n_q_heads=24, n_kv_heads=8, head_dim=128, intermediate=8192,
                              vocab=2048, rope_theta=500000.0)
     ck = decode.synthetic_checkpoint(cfg, seed=70 + batch)
-    a = decode.LlamaDecoder(cfg, ck, "cuda:0", max_pos=256, fuse_ends=True)
-    b = decode.LlamaDecoder(cfg, ck, "cuda:0", max_pos=256, fuse_ends=False)
+    a = decode.LlamaDecoder(cfg, ck, "cuda:0", max_pos=256, fuse_ends=True, exact_norm_in=True)
+    b = decode.LlamaDecoder(cfg, ck, "cuda:0", max_pos=256, fuse_ends=False, fuse_residual=False)
+    c = decode.LlamaDecoder(cfg, ck, "cuda:0", max_pos=256, fuse_ends=True)
+    d = decode.LlamaDecoder(cfg, ck, "cuda:0", max_pos=256)         # the default: the residual end alone, plain norms
     bs, max_blocks = 16, 8
     nblk = batch * max_blocks
     rng = np.random.default_rng(batch)
@@ -630,7 +635,7 @@ def test_matvec_ends_give_the_bits_of_the_separate_operators(batch):
     ids = rng.integers(0, cfg.vocab, size=batch).astype(np.uint32)
     ctx_len = rng.integers(20, 100, size=batch)
     outs = []
-    for dec in (a, b):
+    for dec in (a, b, c, d):
         cache = decode.PagedKvCache(cfg, nblk, bs, "cuda:0")
         for i in range(cfg.n_layers):
             cache.k[i].copy_(bf16_dev(hist[2 * i]))
@@ -648,14 +653,18 @@ def test_matvec_ends_give_the_bits_of_the_separate_operators(batch):
             dec.step(buf, cache)
             torch.cuda.synchronize()
             res.append((bits_of(buf.logits).copy(), bits_of(buf.residual).copy(), buf.next_ids.cpu().numpy().copy()))
-            cur = res[-1][2].view(np.uint32).copy()
+            # every decoder is fed the separate operators' tokens, so that the steps stay comparable
+            cur = (res[-1][2] if dec is not c else outs[1][0][step][2]).view(np.uint32).copy()
         outs.append((res, _lib.context(0).launch_count() - n0))
-    (ra, la), (rb, lb) = outs
-    assert la < lb, f"the ends must save launches ({la} against {lb})"
+    (ra, la), (rb, lb), (rc, lc), (rd, ld) = outs
+    assert la < lb and lc == la and ld == lb, f"the ends must save launches ({la}, {lc} against {lb}, {ld})"
     for step in range(2):
         assert np.array_equal(ra[step][1], rb[step][1]), f"step {step}: residual stream"
         assert np.array_equal(ra[step][0], rb[step][0]), f"step {step}: logits"
         assert np.array_equal(ra[step][2], rb[step][2]), f"step {step}: next token"
+        assert all(np.array_equal(rd[step][j], rb[step][j]) for j in range(3)), f"step {step}: the residual end alone"
+        assert rel_l2(rc[step][1], rb[step][1]) <= STEP_REL_L2_TOL, f"step {step}: residual stream, row-scale norm-in"
+        assert rel_l2(rc[step][0], rb[step][0]) <= STEP_REL_L2_TOL, f"step {step}: logits, row-scale norm-in"
     _lib.context(0).device_status(None)
 
 
@@ -696,6 +705,113 @@ def test_each_matvec_end_against_the_operator_it_replaces(N, K, M):
     got_all = linb.forward_ends(x, bf16_dev(res0), norm_gain=gain, norm_eps=1e-5, scale=0.5, residual=True)
     torch.cuda.synchronize()
     assert torch.equal(got_all.view(torch.int16), want_all.view(torch.int16)), "all ends"
+
+
+def _unit(rng, shape):
+    return rng.uniform(-1.0, 1.0, size=shape)
+
+
+@pytest.mark.parametrize("K,N,offset,f16_scales", [(3072, 1024, 0.0, False), (3072, 1024, 1.0, False), (3072, 1024, 0.0, True),
+                                                   (896, 136, 0.0, False), (128, 256, 0.0, False), (2048, 7, 0.0, False)])
+@pytest.mark.parametrize("M", [1, 2, 3, 5])
+def test_norm_in_is_as_close_to_the_exact_normed_product_as_the_norm_then_the_matvec(K, N, offset, f16_scales, M):
+    """The reference's own test of its normalising matvec, at its shapes, value distributions and bound
+    (crates/targets/metal/tests/affine_qmv_ends_test.rs:86-93 cases, :152-186 weights, :278-296 inputs and the exact
+    product, :361-377 the bound, :421-447 the three arms; the wide variant :449-470 for 2 to 5 rows): against the exact
+    `W . rmsnorm(x, gain + offset)` in f64 over the un-rounded decoded weights, every output must lie within one rounding of
+    the output plus 2 ulp of the row's sum of |terms| — for the RMSNorm followed by the plain matvec, for the norm-in end
+    in the reference's arithmetic (row scaled by 1 / rms after the dot) and in the rounded-row form; the plain matvec of
+    the raw x must fall outside, or the bound could not see a missing norm.  Inputs are seeded draws from the reference
+    test's distributions."""
+    import torch
+    from scratchy_b200 import AffineQuantLinear, decode
+    from util import u32_dev
+    if not AffineQuantLinear.norm_in_supported(M, K):
+        pytest.skip("the normalised rows of this case exceed the end's shared memory")
+    rng = np.random.default_rng(K * 7 + N + 1000 * M + (1 if f16_scales else 0) + int(offset * 10))
+    words = rng.integers(0, 2 ** 32, size=(N, K // 8), dtype=np.uint64).astype(np.uint32)
+    sc = (0.5 + np.abs(_unit(rng, (N, K // 64)))) * 0.02 / 15.0
+    bi = -sc * 7.5 * (1.0 + 0.1 * _unit(rng, (N, K // 64)))
+    if f16_scales:
+        s_st, b_st = sc.astype(np.float16), bi.astype(np.float16)
+        s_val, b_val = s_st.astype(np.float64), b_st.astype(np.float64)
+        s_dev, b_dev = torch.from_numpy(s_st).cuda(), torch.from_numpy(b_st).cuda()
+    else:
+        s_st, b_st = rbits(sc), rbits(bi)
+        s_val, b_val = bf16_to_f32(s_st).astype(np.float64), bf16_to_f32(b_st).astype(np.float64)
+        s_dev, b_dev = bf16_dev(s_st), bf16_dev(b_st)
+    codes = ((words[:, :, None] >> (4 * np.arange(8, dtype=np.uint32))[None, None, :]) & 0xF).reshape(N, K).astype(np.float64)
+    decoded = np.repeat(s_val, 64, axis=1) * codes + np.repeat(b_val, 64, axis=1)
+    x_bits = rbits(4.0 * _unit(rng, (M, K)))
+    g_bits = rbits(1.0 - offset + 0.25 * _unit(rng, K))
+    x, gain = bf16_to_f32(x_bits).astype(np.float64), bf16_to_f32(g_bits).astype(np.float64)
+    eps = 1e-5
+    inv = 1.0 / np.sqrt((x * x).sum(axis=1, keepdims=True) / K + np.float64(np.float32(eps)))
+    xn = x * inv * (gain + offset)[None, :]
+    exact = xn @ decoded.T                                           # [M, N]
+    scale = np.abs(xn) @ np.abs(decoded).T                           # the sum of the terms' magnitudes
+    ulp = 2.0 ** -8
+    bound = ulp * np.abs(exact) + 2.0 * ulp * scale
+
+    lin = AffineQuantLinear.from_tensors(u32_dev(words), s_dev, b_dev, 64, 4)
+    xd, gd = bf16_dev(x_bits), bf16_dev(g_bits)
+    def out():
+        return torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    def within(t):
+        torch.cuda.synchronize()
+        return bool(np.all(np.abs(bf16_to_f32(bits_of(t)).astype(np.float64) - exact) <= bound))
+    # the separate operator takes its gain as stored: fold the offset into a gain of its own (exact for these values or not,
+    # the bound has room for one rounding of the gain)
+    gain_plus = bf16_dev(rbits(gain + offset)) if offset else gd
+    assert within(lin.forward_ends(decode.rmsnorm(xd, gain_plus, eps), out())), "the norm, then the matvec"
+    assert within(lin.forward_ends(xd, out(), norm_gain=gd, norm_eps=eps, norm_gain_offset=offset, norm_row_scale=True)), \
+        "the normalising matvec, the reference's arithmetic"
+    assert within(lin.forward_ends(xd, out(), norm_gain=gd, norm_eps=eps, norm_gain_offset=offset)), \
+        "the normalising matvec, rounded-row form"
+    assert not within(lin.forward_ends(xd, out())), "the bound accepts the raw matvec: it cannot see a missing norm"
+
+
+def test_row_scale_norm_in_with_every_other_end():
+    """Norm-in in the reference's arithmetic together with the bias, a scale and the residual add, and with the gate/up
+    pairing: each equals the same call without the later ends followed by the separate operator (the order of the ends is
+    norm, dot, bias, scale, residual), bit for bit."""
+    import torch
+    from scratchy_b200 import AffineQuantLinear, decode
+    from util import u32_dev
+    N, K, M = 3072, 3072, 2
+    rng = np.random.default_rng(synth.seed_for("ends-rs", N, K, M))
+    w, s, b = synth.affine_int4_weights(N, K, 64, synth.seed_for("endsw-rs", N, K))
+    bias = rbits(rng.normal(0, 1, N))
+    linb = AffineQuantLinear.from_tensors(u32_dev(w), bf16_dev(s), bf16_dev(b), 64, 4, linear_bias=bf16_dev(bias))
+    x = bf16_dev(rbits(rng.standard_normal((M, K)) * 3.0))
+    gain = bf16_dev(rbits(1.0 + 0.1 * rng.standard_normal(K)))
+    res0 = rbits(rng.standard_normal((M, N)))
+    kw = dict(norm_gain=gain, norm_eps=1e-5, norm_row_scale=True, scale=0.5)
+    yn = linb.forward_ends(x, torch.empty((M, N), dtype=torch.bfloat16, device="cuda"), **kw)
+    want = (bf16_dev(res0).float() + yn.float()).to(torch.bfloat16)
+    got = linb.forward_ends(x, bf16_dev(res0), residual=True, **kw)
+    torch.cuda.synchronize()
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16)), "norm-in, bias, scale, residual"
+    # against the oracle's f32 sums over the staged row bf16(x * gain): (acc * inv_rms + bias) * scale
+    xf, gf = bf16_to_f32(bits_of(x)), bf16_to_f32(bits_of(gain))
+    staged = rbits(xf * gf[None, :])
+    _, acc = oracle.affine_qmm_t_b4(w.view(np.uint8).reshape(-1), s, b, staged, M, N, K, 64, want_f32=True)
+    inv = 1.0 / np.sqrt((xf.astype(np.float64) ** 2).sum(axis=1, keepdims=True) / K + 1e-5)
+    want_y = rbits((acc * inv + bf16_to_f32(bias)[None, :]) * 0.5)
+    assert rel_l2(bits_of(yn), want_y) <= REL_L2_TOL
+    assert np.mean(bits_of(yn) == want_y) > 0.97, "the same roundings as the restatement up to the sums' order"
+    # the gate/up pairing
+    pair = AffineQuantLinear.from_tensors(u32_dev(w), bf16_dev(s), bf16_dev(b), 64, 4)
+    pair.pairs8 = True                                              # rows read as runs of 8 gate, 8 up
+    act = pair.forward_ends(x, torch.empty((M, N // 2), dtype=torch.bfloat16, device="cuda"), norm_gain=gain, norm_eps=1e-5,
+                            norm_row_scale=True, silu_pairs=True)
+    full = pair.forward_ends(x, torch.empty((M, N), dtype=torch.bfloat16, device="cuda"), norm_gain=gain, norm_eps=1e-5,
+                             norm_row_scale=True)
+    fr = full.view(M, N // 16, 2, 8)
+    want_act = decode.silu_mul(fr[:, :, 0, :].reshape(M, N // 2).contiguous(), fr[:, :, 1, :].reshape(M, N // 2).contiguous())
+    torch.cuda.synchronize()
+    assert rel_l2(bits_of(act), bits_of(want_act)) <= REL_L2_TOL
+    assert np.mean(bits_of(act) == bits_of(want_act)) > 0.99
 
 
 def test_decode_ops_against_the_committed_fixture():
