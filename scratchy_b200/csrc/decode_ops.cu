@@ -915,10 +915,13 @@ cudaError_t attention_launch(const uint16_t* q, long long ld_q, const uint16_t* 
     while (nsplit > 1 && (long long)batch * num_kv_heads * nsplit > 2LL * sm_count) nsplit /= 2;
     const int table_cap = max_blocks_per_seq / nsplit + 2;
     const size_t fixed = part + size_t((table_cap + 1) & ~1) * 4 + 2 * ATT_MAX_STAGES * sizeof(uint64_t) + 1024 + 128;
-    // alone on its SM (the grid does not oversubscribe the machine): 8 consumer warps and a deep ring;
-    // otherwise two CTAs per SM with 4 consumer warps each.  Every warp owns stages / warps ring stages
+    // alone on its SM: 8 consumer warps and a deep ring; otherwise 4 consumer warps and about half an SM's shared
+    // memory.  The big CTA (48 K registers, ~200 KB) shares its SM with no CTA of the kernels before and after it in
+    // the stream, so it pays only while the grid leaves most SMs to them: up to half the SMs.  (Llama-3.2-3B decode
+    // step, measured inside the step: batch 1, 64 CTAs — 1.074 ms with the big CTA, 1.116 with the small one; batch 2,
+    // 128 CTAs — 1.341 ms with the big one, 1.193 with the small one.)  Every warp owns stages / warps ring stages
     // and wants at least two of them, so that its next block loads while it works on the current one.
-    const bool alone = (long long)batch * num_kv_heads * nsplit <= sm_count;
+    const bool alone = 2LL * batch * num_kv_heads * nsplit <= sm_count;
     const size_t budget = alone ? ATT_SMEM_BUDGET_ALONE : ATT_SMEM_BUDGET;
     int nwarps = alone ? 8 : 4, spw = 0;
     for (; nwarps >= 2; nwarps /= 2) {
