@@ -90,3 +90,30 @@ def test_init_without_a_gpu_reports_cuda_error():
     assert not h.value
     with pytest.raises(_lib.ScratchyCudaError):
         _lib.Context(0)
+
+
+def test_struct_mirrors_have_the_layout_the_c_compiler_gives(tmp_path):
+    """The ctypes mirrors of the header's structs (`scr_qmv_ends`, `scr_tape_linear`) against the C compiler's own sizes
+    and field offsets: a field added to the header and not to the mirror (or in another place) would shift every
+    argument after it."""
+    import shutil
+    import subprocess
+    cc = shutil.which("gcc") or shutil.which("cc")
+    if cc is None:
+        pytest.skip("no C compiler")
+    fields = {"scr_qmv_ends": [f[0] for f in _lib.QmvEnds._fields_], "scr_tape_linear": [f[0] for f in _lib.TapeLinear._fields_]}
+    lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "scratchy_cuda.h"', 'int main(void) {']
+    for s, fs in fields.items():
+        lines.append(f'  printf("{s} %zu\\n", sizeof({s}));')
+        for f in fs:
+            lines.append(f'  printf("{s}.{f} %zu\\n", offsetof({s}, {f}));')
+    lines += ['  return 0;', '}']
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.check_call([cc, "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)])
+    got = dict(line.split() for line in subprocess.check_output([str(exe)], text=True).splitlines())
+    for s, cls in (("scr_qmv_ends", _lib.QmvEnds), ("scr_tape_linear", _lib.TapeLinear)):
+        assert int(got[s]) == ctypes.sizeof(cls), s
+        for f in fields[s]:
+            assert int(got[f"{s}.{f}"]) == getattr(cls, f).offset, f"{s}.{f}"
